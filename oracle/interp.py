@@ -1,0 +1,678 @@
+"""TEST INFRASTRUCTURE — CPU oracle for the plugin's hot path. Never imported
+by the product; only tests, the smoke check and the bench's CPU-baseline leg
+use it.
+
+A NumPy (plus torch-CPU for convolution) interpreter of StableHLO modules in
+text form. It restates, op by op, the semantics the reference's handlers
+implement on top of MLX (file:line below are paths inside the reference
+project), which are the StableHLO semantics jaxlib's CPU backend implements —
+the backend the reference's own tests compare against
+(tests/test_ops.py:108-161, atol = rtol = 1e-5, integers exact).
+
+PARITY PINNING: the reference stores no golden vectors for this path and
+cannot run on Linux; jaxlib is not installable here. The interpreter is
+pinned against (1) the literal expectations of the reference's raw-MLIR test
+(tests/test_ops.py:216-281, arcsin / sinh decompositions vs numpy), (2) the
+literal expectations in tests/test_control_flow_compile.py:114-133, and (3)
+PyTorch autograd twins of the benchmark models (oracle/twins.py), an
+independent implementation of the same mathematics. Everything else is
+"parity unpinned" by reference data.
+
+Values are numpy arrays; bf16 is carried as float32 rounded to bf16 after
+every op. Floating-point reductions accumulate in float64.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+from . import mlir_text as mt
+from .mlir_text import Block, Module, Op, TType, attr_i64s, attr_int, enum_word, struct_fields
+
+FLOATS = ("f32", "bf16", "f16", "f64")
+
+
+def round_bf16(a: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    r = (u + (0x7FFF + ((u >> 16) & 1))) & np.uint32(0xFFFF0000)
+    nan = (u & 0x7FFFFFFF) > 0x7F800000
+    r = np.where(nan, u | 0x00400000, r).astype(np.uint32)
+    return r.view(np.float32)
+
+
+def cast(a, dt: str) -> np.ndarray:
+    """Round/wrap `a` into element type `dt`."""
+    a = np.asarray(a)
+    if dt == "bf16":
+        return round_bf16(a.astype(np.float32))
+    if dt == "token":
+        return np.zeros((), np.bool_)
+    return a.astype(mt.np_dtype(dt), copy=False)
+
+
+# --------------------------------------------------------------------------
+# elementwise rules
+# --------------------------------------------------------------------------
+
+def _bits(dt): return np.dtype(mt.np_dtype(dt)).itemsize * 8
+
+
+def _int_div(a, b):
+    """Truncating integer division (src/pjrt_plugin/ops/arithmetic.cc:492-513);
+    division by zero gives -1 / all-ones, INT_MIN / -1 gives INT_MIN, as XLA."""
+    with np.errstate(all="ignore"):
+        bz = b == 0
+        bs = np.where(bz, 1, b)
+        if np.issubdtype(a.dtype, np.signedinteger):
+            ovf = (a == np.iinfo(a.dtype).min) & (bs == -1)
+            bs = np.where(ovf, 1, bs)
+            q = np.abs(a.astype(object)) // np.abs(bs.astype(object))
+            q = np.where((a < 0) != (bs < 0), -q, q).astype(a.dtype) if a.size else a
+            q = np.where(ovf, a, q)
+            return np.where(bz, a.dtype.type(-1), q).astype(a.dtype)
+        q = a // bs
+        return np.where(bz, np.iinfo(a.dtype).max, q).astype(a.dtype)
+
+
+def _int_rem(a, b):
+    """C remainder: sign follows the dividend (arithmetic.cc:45-83); x % 0 = x."""
+    with np.errstate(all="ignore"):
+        bz = b == 0
+        bs = np.where(bz, 1, b)
+        if np.issubdtype(a.dtype, np.signedinteger):
+            bs = np.where((a == np.iinfo(a.dtype).min) & (bs == -1), 1, bs)
+            r = np.fmod(a, bs)
+        else:
+            r = a % bs
+        return np.where(bz, a, r).astype(a.dtype)
+
+
+def _shift(kind):
+    def f(a, b):
+        """Out-of-range amounts: logical shifts give 0, arithmetic gives the
+        sign fill (src/pjrt_plugin/mlx_executable.cc:272-304, arithmetic.cc:113-144)."""
+        nb = a.dtype.itemsize * 8
+        bu = b.astype(np.int64) if np.issubdtype(b.dtype, np.signedinteger) else b.astype(np.uint64)
+        oor = (bu < 0) | (bu >= nb)
+        sh = np.where(oor, 0, bu).astype(a.dtype)
+        if kind == "l":
+            return np.where(oor, 0, np.left_shift(a, sh)).astype(a.dtype)
+        if kind == "rl":
+            ua = a.view(np.dtype(f"uint{nb}"))
+            return np.where(oor, 0, np.right_shift(ua, sh.view(ua.dtype))).astype(ua.dtype).view(a.dtype)
+        sa = a.view(np.dtype(f"int{nb}"))
+        fill = np.where(sa < 0, -1, 0).astype(sa.dtype)
+        return np.where(oor, fill, np.right_shift(sa, sh.view(sa.dtype))).astype(sa.dtype).view(a.dtype)
+    return f
+
+
+def _sign(a):
+    if np.issubdtype(a.dtype, np.floating):
+        return np.where(np.isnan(a), a, np.sign(a)).astype(a.dtype)      # NaN propagates (arithmetic.cc:515-531)
+    return np.sign(a).astype(a.dtype)
+
+
+def _round_afz(a):
+    return (np.sign(a) * np.floor(np.abs(a) + 0.5)).astype(a.dtype)
+
+
+def _popcnt(a):
+    u = a.view(np.dtype(f"uint{a.dtype.itemsize * 8}"))
+    out = np.zeros(a.shape, np.uint64)
+    v = u.astype(np.uint64)
+    for _ in range(a.dtype.itemsize * 8):
+        out += v & 1
+        v >>= 1
+    return out.astype(a.dtype)
+
+
+def _clz(a):
+    nb = a.dtype.itemsize * 8
+    v = a.view(np.dtype(f"uint{nb}")).astype(np.uint64)
+    out = np.full(a.shape, nb, np.int64)
+    for k in range(nb):
+        out = np.where((v >> np.uint64(k)) != 0, nb - 1 - k, out)
+    return out.astype(a.dtype)
+
+
+def _total_order_key(a):
+    """Sign-magnitude key giving -NaN < -inf < ... < -0 < +0 < ... < +inf < +NaN
+    (arithmetic.cc:236-283)."""
+    nb = a.dtype.itemsize * 8
+    it = np.dtype(f"int{nb}")
+    i = np.ascontiguousarray(a).view(it)
+    mask = (i >> (nb - 1)) & it.type((1 << (nb - 1)) - 1)
+    return i ^ mask
+
+
+_UNARY = {
+    "exponential": np.exp, "log": np.log, "sqrt": np.sqrt, "rsqrt": lambda a: 1.0 / np.sqrt(a),
+    "negate": np.negative, "abs": np.abs, "floor": np.floor, "ceil": np.ceil, "sine": np.sin, "cosine": np.cos,
+    "tanh": np.tanh, "tan": np.tan, "logistic": lambda a: 1.0 / (1.0 + np.exp(-a)), "sign": _sign,
+    "log_plus_one": np.log1p, "exponential_minus_one": np.expm1, "cbrt": np.cbrt,
+    "round_nearest_even": np.rint, "round_nearest_afz": _round_afz, "popcnt": _popcnt,
+    "count_leading_zeros": _clz,
+}
+_BINARY_F = {
+    "add": np.add, "subtract": np.subtract, "multiply": np.multiply, "divide": np.divide,
+    "maximum": np.maximum, "minimum": np.minimum, "power": np.power, "remainder": np.fmod, "atan2": np.arctan2,
+}
+_BINARY_I = {
+    "add": np.add, "subtract": np.subtract, "multiply": np.multiply, "divide": _int_div,
+    "maximum": np.maximum, "minimum": np.minimum, "remainder": _int_rem,
+    "and": np.bitwise_and, "or": np.bitwise_or, "xor": np.bitwise_xor,
+    "shift_left": _shift("l"), "shift_right_logical": _shift("rl"), "shift_right_arithmetic": _shift("ra"),
+}
+_CMP = {"EQ": np.equal, "NE": np.not_equal, "LT": np.less, "LE": np.less_equal, "GT": np.greater,
+        "GE": np.greater_equal}
+
+
+def _int_pow(a, b):
+    out = np.ones_like(a)
+    base, e = a.copy(), b.astype(np.int64).copy()
+    neg = e < 0
+    e = np.where(neg, 0, e)
+    with np.errstate(all="ignore"):
+        while np.any(e > 0):
+            out = np.where(e & 1, out * base, out)
+            base = base * base
+            e >>= 1
+    # negative exponent: 1 for base 1, +-1 for base -1, else 0
+    negv = np.where(a == 1, 1, np.where(a == -1, np.where(b & 1, -1, 1), 0)).astype(a.dtype)
+    return np.where(neg, negv, out).astype(a.dtype)
+
+
+class Interp:
+    def __init__(self, module: Module | str, collective=None, partition_id: int = 0, conv_f64: bool = False,
+                 wide: bool = False):
+        self.m = mt.parse_module(module) if isinstance(module, str) else module
+        self.collective = collective          # callable(list[np.ndarray]) -> list (sum over partitions)
+        self.partition_id = partition_id
+        self.conv_f64 = conv_f64 or wide
+        self.wide = wide
+
+    def cast(self, a, dt: str) -> np.ndarray:
+        """Element-type rounding; with `wide` every f32 value is carried in
+        float64 (ground truth for ill-conditioned comparisons)."""
+        if self.wide and dt == "f32":
+            return np.asarray(a).astype(np.float64, copy=False)
+        return cast(a, dt)
+
+    # ---- entry ----------------------------------------------------------
+    def run(self, args, func: str = "main") -> list:
+        f = self.m.funcs[func]
+        assert len(args) == len(f.args), (len(args), len(f.args))
+        env = {}
+        for (n, t), a in zip(f.args, args):
+            a = np.asarray(a)
+            assert tuple(a.shape) == tuple(t.shape), (n, a.shape, t.shape)
+            env[n] = self.cast(a, t.dtype)
+        return self.block(f.body, env)
+
+    def block(self, blk: Block, env: dict) -> list:
+        for op in blk.ops:
+            if op.name in ("func.return", "stablehlo.return"):
+                return [env[o] for o in op.operands]
+            outs = self.op(op, env)
+            for n, t, v in zip(op.results, op.result_types, outs):
+                v = np.asarray(v)
+                if t.dtype != "token":
+                    assert tuple(v.shape) == tuple(t.shape), (op.name, v.shape, t.shape)
+                env[n] = self.cast(v, t.dtype)
+        return []
+
+    def region(self, blk: Block, env: dict, args) -> list:
+        e = dict(env)
+        for (n, t), a in zip(blk.args, args):
+            e[n] = a
+        return self.block(blk, e)
+
+    # ---- dispatch ----------------------------------------------------------
+    def op(self, op: Op, env: dict) -> list:
+        name = op.name.split(".", 1)[1] if "." in op.name else op.name
+        x = [env[o] for o in op.operands]
+        rt = op.result_types[0] if op.result_types else None
+        fn = getattr(self, "op_" + name, None)
+        if fn is not None:
+            return fn(op, x, env)
+        if name in _UNARY and len(x) == 1:
+            a = x[0]
+            with np.errstate(all="ignore"):
+                if rt.dtype in FLOATS:
+                    w = a.astype(np.float64) if rt.dtype != "f64" else a
+                    return [_UNARY[name](w)]
+                return [_UNARY[name](a)]
+        if name in _BINARY_F or name in _BINARY_I:
+            a, b = x
+            with np.errstate(all="ignore"):
+                if rt.dtype in FLOATS:
+                    if rt.dtype == "bf16":
+                        return [_BINARY_F[name](a.astype(np.float32), b.astype(np.float32))]
+                    return [_BINARY_F[name](a, b)]
+                if rt.dtype == "i1":
+                    return [{"and": np.logical_and, "or": np.logical_or, "xor": np.logical_xor,
+                             "maximum": np.logical_or, "minimum": np.logical_and, "add": np.logical_or,
+                             "multiply": np.logical_and}[name](a, b)]
+                if name == "power":
+                    return [_int_pow(a, b)]
+                return [_BINARY_I[name](a, b)]
+        raise NotImplementedError(f"oracle: unsupported op {op.name}")
+
+    # ---- elementwise specials -------------------------------------------------
+    def op_constant(self, op, x, env):
+        return [mt.dense_array(op.attrs["value"])]
+
+    def op_not(self, op, x, env):
+        a = x[0]
+        return [np.logical_not(a) if a.dtype == np.bool_ else np.invert(a)]     # arithmetic.cc:99-110
+
+    def op_is_finite(self, op, x, env):
+        return [np.isfinite(x[0])]
+
+    def op_convert(self, op, x, env):
+        a, dt = x[0], op.result_types[0].dtype
+        with np.errstate(all="ignore"):
+            if dt == "i1":
+                return [a != 0]
+            if a.dtype.kind == "f" and dt not in FLOATS:
+                info = np.iinfo(mt.np_dtype(dt))
+                t = np.trunc(np.nan_to_num(a.astype(np.float64), nan=0.0, posinf=float(info.max), neginf=float(info.min)))
+                t = np.clip(t, float(info.min), float(info.max))
+                out = np.where(t >= float(info.max), info.max, t.astype(np.int64 if info.min < 0 else np.uint64))
+                return [out.astype(mt.np_dtype(dt))]
+            return [a]
+
+    def op_bitcast_convert(self, op, x, env):
+        a, t = x[0], op.result_types[0]
+        src = op_operand_dtype(a)
+        if t.dtype == "bf16" or src == "bf16":
+            raise NotImplementedError("bf16 bitcast")
+        out = np.ascontiguousarray(a).view(mt.np_dtype(t.dtype))
+        return [out.reshape(t.shape)]
+
+    def op_compare(self, op, x, env):
+        a, b = x
+        d = enum_word(op.attrs["comparison_direction"])
+        ct = enum_word(op.attrs["compare_type"]) if "compare_type" in op.attrs else ""
+        if ct == "TOTALORDER" and a.dtype.kind == "f":
+            a, b = _total_order_key(a), _total_order_key(b)
+        return [_CMP[d](a, b)]
+
+    def op_select(self, op, x, env):
+        p, a, b = x
+        return [np.where(p, a, b)]
+
+    def op_clamp(self, op, x, env):
+        lo, a, hi = x                      # (min, operand, max) order, arithmetic.cc:34-43
+        return [np.minimum(np.maximum(a, lo), hi)]
+
+    def op_reduce_precision(self, op, x, env):
+        eb, mb = attr_int(op.attrs["exponent_bits"]), attr_int(op.attrs["mantissa_bits"])
+        a = x[0].astype(np.float32)
+        if eb >= 8 and mb >= 23:
+            return [a]
+        if eb == 8 and mb == 7:
+            return [round_bf16(a)]
+        if eb == 5 and mb == 10:
+            return [a.astype(np.float16).astype(np.float32)]
+        raise NotImplementedError("reduce_precision format")
+
+    def op_erf(self, op, x, env):
+        from scipy.special import erf
+        return [erf(x[0].astype(np.float64))]
+
+    # ---- shape ops ---------------------------------------------------------------
+    def op_broadcast_in_dim(self, op, x, env):
+        t = op.result_types[0]
+        dims = attr_i64s(op.attrs["broadcast_dimensions"])
+        a = x[0]
+        shape = [1] * len(t.shape)
+        for i, d in enumerate(dims):
+            shape[d] = a.shape[i]
+        return [np.broadcast_to(a.reshape(shape), t.shape)]
+
+    def op_reshape(self, op, x, env):
+        return [np.ascontiguousarray(x[0]).reshape(op.result_types[0].shape)]
+
+    def op_transpose(self, op, x, env):
+        return [np.transpose(x[0], attr_i64s(op.attrs["permutation"]))]
+
+    def op_reverse(self, op, x, env):
+        return [np.flip(x[0], tuple(attr_i64s(op.attrs["dimensions"])))]
+
+    def op_iota(self, op, x, env):
+        t = op.result_types[0]
+        d = attr_int(op.attrs["iota_dimension"])
+        shape = [1] * len(t.shape)
+        shape[d] = t.shape[d]
+        return [np.broadcast_to(np.arange(t.shape[d]).reshape(shape), t.shape)]
+
+    def op_concatenate(self, op, x, env):
+        return [np.concatenate(x, axis=attr_int(op.attrs["dimension"]))]
+
+    def op_slice(self, op, x, env):
+        st, li, sd = (attr_i64s(op.attrs[k]) for k in ("start_indices", "limit_indices", "strides"))
+        return [x[0][tuple(slice(s, l, d) for s, l, d in zip(st, li, sd))]]
+
+    def op_pad(self, op, x, env):
+        """Interior padding first, then (possibly negative) edges
+        (src/pjrt_plugin/ops/slice.cc:14-52,202-276)."""
+        a, pv = x
+        lo, hi, it = (attr_i64s(op.attrs[k]) for k in ("edge_padding_low", "edge_padding_high", "interior_padding"))
+        t = op.result_types[0]
+        out = np.full(t.shape, pv, dtype=a.dtype)
+        src, dst = [], []
+        for d in range(a.ndim):
+            n = a.shape[d]
+            pos = lo[d] + np.arange(n) * (it[d] + 1)
+            ok = (pos >= 0) & (pos < t.shape[d])
+            src.append(np.nonzero(ok)[0]); dst.append(pos[ok])
+        if all(len(s) for s in src) or a.ndim == 0:
+            out[np.ix_(*dst)] = a[np.ix_(*src)]
+        return [out]
+
+    def _starts(self, starts, full, size):
+        """Clamp each start into [0, dim - size] (slice.cc:80-107)."""
+        return [int(min(max(int(s), 0), f - z)) for s, f, z in zip(starts, full, size)]
+
+    def op_dynamic_slice(self, op, x, env):
+        a = x[0]
+        sizes = attr_i64s(op.attrs["slice_sizes"])
+        st = self._starts(x[1:], a.shape, sizes)
+        return [a[tuple(slice(s, s + z) for s, z in zip(st, sizes))]]
+
+    def op_dynamic_update_slice(self, op, x, env):
+        a, u = x[0], x[1]
+        st = self._starts(x[2:], a.shape, u.shape)
+        out = a.copy()
+        out[tuple(slice(s, s + z) for s, z in zip(st, u.shape))] = u
+        return [out]
+
+    # ---- reductions -----------------------------------------------------------------
+    def _simple_body(self, blk: Block):
+        """A body made of one binary op on (acc, value) -> its name."""
+        real = [o for o in blk.ops if o.name != "stablehlo.return"]
+        if len(real) == 1 and len(blk.args) == 2 and set(real[0].operands) == {blk.args[0][0], blk.args[1][0]}:
+            return real[0].name.split(".", 1)[1]
+        return None
+
+    def op_reduce(self, op, x, env):
+        n = len(x) // 2
+        ins, inits = x[:n], x[n:]
+        dims = tuple(attr_i64s(op.attrs["dimensions"]))
+        blk = op.regions[0]
+        kind = self._simple_body(blk) if n == 1 else None
+        a, dt = ins[0], op.result_types[0].dtype
+        with np.errstate(all="ignore"):
+            if kind in ("add", "multiply") and dt in FLOATS:
+                w = a.astype(np.float64)
+                r = w.sum(dims) if kind == "add" else w.prod(dims)
+                r = r + inits[0] if kind == "add" else r * inits[0]
+                return [r]
+            if kind in ("maximum", "minimum") and a.size:
+                f = np.max if kind == "maximum" else np.min
+                r = f(a, axis=dims)
+                return [(np.maximum if kind == "maximum" else np.minimum)(r, inits[0])]
+            if kind in ("add",) and dt not in FLOATS and dt != "i1":
+                return [(a.sum(dims, dtype=a.dtype) + inits[0]).astype(a.dtype)]
+            if kind in ("and", "or") and dt == "i1":
+                r = a.all(dims) if kind == "and" else a.any(dims)
+                return [(np.logical_and if kind == "and" else np.logical_or)(r, inits[0])]
+        # generic: move reduced dims last, flatten, fold pairwise with the body
+        kept = [d for d in range(a.ndim) if d not in dims]
+        perm = kept + list(dims)
+        R = int(np.prod([a.shape[d] for d in dims])) if dims else 1
+        cur = [np.transpose(v, perm).reshape([v.shape[d] for d in kept] + [R]) for v in ins]
+        kshape = cur[0].shape[:-1]
+        while cur[0].shape[-1] > 1:
+            L = cur[0].shape[-1]
+            h = L // 2
+            lo = [c[..., :h] for c in cur]
+            hi = [c[..., h:2 * h] for c in cur]
+            rest = [c[..., 2 * h:] for c in cur]
+            outs = self.region(blk, env, lo + hi)
+            outs = [self.cast(o, t.dtype) for o, t in zip(outs, op.result_types)]
+            cur = [np.concatenate([o, r], axis=-1) for o, r in zip(outs, rest)]
+        if R == 0:
+            return [np.broadcast_to(i, kshape) for i in inits]
+        acc = [c[..., 0] for c in cur]
+        outs = self.region(blk, env, [np.broadcast_to(i, kshape) for i in inits] + acc)
+        return outs
+
+    # ---- contractions -----------------------------------------------------------------
+    def op_dot_general(self, op, x, env):
+        a, b = x
+        f = struct_fields(op.attrs["dot_dimension_numbers"])
+        lb, rb = f.get("lhs_batching_dimensions", []), f.get("rhs_batching_dimensions", [])
+        lc, rc = f.get("lhs_contracting_dimensions", []), f.get("rhs_contracting_dimensions", [])
+        lf = [i for i in range(a.ndim) if i not in lb and i not in lc]
+        rf = [i for i in range(b.ndim) if i not in rb and i not in rc]
+        dt = op.result_types[0].dtype
+        wt = np.float64 if dt in FLOATS else (np.int64 if not dt.startswith("ui") else np.uint64)
+        if dt == "i1":
+            wt = np.int64
+        A = np.transpose(a, lb + lf + lc).astype(wt)
+        B = np.transpose(b, rb + rc + rf).astype(wt)
+        bs = [a.shape[i] for i in lb]
+        m = int(np.prod([a.shape[i] for i in lf])) if lf else 1
+        k = int(np.prod([a.shape[i] for i in lc])) if lc else 1
+        n = int(np.prod([b.shape[i] for i in rf])) if rf else 1
+        nb = int(np.prod(bs)) if bs else 1
+        C = np.matmul(A.reshape(nb, m, k), B.reshape(nb, k, n))
+        C = C.reshape(bs + [a.shape[i] for i in lf] + [b.shape[i] for i in rf])
+        if dt == "i1":
+            C = C != 0
+        return [C]
+
+    def op_convolution(self, op, x, env):
+        """Dilate the input, then pad (negative pad crops), then correlate
+        with the dilated kernel (src/pjrt_plugin/ops/linalg.cc:508-532);
+        batch_group_count folds into feature groups (linalg.cc:339-362)."""
+        import torch
+        lhs, rhs = x
+        dn = op.attrs["dimension_numbers"]
+        inner = dn[dn.index("<") + 1:dn.rindex(">")]
+        ls, rest = inner.split("]x[")
+        rs, os_ = rest.split("]->[")
+        ls, rs, os_ = ([t.strip() for t in s.strip("[] ").split(",")] for s in (ls, rs, os_))
+        nsp = len(ls) - 2
+        assert nsp == 2, "oracle convolution: 2 spatial dims"
+        def get(name, default):
+            return attr_i64s(op.attrs[name]) if name in op.attrs else default
+        stride = get("window_strides", [1] * nsp)
+        ldil = get("lhs_dilation", [1] * nsp)
+        rdil = get("rhs_dilation", [1] * nsp)
+        pad = np.array(mt.dense_array(op.attrs["padding"])).reshape(nsp, 2) if "padding" in op.attrs else np.zeros((nsp, 2), int)
+        G = attr_int(op.attrs.get("feature_group_count", "1"))
+        BG = attr_int(op.attrs.get("batch_group_count", "1"))
+        if "window_reversal" in op.attrs and any(mt.dense_array(op.attrs["window_reversal"]).reshape(-1)):
+            raise NotImplementedError("window_reversal")
+        # to NCHW / OIHW
+        L = np.transpose(lhs, [ls.index("b"), ls.index("f")] + [ls.index(str(s)) for s in range(nsp)])
+        K = np.transpose(rhs, [rs.index("o"), rs.index("i")] + [rs.index(str(s)) for s in range(nsp)])
+        wt = torch.float64 if (self.conv_f64 or op.result_types[0].dtype == "f64") else torch.float32
+        Lt = torch.from_numpy(np.ascontiguousarray(L).astype(np.float64)).to(wt)
+        Kt = torch.from_numpy(np.ascontiguousarray(K).astype(np.float64)).to(wt)
+        if BG > 1:
+            # batch groups: split batch into BG groups, each feeding O/BG output features
+            n, c = Lt.shape[0], Lt.shape[1]
+            Lt = Lt.reshape(BG, n // BG, c, *Lt.shape[2:]).permute(1, 0, 2, 3, 4).reshape(n // BG, BG * c, *Lt.shape[2:])
+            G = BG
+        # lhs dilation
+        if any(d != 1 for d in ldil):
+            n, c, h, w = Lt.shape
+            hd = 0 if h == 0 else (h - 1) * ldil[0] + 1
+            wd = 0 if w == 0 else (w - 1) * ldil[1] + 1
+            Z = torch.zeros((n, c, hd, wd), dtype=wt)
+            Z[:, :, ::ldil[0], ::ldil[1]] = Lt
+            Lt = Z
+        # padding (negative crops)
+        for s in range(nsp):
+            lo, hi = int(pad[s][0]), int(pad[s][1])
+            if lo < 0:
+                Lt = Lt.narrow(2 + s, -lo, Lt.shape[2 + s] + lo); lo = 0
+            if hi < 0:
+                Lt = Lt.narrow(2 + s, 0, Lt.shape[2 + s] + hi); hi = 0
+            if lo or hi:
+                padspec = [0, 0, 0, 0]
+                padspec[(nsp - 1 - s) * 2] = lo; padspec[(nsp - 1 - s) * 2 + 1] = hi
+                Lt = torch.nn.functional.pad(Lt, padspec)
+        out = torch.nn.functional.conv2d(Lt.contiguous(), Kt.contiguous(), None, stride=tuple(stride),
+                                         padding=0, dilation=tuple(rdil), groups=G).numpy()
+        cur = ["b", "f"] + [str(s) for s in range(nsp)]
+        return [np.transpose(out, [cur.index(c) for c in os_])]
+
+    # ---- gather / scatter -------------------------------------------------------------------
+    def op_gather(self, op, x, env):
+        """Per-output-element index arithmetic of stablehlo.gather with clamped
+        starts and batching dims (src/pjrt_plugin/ops/gather_scatter.cc:200-294)."""
+        operand, idx = x
+        f = struct_fields(op.attrs["dimension_numbers"])
+        offset_dims = f.get("offset_dims", [])
+        collapsed = f.get("collapsed_slice_dims", [])
+        obatch = f.get("operand_batching_dims", [])
+        ibatch = f.get("start_indices_batching_dims", [])
+        smap = f.get("start_index_map", [])
+        ivd = f.get("index_vector_dim", idx.ndim)
+        sizes = attr_i64s(op.attrs["slice_sizes"])
+        t = op.result_types[0]
+        out_rank = len(t.shape)
+        batch_dims = [d for d in range(out_rank) if d not in offset_dims]
+        oi = np.indices(t.shape).reshape(out_rank, -1) if t.shape else np.zeros((0, 1), int)
+        nel = oi.shape[1]
+        # batch index into start_indices
+        idx_m = np.moveaxis(idx, ivd, -1) if ivd < idx.ndim else idx[..., None]
+        bidx = tuple(oi[d] for d in batch_dims)
+        starts = idx_m[bidx].astype(np.int64).reshape(nel, -1) if batch_dims else np.broadcast_to(idx_m.reshape(1, -1), (nel, idx_m.size))
+        full = np.zeros((operand.ndim, nel), np.int64)
+        for k, od in enumerate(smap):
+            full[od] = np.clip(starts[:, k], 0, operand.shape[od] - sizes[od])
+        # batching dims: operand batch coordinate = index batch coordinate
+        idx_batch_dims_in_out = [d for d in range(idx.ndim) if d != ivd]
+        for od, ib in zip(obatch, ibatch):
+            pos = idx_batch_dims_in_out.index(ib)
+            full[od] = oi[batch_dims[pos]]
+        window_dims = [d for d in range(operand.ndim) if d not in collapsed and d not in obatch]
+        for k, wd in enumerate(window_dims):
+            full[wd] += oi[offset_dims[k]]
+        return [operand[tuple(full)].reshape(t.shape)]
+
+    def op_scatter(self, op, x, env):
+        """stablehlo.scatter, one operand. Out-of-bounds windows are skipped.
+        Body classification as in gather_scatter.cc:13-53."""
+        operand, idx, upd = x
+        f = struct_fields(op.attrs["scatter_dimension_numbers"])
+        uwd = f.get("update_window_dims", [])
+        iwd = f.get("inserted_window_dims", [])
+        ibd = f.get("input_batching_dims", [])
+        sbd = f.get("scatter_indices_batching_dims", [])
+        sdo = f.get("scatter_dims_to_operand_dims", [])
+        ivd = f.get("index_vector_dim", idx.ndim)
+        kind = self._simple_body(op.regions[0])
+        real = [o for o in op.regions[0].ops if o.name != "stablehlo.return"]
+        if not real:
+            kind = "update"
+        ui = np.indices(upd.shape).reshape(upd.ndim, -1) if upd.shape else np.zeros((0, 1), int)
+        nel = ui.shape[1]
+        scatter_dims = [d for d in range(upd.ndim) if d not in uwd]
+        idx_m = np.moveaxis(idx, ivd, -1) if ivd < idx.ndim else idx[..., None]
+        sidx = tuple(ui[d] for d in scatter_dims)
+        starts = idx_m[sidx].astype(np.int64).reshape(nel, -1) if scatter_dims else np.broadcast_to(idx_m.reshape(1, -1), (nel, idx_m.size))
+        full = np.zeros((operand.ndim, nel), np.int64)
+        for k, od in enumerate(sdo):
+            full[od] = starts[:, k]
+        idx_batch_dims = [d for d in range(idx.ndim) if d != ivd]
+        for od, ib in zip(ibd, sbd):
+            full[od] = ui[scatter_dims[idx_batch_dims.index(ib)]]
+        window_dims = [d for d in range(operand.ndim) if d not in iwd and d not in ibd]
+        # window bounds check uses the window start (whole window must fit)
+        wsize = {wd: upd.shape[uwd[k]] for k, wd in enumerate(window_dims)}
+        ok = np.ones(nel, bool)
+        for d in range(operand.ndim):
+            sz = wsize.get(d, 1)
+            ok &= (full[d] >= 0) & (full[d] + sz <= operand.shape[d])
+        for k, wd in enumerate(window_dims):
+            full[wd] = full[wd] + ui[uwd[k]]
+        tgt = tuple(full[:, ok])
+        vals = upd.reshape(-1)[ok]
+        dt = op.result_types[0].dtype
+        if kind == "add" and dt in FLOATS:
+            acc = operand.astype(np.float64)
+            np.add.at(acc, tgt, vals.astype(np.float64))
+            return [acc]
+        out = operand.copy()
+        if kind == "update":
+            out[tgt] = vals
+        elif kind in ("add", "subtract", "multiply", "maximum", "minimum"):
+            {"add": np.add, "subtract": np.subtract, "multiply": np.multiply, "maximum": np.maximum,
+             "minimum": np.minimum}[kind].at(out, tgt, vals)
+        else:
+            flat_t = np.stack(tgt, 0) if tgt else np.zeros((0, len(vals)), int)
+            for j in range(len(vals)):
+                pos = tuple(flat_t[:, j])
+                out[pos] = self.region(op.regions[0], env, [out[pos], vals[j]])[0]
+        return [out]
+
+    # ---- control flow ----------------------------------------------------------------------------
+    def op_while(self, op, x, env):
+        cur = list(x)
+        cond, body = op.regions
+        it = 0
+        while bool(self.region(cond, env, cur)[0]):
+            cur = self.region(body, env, cur)
+            cur = [self.cast(v, t.dtype) for v, t in zip(cur, op.result_types)]
+            it += 1
+            if it > 10_000_000:
+                raise RuntimeError("oracle while: iteration limit")
+        return cur
+
+    def op_case(self, op, x, env):
+        i = int(x[0])
+        n = len(op.regions)
+        if i < 0 or i >= n:
+            i = n - 1                       # src/pjrt_plugin/ops/control_flow.cc:672-675
+        return self.region(op.regions[i], env, [])
+
+    def op_call(self, op, x, env):
+        callee = op.attrs["callee"].strip().lstrip("@")
+        return Interp(self.m, self.collective, self.partition_id, self.conv_f64, self.wide).run(x, callee)
+
+    def op_composite(self, op, x, env):
+        callee = op.attrs["decomposition"].strip().lstrip("@")
+        return Interp(self.m, self.collective, self.partition_id, self.conv_f64, self.wide).run(x, callee)
+
+    def op_optimization_barrier(self, op, x, env):
+        return list(x)
+
+    def op_create_token(self, op, x, env):
+        return [np.zeros((), np.bool_)]
+
+    def op_after_all(self, op, x, env):
+        return [np.zeros((), np.bool_)]
+
+    def op_custom_call(self, op, x, env):
+        tgt = mt.attr_str(op.attrs["call_target_name"])
+        if tgt in ("Sharding", "SPMDFullToShardShape", "SPMDShardToFullShape"):
+            return [x[0].reshape(op.result_types[0].shape)]         # control_flow.cc:1426-1438
+        raise NotImplementedError(f"oracle: custom_call {tgt}")
+
+    # ---- collectives ---------------------------------------------------------------------------------
+    def op_all_reduce(self, op, x, env):
+        if self.collective is None:
+            return list(x)                  # one partition: identity (src/pjrt_plugin/ops/collectives.cc:41-47)
+        return self.collective(list(x))
+
+    def op_partition_id(self, op, x, env):
+        return [np.uint32(self.partition_id)]
+
+    def op_replica_id(self, op, x, env):
+        return [np.uint32(0)]
+
+
+def op_operand_dtype(a: np.ndarray) -> str:
+    return {np.dtype(v): k for k, v in mt._NPDT.items() if k != "bf16"}[a.dtype]
+
+
+def run_text(text: str, args, **kw) -> list:
+    return Interp(text, **kw).run(args)
