@@ -1,0 +1,213 @@
+/*
+ * b200_core.h — C ABI of the B200 execution core behind the PJRT plugin.
+ *
+ * This is the drop-in boundary for the hot path of the reference plugin
+ * (tillahoffmann/jax-mps): create a client, move host arrays to the device,
+ * compile a StableHLO module, execute it, read results back. Every function
+ * below names the reference entry point it stands in for (paths inside the
+ * reference project). The PJRT veneer (GetPjrtApi function table,
+ * src/pjrt_plugin/pjrt_api.cc:232-400) is a thin adapter over these calls;
+ * it is built only where xla/pjrt/c/pjrt_c_api.h is available.
+ *
+ * Conventions (same as the reference's PJRT layer, pjrt_client.cc:17-31,
+ * pjrt_types.h:137-140):
+ *   - every call returns NULL on success or a heap b200_error* the caller
+ *     frees with b200_error_destroy; no C++ exception crosses the boundary;
+ *   - objects returned through out-parameters are owned by the caller and
+ *     released with the matching *_destroy;
+ *   - all calls are thread-safe; work on a device is stream-ordered.
+ *
+ * One process drives one GPU (data-parallel jobs run one process per GPU and
+ * pass every process the same NCCL unique id); there is no CPU fallback: a
+ * call that needs the GPU fails with B200_FAILED_PRECONDITION when no device
+ * or no CUDA driver is present, and an unsupported operation is a compile
+ * error.
+ */
+#ifndef B200_CORE_H_
+#define B200_CORE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#pragma GCC visibility push(default)
+
+typedef struct b200_client b200_client;
+typedef struct b200_executable b200_executable;
+typedef struct b200_buffer b200_buffer;
+typedef struct b200_event b200_event;
+typedef struct b200_error b200_error;
+
+typedef enum {
+  B200_OK = 0,
+  B200_CANCELLED = 1,
+  B200_UNKNOWN = 2,
+  B200_INVALID_ARGUMENT = 3,
+  B200_NOT_FOUND = 5,
+  B200_RESOURCE_EXHAUSTED = 8,
+  B200_FAILED_PRECONDITION = 9,
+  B200_UNIMPLEMENTED = 12,
+  B200_INTERNAL = 13
+} b200_error_code;
+
+/* Element types (the set the reference maps in PjrtDtypeToMlx, src/pjrt_plugin/mlx_buffer.cc:14-53,
+ * plus F64; complex types are not supported). */
+typedef enum {
+  B200_INVALID = 0,
+  B200_PRED = 1,
+  B200_S8 = 2,
+  B200_S16 = 3,
+  B200_S32 = 4,
+  B200_S64 = 5,
+  B200_U8 = 6,
+  B200_U16 = 7,
+  B200_U32 = 8,
+  B200_U64 = 9,
+  B200_F16 = 10,
+  B200_F32 = 11,
+  B200_F64 = 12,
+  B200_BF16 = 13
+} b200_dtype;
+
+/* ---- errors: PJRT_Error_Destroy / _Message / _GetCode (pjrt_client.cc:17-31) ---- */
+void b200_error_destroy(b200_error* err);
+const char* b200_error_message(const b200_error* err);
+b200_error_code b200_error_get_code(const b200_error* err);
+
+/* ---- client: PJRT_Client_Create (pjrt_client.cc:70-83), MlxClient (mlx_client.cc:19-66) ---- */
+#define B200_NCCL_ID_BYTES 128
+typedef struct {
+  size_t struct_size;
+  int device_ordinal;        /* CUDA device this process drives; -1 = LOCAL_RANK env or 0 */
+  int process_index;         /* rank of this process in the data-parallel job */
+  int num_processes;         /* 1 = single GPU */
+  const char* nccl_unique_id;/* B200_NCCL_ID_BYTES bytes shared by all processes, or NULL when num_processes == 1 */
+  size_t pool_release_threshold; /* bytes kept cached by the stream-ordered pool; 0 = keep everything */
+} b200_client_options;
+
+b200_error* b200_client_create(const b200_client_options* options, b200_client** client);
+b200_error* b200_client_destroy(b200_client* client);                       /* PJRT_Client_Destroy */
+const char* b200_client_platform_name(const b200_client* client);           /* PJRT_Client_PlatformName */
+const char* b200_client_platform_version(const b200_client* client);        /* PJRT_Client_PlatformVersion */
+int b200_client_process_index(const b200_client* client);                   /* PJRT_Client_ProcessIndex */
+int b200_client_device_count(const b200_client* client);                    /* PJRT_Client_Devices: all processes */
+int b200_client_addressable_device_count(const b200_client* client);        /* PJRT_Client_AddressableDevices */
+/* Rank 0 makes the id that every process passes to b200_client_create. */
+b200_error* b200_nccl_unique_id(char out[B200_NCCL_ID_BYTES]);
+
+/* ---- device: pjrt_device.cc:12-147 ---- */
+int b200_device_id(const b200_client* client);                               /* global id == process_index */
+int b200_device_local_hardware_id(const b200_client* client);                /* CUDA ordinal */
+const char* b200_device_kind(const b200_client* client);                     /* "NVIDIA B200" */
+const char* b200_device_debug_string(const b200_client* client);
+typedef struct {
+  size_t struct_size;
+  int64_t bytes_in_use;
+  int64_t peak_bytes_in_use; int peak_bytes_in_use_is_set;
+  int64_t bytes_limit; int bytes_limit_is_set;
+  int64_t pool_bytes; int pool_bytes_is_set;
+  int64_t peak_pool_bytes; int peak_pool_bytes_is_set;
+  int64_t num_allocs; int num_allocs_is_set;
+  int64_t largest_alloc_size; int largest_alloc_size_is_set;
+} b200_memory_stats;
+b200_error* b200_device_memory_stats(b200_client* client, b200_memory_stats* stats);   /* PJRT_Device_MemoryStats */
+
+/* ---- compile: PJRT_Client_Compile (pjrt_client.cc:179-257) ---- */
+typedef struct {
+  size_t struct_size;
+  int num_partitions;        /* 0 = take mhlo.num_partitions from the module */
+  int disable_fusion;        /* one kernel per op (debugging; env B200_NO_FUSE=1 does the same) */
+} b200_compile_options;
+/* `format` is "mlir" (StableHLO text; generic operation form, or custom assembly for common ops). */
+b200_error* b200_client_compile(b200_client* client, const char* code, size_t code_size, const char* format,
+                                const b200_compile_options* options, b200_executable** executable);
+b200_error* b200_executable_destroy(b200_executable* exe);                   /* PJRT_LoadedExecutable_Destroy */
+const char* b200_executable_name(const b200_executable* exe);                /* PJRT_Executable_Name */
+const char* b200_executable_fingerprint(const b200_executable* exe);         /* PJRT_Executable_Fingerprint */
+int b200_executable_num_replicas(const b200_executable* exe);
+int b200_executable_num_partitions(const b200_executable* exe);
+size_t b200_executable_num_args(const b200_executable* exe);
+size_t b200_executable_num_outputs(const b200_executable* exe);              /* PJRT_Executable_NumOutputs */
+/* PJRT_Executable_OutputElementTypes / OutputDimensions; `dims` points at storage owned by the executable. */
+b200_error* b200_executable_output_info(const b200_executable* exe, size_t index, b200_dtype* dtype,
+                                        const int64_t** dims, size_t* num_dims);
+b200_error* b200_executable_arg_info(const b200_executable* exe, size_t index, b200_dtype* dtype,
+                                     const int64_t** dims, size_t* num_dims);
+/* Kernel launches one execution performs (-1 when it depends on data), generated kernel count, arena bytes. */
+int64_t b200_executable_launches_per_execute(const b200_executable* exe);
+int64_t b200_executable_num_kernels(const b200_executable* exe);
+int64_t b200_executable_temp_bytes(const b200_executable* exe);
+/* Text of the kernel plan (what B200_DUMP_PLAN prints); owned by the executable. */
+const char* b200_executable_plan_text(const b200_executable* exe);
+
+/* Host-only compilation (no device needed): parses and plans the module and returns the plan text and
+ * the generated CUDA source as malloc'd strings the caller releases with b200_string_free. With
+ * `validate_kernels` the source is also compiled by NVRTC for sm_100a, so generator mistakes surface as
+ * an error here. Stands in for the reference's IR dump (JAX_MPS_DUMP_OPTIMIZED_IR,
+ * src/pjrt_plugin/stablehlo_parser.cc:210-232), which its fusion tests read. */
+b200_error* b200_compile_to_plan(const char* code, size_t code_size, const b200_compile_options* options,
+                                 int num_processes, int process_index, int validate_kernels, char** plan_text,
+                                 char** cuda_source);
+void b200_string_free(char* s);
+
+/* ---- buffers: PJRT_Client_BufferFromHostBuffer (pjrt_client.cc:267-322), pjrt_buffer.cc:13-188 ---- */
+/* byte_strides may be NULL (dense row-major). `done_with_host_buffer` (may be NULL) becomes ready when
+ * `data` may be reused. */
+b200_error* b200_buffer_from_host(b200_client* client, const void* data, b200_dtype dtype, const int64_t* dims,
+                                  size_t num_dims, const int64_t* byte_strides, b200_buffer** buffer,
+                                  b200_event** done_with_host_buffer);
+/* dst == NULL: only *dst_size is written (bytes needed). Otherwise starts an asynchronous copy; *event
+ * (may be NULL: then the call blocks) is ready when dst holds the data. */
+b200_error* b200_buffer_to_host(b200_buffer* buffer, void* dst, size_t* dst_size, b200_event** event);
+b200_dtype b200_buffer_dtype(const b200_buffer* buffer);
+size_t b200_buffer_num_dims(const b200_buffer* buffer);
+const int64_t* b200_buffer_dims(const b200_buffer* buffer);
+size_t b200_buffer_on_device_size(const b200_buffer* buffer);
+int b200_buffer_device(const b200_buffer* buffer);
+b200_error* b200_buffer_ready_event(b200_buffer* buffer, b200_event** event);   /* PJRT_Buffer_ReadyEvent */
+b200_error* b200_buffer_copy(b200_buffer* buffer, b200_buffer** copy);          /* PJRT_Buffer_CopyToDevice (same device) */
+b200_error* b200_buffer_delete(b200_buffer* buffer);                            /* PJRT_Buffer_Delete: frees device memory */
+int b200_buffer_is_deleted(const b200_buffer* buffer);
+b200_error* b200_buffer_destroy(b200_buffer* buffer);
+/* Raw device address (PJRT_Buffer_UnsafePointer). */
+void* b200_buffer_device_pointer(const b200_buffer* buffer);
+
+/* ---- execute: PJRT_LoadedExecutable_Execute (pjrt_executable.cc:178-258) ---- */
+typedef struct {
+  size_t struct_size;
+  int donate_arguments;      /* honour tf.aliasing_output: a donated argument's storage becomes the result
+                                and the argument buffer is left deleted */
+} b200_execute_options;
+/* `outputs` is a caller-allocated array of b200_executable_num_outputs pointers. `done` (may be NULL)
+ * becomes ready when all outputs are computed. The call returns after enqueueing. */
+b200_error* b200_executable_execute(b200_executable* exe, b200_buffer* const* args, size_t num_args,
+                                    b200_buffer** outputs, b200_event** done, const b200_execute_options* options);
+
+/* ---- events: pjrt_event.cc:101-193 ---- */
+int b200_event_is_ready(b200_event* event);
+b200_error* b200_event_await(b200_event* event);
+b200_error* b200_event_error(b200_event* event);
+typedef void (*b200_event_callback)(b200_error* error, void* user_arg);   /* the callback owns `error` */
+b200_error* b200_event_on_ready(b200_event* event, b200_event_callback callback, void* user_arg);
+b200_error* b200_event_destroy(b200_event* event);
+
+/* Blocks until everything enqueued on the client's streams has finished. */
+b200_error* b200_client_synchronize(b200_client* client);
+/* CUDA stream the client launches on (cudaStream_t), for callers that time with events. */
+void* b200_client_compute_stream(b200_client* client);
+/* Per-step device timing (the reference's MPS_PROFILE counterpart, src/pjrt_plugin/mlx_executable.cc:381-454):
+ * while enabled every plan step is bracketed by CUDA events on the compute stream and executions
+ * synchronise at their end. b200_client_profile_report returns a malloc'd JSON array of
+ * {"kind","key","ms","count"} accumulated since the last report (release with b200_string_free). */
+b200_error* b200_client_set_profiling(b200_client* client, int enabled);
+b200_error* b200_client_profile_report(b200_client* client, char** json);
+/* Total kernels launched by this client since creation (generated + static + collectives). */
+int64_t b200_client_launch_count(const b200_client* client);
+
+#pragma GCC visibility pop
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_CORE_H_ */

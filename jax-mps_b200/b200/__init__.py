@@ -1,0 +1,444 @@
+"""Python face of the B200 PJRT core: a ctypes binding over the C ABI in
+include/b200_core.h, shaped like the client objects jaxlib hands a user of the
+reference plugin (`client.compile_and_load(text)`, `jax.device_put`,
+`exe.execute([buf])`, `numpy.asarray(buf)` — compare the reference's raw-MLIR
+test, tests/test_ops.py:245-281).
+
+There is no CPU fallback: importing works anywhere (so host-side tooling can
+run), but creating a `Client` raises `B200Error` unless the CUDA extension is
+built and a GPU is present.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import numpy as np
+
+_LIB_NAME = "libb200core.so"
+
+
+class B200Error(RuntimeError):
+    def __init__(self, message: str, code: int = 2):
+        super().__init__(message)
+        self.code = code
+
+
+OK, CANCELLED, UNKNOWN, INVALID_ARGUMENT, NOT_FOUND = 0, 1, 2, 3, 5
+RESOURCE_EXHAUSTED, FAILED_PRECONDITION, UNIMPLEMENTED, INTERNAL = 8, 9, 12, 13
+
+# element types (b200_dtype)
+PRED, S8, S16, S32, S64, U8, U16, U32, U64, F16, F32, F64, BF16 = range(1, 14)
+_NP_TO_DT = {np.dtype(np.bool_): PRED, np.dtype(np.int8): S8, np.dtype(np.int16): S16, np.dtype(np.int32): S32,
+             np.dtype(np.int64): S64, np.dtype(np.uint8): U8, np.dtype(np.uint16): U16, np.dtype(np.uint32): U32,
+             np.dtype(np.uint64): U64, np.dtype(np.float16): F16, np.dtype(np.float32): F32,
+             np.dtype(np.float64): F64}
+_DT_TO_NP = {v: k for k, v in _NP_TO_DT.items()}
+_DT_TO_NP[BF16] = np.dtype(np.uint16)          # raw bf16 bit patterns
+_DT_NAMES = {PRED: "i1", S8: "i8", S16: "i16", S32: "i32", S64: "i64", U8: "ui8", U16: "ui16", U32: "ui32",
+             U64: "ui64", F16: "f16", F32: "f32", F64: "f64", BF16: "bf16"}
+_NAME_TO_DT = {v: k for k, v in _DT_NAMES.items()}
+NCCL_ID_BYTES = 128
+
+
+class _ClientOptions(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("device_ordinal", C.c_int), ("process_index", C.c_int),
+                ("num_processes", C.c_int), ("nccl_unique_id", C.c_char_p), ("pool_release_threshold", C.c_size_t)]
+
+
+class _CompileOptions(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("num_partitions", C.c_int), ("disable_fusion", C.c_int)]
+
+
+class _ExecuteOptions(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("donate_arguments", C.c_int)]
+
+
+class MemoryStats(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("bytes_in_use", C.c_int64),
+                ("peak_bytes_in_use", C.c_int64), ("peak_bytes_in_use_is_set", C.c_int),
+                ("bytes_limit", C.c_int64), ("bytes_limit_is_set", C.c_int),
+                ("pool_bytes", C.c_int64), ("pool_bytes_is_set", C.c_int),
+                ("peak_pool_bytes", C.c_int64), ("peak_pool_bytes_is_set", C.c_int),
+                ("num_allocs", C.c_int64), ("num_allocs_is_set", C.c_int),
+                ("largest_alloc_size", C.c_int64), ("largest_alloc_size_is_set", C.c_int)]
+
+
+EVENT_CALLBACK = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p)
+
+# name -> (restype, argtypes); every symbol include/b200_core.h declares
+_P = C.c_void_p
+SIGNATURES = {
+    "b200_error_destroy": (None, [_P]),
+    "b200_error_message": (C.c_char_p, [_P]),
+    "b200_error_get_code": (C.c_int, [_P]),
+    "b200_client_create": (_P, [C.POINTER(_ClientOptions), C.POINTER(_P)]),
+    "b200_client_destroy": (_P, [_P]),
+    "b200_client_platform_name": (C.c_char_p, [_P]),
+    "b200_client_platform_version": (C.c_char_p, [_P]),
+    "b200_client_process_index": (C.c_int, [_P]),
+    "b200_client_device_count": (C.c_int, [_P]),
+    "b200_client_addressable_device_count": (C.c_int, [_P]),
+    "b200_nccl_unique_id": (_P, [C.c_char_p]),
+    "b200_device_id": (C.c_int, [_P]),
+    "b200_device_local_hardware_id": (C.c_int, [_P]),
+    "b200_device_kind": (C.c_char_p, [_P]),
+    "b200_device_debug_string": (C.c_char_p, [_P]),
+    "b200_device_memory_stats": (_P, [_P, C.POINTER(MemoryStats)]),
+    "b200_client_compile": (_P, [_P, C.c_char_p, C.c_size_t, C.c_char_p, C.POINTER(_CompileOptions), C.POINTER(_P)]),
+    "b200_executable_destroy": (_P, [_P]),
+    "b200_executable_name": (C.c_char_p, [_P]),
+    "b200_executable_fingerprint": (C.c_char_p, [_P]),
+    "b200_executable_num_replicas": (C.c_int, [_P]),
+    "b200_executable_num_partitions": (C.c_int, [_P]),
+    "b200_executable_num_args": (C.c_size_t, [_P]),
+    "b200_executable_num_outputs": (C.c_size_t, [_P]),
+    "b200_executable_output_info": (_P, [_P, C.c_size_t, C.POINTER(C.c_int), C.POINTER(C.POINTER(C.c_int64)), C.POINTER(C.c_size_t)]),
+    "b200_executable_arg_info": (_P, [_P, C.c_size_t, C.POINTER(C.c_int), C.POINTER(C.POINTER(C.c_int64)), C.POINTER(C.c_size_t)]),
+    "b200_executable_launches_per_execute": (C.c_int64, [_P]),
+    "b200_executable_num_kernels": (C.c_int64, [_P]),
+    "b200_executable_temp_bytes": (C.c_int64, [_P]),
+    "b200_executable_plan_text": (C.c_char_p, [_P]),
+    "b200_compile_to_plan": (_P, [C.c_char_p, C.c_size_t, C.POINTER(_CompileOptions), C.c_int, C.c_int, C.c_int,
+                                  C.POINTER(_P), C.POINTER(_P)]),
+    "b200_string_free": (None, [_P]),
+    "b200_buffer_from_host": (_P, [_P, _P, C.c_int, C.POINTER(C.c_int64), C.c_size_t, C.POINTER(C.c_int64), C.POINTER(_P), C.POINTER(_P)]),
+    "b200_buffer_to_host": (_P, [_P, _P, C.POINTER(C.c_size_t), C.POINTER(_P)]),
+    "b200_buffer_dtype": (C.c_int, [_P]),
+    "b200_buffer_num_dims": (C.c_size_t, [_P]),
+    "b200_buffer_dims": (C.POINTER(C.c_int64), [_P]),
+    "b200_buffer_on_device_size": (C.c_size_t, [_P]),
+    "b200_buffer_device": (C.c_int, [_P]),
+    "b200_buffer_ready_event": (_P, [_P, C.POINTER(_P)]),
+    "b200_buffer_copy": (_P, [_P, C.POINTER(_P)]),
+    "b200_buffer_delete": (_P, [_P]),
+    "b200_buffer_is_deleted": (C.c_int, [_P]),
+    "b200_buffer_destroy": (_P, [_P]),
+    "b200_buffer_device_pointer": (_P, [_P]),
+    "b200_executable_execute": (_P, [_P, C.POINTER(_P), C.c_size_t, C.POINTER(_P), C.POINTER(_P), C.POINTER(_ExecuteOptions)]),
+    "b200_event_is_ready": (C.c_int, [_P]),
+    "b200_event_await": (_P, [_P]),
+    "b200_event_error": (_P, [_P]),
+    "b200_event_on_ready": (_P, [_P, EVENT_CALLBACK, _P]),
+    "b200_event_destroy": (_P, [_P]),
+    "b200_client_synchronize": (_P, [_P]),
+    "b200_client_compute_stream": (_P, [_P]),
+    "b200_client_launch_count": (C.c_int64, [_P]),
+    "b200_client_set_profiling": (_P, [_P, C.c_int]),
+    "b200_client_profile_report": (_P, [_P, C.POINTER(_P)]),
+}
+
+_lib = None
+
+
+def library_path() -> Path:
+    """B200_LIBRARY_PATH wins, else the in-tree build next to this file (the
+    reference resolves its dylib the same way: src/jax_plugins/mps/__init__.py:37-61)."""
+    env = os.environ.get("B200_LIBRARY_PATH")
+    if env:
+        if not Path(env).exists():
+            raise B200Error(f"B200_LIBRARY_PATH is set to '{env}', but the file does not exist.", FAILED_PRECONDITION)
+        return Path(env)
+    return Path(__file__).resolve().parent / _LIB_NAME
+
+
+def load_library():
+    """dlopen the core and bind every declared symbol. Raises B200Error when
+    the extension has not been built — nothing here falls back to the CPU."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    p = library_path()
+    if not p.exists():
+        raise B200Error(f"{p} not found: build it with `python jax-mps_b200/build.py` (there is no CPU fallback)",
+                        FAILED_PRECONDITION)
+    lib = C.CDLL(str(p))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def _check(err):
+    if err:
+        lib = load_library()
+        msg = lib.b200_error_message(err).decode("utf-8", "replace")
+        code = lib.b200_error_get_code(err)
+        lib.b200_error_destroy(err)
+        raise B200Error(msg, code)
+
+
+def compile_to_plan(text: str | bytes, num_processes: int = 1, process_index: int = 0, validate: bool = False,
+                    disable_fusion: bool = False):
+    """Host-only compile: returns (plan text, generated CUDA source). Needs no GPU."""
+    lib = load_library()
+    code = text.encode() if isinstance(text, str) else text
+    opts = _CompileOptions(C.sizeof(_CompileOptions), 0, 1 if disable_fusion else 0)
+    plan, src = _P(), _P()
+    _check(lib.b200_compile_to_plan(code, len(code), C.byref(opts), num_processes, process_index, 1 if validate else 0,
+                                    C.byref(plan), C.byref(src)))
+    out = (C.string_at(plan.value).decode(), C.string_at(src.value).decode())
+    lib.b200_string_free(plan)
+    lib.b200_string_free(src)
+    return out
+
+
+def nccl_unique_id() -> bytes:
+    buf = C.create_string_buffer(NCCL_ID_BYTES)
+    _check(load_library().b200_nccl_unique_id(buf))
+    return buf.raw
+
+
+class Event:
+    def __init__(self, handle):
+        self._h = handle
+
+    def is_ready(self) -> bool:
+        return bool(load_library().b200_event_is_ready(self._h))
+
+    def wait(self):
+        _check(load_library().b200_event_await(self._h))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            load_library().b200_event_destroy(self._h)
+            self._h = None
+
+
+class Buffer:
+    """A device array (PJRT_Buffer)."""
+
+    def __init__(self, client: "Client", handle):
+        self.client, self._h = client, handle
+
+    @property
+    def dtype_code(self) -> int:
+        return load_library().b200_buffer_dtype(self._h)
+
+    @property
+    def dtype(self) -> str:
+        return _DT_NAMES[self.dtype_code]
+
+    @property
+    def shape(self) -> tuple:
+        lib = load_library()
+        n = lib.b200_buffer_num_dims(self._h)
+        d = lib.b200_buffer_dims(self._h)
+        return tuple(int(d[i]) for i in range(n))
+
+    @property
+    def nbytes(self) -> int:
+        return load_library().b200_buffer_on_device_size(self._h)
+
+    def device_pointer(self) -> int:
+        return load_library().b200_buffer_device_pointer(self._h) or 0
+
+    def is_deleted(self) -> bool:
+        return bool(load_library().b200_buffer_is_deleted(self._h))
+
+    def delete(self):
+        _check(load_library().b200_buffer_delete(self._h))
+
+    def copy(self) -> "Buffer":
+        out = _P()
+        _check(load_library().b200_buffer_copy(self._h, C.byref(out)))
+        return Buffer(self.client, out.value)
+
+    def block_until_ready(self) -> "Buffer":
+        ev = _P()
+        _check(load_library().b200_buffer_ready_event(self._h, C.byref(ev)))
+        Event(ev.value).wait()
+        return self
+
+    def to_host_async(self, out: np.ndarray) -> Event:
+        """Start a device-to-host copy into `out` (same shape/dtype; pinned memory makes it truly asynchronous)."""
+        size = C.c_size_t(out.nbytes)
+        ev = _P()
+        _check(load_library().b200_buffer_to_host(self._h, out.ctypes.data_as(_P), C.byref(size), C.byref(ev)))
+        return Event(ev.value)
+
+    def to_numpy(self) -> np.ndarray:
+        """bf16 buffers come back as float32 (exactly representable)."""
+        code = self.dtype_code
+        out = np.empty(self.shape, dtype=_DT_TO_NP[code])
+        size = C.c_size_t(out.nbytes)
+        _check(load_library().b200_buffer_to_host(self._h, out.ctypes.data_as(_P), C.byref(size), None))
+        if code == BF16:
+            return (out.astype(np.uint32) << 16).view(np.float32)
+        return out
+
+    def __array__(self, dtype=None, copy=None):
+        a = self.to_numpy()
+        return a.astype(dtype) if dtype is not None else a
+
+    def __del__(self):
+        if getattr(self, "_h", None) and load_library is not None:
+            try:
+                load_library().b200_buffer_destroy(self._h)
+            except Exception:
+                pass
+            self._h = None
+
+
+class Executable:
+    """A compiled and loaded program (PJRT_LoadedExecutable)."""
+
+    def __init__(self, client: "Client", handle):
+        self.client, self._h = client, handle
+        lib = load_library()
+        self.num_args = lib.b200_executable_num_args(handle)
+        self.num_outputs = lib.b200_executable_num_outputs(handle)
+
+    @property
+    def name(self) -> str:
+        return load_library().b200_executable_name(self._h).decode()
+
+    @property
+    def fingerprint(self) -> str:
+        return load_library().b200_executable_fingerprint(self._h).decode()
+
+    @property
+    def launches_per_execute(self) -> int:
+        return load_library().b200_executable_launches_per_execute(self._h)
+
+    @property
+    def num_kernels(self) -> int:
+        return load_library().b200_executable_num_kernels(self._h)
+
+    @property
+    def temp_bytes(self) -> int:
+        return load_library().b200_executable_temp_bytes(self._h)
+
+    def plan_text(self) -> str:
+        return load_library().b200_executable_plan_text(self._h).decode()
+
+    def output_info(self, i: int):
+        dt, dims, nd = C.c_int(), C.POINTER(C.c_int64)(), C.c_size_t()
+        _check(load_library().b200_executable_output_info(self._h, i, C.byref(dt), C.byref(dims), C.byref(nd)))
+        return _DT_NAMES[dt.value], tuple(int(dims[k]) for k in range(nd.value))
+
+    def execute(self, args, donate: bool = False) -> list:
+        """Enqueue one execution; returns the output buffers without waiting."""
+        lib = load_library()
+        n = len(args)
+        arr = (_P * max(n, 1))(*[a._h for a in args])
+        outs = (_P * max(self.num_outputs, 1))()
+        opts = _ExecuteOptions(C.sizeof(_ExecuteOptions), 1 if donate else 0)
+        _check(lib.b200_executable_execute(self._h, arr, n, outs, None, C.byref(opts)))
+        return [Buffer(self.client, outs[k]) for k in range(self.num_outputs)]
+
+    def __call__(self, *arrays):
+        bufs = [a if isinstance(a, Buffer) else self.client.buffer_from_host(a) for a in arrays]
+        return [b.to_numpy() for b in self.execute(bufs)]
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            try:
+                load_library().b200_executable_destroy(self._h)
+            except Exception:
+                pass
+            self._h = None
+
+
+class Client:
+    """One process, one B200 (PJRT_Client). For data-parallel jobs every
+    process passes its rank, the world size and the shared NCCL id."""
+
+    def __init__(self, device_ordinal: int = -1, process_index: int = 0, num_processes: int = 1,
+                 nccl_id: bytes | None = None):
+        lib = load_library()
+        self._id = nccl_id
+        opts = _ClientOptions(C.sizeof(_ClientOptions), device_ordinal, process_index, num_processes, nccl_id, 0)
+        h = _P()
+        _check(lib.b200_client_create(C.byref(opts), C.byref(h)))
+        self._h = h.value
+
+    @property
+    def platform(self) -> str:
+        return load_library().b200_client_platform_name(self._h).decode()
+
+    @property
+    def platform_version(self) -> str:
+        return load_library().b200_client_platform_version(self._h).decode()
+
+    @property
+    def process_index(self) -> int:
+        return load_library().b200_client_process_index(self._h)
+
+    def device_count(self) -> int:
+        return load_library().b200_client_device_count(self._h)
+
+    def device_kind(self) -> str:
+        return load_library().b200_device_kind(self._h).decode()
+
+    def device_debug_string(self) -> str:
+        return load_library().b200_device_debug_string(self._h).decode()
+
+    def memory_stats(self) -> MemoryStats:
+        st = MemoryStats(C.sizeof(MemoryStats))
+        _check(load_library().b200_device_memory_stats(self._h, C.byref(st)))
+        return st
+
+    def compile(self, text: str | bytes, disable_fusion: bool = False) -> Executable:
+        """StableHLO module text -> loaded executable (compile_and_load)."""
+        code = text.encode() if isinstance(text, str) else text
+        opts = _CompileOptions(C.sizeof(_CompileOptions), 0, 1 if disable_fusion else 0)
+        h = _P()
+        _check(load_library().b200_client_compile(self._h, code, len(code), b"mlir", C.byref(opts), C.byref(h)))
+        return Executable(self, h.value)
+
+    compile_and_load = compile
+
+    def buffer_from_host(self, array, dtype: str | None = None) -> Buffer:
+        """Host array -> device buffer. `dtype='bf16'` converts float32 input to bfloat16 on the host."""
+        a = np.asarray(array)
+        if dtype == "bf16":
+            from .shlo.builder import f32_to_bf16_bits
+            a = f32_to_bf16_bits(a.astype(np.float32)).reshape(a.shape)
+            code = BF16
+        else:
+            if dtype is not None:
+                a = a.astype(_DT_TO_NP[_NAME_TO_DT[dtype]])
+            if a.dtype not in _NP_TO_DT:
+                raise B200Error(f"unsupported host dtype {a.dtype}", INVALID_ARGUMENT)
+            code = _NP_TO_DT[a.dtype]
+        dims = (C.c_int64 * max(a.ndim, 1))(*a.shape)
+        strides = (C.c_int64 * max(a.ndim, 1))(*a.strides)
+        h = _P()
+        ptr = a.ctypes.data_as(_P) if a.size else None
+        _check(load_library().b200_buffer_from_host(self._h, ptr, code, dims, a.ndim, strides, C.byref(h), None))
+        buf = Buffer(self, h.value)
+        buf._host = a            # a pinned source is read asynchronously: keep it alive with the buffer
+        return buf
+
+    device_put = buffer_from_host
+
+    def synchronize(self):
+        _check(load_library().b200_client_synchronize(self._h))
+
+    def compute_stream(self) -> int:
+        return load_library().b200_client_compute_stream(self._h) or 0
+
+    def set_profiling(self, on: bool):
+        _check(load_library().b200_client_set_profiling(self._h, 1 if on else 0))
+
+    def profile_report(self) -> list:
+        """Per-step device times accumulated while profiling was on: [{'kind','key','ms','count'}]."""
+        import json
+        out = _P()
+        lib = load_library()
+        _check(lib.b200_client_profile_report(self._h, C.byref(out)))
+        txt = C.string_at(out.value).decode()
+        lib.b200_string_free(out)
+        return json.loads(txt)
+
+    def launch_count(self) -> int:
+        return load_library().b200_client_launch_count(self._h)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            load_library().b200_client_destroy(self._h)
+            self._h = None

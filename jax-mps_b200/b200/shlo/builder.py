@@ -521,10 +521,10 @@ class Builder:
         """stablehlo.convolution, 2 spatial dims. `dn` strings use b/f/0/1 for
         input and output and i/o/0/1 for the kernel."""
         ls, rs, os_ = dn
-        nsp = 2
+        nsp = len(ls) - 2
         def dim(spec, c): return spec.index(c)
         padding = [tuple(p) for p in padding]
-        out = [0] * 4
+        out = [0] * (nsp + 2)
         n = x.shape[dim(ls, "b")] // batch_group_count
         o = w.shape[dim(rs, "o")]
         out[dim(os_, "b")] = n
@@ -543,14 +543,14 @@ class Builder:
             "dimension_numbers": f"#stablehlo.conv<{spec(ls)}x{spec(rs)}->{spec(os_)}>",
             "lhs_dilation": _i64arr(lhs_dilation), "rhs_dilation": _i64arr(rhs_dilation),
             "window_strides": _i64arr(strides),
-            "padding": f"dense<{[list(p) for p in padding]}> : tensor<2x2xi64>",
+            "padding": f"dense<{[list(p) for p in padding]}> : tensor<{nsp}x2xi64>",
             "precision_config": "[#stablehlo<precision DEFAULT>, #stablehlo<precision DEFAULT>]",
         }
         (y,) = self.emit("stablehlo.convolution", [x, w], [(tuple(out), x.dtype)], props=props)
         if x.dtype in FLOATS:
-            assert feature_group_count == 1 and batch_group_count == 1, "grouped conv VJP not provided"
             def dil(n, d): return 0 if n == 0 else 1 + d * (n - 1)
             def vjp(g):
+                assert feature_group_count == 1 and batch_group_count == 1, "grouped conv VJP not provided"
                 g0 = g[0]
                 isp = [x.shape[dim(ls, str(s))] for s in range(nsp)]
                 ksp = [w.shape[dim(rs, str(s))] for s in range(nsp)]

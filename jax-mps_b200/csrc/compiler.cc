@@ -1,0 +1,1547 @@
+// StableHLO module -> kernel plan.
+//
+// Pipeline (the reference's counterpart is finalizeModule + MpsFusionPass +
+// the trace-and-replay executor: src/pjrt_plugin/stablehlo_parser.cc:80-285,
+// src/pjrt_plugin/mlx_executable.cc:619-1008):
+//   1. inline func.call / stablehlo.composite, drop pass-through ops
+//      (optimization_barrier, Sharding custom calls), fold identity broadcasts;
+//   2. reject unsupported operations with one error naming all of them;
+//   3. group fusable operations (elementwise, index-rewriting, reductions with
+//      their producers) into generated kernels;
+//   4. order the units, give every materialised tensor a slot and lay the
+//      temporaries out in an arena by liveness;
+//   5. lower dot_general and convolution to the table-driven implicit-GEMM kernel.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <functional>
+#include <queue>
+#include <set>
+#include <sstream>
+
+#include "codegen.h"
+#include "plan.h"
+
+namespace b200 {
+
+const char* codegen_prelude() {
+  static const char* s =
+#include "prelude.inc"
+      ;
+  return s;
+}
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// pass 1: inlining and pass-through removal
+// ---------------------------------------------------------------------------
+struct Inliner {
+  Module& m;
+  std::map<Value*, Value*> remap;
+  int depth = 0;
+  explicit Inliner(Module& mod) : m(mod) {}
+
+  Value* res(Value* v) {
+    auto it = remap.find(v);
+    while (it != remap.end()) { v = it->second; it = remap.find(v); }
+    return v;
+  }
+
+  std::unique_ptr<Op> clone_op(Op* src, std::map<Value*, Value*>& vm) {
+    auto op = std::make_unique<Op>();
+    op->name = src->name;
+    op->attrs = src->attrs;
+    for (auto* o : src->operands) {
+      auto it = vm.find(o);
+      op->operands.push_back(it == vm.end() ? o : it->second);
+    }
+    for (auto* r : src->results) {
+      Value* nv = m.new_value(r->type, r->name);
+      nv->def = op.get();
+      nv->def_index = r->def_index;
+      vm[r] = nv;
+      op->results.push_back(nv);
+    }
+    for (auto& reg : src->regions) {
+      auto b = std::make_unique<Block>();
+      b->parent_op = op.get();
+      for (auto* a : reg->args) {
+        Value* nv = m.new_value(a->type, a->name);
+        nv->owner = b.get();
+        nv->arg_index = a->arg_index;
+        vm[a] = nv;
+        b->args.push_back(nv);
+      }
+      for (auto& inner : reg->ops) {
+        auto c = clone_op(inner.get(), vm);
+        c->parent = b.get();
+        b->ops.push_back(std::move(c));
+      }
+      op->regions.push_back(std::move(b));
+    }
+    return op;
+  }
+
+  void run(Block* b) {
+    std::vector<std::unique_ptr<Op>> in = std::move(b->ops);
+    b->ops.clear();
+    for (auto& op : in) process(std::move(op), b);
+  }
+
+  void process(std::unique_ptr<Op> op, Block* b) {
+    for (auto& o : op->operands) o = res(o);
+    std::string sh = op->short_name();
+    if (op->name == "func.call" || sh == "composite") {
+      std::string callee = attr_str(op->attr(sh == "composite" ? "decomposition" : "callee"));
+      if (!callee.empty() && callee[0] == '@') callee = callee.substr(1);
+      auto it = m.funcs.find(callee);
+      if (it == m.funcs.end()) throw CompileError("call to unknown function @" + callee);
+      if (++depth > 64) throw CompileError("call depth limit (recursive functions are not supported)");
+      Func* f = it->second.get();
+      std::map<Value*, Value*> vm;
+      if (f->body->args.size() != op->operands.size()) throw CompileError("call arity mismatch for @" + callee);
+      for (size_t k = 0; k < op->operands.size(); k++) vm[f->body->args[k]] = op->operands[k];
+      for (auto& inner : f->body->ops) {
+        if (inner->name == "func.return") {
+          for (size_t k = 0; k < op->results.size(); k++) {
+            Value* r = inner->operands[k];
+            auto f2 = vm.find(r);
+            remap[op->results[k]] = res(f2 == vm.end() ? r : f2->second);
+          }
+          break;
+        }
+        auto c = clone_op(inner.get(), vm);
+        process(std::move(c), b);
+      }
+      depth--;
+      return;
+    }
+    if (sh == "optimization_barrier") {
+      for (size_t k = 0; k < op->results.size(); k++) remap[op->results[k]] = op->operands[k];
+      return;
+    }
+    if (sh == "custom_call") {
+      std::string tgt = attr_str(op->attr("call_target_name"));
+      // Pass-through targets of SPMD-lowered programs (src/pjrt_plugin/ops/control_flow.cc:1426-1438).
+      if (tgt == "Sharding" || tgt == "SPMDFullToShardShape" || tgt == "SPMDShardToFullShape") {
+        if (op->operands.size() == 1 && op->results.size() == 1 && op->operands[0]->type == op->results[0]->type) {
+          remap[op->results[0]] = op->operands[0];
+          return;
+        }
+        throw CompileError("custom_call @" + tgt + " that changes the shape needs an SPMD partitioner; "
+                           "compile the per-shard (manual) program instead");
+      }
+    }
+    // x + broadcast(0), x * broadcast(1), x - broadcast(0), x / broadcast(1) -> x
+    // (src/pjrt_plugin/passes/canonicalize_broadcast_identity.cc)
+    if ((sh == "add" || sh == "multiply" || sh == "subtract" || sh == "divide") && op->operands.size() == 2 &&
+        dt_is_float(op->results[0]->type.dt)) {
+      auto splat_of = [&](Value* v, double& out) -> bool {
+        Op* d = v->def;
+        while (d && (d->short_name() == "broadcast_in_dim" || d->short_name() == "reshape")) d = d->operands[0]->def;
+        if (!d || d->short_name() != "constant") return false;
+        DenseValue dv = attr_dense(d->attr("value"));
+        if (!dv.splat || dv.type.numel() == 0) return false;
+        if (dv.type.dt == DT::F32) { float f; memcpy(&f, dv.data.data(), 4); out = f; return true; }
+        if (dv.type.dt == DT::BF16) { uint16_t h; memcpy(&h, dv.data.data(), 2); out = bf16_to_f32(h); return true; }
+        return false;
+      };
+      double c;
+      double ident = (sh == "add" || sh == "subtract") ? 0.0 : 1.0;
+      auto is_ident = [&](double x) { return x == ident && !(ident == 0.0 && std::signbit(x)); };
+      if (splat_of(op->operands[1], c) && is_ident(c) && op->operands[0]->type == op->results[0]->type) {
+        remap[op->results[0]] = op->operands[0];
+        return;
+      }
+      if ((sh == "add" || sh == "multiply") && splat_of(op->operands[0], c) && is_ident(c) &&
+          op->operands[1]->type == op->results[0]->type) {
+        remap[op->results[0]] = op->operands[1];
+        return;
+      }
+    }
+    for (auto& reg : op->regions) run(reg.get());
+    op->parent = b;
+    b->ops.push_back(std::move(op));
+  }
+};
+
+void fix_region_operands(Block* b, Inliner& inl) {
+  for (auto& op : b->ops) {
+    for (auto& o : op->operands) o = inl.res(o);
+    for (auto& r : op->regions) fix_region_operands(r.get(), inl);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// op classification
+// ---------------------------------------------------------------------------
+enum class Cat { ELEMENTWISE, DUP, INDEXING, REDUCE, DOT, CONV, SCATTER, WHILE, CASE, ALL_REDUCE, RETURN, TOKEN, PARTITION_ID, UNSUPPORTED };
+
+Cat categorize(Op* op) {
+  const std::string sh = op->short_name();
+  if (sh == "return") return Cat::RETURN;
+  if (op->name.rfind("stablehlo.", 0) != 0 && op->name.rfind("chlo.", 0) != 0 && op->name.rfind("mhlo.", 0) != 0)
+    return Cat::UNSUPPORTED;
+  if (is_elementwise_op(sh)) return Cat::ELEMENTWISE;
+  if (sh == "constant" || sh == "iota" || sh == "broadcast_in_dim") return Cat::DUP;
+  if (sh == "reshape" || sh == "transpose" || sh == "reverse" || sh == "slice" || sh == "pad" || sh == "concatenate" ||
+      sh == "dynamic_slice" || sh == "dynamic_update_slice" || sh == "gather")
+    return Cat::INDEXING;
+  if (sh == "reduce") return Cat::REDUCE;
+  if (sh == "dot_general") return Cat::DOT;
+  if (sh == "convolution") return Cat::CONV;
+  if (sh == "scatter") return Cat::SCATTER;
+  if (sh == "while") return Cat::WHILE;
+  if (sh == "case") return Cat::CASE;
+  if (sh == "all_reduce") return Cat::ALL_REDUCE;
+  if (sh == "create_token" || sh == "after_all") return Cat::TOKEN;
+  if (sh == "partition_id" || sh == "replica_id") return Cat::PARTITION_ID;
+  return Cat::UNSUPPORTED;
+}
+
+void collect_unsupported(Block* b, std::set<std::string>& out, bool in_combiner) {
+  for (auto& op : b->ops) {
+    Cat c = categorize(op.get());
+    if (c == Cat::UNSUPPORTED) out.insert(op->name);
+    bool comb = c == Cat::REDUCE || c == Cat::SCATTER || c == Cat::ALL_REDUCE;
+    for (auto& r : op->regions) collect_unsupported(r.get(), out, comb);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// planning
+// ---------------------------------------------------------------------------
+struct Group {
+  int id = 0;
+  bool is_reduce = false;
+  std::set<Op*> members;            // non-duplicable ops evaluated inside the kernel (roots included)
+  std::vector<Op*> roots;           // ops whose results are written to memory
+  std::set<Op*> identity;           // members evaluated at the root's own index
+  int max_pos = -1;
+};
+
+struct Unit {
+  enum Kind { GROUP, OP, CONST_MAT } kind = OP;
+  Group* group = nullptr;
+  Op* op = nullptr;
+  int prio = 0;
+};
+
+struct Planner {
+  CompiledProgram& prog;
+  const CompileOptions& opts;
+  Module& mod;
+  std::map<Value*, int> slot_of;
+  std::map<std::string, int> kernel_cache;
+  std::deque<Value> synth_values;
+  std::ostringstream dump;
+  int next_group_id = 0;
+
+  Planner(CompiledProgram& p, const CompileOptions& o, Module& m) : prog(p), opts(o), mod(m) {}
+
+  int new_slot(Slot::Kind kind, const TensorType& t, int arena) {
+    Slot s;
+    s.kind = kind;
+    s.type = t;
+    s.bytes = std::max<size_t>(t.bytes(), 1);
+    s.arena = arena;
+    prog.slots.push_back(s);
+    return (int)prog.slots.size() - 1;
+  }
+  int const_slot(const TensorType& t, std::vector<uint8_t> bytes) {
+    int s = new_slot(Slot::CONST, t, 0);
+    prog.slots[s].index = (int)prog.consts.size();
+    prog.slots[s].bytes = std::max<size_t>(bytes.size(), 1);
+    prog.consts.push_back({std::move(bytes)});
+    return s;
+  }
+  int table_slot(const void* data, size_t bytes) {
+    TensorType t;
+    t.dt = DT::U8;
+    t.dims = {(int64_t)bytes};
+    std::vector<uint8_t> v((const uint8_t*)data, (const uint8_t*)data + bytes);
+    return const_slot(t, std::move(v));
+  }
+  Value* synth(const TensorType& t) {
+    synth_values.emplace_back();
+    Value* v = &synth_values.back();
+    v->id = 1000000 + (int)synth_values.size();
+    v->type = t;
+    return v;
+  }
+  int add_kernel(const std::string& body_without_name) {
+    auto it = kernel_cache.find(body_without_name);
+    if (it != kernel_cache.end()) return it->second;
+    int id = (int)prog.kernels.size();
+    KernelSource ks;
+    ks.name = "k" + std::to_string(id);
+    std::string body = body_without_name;
+    auto p = body.find("@NAME@");
+    body.replace(p, 6, ks.name);
+    ks.body = body;
+    prog.kernels.push_back(ks);
+    kernel_cache[body_without_name] = id;
+    return id;
+  }
+
+  // ---- per-block planning -------------------------------------------------
+  struct BlockState {
+    Block* block;
+    int arena;
+    std::vector<Op*> ops;
+    std::map<Value*, std::vector<Op*>> users;       // users in this block (nested uses lifted to the region owner)
+    std::set<Value*> returned;
+    std::map<Op*, std::vector<Group*>> group_of;   // a cheap op may be evaluated in several kernels
+    std::deque<Group> groups;
+    std::set<Op*> dup_materialize;
+  };
+
+  static void lift_uses(Block* inner, Op* owner, Block* home, BlockState& st) {
+    for (auto& op : inner->ops) {
+      for (auto* o : op->operands) {
+        // defined in `home` (op result or block argument)?
+        bool in_home = (o->def && o->def->parent == home) || (!o->def && o->owner == home);
+        if (in_home) st.users[o].push_back(owner);
+      }
+      for (auto& r : op->regions) lift_uses(r.get(), owner, home, st);
+    }
+  }
+
+  bool is_dup(Op* op) { return categorize(op) == Cat::DUP; }
+  bool fusable(Op* op) {
+    Cat c = categorize(op);
+    return c == Cat::ELEMENTWISE || c == Cat::INDEXING;
+  }
+
+  // May the value produced by `p` be computed inside the kernel of user `u`?
+  bool can_fuse_into(Op* p, Value* pv, Op* u) {
+    Cat cu = categorize(u);
+    if (cu == Cat::ELEMENTWISE) return true;
+    if (cu == Cat::INDEXING) {
+      std::string sh = u->short_name();
+      if (sh == "gather") return u->operands[0] != pv;       // table stays in memory; indices may be computed
+      return true;
+    }
+    if (cu == Cat::REDUCE) {
+      size_t n = u->operands.size() / 2;
+      for (size_t k = n; k < u->operands.size(); k++)
+        if (u->operands[k] == pv) return false;             // init values are read from memory
+      return true;
+    }
+    return false;
+  }
+
+  // Is any member of `g` reachable from `starts` through def-use edges?
+  bool reaches(const std::vector<Op*>& starts, Group* g, BlockState& st) {
+    std::set<Op*> seen;
+    std::vector<Op*> work(starts.begin(), starts.end());
+    while (!work.empty()) {
+      Op* o = work.back();
+      work.pop_back();
+      if (!seen.insert(o).second) continue;
+      if (g->members.count(o)) return true;
+      if (o->pos > g->max_pos) continue;
+      for (auto* r : o->results)
+        for (auto* u : st.users[r]) work.push_back(u);
+    }
+    return false;
+  }
+
+  static bool cheap_to_duplicate(Op* op) {
+    if (categorize(op) != Cat::ELEMENTWISE) return false;
+    static const std::set<std::string> cheap = {"add", "subtract", "multiply", "maximum", "minimum", "negate", "abs",
+                                                "compare", "select", "convert", "and", "or", "xor", "not", "clamp", "sign"};
+    return cheap.count(op->short_name()) != 0;
+  }
+
+  bool identity_in(Group* g, Op* op, BlockState& st) {
+    Value* v = op->results[0];
+    for (auto* u : st.users[v])
+      if (g->identity.count(u) && categorize(u) == Cat::ELEMENTWISE && u->results[0]->type.dims == v->type.dims)
+        return true;
+    return false;
+  }
+
+  void build_groups(BlockState& st) {
+    for (int i = (int)st.ops.size() - 1; i >= 0; i--) {
+      Op* op = st.ops[i];
+      Cat cat = categorize(op);
+      if (cat == Cat::REDUCE) {
+        st.groups.emplace_back();
+        Group* g = &st.groups.back();
+        g->id = next_group_id++;
+        g->is_reduce = true;
+        g->members.insert(op);
+        g->roots.push_back(op);
+        g->max_pos = op->pos;
+        st.group_of[op].push_back(g);
+        continue;
+      }
+      if (cat == Cat::DUP) {
+        bool needs = st.returned.count(op->results[0]) != 0;
+        for (auto* u : st.users[op->results[0]]) {
+          Cat cu = categorize(u);
+          bool inl = cu == Cat::ELEMENTWISE || cu == Cat::INDEXING || cu == Cat::DUP ||
+                     (cu == Cat::REDUCE && can_fuse_into(op, op->results[0], u));
+          if (cu == Cat::INDEXING && u->short_name() == "gather" && u->operands[0] == op->results[0]) inl = false;
+          if (!inl) needs = true;
+        }
+        if (op->short_name() == "constant") {
+          DenseValue dv = attr_dense(op->attr("value"));
+          if (!dv.splat && dv.type.numel() > 0) needs = true;    // dense data always lives in memory
+        }
+        if (needs) st.dup_materialize.insert(op);
+        continue;
+      }
+      if (!fusable(op)) continue;
+      Value* v = op->results[0];
+      std::vector<Group*> gs;          // groups of users that can evaluate this op inline
+      std::vector<Op*> ext;            // users that need the value in memory
+      bool returned = st.returned.count(v) != 0;
+      for (auto* u : st.users[v]) {
+        auto it = st.group_of.find(u);
+        if (opts.fuse && it != st.group_of.end() && can_fuse_into(op, v, u)) {
+          for (auto* g : it->second)
+            if (std::find(gs.begin(), gs.end(), g) == gs.end()) gs.push_back(g);
+        } else ext.push_back(u);
+      }
+      auto join = [&](Group* g, bool as_root) {
+        g->members.insert(op);
+        st.group_of[op].push_back(g);
+        if (as_root) { g->roots.push_back(op); g->identity.insert(op); }
+        else if (identity_in(g, op, st)) g->identity.insert(op);
+      };
+      if (ext.empty() && !returned && gs.size() == 1) { join(gs[0], false); continue; }
+      if (ext.empty() && !returned && gs.size() > 1 && cheap_to_duplicate(op)) {
+        bool small = true;
+        for (auto* g : gs) small &= g->members.size() < 48;
+        if (small) {
+          for (auto* g : gs) join(g, false);
+          continue;
+        }
+      }
+      // written to memory: as an extra output of a consumer kernel when it shares that kernel's index space
+      std::sort(gs.begin(), gs.end(), [](Group* a, Group* b) { return a->max_pos < b->max_pos; });
+      bool placed = false;
+      for (auto* g : gs) {
+        if (g->is_reduce || !identity_in(g, op, st)) continue;
+        std::vector<Op*> others = ext;
+        for (auto* u : st.users[v]) {
+          auto it = st.group_of.find(u);
+          bool in_g = it != st.group_of.end() && std::find(it->second.begin(), it->second.end(), g) != it->second.end();
+          if (!in_g) others.push_back(u);
+        }
+        if (reaches(others, g, st)) continue;
+        join(g, true);
+        placed = true;
+        break;
+      }
+      if (placed) continue;
+      st.groups.emplace_back();
+      Group* g = &st.groups.back();
+      g->id = next_group_id++;
+      g->members.insert(op);
+      g->roots.push_back(op);
+      g->identity.insert(op);
+      g->max_pos = op->pos;
+      st.group_of[op].push_back(g);
+    }
+  }
+
+  // ---- kernel generation -----------------------------------------------------
+  struct Launch {
+    int kernel;
+    unsigned grid[3], block[3];
+    std::vector<Value*> outs, ins;
+  };
+
+  std::string idx_type_for(const std::vector<Value*>& vals, int64_t extra = 0) {
+    int64_t mx = extra;
+    for (auto* v : vals) mx = std::max<int64_t>(mx, v->type.numel());
+    return mx >= (1LL << 31) - 1024 ? "i64" : "int";
+  }
+
+  std::string store_expr(DT d, const std::string& e) {
+    if (d == DT::BF16) return "f_to_bf16(" + e + ")";
+    if (d == DT::F16) return "f_to_f16(" + e + ")";
+    if (d == DT::PRED) return "(u8)(" + e + ")";
+    return e;
+  }
+
+  std::string signature(const std::vector<Value*>& outs, const std::vector<Value*>& ins) {
+    std::string s;
+    for (size_t k = 0; k < outs.size(); k++)
+      s += std::string(k ? ", " : "") + s_type(outs[k]->type.dt) + "* __restrict__ out" + std::to_string(k);
+    for (size_t k = 0; k < ins.size(); k++)
+      s += std::string((k || !outs.empty()) ? ", " : "") + "const " + s_type(ins[k]->type.dt) + "* __restrict__ in" +
+           std::to_string(k);
+    return s;
+  }
+
+  static constexpr int kEPT = 4;       // elements per thread of a pointwise kernel
+  static constexpr int kThreads = 256;
+
+  Launch gen_pointwise(Group* g, BlockState& st) {
+    std::vector<Value*> outs;
+    for (auto* r : g->roots) outs.push_back(r->results[0]);
+    const TensorType& rt = outs[0]->type;
+    for (auto* o : outs)
+      if (o->type.dims != rt.dims) throw CompileError("internal: fused outputs of different shapes");
+    int64_t n = rt.numel();
+    Emitter em;
+    em.is_internal = [&](Op* o) { return g->members.count(o) || (is_dup(o) && !st.dup_materialize.count(o)); };
+    std::vector<Value*> all;
+    for (auto* m : g->members) {
+      all.push_back(m->results[0]);
+      for (auto* o : m->operands) all.push_back(o);
+    }
+    em.idx_t = idx_type_for(all, n + kThreads * kEPT);
+    Ctx root;
+    root.shape = rt.dims;
+    root.lin = "lin";
+    em.ensure_idx(root);
+    std::vector<std::string> vals;
+    for (auto* o : outs) vals.push_back(em.emit(o, root));
+    for (size_t k = 0; k < outs.size(); k++)
+      em.line("out" + std::to_string(k) + "[lin] = " + store_expr(outs[k]->type.dt, vals[k]) + ";");
+    std::ostringstream src;
+    src << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(" << signature(outs, em.inputs)
+        << ") {\n";
+    src << "  #pragma unroll\n  for (int e = 0; e < " << kEPT << "; ++e) {\n";
+    src << "    const " << em.idx_t << " lin = ((" << em.idx_t << ")blockIdx.x * " << kEPT << " + e) * " << kThreads
+        << " + threadIdx.x;\n";
+    src << "    if (lin >= (" << em.idx_t << ")" << n << "LL) break;\n";
+    src << em.str();
+    src << "  }\n}\n";
+    Launch L;
+    L.kernel = add_kernel(src.str());
+    int64_t blocks = std::max<int64_t>(1, (n + (int64_t)kThreads * kEPT - 1) / ((int64_t)kThreads * kEPT));
+    L.grid[0] = (unsigned)blocks; L.grid[1] = L.grid[2] = 1;
+    L.block[0] = kThreads; L.block[1] = L.block[2] = 1;
+    L.outs = outs;
+    L.ins = em.inputs;
+    return L;
+  }
+
+  // A reduction kernel over `in_shape` along `dims`. `operands` are evaluated by
+  // the emitter (fusion members inline). Writes `outs` (kept-dims shape) or,
+  // when `splits` > 1, partial results laid out [split][kept].
+  struct ReduceGen {
+    std::vector<Value*> operands;      // values reduced
+    std::vector<Value*> inits;
+    std::vector<int64_t> in_shape, dims;
+    Block* body = nullptr;
+    std::vector<DT> dts;
+  };
+
+  Launch gen_reduce_kernel(const ReduceGen& rg, std::function<bool(Op*)> internal, int splits, bool col,
+                           std::vector<Value*> outs) {
+    size_t n = rg.operands.size();
+    std::vector<int64_t> kept_dims, kept_shape, red_shape;
+    for (size_t d = 0; d < rg.in_shape.size(); d++) {
+      if (std::find(rg.dims.begin(), rg.dims.end(), (int64_t)d) == rg.dims.end()) {
+        kept_dims.push_back(d);
+        kept_shape.push_back(rg.in_shape[d]);
+      } else red_shape.push_back(rg.in_shape[d]);
+    }
+    int64_t Nk = 1, Nr = 1;
+    for (auto s : kept_shape) Nk *= s;
+    for (auto s : red_shape) Nr *= s;
+    Emitter em;
+    em.is_internal = internal;
+    em.round_small_floats = true;
+    int64_t total = Nk * std::max<int64_t>(Nr, 1);
+    em.idx_t = total >= (1LL << 31) - 65536 ? "i64" : "int";
+    em.indent_ = 6;
+    // contexts
+    Ctx kc;
+    kc.shape = kept_shape;
+    kc.lin = "o";
+    Ctx rc;
+    rc.shape = red_shape;
+    rc.lin = "r";
+    std::ostringstream pre;       // code before the loop (kept index decomposition, init loads)
+    Emitter pe;
+    pe.is_internal = [](Op*) { return false; };
+    pe.idx_t = em.idx_t;
+    pe.name_prefix = "k";
+    pe.indent_ = 4;
+    pe.ensure_idx(kc);
+    // the emitter for the loop body needs the kept index names; reduced ones are computed inside
+    em.ensure_idx(rc);
+    Ctx oc;
+    oc.shape = rg.in_shape;
+    oc.idx.resize(rg.in_shape.size());
+    {
+      size_t ki = 0, ri = 0;
+      for (size_t d = 0; d < rg.in_shape.size(); d++) {
+        if (std::find(rg.dims.begin(), rg.dims.end(), (int64_t)d) == rg.dims.end()) oc.idx[d] = kc.idx[ki++];
+        else oc.idx[d] = rc.idx[ri++];
+      }
+    }
+    std::vector<std::string> vals;
+    for (auto* v : rg.operands) vals.push_back(em.emit(v, oc));
+    // combine(acc, val)
+    std::vector<std::string> args;
+    for (size_t k = 0; k < n; k++) args.push_back("acc" + std::to_string(k));
+    for (size_t k = 0; k < n; k++) args.push_back(vals[k]);
+    em.round_small_floats = false;
+    auto comb = em.emit_scalar_region(rg.body, args);
+    for (size_t k = 0; k < n; k++) em.line("acc" + std::to_string(k) + " = " + comb[k] + ";");
+    // a second emitter instance renders combine(acc, other) for the cross-thread tree
+    auto tree_combine = [&](Emitter& te, const std::string& other_prefix) {
+      std::vector<std::string> a2;
+      for (size_t k = 0; k < n; k++) a2.push_back("acc" + std::to_string(k));
+      for (size_t k = 0; k < n; k++) a2.push_back(other_prefix + std::to_string(k));
+      te.round_small_floats = false;
+      auto c2 = te.emit_scalar_region(rg.body, a2);
+      for (size_t k = 0; k < n; k++) te.line("acc" + std::to_string(k) + " = " + c2[k] + ";");
+    };
+    // kernel parameters: outputs, then loop inputs, then init values
+    std::vector<Value*> ins = em.inputs;
+    std::vector<std::string> init_names;
+    for (size_t k = 0; k < n; k++) {
+      Value* iv = rg.inits[k];
+      Op* d = iv->def;
+      if (d && d->short_name() == "constant") {
+        DenseValue dv = attr_dense(d->attr("value"));
+        init_names.push_back(literal(dv.type.dt, dv.data.data()));
+      } else {
+        size_t pos = std::find(ins.begin(), ins.end(), iv) - ins.begin();
+        if (pos == ins.size()) ins.push_back(iv);
+        std::string e = "in" + std::to_string(pos) + "[0]";
+        if (iv->type.dt == DT::BF16) e = "bf16_to_f(" + e + ")";
+        else if (iv->type.dt == DT::F16) e = "f16_to_f(" + e + ")";
+        else if (iv->type.dt == DT::PRED) e = "(" + e + " != 0)";
+        init_names.push_back(e);
+      }
+    }
+    std::ostringstream src;
+    const char* it = em.idx_t.c_str();
+    Launch L;
+    L.outs = outs;
+    L.ins = ins;
+    if (col) {
+      // threads along the kept index (coalesced), rows of the reduced range over threadIdx.y and blockIdx.y
+      const int TX = 32, TY = 8;
+      src << "extern \"C\" __global__ void __launch_bounds__(" << TX * TY << ") @NAME@(" << signature(outs, ins) << ") {\n";
+      for (size_t k = 0; k < n; k++)
+        src << "  __shared__ " << c_type(rg.dts[k]) << " sm" << k << "[" << TY << "][" << TX + 1 << "];\n";
+      src << "  const " << it << " o = (" << it << ")blockIdx.x * " << TX << " + threadIdx.x;\n";
+      src << "  const bool live = o < (" << it << ")" << Nk << "LL;\n";
+      for (size_t k = 0; k < n; k++) src << "  " << c_type(rg.dts[k]) << " acc" << k << " = " << init_names[k] << ";\n";
+      src << "  if (live) {\n" << pe.str();
+      src << "    for (" << it << " r = (" << it << ")blockIdx.y * " << TY << " + threadIdx.y; r < (" << it << ")" << Nr
+          << "LL; r += " << TY << " * (" << it << ")gridDim.y) {\n";
+      src << em.str();
+      src << "    }\n  }\n";
+      for (size_t k = 0; k < n; k++) src << "  sm" << k << "[threadIdx.y][threadIdx.x] = acc" << k << ";\n";
+      src << "  __syncthreads();\n";
+      src << "  if (threadIdx.y == 0 && live) {\n";
+      src << "    for (int y = 1; y < " << TY << "; ++y) {\n";
+      for (size_t k = 0; k < n; k++)
+        src << "      const " << c_type(rg.dts[k]) << " oth" << k << " = sm" << k << "[y][threadIdx.x];\n";
+      Emitter te;
+      te.idx_t = em.idx_t;
+      te.name_prefix = "t";
+      te.indent_ = 6;
+      tree_combine(te, "oth");
+      src << te.str();
+      src << "    }\n";
+      for (size_t k = 0; k < n; k++)
+        src << "    out" << k << "[(" << it << ")blockIdx.y * " << Nk << " + o] = "
+            << store_expr(outs[k]->type.dt, "acc" + std::to_string(k)) << ";\n";
+      src << "  }\n}\n";
+      L.grid[0] = (unsigned)((Nk + TX - 1) / TX); L.grid[1] = (unsigned)splits; L.grid[2] = 1;
+      L.block[0] = TX; L.block[1] = TY; L.block[2] = 1;
+    } else {
+      // T threads cooperate on one output; the reduced range is contiguous-ish along threads
+      int T = Nr >= 1024 ? 256 : 32;
+      int per_block = 256 / T;
+      src << "extern \"C\" __global__ void __launch_bounds__(256) @NAME@(" << signature(outs, ins) << ") {\n";
+      if (T == 256)
+        for (size_t k = 0; k < n; k++) src << "  __shared__ " << c_type(rg.dts[k]) << " sm" << k << "[8];\n";
+      src << "  const " << it << " o = (" << it << ")blockIdx.x * " << per_block << " + threadIdx.x / " << T << ";\n";
+      src << "  const int lane = threadIdx.x % " << T << ";\n";
+      src << "  const bool live = o < (" << it << ")" << Nk << "LL;\n";
+      for (size_t k = 0; k < n; k++) src << "  " << c_type(rg.dts[k]) << " acc" << k << " = " << init_names[k] << ";\n";
+      src << "  if (live) {\n" << pe.str();
+      src << "    for (" << it << " r = (" << it << ")blockIdx.y * " << T << " + lane; r < (" << it << ")" << Nr
+          << "LL; r += " << T << " * (" << it << ")gridDim.y) {\n";
+      src << em.str();
+      src << "    }\n  }\n";
+      src << "  #pragma unroll\n  for (int m = 16; m >= 1; m >>= 1) {\n";
+      for (size_t k = 0; k < n; k++)
+        src << "    const " << c_type(rg.dts[k]) << " oth" << k << " = shfl_xor(acc" << k << ", m);\n";
+      {
+        Emitter te;
+        te.idx_t = em.idx_t;
+        te.name_prefix = "t";
+        te.indent_ = 4;
+        tree_combine(te, "oth");
+        src << te.str();
+      }
+      src << "  }\n";
+      if (T == 256) {
+        src << "  const int warp = threadIdx.x / 32;\n";
+        src << "  if ((threadIdx.x & 31) == 0) {";
+        for (size_t k = 0; k < n; k++) src << " sm" << k << "[warp] = acc" << k << ";";
+        src << " }\n  __syncthreads();\n";
+        src << "  if (threadIdx.x == 0) {\n    for (int w = 1; w < 8; ++w) {\n";
+        for (size_t k = 0; k < n; k++)
+          src << "      const " << c_type(rg.dts[k]) << " oth" << k << " = sm" << k << "[w];\n";
+        Emitter te;
+        te.idx_t = em.idx_t;
+        te.name_prefix = "u";
+        te.indent_ = 6;
+        tree_combine(te, "oth");
+        src << te.str();
+        src << "    }\n  }\n";
+      }
+      src << "  if (lane == 0 && live) {\n";
+      for (size_t k = 0; k < n; k++)
+        src << "    out" << k << "[(" << it << ")blockIdx.y * " << Nk << " + o] = "
+            << store_expr(outs[k]->type.dt, "acc" + std::to_string(k)) << ";\n";
+      src << "  }\n}\n";
+      L.grid[0] = (unsigned)((Nk + per_block - 1) / per_block); L.grid[1] = (unsigned)splits; L.grid[2] = 1;
+      L.block[0] = 256; L.block[1] = L.block[2] = 1;
+    }
+    L.kernel = add_kernel(src.str());
+    return L;
+  }
+
+  // ---- implicit GEMM lowering ----------------------------------------------------
+  struct RowEnt { long long off; int h0, w0; };
+  struct ColEnt { long long off; int dh, dw; };
+
+  static std::vector<int64_t> strides_of(const std::vector<int64_t>& dims) {
+    std::vector<int64_t> s(dims.size());
+    int64_t st = 1;
+    for (int d = (int)dims.size() - 1; d >= 0; d--) { s[d] = st; st *= dims[d]; }
+    return s;
+  }
+
+  void choose_split_k(IGemmParams& p) {
+    long long tiles = (long long)((p.M + 127) / 128) * ((p.N + 63) / 64) * p.groups;
+    int split = 1;
+    if (tiles < 148 && p.K >= 512) {
+      split = (int)std::min<long long>((2 * 148 + tiles - 1) / tiles, (p.K + 255) / 256);
+      split = std::max(1, std::min(split, 64));
+    }
+    p.split_k = split;
+  }
+
+  Step lower_conv(Op* op, BlockState& st) {
+    Value *lhs = op->operands[0], *rhs = op->operands[1], *out = op->results[0];
+    if (lhs->type.dt != DT::F32 || rhs->type.dt != DT::F32 || out->type.dt != DT::F32)
+      throw CompileError("stablehlo.convolution: only f32 operands are supported so far, got " + lhs->type.str());
+    std::string dn = op->attr("dimension_numbers");
+    // '#stablehlo.conv<[b, 0, 1, f]x[0, 1, i, o]->[b, 0, 1, f]>' (also accepts the 'raw' keyword-less form)
+    auto parse_spec = [&](const std::string& s) {
+      std::vector<std::string> toks;
+      std::string cur;
+      for (char c : s) {
+        if (c == ',' ) { toks.push_back(cur); cur.clear(); }
+        else if (!isspace((unsigned char)c)) cur += c;
+      }
+      if (!cur.empty()) toks.push_back(cur);
+      return toks;
+    };
+    size_t a0 = dn.find('['), a1 = dn.find(']', a0);
+    size_t b0 = dn.find('[', a1), b1 = dn.find(']', b0);
+    size_t c0 = dn.find('[', b1), c1 = dn.find(']', c0);
+    if (a0 == std::string::npos || c1 == std::string::npos) throw CompileError("convolution: cannot read dimension_numbers");
+    auto ls = parse_spec(dn.substr(a0 + 1, a1 - a0 - 1));
+    auto rs = parse_spec(dn.substr(b0 + 1, b1 - b0 - 1));
+    auto os = parse_spec(dn.substr(c0 + 1, c1 - c0 - 1));
+    if (ls.size() != 4 && ls.size() != 3) throw CompileError("convolution: only 1 or 2 spatial dimensions are supported");
+    const bool one_d = ls.size() == 3;
+    auto pos = [&](const std::vector<std::string>& spec, const std::string& c) -> int {
+      for (size_t k = 0; k < spec.size(); k++)
+        if (spec[k] == c) return (int)k;
+      throw CompileError("convolution: dimension_numbers lacks '" + c + "'");
+    };
+    auto get2 = [&](const char* name, int64_t dflt) {
+      std::vector<int64_t> v = op->has(name) ? attr_i64s(op->attr(name)) : std::vector<int64_t>{};
+      if (v.empty()) v = {dflt, dflt};
+      if (v.size() == 1) v.push_back(dflt);
+      return v;
+    };
+    auto stride = get2("window_strides", 1), ldil = get2("lhs_dilation", 1), rdil = get2("rhs_dilation", 1);
+    std::vector<int64_t> pad = {0, 0, 0, 0};
+    if (op->has("padding")) pad = attr_i64s(op->attr("padding"));
+    while (pad.size() < 4) pad.push_back(0);
+    if (op->has("window_reversal")) {
+      std::string wr = op->attr("window_reversal");
+      if (wr.find("true") != std::string::npos) throw CompileError("convolution: window_reversal is not supported");
+    }
+    int64_t G = op->has("feature_group_count") ? attr_int(op->attr("feature_group_count")) : 1;
+    int64_t BG = op->has("batch_group_count") ? attr_int(op->attr("batch_group_count")) : 1;
+    if (BG > 1 && G > 1) throw CompileError("convolution: feature_group_count and batch_group_count cannot both exceed 1");
+    auto sl = strides_of(lhs->type.dims), sr = strides_of(rhs->type.dims), so = strides_of(out->type.dims);
+    int lb = pos(ls, "b"), lf = pos(ls, "f"), l0 = pos(ls, "0"), l1 = one_d ? -1 : pos(ls, "1");
+    int ro = pos(rs, "o"), ri = pos(rs, "i"), r0 = pos(rs, "0"), r1 = one_d ? -1 : pos(rs, "1");
+    int ob = pos(os, "b"), of = pos(os, "f"), o0 = pos(os, "0"), o1 = one_d ? -1 : pos(os, "1");
+    auto dim_or1 = [](const TensorType& t, int d) -> int64_t { return d < 0 ? 1 : t.dims[d]; };
+    auto str_or0 = [](const std::vector<int64_t>& s, int d) -> int64_t { return d < 0 ? 0 : s[d]; };
+    int64_t Nb = lhs->type.dims[lb] / BG, Cin = lhs->type.dims[lf], H = lhs->type.dims[l0], W = dim_or1(lhs->type, l1);
+    int64_t KH = rhs->type.dims[r0], KW = dim_or1(rhs->type, r1), Cg = rhs->type.dims[ri], O = rhs->type.dims[ro];
+    int64_t OH = out->type.dims[o0], OW = dim_or1(out->type, o1);
+    const int64_t groups = std::max(G, BG);
+    if (Cin != Cg * G || O % groups) throw CompileError("convolution: inconsistent feature groups");
+    int64_t Og = O / groups;
+    const int64_t sl1 = str_or0(sl, l1), sr1 = str_or0(sr, r1), so1 = str_or0(so, o1);
+    IGemmParams p;
+    p.M = (int)(Nb * OH * OW);
+    p.N = (int)Og;
+    p.K = (int)(KH * KW * Cg);
+    p.groups = (int)groups;
+    p.Hd = (int)(H == 0 ? 0 : (H - 1) * ldil[0] + 1);
+    p.Wd = (int)(W == 0 ? 0 : (W - 1) * ldil[1] + 1);
+    p.ldh = (int)ldil[0];
+    p.ldw = (int)ldil[1];
+    p.a_sh = sl[l0];
+    p.a_sw = sl1;
+    p.needs_mask = 1;
+    bool batch_fastest = sl[lb] == 1 && sl[lf] != 1;
+    std::vector<RowEnt> arow(p.M);
+    std::vector<long long> crow(p.M);
+    for (int64_t m = 0; m < p.M; m++) {
+      int64_t n, oh, ow;
+      if (batch_fastest) { n = m % Nb; ow = (m / Nb) % OW; oh = m / (Nb * OW); }
+      else { ow = m % OW; oh = (m / OW) % OH; n = m / (OW * OH); }
+      arow[m] = {n * sl[lb], (int)(oh * stride[0] - pad[0]), (int)(ow * stride[1] - pad[2])};
+      crow[m] = n * so[ob] + oh * so[o0] + ow * so1;
+    }
+    std::vector<ColEnt> acol(p.K);
+    std::vector<long long> bcol(p.K);
+    for (int64_t k = 0; k < p.K; k++) {
+      int64_t c = k % Cg, kw = (k / Cg) % KW, kh = k / (Cg * KW);
+      acol[k] = {c * sl[lf], (int)(kh * rdil[0]), (int)(kw * rdil[1])};
+      bcol[k] = c * sr[ri] + kh * sr[r0] + kw * sr1;
+    }
+    std::vector<long long> bn(p.N), cn(p.N), ag(groups), bg(groups), cg(groups);
+    for (int64_t n = 0; n < p.N; n++) { bn[n] = n * sr[ro]; cn[n] = n * so[of]; }
+    for (int64_t g = 0; g < groups; g++) {
+      // feature groups slice the input channels; batch groups slice the input batch (linalg.cc:339-362)
+      ag[g] = BG > 1 ? g * Nb * sl[lb] : g * Cg * sl[lf];
+      bg[g] = g * Og * sr[ro];
+      cg[g] = g * Og * so[of];
+    }
+    p.a_contig = (sl[lf] == 1 && Cg > 1) ? 0 : (batch_fastest ? 1 : 0);
+    p.b_contig = sr[ro] == 1 ? 0 : 1;
+    choose_split_k(p);
+    return make_igemm(op, p, lhs, rhs, out, arow, acol, bcol, bn, crow, cn, ag, bg, cg, st);
+  }
+
+  Step lower_dot(Op* op, BlockState& st) {
+    Value *lhs = op->operands[0], *rhs = op->operands[1], *out = op->results[0];
+    if (lhs->type.dt != DT::F32 || rhs->type.dt != DT::F32 || out->type.dt != DT::F32)
+      throw CompileError("stablehlo.dot_general: only f32 operands are supported so far, got " + lhs->type.str());
+    auto f = attr_struct(op->attr("dot_dimension_numbers"));
+    auto lbd = f["lhs_batching_dimensions"], rbd = f["rhs_batching_dimensions"];
+    auto lcd = f["lhs_contracting_dimensions"], rcd = f["rhs_contracting_dimensions"];
+    auto in = [](const std::vector<int64_t>& v, int64_t x) { return std::find(v.begin(), v.end(), x) != v.end(); };
+    std::vector<int64_t> lfree, rfree;
+    for (int d = 0; d < lhs->type.rank(); d++) if (!in(lbd, d) && !in(lcd, d)) lfree.push_back(d);
+    for (int d = 0; d < rhs->type.rank(); d++) if (!in(rbd, d) && !in(rcd, d)) rfree.push_back(d);
+    auto sl = strides_of(lhs->type.dims), sr = strides_of(rhs->type.dims);
+    auto extent = [](const std::vector<int64_t>& dims, const std::vector<int64_t>& which) {
+      int64_t n = 1;
+      for (auto d : which) n *= dims[d];
+      return n;
+    };
+    int64_t G = extent(lhs->type.dims, lbd), M = extent(lhs->type.dims, lfree), K = extent(lhs->type.dims, lcd),
+            N = extent(rhs->type.dims, rfree);
+    // offset of the multi-index (row-major over `which`) in a tensor with strides s
+    auto offsets = [](const std::vector<int64_t>& dims, const std::vector<int64_t>& s, const std::vector<int64_t>& which,
+                      int64_t count) {
+      std::vector<long long> out(count);
+      for (int64_t i = 0; i < count; i++) {
+        int64_t rem = i;
+        long long off = 0;
+        for (int q = (int)which.size() - 1; q >= 0; q--) {
+          int64_t dsz = dims[which[q]];
+          off += (rem % dsz) * s[which[q]];
+          rem /= dsz;
+        }
+        out[i] = off;
+      }
+      return out;
+    };
+    IGemmParams p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.groups = (int)G;
+    p.needs_mask = 0;
+    auto am = offsets(lhs->type.dims, sl, lfree, M), ak = offsets(lhs->type.dims, sl, lcd, K);
+    auto bk = offsets(rhs->type.dims, sr, rcd, K), bn = offsets(rhs->type.dims, sr, rfree, N);
+    auto ag = offsets(lhs->type.dims, sl, lbd, G), bg = offsets(rhs->type.dims, sr, rbd, G);
+    std::vector<RowEnt> arow(M);
+    std::vector<ColEnt> acol(K);
+    std::vector<long long> crow(M), cn(N), cg(G);
+    for (int64_t m = 0; m < M; m++) { arow[m] = {am[m], 0, 0}; crow[m] = m * N; }
+    for (int64_t k = 0; k < K; k++) acol[k] = {ak[k], 0, 0};
+    for (int64_t n = 0; n < N; n++) cn[n] = n;
+    for (int64_t g = 0; g < G; g++) cg[g] = g * M * N;
+    p.a_contig = (K > 1 && ak[1] == 1) ? 0 : ((M > 1 && am[1] == 1) ? 1 : 0);
+    p.b_contig = (N > 1 && bn[1] == 1) ? 0 : 1;
+    choose_split_k(p);
+    return make_igemm(op, p, lhs, rhs, out, arow, acol, bk, bn, crow, cn, ag, bg, cg, st);
+  }
+
+  Step make_igemm(Op* op, IGemmParams p, Value* lhs, Value* rhs, Value* out, const std::vector<RowEnt>& arow,
+                  const std::vector<ColEnt>& acol, const std::vector<long long>& bcol, const std::vector<long long>& bn,
+                  const std::vector<long long>& crow, const std::vector<long long>& cn, const std::vector<long long>& ag,
+                  const std::vector<long long>& bg, const std::vector<long long>& cg, BlockState& st) {
+    Step s;
+    s.kind = Step::IGEMM;
+    s.label = op->name;
+    s.ig = p;
+    auto tab = [&](const void* d, size_t n) { return table_slot(d, std::max<size_t>(n, 1)); };
+    s.args = {slot_of.at(lhs), slot_of.at(rhs), slot_of.at(out),
+              tab(arow.data(), arow.size() * sizeof(RowEnt)), tab(acol.data(), acol.size() * sizeof(ColEnt)),
+              tab(bcol.data(), bcol.size() * 8), tab(bn.data(), bn.size() * 8), tab(crow.data(), crow.size() * 8),
+              tab(cn.data(), cn.size() * 8), tab(ag.data(), ag.size() * 8), tab(bg.data(), bg.size() * 8),
+              tab(cg.data(), cg.size() * 8)};
+    if (p.split_k > 1) {
+      TensorType t;
+      t.dt = DT::F32;
+      t.dims = {(int64_t)p.split_k, (int64_t)p.groups, (int64_t)p.M, (int64_t)p.N};
+      s.args.push_back(new_slot(Slot::TEMP, t, st.arena));
+    }
+    return s;
+  }
+
+  // ---- block -> steps ----------------------------------------------------------------
+  void ensure_slot(Value* v, BlockState& st) {
+    if (slot_of.count(v)) return;
+    if (v->type.dt == DT::TOKEN) {
+      TensorType t;
+      t.dt = DT::U8;
+      slot_of[v] = new_slot(Slot::TEMP, t, st.arena);
+      return;
+    }
+    slot_of[v] = new_slot(Slot::TEMP, v->type, st.arena);
+  }
+
+  void add_launch(Plan& plan, const Launch& L, const std::string& label, BlockState& st) {
+    Step s;
+    s.kind = Step::KERNEL;
+    s.kernel = L.kernel;
+    s.label = label;
+    for (int k = 0; k < 3; k++) { s.grid[k] = L.grid[k]; s.block[k] = L.block[k]; }
+    for (auto* o : L.outs) { ensure_slot(o, st); s.args.push_back(slot_of.at(o)); }
+    for (auto* i : L.ins) {
+      if (!slot_of.count(i)) throw CompileError("internal: kernel input without storage: " + i->name + " (" + label + ")");
+      s.args.push_back(slot_of.at(i));
+    }
+    plan.steps.push_back(std::move(s));
+  }
+
+  std::string group_label(Group* g) {
+    std::map<std::string, int> cnt;
+    for (auto* m : g->members) cnt[m->short_name()]++;
+    std::string s = g->is_reduce ? "reduce_fusion{" : "fusion{";
+    bool first = true;
+    for (auto& kv : cnt) { s += (first ? "" : ",") + kv.first + (kv.second > 1 ? "x" + std::to_string(kv.second) : ""); first = false; }
+    return s + "}";
+  }
+
+  void emit_group(Group* g, Plan& plan, BlockState& st) {
+    if (!g->is_reduce) {
+      // a lone reshape of a value that already lives in memory is a view
+      if (g->members.size() == 1 && g->roots.size() == 1 && g->roots[0]->short_name() == "reshape") {
+        Value* src = g->roots[0]->operands[0];
+        if (slot_of.count(src) && !(src->def && is_dup(src->def) && !st.dup_materialize.count(src->def))) {
+          slot_of[g->roots[0]->results[0]] = slot_of.at(src);
+          return;
+        }
+      }
+      if (g->roots[0]->results[0]->type.numel() == 0) {
+        for (auto* r : g->roots) ensure_slot(r->results[0], st);
+        return;
+      }
+      Launch L = gen_pointwise(g, st);
+      add_launch(plan, L, group_label(g), st);
+      return;
+    }
+    Op* r = g->roots[0];
+    size_t n = r->operands.size() / 2;
+    ReduceGen rg;
+    rg.operands.assign(r->operands.begin(), r->operands.begin() + n);
+    rg.inits.assign(r->operands.begin() + n, r->operands.end());
+    rg.in_shape = r->operands[0]->type.dims;
+    rg.dims = attr_i64s(r->attr("dimensions"));
+    rg.body = r->regions[0].get();
+    for (auto* v : r->results) rg.dts.push_back(v->type.dt);
+    for (auto* iv : rg.inits)
+      if (!(iv->def && iv->def->short_name() == "constant")) {
+        if (!slot_of.count(iv)) throw CompileError("reduce: init value must be a constant or live in memory");
+      }
+    std::vector<int64_t> kept_shape;
+    int64_t Nk = 1, Nr = 1, trailing = 1;
+    int last_red = -1;
+    for (size_t d = 0; d < rg.in_shape.size(); d++) {
+      bool red = std::find(rg.dims.begin(), rg.dims.end(), (int64_t)d) != rg.dims.end();
+      if (red) { Nr *= rg.in_shape[d]; last_red = (int)d; }
+      else { Nk *= rg.in_shape[d]; kept_shape.push_back(rg.in_shape[d]); }
+    }
+    for (size_t d = last_red + 1; d < rg.in_shape.size(); d++) trailing *= rg.in_shape[d];
+    std::vector<Value*> outs(r->results.begin(), r->results.end());
+    if (Nk == 0) { for (auto* o : outs) ensure_slot(o, st); return; }
+    bool col = trailing >= 16;
+    // parallelism: split the reduced range over blockIdx.y when there are few outputs
+    int64_t blocks = col ? (Nk + 31) / 32 : (Nk + (Nr >= 1024 ? 0 : 7)) / (Nr >= 1024 ? 1 : 8);
+    int64_t per_split_min = col ? 64 : (Nr >= 1024 ? 4096 : 256);
+    int splits = 1;
+    if (blocks < 296 && Nr > per_split_min) {
+      splits = (int)std::min<int64_t>((296 + blocks - 1) / blocks, (Nr + per_split_min - 1) / per_split_min);
+      splits = std::max(1, std::min(splits, 256));
+    }
+    auto internal = [this, g, &st](Op* o) {
+      return (g->members.count(o) && categorize(o) != Cat::REDUCE) || (is_dup(o) && !st.dup_materialize.count(o));
+    };
+    if (splits == 1) {
+      Launch L = gen_reduce_kernel(rg, internal, 1, col, outs);
+      add_launch(plan, L, group_label(g), st);
+      return;
+    }
+    // pass 1 -> partials [splits, kept...]; pass 2 reduces dim 0 with the same combiner
+    std::vector<Value*> partials;
+    for (size_t k = 0; k < n; k++) {
+      TensorType t;
+      t.dt = rg.dts[k];
+      t.dims.push_back(splits);
+      for (auto s : kept_shape) t.dims.push_back(s);
+      Value* pv = synth(t);
+      partials.push_back(pv);
+    }
+    Launch L1 = gen_reduce_kernel(rg, internal, splits, col, partials);
+    add_launch(plan, L1, group_label(g) + ".partial", st);
+    ReduceGen r2;
+    r2.operands = partials;
+    r2.inits = rg.inits;
+    r2.in_shape = partials[0]->type.dims;
+    r2.dims = {0};
+    r2.body = rg.body;
+    r2.dts = rg.dts;
+    Launch L2 = gen_reduce_kernel(r2, [](Op*) { return false; }, 1, Nk >= 16, outs);
+    add_launch(plan, L2, group_label(g) + ".final", st);
+  }
+
+  void materialize_dup(Op* op, Plan& plan, BlockState& st) {
+    Value* v = op->results[0];
+    if (slot_of.count(v)) return;
+    if (op->short_name() == "constant") {
+      DenseValue dv = attr_dense(op->attr("value"));
+      slot_of[v] = const_slot(dv.type, dv.data);
+      return;
+    }
+    Group g;
+    g.id = next_group_id++;
+    g.members.insert(op);
+    g.roots.push_back(op);
+    g.identity.insert(op);
+    if (v->type.numel() == 0) { ensure_slot(v, st); return; }
+    // operand of a broadcast must itself be in memory or duplicable
+    Launch L = gen_pointwise(&g, st);
+    add_launch(plan, L, op->short_name(), st);
+  }
+
+  long long static_trip_count(Op* w) {
+    // Counted-loop form (src/pjrt_plugin/ops/control_flow.cc:223-312): cond is `compare LT, counter, limit`
+    // with a constant limit, body adds a positive constant to the counter, init is a constant.
+    Block* cond = w->regions[0].get();
+    Block* body = w->regions[1].get();
+    Op* ret = cond->ops.back().get();
+    if (ret->operands.size() != 1 || !ret->operands[0]->def) return -1;
+    Op* cmp = ret->operands[0]->def;
+    if (cmp->short_name() != "compare" || attr_enum(cmp->attr("comparison_direction")) != "LT") return -1;
+    Value* counter = cmp->operands[0];
+    if (counter->def || counter->owner != cond) return -1;
+    int ci = counter->arg_index;
+    auto const_int = [&](Value* v, long long& out) -> bool {
+      if (!v->def || v->def->short_name() != "constant") return false;
+      DenseValue dv = attr_dense(v->def->attr("value"));
+      if (dv.type.numel() != 1 || !dt_is_int(dv.type.dt)) return false;
+      long long x = 0;
+      switch (dv.type.dt) {
+        case DT::I32: { int32_t t; memcpy(&t, dv.data.data(), 4); x = t; break; }
+        case DT::U32: { uint32_t t; memcpy(&t, dv.data.data(), 4); x = t; break; }
+        case DT::I64: case DT::U64: { int64_t t; memcpy(&t, dv.data.data(), 8); x = t; break; }
+        default: return false;
+      }
+      out = x;
+      return true;
+    };
+    long long limit, init, step;
+    if (!const_int(cmp->operands[1], limit)) return -1;
+    if (!const_int(w->operands[ci], init)) return -1;
+    Op* bret = body->ops.back().get();
+    Value* next = bret->operands[ci];
+    if (!next->def || next->def->short_name() != "add") return -1;
+    Value *a = next->def->operands[0], *b = next->def->operands[1];
+    Value* barg = body->args[ci];
+    Value* other = a == barg ? b : (b == barg ? a : nullptr);
+    if (!other || !const_int(other, step) || step <= 0) return -1;
+    if (limit <= init) return 0;
+    return (limit - init + step - 1) / step;
+  }
+
+  void plan_block(Block* block, Plan& plan, int arena, const std::vector<Value*>& returned_vals) {
+    BlockState st;
+    st.block = block;
+    st.arena = arena;
+    int pos = 0;
+    for (auto& op : block->ops) {
+      op->pos = pos++;
+      st.ops.push_back(op.get());
+    }
+    for (auto* v : returned_vals) st.returned.insert(v);
+    for (auto* op : st.ops) {
+      if (categorize(op) == Cat::RETURN) continue;
+      for (auto* o : op->operands) st.users[o].push_back(op);
+      for (auto& r : op->regions) lift_uses(r.get(), op, block, st);
+    }
+    // dead code: results nobody reads (e.g. the input gradient of the first convolution) are not computed
+    {
+      std::set<Op*> live;
+      for (int i = (int)st.ops.size() - 1; i >= 0; i--) {
+        Op* op = st.ops[i];
+        Cat c = categorize(op);
+        bool keep = c == Cat::RETURN || c == Cat::ALL_REDUCE;
+        for (auto* r : op->results) {
+          if (st.returned.count(r)) keep = true;
+          for (auto* u : st.users[r])
+            if (live.count(u)) keep = true;
+        }
+        if (keep) live.insert(op);
+      }
+      std::vector<Op*> kept;
+      for (auto* op : st.ops)
+        if (live.count(op)) kept.push_back(op);
+      if (kept.size() != st.ops.size()) {
+        st.ops = kept;
+        st.users.clear();
+        for (auto* op : st.ops) {
+          if (categorize(op) == Cat::RETURN) continue;
+          for (auto* o : op->operands) st.users[o].push_back(op);
+          for (auto& r : op->regions) lift_uses(r.get(), op, block, st);
+        }
+      }
+    }
+    build_groups(st);
+    for (auto& g : st.groups)
+      for (auto* m : g.members) g.max_pos = std::max(g.max_pos, m->pos);
+
+    // units and their dependencies
+    std::vector<Unit> units;
+    std::map<Op*, int> unit_of_op;          // unit that writes the op's results to memory
+    std::map<Group*, int> unit_of_group;
+    for (auto* op : st.ops) {
+      Cat c = categorize(op);
+      if (c == Cat::RETURN) continue;
+      auto git = st.group_of.find(op);
+      if (git != st.group_of.end()) {
+        for (Group* g : git->second) {
+          if (!unit_of_group.count(g)) {
+            Unit u;
+            u.kind = Unit::GROUP;
+            u.group = g;
+            u.prio = g->max_pos;
+            unit_of_group[g] = (int)units.size();
+            units.push_back(u);
+          }
+          if (std::find(g->roots.begin(), g->roots.end(), op) != g->roots.end()) unit_of_op[op] = unit_of_group[g];
+        }
+        continue;
+      }
+      if (c == Cat::DUP) {
+        if (!st.dup_materialize.count(op)) continue;
+        Unit u;
+        u.kind = Unit::CONST_MAT;
+        u.op = op;
+        u.prio = op->pos;
+        unit_of_op[op] = (int)units.size();
+        units.push_back(u);
+        continue;
+      }
+      Unit u;
+      u.kind = Unit::OP;
+      u.op = op;
+      u.prio = op->pos;
+      unit_of_op[op] = (int)units.size();
+      units.push_back(u);
+    }
+    size_t U = units.size();
+    std::vector<std::set<int>> succ(U);
+    std::vector<int> indeg(U, 0);
+    auto add_dep = [&](Value* v, int consumer) {
+      // walks through duplicable ops that are evaluated inline
+      std::vector<Value*> work{v};
+      std::set<Value*> seen;
+      while (!work.empty()) {
+        Value* x = work.back();
+        work.pop_back();
+        if (!seen.insert(x).second) continue;
+        Op* d = x->def;
+        if (!d || d->parent != block) continue;
+        auto it = unit_of_op.find(d);
+        if (it != unit_of_op.end()) {
+          if (it->second != consumer && succ[it->second].insert(consumer).second) indeg[consumer]++;
+          continue;
+        }
+        if (is_dup(d)) for (auto* o : d->operands) work.push_back(o);
+      }
+    };
+    std::function<void(Block*, int)> nested_deps = [&](Block* b, int consumer) {
+      for (auto& op : b->ops) {
+        for (auto* o : op->operands) add_dep(o, consumer);
+        for (auto& r : op->regions) nested_deps(r.get(), consumer);
+      }
+    };
+    for (auto* op : st.ops) {
+      std::vector<int> consumers;
+      auto git = st.group_of.find(op);
+      if (git != st.group_of.end()) for (Group* g : git->second) consumers.push_back(unit_of_group.at(g));
+      else {
+        auto it = unit_of_op.find(op);
+        if (it != unit_of_op.end()) consumers.push_back(it->second);
+      }
+      for (int cu : consumers) {
+        for (auto* o : op->operands) add_dep(o, cu);
+        for (auto& r : op->regions) nested_deps(r.get(), cu);
+      }
+    }
+    // Kahn with original position as priority
+    typedef std::pair<int, int> PI;
+    std::priority_queue<PI, std::vector<PI>, std::greater<PI>> ready;
+    for (size_t u = 0; u < U; u++)
+      if (indeg[u] == 0) ready.push({units[u].prio, (int)u});
+    std::vector<int> order;
+    while (!ready.empty()) {
+      int u = ready.top().second;
+      ready.pop();
+      order.push_back(u);
+      for (int s : succ[u])
+        if (--indeg[s] == 0) ready.push({units[s].prio, s});
+    }
+    if (order.size() != U) throw CompileError("internal: fusion produced a cyclic schedule");
+
+    for (int ui : order) {
+      Unit& u = units[ui];
+      if (u.kind == Unit::GROUP) { emit_group(u.group, plan, st); continue; }
+      if (u.kind == Unit::CONST_MAT) { materialize_dup(u.op, plan, st); continue; }
+      Op* op = u.op;
+      Cat c = categorize(op);
+      switch (c) {
+        case Cat::CONV: case Cat::DOT: {
+          ensure_slot(op->results[0], st);
+          for (auto* o : op->operands)
+            if (!slot_of.count(o)) throw CompileError("internal: operand of " + op->name + " has no storage");
+          if (op->results[0]->type.numel() == 0) break;
+          Step s = c == Cat::CONV ? lower_conv(op, st) : lower_dot(op, st);
+          plan.steps.push_back(std::move(s));
+          break;
+        }
+        case Cat::ALL_REDUCE: {
+          // only sum over all partitions is implemented
+          Block* body = op->regions[0].get();
+          bool is_sum = body->ops.size() == 2 && body->ops[0]->short_name() == "add";
+          if (!is_sum) throw CompileError("all_reduce: only a sum reduction is supported");
+          if (op->has("replica_groups")) {
+            DenseValue rg = attr_dense(op->attr("replica_groups"));
+            if (rg.type.rank() != 2) throw CompileError("all_reduce: replica_groups must be rank 2");   // collectives.cc:22-33
+            int64_t groups = rg.type.dims[0], gsize = rg.type.dims[1];
+            if (groups > 1 || (gsize != opts.num_partitions && gsize != 0 && !(gsize == 1 && opts.num_partitions == 1)))
+              throw CompileError("all_reduce: only one group spanning all " + std::to_string(opts.num_partitions) +
+                                 " partitions is supported (got " + std::to_string(groups) + " x " + std::to_string(gsize) + ")");
+          }
+          for (size_t k = 0; k < op->operands.size(); k++) {
+            Step s;
+            s.kind = Step::ALL_REDUCE;
+            s.label = op->name;
+            s.dtype = op->operands[k]->type.dt;
+            s.bytes = op->operands[k]->type.bytes();
+            ensure_slot(op->results[k], st);
+            s.args = {slot_of.at(op->operands[k]), slot_of.at(op->results[k])};
+            plan.steps.push_back(std::move(s));
+          }
+          break;
+        }
+        case Cat::WHILE: {
+          Step s;
+          s.kind = Step::WHILE;
+          s.label = op->name;
+          s.trip_count = static_trip_count(op);
+          Block* cond = op->regions[0].get();
+          Block* body = op->regions[1].get();
+          size_t n = op->operands.size();
+          for (size_t k = 0; k < n; k++) {
+            ensure_slot(op->results[k], st);
+            int sl = slot_of.at(op->results[k]);
+            s.state.push_back(sl);
+            s.init.push_back(slot_of.at(op->operands[k]));
+            slot_of[cond->args[k]] = sl;
+            slot_of[body->args[k]] = sl;
+          }
+          int a_cond = (int)prog.arena_bytes.size();
+          prog.arena_bytes.push_back(0);
+          int a_body = (int)prog.arena_bytes.size();
+          prog.arena_bytes.push_back(0);
+          auto pc = std::make_unique<Plan>();
+          auto pb = std::make_unique<Plan>();
+          Op* cret = cond->ops.back().get();
+          Op* bret = body->ops.back().get();
+          pc->arena = a_cond;
+          pb->arena = a_body;
+          plan_block(cond, *pc, a_cond, cret->operands);
+          plan_block(body, *pb, a_body, bret->operands);
+          s.pred = slot_of.at(cret->operands[0]);
+          persistent.insert(s.pred);
+          std::set<int> state_set(s.state.begin(), s.state.end());
+          for (size_t k = 0; k < n; k++) {
+            int ns = slot_of.at(bret->operands[k]);
+            if (ns != s.state[k] && state_set.count(ns)) {
+              // a carried value handed to another position: stage it so the copies below cannot clobber it
+              int tmp = new_slot(Slot::TEMP, prog.slots[ns].type, a_body);
+              Step c;
+              c.kind = Step::MEMCPY;
+              c.label = "loop-carried permutation";
+              c.args = {tmp, ns};
+              c.bytes = prog.slots[ns].type.bytes();
+              pb->steps.push_back(std::move(c));
+              ns = tmp;
+            }
+            persistent.insert(ns);
+            s.next.push_back(ns);
+          }
+          s.sub.push_back(std::move(pc));
+          s.sub.push_back(std::move(pb));
+          // every slot read inside the loop stays live across it: list them as args
+          std::set<int> used;
+          std::function<void(const Plan&)> collect = [&](const Plan& p) {
+            for (auto& q : p.steps) {
+              for (int a : q.args) used.insert(a);
+              for (int a : q.init) used.insert(a);
+              for (auto& sp : q.sub) collect(*sp);
+            }
+          };
+          collect(*s.sub[0]);
+          collect(*s.sub[1]);
+          for (int a : used)
+            if (prog.slots[a].arena == arena && prog.slots[a].kind == Slot::TEMP) s.args.push_back(a);
+          plan.steps.push_back(std::move(s));
+          break;
+        }
+        case Cat::TOKEN: {
+          ensure_slot(op->results[0], st);
+          break;
+        }
+        case Cat::PARTITION_ID: {
+          std::vector<uint8_t> b(4);
+          uint32_t id = op->short_name() == "partition_id" ? (uint32_t)partition_id : 0u;
+          memcpy(b.data(), &id, 4);
+          slot_of[op->results[0]] = const_slot(op->results[0]->type, b);
+          break;
+        }
+        default:
+          throw CompileError("operation " + op->name + " is not supported by the B200 plugin");
+      }
+    }
+    // block results must live in memory
+    for (auto* v : returned_vals) {
+      if (slot_of.count(v)) continue;
+      if (v->def && v->def->parent == block && is_dup(v->def)) { materialize_dup(v->def, plan, st); continue; }
+      throw CompileError("internal: returned value without storage: " + v->name);
+    }
+  }
+
+  int partition_id = 0;
+
+  // ---- arena layout ---------------------------------------------------------------
+  void layout_arena(Plan& plan) {
+    const int arena = plan.arena;
+    // liveness over the step sequence of this plan
+    size_t S = plan.steps.size();
+    std::map<int, std::pair<int, int>> live;    // slot -> [first, last]
+    auto touch = [&](int slot, int at) {
+      if (slot < 0) return;
+      const Slot& s = prog.slots[slot];
+      if (s.kind != Slot::TEMP || s.arena != arena) return;
+      auto it = live.find(slot);
+      if (it == live.end()) live[slot] = {at, at};
+      else it->second.second = std::max(it->second.second, at);
+    };
+    for (size_t i = 0; i < S; i++) {
+      Step& s = plan.steps[i];
+      for (int a : s.args) touch(a, (int)i);
+      for (int a : s.state) touch(a, (int)i);
+      for (int a : s.init) touch(a, (int)i);
+      for (int a : s.results) touch(a, (int)i);
+      touch(s.pred, (int)i);
+    }
+    // slots marked persistent (results of nested blocks) live to the end
+    for (int ps : persistent)
+      if (live.count(ps)) live[ps].second = (int)S;
+    for (auto& sub_steps : plan.steps)
+      for (auto& sp : sub_steps.sub) layout_arena(*sp);
+    // greedy first-fit by start time
+    std::vector<std::pair<int, int>> order;   // (first, slot)
+    for (auto& kv : live) order.push_back({kv.second.first, kv.first});
+    std::sort(order.begin(), order.end());
+    struct Blk { size_t off, size; int last; };
+    std::vector<Blk> active;
+    size_t peak = 0;
+    for (auto& pr : order) {
+      int slot = pr.second;
+      int first = pr.first, last = live[slot].second;
+      size_t need = (prog.slots[slot].bytes + 255) & ~(size_t)255;
+      // drop blocks that ended before `first`
+      active.erase(std::remove_if(active.begin(), active.end(), [&](const Blk& b) { return b.last < first; }), active.end());
+      std::sort(active.begin(), active.end(), [](const Blk& a, const Blk& b) { return a.off < b.off; });
+      size_t off = 0;
+      for (auto& b : active) {
+        if (off + need <= b.off) break;
+        off = std::max(off, b.off + b.size);
+      }
+      prog.slots[slot].offset = off;
+      active.push_back({off, need, last});
+      peak = std::max(peak, off + need);
+    }
+    prog.arena_bytes[arena] = std::max(prog.arena_bytes[arena], peak);
+  }
+
+  std::set<int> persistent;
+};
+
+void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& os, int indent) {
+  for (auto& s : p.steps) {
+    os << std::string(indent, ' ');
+    switch (s.kind) {
+      case Step::KERNEL:
+        os << "kernel " << prog.kernels[s.kernel].name << " grid=" << s.grid[0] << "x" << s.grid[1] << " block=" << s.block[0]
+           << "x" << s.block[1] << " " << s.label;
+        break;
+      case Step::IGEMM:
+        os << "igemm M=" << s.ig.M << " N=" << s.ig.N << " K=" << s.ig.K << " G=" << s.ig.groups << " splitK=" << s.ig.split_k
+           << " a_contig=" << s.ig.a_contig << " b_contig=" << s.ig.b_contig << " " << s.label;
+        break;
+      case Step::MEMCPY: os << "memcpy " << s.bytes; break;
+      case Step::WHILE: os << "while trip=" << s.trip_count; break;
+      case Step::ALL_REDUCE: os << "all_reduce " << s.bytes << " bytes"; break;
+      default: os << "step";
+    }
+    os << " args=[";
+    for (size_t k = 0; k < s.args.size() && k < 16; k++) os << (k ? "," : "") << s.args[k];
+    os << "]\n";
+    for (auto& sp : s.sub) dump_plan(prog, *sp, os, indent + 2);
+  }
+}
+
+uint64_t fnv1a(const std::string& s) {
+  uint64_t h = 1469598103934665603ull;
+  for (unsigned char c : s) { h ^= c; h *= 1099511628211ull; }
+  return h;
+}
+
+}  // namespace
+
+std::unique_ptr<CompiledProgram> compile_module(Module& m, const CompileOptions& opts) {
+  auto prog = std::make_unique<CompiledProgram>();
+  prog->name = m.name.empty() ? "main" : m.name;
+  if (m.attrs.count("mhlo.num_partitions")) prog->num_partitions = (int)attr_int(m.attrs.at("mhlo.num_partitions"));
+  if (m.attrs.count("mhlo.num_replicas")) prog->num_replicas = (int)attr_int(m.attrs.at("mhlo.num_replicas"));
+  Func* f = m.main();
+  Inliner inl(m);
+  inl.run(f->body.get());
+  fix_region_operands(f->body.get(), inl);
+  // unsupported-op check names every offender at once (src/pjrt_plugin/stablehlo_parser.cc:167-184)
+  std::set<std::string> bad;
+  collect_unsupported(f->body.get(), bad, false);
+  if (!bad.empty()) {
+    std::string msg = "Unsupported operations for the B200 plugin (no CPU fallback exists):";
+    for (auto& b : bad) msg += " " + b;
+    throw CompileError(msg);
+  }
+  Planner pl(*prog, opts, m);
+  pl.partition_id = opts.partition_id;
+  prog->arena_bytes.push_back(0);
+  Block* body = f->body.get();
+  for (size_t k = 0; k < body->args.size(); k++) {
+    Value* a = body->args[k];
+    prog->arg_types.push_back(a->type);
+    TensorType t = a->type;
+    if (t.dt == DT::TOKEN) { t.dt = DT::U8; t.dims.clear(); }
+    int s = pl.new_slot(Slot::ARG, t, 0);
+    prog->slots[s].index = (int)k;
+    pl.slot_of[a] = s;
+  }
+  Op* ret = body->ops.empty() ? nullptr : body->ops.back().get();
+  if (!ret || ret->name != "func.return") throw CompileError("entry function does not end in func.return");
+  std::vector<Value*> rets;
+  for (auto* v : ret->operands) rets.push_back(inl.res(v));
+  pl.plan_block(body, prog->main, 0, rets);
+  // results: a TEMP defined by main becomes the result buffer itself; anything else is copied
+  std::set<int> claimed;
+  for (size_t k = 0; k < rets.size(); k++) {
+    ResultInfo ri;
+    ri.type = rets[k]->type;
+    if (ri.type.dt == DT::TOKEN) { ri.type.dt = DT::U8; ri.type.dims.clear(); }
+    int s = pl.slot_of.at(rets[k]);
+    if (prog->slots[s].kind == Slot::TEMP && prog->slots[s].arena == 0 && !claimed.count(s)) {
+      prog->slots[s].kind = Slot::RESULT;
+      prog->slots[s].index = (int)k;
+      claimed.insert(s);
+      ri.slot = s;
+    } else {
+      int rs = pl.new_slot(Slot::RESULT, ri.type, 0);
+      prog->slots[rs].index = (int)k;
+      Step c;
+      c.kind = Step::MEMCPY;
+      c.label = "result copy";
+      c.args = {rs, s};
+      c.bytes = ri.type.bytes();
+      prog->main.steps.push_back(std::move(c));
+      ri.slot = rs;
+    }
+    // donation hints (jax: tf.aliasing_output = k / jax.buffer_donor = true)
+    for (size_t a = 0; a < f->arg_attrs.size(); a++) {
+      auto it = f->arg_attrs[a].find("tf.aliasing_output");
+      if (it != f->arg_attrs[a].end() && attr_int(it->second) == (int64_t)k) ri.donated_arg = (int)a;
+    }
+    prog->results.push_back(ri);
+  }
+  pl.layout_arena(prog->main);
+  // static launch count
+  {
+    bool dynamic = false;
+    std::function<long long(const Plan&)> count = [&](const Plan& p) -> long long {
+      long long n = 0;
+      for (auto& s : p.steps) {
+        if (s.kind == Step::KERNEL || s.kind == Step::ALL_REDUCE) n += 1;
+        else if (s.kind == Step::IGEMM) n += s.ig.split_k > 1 ? 2 : 1;
+        else if (s.kind == Step::WHILE) {
+          if (s.trip_count < 0) { dynamic = true; continue; }
+          n += (s.trip_count + 1) * count(*s.sub[0]) + s.trip_count * count(*s.sub[1]);
+        }
+      }
+      return n;
+    };
+    long long n = count(prog->main);
+    prog->launches_per_execute = dynamic ? -1 : (int)n;
+  }
+  std::ostringstream os;
+  os << "program " << prog->name << ": " << prog->kernels.size() << " generated kernels, " << prog->slots.size()
+     << " slots, arena0 " << prog->arena_bytes[0] << " bytes\n";
+  dump_plan(*prog, prog->main, os, 2);
+  prog->dump = os.str();
+  std::string all;
+  for (auto& k : prog->kernels) all += k.body;
+  char buf[32];
+  snprintf(buf, sizeof buf, "%016llx", (unsigned long long)fnv1a(all + prog->dump));
+  prog->fingerprint = buf;
+  return prog;
+}
+
+}  // namespace b200

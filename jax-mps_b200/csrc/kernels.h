@@ -1,0 +1,20 @@
+// Launchers of the statically compiled device kernels (kernels.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace b200 {
+
+struct IGemmLaunch {
+  int M, N, K, groups, split_k;
+  int Hd, Wd, ldh, ldw;          // dilated input extent and input dilation (masking)
+  long long a_sh, a_sw;          // input strides of the two spatial dims
+  int a_mcontig, b_kcontig, mask;
+};
+
+// tables: a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp (device pointers).
+// `partial` is the split-K scratch ([split_k][groups][M][N] floats) or null when split_k == 1.
+// Adds the number of kernels launched to *launches.
+cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B, void* C, const void* const* tables,
+                             void* partial, cudaStream_t stream, int* launches);
+
+}  // namespace b200

@@ -1,0 +1,1287 @@
+// Client, buffers, events, executable loading and plan execution, and the C
+// ABI declared in include/b200_core.h.
+//
+// Reference counterparts: MlxClient (src/pjrt_plugin/mlx_client.cc:19-66),
+// MlxBuffer (mlx_buffer.cc:104-335), PJRT_Event + CompletionService
+// (pjrt_event.cc:28-150), MlxExecutable::Execute (mlx_executable.cc:799-1008)
+// and the PJRT entry points in pjrt_client.cc / pjrt_buffer.cc /
+// pjrt_executable.cc. Differences by design: one CUDA device per process,
+// three streams (compute, host-to-device, device-to-host) ordered by events
+// instead of one process-wide mutex around a lazy graph, a stream-ordered
+// memory pool (cudaMallocAsync), pinned staging for pageable host arrays, a
+// static kernel plan instead of trace-and-replay, NCCL for all_reduce.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
+#include <nvrtc.h>
+
+#include <atomic>
+#include <condition_variable>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <deque>
+#include <functional>
+#include <map>
+#include <mutex>
+#include <thread>
+
+#include "../../include/b200_core.h"
+#include "kernels.h"
+#include "plan.h"
+
+using namespace b200;
+
+struct b200_error {
+  std::string message;
+  b200_error_code code;
+};
+
+namespace {
+
+b200_error* make_error(b200_error_code code, const std::string& msg) { return new b200_error{msg, code}; }
+
+#define CUDA_TRY(expr)                                                                                   \
+  do {                                                                                                   \
+    cudaError_t _e = (expr);                                                                             \
+    if (_e != cudaSuccess)                                                                               \
+      return make_error(_e == cudaErrorMemoryAllocation ? B200_RESOURCE_EXHAUSTED : B200_INTERNAL,       \
+                        std::string(#expr) + " failed: " + cudaGetErrorString(_e));                      \
+  } while (0)
+
+int log_level() {
+  static int lvl = [] {
+    const char* e = getenv("B200_LOG_LEVEL");
+    return e ? atoi(e) : 1;
+  }();
+  return lvl;
+}
+void logf(int lvl, const char* fmt, ...) {
+  if (lvl > log_level()) return;
+  va_list ap;
+  va_start(ap, fmt);
+  fprintf(stderr, "[b200] ");
+  vfprintf(stderr, fmt, ap);
+  fprintf(stderr, "\n");
+  va_end(ap);
+}
+
+// ---- driver / NVRTC / NCCL entry points, resolved at first use ----------------
+struct DriverApi {
+  CUresult (*ModuleLoadData)(CUmodule*, const void*) = nullptr;
+  CUresult (*ModuleUnload)(CUmodule) = nullptr;
+  CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+  CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+                           void**, void**) = nullptr;
+  CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
+  std::string error;
+  bool ok = false;
+};
+
+DriverApi& driver() {
+  static DriverApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    auto get = [&](const char* name, void** fn) {
+      cudaDriverEntryPointQueryResult st;
+      cudaError_t e = cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &st);
+      if (e != cudaSuccess || st != cudaDriverEntryPointSuccess || !*fn) {
+        api.error = std::string("CUDA driver entry point ") + name + " not available";
+        return false;
+      }
+      return true;
+    };
+    api.ok = get("cuModuleLoadData", (void**)&api.ModuleLoadData) && get("cuModuleUnload", (void**)&api.ModuleUnload) &&
+             get("cuModuleGetFunction", (void**)&api.ModuleGetFunction) &&
+             get("cuLaunchKernel", (void**)&api.LaunchKernel) && get("cuGetErrorString", (void**)&api.GetErrorString);
+  });
+  return api;
+}
+
+struct NvrtcApi {
+  nvrtcResult (*CreateProgram)(nvrtcProgram*, const char*, const char*, int, const char* const*, const char* const*);
+  nvrtcResult (*CompileProgram)(nvrtcProgram, int, const char* const*);
+  nvrtcResult (*GetCUBINSize)(nvrtcProgram, size_t*);
+  nvrtcResult (*GetCUBIN)(nvrtcProgram, char*);
+  nvrtcResult (*GetProgramLogSize)(nvrtcProgram, size_t*);
+  nvrtcResult (*GetProgramLog)(nvrtcProgram, char*);
+  nvrtcResult (*DestroyProgram)(nvrtcProgram*);
+  const char* (*GetErrorString)(nvrtcResult);
+  std::string error;
+  bool ok = false;
+};
+
+NvrtcApi& nvrtc() {
+  static NvrtcApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* h = nullptr;
+    const char* env = getenv("B200_NVRTC_PATH");
+    const char* names[] = {env, "/usr/local/cuda/lib64/libnvrtc.so.12", "libnvrtc.so.12", "libnvrtc.so"};
+    for (const char* n : names) {
+      if (!n) continue;
+      h = dlopen(n, RTLD_NOW | RTLD_LOCAL);
+      if (h) break;
+    }
+    if (!h) {
+      api.error = "cannot load libnvrtc.so.12 (set B200_NVRTC_PATH)";
+      return;
+    }
+    bool ok = true;
+    auto get = [&](const char* name, void** fn) {
+      *fn = dlsym(h, name);
+      if (!*fn) { ok = false; api.error = std::string("libnvrtc lacks ") + name; }
+    };
+    get("nvrtcCreateProgram", (void**)&api.CreateProgram);
+    get("nvrtcCompileProgram", (void**)&api.CompileProgram);
+    get("nvrtcGetCUBINSize", (void**)&api.GetCUBINSize);
+    get("nvrtcGetCUBIN", (void**)&api.GetCUBIN);
+    get("nvrtcGetProgramLogSize", (void**)&api.GetProgramLogSize);
+    get("nvrtcGetProgramLog", (void**)&api.GetProgramLog);
+    get("nvrtcDestroyProgram", (void**)&api.DestroyProgram);
+    get("nvrtcGetErrorString", (void**)&api.GetErrorString);
+    api.ok = ok;
+  });
+  return api;
+}
+
+struct NcclApi {
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*);
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
+  ncclResult_t (*CommDestroy)(ncclComm_t);
+  ncclResult_t (*CommAbort)(ncclComm_t);
+  ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*);
+  ncclResult_t (*GroupStart)();
+  ncclResult_t (*GroupEnd)();
+  const char* (*GetErrorString)(ncclResult_t);
+  std::string error;
+  bool ok = false;
+};
+
+NcclApi& nccl() {
+  static NcclApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* h = nullptr;
+    const char* env = getenv("B200_NCCL_PATH");
+    const char* names[] = {env, "libnccl.so.2", "/usr/lib/x86_64-linux-gnu/libnccl.so.2"};
+    for (const char* n : names) {
+      if (!n) continue;
+      h = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+      if (h) break;
+    }
+    if (!h) {
+      api.error = "cannot load libnccl.so.2 (set B200_NCCL_PATH)";
+      return;
+    }
+    bool ok = true;
+    auto get = [&](const char* name, void** fn) {
+      *fn = dlsym(h, name);
+      if (!*fn) { ok = false; api.error = std::string("libnccl lacks ") + name; }
+    };
+    get("ncclGetUniqueId", (void**)&api.GetUniqueId);
+    get("ncclCommInitRank", (void**)&api.CommInitRank);
+    get("ncclAllReduce", (void**)&api.AllReduce);
+    get("ncclCommDestroy", (void**)&api.CommDestroy);
+    get("ncclCommAbort", (void**)&api.CommAbort);
+    get("ncclCommGetAsyncError", (void**)&api.CommGetAsyncError);
+    get("ncclGroupStart", (void**)&api.GroupStart);
+    get("ncclGroupEnd", (void**)&api.GroupEnd);
+    get("ncclGetErrorString", (void**)&api.GetErrorString);
+    api.ok = ok;
+  });
+  return api;
+}
+
+size_t dtype_size(b200_dtype d) {
+  switch (d) {
+    case B200_PRED: case B200_S8: case B200_U8: return 1;
+    case B200_S16: case B200_U16: case B200_F16: case B200_BF16: return 2;
+    case B200_S32: case B200_U32: case B200_F32: return 4;
+    case B200_S64: case B200_U64: case B200_F64: return 8;
+    default: return 0;
+  }
+}
+b200_dtype to_api(DT d) {
+  switch (d) {
+    case DT::PRED: return B200_PRED;
+    case DT::I8: return B200_S8;
+    case DT::I16: return B200_S16;
+    case DT::I32: return B200_S32;
+    case DT::I64: return B200_S64;
+    case DT::U8: return B200_U8;
+    case DT::U16: return B200_U16;
+    case DT::U32: return B200_U32;
+    case DT::U64: return B200_U64;
+    case DT::F16: return B200_F16;
+    case DT::F32: return B200_F32;
+    case DT::F64: return B200_F64;
+    case DT::BF16: return B200_BF16;
+    default: return B200_INVALID;
+  }
+}
+
+// ---- completion thread: fires on_ready callbacks (pjrt_event.cc:28-78) ----------
+struct Completion {
+  std::mutex mu;
+  std::condition_variable cv;
+  std::deque<std::function<void()>> q;
+  bool started = false;
+  void post(std::function<void()> f) {
+    std::lock_guard<std::mutex> l(mu);
+    if (!started) {
+      started = true;
+      std::thread([this] {
+        for (;;) {
+          std::function<void()> f;
+          {
+            std::unique_lock<std::mutex> l(mu);
+            cv.wait(l, [this] { return !q.empty(); });
+            f = std::move(q.front());
+            q.pop_front();
+          }
+          f();
+        }
+      }).detach();
+    }
+    q.push_back(std::move(f));
+    cv.notify_one();
+  }
+};
+Completion& completion() {
+  static Completion* c = new Completion();   // never destroyed: the thread outlives static destructors
+  return *c;
+}
+
+}  // namespace
+
+struct b200_event {
+  cudaEvent_t ev = nullptr;       // null: ready at creation
+  int device = 0;
+  std::string error;              // non-empty: the event completed with an error
+  b200_error_code code = B200_OK;
+  ~b200_event() {
+    if (ev) cudaEventDestroy(ev);
+  }
+};
+
+struct PinnedBlock {
+  void* ptr = nullptr;
+  size_t size = 0;
+  cudaEvent_t ev = nullptr;
+  bool in_flight = false;
+};
+
+struct LoadedProgram {
+  std::unique_ptr<CompiledProgram> prog;
+  std::vector<CUmodule> modules;
+  std::vector<CUfunction> functions;
+  std::vector<void*> const_ptrs;
+  std::vector<void*> arenas;
+  void* const_block = nullptr;
+  ~LoadedProgram() {
+    for (auto* a : arenas)
+      if (a) cudaFree(a);
+    if (const_block) cudaFree(const_block);
+    if (driver().ok)
+      for (auto m : modules) driver().ModuleUnload(m);
+  }
+};
+
+struct b200_client {
+  int ordinal = 0, rank = 0, nprocs = 1;
+  cudaStream_t compute = nullptr, h2d = nullptr, d2h = nullptr;
+  cudaMemPool_t pool = nullptr;
+  ncclComm_t comm = nullptr;
+  std::recursive_mutex mu;
+  std::string kind, debug, version;
+  std::atomic<int64_t> bytes_in_use{0}, peak_bytes{0}, num_allocs{0}, largest_alloc{0}, launches{0};
+  std::map<std::string, std::shared_ptr<LoadedProgram>> cache;    // program text hash -> loaded plan
+  std::vector<PinnedBlock> pinned;
+  unsigned char* pred_host = nullptr;   // pinned byte for while-loop predicates
+  bool profiling = false;
+  struct ProfEntry { std::string kind; double ms = 0; long long count = 0; };
+  std::map<std::string, ProfEntry> profile;
+  int64_t total_mem = 0;
+
+  void note_alloc(size_t n) {
+    int64_t cur = bytes_in_use.fetch_add((int64_t)n) + (int64_t)n;
+    int64_t pk = peak_bytes.load();
+    while (cur > pk && !peak_bytes.compare_exchange_weak(pk, cur)) {}
+    num_allocs++;
+    int64_t lg = largest_alloc.load();
+    while ((int64_t)n > lg && !largest_alloc.compare_exchange_weak(lg, (int64_t)n)) {}
+  }
+  void note_free(size_t n) { bytes_in_use.fetch_sub((int64_t)n); }
+};
+
+struct b200_buffer {
+  b200_client* client = nullptr;
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  b200_dtype dtype = B200_INVALID;
+  std::vector<int64_t> dims;
+  cudaEvent_t ready = nullptr;                 // recorded on the producing stream
+  std::vector<cudaEvent_t> reads;              // pending reads on other streams
+  bool deleted = false;
+};
+
+struct b200_executable {
+  b200_client* client = nullptr;
+  std::shared_ptr<LoadedProgram> lp;
+};
+
+namespace {
+
+b200_error* set_device(b200_client* c) {
+  CUDA_TRY(cudaSetDevice(c->ordinal));
+  return nullptr;
+}
+
+b200_error* device_alloc(b200_client* c, size_t bytes, cudaStream_t stream, void** out) {
+  size_t n = std::max<size_t>(bytes, 16);
+  cudaError_t e = cudaMallocAsync(out, n, stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return make_error(B200_RESOURCE_EXHAUSTED, "device allocation of " + std::to_string(n) + " bytes failed: " +
+                                                   cudaGetErrorString(e));
+  }
+  c->note_alloc(n);
+  return nullptr;
+}
+
+b200_event* new_event_on(b200_client* c, cudaStream_t stream, b200_error** err) {
+  auto* e = new b200_event();
+  e->device = c->ordinal;
+  cudaError_t r = cudaEventCreateWithFlags(&e->ev, cudaEventDisableTiming);
+  if (r == cudaSuccess) r = cudaEventRecord(e->ev, stream);
+  if (r != cudaSuccess) {
+    *err = make_error(B200_INTERNAL, std::string("event creation failed: ") + cudaGetErrorString(r));
+    delete e;
+    return nullptr;
+  }
+  return e;
+}
+
+// Pinned staging blocks are reused once the copy that read them has finished.
+void* acquire_pinned(b200_client* c, size_t bytes, int* index) {
+  for (size_t i = 0; i < c->pinned.size(); i++) {
+    PinnedBlock& b = c->pinned[i];
+    if (b.size < bytes) continue;
+    if (b.in_flight) {
+      if (cudaEventQuery(b.ev) != cudaSuccess) continue;
+      b.in_flight = false;
+    }
+    *index = (int)i;
+    return b.ptr;
+  }
+  PinnedBlock nb;
+  size_t sz = 1 << 20;
+  while (sz < bytes) sz <<= 1;
+  if (cudaMallocHost(&nb.ptr, sz) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  nb.size = sz;
+  cudaEventCreateWithFlags(&nb.ev, cudaEventDisableTiming);
+  c->pinned.push_back(nb);
+  *index = (int)c->pinned.size() - 1;
+  return nb.ptr;
+}
+
+// Packs a strided host array into dense row-major order (mlx_buffer.cc:151-201 does the same row by row).
+void pack_strided(const char* src, char* dst, const int64_t* dims, const int64_t* strides, size_t nd, size_t elem) {
+  if (nd == 0) { memcpy(dst, src, elem); return; }
+  std::vector<int64_t> idx(nd, 0);
+  int64_t total = 1;
+  for (size_t d = 0; d < nd; d++) total *= dims[d];
+  bool inner_dense = strides[nd - 1] == (int64_t)elem;
+  int64_t inner = dims[nd - 1];
+  for (int64_t done = 0; done < total; done += inner) {
+    const char* p = src;
+    for (size_t d = 0; d + 1 < nd; d++) p += idx[d] * strides[d];
+    if (inner_dense) memcpy(dst, p, (size_t)inner * elem);
+    else
+      for (int64_t i = 0; i < inner; i++) memcpy(dst + i * elem, p + i * strides[nd - 1], elem);
+    dst += inner * elem;
+    for (int d = (int)nd - 2; d >= 0; d--) {
+      if (++idx[d] < dims[d]) break;
+      idx[d] = 0;
+    }
+  }
+}
+
+ncclDataType_t nccl_type(DT d, bool* ok) {
+  *ok = true;
+  switch (d) {
+    case DT::F32: return ncclFloat32;
+    case DT::F64: return ncclFloat64;
+    case DT::F16: return ncclFloat16;
+    case DT::BF16: return ncclBfloat16;
+    case DT::I32: return ncclInt32;
+    case DT::U32: return ncclUint32;
+    case DT::I64: return ncclInt64;
+    case DT::U64: return ncclUint64;
+    case DT::I8: return ncclInt8;
+    case DT::U8: return ncclUint8;
+    default: *ok = false; return ncclFloat32;
+  }
+}
+
+// ---- NVRTC compilation of the generated kernels ------------------------------------
+b200_error* build_kernels(LoadedProgram& lp) {
+  CompiledProgram& p = *lp.prog;
+  if (p.kernels.empty()) return nullptr;
+  NvrtcApi& rt = nvrtc();
+  if (!rt.ok) return make_error(B200_FAILED_PRECONDITION, "NVRTC unavailable: " + rt.error);
+  DriverApi& drv = driver();
+  if (!drv.ok) return make_error(B200_FAILED_PRECONDITION, drv.error);
+  size_t n = p.kernels.size();
+  unsigned hw = std::max(1u, std::thread::hardware_concurrency());
+  size_t chunks = std::min<size_t>(std::min<size_t>(hw, 16), (n + 7) / 8);
+  chunks = std::max<size_t>(chunks, 1);
+  std::vector<std::string> cubins(chunks), errors(chunks);
+  std::vector<std::thread> threads;
+  for (size_t c = 0; c < chunks; c++) {
+    threads.emplace_back([&, c] {
+      std::string src = codegen_prelude();
+      for (size_t k = c; k < n; k += chunks) src += p.kernels[k].body + "\n";
+      nvrtcProgram prog;
+      if (rt.CreateProgram(&prog, src.c_str(), "b200_fused.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS) {
+        errors[c] = "nvrtcCreateProgram failed";
+        return;
+      }
+      const char* opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "-lineinfo", "-w"};
+      nvrtcResult r = rt.CompileProgram(prog, 4, opts);
+      if (r != NVRTC_SUCCESS) {
+        size_t ls = 0;
+        rt.GetProgramLogSize(prog, &ls);
+        std::string log(ls, '\0');
+        if (ls) rt.GetProgramLog(prog, &log[0]);
+        errors[c] = std::string("NVRTC: ") + rt.GetErrorString(r) + "\n" + log.substr(0, 4000);
+        rt.DestroyProgram(&prog);
+        return;
+      }
+      size_t cs = 0;
+      rt.GetCUBINSize(prog, &cs);
+      cubins[c].resize(cs);
+      rt.GetCUBIN(prog, &cubins[c][0]);
+      rt.DestroyProgram(&prog);
+    });
+  }
+  for (auto& t : threads) t.join();
+  for (auto& e : errors)
+    if (!e.empty()) return make_error(B200_INTERNAL, "kernel generation failed: " + e);
+  lp.functions.assign(n, nullptr);
+  for (size_t c = 0; c < chunks; c++) {
+    CUmodule mod;
+    CUresult r = drv.ModuleLoadData(&mod, cubins[c].data());
+    if (r != CUDA_SUCCESS) {
+      const char* s = nullptr;
+      drv.GetErrorString(r, &s);
+      return make_error(B200_INTERNAL, std::string("cuModuleLoadData failed: ") + (s ? s : "?"));
+    }
+    lp.modules.push_back(mod);
+    for (size_t k = c; k < n; k += chunks) {
+      r = drv.ModuleGetFunction(&lp.functions[k], mod, p.kernels[k].name.c_str());
+      if (r != CUDA_SUCCESS) return make_error(B200_INTERNAL, "generated kernel " + p.kernels[k].name + " not found in module");
+    }
+  }
+  return nullptr;
+}
+
+struct ExecCtx {
+  b200_client* c;
+  LoadedProgram* lp;
+  std::vector<void*> ptrs;
+  int launches = 0;
+  struct Timed { std::string kind, key; cudaEvent_t a, b; };
+  std::vector<Timed> timed;
+};
+
+b200_error* run_plan(ExecCtx& x, const Plan& plan);
+
+b200_error* run_step(ExecCtx& x, const Step& s) {
+  b200_client* c = x.c;
+  cudaStream_t st = c->compute;
+  switch (s.kind) {
+    case Step::KERNEL: {
+      void* vals[512];
+      void* argv[512];
+      size_t n = s.args.size();
+      if (n > 512) return make_error(B200_INTERNAL, "kernel with more than 512 parameters");
+      for (size_t k = 0; k < n; k++) {
+        vals[k] = x.ptrs[s.args[k]];
+        argv[k] = &vals[k];
+      }
+      CUresult r = driver().LaunchKernel(x.lp->functions[s.kernel], s.grid[0], s.grid[1], s.grid[2], s.block[0], s.block[1],
+                                         s.block[2], 0, (CUstream)st, argv, nullptr);
+      if (r != CUDA_SUCCESS) {
+        const char* msg = nullptr;
+        driver().GetErrorString(r, &msg);
+        return make_error(B200_INTERNAL, "launch of " + s.label + " failed: " + (msg ? msg : "?"));
+      }
+      x.launches++;
+      return nullptr;
+    }
+    case Step::IGEMM: {
+      IGemmLaunch p;
+      p.M = s.ig.M; p.N = s.ig.N; p.K = s.ig.K; p.groups = s.ig.groups; p.split_k = s.ig.split_k;
+      p.Hd = s.ig.Hd; p.Wd = s.ig.Wd; p.ldh = s.ig.ldh; p.ldw = s.ig.ldw;
+      p.a_sh = s.ig.a_sh; p.a_sw = s.ig.a_sw;
+      p.a_mcontig = s.ig.a_contig; p.b_kcontig = s.ig.b_contig; p.mask = s.ig.needs_mask;
+      const void* tables[9];
+      for (int k = 0; k < 9; k++) tables[k] = x.ptrs[s.args[3 + k]];
+      void* partial = s.ig.split_k > 1 ? x.ptrs[s.args[12]] : nullptr;
+      cudaError_t e = launch_igemm_f32(p, x.ptrs[s.args[0]], x.ptrs[s.args[1]], x.ptrs[s.args[2]], tables, partial, st,
+                                       &x.launches);
+      if (e != cudaSuccess) return make_error(B200_INTERNAL, "launch of " + s.label + " failed: " + cudaGetErrorString(e));
+      return nullptr;
+    }
+    case Step::MEMCPY: {
+      if (s.bytes && x.ptrs[s.args[0]] != x.ptrs[s.args[1]])
+        CUDA_TRY(cudaMemcpyAsync(x.ptrs[s.args[0]], x.ptrs[s.args[1]], s.bytes, cudaMemcpyDeviceToDevice, st));
+      return nullptr;
+    }
+    case Step::ALL_REDUCE: {
+      void* in = x.ptrs[s.args[0]];
+      void* out = x.ptrs[s.args[1]];
+      if (c->nprocs == 1) {
+        // one partition: identity (src/pjrt_plugin/ops/collectives.cc:41-47)
+        if (in != out && s.bytes) CUDA_TRY(cudaMemcpyAsync(out, in, s.bytes, cudaMemcpyDeviceToDevice, st));
+        return nullptr;
+      }
+      bool ok;
+      ncclDataType_t t = nccl_type(s.dtype, &ok);
+      if (!ok) return make_error(B200_UNIMPLEMENTED, "all_reduce of this element type");
+      ncclResult_t r = nccl().AllReduce(in, out, s.bytes / dt_size(s.dtype), t, ncclSum, c->comm, st);
+      if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclAllReduce failed: ") + nccl().GetErrorString(r));
+      x.launches++;
+      return nullptr;
+    }
+    case Step::WHILE: {
+      size_t n = s.state.size();
+      for (size_t k = 0; k < n; k++) {
+        void *d = x.ptrs[s.state[k]], *src = x.ptrs[s.init[k]];
+        size_t b = x.lp->prog->slots[s.state[k]].type.bytes();
+        if (d != src && b) CUDA_TRY(cudaMemcpyAsync(d, src, b, cudaMemcpyDeviceToDevice, st));
+      }
+      auto iterate = [&]() -> b200_error* {
+        if (auto* e = run_plan(x, *s.sub[1])) return e;
+        for (size_t k = 0; k < n; k++) {
+          void *d = x.ptrs[s.state[k]], *src = x.ptrs[s.next[k]];
+          size_t b = x.lp->prog->slots[s.state[k]].type.bytes();
+          if (d != src && b) CUDA_TRY(cudaMemcpyAsync(d, src, b, cudaMemcpyDeviceToDevice, st));
+        }
+        return nullptr;
+      };
+      if (s.trip_count >= 0) {
+        // counted loop: trip count known at compile time, no host round trip
+        // (the reference's counted path, src/pjrt_plugin/ops/control_flow.cc:476-503)
+        for (long long i = 0; i < s.trip_count; i++)
+          if (auto* e = iterate()) return e;
+        return nullptr;
+      }
+      for (long long it = 0;; it++) {
+        if (auto* e = run_plan(x, *s.sub[0])) return e;
+        CUDA_TRY(cudaMemcpyAsync(c->pred_host, x.ptrs[s.pred], 1, cudaMemcpyDeviceToHost, st));
+        CUDA_TRY(cudaStreamSynchronize(st));
+        if (!*c->pred_host) break;
+        if (auto* e = iterate()) return e;
+      }
+      return nullptr;
+    }
+    default:
+      return make_error(B200_UNIMPLEMENTED, "plan step kind not implemented: " + s.label);
+  }
+}
+
+b200_error* run_plan(ExecCtx& x, const Plan& plan) {
+  for (auto& s : plan.steps) {
+    bool timed = x.c->profiling && s.kind != Step::WHILE && s.kind != Step::CASE;
+    ExecCtx::Timed t;
+    if (timed) {
+      switch (s.kind) {
+        case Step::KERNEL:
+          t.kind = s.label.rfind("reduce_fusion", 0) == 0 ? "reduce" : "fused";
+          t.key = s.label + " grid=" + std::to_string(s.grid[0]) + "x" + std::to_string(s.grid[1]);
+          break;
+        case Step::IGEMM:
+          t.kind = "igemm";
+          t.key = "igemm M=" + std::to_string(s.ig.M) + " N=" + std::to_string(s.ig.N) + " K=" + std::to_string(s.ig.K) +
+                  " G=" + std::to_string(s.ig.groups) + " splitK=" + std::to_string(s.ig.split_k) + " a_mcontig=" +
+                  std::to_string(s.ig.a_contig) + " b_kcontig=" + std::to_string(s.ig.b_contig) + " mask=" +
+                  std::to_string(s.ig.needs_mask) + " ld=" + std::to_string(s.ig.ldh) + "x" + std::to_string(s.ig.ldw);
+          break;
+        case Step::ALL_REDUCE: t.kind = "all_reduce"; t.key = "all_reduce " + std::to_string(s.bytes); break;
+        default: t.kind = "copy"; t.key = s.label; break;
+      }
+      cudaEventCreate(&t.a);
+      cudaEventCreate(&t.b);
+      cudaEventRecord(t.a, x.c->compute);
+    }
+    if (auto* e = run_step(x, s)) return e;
+    if (timed) {
+      cudaEventRecord(t.b, x.c->compute);
+      x.timed.push_back(t);
+    }
+  }
+  return nullptr;
+}
+
+uint64_t hash_text(const char* s, size_t n, uint64_t seed) {
+  uint64_t h = 1469598103934665603ull ^ seed;
+  for (size_t i = 0; i < n; i++) { h ^= (unsigned char)s[i]; h *= 1099511628211ull; }
+  return h;
+}
+
+}  // namespace
+
+// ===========================================================================
+// C ABI
+// ===========================================================================
+extern "C" {
+
+void b200_error_destroy(b200_error* err) { delete err; }
+const char* b200_error_message(const b200_error* err) { return err ? err->message.c_str() : ""; }
+b200_error_code b200_error_get_code(const b200_error* err) { return err ? err->code : B200_OK; }
+
+b200_error* b200_nccl_unique_id(char out[B200_NCCL_ID_BYTES]) {
+  NcclApi& n = nccl();
+  if (!n.ok) return make_error(B200_FAILED_PRECONDITION, n.error);
+  ncclUniqueId id;
+  static_assert(sizeof(ncclUniqueId) == B200_NCCL_ID_BYTES, "NCCL id size");
+  ncclResult_t r = n.GetUniqueId(&id);
+  if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclGetUniqueId: ") + n.GetErrorString(r));
+  memcpy(out, &id, sizeof id);
+  return nullptr;
+}
+
+b200_error* b200_client_create(const b200_client_options* o, b200_client** out) {
+  if (!out) return make_error(B200_INVALID_ARGUMENT, "client out-pointer is null");
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    return make_error(B200_FAILED_PRECONDITION,
+                      std::string("no CUDA device available (this plugin has no CPU fallback): ") +
+                          (e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0"));
+  }
+  auto c = std::make_unique<b200_client>();
+  int ord = o ? o->device_ordinal : -1;
+  if (ord < 0) {
+    const char* lr = getenv("LOCAL_RANK");
+    ord = lr ? atoi(lr) % count : 0;
+  }
+  if (ord >= count) return make_error(B200_INVALID_ARGUMENT, "device ordinal " + std::to_string(ord) + " out of range");
+  c->ordinal = ord;
+  c->rank = o ? o->process_index : 0;
+  c->nprocs = (o && o->num_processes > 0) ? o->num_processes : 1;
+  CUDA_TRY(cudaSetDevice(ord));
+  CUDA_TRY(cudaFree(0));
+  cudaDeviceProp prop;
+  CUDA_TRY(cudaGetDeviceProperties(&prop, ord));
+  c->kind = prop.name;
+  c->total_mem = (int64_t)prop.totalGlobalMem;
+  c->debug = "B200:" + std::to_string(c->rank) + " (cuda:" + std::to_string(ord) + ", sm_" + std::to_string(prop.major) +
+             std::to_string(prop.minor) + ")";
+  int rtv = 0;
+  cudaRuntimeGetVersion(&rtv);
+  c->version = "cuda " + std::to_string(rtv / 1000) + "." + std::to_string((rtv % 1000) / 10);
+  if (prop.major != 10)
+    logf(1, "warning: device %d is sm_%d%d; generated kernels target sm_100a", ord, prop.major, prop.minor);
+  CUDA_TRY(cudaStreamCreateWithFlags(&c->compute, cudaStreamNonBlocking));
+  CUDA_TRY(cudaStreamCreateWithFlags(&c->h2d, cudaStreamNonBlocking));
+  CUDA_TRY(cudaStreamCreateWithFlags(&c->d2h, cudaStreamNonBlocking));
+  CUDA_TRY(cudaDeviceGetDefaultMemPool(&c->pool, ord));
+  uint64_t thr = (o && o->pool_release_threshold) ? o->pool_release_threshold : UINT64_MAX;
+  CUDA_TRY(cudaMemPoolSetAttribute(c->pool, cudaMemPoolAttrReleaseThreshold, &thr));
+  CUDA_TRY(cudaMallocHost((void**)&c->pred_host, 64));
+  if (!driver().ok) return make_error(B200_FAILED_PRECONDITION, driver().error);
+  if (c->nprocs > 1) {
+    if (!o->nccl_unique_id) return make_error(B200_INVALID_ARGUMENT, "num_processes > 1 needs nccl_unique_id");
+    NcclApi& n = nccl();
+    if (!n.ok) return make_error(B200_FAILED_PRECONDITION, n.error);
+    ncclUniqueId id;
+    memcpy(&id, o->nccl_unique_id, sizeof id);
+    ncclResult_t r = n.CommInitRank(&c->comm, c->nprocs, id, c->rank);
+    if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclCommInitRank: ") + n.GetErrorString(r));
+  }
+  *out = c.release();
+  return nullptr;
+}
+
+b200_error* b200_client_destroy(b200_client* c) {
+  if (!c) return nullptr;
+  cudaSetDevice(c->ordinal);
+  cudaDeviceSynchronize();
+  c->cache.clear();
+  if (c->comm) nccl().CommDestroy(c->comm);
+  for (auto& b : c->pinned) {
+    cudaFreeHost(b.ptr);
+    cudaEventDestroy(b.ev);
+  }
+  if (c->pred_host) cudaFreeHost(c->pred_host);
+  cudaStreamDestroy(c->compute);
+  cudaStreamDestroy(c->h2d);
+  cudaStreamDestroy(c->d2h);
+  delete c;
+  return nullptr;
+}
+
+const char* b200_client_platform_name(const b200_client*) { return "b200"; }
+const char* b200_client_platform_version(const b200_client* c) { return c->version.c_str(); }
+int b200_client_process_index(const b200_client* c) { return c->rank; }
+int b200_client_device_count(const b200_client* c) { return c->nprocs; }
+int b200_client_addressable_device_count(const b200_client*) { return 1; }
+int b200_device_id(const b200_client* c) { return c->rank; }
+int b200_device_local_hardware_id(const b200_client* c) { return c->ordinal; }
+const char* b200_device_kind(const b200_client* c) { return c->kind.c_str(); }
+const char* b200_device_debug_string(const b200_client* c) { return c->debug.c_str(); }
+void* b200_client_compute_stream(b200_client* c) { return (void*)c->compute; }
+int64_t b200_client_launch_count(const b200_client* c) { return c->launches.load(); }
+
+b200_error* b200_device_memory_stats(b200_client* c, b200_memory_stats* s) {
+  if (!c || !s) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  if (auto* e = set_device(c)) return e;
+  s->bytes_in_use = c->bytes_in_use.load();
+  s->peak_bytes_in_use = c->peak_bytes.load(); s->peak_bytes_in_use_is_set = 1;
+  s->bytes_limit = c->total_mem; s->bytes_limit_is_set = 1;
+  uint64_t v = 0;
+  s->pool_bytes_is_set = cudaMemPoolGetAttribute(c->pool, cudaMemPoolAttrReservedMemCurrent, &v) == cudaSuccess;
+  s->pool_bytes = (int64_t)v;
+  s->peak_pool_bytes_is_set = cudaMemPoolGetAttribute(c->pool, cudaMemPoolAttrReservedMemHigh, &v) == cudaSuccess;
+  s->peak_pool_bytes = (int64_t)v;
+  s->num_allocs = c->num_allocs.load(); s->num_allocs_is_set = 1;
+  s->largest_alloc_size = c->largest_alloc.load(); s->largest_alloc_size_is_set = 1;
+  return nullptr;
+}
+
+b200_error* b200_client_set_profiling(b200_client* c, int enabled) {
+  if (!c) return make_error(B200_INVALID_ARGUMENT, "null client");
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  c->profiling = enabled != 0;
+  return nullptr;
+}
+
+b200_error* b200_client_profile_report(b200_client* c, char** json) {
+  if (!c || !json) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  std::string out = "[";
+  bool first = true;
+  for (auto& kv : c->profile) {
+    std::string key;
+    for (char ch : kv.first) { if (ch == '"' || ch == '\\') key += '\\'; key += ch; }
+    char buf[64];
+    snprintf(buf, sizeof buf, "%.6f", kv.second.ms);
+    out += std::string(first ? "" : ",") + "{\"kind\":\"" + kv.second.kind + "\",\"key\":\"" + key + "\",\"ms\":" + buf +
+           ",\"count\":" + std::to_string(kv.second.count) + "}";
+    first = false;
+  }
+  out += "]";
+  c->profile.clear();
+  *json = strdup(out.c_str());
+  return nullptr;
+}
+
+b200_error* b200_client_synchronize(b200_client* c) {
+  if (auto* e = set_device(c)) return e;
+  CUDA_TRY(cudaStreamSynchronize(c->h2d));
+  CUDA_TRY(cudaStreamSynchronize(c->compute));
+  CUDA_TRY(cudaStreamSynchronize(c->d2h));
+  return nullptr;
+}
+
+// ---- compile -------------------------------------------------------------------
+b200_error* b200_client_compile(b200_client* c, const char* code, size_t code_size, const char* format,
+                                const b200_compile_options* o, b200_executable** out) {
+  if (!c || !code || !out) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  *out = nullptr;
+  std::string fmt = format ? format : "mlir";
+  if (fmt != "mlir" && fmt != "hlo" && fmt != "hlo_with_config")
+    return make_error(B200_INVALID_ARGUMENT, "unknown program format '" + fmt + "'");
+  if (code_size >= 4 && memcmp(code, "ML\xefR", 4) == 0)
+    return make_error(B200_UNIMPLEMENTED,
+                      "MLIR bytecode (VHLO portable artifact) cannot be read without the StableHLO libraries; "
+                      "pass the module as text");
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  if (auto* e = set_device(c)) return e;
+  CompileOptions co;
+  co.fuse = !(o && o->disable_fusion) && !(getenv("B200_NO_FUSE") && atoi(getenv("B200_NO_FUSE")));
+  co.partition_id = c->rank;
+  co.num_partitions = c->nprocs;
+  char key[64];
+  snprintf(key, sizeof key, "%016llx-%d-%d-%d", (unsigned long long)hash_text(code, code_size, 0), (int)co.fuse, c->rank,
+           c->nprocs);
+  auto hit = c->cache.find(key);
+  std::shared_ptr<LoadedProgram> lp;
+  if (hit != c->cache.end()) lp = hit->second;
+  else {
+    lp = std::make_shared<LoadedProgram>();
+    try {
+      auto m = parse_module(code, code_size);
+      int np = (o && o->num_partitions > 0) ? o->num_partitions : 0;
+      if (np == 0 && m->attrs.count("mhlo.num_partitions")) np = (int)attr_int(m->attrs.at("mhlo.num_partitions"));
+      if (np > 1 && np != c->nprocs)
+        return make_error(B200_INVALID_ARGUMENT, "program wants " + std::to_string(np) + " partitions but the job has " +
+                                                     std::to_string(c->nprocs) + " processes");
+      lp->prog = compile_module(*m, co);
+    } catch (const CompileError& e) {
+      return make_error(B200_INVALID_ARGUMENT, e.what());
+    } catch (const std::exception& e) {
+      return make_error(B200_INTERNAL, std::string("compiler failure: ") + e.what());
+    }
+    if (const char* d = getenv("B200_DUMP_PLAN")) {
+      if (FILE* f = fopen(d, "a")) { fputs(lp->prog->dump.c_str(), f); fclose(f); }
+      else fputs(lp->prog->dump.c_str(), stderr);
+    }
+    if (auto* e = build_kernels(*lp)) return e;
+    // constants: one device block, uploaded once
+    CompiledProgram& p = *lp->prog;
+    size_t total = 0;
+    std::vector<size_t> offs(p.consts.size());
+    for (size_t k = 0; k < p.consts.size(); k++) {
+      offs[k] = total;
+      total += (p.consts[k].bytes.size() + 255) & ~(size_t)255;
+    }
+    if (total) {
+      CUDA_TRY(cudaMalloc(&lp->const_block, total));
+      std::vector<uint8_t> host(total, 0);
+      for (size_t k = 0; k < p.consts.size(); k++)
+        memcpy(host.data() + offs[k], p.consts[k].bytes.data(), p.consts[k].bytes.size());
+      CUDA_TRY(cudaMemcpy(lp->const_block, host.data(), total, cudaMemcpyHostToDevice));
+    }
+    for (size_t k = 0; k < p.consts.size(); k++) lp->const_ptrs.push_back((char*)lp->const_block + offs[k]);
+    for (size_t a = 0; a < p.arena_bytes.size(); a++) {
+      void* ptr = nullptr;
+      if (p.arena_bytes[a]) {
+        cudaError_t e = cudaMalloc(&ptr, p.arena_bytes[a]);
+        if (e != cudaSuccess) {
+          cudaGetLastError();
+          return make_error(B200_RESOURCE_EXHAUSTED, "cannot allocate " + std::to_string(p.arena_bytes[a]) +
+                                                         " bytes of temporaries: " + cudaGetErrorString(e));
+        }
+      }
+      lp->arenas.push_back(ptr);
+    }
+    c->cache[key] = lp;
+    logf(2, "compiled %s: %zu generated kernels, %zu constants, arena %zu bytes", p.name.c_str(), p.kernels.size(),
+         p.consts.size(), p.arena_bytes[0]);
+  }
+  auto* exe = new b200_executable();
+  exe->client = c;
+  exe->lp = lp;
+  *out = exe;
+  return nullptr;
+}
+
+void b200_string_free(char* s) { free(s); }
+
+b200_error* b200_compile_to_plan(const char* code, size_t code_size, const b200_compile_options* o, int num_processes,
+                                 int process_index, int validate_kernels, char** plan_text, char** cuda_source) {
+  if (!code) return make_error(B200_INVALID_ARGUMENT, "null program");
+  if (plan_text) *plan_text = nullptr;
+  if (cuda_source) *cuda_source = nullptr;
+  CompileOptions co;
+  co.fuse = !(o && o->disable_fusion) && !(getenv("B200_NO_FUSE") && atoi(getenv("B200_NO_FUSE")));
+  co.num_partitions = num_processes > 0 ? num_processes : 1;
+  co.partition_id = process_index;
+  std::unique_ptr<CompiledProgram> prog;
+  try {
+    auto m = parse_module(code, code_size);
+    prog = compile_module(*m, co);
+  } catch (const CompileError& e) {
+    return make_error(B200_INVALID_ARGUMENT, e.what());
+  } catch (const std::exception& e) {
+    return make_error(B200_INTERNAL, std::string("compiler failure: ") + e.what());
+  }
+  std::string src = codegen_prelude();
+  for (auto& k : prog->kernels) src += k.body + "\n";
+  if (validate_kernels && !prog->kernels.empty()) {
+    NvrtcApi& rt = nvrtc();
+    if (!rt.ok) return make_error(B200_FAILED_PRECONDITION, "NVRTC unavailable: " + rt.error);
+    nvrtcProgram np;
+    if (rt.CreateProgram(&np, src.c_str(), "b200_fused.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS)
+      return make_error(B200_INTERNAL, "nvrtcCreateProgram failed");
+    const char* opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "-w"};
+    nvrtcResult r = rt.CompileProgram(np, 3, opts);
+    if (r != NVRTC_SUCCESS) {
+      size_t ls = 0;
+      rt.GetProgramLogSize(np, &ls);
+      std::string log(ls, '\0');
+      if (ls) rt.GetProgramLog(np, &log[0]);
+      rt.DestroyProgram(&np);
+      return make_error(B200_INTERNAL, std::string("generated kernels do not compile: ") + log.substr(0, 4000));
+    }
+    rt.DestroyProgram(&np);
+  }
+  if (plan_text) *plan_text = strdup(prog->dump.c_str());
+  if (cuda_source) *cuda_source = strdup(src.c_str());
+  return nullptr;
+}
+
+b200_error* b200_executable_destroy(b200_executable* e) {
+  delete e;
+  return nullptr;
+}
+const char* b200_executable_name(const b200_executable* e) { return e->lp->prog->name.c_str(); }
+const char* b200_executable_fingerprint(const b200_executable* e) { return e->lp->prog->fingerprint.c_str(); }
+int b200_executable_num_replicas(const b200_executable* e) { return e->lp->prog->num_replicas; }
+int b200_executable_num_partitions(const b200_executable* e) { return e->lp->prog->num_partitions; }
+size_t b200_executable_num_args(const b200_executable* e) { return e->lp->prog->arg_types.size(); }
+size_t b200_executable_num_outputs(const b200_executable* e) { return e->lp->prog->results.size(); }
+int64_t b200_executable_launches_per_execute(const b200_executable* e) { return e->lp->prog->launches_per_execute; }
+int64_t b200_executable_num_kernels(const b200_executable* e) { return (int64_t)e->lp->prog->kernels.size(); }
+int64_t b200_executable_temp_bytes(const b200_executable* e) {
+  int64_t t = 0;
+  for (auto b : e->lp->prog->arena_bytes) t += (int64_t)b;
+  return t;
+}
+const char* b200_executable_plan_text(const b200_executable* e) { return e->lp->prog->dump.c_str(); }
+
+b200_error* b200_executable_output_info(const b200_executable* e, size_t i, b200_dtype* dt, const int64_t** dims,
+                                        size_t* nd) {
+  auto& r = e->lp->prog->results;
+  if (i >= r.size()) return make_error(B200_INVALID_ARGUMENT, "output index out of range");
+  if (dt) *dt = to_api(r[i].type.dt);
+  if (dims) *dims = r[i].type.dims.data();
+  if (nd) *nd = r[i].type.dims.size();
+  return nullptr;
+}
+b200_error* b200_executable_arg_info(const b200_executable* e, size_t i, b200_dtype* dt, const int64_t** dims, size_t* nd) {
+  auto& a = e->lp->prog->arg_types;
+  if (i >= a.size()) return make_error(B200_INVALID_ARGUMENT, "argument index out of range");
+  if (dt) *dt = to_api(a[i].dt);
+  if (dims) *dims = a[i].dims.data();
+  if (nd) *nd = a[i].dims.size();
+  return nullptr;
+}
+
+// ---- buffers ----------------------------------------------------------------------
+b200_error* b200_buffer_from_host(b200_client* c, const void* data, b200_dtype dtype, const int64_t* dims, size_t nd,
+                                  const int64_t* byte_strides, b200_buffer** out, b200_event** done) {
+  if (!c || !out) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  *out = nullptr;
+  if (done) *done = nullptr;
+  size_t es = dtype_size(dtype);
+  if (!es) return make_error(B200_INVALID_ARGUMENT, "unsupported element type " + std::to_string((int)dtype));
+  size_t count = 1;
+  for (size_t d = 0; d < nd; d++) {
+    if (dims[d] < 0) return make_error(B200_INVALID_ARGUMENT, "negative dimension");
+    count *= (size_t)dims[d];
+  }
+  size_t bytes = count * es;
+  // null data only for zero-size arrays (pjrt_client.cc:285-295)
+  if (!data && bytes) return make_error(B200_INVALID_ARGUMENT, "host data pointer is null for a non-empty array");
+  bool dense = true;
+  if (byte_strides) {
+    int64_t st = (int64_t)es;
+    for (int d = (int)nd - 1; d >= 0; d--) {
+      if (byte_strides[d] < 0) return make_error(B200_INVALID_ARGUMENT, "negative byte strides are not supported");   // mlx_buffer.cc:157-163
+      if (dims[d] > 1 && byte_strides[d] != st) dense = false;
+      st *= dims[d];
+    }
+  }
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  if (auto* e = set_device(c)) return e;
+  auto b = std::make_unique<b200_buffer>();
+  b->client = c;
+  b->dtype = dtype;
+  b->dims.assign(dims, dims + nd);
+  b->bytes = bytes;
+  if (auto* e = device_alloc(c, bytes, c->h2d, &b->ptr)) return e;
+  bool host_ready_now = true;
+  if (bytes) {
+    cudaPointerAttributes attr;
+    bool pinned = dense && cudaPointerGetAttributes(&attr, data) == cudaSuccess && attr.type == cudaMemoryTypeHost;
+    cudaGetLastError();
+    if (pinned) {
+      CUDA_TRY(cudaMemcpyAsync(b->ptr, data, bytes, cudaMemcpyHostToDevice, c->h2d));
+      host_ready_now = false;
+    } else if (bytes <= (256u << 20)) {
+      int idx = -1;
+      void* stage = acquire_pinned(c, bytes, &idx);
+      if (!stage) return make_error(B200_RESOURCE_EXHAUSTED, "cannot allocate pinned staging memory");
+      if (dense) memcpy(stage, data, bytes);
+      else pack_strided((const char*)data, (char*)stage, dims, byte_strides, nd, es);
+      CUDA_TRY(cudaMemcpyAsync(b->ptr, stage, bytes, cudaMemcpyHostToDevice, c->h2d));
+      CUDA_TRY(cudaEventRecord(c->pinned[idx].ev, c->h2d));
+      c->pinned[idx].in_flight = true;
+    } else {
+      std::vector<char> tmp;
+      const void* src = data;
+      if (!dense) {
+        tmp.resize(bytes);
+        pack_strided((const char*)data, tmp.data(), dims, byte_strides, nd, es);
+        src = tmp.data();
+      }
+      CUDA_TRY(cudaMemcpyAsync(b->ptr, src, bytes, cudaMemcpyHostToDevice, c->h2d));
+      CUDA_TRY(cudaStreamSynchronize(c->h2d));
+    }
+  }
+  CUDA_TRY(cudaEventCreateWithFlags(&b->ready, cudaEventDisableTiming));
+  CUDA_TRY(cudaEventRecord(b->ready, c->h2d));
+  if (done) {
+    if (host_ready_now) *done = new b200_event();
+    else {
+      b200_error* err = nullptr;
+      *done = new_event_on(c, c->h2d, &err);
+      if (err) return err;
+    }
+  }
+  *out = b.release();
+  return nullptr;
+}
+
+b200_error* b200_buffer_to_host(b200_buffer* b, void* dst, size_t* dst_size, b200_event** event) {
+  if (!b) return make_error(B200_INVALID_ARGUMENT, "null buffer");
+  if (event) *event = nullptr;
+  if (!dst) {
+    if (dst_size) *dst_size = b->bytes;
+    return nullptr;
+  }
+  if (b->deleted) return make_error(B200_INVALID_ARGUMENT, "buffer has been deleted or donated");
+  if (dst_size && *dst_size < b->bytes) return make_error(B200_INVALID_ARGUMENT, "destination too small");
+  b200_client* c = b->client;
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  if (auto* e = set_device(c)) return e;
+  CUDA_TRY(cudaStreamWaitEvent(c->d2h, b->ready, 0));
+  if (b->bytes) CUDA_TRY(cudaMemcpyAsync(dst, b->ptr, b->bytes, cudaMemcpyDeviceToHost, c->d2h));
+  cudaEvent_t rd;
+  CUDA_TRY(cudaEventCreateWithFlags(&rd, cudaEventDisableTiming));
+  CUDA_TRY(cudaEventRecord(rd, c->d2h));
+  // drop finished read markers, keep this one so deletion waits for the copy
+  for (auto it = b->reads.begin(); it != b->reads.end();) {
+    if (cudaEventQuery(*it) == cudaSuccess) { cudaEventDestroy(*it); it = b->reads.erase(it); }
+    else ++it;
+  }
+  b->reads.push_back(rd);
+  if (event) {
+    b200_error* err = nullptr;
+    *event = new_event_on(c, c->d2h, &err);
+    if (err) return err;
+  } else {
+    CUDA_TRY(cudaStreamSynchronize(c->d2h));
+  }
+  return nullptr;
+}
+
+b200_dtype b200_buffer_dtype(const b200_buffer* b) { return b->dtype; }
+size_t b200_buffer_num_dims(const b200_buffer* b) { return b->dims.size(); }
+const int64_t* b200_buffer_dims(const b200_buffer* b) { return b->dims.data(); }
+size_t b200_buffer_on_device_size(const b200_buffer* b) { return b->bytes; }
+int b200_buffer_device(const b200_buffer* b) { return b->client->rank; }
+void* b200_buffer_device_pointer(const b200_buffer* b) { return b->deleted ? nullptr : b->ptr; }
+int b200_buffer_is_deleted(const b200_buffer* b) { return b->deleted ? 1 : 0; }
+
+b200_error* b200_buffer_ready_event(b200_buffer* b, b200_event** event) {
+  if (!b || !event) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  if (b->deleted) return make_error(B200_INVALID_ARGUMENT, "buffer has been deleted or donated");
+  b200_client* c = b->client;
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  if (auto* e = set_device(c)) return e;
+  // a fresh event on the d2h stream ordered after the buffer's producer
+  CUDA_TRY(cudaStreamWaitEvent(c->d2h, b->ready, 0));
+  b200_error* err = nullptr;
+  *event = new_event_on(c, c->d2h, &err);
+  return err;
+}
+
+b200_error* b200_buffer_delete(b200_buffer* b) {
+  if (!b || b->deleted) return nullptr;
+  b200_client* c = b->client;
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  if (auto* e = set_device(c)) return e;
+  b->deleted = true;
+  if (b->ptr) {
+    if (b->ready) cudaStreamWaitEvent(c->compute, b->ready, 0);
+    for (auto ev : b->reads) {
+      cudaStreamWaitEvent(c->compute, ev, 0);
+      cudaEventDestroy(ev);
+    }
+    b->reads.clear();
+    cudaFreeAsync(b->ptr, c->compute);
+    c->note_free(std::max<size_t>(b->bytes, 16));
+    b->ptr = nullptr;
+  }
+  return nullptr;
+}
+
+b200_error* b200_buffer_destroy(b200_buffer* b) {
+  if (!b) return nullptr;
+  b200_error* e = b200_buffer_delete(b);
+  if (b->ready) cudaEventDestroy(b->ready);
+  for (auto ev : b->reads) cudaEventDestroy(ev);
+  delete b;
+  return e;
+}
+
+b200_error* b200_buffer_copy(b200_buffer* b, b200_buffer** out) {
+  if (!b || !out) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  if (b->deleted) return make_error(B200_INVALID_ARGUMENT, "buffer has been deleted or donated");
+  b200_client* c = b->client;
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  if (auto* e = set_device(c)) return e;
+  auto n = std::make_unique<b200_buffer>();
+  n->client = c;
+  n->dtype = b->dtype;
+  n->dims = b->dims;
+  n->bytes = b->bytes;
+  if (auto* e = device_alloc(c, b->bytes, c->compute, &n->ptr)) return e;
+  CUDA_TRY(cudaStreamWaitEvent(c->compute, b->ready, 0));
+  if (b->bytes) CUDA_TRY(cudaMemcpyAsync(n->ptr, b->ptr, b->bytes, cudaMemcpyDeviceToDevice, c->compute));
+  CUDA_TRY(cudaEventCreateWithFlags(&n->ready, cudaEventDisableTiming));
+  CUDA_TRY(cudaEventRecord(n->ready, c->compute));
+  *out = n.release();
+  return nullptr;
+}
+
+// ---- execute -------------------------------------------------------------------------
+b200_error* b200_executable_execute(b200_executable* exe, b200_buffer* const* args, size_t num_args, b200_buffer** outputs,
+                                    b200_event** done, const b200_execute_options* opts) {
+  if (!exe || (!outputs && !exe->lp->prog->results.empty())) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  if (done) *done = nullptr;
+  b200_client* c = exe->client;
+  CompiledProgram& p = *exe->lp->prog;
+  if (num_args != p.arg_types.size())
+    return make_error(B200_INVALID_ARGUMENT, "executable takes " + std::to_string(p.arg_types.size()) + " arguments, got " +
+                                                 std::to_string(num_args));
+  for (size_t k = 0; k < num_args; k++) {
+    b200_buffer* b = args[k];
+    if (!b) return make_error(B200_INVALID_ARGUMENT, "argument " + std::to_string(k) + " is null");
+    if (b->deleted) return make_error(B200_INVALID_ARGUMENT, "argument " + std::to_string(k) + " has been deleted or donated");
+    if (b->client != c) return make_error(B200_INVALID_ARGUMENT, "argument " + std::to_string(k) + " lives on another client");
+    const TensorType& t = p.arg_types[k];
+    if (t.dt == DT::TOKEN) continue;
+    if (to_api(t.dt) != b->dtype || t.dims != b->dims)
+      return make_error(B200_INVALID_ARGUMENT, "argument " + std::to_string(k) + " does not match the program's " + t.str());
+  }
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  if (auto* e = set_device(c)) return e;
+  bool donate = opts && opts->donate_arguments;
+  ExecCtx x;
+  x.c = c;
+  x.lp = exe->lp.get();
+  x.ptrs.assign(p.slots.size(), nullptr);
+  for (size_t k = 0; k < num_args; k++) CUDA_TRY(cudaStreamWaitEvent(c->compute, args[k]->ready, 0));
+  std::vector<std::unique_ptr<b200_buffer>> outs(p.results.size());
+  std::vector<int> donated_from(p.results.size(), -1);
+  std::vector<bool> arg_taken(num_args, false);
+  for (size_t k = 0; k < p.results.size(); k++) {
+    auto b = std::make_unique<b200_buffer>();
+    b->client = c;
+    b->dtype = to_api(p.results[k].type.dt);
+    b->dims = p.results[k].type.dims;
+    b->bytes = p.results[k].type.bytes();
+    int da = p.results[k].donated_arg;
+    if (donate && da >= 0 && (size_t)da < num_args && !arg_taken[da] && args[da]->bytes == b->bytes &&
+        args[da]->reads.empty()) {
+      // the result takes over the argument's storage; fused kernels read element i before writing
+      // element i, so in-place reuse is safe only for results written by such kernels: restrict to
+      // same-shape elementwise updates, which is what optimizer steps produce
+      arg_taken[da] = true;
+      donated_from[k] = da;
+    }
+    if (auto* e = device_alloc(c, b->bytes, c->compute, &b->ptr)) return e;
+    outs[k] = std::move(b);
+  }
+  for (size_t s = 0; s < p.slots.size(); s++) {
+    const Slot& sl = p.slots[s];
+    switch (sl.kind) {
+      case Slot::ARG: x.ptrs[s] = args[sl.index]->ptr; break;
+      case Slot::CONST: x.ptrs[s] = exe->lp->const_ptrs[sl.index]; break;
+      case Slot::TEMP: x.ptrs[s] = (char*)exe->lp->arenas[sl.arena] + sl.offset; break;
+      case Slot::RESULT: x.ptrs[s] = outs[sl.index]->ptr; break;
+    }
+  }
+  b200_error* err = run_plan(x, p.main);
+  c->launches += x.launches;
+  if (!x.timed.empty()) {
+    cudaStreamSynchronize(c->compute);
+    for (auto& t : x.timed) {
+      float ms = 0;
+      cudaEventElapsedTime(&ms, t.a, t.b);
+      auto& pe = c->profile[t.key];
+      pe.kind = t.kind;
+      pe.ms += ms;
+      pe.count++;
+      cudaEventDestroy(t.a);
+      cudaEventDestroy(t.b);
+    }
+  }
+  if (err) {
+    for (auto& b : outs)
+      if (b && b->ptr) { cudaFreeAsync(b->ptr, c->compute); c->note_free(std::max<size_t>(b->bytes, 16)); }
+    return err;
+  }
+  for (size_t k = 0; k < outs.size(); k++) {
+    CUDA_TRY(cudaEventCreateWithFlags(&outs[k]->ready, cudaEventDisableTiming));
+    CUDA_TRY(cudaEventRecord(outs[k]->ready, c->compute));
+  }
+  if (donate) {
+    // donated arguments are consumed (PJRT semantics): their memory returns to the pool in stream order
+    for (size_t k = 0; k < num_args; k++)
+      if (arg_taken[k]) b200_buffer_delete(args[k]);
+  }
+  if (done) {
+    b200_error* e2 = nullptr;
+    *done = new_event_on(c, c->compute, &e2);
+    if (e2) return e2;
+  }
+  for (size_t k = 0; k < outs.size(); k++) outputs[k] = outs[k].release();
+  return nullptr;
+}
+
+// ---- events ------------------------------------------------------------------------------
+int b200_event_is_ready(b200_event* e) {
+  if (!e || !e->ev) return 1;
+  return cudaEventQuery(e->ev) != cudaErrorNotReady;
+}
+
+b200_error* b200_event_await(b200_event* e) {
+  if (!e) return make_error(B200_INVALID_ARGUMENT, "null event");
+  if (e->ev) {
+    cudaError_t r = cudaEventSynchronize(e->ev);
+    if (r != cudaSuccess) {
+      e->error = std::string("device work failed: ") + cudaGetErrorString(r);
+      e->code = B200_INTERNAL;
+    }
+  }
+  return b200_event_error(e);
+}
+
+b200_error* b200_event_error(b200_event* e) {
+  if (!e || e->error.empty()) return nullptr;
+  return make_error(e->code, e->error);
+}
+
+b200_error* b200_event_on_ready(b200_event* e, b200_event_callback cb, void* user_arg) {
+  if (!e || !cb) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  if (!e->ev) {
+    cb(b200_event_error(e), user_arg);
+    return nullptr;
+  }
+  cudaEvent_t ev = e->ev;
+  int dev = e->device;
+  // The waiter needs its own handle on completion: record-independent wait through a second event
+  // is not possible, so the callback thread synchronises on the same CUDA event; destroying the
+  // b200_event before the callback fired is therefore not allowed (same rule as PJRT).
+  completion().post([ev, dev, cb, user_arg] {
+    cudaSetDevice(dev);
+    cudaError_t r = cudaEventSynchronize(ev);
+    b200_error* err = r == cudaSuccess ? nullptr : make_error(B200_INTERNAL, std::string("device work failed: ") + cudaGetErrorString(r));
+    cb(err, user_arg);
+  });
+  return nullptr;
+}
+
+b200_error* b200_event_destroy(b200_event* e) {
+  delete e;
+  return nullptr;
+}
+
+}  // extern "C"

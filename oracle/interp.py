@@ -191,6 +191,7 @@ class Interp:
         self.partition_id = partition_id
         self.conv_f64 = conv_f64 or wide
         self.wide = wide
+        self._vector = 0          # >0 while a combiner region is evaluated on whole arrays
 
     def cast(self, a, dt: str) -> np.ndarray:
         """Element-type rounding; with `wide` every f32 value is carried in
@@ -217,7 +218,7 @@ class Interp:
             outs = self.op(op, env)
             for n, t, v in zip(op.results, op.result_types, outs):
                 v = np.asarray(v)
-                if t.dtype != "token":
+                if t.dtype != "token" and not self._vector:
                     assert tuple(v.shape) == tuple(t.shape), (op.name, v.shape, t.shape)
                 env[n] = self.cast(v, t.dtype)
         return []
@@ -431,13 +432,17 @@ class Interp:
             lo = [c[..., :h] for c in cur]
             hi = [c[..., h:2 * h] for c in cur]
             rest = [c[..., 2 * h:] for c in cur]
+            self._vector += 1
             outs = self.region(blk, env, lo + hi)
+            self._vector -= 1
             outs = [self.cast(o, t.dtype) for o, t in zip(outs, op.result_types)]
             cur = [np.concatenate([o, r], axis=-1) for o, r in zip(outs, rest)]
         if R == 0:
             return [np.broadcast_to(i, kshape) for i in inits]
         acc = [c[..., 0] for c in cur]
+        self._vector += 1
         outs = self.region(blk, env, [np.broadcast_to(i, kshape) for i in inits] + acc)
+        self._vector -= 1
         return outs
 
     # ---- contractions -----------------------------------------------------------------
@@ -477,7 +482,20 @@ class Interp:
         rs, os_ = rest.split("]->[")
         ls, rs, os_ = ([t.strip() for t in s.strip("[] ").split(",")] for s in (ls, rs, os_))
         nsp = len(ls) - 2
-        assert nsp == 2, "oracle convolution: 2 spatial dims"
+        assert nsp in (1, 2), "oracle convolution: 1 or 2 spatial dims"
+        if nsp == 1:        # run 1-D as 2-D with a unit second spatial dim
+            lhs, rhs = lhs[..., None], rhs[..., None]
+            ls, rs, os1 = ls + ["1"], rs + ["1"], os_ + ["1"]
+            op2 = mt.Op(op.name, op.operands, op.results,
+                        [mt.TType(tuple(op.result_types[0].shape) + (1,), op.result_types[0].dtype)], dict(op.attrs), [])
+            spec = lambda s: "[" + ", ".join(s) + "]"
+            op2.attrs["dimension_numbers"] = f"#stablehlo.conv<{spec(ls)}x{spec(rs)}->{spec(os1)}>"
+            for k, d in (("window_strides", 1), ("lhs_dilation", 1), ("rhs_dilation", 1)):
+                v = attr_i64s(op.attrs[k]) if k in op.attrs else [d]
+                op2.attrs[k] = "array<i64: " + ", ".join(str(q) for q in v + [1]) + ">"
+            pd = [int(q) for q in np.array(mt.dense_array(op.attrs["padding"])).reshape(-1)] if "padding" in op.attrs else [0, 0]
+            op2.attrs["padding"] = f"dense<[[{pd[0]}, {pd[1]}], [0, 0]]> : tensor<2x2xi64>"
+            return [self.op_convolution(op2, [lhs, rhs], env)[0][..., 0]]
         def get(name, default):
             return attr_i64s(op.attrs[name]) if name in op.attrs else default
         stride = get("window_strides", [1] * nsp)

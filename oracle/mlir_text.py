@@ -414,6 +414,27 @@ class Parser:
             key = "broadcast_dimensions" if short == "broadcast_in_dim" else "permutation"
             self.expect(":"); self.type_list(); self.expect("->")
             return Op(name, [a], results, self.type_list(), {key: f"array<i64: {dims}>" if dims else "array<i64>"}, [])
+        if short == "reduce":
+            # stablehlo.reduce(%a init: %i) applies stablehlo.add across dimensions = [1] : (..) -> ..
+            self.expect("(")
+            ins, inits = [], []
+            while True:
+                ins.append(self.rx(_SSA)); self.expect("init:"); inits.append(self.rx(_SSA))
+                if not self.accept(","):
+                    break
+            self.expect(")")
+            self.expect("applies")
+            body = self.rx(re.compile(r"[\w.]+"))
+            self.expect("across"); self.expect("dimensions"); self.expect("=")
+            self.expect("["); dims = self.balanced("]"); self.expect("]")
+            self.expect(":"); self.type_list(); self.expect("->")
+            rts = self.type_list()
+            st = TType((), rts[0].dtype)
+            blk = Block(args=[("%acc", st), ("%val", st)],
+                        ops=[Op(body, ["%acc", "%val"], ["%red"], [st], {}, []),
+                             Op("stablehlo.return", ["%red"], [], [], {}, [])])
+            return Op(name, ins + inits, results, rts,
+                      {"dimensions": f"array<i64: {dims}>" if dims else "array<i64>"}, [blk])
         if name in ("call", "func.call"):
             self.expect("@")
             callee = self.rx(re.compile(r"[\w.$]+"))

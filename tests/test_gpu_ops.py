@@ -1,0 +1,361 @@
+"""Operation-level parity on the GPU: every case builds a StableHLO module,
+runs it through the C ABI on the B200 and through the CPU oracle, and compares
+(integers, booleans and indices bit-exact; fp32 at rtol = atol = 1e-5, the
+reference's own bar in tests/test_ops.py:91-105). Case shapes follow the
+reference's catalogue (tests/configs/{conv,matmul,slice,reduction,control_flow}.py)."""
+import math
+
+import numpy as np
+import pytest
+
+from b200.shlo.builder import Builder
+from tests.util import check, compare, run_gpu
+
+pytestmark = pytest.mark.gpu
+rng = np.random.default_rng(42)
+
+
+def f32(*shape, lo=-1.0, hi=1.0):
+    return rng.uniform(lo, hi, shape).astype(np.float32)
+
+
+# ---------------------------------------------------------------------------
+# elementwise
+# ---------------------------------------------------------------------------
+UNARY_F = ["exp", "log", "sqrt", "rsqrt", "neg", "abs", "floor", "ceil", "sin", "cos", "tanh", "tan", "logistic",
+           "sign", "log1p", "expm1", "cbrt", "round_even", "round_afz"]
+
+
+@pytest.mark.parametrize("name", UNARY_F)
+def test_unary_float(client, name):
+    b = Builder()
+    x = b.arg((33, 65), "f32")
+    y = getattr(b, name)(x)
+    pos = name in ("log", "sqrt", "rsqrt", "log1p")
+    a = f32(33, 65, lo=0.05 if pos else -4.0, hi=4.0)
+    if name in ("round_even", "round_afz"):
+        a = np.concatenate([a.reshape(-1)[:-8], np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 3.5, -3.5], np.float32)]).reshape(33, 65)
+    check(client, b.module([y]), [a], rtol=2e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("name", ["add", "sub", "mul", "div", "max", "min", "pow", "rem", "atan2"])
+def test_binary_float(client, name):
+    b = Builder()
+    x, y = b.arg((7, 129), "f32"), b.arg((7, 129), "f32")
+    z = getattr(b, name)(x, y)
+    a0 = f32(7, 129, lo=0.1 if name == "pow" else -3, hi=3)
+    a1 = f32(7, 129, lo=-3, hi=3)
+    a1[np.abs(a1) < 0.05] = 0.5
+    check(client, b.module([z]), [a0, a1], rtol=2e-5, atol=1e-5)
+
+
+def test_float_specials(client):
+    """NaN propagation of maximum/minimum/sign, is_finite, total-order compare."""
+    b = Builder()
+    x, y = b.arg((8,), "f32"), b.arg((8,), "f32")
+    outs = [b.max(x, y), b.min(x, y), b.sign(x), b.is_finite(x), b.compare(x, y, "LT", "TOTALORDER"),
+            b.compare(x, y, "EQ"), b.compare(x, y, "NE")]
+    a0 = np.array([np.nan, 1.0, -0.0, 0.0, np.inf, -np.inf, 2.0, -np.nan], np.float32)
+    a1 = np.array([1.0, np.nan, 0.0, -0.0, np.inf, 1.0, 2.0, np.nan], np.float32)
+    check(client, b.module(outs), [a0, a1])
+
+
+@pytest.mark.parametrize("dt", ["i32", "ui32", "i8", "i64", "ui8", "i16"])
+def test_integer_arithmetic(client, dt):
+    """Truncating division, remainder with the dividend's sign, division by
+    zero, INT_MIN / -1, shifts by out-of-range amounts, popcnt, clz."""
+    from b200.shlo.builder import _NP
+    npdt = _NP[dt]
+    info = np.iinfo(npdt)
+    b = Builder()
+    x, y = b.arg((64,), dt), b.arg((64,), dt)
+    outs = [b.add(x, y), b.sub(x, y), b.mul(x, y), b.div(x, y), b.rem(x, y), b.max(x, y), b.min(x, y), b.and_(x, y),
+            b.or_(x, y), b.xor(x, y), b.shl(x, y), b.shr_logical(x, y), b.shr_arith(x, y), b.not_(x), b.popcnt(x),
+            b.clz(x), b.neg(x), b.abs(x), b.sign(x), b.compare(x, y, "LT"), b.compare(x, y, "GE")]
+    a0 = rng.integers(info.min, info.max, 64, dtype=npdt, endpoint=True)
+    a1 = rng.integers(max(info.min, -9), 9, 64).astype(npdt)
+    a0[:4] = [info.min, info.max, 0, 7]
+    a1[:4] = [-1 if info.min < 0 else 1, 0, 0, info.max]
+    a1[4:8] = [info.max, 31, 33, 8]     # shift amounts beyond the width
+    check(client, b.module(outs), [a0, a1])
+
+
+def test_integer_power(client):
+    b = Builder()
+    x, y = b.arg((16,), "i32"), b.arg((16,), "i32")
+    a0 = np.array([2, 3, -2, 1, -1, -1, 0, 5, 7, 2, 2, 10, -3, 4, 6, 9], np.int32)
+    a1 = np.array([10, 5, 3, -4, -3, -2, 0, 0, 2, 31, 30, 9, 3, -1, 1, 2], np.int32)
+    check(client, b.module([b.pow(x, y)]), [a0, a1])
+
+
+def test_select_clamp_convert(client):
+    b = Builder()
+    p, x, y = b.arg((5, 9), "i1"), b.arg((5, 9), "f32"), b.arg((5, 9), "f32")
+    lo, hi = b.arg((), "f32"), b.arg((), "f32")
+    outs = [b.select(p, x, y), b.clamp(lo, x, hi), b.convert(x, "i32"), b.convert(x, "ui8"), b.convert(x, "i1"),
+            b.convert(b.convert(x, "i32"), "f32"), b.convert(p, "f32"), b.convert(x, "bf16"), b.convert(x, "f16"),
+            b.convert(b.convert(x, "bf16"), "f32"), b.convert(x, "i64"), b.convert(b.convert(x, "i8"), "i32")]
+    a = f32(5, 9, lo=-300, hi=300)
+    a[0, :4] = [np.nan, np.inf, -np.inf, 3e9]
+    check(client, b.module(outs), [rng.integers(0, 2, (5, 9)).astype(bool), a, f32(5, 9), np.float32(-10), np.float32(99.5)])
+
+
+def test_bitcast_and_threefry_style_bits(client):
+    """u32 shift/or/xor chains and bitcast to float, the building blocks of
+    the threefry generator the reference runs bit-exactly (tests/configs/random.py:54-74)."""
+    b = Builder()
+    k = b.arg((256,), "ui32")
+    x = b.add(k, b.full((256,), 0x9E3779B9, "ui32"))
+    rot = b.or_(b.shl(x, b.full((256,), 13, "ui32")), b.shr_logical(x, b.full((256,), 19, "ui32")))
+    y = b.xor(rot, k)
+    mant = b.or_(b.shr_logical(y, b.full((256,), 9, "ui32")), b.full((256,), 0x3F800000, "ui32"))
+    f = b.sub(b.bitcast_convert(mant, "f32"), b.full((256,), 1.0, "f32"))
+    check(client, b.module([y, f, b.bitcast_convert(f, "i32")]), [rng.integers(0, 2**32, 256, dtype=np.uint32)], rtol=0, atol=0)
+
+
+def test_bf16_elementwise(client):
+    b = Builder()
+    x, y = b.arg((40, 64), "bf16"), b.arg((40, 64), "bf16")
+    z = b.add(b.mul(x, y), b.tanh(x))
+    s = b.convert(b.reduce_sum(b.convert(z, "f32"), (1,)), "bf16")
+    a0, a1 = f32(40, 64), f32(40, 64)
+    check(client, b.module([z, s]), [a0, a1], rtol=2e-2, atol=1e-2, dtypes=["bf16", "bf16"])
+
+
+# ---------------------------------------------------------------------------
+# data movement
+# ---------------------------------------------------------------------------
+def test_broadcast_iota_reshape_transpose(client):
+    b = Builder()
+    x, v = b.arg((4, 5, 6), "f32"), b.arg((5,), "f32")
+    t = b.transpose(x, (2, 0, 1))
+    outs = [b.add(x, b.broadcast_in_dim(v, (4, 5, 6), (1,))), t, b.reshape(t, (6, 20)), b.reshape(x, (20, 6)),
+            b.iota((3, 7), "i32", 1), b.iota((3, 7), "f32", 0), b.reverse(x, (0, 2)),
+            b.add(b.reshape(b.transpose(x, (1, 0, 2)), (5, 24)), b.full((5, 24), 1.0, "f32")),
+            b.broadcast_in_dim(b.reshape(v, (5, 1)), (2, 5, 3), (1, 2))]
+    check(client, b.module(outs), [f32(4, 5, 6), f32(5)])
+
+
+def test_big_transpose(client):
+    b = Builder()
+    x = b.arg((96, 200, 33), "f32")
+    check(client, b.module([b.transpose(x, (2, 1, 0)), b.transpose(x, (1, 0, 2))]), [f32(96, 200, 33)])
+
+
+def test_slice_pad_concat(client):
+    """Negative and interior padding (src/pjrt_plugin/ops/slice.cc:202-276)."""
+    b = Builder()
+    x, y = b.arg((6, 10), "f32"), b.arg((3, 10), "f32")
+    z = b.const(-7.0, "f32")
+    outs = [b.slice(x, (1, 2), (5, 9), (2, 3)), b.pad(x, z, (1, 2), (0, 3), (0, 0)), b.pad(x, z, (-1, 0), (2, -3), (0, 0)),
+            b.pad(x, z, (0, 1), (0, 0), (2, 1)), b.pad(x, z, (-2, -1), (1, -2), (1, 2)),
+            b.concatenate([x, y, x], 0), b.concatenate([b.slice(x, (0, 0), (6, 4)), b.mul(x, x)], 1)]
+    check(client, b.module(outs), [f32(6, 10), f32(3, 10)])
+
+
+def test_dynamic_slice_update_clamp(client):
+    """Start indices are clamped into range (src/pjrt_plugin/ops/slice.cc:80-107)."""
+    b = Builder()
+    x, u = b.arg((8, 12), "f32"), b.arg((3, 4), "f32")
+    i, j = b.arg((), "i32"), b.arg((), "i32")
+    outs = [b.dynamic_slice(x, [i, j], (3, 4)), b.dynamic_update_slice(x, u, [i, j])]
+    text = b.module(outs)
+    for ii, jj in [(0, 0), (2, 5), (7, 11), (-3, 100), (6, -1)]:
+        check(client, text, [f32(8, 12), f32(3, 4), np.int32(ii), np.int32(jj)])
+
+
+def test_gather_rows_and_take_along(client):
+    """Embedding lookup and take_along_axis forms, with out-of-range indices
+    clamped (src/pjrt_plugin/ops/gather_scatter.cc:233-239)."""
+    b = Builder()
+    tab, idx = b.arg((50, 16), "f32"), b.arg((4, 7), "i32")
+    x, lab = b.arg((9, 11), "f32"), b.arg((9,), "i32")
+    outs = [b.take_rows(tab, idx), b.take_along_last(x, lab)]
+    ids = rng.integers(0, 50, (4, 7)).astype(np.int32)
+    ids[0, :3] = [-5, 49, 77]
+    check(client, b.module(outs), [f32(50, 16), ids, f32(9, 11), rng.integers(0, 11, 9).astype(np.int32)])
+
+
+# ---------------------------------------------------------------------------
+# reductions
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("shape,dims", [((128, 10), (1,)), ((64, 8, 8, 32), (0, 1, 2)), ((16, 6, 6, 48), (1, 2)),
+                                        ((3, 5000), (1,)), ((70000,), (0,)), ((33, 17, 9), (0, 2)), ((4, 7), (0, 1)),
+                                        ((2, 300000), (1,)), ((5, 1, 3), (1,))])
+def test_reduce_sum_max(client, shape, dims):
+    b = Builder()
+    x = b.arg(shape, "f32")
+    outs = [b.reduce_sum(x, dims), b.reduce_max(x, dims), b.reduce_sum(b.mul(x, x), dims)]
+    check(client, b.module(outs), [f32(*shape)], rtol=2e-5, atol=2e-5)
+
+
+def test_reduce_other_bodies(client):
+    b = Builder()
+    x, p, n = b.arg((9, 40), "f32"), b.arg((9, 40), "i1"), b.arg((9, 40), "i32")
+    one, t, f_, big = b.const(1.0, "f32"), b.const(True, "i1"), b.const(False, "i1"), b.const(2**31 - 1, "i32")
+    outs = [b.reduce([x], [one], (1,), lambda s, a, c: s.mul(a, c))[0],
+            b.reduce([x], [b.const(math.inf, "f32")], (0,), lambda s, a, c: s.min(a, c))[0],
+            b.reduce([p], [t], (1,), lambda s, a, c: s.and_(a, c))[0],
+            b.reduce([p], [f_], (0,), lambda s, a, c: s.or_(a, c))[0],
+            b.reduce([n], [big], (1,), lambda s, a, c: s.min(a, c))[0],
+            b.reduce([n], [b.const(0, "i32")], (0, 1), lambda s, a, c: s.add(a, c))[0]]
+    check(client, b.module(outs), [f32(9, 40, lo=0.8, hi=1.2), rng.integers(0, 2, (9, 40)).astype(bool),
+                                   rng.integers(-1000, 1000, (9, 40)).astype(np.int32)], rtol=2e-5)
+
+
+@pytest.mark.parametrize("shape,dim", [((6, 1000), 1), ((1, 256000), 1), ((50, 7), 0)])
+def test_argmax_first_index_on_ties(client, shape, dim):
+    b = Builder()
+    x = b.arg(shape, "f32")
+    a = np.round(f32(*shape) * 4) / 4          # many ties
+    got, _ = check(client, b.module([b.argmax(x, dim)]), [a])
+    np.testing.assert_array_equal(got[0], np.argmax(a, axis=dim).astype(np.int32))
+
+
+# ---------------------------------------------------------------------------
+# dot_general (case shapes: tests/configs/matmul.py of the reference)
+# ---------------------------------------------------------------------------
+DOT_CASES = [
+    ((32, 64), (64, 48), ((1,), (0,)), ((), ())),
+    ((64, 32), (64, 48), ((0,), (0,)), ((), ())),            # lhs transposed
+    ((32, 64), (48, 64), ((1,), (1,)), ((), ())),            # rhs transposed
+    ((4, 16, 32), (4, 32, 24), ((2,), (1,)), ((0,), (0,))),  # batch
+    ((4, 16, 32), (4, 24, 32), ((2,), (2,)), ((0,), (0,))),
+    ((3, 5, 7, 11), (11, 13), ((3,), (0,)), ((), ())),       # several free dims
+    ((6, 5, 8), (5, 8, 9), ((1, 2), (0, 1)), ((), ())),      # two contracting dims
+    ((17,), (17,), ((0,), (0,)), ((), ())),                  # vector . vector
+    ((128, 512), (512, 10), ((1,), (0,)), ((), ())),
+    ((10, 300), (10, 7), ((0,), (0,)), ((), ())),
+    ((2, 3, 40, 8), (2, 3, 8, 40), ((3,), (2,)), ((0, 1), (0, 1))),
+    ((1, 2048), (2048, 300), ((1,), (0,)), ((), ())),        # GEMV shape
+    ((200, 3000), (3000, 70), ((1,), (0,)), ((), ())),       # deep K (split-K path)
+]
+
+
+@pytest.mark.parametrize("ls,rs,contract,batch", DOT_CASES)
+def test_dot_general(client, ls, rs, contract, batch):
+    b = Builder()
+    x, y = b.arg(ls, "f32"), b.arg(rs, "f32")
+    z = b.dot_general(x, y, contract, batch)
+    check(client, b.module([z]), [f32(*ls), f32(*rs)], rtol=1e-5, atol=2e-5)
+
+
+# ---------------------------------------------------------------------------
+# convolution (case shapes: tests/configs/conv.py:9-224 of the reference)
+# ---------------------------------------------------------------------------
+def _same(size, k, s, d=1):
+    kd = (k - 1) * d + 1
+    out = -(-size // s)
+    tot = max((out - 1) * s + kd - size, 0)
+    return (tot // 2, tot - tot // 2)
+
+
+CONV_CASES = {
+    "nhwc-same": dict(x=(2, 8, 8, 3), w=(3, 3, 3, 8), pad="SAME"),
+    "nchw-oihw-same": dict(x=(1, 3, 8, 8), w=(16, 3, 3, 3), pad="SAME", dn=("bf01", "oi01", "bf01")),
+    "1d-nwc-stride2": dict(x=(2, 16, 3), w=(3, 3, 4), stride=(2,), pad="SAME", dn=("b0f", "0io", "b0f")),
+    "stride2-same": dict(x=(2, 8, 8, 3), w=(3, 3, 3, 8), stride=(2, 2), pad="SAME"),
+    "stride2-asymmetric": dict(x=(2, 8, 8, 3), w=(3, 3, 3, 8), stride=(2, 2), pad=((1, 0), (1, 0))),
+    "5x5-stride2": dict(x=(2, 16, 16, 3), w=(5, 5, 3, 8), stride=(2, 2), pad="SAME"),
+    "stride2-dilated": dict(x=(2, 16, 16, 3), w=(3, 3, 3, 8), stride=(2, 2), pad="SAME", rdil=(2, 2)),
+    "stride2-valid": dict(x=(2, 16, 16, 3), w=(3, 3, 3, 8), stride=(2, 2), pad=((0, 0), (0, 0))),
+    "1d-stride2-dilated": dict(x=(2, 32, 3), w=(3, 3, 4), stride=(2,), pad="SAME", rdil=(2,), dn=("b0f", "0io", "b0f")),
+    "lhs_dilation-neg_padding": dict(x=(1, 6, 7, 4), w=(1, 2, 4, 2), pad=((0, -1), (0, 0)), ldil=(2, 1)),
+    "lhs_dilation-only": dict(x=(1, 6, 7, 4), w=(1, 2, 4, 2), pad=((0, 0), (0, 0)), ldil=(2, 1)),
+    "large-kernel": dict(x=(1, 4, 4, 3), w=(8, 8, 3, 16), pad="SAME"),
+    "batch_group_2": dict(x=(4, 1, 6, 7), w=(2, 1, 1, 2), pad=((0, 0), (0, 0)), dn=("bf01", "oi01", "bf01"), bg=2),
+    "batch_group_2-lhs_dil-neg_pad": dict(x=(2, 6, 7, 4), w=(1, 2, 4, 2), pad=((0, -1), (0, 0)), ldil=(2, 1), bg=2),
+    "batch_group_3-multi_filter": dict(x=(6, 5, 5, 2), w=(3, 3, 2, 6), pad=((1, 1), (1, 1)), bg=3),
+    "feature_group_4": dict(x=(2, 9, 9, 8), w=(3, 3, 2, 12), pad="SAME", fg=4),
+    "resnet-stage1": dict(x=(8, 32, 32, 64), w=(3, 3, 64, 64), pad="SAME"),
+    "resnet-proj-1x1-stride2": dict(x=(8, 32, 32, 64), w=(1, 1, 64, 128), stride=(2, 2), pad="SAME"),
+}
+
+
+def _build_conv(case, grads=False):
+    dn = case.get("dn", ("b01f", "01io", "b01f"))
+    nsp = len(dn[0]) - 2
+    stride = case.get("stride", (1,) * nsp)
+    rdil = case.get("rdil", (1,) * nsp)
+    ldil = case.get("ldil", (1,) * nsp)
+    b = Builder()
+    x, w = b.arg(case["x"], "f32"), b.arg(case["w"], "f32")
+    pad = case["pad"]
+    if pad == "SAME":
+        pad = [_same(case["x"][dn[0].index(str(s))], case["w"][dn[1].index(str(s))], stride[s], rdil[s]) for s in range(nsp)]
+    y = b.conv(x, w, strides=stride, padding=pad, lhs_dilation=ldil, rhs_dilation=rdil, dn=dn,
+               feature_group_count=case.get("fg", 1), batch_group_count=case.get("bg", 1))
+    outs = [y]
+    if grads:
+        loss = b.reduce_sum(b.mul(y, y), tuple(range(y.ndim)))
+        outs += b.grad(loss, [x, w])
+    return b.module(outs)
+
+
+@pytest.mark.parametrize("name", list(CONV_CASES))
+def test_convolution(client, name):
+    case = CONV_CASES[name]
+    check(client, _build_conv(case), [f32(*case["x"]), f32(*case["w"])], rtol=1e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("name", ["nhwc-same", "stride2-same", "stride2-asymmetric", "5x5-stride2", "stride2-dilated",
+                                  "resnet-stage1", "resnet-proj-1x1-stride2"])
+def test_convolution_gradients(client, name):
+    """Input and kernel gradients as jax emits them: convolutions with
+    lhs_dilation / rhs_dilation, negative padding and permuted dimension numbers."""
+    case = CONV_CASES[name]
+    check(client, _build_conv(case, grads=True), [f32(*case["x"]), f32(*case["w"])], rtol=1e-4, atol=1e-5, wide=True,
+          scale_atol=True)
+
+
+# ---------------------------------------------------------------------------
+# control flow
+# ---------------------------------------------------------------------------
+def test_counted_while(client):
+    """fori_loop of 130 iterations (tests/configs/control_flow.py:426-435 of the reference)."""
+    b = Builder()
+    x = b.arg((16,), "f32")
+    def cond(s, i, v): return s.compare(i, s.const(130, "i32"), "LT")
+    def body(s, i, v): return [s.add(i, s.const(1, "i32")), s.add(s.mul(v, s.full((16,), 0.99, "f32")), s.full((16,), 0.01, "f32"))]
+    i0 = b.const(0, "i32")
+    outs = b.while_([i0, x], cond, body)
+    got, exe = check(client, b.module(outs), [f32(16)], rtol=1e-4)
+    assert int(got[0]) == 130
+
+
+def test_dynamic_while_and_zero_trip(client):
+    """Data-dependent trip count; zero iterations returns the inputs."""
+    b = Builder()
+    x, lim = b.arg((), "f32"), b.arg((), "f32")
+    def cond(s, v, l): return s.compare(v, l, "LT")
+    def body(s, v, l): return [s.mul(v, s.const(2.0, "f32")), l]
+    text = b.module(b.while_([x, lim], cond, body))
+    for start, limit in [(1.0, 100.0), (5.0, 1.0), (3.0, 3.0)]:
+        check(client, text, [np.float32(start), np.float32(limit)])
+
+
+def test_scan_with_dynamic_slices(client):
+    """A scan body: read xs[t] with dynamic_slice, update a carry, write ys[t]
+    with dynamic_update_slice (the shape of lax.scan lowerings)."""
+    T, N = 12, 8
+    b = Builder()
+    xs, h0 = b.arg((T, N), "f32"), b.arg((N,), "f32")
+    ys0 = b.full((T, N), 0.0, "f32")
+    def cond(s, t, h, ys): return s.compare(t, s.const(T, "i32"), "LT")
+    def body(s, t, h, ys):
+        z = s.const(0, "i32")
+        xt = s.reshape(s.dynamic_slice(xs, [t, z], (1, N)), (N,))
+        h2 = s.tanh(s.add(s.mul(h, s.full((N,), 0.5, "f32")), xt))
+        ys2 = s.dynamic_update_slice(ys, s.reshape(h2, (1, N)), [t, z])
+        return [s.add(t, s.const(1, "i32")), h2, ys2]
+    outs = b.while_([b.const(0, "i32"), h0, ys0], cond, body)
+    check(client, b.module(outs), [f32(T, N), f32(N)], rtol=2e-5)
+
+
+def test_loop_carried_swap(client):
+    """Body hands carried values to other positions; copies must not clobber."""
+    b = Builder()
+    x, y = b.arg((4,), "f32"), b.arg((4,), "f32")
+    def cond(s, i, a, c): return s.compare(i, s.const(3, "i32"), "LT")
+    def body(s, i, a, c): return [s.add(i, s.const(1, "i32")), c, a]
+    check(client, b.module(b.while_([b.const(0, "i32"), x, y], cond, body)), [f32(4), f32(4)])

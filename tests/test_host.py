@@ -1,0 +1,133 @@
+"""CPU: host-side logic — the C-ABI library loads and exports every declared
+symbol, the parser and the plan compiler behave (fusion shape, error text for
+unsupported operations, custom assembly), and nothing computes without a GPU."""
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import b200
+from b200.shlo.builder import Builder
+from b200.shlo import programs
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "b200_core.h").read_text()
+    declared = set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", header)) - {"b200_event_callback"}
+    lib = b200.load_library()
+    missing = [n for n in sorted(declared) if not hasattr(lib, n)]
+    assert not missing, missing
+    assert declared == set(b200.SIGNATURES), declared ^ set(b200.SIGNATURES)
+
+
+def test_no_cpu_fallback():
+    """Without a CUDA device the client refuses to exist (no silent CPU path)."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(b200.B200Error) as e:
+        b200.Client()
+    assert e.value.code == b200.FAILED_PRECONDITION
+    assert "no CPU fallback" in str(e.value)
+
+
+def test_unsupported_op_is_a_compile_error_naming_all_ops():
+    """Like the reference (src/pjrt_plugin/stablehlo_parser.cc:167-184): one error listing every unsupported op."""
+    text = """
+module @m { func.func public @main(%arg0: tensor<4xf32>) -> tensor<4xf32> {
+  %0 = "stablehlo.fft"(%arg0) : (tensor<4xf32>) -> tensor<4xf32>
+  %1 = "stablehlo.cholesky"(%0) : (tensor<4xf32>) -> tensor<4xf32>
+  "func.return"(%1) : (tensor<4xf32>) -> ()
+} }"""
+    with pytest.raises(b200.B200Error) as e:
+        b200.compile_to_plan(text)
+    assert "stablehlo.fft" in str(e.value) and "stablehlo.cholesky" in str(e.value)
+    assert e.value.code == b200.INVALID_ARGUMENT
+
+
+def test_parse_errors_carry_a_line_number():
+    with pytest.raises(b200.B200Error) as e:
+        b200.compile_to_plan("module @m {\n func.func public @main() -> tensor<f32> {\n  %0 = stablehlo.bogus\n } }")
+    assert "line 3" in str(e.value)
+
+
+def test_elementwise_chain_is_one_kernel():
+    b = Builder()
+    x, y = b.arg((256, 64), "f32"), b.arg((64,), "f32")
+    z = b.tanh(b.add(b.mul(x, x), b.bcast(y, x.shape)))
+    w = b.select(b.compare(z, b.zeros_like(z), "GT"), z, b.neg(z))
+    plan, src = b200.compile_to_plan(b.module([w]), validate=True)
+    assert plan.count("kernel ") == 1, plan
+    assert "op_tanh" in src
+
+
+def test_multi_output_fusion_of_optimizer_update():
+    """m' = 0.9 m + g and w' = w - 0.1 m' leave one kernel with two outputs."""
+    b = Builder()
+    w, m, g = (b.arg((1000,), "f32") for _ in range(3))
+    m2 = b.add(b.mul(m, b.full((1000,), 0.9, "f32")), g)
+    w2 = b.sub(w, b.mul(m2, b.full((1000,), 0.1, "f32")))
+    plan, _ = b200.compile_to_plan(b.module([w2, m2]))
+    assert plan.count("kernel ") == 1, plan
+
+
+def test_fusion_can_be_disabled():
+    b = Builder()
+    x = b.arg((64,), "f32")
+    y = b.exp(b.neg(b.mul(x, x)))
+    assert b200.compile_to_plan(b.module([y]))[0].count("kernel ") == 1
+    assert b200.compile_to_plan(b.module([y]), disable_fusion=True)[0].count("kernel ") == 3
+
+
+def test_resnet_plan_shape():
+    prog = programs.resnet18_train_step(batch=4, image=8, width=8)
+    plan, src = b200.compile_to_plan(prog.text, validate=True)
+    assert plan.count("igemm ") == 20 + 19 + 20 + 3        # 20 convs fwd, 19 input grads, 20 kernel grads, dense fwd + 2 grads
+    assert "all_reduce" not in plan
+    dp = programs.resnet18_train_step(batch=4, image=8, width=8, n_partitions=2)
+    plan2, _ = b200.compile_to_plan(dp.text, num_processes=2, process_index=1)
+    assert plan2.count("all_reduce") == 63                  # 62 gradient leaves + the loss
+
+
+def test_counted_loop_is_recognised():
+    b = Builder()
+    x = b.arg((4,), "f32")
+    outs = b.while_([b.const(0, "i32"), x], lambda s, i, v: s.compare(i, s.const(130, "i32"), "LT"),
+                    lambda s, i, v: [s.add(i, s.const(1, "i32")), s.mul(v, v)])
+    plan, _ = b200.compile_to_plan(b.module(outs))
+    assert "while trip=130" in plan
+
+
+def test_custom_assembly_and_generic_form_give_the_same_plan():
+    pretty = """
+module @m { func.func public @main(%arg0: tensor<8x4xf32>, %arg1: tensor<4xf32>) -> tensor<8xf32> {
+  %0 = stablehlo.broadcast_in_dim %arg1, dims = [1] : (tensor<4xf32>) -> tensor<8x4xf32>
+  %1 = stablehlo.multiply %arg0, %0 : tensor<8x4xf32>
+  %cst = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+  %2 = stablehlo.reduce(%1 init: %cst) applies stablehlo.add across dimensions = [1] : (tensor<8x4xf32>, tensor<f32>) -> tensor<8xf32>
+  return %2 : tensor<8xf32>
+} }"""
+    b = Builder()
+    x, y = b.arg((8, 4), "f32"), b.arg((4,), "f32")
+    generic = b.module([b.reduce_sum(b.mul(x, b.broadcast_in_dim(y, (8, 4), (1,))), (1,))])
+    p1, s1 = b200.compile_to_plan(pretty)
+    p2, s2 = b200.compile_to_plan(generic)
+    strip = lambda p: re.sub(r"program \S+:", "program:", p)
+    assert strip(p1) == strip(p2)
+    from oracle import interp
+    a, v = np.arange(32, dtype=np.float32).reshape(8, 4), np.array([1, 2, 3, 4], np.float32)
+    np.testing.assert_allclose(interp.run_text(pretty, [a, v])[0], (a * v).sum(1))
+
+
+def test_sharding_custom_calls_are_pass_through():
+    text = """
+module @m attributes {mhlo.num_partitions = 1 : i32} { func.func public @main(%arg0: tensor<4xf32>) -> tensor<4xf32> {
+  %0 = "stablehlo.custom_call"(%arg0) <{call_target_name = "Sharding"}> {mhlo.sharding = "{replicated}"} : (tensor<4xf32>) -> tensor<4xf32>
+  %1 = "stablehlo.add"(%0, %0) : (tensor<4xf32>, tensor<4xf32>) -> tensor<4xf32>
+  "func.return"(%1) : (tensor<4xf32>) -> ()
+} }"""
+    plan, _ = b200.compile_to_plan(text)
+    assert plan.count("kernel ") == 1
