@@ -684,7 +684,7 @@ class Builder:
             for outs, ins, vjp in reversed(self.tape):
                 if not any(o.name in ct for o in outs):
                     continue
-                gs = [ct.pop(o.name, None) for o in outs]
+                gs = [ct.get(o.name) for o in outs]
                 gs = [g if g is not None else self.zeros_like(o) for g, o in zip(gs, outs)]
                 for i, gi in zip(ins, vjp(gs)):
                     if gi is None or isinstance(i, _Stopped):

@@ -79,9 +79,15 @@ def _same_pad(size: int, k: int, s: int):
     return (tot // 2, tot - tot // 2)
 
 
+_CONV_TAPS = None      # debugging aid: when a list, every convolution output is appended to it
+
+
 def _conv_same(b: Builder, x: Val, w: Val, stride: int) -> Val:
     pads = [_same_pad(x.shape[1], w.shape[0], stride), _same_pad(x.shape[2], w.shape[1], stride)]
-    return b.conv(x, w, strides=(stride, stride), padding=pads)
+    y = b.conv(x, w, strides=(stride, stride), padding=pads)
+    if _CONV_TAPS is not None:
+        _CONV_TAPS.append(y)
+    return y
 
 
 def _batch_norm(b: Builder, x: Val, scale: Val, bias: Val, eps: float = 1e-5) -> Val:
@@ -105,7 +111,7 @@ def _relu(b: Builder, x: Val) -> Val:
     return y
 
 
-def resnet18_logits(b: Builder, p: dict, x: Val) -> Val:
+def resnet18_logits(b: Builder, p: dict, x: Val, taps: list | None = None) -> Val:
     y = _relu(b, _batch_norm(b, _conv_same(b, x, p["conv_init.kernel"], 1), p["bn_init.scale"], p["bn_init.bias"]))
     cin = y.shape[-1]
     for stage in range(4):
@@ -121,6 +127,8 @@ def resnet18_logits(b: Builder, p: dict, x: Val) -> Val:
                 res = _conv_same(b, res, p[n + ".conv_proj.kernel"], stride)
                 res = _batch_norm(b, res, p[n + ".bn_proj.scale"], p[n + ".bn_proj.bias"])
             y = _relu(b, b.add(res, z))
+            if taps is not None:
+                taps.append((n, y))
     y = b.mean(y, (1, 2))
     y = b.matmul(y, p["dense.kernel"])
     return b.add(y, b.bcast(p["dense.bias"], y.shape))

@@ -332,15 +332,31 @@ struct Planner {
     return false;
   }
 
-  // Is any member of `g` reachable from `starts` through def-use edges?
-  bool reaches(const std::vector<Op*>& starts, Group* g, BlockState& st) {
+  // Would the kernel of group `g` have to run after any of the start ops / start groups have run?
+  // Def-use edges are followed at the granularity of kernels: an op that is consumed inside a group makes
+  // every output of that group "later"; a cheap op shared by several groups is no edge between them.
+  bool reaches(const std::vector<Op*>& start_ops, const std::vector<Group*>& start_groups, Group* g, BlockState& st) {
     std::set<Op*> seen;
-    std::vector<Op*> work(starts.begin(), starts.end());
+    std::set<Group*> seen_groups;
+    std::vector<Op*> work;
+    auto expand_group = [&](Group* h) {
+      if (h == g || !seen_groups.insert(h).second) return;
+      for (Op* r : h->roots)
+        for (auto* res : r->results)
+          for (auto* u : st.users[res]) work.push_back(u);
+    };
+    for (Group* h : start_groups) expand_group(h);
+    for (Op* o : start_ops) work.push_back(o);
     while (!work.empty()) {
       Op* o = work.back();
       work.pop_back();
       if (!seen.insert(o).second) continue;
-      if (g->members.count(o)) return true;
+      if (g->members.count(o)) return true;          // reached through a def-use edge: g consumes a later value
+      auto git = st.group_of.find(o);
+      if (git != st.group_of.end()) {
+        for (Group* h : git->second) expand_group(h);
+        continue;
+      }
       if (o->pos > g->max_pos) continue;
       for (auto* r : o->results)
         for (auto* u : st.users[r]) work.push_back(u);
@@ -426,13 +442,18 @@ struct Planner {
       bool placed = false;
       for (auto* g : gs) {
         if (g->is_reduce || !identity_in(g, op, st)) continue;
+        // consumers that will read the value from memory: non-fusable users, and every other group
+        // holding one of its users
         std::vector<Op*> others = ext;
+        std::vector<Group*> other_groups;
         for (auto* u : st.users[v]) {
           auto it = st.group_of.find(u);
-          bool in_g = it != st.group_of.end() && std::find(it->second.begin(), it->second.end(), g) != it->second.end();
-          if (!in_g) others.push_back(u);
+          if (it == st.group_of.end()) continue;
+          for (Group* h : it->second)
+            if (h != g && std::find(other_groups.begin(), other_groups.end(), h) == other_groups.end())
+              other_groups.push_back(h);
         }
-        if (reaches(others, g, st)) continue;
+        if (reaches(others, other_groups, g, st)) continue;
         join(g, true);
         placed = true;
         break;
@@ -1226,7 +1247,43 @@ struct Planner {
       for (int s : succ[u])
         if (--indeg[s] == 0) ready.push({units[s].prio, s});
     }
-    if (order.size() != U) throw CompileError("internal: fusion produced a cyclic schedule");
+    if (order.size() != U) {
+      std::string msg = "internal: fusion produced a cyclic schedule:";
+      // find one cycle among the unscheduled units
+      std::set<int> remaining;
+      for (size_t u = 0; u < U; u++)
+        if (std::find(order.begin(), order.end(), (int)u) == order.end()) remaining.insert((int)u);
+      std::vector<int> path;
+      std::set<int> on_path;
+      int cur = *remaining.begin();
+      while (!on_path.count(cur)) {
+        on_path.insert(cur);
+        path.push_back(cur);
+        int nxt = -1;
+        for (int p2 : remaining)
+          if (succ[p2].count(cur)) { nxt = p2; break; }      // walk to an unscheduled predecessor
+        if (nxt < 0) break;
+        cur = nxt;
+      }
+      std::set<int> cyc;
+      bool in = false;
+      for (int u : path) { if (u == cur) in = true; if (in) cyc.insert(u); }
+      int shown = 0;
+      for (size_t u = 0; u < U && shown < 8; u++) {
+        if (!cyc.count((int)u)) continue;
+        shown++;
+        msg += "\n  unit " + std::to_string(u) + " prio " + std::to_string(units[u].prio) + " ";
+        if (units[u].kind == Unit::GROUP) {
+          msg += group_label(units[u].group) + " members:";
+          for (auto* m : units[u].group->members) msg += " " + m->short_name() + "@" + std::to_string(m->pos);
+          msg += " roots:";
+          for (auto* m : units[u].group->roots) msg += " " + m->short_name() + "@" + std::to_string(m->pos);
+        } else msg += units[u].op->name + "@" + std::to_string(units[u].op->pos);
+        msg += " -> succ:";
+        for (int sx : succ[u]) msg += " " + std::to_string(sx);
+      }
+      throw CompileError(msg);
+    }
 
     for (int ui : order) {
       Unit& u = units[ui];
@@ -1393,6 +1450,9 @@ struct Planner {
     struct Blk { size_t off, size; int last; };
     std::vector<Blk> active;
     size_t peak = 0;
+    const bool no_reuse = getenv("B200_DEBUG_NO_REUSE") != nullptr;   // debugging: every temporary gets its own memory
+    if (no_reuse)
+      for (auto& pr : order) live[pr.second].second = 1 << 30;
     for (auto& pr : order) {
       int slot = pr.second;
       int first = pr.first, last = live[slot].second;

@@ -269,6 +269,11 @@ CONV_CASES = {
     "feature_group_4": dict(x=(2, 9, 9, 8), w=(3, 3, 2, 12), pad="SAME", fg=4),
     "resnet-stage1": dict(x=(8, 32, 32, 64), w=(3, 3, 64, 64), pad="SAME"),
     "resnet-proj-1x1-stride2": dict(x=(8, 32, 32, 64), w=(1, 1, 64, 128), stride=(2, 2), pad="SAME"),
+    "small-map-stride2": dict(x=(16, 4, 4, 64), w=(3, 3, 64, 128), stride=(2, 2), pad="SAME"),
+    "small-map-proj-stride2": dict(x=(16, 4, 4, 64), w=(1, 1, 64, 128), stride=(2, 2), pad="SAME"),
+    "narrow-stride2": dict(x=(32, 16, 16, 16), w=(3, 3, 16, 32), stride=(2, 2), pad="SAME"),
+    "narrow-proj-stride2": dict(x=(32, 16, 16, 16), w=(1, 1, 16, 32), stride=(2, 2), pad="SAME"),
+    "tiny-map-3x3": dict(x=(16, 2, 2, 128), w=(3, 3, 128, 128), pad="SAME"),
 }
 
 
@@ -299,7 +304,8 @@ def test_convolution(client, name):
 
 
 @pytest.mark.parametrize("name", ["nhwc-same", "stride2-same", "stride2-asymmetric", "5x5-stride2", "stride2-dilated",
-                                  "resnet-stage1", "resnet-proj-1x1-stride2"])
+                                  "resnet-stage1", "resnet-proj-1x1-stride2", "small-map-stride2",
+                                  "small-map-proj-stride2", "narrow-stride2", "narrow-proj-stride2", "tiny-map-3x3"])
 def test_convolution_gradients(client, name):
     """Input and kernel gradients as jax emits them: convolutions with
     lhs_dilation / rhs_dilation, negative padding and permuted dimension numbers."""
@@ -359,3 +365,19 @@ def test_loop_carried_swap(client):
     def cond(s, i, a, c): return s.compare(i, s.const(3, "i32"), "LT")
     def body(s, i, a, c): return [s.add(i, s.const(1, "i32")), c, a]
     check(client, b.module(b.while_([b.const(0, "i32"), x, y], cond, body)), [f32(4), f32(4)])
+
+
+# ---------------------------------------------------------------------------
+# BatchNorm forward + backward (reductions with fused producers, split over blocks)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("shape", [(16, 2, 2, 128), (16, 4, 4, 64), (16, 8, 8, 32), (32, 16, 16, 16), (16, 16, 16, 8),
+                                   (128, 8, 8, 48)])
+def test_batch_norm_relu_gradients(client, shape):
+    from b200.shlo.programs import _batch_norm, _relu
+    b = Builder()
+    x, scale, bias, g = b.arg(shape, "f32"), b.arg(shape[-1:], "f32"), b.arg(shape[-1:], "f32"), b.arg(shape, "f32")
+    y = _relu(b, _batch_norm(b, x, scale, bias))
+    loss = b.reduce_sum(b.mul(y, g), (0, 1, 2, 3))
+    grads = b.grad(loss, [x, scale, bias])
+    check(client, b.module([y, loss] + grads), [f32(*shape, lo=-2, hi=3), f32(shape[-1], lo=0.5, hi=1.5), f32(shape[-1]),
+                                                f32(*shape)], rtol=1e-4, atol=1e-5, wide=True, scale_atol=True)
