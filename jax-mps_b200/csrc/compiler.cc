@@ -914,6 +914,66 @@ struct Planner {
                   const std::vector<ColEnt>& acol, const std::vector<long long>& bcol, const std::vector<long long>& bn,
                   const std::vector<long long>& crow, const std::vector<long long>& cn, const std::vector<long long>& ag,
                   const std::vector<long long>& bg, const std::vector<long long>& cg, BlockState& st) {
+    // Can the operands be gathered 16 bytes at a time? A chunk is four consecutive contraction indices of one
+    // row (K-major storage) or four consecutive rows at one contraction index (MN-major storage); it must be
+    // four consecutive, 16-byte aligned floats that share one convolution-window position.
+    auto a_kmajor_ok = [&]() {
+      if (p.K % 4) return false;
+      for (int k = 0; k < p.K; k += 4) {
+        if (acol[k].off % 4) return false;
+        for (int i = 1; i < 4; i++)
+          if (acol[k + i].off != acol[k].off + i || acol[k + i].dh != acol[k].dh || acol[k + i].dw != acol[k].dw) return false;
+      }
+      for (auto& r : arow) if (r.off % 4) return false;
+      return true;
+    };
+    auto a_mnmajor_ok = [&]() {
+      if (p.M % 4) return false;
+      for (int m = 0; m < p.M; m += 4) {
+        if (arow[m].off % 4) return false;
+        for (int i = 1; i < 4; i++)
+          if (arow[m + i].off != arow[m].off + i || arow[m + i].h0 != arow[m].h0 || arow[m + i].w0 != arow[m].w0) return false;
+      }
+      for (auto& c : acol) if (c.off % 4) return false;
+      return true;
+    };
+    auto b_kmajor_ok = [&]() {
+      if (p.K % 4) return false;
+      for (int k = 0; k < p.K; k += 4) {
+        if (bcol[k] % 4) return false;
+        for (int i = 1; i < 4; i++) if (bcol[k + i] != bcol[k] + i) return false;
+      }
+      for (auto v : bn) if (v % 4) return false;
+      return true;
+    };
+    auto b_mnmajor_ok = [&]() {
+      if (p.N % 4) return false;
+      for (int n = 0; n < p.N; n += 4) {
+        if (bn[n] % 4) return false;
+        for (int i = 1; i < 4; i++) if (bn[n + i] != bn[n] + i) return false;
+      }
+      for (auto v : bcol) if (v % 4) return false;
+      return true;
+    };
+    bool strides_ok = (!p.needs_mask || (p.a_sh % 4 == 0 && p.a_sw % 4 == 0));
+    for (auto v : ag) strides_ok &= v % 4 == 0;
+    for (auto v : bg) strides_ok &= v % 4 == 0;
+    int a_major = -1, b_major = -1;        // 0: K-major, 1: MN-major
+    if (strides_ok) {
+      if (p.a_contig == 0 && a_kmajor_ok()) a_major = 0;
+      else if (a_mnmajor_ok()) a_major = 1;
+      else if (a_kmajor_ok()) a_major = 0;
+      if (p.b_contig == 1 && b_kmajor_ok()) b_major = 0;
+      else if (b_mnmajor_ok()) b_major = 1;
+      else if (b_kmajor_ok()) b_major = 0;
+    }
+    if (a_major >= 0 && b_major >= 0) {
+      p.vec = 1;
+      p.a_contig = a_major;
+      p.b_contig = b_major == 0 ? 1 : 0;
+    }
+    p.c_vec = 1;
+    for (size_t n = 1; n < cn.size(); n++) if (cn[n] != cn[0] + (long long)n) p.c_vec = 0;
     Step s;
     s.kind = Step::IGEMM;
     s.label = op->name;
@@ -1485,7 +1545,7 @@ void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& o
         break;
       case Step::IGEMM:
         os << "igemm M=" << s.ig.M << " N=" << s.ig.N << " K=" << s.ig.K << " G=" << s.ig.groups << " splitK=" << s.ig.split_k
-           << " a_contig=" << s.ig.a_contig << " b_contig=" << s.ig.b_contig << " " << s.label;
+           << " a_contig=" << s.ig.a_contig << " b_contig=" << s.ig.b_contig << " vec=" << s.ig.vec << " " << s.label;
         break;
       case Step::MEMCPY: os << "memcpy " << s.bytes; break;
       case Step::WHILE: os << "while trip=" << s.trip_count; break;

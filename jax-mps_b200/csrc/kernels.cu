@@ -15,6 +15,7 @@
 //   B address = b_grp[g] + b_row[k] + b_col[n]
 //   C address = c_grp[g] + c_row[m] + c_col[n]
 #include <cuda_runtime.h>
+#include <cstdint>
 
 #include "kernels.h"
 
@@ -211,12 +212,638 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
   C[c_grp[g] + c_row[m] + c_col[n]] = s;
 }
 
+
+// ---------------------------------------------------------------------------
+// Tensor-core path: the same table-driven implicit GEMM on tcgen05 (sm_100a).
+//
+// fp32 operands are split in registers into a TF32-representable high part and
+// a low part (x = hi + lo, both rounded to 10 mantissa bits) and the product is
+// accumulated as hi*hi + hi*lo + lo*hi by three tcgen05.mma.kind::tf32
+// instructions per k-step into one fp32 accumulator in tensor memory: the
+// result carries about 21 bits, i.e. fp32-level accuracy, never plain TF32.
+//
+// One CTA computes a 128 x 64 tile. Per 32-deep k-tile all 256 threads gather
+// A (128 x 32) and B (64 x 32) from global memory through the index tables
+// (im2col, padding and dilation masks included), split them and store the four
+// operand tiles (A hi/lo, B hi/lo) in shared memory in the K-major 128-byte
+// swizzled layout the MMA unit reads; one thread then issues 12 MMAs and
+// commits them to the stage's mbarrier, so the tensor pipe works on tile k
+// while the CTA gathers tile k+1 into the other stage (two CTAs per SM
+// interleave further). The accumulator is read back with tcgen05.ld.
+// Every mbarrier wait is bounded: on expiry the CTA raises *error_flag, skips
+// its stores, releases its tensor memory and returns.
+constexpr int TBM = 128, TBN = 64, TBK = 32, TSTAGES = 2, TNT = 256;
+constexpr int TA_BYTES = TBM * TBK * 4, TB_BYTES = TBN * TBK * 4;
+constexpr int TSTAGE_BYTES = 2 * TA_BYTES + 2 * TB_BYTES;
+constexpr int TSMEM_BYTES = TSTAGES * TSTAGE_BYTES + 1024 + 64;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+// Bounded wait: false when the phase did not complete within the budget.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int spin = 0; spin < (1 << 22); ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart (SBO), LBO unused (1), descriptor version 1
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// x = hi + lo with hi and lo representable in TF32 (round to nearest on 10 mantissa bits)
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+  uint32_t u = __float_as_uint(x);
+  uint32_t h = ((u & 0x7F800000u) == 0x7F800000u) ? u : ((u + 0x1000u) & 0xFFFFE000u);
+  hi = __uint_as_float(h);
+  float l = x - hi;
+  uint32_t lu = __float_as_uint(l);
+  lo = __uint_as_float(((lu & 0x7F800000u) == 0x7F800000u) ? lu : ((lu + 0x1000u) & 0xFFFFE000u));
+}
+
+// byte offset of the 16-byte chunk `chunk` (0..7) of row `r` inside a K-major SW128 tile
+__device__ __forceinline__ uint32_t sw128(int r, int chunk) {
+  return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4));
+}
+
+template <bool A_MCONTIG, bool B_KCONTIG, bool MASK>
+__global__ void __launch_bounds__(TNT, 2) igemm_tf32x3_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                                                             float* __restrict__ C, const RowEnt* __restrict__ a_row,
+                                                             const ColEnt* __restrict__ a_col,
+                                                             const long long* __restrict__ b_row,
+                                                             const long long* __restrict__ b_col,
+                                                             const long long* __restrict__ c_row,
+                                                             const long long* __restrict__ c_col,
+                                                             const long long* __restrict__ a_grp,
+                                                             const long long* __restrict__ b_grp,
+                                                             const long long* __restrict__ c_grp,
+                                                             float* __restrict__ partial, int* __restrict__ error_flag,
+                                                             IGemmLaunch p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + TSTAGES * TSTAGE_BYTES);      // one mbarrier per stage
+  uint32_t* tmem_slot = (uint32_t*)(bars + TSTAGES);
+  int* failed = (int*)(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = blockIdx.x * TBM, n0 = blockIdx.y * TBN;
+  const int g = blockIdx.z / p.split_k, sp = blockIdx.z % p.split_k;
+  const int kchunk = ((p.K + p.split_k - 1) / p.split_k + TBK - 1) / TBK * TBK;
+  const int kbeg = sp * kchunk, kend = min(p.K, kbeg + kchunk);
+  const int ktiles = kend > kbeg ? (kend - kbeg + TBK - 1) / TBK : 0;
+  const float* Ag = A + a_grp[g];
+  const float* Bg = B + b_grp[g];
+
+  if (tid == 0) {
+    for (int s = 0; s < TSTAGES; ++s) mbar_init(smem_u32(&bars[s]), 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TBN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  // ---- what this thread gathers: 4 chunks of A (16 floats) and 2 chunks of B (8 floats) per k-tile ----
+  // K-contiguous operand: chunk = tid % 8, rows tid / 8 + 32 i.  M/N-contiguous operand: row = tid % rows, chunks strided.
+  RowEnt arow[A_MCONTIG ? 1 : 4];
+  bool arow_ok[A_MCONTIG ? 1 : 4];
+  if (A_MCONTIG) {
+    int m = m0 + (tid & 127);
+    arow_ok[0] = m < p.M;
+    arow[0] = arow_ok[0] ? a_row[m] : RowEnt{0, 0, 0};
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int m = m0 + (tid >> 3) + 32 * i;
+      arow_ok[i] = m < p.M;
+      arow[i] = arow_ok[i] ? a_row[m] : RowEnt{0, 0, 0};
+    }
+  }
+  long long bcol[B_KCONTIG ? 2 : 1];
+  bool bcol_ok[B_KCONTIG ? 2 : 1];
+  if (B_KCONTIG) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      int n = n0 + (tid >> 3) + 32 * i;
+      bcol_ok[i] = n < p.N;
+      bcol[i] = bcol_ok[i] ? b_col[n] : 0;
+    }
+  } else {
+    int n = n0 + (tid & 63);
+    bcol_ok[0] = n < p.N;
+    bcol[0] = bcol_ok[0] ? b_col[n] : 0;
+  }
+
+  auto fetch_a = [&](const RowEnt& r, bool rok, const ColEnt& c, bool cok) -> float {
+    if (!rok || !cok) return 0.f;
+    if (MASK) {
+      int ih = r.h0 + c.dh, iw = r.w0 + c.dw;
+      if (ih < 0 || iw < 0 || ih >= p.Hd || iw >= p.Wd) return 0.f;
+      if (p.ldh != 1) { if (ih % p.ldh) return 0.f; ih /= p.ldh; }
+      if (p.ldw != 1) { if (iw % p.ldw) return 0.f; iw /= p.ldw; }
+      return __ldg(Ag + r.off + c.off + (long long)ih * p.a_sh + (long long)iw * p.a_sw);
+    }
+    return __ldg(Ag + r.off + c.off);
+  };
+
+  float ra[16], rb[8];
+  auto load_tile = [&](int kt) {
+    const int k0 = kbeg + kt * TBK;
+    if (A_MCONTIG) {
+      // chunks (tid / 128) + 2 j, j = 0..3
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int kq = (tid >> 7) + 2 * j;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          int k = k0 + kq * 4 + e;
+          bool cok = k < kend;
+          ColEnt c = cok ? a_col[k] : ColEnt{0, 0, 0};
+          ra[j * 4 + e] = fetch_a(arow[0], arow_ok[0], c, cok);
+        }
+      }
+    } else {
+      ColEnt c[4];
+      bool cok[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        int k = k0 + (tid & 7) * 4 + e;
+        cok[e] = k < kend;
+        c[e] = cok[e] ? a_col[k] : ColEnt{0, 0, 0};
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ra[i * 4 + e] = fetch_a(arow[i], arow_ok[i], c[e], cok[e]);
+    }
+    if (B_KCONTIG) {
+      long long br[4];
+      bool kok[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        int k = k0 + (tid & 7) * 4 + e;
+        kok[e] = k < kend;
+        br[e] = kok[e] ? b_row[k] : 0;
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) rb[i * 4 + e] = (kok[e] && bcol_ok[i]) ? __ldg(Bg + br[e] + bcol[i]) : 0.f;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        int kq = (tid >> 6) + 4 * j;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          int k = k0 + kq * 4 + e;
+          bool kok = k < kend;
+          rb[j * 4 + e] = (kok && bcol_ok[0]) ? __ldg(Bg + b_row[kok ? k : 0] + bcol[0]) : 0.f;
+        }
+      }
+    }
+  };
+  auto store_tile = [&](int s) {
+    uint8_t* st = smem + s * TSTAGE_BYTES;
+    uint8_t *a_hi = st, *a_lo = st + TA_BYTES, *b_hi = st + 2 * TA_BYTES, *b_lo = st + 2 * TA_BYTES + TB_BYTES;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      int r = A_MCONTIG ? (tid & 127) : (tid >> 3) + 32 * q;
+      int chunk = A_MCONTIG ? (tid >> 7) + 2 * q : (tid & 7);
+      float4 h, l;
+      split_tf32(ra[q * 4 + 0], h.x, l.x);
+      split_tf32(ra[q * 4 + 1], h.y, l.y);
+      split_tf32(ra[q * 4 + 2], h.z, l.z);
+      split_tf32(ra[q * 4 + 3], h.w, l.w);
+      uint32_t off = sw128(r, chunk);
+      *reinterpret_cast<float4*>(a_hi + off) = h;
+      *reinterpret_cast<float4*>(a_lo + off) = l;
+    }
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      int r = B_KCONTIG ? (tid >> 3) + 32 * q : (tid & 63);
+      int chunk = B_KCONTIG ? (tid & 7) : (tid >> 6) + 4 * q;
+      float4 h, l;
+      split_tf32(rb[q * 4 + 0], h.x, l.x);
+      split_tf32(rb[q * 4 + 1], h.y, l.y);
+      split_tf32(rb[q * 4 + 2], h.z, l.z);
+      split_tf32(rb[q * 4 + 3], h.w, l.w);
+      uint32_t off = sw128(r, chunk);
+      *reinterpret_cast<float4*>(b_hi + off) = h;
+      *reinterpret_cast<float4*>(b_lo + off) = l;
+    }
+  };
+
+  // instruction descriptor: D fp32, A and B tf32, both K-major, N = 64, M = 128
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TBN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
+  bool ok = true;
+  if (ktiles > 0) load_tile(0);
+  for (int kt = 0; kt < ktiles; ++kt) {
+    const int s = kt % TSTAGES;
+    if (kt >= TSTAGES) {
+      // the MMAs that read this stage (k-tile kt - TSTAGES) must have retired
+      // (the verdict is made uniform across the CTA so that nobody is left behind at a barrier)
+      const bool mine = mbar_wait(smem_u32(&bars[s]), (uint32_t)((kt / TSTAGES - 1) & 1));
+      if (!__syncthreads_and(mine)) { ok = false; break; }
+    }
+    store_tile(s);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores -> visible to the MMA unit
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t base = smem_u32(smem + s * TSTAGE_BYTES);
+      const uint64_t da_hi = umma_desc(base), da_lo = umma_desc(base + TA_BYTES);
+      const uint64_t db_hi = umma_desc(base + 2 * TA_BYTES), db_lo = umma_desc(base + 2 * TA_BYTES + TB_BYTES);
+#pragma unroll
+      for (int kk = 0; kk < TBK / 8; ++kk) {
+        const uint64_t adv = (uint64_t)(kk * 32 >> 4);       // 8 tf32 = 32 bytes along K inside the swizzle atom
+        umma_tf32(tmem, da_hi + adv, db_hi + adv, idesc, (kt | kk) != 0);
+        umma_tf32(tmem, da_hi + adv, db_lo + adv, idesc, 1);
+        umma_tf32(tmem, da_lo + adv, db_hi + adv, idesc, 1);
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[s]))
+                   : "memory");
+    }
+    if (kt + 1 < ktiles) load_tile(kt + 1);
+  }
+  if (ok && ktiles > 0) {
+    const int last = ktiles - 1;
+    ok = mbar_wait(smem_u32(&bars[last % TSTAGES]), (uint32_t)((last / TSTAGES) & 1));
+  }
+  ok = __syncthreads_and(ok);
+  if (!ok && tid == 0) {
+    *failed = 1;
+    atomicExch(error_flag, 1);
+  }
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+  // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31, columns 32 (w / 4) .. +31 ----
+  if (ok) {
+    uint32_t v[32];
+    if (ktiles > 0) {
+      const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(32 * (warp >> 2));
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
+          "%24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+            "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+            "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+            "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+          : "r"(taddr)
+          : "memory");
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = 0u;
+    }
+    const int m = m0 + 32 * (warp & 3) + lane;
+    const int nb = n0 + 32 * (warp >> 2);
+    if (m < p.M) {
+      if (p.split_k > 1) {
+        float* out = partial + ((long long)sp * p.groups + g) * (long long)p.M * p.N + (long long)m * p.N;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (nb + j < p.N) out[nb + j] = __uint_as_float(v[j]);
+      } else {
+        float* out = C + c_grp[g] + c_row[m];
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (nb + j < p.N) out[c_col[nb + j]] = __uint_as_float(v[j]);
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TBN) : "memory");
+  }
+}
+
+
+// ---------------------------------------------------------------------------
+// Tensor-core path, vector gather: as above, but operands move in 16-byte
+// chunks with cp.async (zero-filled where the convolution window falls on
+// padding or between dilated input pixels) straight into the swizzled tile the
+// MMA unit reads, so the raw fp32 tile is the "high" operand as it stands: the
+// tensor core reads only the TF32 bits of each word (sign, exponent, top 10
+// mantissa bits). The only transformation is lo = x - trunc_tf32(x), written to
+// a second tile. An operand whose contraction index is contiguous in memory is
+// stored K-major; one whose row index (m or n) is contiguous is stored
+// MN-major, so both kinds gather with full 16-byte requests.
+// The host enables this kernel only when every chunk is uniform: four
+// consecutive table entries are four consecutive, 16-byte aligned floats
+// sharing one window position (IGemmLaunch::vec).
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+
+// byte offset of 16-byte chunk `mc` (4 consecutive m or n) at contraction index k (0..31) in an MN-major
+// SW128 tile: 1 KB atoms of 8 k-rows x 32 mn, atoms ordered k-atom major: offset = (ka * mn_atoms + ma) * 1024
+__device__ __forceinline__ uint32_t sw128_mn(int mc, int k, int mn_atoms) {
+  const int ma = mc >> 3, c8 = mc & 7, ka = k >> 3, ki = k & 7;
+  return (uint32_t)(((ka * mn_atoms + ma) << 10) + (ki << 7) + ((c8 ^ ki) << 4));
+}
+
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, int mn_atoms) {
+  // MN-major, 128-byte swizzle: LBO = distance between atoms along M/N (1 KB), SBO = between atoms along K
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 16) |
+         ((uint64_t)((mn_atoms * 1024) >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+template <bool A_MCONTIG, bool B_KCONTIG, bool MASK>
+__global__ void __launch_bounds__(TNT, 2) igemm_tf32x3_vec_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                                                                 float* __restrict__ C, const RowEnt* __restrict__ a_row,
+                                                                 const ColEnt* __restrict__ a_col,
+                                                                 const long long* __restrict__ b_row,
+                                                                 const long long* __restrict__ b_col,
+                                                                 const long long* __restrict__ c_row,
+                                                                 const long long* __restrict__ c_col,
+                                                                 const long long* __restrict__ a_grp,
+                                                                 const long long* __restrict__ b_grp,
+                                                                 const long long* __restrict__ c_grp,
+                                                                 float* __restrict__ partial, int* __restrict__ error_flag,
+                                                                 IGemmLaunch p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + TSTAGES * TSTAGE_BYTES);
+  uint32_t* tmem_slot = (uint32_t*)(bars + TSTAGES);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = blockIdx.x * TBM, n0 = blockIdx.y * TBN;
+  const int g = blockIdx.z / p.split_k, sp = blockIdx.z % p.split_k;
+  const int kchunk = ((p.K + p.split_k - 1) / p.split_k + TBK - 1) / TBK * TBK;
+  const int kbeg = sp * kchunk, kend = min(p.K, kbeg + kchunk);
+  const int ktiles = kend > kbeg ? (kend - kbeg + TBK - 1) / TBK : 0;
+  const float* Ag = A + a_grp[g];
+  const float* Bg = B + b_grp[g];
+
+  if (tid == 0) {
+    for (int s = 0; s < TSTAGES; ++s) mbar_init(smem_u32(&bars[s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TBN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  // ---- per-thread gather state --------------------------------------------------------------------
+  // A K-major : chunk tid % 8 of rows tid / 8 + 32 i (i < 4)        A MN-major: m-chunk tid % 32, k = tid / 32 + 8 i
+  // B K-major : chunk tid % 8 of rows tid / 8 + 32 i (i < 2)        B MN-major: n-chunk tid % 16, k = tid / 16 + 16 i
+  RowEnt arow[A_MCONTIG ? 1 : 4];
+  bool arow_ok[A_MCONTIG ? 1 : 4];
+  if (A_MCONTIG) {
+    int m = m0 + (tid & 31) * 4;
+    arow_ok[0] = m < p.M;                          // M % 4 == 0: the whole chunk is in range or out
+    arow[0] = arow_ok[0] ? a_row[m] : RowEnt{0, 0, 0};
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int m = m0 + (tid >> 3) + 32 * i;
+      arow_ok[i] = m < p.M;
+      arow[i] = arow_ok[i] ? a_row[m] : RowEnt{0, 0, 0};
+    }
+  }
+  long long bcol[B_KCONTIG ? 2 : 1];
+  bool bcol_ok[B_KCONTIG ? 2 : 1];
+  if (B_KCONTIG) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      int n = n0 + (tid >> 3) + 32 * i;
+      bcol_ok[i] = n < p.N;
+      bcol[i] = bcol_ok[i] ? b_col[n] : 0;
+    }
+  } else {
+    int n = n0 + (tid & 15) * 4;
+    bcol_ok[0] = n < p.N;
+    bcol[0] = bcol_ok[0] ? b_col[n] : 0;
+  }
+
+  auto a_src = [&](const RowEnt& r, bool rok, const ColEnt& c, bool cok, bool& valid) -> const float* {
+    valid = rok && cok;
+    if (!valid) return Ag;
+    if (MASK) {
+      int ih = r.h0 + c.dh, iw = r.w0 + c.dw;
+      if (ih < 0 || iw < 0 || ih >= p.Hd || iw >= p.Wd) { valid = false; return Ag; }
+      if (p.ldh != 1) { if (ih % p.ldh) { valid = false; return Ag; } ih /= p.ldh; }
+      if (p.ldw != 1) { if (iw % p.ldw) { valid = false; return Ag; } iw /= p.ldw; }
+      return Ag + r.off + c.off + (long long)ih * p.a_sh + (long long)iw * p.a_sw;
+    }
+    return Ag + r.off + c.off;
+  };
+
+  // smem offsets of this thread's chunks (the same in every stage and in the raw and lo tiles)
+  uint32_t a_off[4], b_off[2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    a_off[i] = A_MCONTIG ? sw128_mn(tid & 31, (tid >> 5) + 8 * i, TBM / 32) : sw128((tid >> 3) + 32 * i, tid & 7);
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+    b_off[i] = B_KCONTIG ? sw128((tid >> 3) + 32 * i, tid & 7) : sw128_mn(tid & 15, (tid >> 4) + 16 * i, TBN / 32);
+
+  auto issue_tile = [&](int kt, int s) {
+    const int k0 = kbeg + kt * TBK;
+    const uint32_t st = smem_u32(smem + s * TSTAGE_BYTES);
+    const uint32_t a_raw = st, b_raw = st + 2 * TA_BYTES;
+    if (A_MCONTIG) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        int k = k0 + (tid >> 5) + 8 * i;
+        bool cok = k < kend, valid;
+        ColEnt c = cok ? a_col[k] : ColEnt{0, 0, 0};
+        const float* src = a_src(arow[0], arow_ok[0], c, cok, valid);
+        cp_async16(a_raw + a_off[i], src, valid);
+      }
+    } else {
+      int k = k0 + (tid & 7) * 4;
+      bool cok = k < kend;                          // K % 4 == 0: whole chunk in or out
+      ColEnt c = cok ? a_col[k] : ColEnt{0, 0, 0};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        bool valid;
+        const float* src = a_src(arow[i], arow_ok[i], c, cok, valid);
+        cp_async16(a_raw + a_off[i], src, valid);
+      }
+    }
+    if (B_KCONTIG) {
+      int k = k0 + (tid & 7) * 4;
+      bool kok = k < kend;
+      long long br = kok ? b_row[k] : 0;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) cp_async16(b_raw + b_off[i], Bg + br + bcol[i], kok && bcol_ok[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        int k = k0 + (tid >> 4) + 16 * i;
+        bool kok = k < kend;
+        long long br = kok ? b_row[k] : 0;
+        cp_async16(b_raw + b_off[i], Bg + br + bcol[0], kok && bcol_ok[0]);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  auto lo_of = [](float x) -> float {
+    const uint32_t u = __float_as_uint(x);
+    if ((u & 0x7F800000u) == 0x7F800000u) return 0.f;          // inf / nan stay in the high operand only
+    return x - __uint_as_float(u & 0xFFFFE000u);
+  };
+  auto transform = [&](int s) {
+    uint8_t* st = smem + s * TSTAGE_BYTES;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float4 v = *reinterpret_cast<const float4*>(st + a_off[i]);
+      float4 l = make_float4(lo_of(v.x), lo_of(v.y), lo_of(v.z), lo_of(v.w));
+      *reinterpret_cast<float4*>(st + TA_BYTES + a_off[i]) = l;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float4 v = *reinterpret_cast<const float4*>(st + 2 * TA_BYTES + b_off[i]);
+      float4 l = make_float4(lo_of(v.x), lo_of(v.y), lo_of(v.z), lo_of(v.w));
+      *reinterpret_cast<float4*>(st + 2 * TA_BYTES + TB_BYTES + b_off[i]) = l;
+    }
+  };
+
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MCONTIG ? 1u : 0u) << 15) | ((B_KCONTIG ? 0u : 1u) << 16) |
+                         ((uint32_t)(TBN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
+  bool ok = true;
+  if (ktiles > 0) issue_tile(0, 0);
+  for (int kt = 0; kt < ktiles; ++kt) {
+    const int s = kt & 1;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");       // this thread's chunks of tile kt have landed
+    transform(s);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t base = smem_u32(smem + s * TSTAGE_BYTES);
+#pragma unroll
+      for (int kk = 0; kk < TBK / 8; ++kk) {
+        // one k-step = 8 values: 32 bytes inside a K-major swizzle row, or one 8-row atom in an MN-major tile
+        const uint32_t a_adv = A_MCONTIG ? (uint32_t)(kk * (TBM / 32) * 1024) : (uint32_t)(kk * 32);
+        const uint32_t b_adv = B_KCONTIG ? (uint32_t)(kk * 32) : (uint32_t)(kk * (TBN / 32) * 1024);
+        const uint64_t da = A_MCONTIG ? umma_desc_mn(base + a_adv, TBM / 32) : umma_desc(base + a_adv);
+        const uint64_t dal = A_MCONTIG ? umma_desc_mn(base + TA_BYTES + a_adv, TBM / 32) : umma_desc(base + TA_BYTES + a_adv);
+        const uint64_t db = B_KCONTIG ? umma_desc(base + 2 * TA_BYTES + b_adv) : umma_desc_mn(base + 2 * TA_BYTES + b_adv, TBN / 32);
+        const uint64_t dbl = B_KCONTIG ? umma_desc(base + 2 * TA_BYTES + TB_BYTES + b_adv)
+                                       : umma_desc_mn(base + 2 * TA_BYTES + TB_BYTES + b_adv, TBN / 32);
+        umma_tf32(tmem, da, db, idesc, (kt | kk) != 0);
+        umma_tf32(tmem, da, dbl, idesc, 1);
+        umma_tf32(tmem, dal, db, idesc, 1);
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[s]))
+                   : "memory");
+    }
+    if (kt + 1 < ktiles) {
+      if (kt >= 1) {
+        // the other stage was read by the MMAs of tile kt - 1 (commit number (kt - 1) / 2 on its barrier)
+        const bool mine = mbar_wait(smem_u32(&bars[s ^ 1]), (uint32_t)(((kt - 1) >> 1) & 1));
+        if (!__syncthreads_and(mine)) { ok = false; break; }
+      }
+      issue_tile(kt + 1, s ^ 1);
+    }
+  }
+  if (ok && ktiles > 0) {
+    const int last = ktiles - 1;
+    ok = mbar_wait(smem_u32(&bars[last & 1]), (uint32_t)((last >> 1) & 1));
+  }
+  ok = __syncthreads_and(ok);
+  if (!ok && tid == 0) atomicExch(error_flag, 1);
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+  if (ok) {
+    uint32_t v[32];
+    if (ktiles > 0) {
+      const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(32 * (warp >> 2));
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
+          "%24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+            "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+            "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+            "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+          : "r"(taddr)
+          : "memory");
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = 0u;
+    }
+    const int m = m0 + 32 * (warp & 3) + lane;
+    const int nb = n0 + 32 * (warp >> 2);
+    if (m < p.M) {
+      float* out;
+      bool contiguous;
+      if (p.split_k > 1) {
+        out = partial + ((long long)sp * p.groups + g) * (long long)p.M * p.N + (long long)m * p.N + nb;
+        contiguous = (p.N & 3) == 0;
+      } else {
+        out = C + c_grp[g] + c_row[m] + (nb < p.N ? c_col[nb] : 0);
+        contiguous = p.c_vec != 0;
+      }
+      if (contiguous && nb + 32 <= p.N && (((uintptr_t)out) & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(out + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                            __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+      } else if (p.split_k > 1) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (nb + j < p.N) out[j] = __uint_as_float(v[j]);
+      } else {
+        float* row = C + c_grp[g] + c_row[m];
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (nb + j < p.N) row[c_col[nb + j]] = __uint_as_float(v[j]);
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TBN) : "memory");
+  }
+}
+
 }  // namespace
 
 cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B, void* C, const void* const* tables,
-                             void* partial, cudaStream_t stream, int* launches) {
-  dim3 grid((p.M + BM - 1) / BM, (p.N + BN - 1) / BN, p.groups * p.split_k);
-  dim3 block(NT);
+                             void* partial, int* error_flag, cudaStream_t stream, int* launches) {
   auto a_row = (const RowEnt*)tables[0];
   auto a_col = (const ColEnt*)tables[1];
   auto b_row = (const long long*)tables[2];
@@ -226,22 +853,81 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
   auto a_grp = (const long long*)tables[6];
   auto b_grp = (const long long*)tables[7];
   auto c_grp = (const long long*)tables[8];
+  int v = (p.a_mcontig ? 4 : 0) | (p.b_kcontig ? 2 : 0) | (p.mask ? 1 : 0);
+  if (p.tensor_cores) {
+    static bool configured = false;
+    if (!configured) {
+#define SETATTR(AM, BK_, MK) \
+  cudaFuncSetAttribute(igemm_tf32x3_kernel<AM, BK_, MK>, cudaFuncAttributeMaxDynamicSharedMemorySize, TSMEM_BYTES)
+      SETATTR(false, false, false); SETATTR(false, false, true); SETATTR(false, true, false); SETATTR(false, true, true);
+      SETATTR(true, false, false); SETATTR(true, false, true); SETATTR(true, true, false); SETATTR(true, true, true);
+#undef SETATTR
+      configured = true;
+    }
+    dim3 grid((p.M + TBM - 1) / TBM, (p.N + TBN - 1) / TBN, p.groups * p.split_k);
+    if (p.vec) {
+      static bool configured_v = false;
+      if (!configured_v) {
+#define SETATTRV(AM, BK_, MK) \
+  cudaFuncSetAttribute(igemm_tf32x3_vec_kernel<AM, BK_, MK>, cudaFuncAttributeMaxDynamicSharedMemorySize, TSMEM_BYTES)
+        SETATTRV(false, false, false); SETATTRV(false, false, true); SETATTRV(false, true, false); SETATTRV(false, true, true);
+        SETATTRV(true, false, false); SETATTRV(true, false, true); SETATTRV(true, true, false); SETATTRV(true, true, true);
+#undef SETATTRV
+        configured_v = true;
+      }
+#define LAUNCHV(AM, BK_, MK)                                                                                          \
+  igemm_tf32x3_vec_kernel<AM, BK_, MK><<<grid, TNT, TSMEM_BYTES, stream>>>((const float*)A, (const float*)B, (float*)C, \
+                                                                            a_row, a_col, b_row, b_col, c_row, c_col,   \
+                                                                            a_grp, b_grp, c_grp, (float*)partial,       \
+                                                                            error_flag, p)
+      switch (v) {
+        case 0: LAUNCHV(false, false, false); break;
+        case 1: LAUNCHV(false, false, true); break;
+        case 2: LAUNCHV(false, true, false); break;
+        case 3: LAUNCHV(false, true, true); break;
+        case 4: LAUNCHV(true, false, false); break;
+        case 5: LAUNCHV(true, false, true); break;
+        case 6: LAUNCHV(true, true, false); break;
+        default: LAUNCHV(true, true, true); break;
+      }
+#undef LAUNCHV
+    } else {
+#define LAUNCHT(AM, BK_, MK)                                                                                     \
+  igemm_tf32x3_kernel<AM, BK_, MK><<<grid, TNT, TSMEM_BYTES, stream>>>((const float*)A, (const float*)B, (float*)C, \
+                                                                        a_row, a_col, b_row, b_col, c_row, c_col,   \
+                                                                        a_grp, b_grp, c_grp, (float*)partial,       \
+                                                                        error_flag, p)
+    switch (v) {
+      case 0: LAUNCHT(false, false, false); break;
+      case 1: LAUNCHT(false, false, true); break;
+      case 2: LAUNCHT(false, true, false); break;
+      case 3: LAUNCHT(false, true, true); break;
+      case 4: LAUNCHT(true, false, false); break;
+      case 5: LAUNCHT(true, false, true); break;
+      case 6: LAUNCHT(true, true, false); break;
+      default: LAUNCHT(true, true, true); break;
+    }
+#undef LAUNCHT
+    }
+  } else {
+    dim3 grid((p.M + BM - 1) / BM, (p.N + BN - 1) / BN, p.groups * p.split_k);
+    dim3 block(NT);
 #define LAUNCH(AM, BK_, MK)                                                                                          \
   igemm_f32_kernel<AM, BK_, MK><<<grid, block, 0, stream>>>((const float*)A, (const float*)B, (float*)C, a_row, a_col, \
                                                             b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,           \
                                                             (float*)partial, p)
-  int v = (p.a_mcontig ? 4 : 0) | (p.b_kcontig ? 2 : 0) | (p.mask ? 1 : 0);
-  switch (v) {
-    case 0: LAUNCH(false, false, false); break;
-    case 1: LAUNCH(false, false, true); break;
-    case 2: LAUNCH(false, true, false); break;
-    case 3: LAUNCH(false, true, true); break;
-    case 4: LAUNCH(true, false, false); break;
-    case 5: LAUNCH(true, false, true); break;
-    case 6: LAUNCH(true, true, false); break;
-    default: LAUNCH(true, true, true); break;
-  }
+    switch (v) {
+      case 0: LAUNCH(false, false, false); break;
+      case 1: LAUNCH(false, false, true); break;
+      case 2: LAUNCH(false, true, false); break;
+      case 3: LAUNCH(false, true, true); break;
+      case 4: LAUNCH(true, false, false); break;
+      case 5: LAUNCH(true, false, true); break;
+      case 6: LAUNCH(true, true, false); break;
+      default: LAUNCH(true, true, true); break;
+    }
 #undef LAUNCH
+  }
   if (launches) (*launches)++;
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;

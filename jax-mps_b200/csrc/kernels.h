@@ -9,12 +9,16 @@ struct IGemmLaunch {
   int Hd, Wd, ldh, ldw;          // dilated input extent and input dilation (masking)
   long long a_sh, a_sw;          // input strides of the two spatial dims
   int a_mcontig, b_kcontig, mask;
+  int tensor_cores;              // 1: tcgen05 3xTF32 kernel, 0: fp32 FMA kernel
+  int vec;                       // operands can be gathered in uniform, aligned 16-byte chunks
+  int c_vec;                     // consecutive n are consecutive, 16-byte alignable floats in C
 };
 
 // tables: a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp (device pointers).
 // `partial` is the split-K scratch ([split_k][groups][M][N] floats) or null when split_k == 1.
+// `error_flag` (device int) is set by the tensor-core kernel when one of its bounded waits expires.
 // Adds the number of kernels launched to *launches.
 cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B, void* C, const void* const* tables,
-                             void* partial, cudaStream_t stream, int* launches);
+                             void* partial, int* error_flag, cudaStream_t stream, int* launches);
 
 }  // namespace b200

@@ -40,6 +40,8 @@ struct IGemmParams {
   int b_contig = 0;                          // 0: n contiguous in B, 1: k contiguous
   int split_k = 1;
   int needs_mask = 0;
+  int vec = 0;                               // both operands gather in uniform, aligned 16-byte chunks
+  int c_vec = 0;                             // consecutive n are consecutive floats in C
 };
 
 struct Plan;

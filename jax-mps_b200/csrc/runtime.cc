@@ -302,6 +302,8 @@ struct b200_client {
   std::map<std::string, std::shared_ptr<LoadedProgram>> cache;    // program text hash -> loaded plan
   std::vector<PinnedBlock> pinned;
   unsigned char* pred_host = nullptr;   // pinned byte for while-loop predicates
+  int* error_flag = nullptr;            // device word raised by kernels whose bounded waits expire
+  bool tensor_cores = true;
   bool profiling = false;
   struct ProfEntry { std::string kind; double ms = 0; long long count = 0; };
   std::map<std::string, ProfEntry> profile;
@@ -533,11 +535,15 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       p.Hd = s.ig.Hd; p.Wd = s.ig.Wd; p.ldh = s.ig.ldh; p.ldw = s.ig.ldw;
       p.a_sh = s.ig.a_sh; p.a_sw = s.ig.a_sw;
       p.a_mcontig = s.ig.a_contig; p.b_kcontig = s.ig.b_contig; p.mask = s.ig.needs_mask;
+      // tiny products stay on the fp32 FMA kernel; everything else goes to the tensor cores (3xTF32)
+      p.vec = s.ig.vec && !getenv("B200_NO_VEC_GATHER");
+      p.c_vec = s.ig.c_vec;
+      p.tensor_cores = c->tensor_cores && (long long)s.ig.M * s.ig.N * s.ig.K * s.ig.groups >= (1LL << 18) && s.ig.K >= 16;
       const void* tables[9];
       for (int k = 0; k < 9; k++) tables[k] = x.ptrs[s.args[3 + k]];
       void* partial = s.ig.split_k > 1 ? x.ptrs[s.args[12]] : nullptr;
-      cudaError_t e = launch_igemm_f32(p, x.ptrs[s.args[0]], x.ptrs[s.args[1]], x.ptrs[s.args[2]], tables, partial, st,
-                                       &x.launches);
+      cudaError_t e = launch_igemm_f32(p, x.ptrs[s.args[0]], x.ptrs[s.args[1]], x.ptrs[s.args[2]], tables, partial,
+                                       c->error_flag, st, &x.launches);
       if (e != cudaSuccess) return make_error(B200_INTERNAL, "launch of " + s.label + " failed: " + cudaGetErrorString(e));
       return nullptr;
     }
@@ -614,7 +620,9 @@ b200_error* run_plan(ExecCtx& x, const Plan& plan) {
           t.key = "igemm M=" + std::to_string(s.ig.M) + " N=" + std::to_string(s.ig.N) + " K=" + std::to_string(s.ig.K) +
                   " G=" + std::to_string(s.ig.groups) + " splitK=" + std::to_string(s.ig.split_k) + " a_mcontig=" +
                   std::to_string(s.ig.a_contig) + " b_kcontig=" + std::to_string(s.ig.b_contig) + " mask=" +
-                  std::to_string(s.ig.needs_mask) + " ld=" + std::to_string(s.ig.ldh) + "x" + std::to_string(s.ig.ldw);
+                  std::to_string(s.ig.needs_mask) + " ld=" + std::to_string(s.ig.ldh) + "x" + std::to_string(s.ig.ldw) + " vec=" + std::to_string(s.ig.vec);
+          if (!(x.c->tensor_cores && (long long)s.ig.M * s.ig.N * s.ig.K * s.ig.groups >= (1LL << 18) && s.ig.K >= 16))
+            t.kind = "igemm_fma";
           break;
         case Step::ALL_REDUCE: t.kind = "all_reduce"; t.key = "all_reduce " + std::to_string(s.bytes); break;
         default: t.kind = "copy"; t.key = s.label; break;
@@ -701,6 +709,9 @@ b200_error* b200_client_create(const b200_client_options* o, b200_client** out) 
   uint64_t thr = (o && o->pool_release_threshold) ? o->pool_release_threshold : UINT64_MAX;
   CUDA_TRY(cudaMemPoolSetAttribute(c->pool, cudaMemPoolAttrReleaseThreshold, &thr));
   CUDA_TRY(cudaMallocHost((void**)&c->pred_host, 64));
+  CUDA_TRY(cudaMalloc((void**)&c->error_flag, sizeof(int)));
+  CUDA_TRY(cudaMemset(c->error_flag, 0, sizeof(int)));
+  if (const char* e2 = getenv("B200_NO_TENSOR_CORES")) c->tensor_cores = atoi(e2) == 0;
   if (!driver().ok) return make_error(B200_FAILED_PRECONDITION, driver().error);
   if (c->nprocs > 1) {
     if (!o->nccl_unique_id) return make_error(B200_INVALID_ARGUMENT, "num_processes > 1 needs nccl_unique_id");
@@ -726,6 +737,7 @@ b200_error* b200_client_destroy(b200_client* c) {
     cudaEventDestroy(b.ev);
   }
   if (c->pred_host) cudaFreeHost(c->pred_host);
+  if (c->error_flag) cudaFree(c->error_flag);
   cudaStreamDestroy(c->compute);
   cudaStreamDestroy(c->h2d);
   cudaStreamDestroy(c->d2h);
@@ -793,6 +805,13 @@ b200_error* b200_client_synchronize(b200_client* c) {
   CUDA_TRY(cudaStreamSynchronize(c->h2d));
   CUDA_TRY(cudaStreamSynchronize(c->compute));
   CUDA_TRY(cudaStreamSynchronize(c->d2h));
+  int flag = 0;
+  CUDA_TRY(cudaMemcpy(&flag, c->error_flag, sizeof(int), cudaMemcpyDeviceToHost));
+  if (flag) {
+    cudaMemset(c->error_flag, 0, sizeof(int));
+    return make_error(B200_INTERNAL, "a kernel gave up on a bounded wait (tensor-core pipeline did not complete); "
+                                     "results of the affected execution are invalid");
+  }
   return nullptr;
 }
 

@@ -237,7 +237,8 @@ def test_dot_general(client, ls, rs, contract, batch):
     b = Builder()
     x, y = b.arg(ls, "f32"), b.arg(rs, "f32")
     z = b.dot_general(x, y, contract, batch)
-    check(client, b.module([z]), [f32(*ls), f32(*rs)], rtol=1e-5, atol=2e-5)
+    # atol scales with the largest output: a sum of K products carries absolute error ~ eps * sqrt(K) * |terms|
+    check(client, b.module([z]), [f32(*ls), f32(*rs)], rtol=1e-5, atol=1e-5, scale_atol=True)
 
 
 # ---------------------------------------------------------------------------
@@ -300,7 +301,7 @@ def _build_conv(case, grads=False):
 @pytest.mark.parametrize("name", list(CONV_CASES))
 def test_convolution(client, name):
     case = CONV_CASES[name]
-    check(client, _build_conv(case), [f32(*case["x"]), f32(*case["w"])], rtol=1e-5, atol=2e-5)
+    check(client, _build_conv(case), [f32(*case["x"]), f32(*case["w"])], rtol=1e-5, atol=1e-5, scale_atol=True)
 
 
 @pytest.mark.parametrize("name", ["nhwc-same", "stride2-same", "stride2-asymmetric", "5x5-stride2", "stride2-dilated",
