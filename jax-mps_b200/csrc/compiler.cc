@@ -653,6 +653,7 @@ struct Planner {
       src << "  const bool live = o < (" << it << ")" << Nk << "LL;\n";
       for (size_t k = 0; k < n; k++) src << "  " << c_type(rg.dts[k]) << " acc" << k << " = " << init_names[k] << ";\n";
       src << "  if (live) {\n" << pe.str();
+      src << "    #pragma unroll 4\n";      // independent loads of several rows in flight per thread
       src << "    for (" << it << " r = (" << it << ")blockIdx.y * " << TY << " + threadIdx.y; r < (" << it << ")" << Nr
           << "LL; r += " << TY << " * (" << it << ")gridDim.y) {\n";
       src << em.str();
@@ -688,6 +689,7 @@ struct Planner {
       src << "  const bool live = o < (" << it << ")" << Nk << "LL;\n";
       for (size_t k = 0; k < n; k++) src << "  " << c_type(rg.dts[k]) << " acc" << k << " = " << init_names[k] << ";\n";
       src << "  if (live) {\n" << pe.str();
+      src << "    #pragma unroll 4\n";
       src << "    for (" << it << " r = (" << it << ")blockIdx.y * " << T << " + lane; r < (" << it << ")" << Nr
           << "LL; r += " << T << " * (" << it << ")gridDim.y) {\n";
       src << em.str();
@@ -967,7 +969,8 @@ struct Planner {
       else if (b_mnmajor_ok()) b_major = 1;
       else if (b_kmajor_ok()) b_major = 0;
     }
-    if (a_major >= 0 && b_major >= 0) {
+    const bool fits_int = lhs->type.numel() < (1LL << 31) && rhs->type.numel() < (1LL << 31);   // kernels use 32-bit offsets
+    if (a_major >= 0 && b_major >= 0 && fits_int) {
       p.vec = 1;
       p.a_contig = a_major;
       p.b_contig = b_major == 0 ? 1 : 0;
@@ -1073,11 +1076,14 @@ struct Planner {
     bool col = trailing >= 16;
     // parallelism: split the reduced range over blockIdx.y when there are few outputs
     int64_t blocks = col ? (Nk + 31) / 32 : (Nk + (Nr >= 1024 ? 0 : 7)) / (Nr >= 1024 ? 1 : 8);
-    int64_t per_split_min = col ? 64 : (Nr >= 1024 ? 4096 : 256);
+    // enough blocks to fill 148 SMs with 2048 threads each (1184 blocks of 256 threads), each split keeping
+    // at least a few unrolled iterations per thread
+    int64_t per_split_min = col ? 64 : (Nr >= 1024 ? 2048 : 256);
+    const int64_t target_blocks = 1184;
     int splits = 1;
-    if (blocks < 296 && Nr > per_split_min) {
-      splits = (int)std::min<int64_t>((296 + blocks - 1) / blocks, (Nr + per_split_min - 1) / per_split_min);
-      splits = std::max(1, std::min(splits, 256));
+    if (blocks < target_blocks && Nr > per_split_min) {
+      splits = (int)std::min<int64_t>((target_blocks + blocks - 1) / blocks, (Nr + per_split_min - 1) / per_split_min);
+      splits = std::max(1, std::min(splits, 1024));
     }
     auto internal = [this, g, &st](Op* o) {
       return (g->members.count(o) && categorize(o) != Cat::REDUCE) || (is_dup(o) && !st.dup_materialize.count(o));

@@ -16,6 +16,7 @@
 //   C address = c_grp[g] + c_row[m] + c_col[n]
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <cstdio>
 
 #include "kernels.h"
 
@@ -567,20 +568,40 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
 }
 
 // byte offset of 16-byte chunk `mc` (4 consecutive m or n) at contraction index k (0..31) in an MN-major
-// SW128 tile: 1 KB atoms of 8 k-rows x 32 mn, atoms ordered k-atom major: offset = (ka * mn_atoms + ma) * 1024
+// tile. 32-bit operands stored MN-major use the "128-byte swizzle with 32-byte base" layout: atoms of
+// 4 k-rows x 128 bytes (32 values along m/n), 32-byte pieces of a row XOR-ed with the row number; atoms are
+// ordered k-atom major: offset = (ka * mn_atoms + ma) * 512.
 __device__ __forceinline__ uint32_t sw128_mn(int mc, int k, int mn_atoms) {
-  const int ma = mc >> 3, c8 = mc & 7, ka = k >> 3, ki = k & 7;
-  return (uint32_t)(((ka * mn_atoms + ma) << 10) + (ki << 7) + ((c8 ^ ki) << 4));
+  const int ma = mc >> 3, c16 = mc & 7, ka = k >> 2, ki = k & 3;
+  return (uint32_t)(((ka * mn_atoms + ma) << 9) + (ki << 7) + ((((c16 >> 1) ^ ki)) << 5) + ((c16 & 1) << 4));
 }
 
 __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, int mn_atoms) {
-  // MN-major, 128-byte swizzle: LBO = distance between atoms along M/N (1 KB), SBO = between atoms along K
-  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 16) |
-         ((uint64_t)((mn_atoms * 1024) >> 4) << 32) | (1ull << 46) | (2ull << 61);
+  // MN-major, SWIZZLE_128B_BASE32B (layout type 1): LBO = distance between atoms along M/N (512 B),
+  // SBO = distance between 4-row atoms along K
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(512 >> 4) << 16) |
+         ((uint64_t)((mn_atoms * 512) >> 4) << 32) | (1ull << 46) | (1ull << 61);
 }
 
-template <bool A_MCONTIG, bool B_KCONTIG, bool MASK>
-__global__ void __launch_bounds__(TNT, 2) igemm_tf32x3_vec_kernel(const float* __restrict__ A, const float* __restrict__ B,
+// Pipeline of the vector-gather kernel: raw tiles live in a ring of RAW_STAGES stages filled PREFETCH k-tiles
+// ahead by cp.async; the low-part tiles are double-buffered. Iteration kt: (a) wait until the MMAs of tile
+// kt - 2 have retired (they were the last readers of the ring stage about to be refilled and of the low-part
+// buffer about to be rewritten), (b) issue the gather of tile kt + PREFETCH, (c) wait for this thread's chunks
+// of tile kt, (d) write their low parts, (e) fence + barrier, (f) one thread issues the 12 MMAs of tile kt and
+// commits them to bars[kt % RAW_STAGES].
+template <int BN_>
+struct VecCfg {
+  static constexpr int BN = BN_;
+  static constexpr int PREFETCH = BN_ == 64 ? 3 : 2;
+  static constexpr int RAW_STAGES = PREFETCH + 2;
+  static constexpr int A_BYTES = TBM * TBK * 4, B_BYTES = BN_ * TBK * 4;
+  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SMEM = RAW_STAGES * RAW_BYTES + 2 * RAW_BYTES + 1024 + 128;
+  static constexpr int B_CHUNKS = BN_ / 32;          // 16-byte chunks of B per thread and k-tile
+};
+
+template <int BN, bool A_MCONTIG, bool B_KCONTIG, bool MASK>
+__global__ void __launch_bounds__(TNT, 1) igemm_tf32x3_vec_kernel(const float* __restrict__ A, const float* __restrict__ B,
                                                                  float* __restrict__ C, const RowEnt* __restrict__ a_row,
                                                                  const ColEnt* __restrict__ a_col,
                                                                  const long long* __restrict__ b_row,
@@ -592,13 +613,17 @@ __global__ void __launch_bounds__(TNT, 2) igemm_tf32x3_vec_kernel(const float* _
                                                                  const long long* __restrict__ c_grp,
                                                                  float* __restrict__ partial, int* __restrict__ error_flag,
                                                                  IGemmLaunch p) {
+  using Cfg = VecCfg<BN>;
+  constexpr int S = Cfg::RAW_STAGES, D = Cfg::PREFETCH, NBC = Cfg::B_CHUNKS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = (uint64_t*)(smem + TSTAGES * TSTAGE_BYTES);
-  uint32_t* tmem_slot = (uint32_t*)(bars + TSTAGES);
+  uint8_t* lo_base = smem + S * Cfg::RAW_BYTES;                       // two low-part buffers
+  uint64_t* bars = (uint64_t*)(lo_base + 2 * Cfg::RAW_BYTES);
+  uint32_t* tmem_slot = (uint32_t*)(bars + S);
+  volatile int* failed = (volatile int*)(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.x * TBM, n0 = blockIdx.y * TBN;
+  const int m0 = blockIdx.x * TBM, n0 = blockIdx.y * BN;
   const int g = blockIdx.z / p.split_k, sp = blockIdx.z % p.split_k;
   const int kchunk = ((p.K + p.split_k - 1) / p.split_k + TBK - 1) / TBK * TBK;
   const int kbeg = sp * kchunk, kend = min(p.K, kbeg + kchunk);
@@ -607,11 +632,12 @@ __global__ void __launch_bounds__(TNT, 2) igemm_tf32x3_vec_kernel(const float* _
   const float* Bg = B + b_grp[g];
 
   if (tid == 0) {
-    for (int s = 0; s < TSTAGES; ++s) mbar_init(smem_u32(&bars[s]), 1);
+    for (int s = 0; s < S; ++s) mbar_init(smem_u32(&bars[s]), 1);
+    *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TBN)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -621,13 +647,13 @@ __global__ void __launch_bounds__(TNT, 2) igemm_tf32x3_vec_kernel(const float* _
   const uint32_t tmem = *tmem_slot;
 
   // ---- per-thread gather state --------------------------------------------------------------------
-  // A K-major : chunk tid % 8 of rows tid / 8 + 32 i (i < 4)        A MN-major: m-chunk tid % 32, k = tid / 32 + 8 i
-  // B K-major : chunk tid % 8 of rows tid / 8 + 32 i (i < 2)        B MN-major: n-chunk tid % 16, k = tid / 16 + 16 i
+  // K-major operand : chunk tid % 8 of rows tid / 8 + 32 i        MN-major operand: row-chunk tid % 32 (A) or
+  //                                                               tid % (BN / 4) (B), k strided over the rest
   RowEnt arow[A_MCONTIG ? 1 : 4];
   bool arow_ok[A_MCONTIG ? 1 : 4];
   if (A_MCONTIG) {
     int m = m0 + (tid & 31) * 4;
-    arow_ok[0] = m < p.M;                          // M % 4 == 0: the whole chunk is in range or out
+    arow_ok[0] = m < p.M;
     arow[0] = arow_ok[0] ? a_row[m] : RowEnt{0, 0, 0};
   } else {
 #pragma unroll
@@ -637,17 +663,18 @@ __global__ void __launch_bounds__(TNT, 2) igemm_tf32x3_vec_kernel(const float* _
       arow[i] = arow_ok[i] ? a_row[m] : RowEnt{0, 0, 0};
     }
   }
-  long long bcol[B_KCONTIG ? 2 : 1];
-  bool bcol_ok[B_KCONTIG ? 2 : 1];
+  constexpr int BMC = BN / 4;                       // n-chunks per k-row of an MN-major B tile
+  long long bcol[B_KCONTIG ? NBC : 1];
+  bool bcol_ok[B_KCONTIG ? NBC : 1];
   if (B_KCONTIG) {
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NBC; ++i) {
       int n = n0 + (tid >> 3) + 32 * i;
       bcol_ok[i] = n < p.N;
       bcol[i] = bcol_ok[i] ? b_col[n] : 0;
     }
   } else {
-    int n = n0 + (tid & 15) * 4;
+    int n = n0 + (tid % BMC) * 4;
     bcol_ok[0] = n < p.N;
     bcol[0] = bcol_ok[0] ? b_col[n] : 0;
   }
@@ -665,55 +692,56 @@ __global__ void __launch_bounds__(TNT, 2) igemm_tf32x3_vec_kernel(const float* _
     return Ag + r.off + c.off;
   };
 
-  // smem offsets of this thread's chunks (the same in every stage and in the raw and lo tiles)
-  uint32_t a_off[4], b_off[2];
+  uint32_t a_off[4], b_off[NBC];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
     a_off[i] = A_MCONTIG ? sw128_mn(tid & 31, (tid >> 5) + 8 * i, TBM / 32) : sw128((tid >> 3) + 32 * i, tid & 7);
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
-    b_off[i] = B_KCONTIG ? sw128((tid >> 3) + 32 * i, tid & 7) : sw128_mn(tid & 15, (tid >> 4) + 16 * i, TBN / 32);
+  for (int i = 0; i < NBC; ++i)
+    b_off[i] = B_KCONTIG ? sw128((tid >> 3) + 32 * i, tid & 7) : sw128_mn(tid % BMC, tid / BMC + (TNT / BMC) * i, BN / 32);
 
-  auto issue_tile = [&](int kt, int s) {
-    const int k0 = kbeg + kt * TBK;
-    const uint32_t st = smem_u32(smem + s * TSTAGE_BYTES);
-    const uint32_t a_raw = st, b_raw = st + 2 * TA_BYTES;
-    if (A_MCONTIG) {
+  auto issue_tile = [&](int kt) {
+    if (kt < ktiles && !(p.debug_skip & 2)) {
+      const int k0 = kbeg + kt * TBK;
+      const uint32_t st = smem_u32(smem + (kt % S) * Cfg::RAW_BYTES);
+      const uint32_t a_raw = st, b_raw = st + Cfg::A_BYTES;
+      if (A_MCONTIG) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        int k = k0 + (tid >> 5) + 8 * i;
-        bool cok = k < kend, valid;
+        for (int i = 0; i < 4; ++i) {
+          int k = k0 + (tid >> 5) + 8 * i;
+          bool cok = k < kend, valid;
+          ColEnt c = cok ? a_col[k] : ColEnt{0, 0, 0};
+          const float* src = a_src(arow[0], arow_ok[0], c, cok, valid);
+          cp_async16(a_raw + a_off[i], src, valid);
+        }
+      } else {
+        int k = k0 + (tid & 7) * 4;
+        bool cok = k < kend;
         ColEnt c = cok ? a_col[k] : ColEnt{0, 0, 0};
-        const float* src = a_src(arow[0], arow_ok[0], c, cok, valid);
-        cp_async16(a_raw + a_off[i], src, valid);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          bool valid;
+          const float* src = a_src(arow[i], arow_ok[i], c, cok, valid);
+          cp_async16(a_raw + a_off[i], src, valid);
+        }
       }
-    } else {
-      int k = k0 + (tid & 7) * 4;
-      bool cok = k < kend;                          // K % 4 == 0: whole chunk in or out
-      ColEnt c = cok ? a_col[k] : ColEnt{0, 0, 0};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        bool valid;
-        const float* src = a_src(arow[i], arow_ok[i], c, cok, valid);
-        cp_async16(a_raw + a_off[i], src, valid);
-      }
-    }
-    if (B_KCONTIG) {
-      int k = k0 + (tid & 7) * 4;
-      bool kok = k < kend;
-      long long br = kok ? b_row[k] : 0;
-#pragma unroll
-      for (int i = 0; i < 2; ++i) cp_async16(b_raw + b_off[i], Bg + br + bcol[i], kok && bcol_ok[i]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        int k = k0 + (tid >> 4) + 16 * i;
+      if (B_KCONTIG) {
+        int k = k0 + (tid & 7) * 4;
         bool kok = k < kend;
         long long br = kok ? b_row[k] : 0;
-        cp_async16(b_raw + b_off[i], Bg + br + bcol[0], kok && bcol_ok[0]);
+#pragma unroll
+        for (int i = 0; i < NBC; ++i) cp_async16(b_raw + b_off[i], Bg + br + bcol[i], kok && bcol_ok[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < NBC; ++i) {
+          int k = k0 + tid / BMC + (TNT / BMC) * i;
+          bool kok = k < kend;
+          long long br = kok ? b_row[k] : 0;
+          cp_async16(b_raw + b_off[i], Bg + br + bcol[0], kok && bcol_ok[0]);
+        }
       }
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");          // one group per k-tile, empty past the end
   };
 
   auto lo_of = [](float x) -> float {
@@ -721,122 +749,423 @@ __global__ void __launch_bounds__(TNT, 2) igemm_tf32x3_vec_kernel(const float* _
     if ((u & 0x7F800000u) == 0x7F800000u) return 0.f;          // inf / nan stay in the high operand only
     return x - __uint_as_float(u & 0xFFFFE000u);
   };
-  auto transform = [&](int s) {
-    uint8_t* st = smem + s * TSTAGE_BYTES;
+  auto transform = [&](int kt) {
+    const uint8_t* raw = smem + (kt % S) * Cfg::RAW_BYTES;
+    uint8_t* lo = lo_base + (kt & 1) * Cfg::RAW_BYTES;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      float4 v = *reinterpret_cast<const float4*>(st + a_off[i]);
-      float4 l = make_float4(lo_of(v.x), lo_of(v.y), lo_of(v.z), lo_of(v.w));
-      *reinterpret_cast<float4*>(st + TA_BYTES + a_off[i]) = l;
+      float4 v = *reinterpret_cast<const float4*>(raw + a_off[i]);
+      *reinterpret_cast<float4*>(lo + a_off[i]) = make_float4(lo_of(v.x), lo_of(v.y), lo_of(v.z), lo_of(v.w));
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      float4 v = *reinterpret_cast<const float4*>(st + 2 * TA_BYTES + b_off[i]);
-      float4 l = make_float4(lo_of(v.x), lo_of(v.y), lo_of(v.z), lo_of(v.w));
-      *reinterpret_cast<float4*>(st + 2 * TA_BYTES + TB_BYTES + b_off[i]) = l;
+    for (int i = 0; i < NBC; ++i) {
+      float4 v = *reinterpret_cast<const float4*>(raw + Cfg::A_BYTES + b_off[i]);
+      *reinterpret_cast<float4*>(lo + Cfg::A_BYTES + b_off[i]) = make_float4(lo_of(v.x), lo_of(v.y), lo_of(v.z), lo_of(v.w));
     }
   };
 
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MCONTIG ? 1u : 0u) << 15) | ((B_KCONTIG ? 0u : 1u) << 16) |
-                         ((uint32_t)(TBN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
-  bool ok = true;
-  if (ktiles > 0) issue_tile(0, 0);
+                         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
+#pragma unroll
+  for (int d = 0; d < D; ++d) issue_tile(d);
   for (int kt = 0; kt < ktiles; ++kt) {
-    const int s = kt & 1;
-    asm volatile("cp.async.wait_group 0;" ::: "memory");       // this thread's chunks of tile kt have landed
-    transform(s);
+    if (kt >= 2 && !*failed) {
+      // MMAs of tile kt - 2 read ring stage (kt + D) % S and low-part buffer kt % 2
+      if (!mbar_wait(smem_u32(&bars[(kt - 2) % S]), (uint32_t)(((kt - 2) / S) & 1))) *failed = 1;
+    }
+    issue_tile(kt + D);
+    asm volatile("cp.async.wait_group %0;" ::"n"(D) : "memory");        // this thread's chunks of tile kt have landed
+    if (!(p.debug_skip & 4)) transform(kt);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
     if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t base = smem_u32(smem + s * TSTAGE_BYTES);
+      const uint32_t raw = smem_u32(smem + (kt % S) * Cfg::RAW_BYTES);
+      const uint32_t lo = smem_u32(lo_base + (kt & 1) * Cfg::RAW_BYTES);
 #pragma unroll
       for (int kk = 0; kk < TBK / 8; ++kk) {
-        // one k-step = 8 values: 32 bytes inside a K-major swizzle row, or one 8-row atom in an MN-major tile
+        // one k-step = 8 values: 32 bytes inside a K-major swizzle row, or two 4-row atoms of an MN-major tile
         const uint32_t a_adv = A_MCONTIG ? (uint32_t)(kk * (TBM / 32) * 1024) : (uint32_t)(kk * 32);
-        const uint32_t b_adv = B_KCONTIG ? (uint32_t)(kk * 32) : (uint32_t)(kk * (TBN / 32) * 1024);
-        const uint64_t da = A_MCONTIG ? umma_desc_mn(base + a_adv, TBM / 32) : umma_desc(base + a_adv);
-        const uint64_t dal = A_MCONTIG ? umma_desc_mn(base + TA_BYTES + a_adv, TBM / 32) : umma_desc(base + TA_BYTES + a_adv);
-        const uint64_t db = B_KCONTIG ? umma_desc(base + 2 * TA_BYTES + b_adv) : umma_desc_mn(base + 2 * TA_BYTES + b_adv, TBN / 32);
-        const uint64_t dbl = B_KCONTIG ? umma_desc(base + 2 * TA_BYTES + TB_BYTES + b_adv)
-                                       : umma_desc_mn(base + 2 * TA_BYTES + TB_BYTES + b_adv, TBN / 32);
-        umma_tf32(tmem, da, db, idesc, (kt | kk) != 0);
-        umma_tf32(tmem, da, dbl, idesc, 1);
-        umma_tf32(tmem, dal, db, idesc, 1);
+        const uint32_t b_adv = B_KCONTIG ? (uint32_t)(kk * 32) : (uint32_t)(kk * (BN / 32) * 1024);
+        const uint64_t da = A_MCONTIG ? umma_desc_mn(raw + a_adv, TBM / 32) : umma_desc(raw + a_adv);
+        const uint64_t dal = A_MCONTIG ? umma_desc_mn(lo + a_adv, TBM / 32) : umma_desc(lo + a_adv);
+        const uint64_t db = B_KCONTIG ? umma_desc(raw + Cfg::A_BYTES + b_adv) : umma_desc_mn(raw + Cfg::A_BYTES + b_adv, BN / 32);
+        const uint64_t dbl = B_KCONTIG ? umma_desc(lo + Cfg::A_BYTES + b_adv) : umma_desc_mn(lo + Cfg::A_BYTES + b_adv, BN / 32);
+        if (!(p.debug_skip & 1)) {
+          umma_tf32(tmem, da, db, idesc, (kt | kk) != 0);
+          umma_tf32(tmem, da, dbl, idesc, 1);
+          umma_tf32(tmem, dal, db, idesc, 1);
+        }
       }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[s]))
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[kt % S]))
                    : "memory");
     }
-    if (kt + 1 < ktiles) {
-      if (kt >= 1) {
-        // the other stage was read by the MMAs of tile kt - 1 (commit number (kt - 1) / 2 on its barrier)
-        const bool mine = mbar_wait(smem_u32(&bars[s ^ 1]), (uint32_t)(((kt - 1) >> 1) & 1));
-        if (!__syncthreads_and(mine)) { ok = false; break; }
-      }
-      issue_tile(kt + 1, s ^ 1);
-    }
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  bool ok = !*failed;
   if (ok && ktiles > 0) {
     const int last = ktiles - 1;
-    ok = mbar_wait(smem_u32(&bars[last & 1]), (uint32_t)((last >> 1) & 1));
+    ok = mbar_wait(smem_u32(&bars[last % S]), (uint32_t)((last / S) & 1));
   }
-  ok = __syncthreads_and(ok);
+  ok = __syncthreads_and(ok) && !*failed;
   if (!ok && tid == 0) atomicExch(error_flag, 1);
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
+  // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 and a (BN / 2)-column half -------------------
   if (ok) {
-    uint32_t v[32];
-    if (ktiles > 0) {
-      const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(32 * (warp >> 2));
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
-          "%24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-            "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-            "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-            "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-          : "r"(taddr)
-          : "memory");
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = 0u;
-    }
     const int m = m0 + 32 * (warp & 3) + lane;
-    const int nb = n0 + 32 * (warp >> 2);
-    if (m < p.M) {
-      float* out;
-      bool contiguous;
-      if (p.split_k > 1) {
-        out = partial + ((long long)sp * p.groups + g) * (long long)p.M * p.N + (long long)m * p.N + nb;
-        contiguous = (p.N & 3) == 0;
+#pragma unroll
+    for (int part = 0; part < BN / 64; ++part) {
+      const int col0 = (warp >> 2) * (BN / 2) + part * 32;
+      uint32_t v[32];
+      if (ktiles > 0) {
+        const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)col0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
+            "%24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       } else {
-        out = C + c_grp[g] + c_row[m] + (nb < p.N ? c_col[nb] : 0);
-        contiguous = p.c_vec != 0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0u;
       }
-      if (contiguous && nb + 32 <= p.N && (((uintptr_t)out) & 15) == 0) {
+      const int nb = n0 + col0;
+      if (m < p.M && nb < p.N) {
+        float* out;
+        bool contiguous;
+        if (p.split_k > 1) {
+          out = partial + ((long long)sp * p.groups + g) * (long long)p.M * p.N + (long long)m * p.N + nb;
+          contiguous = (p.N & 3) == 0;
+        } else {
+          out = C + c_grp[g] + c_row[m] + c_col[nb];
+          contiguous = p.c_vec != 0;
+        }
+        if (contiguous && nb + 32 <= p.N && (((uintptr_t)out) & 15) == 0) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(out + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                            __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-      } else if (p.split_k > 1) {
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(out + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                              __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+        } else if (p.split_k > 1) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (nb + j < p.N) out[j] = __uint_as_float(v[j]);
-      } else {
-        float* row = C + c_grp[g] + c_row[m];
+          for (int j = 0; j < 32; ++j)
+            if (nb + j < p.N) out[j] = __uint_as_float(v[j]);
+        } else {
+          float* row = C + c_grp[g] + c_row[m];
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (nb + j < p.N) row[c_col[nb + j]] = __uint_as_float(v[j]);
+          for (int j = 0; j < 32; ++j)
+            if (nb + j < p.N) row[c_col[nb + j]] = __uint_as_float(v[j]);
+        }
       }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TBN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+  }
+}
+
+
+// ---------------------------------------------------------------------------
+// Tensor-core path, warp-specialised (used for every contraction whose operands gather in uniform 16-byte
+// chunks). Cycle counters in the roles of earlier versions showed that a handful of warps each walking a long
+// dependent chain (table lookup -> mask -> address -> copy; 16 descriptors per k-tile in the MMA thread) bound
+// the kernel, not bandwidth or the tensor pipe. Hence many thin roles:
+//   warps 0-15, gather : the 16-byte chunks of a k-tile (A then B) form one flat list; thread t takes chunks
+//       t, t + 512, ...; each is one table lookup pair, one mask test and one cp.async (zero-filled where the
+//       window falls on padding or a dilation hole) into the raw tile of a ring stage; the thread's copies
+//       arrive on the stage's `landed` barrier when they complete. The warps run up to STAGES - 1 tiles ahead.
+//   warps 16-23, low part: wait for `landed`, read chunks back, store lo = x - tf32(x) into the stage's
+//       low-part tile, fence towards the async proxy and arrive on `ready`.
+//   warp 24, one thread : waits for `ready`, issues the 12 MMAs of the tile (raw x raw, raw x lo, lo x raw per
+//       k-step) from descriptors prepared before the loop, commits them to the stage's `empty` barrier.
+// After the last commit warps 0-7 read the accumulator from tensor memory and store it.
+// All waits are bounded; a role that times out raises the error word and leaves its loop, the others time
+// out in turn, everybody meets at the final barrier and tensor memory is released.
+template <int BN_>
+struct WsCfg {
+  static constexpr int BN = BN_;
+  static constexpr int STAGES = BN_ == 64 ? 4 : 3;
+  static constexpr int A_BYTES = TBM * TBK * 4, B_BYTES = BN_ * TBK * 4;
+  static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);          // raw A, raw B, low A, low B
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int A_CHUNKS = TBM * TBK / 4, B_CHUNKS = BN_ * TBK / 4;
+};
+constexpr int WS_GATHER = 512, WS_LOW = 256, WS_THREADS = WS_GATHER + WS_LOW + 32;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int BN, bool A_MCONTIG, bool B_KCONTIG, bool MASK>
+__global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
+    const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, const RowEnt* __restrict__ a_row,
+    const ColEnt* __restrict__ a_col, const long long* __restrict__ b_row, const long long* __restrict__ b_col,
+    const long long* __restrict__ c_row, const long long* __restrict__ c_col, const long long* __restrict__ a_grp,
+    const long long* __restrict__ b_grp, const long long* __restrict__ c_grp, float* __restrict__ partial,
+    int* __restrict__ error_flag, IGemmLaunch p) {
+  using Cfg = WsCfg<BN>;
+  constexpr int S = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* landed = (uint64_t*)(smem + S * Cfg::STAGE_BYTES);
+  uint64_t* ready = landed + S;
+  uint64_t* empty = ready + S;
+  uint32_t* tmem_slot = (uint32_t*)(empty + S);
+  volatile int* failed = (volatile int*)(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = blockIdx.x * TBM, n0 = blockIdx.y * BN;
+  const int g = blockIdx.z / p.split_k, sp = blockIdx.z % p.split_k;
+  const int kchunk = ((p.K + p.split_k - 1) / p.split_k + TBK - 1) / TBK * TBK;
+  const int kbeg = sp * kchunk, kend = min(p.K, kbeg + kchunk);
+  const int ktiles = kend > kbeg ? (kend - kbeg + TBK - 1) / TBK : 0;
+  constexpr int MMA_WARP = (WS_GATHER + WS_LOW) / 32;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&landed[s]), WS_GATHER);
+      mbar_init(smem_u32(&ready[s]), WS_LOW);
+      mbar_init(smem_u32(&empty[s]), 1);
+    }
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == MMA_WARP) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  // flat chunk index -> (offset inside the A or B tile, row index, k index of the chunk's first element)
+  //   K-major tile : chunk = row * 8 + kc         (4 consecutive k of one row)
+  //   MN-major tile: chunk = k * (rows / 4) + rc  (4 consecutive rows at one k)
+  auto a_chunk = [&](int idx, int& row, int& k) -> uint32_t {
+    if (A_MCONTIG) { k = idx >> 5; row = (idx & 31) * 4; return sw128_mn(idx & 31, k, TBM / 32); }
+    row = idx >> 3; k = (idx & 7) * 4; return sw128(row, idx & 7);
+  };
+  auto b_chunk = [&](int idx, int& row, int& k) -> uint32_t {
+    if (B_KCONTIG) { row = idx >> 3; k = (idx & 7) * 4; return sw128(row, idx & 7); }
+    constexpr int BMC = BN / 4;
+    k = idx / BMC; row = (idx % BMC) * 4; return sw128_mn(idx % BMC, k, BN / 32);
+  };
+
+  if (tid < WS_GATHER) {
+    // ------------------------------ gather -----------------------------------------------------------------
+    const float* Ag = A + a_grp[g];
+    const float* Bg = B + b_grp[g];
+    const int a_sh = (int)p.a_sh, a_sw = (int)p.a_sw;
+    // A thread's chunks sit at the same rows and k offsets in every k-tile: row lookups happen once, here;
+    // per tile only the k-dependent entries are fetched.
+    constexpr int NA = Cfg::A_CHUNKS / WS_GATHER, NBQ = Cfg::B_CHUNKS / WS_GATHER;
+    uint32_t a_so[NA], b_so[NBQ];
+    int a_kk[NA], b_kk[NBQ], a_ro[NA], a_h0[NA], a_w0[NA], b_no[NBQ];
+#pragma unroll
+    for (int q = 0; q < NA; ++q) {
+      int row;
+      a_so[q] = a_chunk(tid + q * WS_GATHER, row, a_kk[q]);
+      const int m = m0 + row;
+      if (m < p.M) { const RowEnt r = a_row[m]; a_ro[q] = (int)r.off; a_h0[q] = r.h0; a_w0[q] = r.w0; }
+      else { a_ro[q] = -1; a_h0[q] = 0; a_w0[q] = 0; }
+    }
+#pragma unroll
+    for (int q = 0; q < NBQ; ++q) {
+      int row;
+      b_so[q] = b_chunk(tid + q * WS_GATHER, row, b_kk[q]);
+      const int n = n0 + row;
+      b_no[q] = n < p.N ? (int)b_col[n] : -1;
+    }
+    long long dbg_wait = 0, dbg_t0 = clock64();
+    for (int j = 0; j < ktiles; ++j) {
+      const int s = j % S;
+      const int k0 = kbeg + j * TBK;
+      // k-dependent table entries first: their latency overlaps the wait for the stage
+      ColEnt ac[NA];
+      int br[NBQ];
+#pragma unroll
+      for (int q = 0; q < NA; ++q) {
+        const int k = k0 + a_kk[q];
+        ac[q] = (k < kend && (q == 0 || A_MCONTIG)) ? a_col[k] : ColEnt{-1, 0, 0};
+        if (!A_MCONTIG && q > 0) ac[q] = ac[0];                 // K-major: all of a thread's chunks share one k
+        if (k >= kend) ac[q].off = -1;
+      }
+#pragma unroll
+      for (int q = 0; q < NBQ; ++q) {
+        const int k = k0 + b_kk[q];
+        br[q] = k < kend ? (int)b_row[k] : -1;
+      }
+      if (j >= S) {
+        // the MMAs of tile j - S were the last readers of this stage
+        long long w0 = clock64();
+        if (*failed || !mbar_wait(smem_u32(&empty[s]), (uint32_t)((j / S - 1) & 1))) { *failed = 1; break; }
+        dbg_wait += clock64() - w0;
+      }
+      const uint32_t a_raw = smem_u32(smem + s * Cfg::STAGE_BYTES), b_raw = a_raw + Cfg::A_BYTES;
+#pragma unroll
+      for (int q = 0; q < NA; ++q) {
+        bool valid = a_ro[q] >= 0 && ac[q].off >= 0;
+        int o = a_ro[q] + (int)ac[q].off;
+        if (MASK) {
+          int ih = a_h0[q] + ac[q].dh, iw = a_w0[q] + ac[q].dw;
+          valid = valid && ih >= 0 && iw >= 0 && ih < p.Hd && iw < p.Wd;
+          if (p.ldh != 1) { valid = valid && (ih % p.ldh == 0); ih /= p.ldh; }
+          if (p.ldw != 1) { valid = valid && (iw % p.ldw == 0); iw /= p.ldw; }
+          o += ih * a_sh + iw * a_sw;
+        }
+        cp_async16(a_raw + a_so[q], valid ? Ag + o : Ag, valid);
+      }
+#pragma unroll
+      for (int q = 0; q < NBQ; ++q) {
+        const bool valid = b_no[q] >= 0 && br[q] >= 0;
+        cp_async16(b_raw + b_so[q], valid ? Bg + br[q] + b_no[q] : Bg, valid);
+      }
+      // this thread's arrival on `landed` fires when its copies above have completed
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&landed[s])) : "memory");
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    if ((p.debug_skip & 8) && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+      printf("gather : total %lld cycles, waiting for empty %lld, k-tiles %d\n", clock64() - dbg_t0, dbg_wait, ktiles);
+  } else if (tid < WS_GATHER + WS_LOW) {
+    // ------------------------------ low part ----------------------------------------------------------------
+    const int t = tid - WS_GATHER;
+    auto lo4 = [](const float4& v) -> float4 {
+      auto lo1 = [](float x) -> float {
+        const uint32_t u = __float_as_uint(x);
+        if ((u & 0x7F800000u) == 0x7F800000u) return 0.f;        // inf / nan stay in the high operand only
+        return x - __uint_as_float(u & 0xFFFFE000u);
+      };
+      return make_float4(lo1(v.x), lo1(v.y), lo1(v.z), lo1(v.w));
+    };
+    long long dbg_wait = 0, dbg_t0 = clock64();
+    for (int j = 0; j < ktiles; ++j) {
+      const int s = j % S;
+      long long w0 = clock64();
+      if (*failed || !mbar_wait(smem_u32(&landed[s]), (uint32_t)((j / S) & 1))) { *failed = 1; break; }
+      dbg_wait += clock64() - w0;
+      uint8_t* raw = smem + s * Cfg::STAGE_BYTES;                 // raw A, raw B contiguous; low parts follow
+      uint8_t* low = raw + Cfg::A_BYTES + Cfg::B_BYTES;
+      // the swizzle only permutes 16-byte chunks inside a tile, so the low-part pass can walk the bytes linearly
+#pragma unroll
+      for (int q = 0; q < (Cfg::A_CHUNKS + Cfg::B_CHUNKS) / WS_LOW; ++q) {
+        const uint32_t off = (uint32_t)(t + q * WS_LOW) * 16u;
+        *reinterpret_cast<float4*>(low + off) = lo4(*reinterpret_cast<const float4*>(raw + off));
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(smem_u32(&ready[s]));
+    }
+    if ((p.debug_skip & 8) && t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+      printf("lowpart: total %lld cycles, waiting for landed %lld\n", clock64() - dbg_t0, dbg_wait);
+  } else if (lane == 0) {
+    // ------------------------------ MMA issuer --------------------------------------------------------------
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MCONTIG ? 1u : 0u) << 15) |
+                           ((B_KCONTIG ? 0u : 1u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
+    // descriptors of stage 0; another stage adds STAGE_BYTES / 16 to the address field, a k-step adds a constant
+    const uint32_t base0 = smem_u32(smem);
+    const uint64_t d_a = A_MCONTIG ? umma_desc_mn(base0, TBM / 32) : umma_desc(base0);
+    const uint64_t d_b = B_KCONTIG ? umma_desc(base0 + Cfg::A_BYTES) : umma_desc_mn(base0 + Cfg::A_BYTES, BN / 32);
+    constexpr uint64_t LOW = (uint64_t)((Cfg::A_BYTES + Cfg::B_BYTES) >> 4);
+    constexpr uint64_t A_STEP = (uint64_t)((A_MCONTIG ? (TBM / 32) * 1024 : 32) >> 4);
+    constexpr uint64_t B_STEP = (uint64_t)((B_KCONTIG ? 32 : (BN / 32) * 1024) >> 4);
+    long long dbg_wait = 0, dbg_t0 = clock64();
+    for (int j = 0; j < ktiles; ++j) {
+      const int s = j % S;
+      long long w0 = clock64();
+      if (*failed || !mbar_wait(smem_u32(&ready[s]), (uint32_t)((j / S) & 1))) { *failed = 1; break; }
+      dbg_wait += clock64() - w0;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint64_t st = (uint64_t)((s * Cfg::STAGE_BYTES) >> 4);
+#pragma unroll
+      for (int kk = 0; kk < TBK / 8; ++kk) {
+        const uint64_t da = d_a + st + kk * A_STEP, db = d_b + st + kk * B_STEP;
+        umma_tf32(tmem, da, db, idesc, (j | kk) != 0);
+        umma_tf32(tmem, da, db + LOW, idesc, 1);
+        umma_tf32(tmem, da + LOW, db, idesc, 1);
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty[s]))
+                   : "memory");
+    }
+    if ((p.debug_skip & 8) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+      printf("mma    : total %lld cycles, waiting for ready %lld\n", clock64() - dbg_t0, dbg_wait);
+  }
+
+  if (warp < 8) {
+    // ------------------------------ epilogue ---------------------------------------------------------------
+    bool ok = !*failed;
+    if (ok && ktiles > 0) {
+      const int last = ktiles - 1;
+      ok = mbar_wait(smem_u32(&empty[last % S]), (uint32_t)((last / S) & 1));
+      if (!ok) *failed = 1;
+    }
+    ok = __all_sync(0xFFFFFFFFu, ok);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const int m = m0 + 32 * (warp & 3) + lane;
+#pragma unroll
+      for (int part = 0; part < BN / 64; ++part) {
+        const int col0 = (warp >> 2) * (BN / 2) + part * 32;
+        uint32_t v[32];
+        if (ktiles > 0) {
+          const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)col0;
+          asm volatile(
+              "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+              "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+              "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+              : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+                "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+              : "r"(taddr)
+              : "memory");
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int q = 0; q < 32; ++q) v[q] = 0u;
+        }
+        const int nb = n0 + col0;
+        if (m < p.M && nb < p.N) {
+          float* out;
+          bool contiguous;
+          if (p.split_k > 1) {
+            out = partial + ((long long)sp * p.groups + g) * (long long)p.M * p.N + (long long)m * p.N + nb;
+            contiguous = (p.N & 3) == 0;
+          } else {
+            out = C + c_grp[g] + c_row[m] + c_col[nb];
+            contiguous = p.c_vec != 0;
+          }
+          if (contiguous && nb + 32 <= p.N && (((uintptr_t)out) & 15) == 0) {
+#pragma unroll
+            for (int q = 0; q < 32; q += 4)
+              *reinterpret_cast<float4*>(out + q) = make_float4(__uint_as_float(v[q]), __uint_as_float(v[q + 1]),
+                                                                __uint_as_float(v[q + 2]), __uint_as_float(v[q + 3]));
+          } else if (p.split_k > 1) {
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              if (nb + q < p.N) out[q] = __uint_as_float(v[q]);
+          } else {
+            float* row = C + c_grp[g] + c_row[m];
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              if (nb + q < p.N) row[c_col[nb + q]] = __uint_as_float(v[q]);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (tid == 0 && *failed) atomicExch(error_flag, 1);
+  if (warp == MMA_WARP) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
   }
 }
 
@@ -865,31 +1194,77 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
       configured = true;
     }
     dim3 grid((p.M + TBM - 1) / TBM, (p.N + TBN - 1) / TBN, p.groups * p.split_k);
-    if (p.vec) {
+    if (p.vec && !p.old_vec) {
+      static bool configured_w = false;
+      if (!configured_w) {
+#define SETATTRW(BN_, AM, BK_, MK)                                                                             \
+  cudaFuncSetAttribute(igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                       WsCfg<BN_>::SMEM)
+#define SETALLW(BN_)                                                                                                  \
+  SETATTRW(BN_, false, false, false); SETATTRW(BN_, false, false, true); SETATTRW(BN_, false, true, false);           \
+  SETATTRW(BN_, false, true, true); SETATTRW(BN_, true, false, false); SETATTRW(BN_, true, false, true);              \
+  SETATTRW(BN_, true, true, false); SETATTRW(BN_, true, true, true)
+        SETALLW(64);
+        SETALLW(128);
+#undef SETALLW
+#undef SETATTRW
+        configured_w = true;
+      }
+      const bool wide = p.N >= 128 && p.wide_n;
+      dim3 gridw((p.M + TBM - 1) / TBM, (p.N + (wide ? 128 : 64) - 1) / (wide ? 128 : 64), p.groups * p.split_k);
+#define LAUNCHW(BN_, AM, BK_, MK)                                                                                     \
+  igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK><<<gridw, WS_THREADS, WsCfg<BN_>::SMEM, stream>>>(                          \
+      (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,       \
+      (float*)partial, error_flag, p)
+#define SWITCHW(BN_)                                   \
+  switch (v) {                                         \
+    case 0: LAUNCHW(BN_, false, false, false); break;  \
+    case 1: LAUNCHW(BN_, false, false, true); break;   \
+    case 2: LAUNCHW(BN_, false, true, false); break;   \
+    case 3: LAUNCHW(BN_, false, true, true); break;    \
+    case 4: LAUNCHW(BN_, true, false, false); break;   \
+    case 5: LAUNCHW(BN_, true, false, true); break;    \
+    case 6: LAUNCHW(BN_, true, true, false); break;    \
+    default: LAUNCHW(BN_, true, true, true); break;    \
+  }
+      if (wide) { SWITCHW(128) } else { SWITCHW(64) }
+#undef SWITCHW
+#undef LAUNCHW
+    } else if (p.vec) {
       static bool configured_v = false;
       if (!configured_v) {
-#define SETATTRV(AM, BK_, MK) \
-  cudaFuncSetAttribute(igemm_tf32x3_vec_kernel<AM, BK_, MK>, cudaFuncAttributeMaxDynamicSharedMemorySize, TSMEM_BYTES)
-        SETATTRV(false, false, false); SETATTRV(false, false, true); SETATTRV(false, true, false); SETATTRV(false, true, true);
-        SETATTRV(true, false, false); SETATTRV(true, false, true); SETATTRV(true, true, false); SETATTRV(true, true, true);
+#define SETATTRV(BN_, AM, BK_, MK)                                                                              \
+  cudaFuncSetAttribute(igemm_tf32x3_vec_kernel<BN_, AM, BK_, MK>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                       VecCfg<BN_>::SMEM)
+#define SETALL(BN_)                                                                                                   \
+  SETATTRV(BN_, false, false, false); SETATTRV(BN_, false, false, true); SETATTRV(BN_, false, true, false);           \
+  SETATTRV(BN_, false, true, true); SETATTRV(BN_, true, false, false); SETATTRV(BN_, true, false, true);              \
+  SETATTRV(BN_, true, true, false); SETATTRV(BN_, true, true, true)
+        SETALL(64);
+        SETALL(128);
+#undef SETALL
 #undef SETATTRV
         configured_v = true;
       }
-#define LAUNCHV(AM, BK_, MK)                                                                                          \
-  igemm_tf32x3_vec_kernel<AM, BK_, MK><<<grid, TNT, TSMEM_BYTES, stream>>>((const float*)A, (const float*)B, (float*)C, \
-                                                                            a_row, a_col, b_row, b_col, c_row, c_col,   \
-                                                                            a_grp, b_grp, c_grp, (float*)partial,       \
-                                                                            error_flag, p)
-      switch (v) {
-        case 0: LAUNCHV(false, false, false); break;
-        case 1: LAUNCHV(false, false, true); break;
-        case 2: LAUNCHV(false, true, false); break;
-        case 3: LAUNCHV(false, true, true); break;
-        case 4: LAUNCHV(true, false, false); break;
-        case 5: LAUNCHV(true, false, true); break;
-        case 6: LAUNCHV(true, true, false); break;
-        default: LAUNCHV(true, true, true); break;
-      }
+      const bool wide = p.N >= 128 && p.wide_n;
+      dim3 gridv((p.M + TBM - 1) / TBM, (p.N + (wide ? 128 : 64) - 1) / (wide ? 128 : 64), p.groups * p.split_k);
+#define LAUNCHV(BN_, AM, BK_, MK)                                                                                     \
+  igemm_tf32x3_vec_kernel<BN_, AM, BK_, MK><<<gridv, TNT, VecCfg<BN_>::SMEM, stream>>>(                               \
+      (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,       \
+      (float*)partial, error_flag, p)
+#define SWITCHV(BN_)                                   \
+  switch (v) {                                         \
+    case 0: LAUNCHV(BN_, false, false, false); break;  \
+    case 1: LAUNCHV(BN_, false, false, true); break;   \
+    case 2: LAUNCHV(BN_, false, true, false); break;   \
+    case 3: LAUNCHV(BN_, false, true, true); break;    \
+    case 4: LAUNCHV(BN_, true, false, false); break;   \
+    case 5: LAUNCHV(BN_, true, false, true); break;    \
+    case 6: LAUNCHV(BN_, true, true, false); break;    \
+    default: LAUNCHV(BN_, true, true, true); break;    \
+  }
+      if (wide) { SWITCHV(128) } else { SWITCHV(64) }
+#undef SWITCHV
 #undef LAUNCHV
     } else {
 #define LAUNCHT(AM, BK_, MK)                                                                                     \

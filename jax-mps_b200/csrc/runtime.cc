@@ -538,6 +538,9 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       // tiny products stay on the fp32 FMA kernel; everything else goes to the tensor cores (3xTF32)
       p.vec = s.ig.vec && !getenv("B200_NO_VEC_GATHER");
       p.c_vec = s.ig.c_vec;
+      p.wide_n = getenv("B200_NARROW_TILES") ? 0 : 1;
+      p.old_vec = getenv("B200_OLD_VEC") ? 1 : 0;
+      p.debug_skip = getenv("B200_DEBUG_SKIP") ? atoi(getenv("B200_DEBUG_SKIP")) : 0;
       p.tensor_cores = c->tensor_cores && (long long)s.ig.M * s.ig.N * s.ig.K * s.ig.groups >= (1LL << 18) && s.ig.K >= 16;
       const void* tables[9];
       for (int k = 0; k < 9; k++) tables[k] = x.ptrs[s.args[3 + k]];
