@@ -1042,7 +1042,10 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
       auto lo1 = [](float x) -> float {
         const uint32_t u = __float_as_uint(x);
         if ((u & 0x7F800000u) == 0x7F800000u) return 0.f;        // inf / nan stay in the high operand only
-        return x - __uint_as_float(u & 0xFFFFE000u);
+        // the tensor core truncates the raw word to its TF32 bits; the remainder is exact in fp32 and is
+        // rounded to nearest on 10 mantissa bits here, so the second truncation in hardware is a no-op
+        const float l = x - __uint_as_float(u & 0xFFFFE000u);
+        return __uint_as_float((__float_as_uint(l) + 0x1000u) & 0xFFFFE000u);
       };
       return make_float4(lo1(v.x), lo1(v.y), lo1(v.z), lo1(v.w));
     };

@@ -36,14 +36,17 @@ def _rank_main(rank, world, port, q):
     def all_reduce(xs):
         out = []
         for x in xs:
-            t = torch.from_numpy(np.ascontiguousarray(x, dtype=np.float64))
+            t = torch.from_numpy(np.array(x, dtype=np.float64).reshape(-1))
             dist.all_reduce(t)
-            out.append(t.numpy())
+            out.append(t.numpy().reshape(np.shape(x)))
         return out
 
-    outs = interp.Interp(prog.text, collective=all_reduce, partition_id=rank, wide=True).run(args)
-    q.put((rank, [np.asarray(o) for o in outs]))
-    dist.barrier()
+    try:
+        outs = interp.Interp(prog.text, collective=all_reduce, partition_id=rank, wide=True).run(args)
+        q.put((rank, [np.asarray(o) for o in outs]))
+        dist.barrier()
+    except Exception as e:                       # surface the failure instead of leaving the parent to time out
+        q.put((rank, repr(e)))
     dist.destroy_process_group()
 
 
@@ -60,6 +63,8 @@ def test_two_rank_data_parallel_step_matches_averaged_twin():
     for p in procs:
         p.start()
     got = dict(q.get(timeout=300) for _ in range(world))
+    for r, v in got.items():
+        assert not isinstance(v, str), f"rank {r} failed: {v}"
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
