@@ -206,6 +206,19 @@ b200_error* b200_client_profile_report(b200_client* client, char** json);
 /* Total kernels launched by this client since creation (generated + static + collectives). */
 int64_t b200_client_launch_count(const b200_client* client);
 
+/* Split-K fp32 matrix product that allocates nothing: c[m,n] = a[m,k] * b[k,n], dense row-major DEVICE pointers,
+ * enqueued on `cuda_stream` (a cudaStream_t; NULL = the default stream) of the current device. It has no
+ * counterpart in the reference. It is for callers that must not allocate device memory when they need a product:
+ * code inside a memory-pool callback or under a framework allocator's lock, and loops that may not take the
+ * driver's allocation lock. The partial sums of the K splits live in an 8 MiB array inside the library image (held
+ * by every GPU that loads the library, until exit), so 2 * m * n floats must fit in 8 MiB (m * n <= 1048576);
+ * larger products are refused with B200_INVALID_ARGUMENT. The first call on each device looks up the array's
+ * device address; make that call before any stream capture. All calls share the array and it keeps the last
+ * call's contents (each call overwrites the part it reads, nothing needs to start at zero): calls that overlap
+ * in time on one device, from different streams or threads, race - serialise them. */
+b200_error* b200_matmul_f32_static_scratch(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                                           void* cuda_stream);
+
 #pragma GCC visibility pop
 #ifdef __cplusplus
 }

@@ -127,6 +127,7 @@ SIGNATURES = {
     "b200_client_launch_count": (C.c_int64, [_P]),
     "b200_client_set_profiling": (_P, [_P, C.c_int]),
     "b200_client_profile_report": (_P, [_P, C.POINTER(_P)]),
+    "b200_matmul_f32_static_scratch": (_P, [_P, _P, _P, C.c_int64, C.c_int64, C.c_int64, _P]),
 }
 
 _lib = None
@@ -437,6 +438,18 @@ class Client:
 
     def launch_count(self) -> int:
         return load_library().b200_client_launch_count(self._h)
+
+    def matmul_static_scratch(self, a: Buffer, b: Buffer, out: Buffer):
+        """out[m,n] = a[m,k] @ b[k,n] (float32 buffers of this client) through the entry point that allocates
+        nothing: the K-split partial sums use an 8 MiB array inside the library (m * n <= 1048576). Enqueued on
+        the compute stream after the operands are ready; calls share the array, so do not overlap them."""
+        (m, k), (k2, n) = a.shape, b.shape
+        if k != k2 or out.shape != (m, n) or not (a.dtype == b.dtype == out.dtype == "f32"):
+            raise B200Error("matmul_static_scratch wants f32 buffers a[m,k], b[k,n], out[m,n]", 3)
+        for x in (a, b, out):
+            x.block_until_ready()
+        _check(load_library().b200_matmul_f32_static_scratch(a.device_pointer(), b.device_pointer(),
+                                                             out.device_pointer(), m, n, k, self.compute_stream()))
 
     def close(self):
         if getattr(self, "_h", None):

@@ -16,6 +16,8 @@
 //   C address = c_grp[g] + c_row[m] + c_col[n]
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <algorithm>
+#include <mutex>
 #include <cstdio>
 
 #include "kernels.h"
@@ -1317,6 +1319,113 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
     e = cudaGetLastError();
   }
   return e;
+}
+
+
+// ---------------------------------------------------------------------------
+// Split-K fp32 matrix product whose scratch lives in the library image instead of an allocation.
+//
+// Some callers may not allocate device memory at the moment they need a product: code running inside a
+// memory-pool callback or under a framework allocator lock, a library initialiser that must not disturb the
+// process's memory accounting, a real-time loop that forbids anything that can take the driver's allocation
+// lock. For them the partial sums of the K splits go to a file-scope device array (8 MiB, resident on every
+// GPU that loads this library until the process exits) rather than to arena or pool memory.
+namespace {
+
+constexpr size_t kStaticScratchFloats = 2u << 20;                    // 8 MiB
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+constexpr int SBM = 64, SBN = 64, SBK = 16;
+
+// C partial [split][M][N] = A[M, k-range] * B[k-range, N]; dense row-major operands, 256 threads, 4 x 4 per thread.
+__global__ void __launch_bounds__(256) matmul_splitk_static_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                                                                  float* __restrict__ partial, int M, int N, int K,
+                                                                  int splits) {
+  __shared__ float As[SBK][SBM + 1];
+  __shared__ float Bs[SBK][SBN + 1];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.x * SBM, n0 = blockIdx.y * SBN, sp = blockIdx.z;
+  const int kchunk = ((K + splits - 1) / splits + SBK - 1) / SBK * SBK;
+  const int kbeg = sp * kchunk, kend = min(K, kbeg + kchunk);
+  float acc[4][4] = {};
+  for (int k0 = kbeg; k0 < kend; k0 += SBK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int idx = tid + 256 * i;                      // 1024 elements of each tile
+      int am = idx / SBK, ak = idx % SBK;
+      As[ak][am] = (m0 + am < M && k0 + ak < kend) ? A[(size_t)(m0 + am) * K + k0 + ak] : 0.f;
+      int bk = idx / SBN, bn = idx % SBN;
+      Bs[bk][bn] = (k0 + bk < kend && n0 + bn < N) ? B[(size_t)(k0 + bk) * N + n0 + bn] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < SBK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty * 4 + i]; b[i] = Bs[kk][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  float* out = partial + (size_t)sp * M * N;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (m < M && n < N) out[(size_t)m * N + n] = acc[i][j];      // every element of the split's slab is written
+    }
+}
+
+__global__ void __launch_bounds__(256) splitk_sum_static_kernel(const float* __restrict__ partial, float* __restrict__ C,
+                                                               long long total, int splits) {
+  long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= total) return;
+  float s = 0.f;
+  for (int k = 0; k < splits; ++k) s += partial[(long long)k * total + i];
+  C[i] = s;
+}
+
+}  // namespace
+
+size_t static_scratch_bytes() { return kStaticScratchFloats * sizeof(float); }
+
+cudaError_t matmul_f32_static_scratch(const float* A, const float* B, float* C, int M, int N, int K, cudaStream_t stream,
+                                      const char** why) {
+  *why = nullptr;
+  // The array's name is a host-side handle; kernels need its device address, which differs per device.
+  static float* scratch_of_device[64] = {};
+  static bool resolved[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) { *why = "device ordinal out of range"; return cudaErrorInvalidDevice; }
+  std::lock_guard<std::mutex> lock(mu);     // also keeps two host threads from launching into the array at once
+  if (!resolved[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) { *why = "cudaGetSymbolAddress(g_static_scratch) failed"; return e; }
+    scratch_of_device[dev] = (float*)ptr;
+    resolved[dev] = true;
+  }
+  float* scratch = scratch_of_device[dev];
+  const long long mn = (long long)M * N;
+  int splits = (int)std::min<long long>(std::max(2, (K + 255) / 256), 32);
+  while (splits > 2 && (long long)splits * mn > (long long)kStaticScratchFloats) splits--;
+  if ((long long)splits * mn > (long long)kStaticScratchFloats) {
+    *why = "M * N is too large for the static scratch (two K splits of M * N floats must fit in 8 MiB)";
+    return cudaErrorInvalidValue;
+  }
+  dim3 grid((M + SBM - 1) / SBM, (N + SBN - 1) / SBN, splits);
+  matmul_splitk_static_kernel<<<grid, 256, 0, stream>>>(A, B, scratch, M, N, K, splits);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  splitk_sum_static_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, stream>>>(scratch, C, mn, splits);
+  return cudaGetLastError();
 }
 
 }  // namespace b200

@@ -25,3 +25,12 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
                              void* partial, int* error_flag, cudaStream_t stream, int* launches);
 
 }  // namespace b200
+
+namespace b200 {
+// Split-K fp32 product C[M,N] = A[M,K] * B[K,N] (dense row-major device pointers) whose partial sums go to a
+// file-scope device array instead of allocated memory. `*why` explains a refusal. The first call on a device
+// resolves the array's device address (cudaGetSymbolAddress); make it before any stream capture.
+cudaError_t matmul_f32_static_scratch(const float* A, const float* B, float* C, int M, int N, int K, cudaStream_t stream,
+                                      const char** why);
+size_t static_scratch_bytes();
+}  // namespace b200

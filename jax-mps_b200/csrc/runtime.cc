@@ -1306,4 +1306,20 @@ b200_error* b200_event_destroy(b200_event* e) {
   return nullptr;
 }
 
+b200_error* b200_matmul_f32_static_scratch(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                                           void* cuda_stream) {
+  if (!a || !b || !c) return make_error(B200_INVALID_ARGUMENT, "null operand pointer");
+  if (m <= 0 || n <= 0 || k <= 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX || m * k > INT32_MAX * 64ll ||
+      k * n > INT32_MAX * 64ll)
+    return make_error(B200_INVALID_ARGUMENT, "matrix extents must be positive and fit the kernel's index range");
+  const char* why = nullptr;
+  cudaError_t e = b200::matmul_f32_static_scratch(a, b, c, (int)m, (int)n, (int)k, (cudaStream_t)cuda_stream, &why);
+  if (e == cudaSuccess) return nullptr;
+  std::string msg = why ? why : cudaGetErrorString(e);
+  if (e == cudaErrorInvalidValue && why)
+    return make_error(B200_INVALID_ARGUMENT, msg + " (m=" + std::to_string(m) + ", n=" + std::to_string(n) + ", limit " +
+                                                 std::to_string(b200::static_scratch_bytes()) + " bytes)");
+  return make_error(B200_INTERNAL, "static-scratch product failed: " + msg);
+}
+
 }  // extern "C"
