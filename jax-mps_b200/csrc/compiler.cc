@@ -974,6 +974,25 @@ struct Planner {
       p.vec = 1;
       p.a_contig = a_major;
       p.b_contig = b_major == 0 ? 1 : 0;
+      // Segment gather: every aligned run of 32 indices along an operand's contiguous dimension is 32 consecutive
+      // floats at one window position, so a whole 128-byte tile row shares one address and one mask.
+      auto a_run = [&](int i0) {
+        for (int i = 1; i < 32; i++) {
+          if (a_major == 0) { if (acol[i0 + i].off != acol[i0].off + i || acol[i0 + i].dh != acol[i0].dh || acol[i0 + i].dw != acol[i0].dw) return false; }
+          else if (arow[i0 + i].off != arow[i0].off + i || arow[i0 + i].h0 != arow[i0].h0 || arow[i0 + i].w0 != arow[i0].w0) return false;
+        }
+        return true;
+      };
+      auto b_run = [&](int i0) {
+        const auto& t = b_major == 0 ? bcol : bn;
+        for (int i = 1; i < 32; i++) if (t[i0 + i] != t[i0] + i) return false;
+        return true;
+      };
+      const int a_ext = a_major == 0 ? p.K : p.M, b_ext = b_major == 0 ? p.K : p.N;
+      bool seg = p.K % 32 == 0 && a_ext % 32 == 0 && b_ext % 32 == 0;
+      for (int i = 0; seg && i < a_ext; i += 32) seg = a_run(i);
+      for (int i = 0; seg && i < b_ext; i += 32) seg = b_run(i);
+      p.seg = seg ? 1 : 0;
     }
     p.c_vec = 1;
     for (size_t n = 1; n < cn.size(); n++) if (cn[n] != cn[0] + (long long)n) p.c_vec = 0;
@@ -1551,7 +1570,7 @@ void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& o
         break;
       case Step::IGEMM:
         os << "igemm M=" << s.ig.M << " N=" << s.ig.N << " K=" << s.ig.K << " G=" << s.ig.groups << " splitK=" << s.ig.split_k
-           << " a_contig=" << s.ig.a_contig << " b_contig=" << s.ig.b_contig << " vec=" << s.ig.vec << " " << s.label;
+           << " a_contig=" << s.ig.a_contig << " b_contig=" << s.ig.b_contig << " vec=" << s.ig.vec << " seg=" << s.ig.seg << " " << s.label;
         break;
       case Step::MEMCPY: os << "memcpy " << s.bytes; break;
       case Step::WHILE: os << "while trip=" << s.trip_count; break;

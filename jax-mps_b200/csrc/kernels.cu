@@ -585,295 +585,6 @@ __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, int mn_atom
          ((uint64_t)((mn_atoms * 512) >> 4) << 32) | (1ull << 46) | (1ull << 61);
 }
 
-// Pipeline of the vector-gather kernel: raw tiles live in a ring of RAW_STAGES stages filled PREFETCH k-tiles
-// ahead by cp.async; the low-part tiles are double-buffered. Iteration kt: (a) wait until the MMAs of tile
-// kt - 2 have retired (they were the last readers of the ring stage about to be refilled and of the low-part
-// buffer about to be rewritten), (b) issue the gather of tile kt + PREFETCH, (c) wait for this thread's chunks
-// of tile kt, (d) write their low parts, (e) fence + barrier, (f) one thread issues the 12 MMAs of tile kt and
-// commits them to bars[kt % RAW_STAGES].
-template <int BN_>
-struct VecCfg {
-  static constexpr int BN = BN_;
-  static constexpr int PREFETCH = BN_ == 64 ? 3 : 2;
-  static constexpr int RAW_STAGES = PREFETCH + 2;
-  static constexpr int A_BYTES = TBM * TBK * 4, B_BYTES = BN_ * TBK * 4;
-  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;
-  static constexpr int SMEM = RAW_STAGES * RAW_BYTES + 2 * RAW_BYTES + 1024 + 128;
-  static constexpr int B_CHUNKS = BN_ / 32;          // 16-byte chunks of B per thread and k-tile
-};
-
-template <int BN, bool A_MCONTIG, bool B_KCONTIG, bool MASK>
-__global__ void __launch_bounds__(TNT, 1) igemm_tf32x3_vec_kernel(const float* __restrict__ A, const float* __restrict__ B,
-                                                                 float* __restrict__ C, const RowEnt* __restrict__ a_row,
-                                                                 const ColEnt* __restrict__ a_col,
-                                                                 const long long* __restrict__ b_row,
-                                                                 const long long* __restrict__ b_col,
-                                                                 const long long* __restrict__ c_row,
-                                                                 const long long* __restrict__ c_col,
-                                                                 const long long* __restrict__ a_grp,
-                                                                 const long long* __restrict__ b_grp,
-                                                                 const long long* __restrict__ c_grp,
-                                                                 float* __restrict__ partial, int* __restrict__ error_flag,
-                                                                 IGemmLaunch p) {
-  using Cfg = VecCfg<BN>;
-  constexpr int S = Cfg::RAW_STAGES, D = Cfg::PREFETCH, NBC = Cfg::B_CHUNKS;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* lo_base = smem + S * Cfg::RAW_BYTES;                       // two low-part buffers
-  uint64_t* bars = (uint64_t*)(lo_base + 2 * Cfg::RAW_BYTES);
-  uint32_t* tmem_slot = (uint32_t*)(bars + S);
-  volatile int* failed = (volatile int*)(tmem_slot + 1);
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.x * TBM, n0 = blockIdx.y * BN;
-  const int g = blockIdx.z / p.split_k, sp = blockIdx.z % p.split_k;
-  const int kchunk = ((p.K + p.split_k - 1) / p.split_k + TBK - 1) / TBK * TBK;
-  const int kbeg = sp * kchunk, kend = min(p.K, kbeg + kchunk);
-  const int ktiles = kend > kbeg ? (kend - kbeg + TBK - 1) / TBK : 0;
-  const float* Ag = A + a_grp[g];
-  const float* Bg = B + b_grp[g];
-
-  if (tid == 0) {
-    for (int s = 0; s < S; ++s) mbar_init(smem_u32(&bars[s]), 1);
-    *failed = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = *tmem_slot;
-
-  // ---- per-thread gather state --------------------------------------------------------------------
-  // K-major operand : chunk tid % 8 of rows tid / 8 + 32 i        MN-major operand: row-chunk tid % 32 (A) or
-  //                                                               tid % (BN / 4) (B), k strided over the rest
-  RowEnt arow[A_MCONTIG ? 1 : 4];
-  bool arow_ok[A_MCONTIG ? 1 : 4];
-  if (A_MCONTIG) {
-    int m = m0 + (tid & 31) * 4;
-    arow_ok[0] = m < p.M;
-    arow[0] = arow_ok[0] ? a_row[m] : RowEnt{0, 0, 0};
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      int m = m0 + (tid >> 3) + 32 * i;
-      arow_ok[i] = m < p.M;
-      arow[i] = arow_ok[i] ? a_row[m] : RowEnt{0, 0, 0};
-    }
-  }
-  constexpr int BMC = BN / 4;                       // n-chunks per k-row of an MN-major B tile
-  long long bcol[B_KCONTIG ? NBC : 1];
-  bool bcol_ok[B_KCONTIG ? NBC : 1];
-  if (B_KCONTIG) {
-#pragma unroll
-    for (int i = 0; i < NBC; ++i) {
-      int n = n0 + (tid >> 3) + 32 * i;
-      bcol_ok[i] = n < p.N;
-      bcol[i] = bcol_ok[i] ? b_col[n] : 0;
-    }
-  } else {
-    int n = n0 + (tid % BMC) * 4;
-    bcol_ok[0] = n < p.N;
-    bcol[0] = bcol_ok[0] ? b_col[n] : 0;
-  }
-
-  auto a_src = [&](const RowEnt& r, bool rok, const ColEnt& c, bool cok, bool& valid) -> const float* {
-    valid = rok && cok;
-    if (!valid) return Ag;
-    if (MASK) {
-      int ih = r.h0 + c.dh, iw = r.w0 + c.dw;
-      if (ih < 0 || iw < 0 || ih >= p.Hd || iw >= p.Wd) { valid = false; return Ag; }
-      if (p.ldh != 1) { if (ih % p.ldh) { valid = false; return Ag; } ih /= p.ldh; }
-      if (p.ldw != 1) { if (iw % p.ldw) { valid = false; return Ag; } iw /= p.ldw; }
-      return Ag + r.off + c.off + (long long)ih * p.a_sh + (long long)iw * p.a_sw;
-    }
-    return Ag + r.off + c.off;
-  };
-
-  uint32_t a_off[4], b_off[NBC];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-    a_off[i] = A_MCONTIG ? sw128_mn(tid & 31, (tid >> 5) + 8 * i, TBM / 32) : sw128((tid >> 3) + 32 * i, tid & 7);
-#pragma unroll
-  for (int i = 0; i < NBC; ++i)
-    b_off[i] = B_KCONTIG ? sw128((tid >> 3) + 32 * i, tid & 7) : sw128_mn(tid % BMC, tid / BMC + (TNT / BMC) * i, BN / 32);
-
-  auto issue_tile = [&](int kt) {
-    if (kt < ktiles && !(p.debug_skip & 2)) {
-      const int k0 = kbeg + kt * TBK;
-      const uint32_t st = smem_u32(smem + (kt % S) * Cfg::RAW_BYTES);
-      const uint32_t a_raw = st, b_raw = st + Cfg::A_BYTES;
-      if (A_MCONTIG) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          int k = k0 + (tid >> 5) + 8 * i;
-          bool cok = k < kend, valid;
-          ColEnt c = cok ? a_col[k] : ColEnt{0, 0, 0};
-          const float* src = a_src(arow[0], arow_ok[0], c, cok, valid);
-          cp_async16(a_raw + a_off[i], src, valid);
-        }
-      } else {
-        int k = k0 + (tid & 7) * 4;
-        bool cok = k < kend;
-        ColEnt c = cok ? a_col[k] : ColEnt{0, 0, 0};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          bool valid;
-          const float* src = a_src(arow[i], arow_ok[i], c, cok, valid);
-          cp_async16(a_raw + a_off[i], src, valid);
-        }
-      }
-      if (B_KCONTIG) {
-        int k = k0 + (tid & 7) * 4;
-        bool kok = k < kend;
-        long long br = kok ? b_row[k] : 0;
-#pragma unroll
-        for (int i = 0; i < NBC; ++i) cp_async16(b_raw + b_off[i], Bg + br + bcol[i], kok && bcol_ok[i]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < NBC; ++i) {
-          int k = k0 + tid / BMC + (TNT / BMC) * i;
-          bool kok = k < kend;
-          long long br = kok ? b_row[k] : 0;
-          cp_async16(b_raw + b_off[i], Bg + br + bcol[0], kok && bcol_ok[0]);
-        }
-      }
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");          // one group per k-tile, empty past the end
-  };
-
-  auto lo_of = [](float x) -> float {
-    const uint32_t u = __float_as_uint(x);
-    if ((u & 0x7F800000u) == 0x7F800000u) return 0.f;          // inf / nan stay in the high operand only
-    return x - __uint_as_float(u & 0xFFFFE000u);
-  };
-  auto transform = [&](int kt) {
-    const uint8_t* raw = smem + (kt % S) * Cfg::RAW_BYTES;
-    uint8_t* lo = lo_base + (kt & 1) * Cfg::RAW_BYTES;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float4 v = *reinterpret_cast<const float4*>(raw + a_off[i]);
-      *reinterpret_cast<float4*>(lo + a_off[i]) = make_float4(lo_of(v.x), lo_of(v.y), lo_of(v.z), lo_of(v.w));
-    }
-#pragma unroll
-    for (int i = 0; i < NBC; ++i) {
-      float4 v = *reinterpret_cast<const float4*>(raw + Cfg::A_BYTES + b_off[i]);
-      *reinterpret_cast<float4*>(lo + Cfg::A_BYTES + b_off[i]) = make_float4(lo_of(v.x), lo_of(v.y), lo_of(v.z), lo_of(v.w));
-    }
-  };
-
-  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MCONTIG ? 1u : 0u) << 15) | ((B_KCONTIG ? 0u : 1u) << 16) |
-                         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
-#pragma unroll
-  for (int d = 0; d < D; ++d) issue_tile(d);
-  for (int kt = 0; kt < ktiles; ++kt) {
-    if (kt >= 2 && !*failed) {
-      // MMAs of tile kt - 2 read ring stage (kt + D) % S and low-part buffer kt % 2
-      if (!mbar_wait(smem_u32(&bars[(kt - 2) % S]), (uint32_t)(((kt - 2) / S) & 1))) *failed = 1;
-    }
-    issue_tile(kt + D);
-    asm volatile("cp.async.wait_group %0;" ::"n"(D) : "memory");        // this thread's chunks of tile kt have landed
-    if (!(p.debug_skip & 4)) transform(kt);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t raw = smem_u32(smem + (kt % S) * Cfg::RAW_BYTES);
-      const uint32_t lo = smem_u32(lo_base + (kt & 1) * Cfg::RAW_BYTES);
-#pragma unroll
-      for (int kk = 0; kk < TBK / 8; ++kk) {
-        // one k-step = 8 values: 32 bytes inside a K-major swizzle row, or two 4-row atoms of an MN-major tile
-        const uint32_t a_adv = A_MCONTIG ? (uint32_t)(kk * (TBM / 32) * 1024) : (uint32_t)(kk * 32);
-        const uint32_t b_adv = B_KCONTIG ? (uint32_t)(kk * 32) : (uint32_t)(kk * (BN / 32) * 1024);
-        const uint64_t da = A_MCONTIG ? umma_desc_mn(raw + a_adv, TBM / 32) : umma_desc(raw + a_adv);
-        const uint64_t dal = A_MCONTIG ? umma_desc_mn(lo + a_adv, TBM / 32) : umma_desc(lo + a_adv);
-        const uint64_t db = B_KCONTIG ? umma_desc(raw + Cfg::A_BYTES + b_adv) : umma_desc_mn(raw + Cfg::A_BYTES + b_adv, BN / 32);
-        const uint64_t dbl = B_KCONTIG ? umma_desc(lo + Cfg::A_BYTES + b_adv) : umma_desc_mn(lo + Cfg::A_BYTES + b_adv, BN / 32);
-        if (!(p.debug_skip & 1)) {
-          umma_tf32(tmem, da, db, idesc, (kt | kk) != 0);
-          umma_tf32(tmem, da, dbl, idesc, 1);
-          umma_tf32(tmem, dal, db, idesc, 1);
-        }
-      }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[kt % S]))
-                   : "memory");
-    }
-  }
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
-  bool ok = !*failed;
-  if (ok && ktiles > 0) {
-    const int last = ktiles - 1;
-    ok = mbar_wait(smem_u32(&bars[last % S]), (uint32_t)((last / S) & 1));
-  }
-  ok = __syncthreads_and(ok) && !*failed;
-  if (!ok && tid == 0) atomicExch(error_flag, 1);
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-
-  // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 and a (BN / 2)-column half -------------------
-  if (ok) {
-    const int m = m0 + 32 * (warp & 3) + lane;
-#pragma unroll
-    for (int part = 0; part < BN / 64; ++part) {
-      const int col0 = (warp >> 2) * (BN / 2) + part * 32;
-      uint32_t v[32];
-      if (ktiles > 0) {
-        const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)col0;
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
-            "%24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-            : "r"(taddr)
-            : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = 0u;
-      }
-      const int nb = n0 + col0;
-      if (m < p.M && nb < p.N) {
-        float* out;
-        bool contiguous;
-        if (p.split_k > 1) {
-          out = partial + ((long long)sp * p.groups + g) * (long long)p.M * p.N + (long long)m * p.N + nb;
-          contiguous = (p.N & 3) == 0;
-        } else {
-          out = C + c_grp[g] + c_row[m] + c_col[nb];
-          contiguous = p.c_vec != 0;
-        }
-        if (contiguous && nb + 32 <= p.N && (((uintptr_t)out) & 15) == 0) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<float4*>(out + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                              __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-        } else if (p.split_k > 1) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (nb + j < p.N) out[j] = __uint_as_float(v[j]);
-        } else {
-          float* row = C + c_grp[g] + c_row[m];
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (nb + j < p.N) row[c_col[nb + j]] = __uint_as_float(v[j]);
-        }
-      }
-    }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 0) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
-  }
-}
-
-
 // ---------------------------------------------------------------------------
 // Tensor-core path, warp-specialised (used for every contraction whose operands gather in uniform 16-byte
 // chunks). Cycle counters in the roles of earlier versions showed that a handful of warps each walking a long
@@ -899,13 +610,93 @@ struct WsCfg {
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
   static constexpr int A_CHUNKS = TBM * TBK / 4, B_CHUNKS = BN_ * TBK / 4;
 };
-constexpr int WS_GATHER = 512, WS_LOW = 256, WS_THREADS = WS_GATHER + WS_LOW + 32;
+// role sizes: chunk gather 512 + 256 low-part threads, segment gather 256 + 512; one more warp issues the MMAs
+constexpr int WS_THREADS = 768 + 32;
+
+// One lane of a converged warp. The MMA warps run their loops with all 32 lanes (so that descriptor arithmetic
+// stays warp-uniform) and only the elected lane issues tcgen05.mma / tcgen05.commit: issued from a loop that a
+// single thread runs alone, the same instruction stream feeds the tensor core at two thirds of the rate.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <int BN, bool A_MCONTIG, bool B_KCONTIG, bool MASK>
+// Accumulator read-back shared by the tensor-core kernels: eight warps; warp `ew` reads TMEM lanes 32 * (ew & 3) ..
+// (row m0 + lane of that quadrant) and the column half ew >> 2, waits (bounded) for the MMAs of the last k-tile
+// (barrier `last_bar`, phase `last_parity`), and stores to C or to the split-K partial buffer.
+template <int BN>
+__device__ __forceinline__ void store_accumulator(uint32_t tmem, int warp, int lane, int m0, int n0, int g, int sp, int ktiles,
+                                                  const IGemmLaunch& p, float* __restrict__ C, float* __restrict__ partial,
+                                                  const long long* __restrict__ c_row, const long long* __restrict__ c_col,
+                                                  const long long* __restrict__ c_grp, volatile int* failed,
+                                                  uint32_t last_bar, uint32_t last_parity) {
+  bool ok = !*failed;
+  if (ok && ktiles > 0) {
+    ok = mbar_wait(last_bar, last_parity);
+    if (!ok) *failed = 1;
+  }
+  ok = __all_sync(0xFFFFFFFFu, ok);
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (ok) {
+    const int m = m0 + 32 * (warp & 3) + lane;
+#pragma unroll
+    for (int part = 0; part < BN / 64; ++part) {
+      const int col0 = (warp >> 2) * (BN / 2) + part * 32;
+      uint32_t v[32];
+      if (ktiles > 0) {
+        const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)col0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+            "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      } else {
+#pragma unroll
+        for (int q = 0; q < 32; ++q) v[q] = 0u;
+      }
+      const int nb = n0 + col0;
+      if (m < p.M && nb < p.N) {
+        float* out;
+        bool contiguous;
+        if (p.split_k > 1) {
+          out = partial + ((long long)sp * p.groups + g) * (long long)p.M * p.N + (long long)m * p.N + nb;
+          contiguous = (p.N & 3) == 0;
+        } else {
+          out = C + c_grp[g] + c_row[m] + c_col[nb];
+          contiguous = p.c_vec != 0;
+        }
+        if (contiguous && nb + 32 <= p.N && (((uintptr_t)out) & 15) == 0) {
+#pragma unroll
+          for (int q = 0; q < 32; q += 4)
+            *reinterpret_cast<float4*>(out + q) = make_float4(__uint_as_float(v[q]), __uint_as_float(v[q + 1]),
+                                                              __uint_as_float(v[q + 2]), __uint_as_float(v[q + 3]));
+        } else if (p.split_k > 1) {
+#pragma unroll
+          for (int q = 0; q < 32; ++q)
+            if (nb + q < p.N) out[q] = __uint_as_float(v[q]);
+        } else {
+          float* row = C + c_grp[g] + c_row[m];
+#pragma unroll
+          for (int q = 0; q < 32; ++q)
+            if (nb + q < p.N) row[c_col[nb + q]] = __uint_as_float(v[q]);
+        }
+      }
+    }
+  }
+}
+
+template <int BN, bool A_MCONTIG, bool B_KCONTIG, bool MASK, bool SEG>
 __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
     const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, const RowEnt* __restrict__ a_row,
     const ColEnt* __restrict__ a_col, const long long* __restrict__ b_row, const long long* __restrict__ b_col,
@@ -914,6 +705,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
     int* __restrict__ error_flag, IGemmLaunch p) {
   using Cfg = WsCfg<BN>;
   constexpr int S = Cfg::STAGES;
+  constexpr int WS_GATHER = SEG ? 256 : 512, WS_LOW = 768 - WS_GATHER;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* landed = (uint64_t*)(smem + S * Cfg::STAGE_BYTES);
@@ -962,7 +754,96 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
     k = idx / BMC; row = (idx % BMC) * 4; return sw128_mn(idx % BMC, k, BN / 32);
   };
 
-  if (tid < WS_GATHER) {
+  if (SEG && tid < WS_GATHER) {
+    // ------------------------------ gather by 128-byte rows --------------------------------------------------
+    // The host sets IGemmLaunch::seg when every aligned run of 32 indices along an operand's contiguous
+    // dimension is 32 consecutive floats sharing one window position. A row of the swizzled tile (K-major:
+    // one m or n with 32 k; MN-major: one k with 32 m or n) is then one 128-byte line of memory with one
+    // address and one padding mask. Warps 0-3 own 32 rows of the A tile each, warps 4-7 own BN / 4 rows of
+    // the B tile each: lane l works out address and mask of row l, then the warp copies four rows per
+    // instruction, eight lanes per row, so every cp.async instruction touches four whole lines.
+    const int a_sh = (int)p.a_sh, a_sw = (int)p.a_sw;
+    const bool is_a = warp < 4;
+    constexpr int B_ROWS = BN / 4;                   // rows per B warp
+    const int rows = is_a ? 32 : B_ROWS;
+    const int u = is_a ? warp * 32 + lane : (warp - 4) * B_ROWS + (lane % B_ROWS);   // tile row owned by this lane
+    int k_local = 0;                                 // MN-major rows sit at their own k inside the tile
+    uint32_t x_off;                                  // byte offset of the row in the stage, swizzle key folded in
+    int base_off = -1, h0 = 0, w0 = 0;               // m- or n-dependent part of the address (-1: out of range)
+    const float* src_base;
+    if (is_a) {
+      src_base = A + a_grp[g];
+      int m;
+      if (A_MCONTIG) { k_local = u >> 2; const int mg = u & 3; m = m0 + mg * 32;
+        x_off = (uint32_t)((((k_local >> 2) * (TBM / 32) + mg) << 9) + ((k_local & 3) << 7) + ((k_local & 3) << 5));
+      } else { m = m0 + u; x_off = (uint32_t)((u >> 3) * 1024 + (u & 7) * 128 + ((u & 7) << 4)); }
+      if (m < p.M) { const RowEnt r = a_row[m]; base_off = (int)r.off; h0 = r.h0; w0 = r.w0; }
+    } else {
+      src_base = B + b_grp[g];
+      int n;
+      if (B_KCONTIG) { n = n0 + u; x_off = (uint32_t)((u >> 3) * 1024 + (u & 7) * 128 + ((u & 7) << 4)); }
+      else { k_local = u / (BN / 32); const int ng = u % (BN / 32); n = n0 + ng * 32;
+        x_off = (uint32_t)((((k_local >> 2) * (BN / 32) + ng) << 9) + ((k_local & 3) << 7) + ((k_local & 3) << 5)); }
+      if (n < p.N) base_off = (int)b_col[n];
+      x_off += Cfg::A_BYTES;
+    }
+    // destination of this lane's chunk in the q-th group of four rows
+    const int cl = lane & 7;
+    uint32_t dst[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) dst[q] = __shfl_sync(0xFFFFFFFFu, x_off, (4 * q + (lane >> 3)) % rows) ^ (uint32_t)(cl << 4);
+    src_base += 4 * cl;
+    struct Ent { int off, dh, dw; };
+    // k-dependent table entry of tile j for this lane's row; fetched two tiles ahead into alternating registers
+    auto fetch = [&](int j, Ent& e) {
+      const int k = kbeg + j * TBK + k_local;
+      e.off = -1; e.dh = 0; e.dw = 0;
+      if (j < ktiles && k < kend) {
+        if (is_a) { const ColEnt c = a_col[k]; e.off = (int)c.off; e.dh = c.dh; e.dw = c.dw; }
+        else e.off = (int)b_row[k];
+      }
+    };
+    auto tile = [&](int j, const Ent& e) -> bool {
+      const int s = j % S;
+      bool valid = base_off >= 0 && e.off >= 0;
+      int o = base_off + e.off;
+      if (MASK && is_a) {
+        int ih = h0 + e.dh, iw = w0 + e.dw;
+        valid = valid && ih >= 0 && iw >= 0 && ih < p.Hd && iw < p.Wd;
+        if (p.ldh != 1) { valid = valid && (ih % p.ldh == 0); ih /= p.ldh; }
+        if (p.ldw != 1) { valid = valid && (iw % p.ldw == 0); iw /= p.ldw; }
+        o += ih * a_sh + iw * a_sw;
+      }
+      if (!valid) o = -1;
+      if (j >= S) {
+        // the MMAs of tile j - S were the last readers of this stage
+        if (*failed || !mbar_wait(smem_u32(&empty[s]), (uint32_t)((j / S - 1) & 1))) { *failed = 1; return false; }
+      }
+      const uint32_t x = smem_u32(smem + s * Cfg::STAGE_BYTES);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (4 * q < rows) {
+          const int oq = __shfl_sync(0xFFFFFFFFu, o, 4 * q + (lane >> 3));
+          cp_async16(x + dst[q], oq >= 0 ? src_base + oq : src_base, oq >= 0);
+        }
+      }
+      // this thread's arrival on `landed` fires when its copies above have completed
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&landed[s])) : "memory");
+      return true;
+    };
+    Ent e0, e1;
+    fetch(0, e0);
+    fetch(1, e1);
+    for (int j = 0; j < ktiles; j += 2) {
+      if (!tile(j, e0)) break;
+      fetch(j + 2, e0);
+      if (j + 1 < ktiles) {
+        if (!tile(j + 1, e1)) break;
+        fetch(j + 3, e1);
+      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  } else if (!SEG && tid < WS_GATHER) {
     // ------------------------------ gather -----------------------------------------------------------------
     const float* Ag = A + a_grp[g];
     const float* Bg = B + b_grp[g];
@@ -987,7 +868,6 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
       const int n = n0 + row;
       b_no[q] = n < p.N ? (int)b_col[n] : -1;
     }
-    long long dbg_wait = 0, dbg_t0 = clock64();
     for (int j = 0; j < ktiles; ++j) {
       const int s = j % S;
       const int k0 = kbeg + j * TBK;
@@ -1008,9 +888,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
       }
       if (j >= S) {
         // the MMAs of tile j - S were the last readers of this stage
-        long long w0 = clock64();
         if (*failed || !mbar_wait(smem_u32(&empty[s]), (uint32_t)((j / S - 1) & 1))) { *failed = 1; break; }
-        dbg_wait += clock64() - w0;
       }
       const uint32_t a_raw = smem_u32(smem + s * Cfg::STAGE_BYTES), b_raw = a_raw + Cfg::A_BYTES;
 #pragma unroll
@@ -1035,43 +913,44 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
       asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&landed[s])) : "memory");
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
-    if ((p.debug_skip & 8) && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
-      printf("gather : total %lld cycles, waiting for empty %lld, k-tiles %d\n", clock64() - dbg_t0, dbg_wait, ktiles);
   } else if (tid < WS_GATHER + WS_LOW) {
     // ------------------------------ low part ----------------------------------------------------------------
     const int t = tid - WS_GATHER;
-    auto lo4 = [](const float4& v) -> float4 {
-      auto lo1 = [](float x) -> float {
-        const uint32_t u = __float_as_uint(x);
-        if ((u & 0x7F800000u) == 0x7F800000u) return 0.f;        // inf / nan stay in the high operand only
-        // the tensor core truncates the raw word to its TF32 bits; the remainder is exact in fp32 and is
-        // rounded to nearest on 10 mantissa bits here, so the second truncation in hardware is a no-op
-        const float l = x - __uint_as_float(u & 0xFFFFE000u);
-        return __uint_as_float((__float_as_uint(l) + 0x1000u) & 0xFFFFE000u);
-      };
-      return make_float4(lo1(v.x), lo1(v.y), lo1(v.z), lo1(v.w));
+    // lo = x - (TF32 bits of x): exact in fp32. Adding half a TF32 unit to its bit pattern makes the tensor
+    // core's truncation of the stored word a round-to-nearest. An infinite x would give inf - inf = NaN; those
+    // are rare, so the fast pass only tracks max|x| and a tile that saw an infinity is redone element-wise.
+    auto lo1 = [](float x) -> float {
+      const float l = x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+      return __uint_as_float(__float_as_uint(l) + 0x1000u);
     };
-    long long dbg_wait = 0, dbg_t0 = clock64();
+    auto lo1_safe = [&](float x) -> float { return fabsf(x) == INFINITY ? 0.f : lo1(x); };
     for (int j = 0; j < ktiles; ++j) {
       const int s = j % S;
-      long long w0 = clock64();
       if (*failed || !mbar_wait(smem_u32(&landed[s]), (uint32_t)((j / S) & 1))) { *failed = 1; break; }
-      dbg_wait += clock64() - w0;
       uint8_t* raw = smem + s * Cfg::STAGE_BYTES;                 // raw A, raw B contiguous; low parts follow
       uint8_t* low = raw + Cfg::A_BYTES + Cfg::B_BYTES;
       // the swizzle only permutes 16-byte chunks inside a tile, so the low-part pass can walk the bytes linearly
+      constexpr int NQ = (Cfg::A_CHUNKS + Cfg::B_CHUNKS) / WS_LOW;
+      float mx = 0.f;
 #pragma unroll
-      for (int q = 0; q < (Cfg::A_CHUNKS + Cfg::B_CHUNKS) / WS_LOW; ++q) {
+      for (int q = 0; q < NQ; ++q) {
         const uint32_t off = (uint32_t)(t + q * WS_LOW) * 16u;
-        *reinterpret_cast<float4*>(low + off) = lo4(*reinterpret_cast<const float4*>(raw + off));
+        const float4 v = *reinterpret_cast<const float4*>(raw + off);
+        mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        *reinterpret_cast<float4*>(low + off) = make_float4(lo1(v.x), lo1(v.y), lo1(v.z), lo1(v.w));
+      }
+      if (mx == INFINITY) {
+        for (int q = 0; q < NQ; ++q) {
+          const uint32_t off = (uint32_t)(t + q * WS_LOW) * 16u;
+          const float4 v = *reinterpret_cast<const float4*>(raw + off);
+          *reinterpret_cast<float4*>(low + off) = make_float4(lo1_safe(v.x), lo1_safe(v.y), lo1_safe(v.z), lo1_safe(v.w));
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(smem_u32(&ready[s]));
     }
-    if ((p.debug_skip & 8) && t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
-      printf("lowpart: total %lld cycles, waiting for landed %lld\n", clock64() - dbg_t0, dbg_wait);
-  } else if (lane == 0) {
-    // ------------------------------ MMA issuer --------------------------------------------------------------
+  } else {
+    // ------------------------------ MMA issuer (whole warp, one elected lane issues) --------------------------
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MCONTIG ? 1u : 0u) << 15) |
                            ((B_KCONTIG ? 0u : 1u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
     // descriptors of stage 0; another stage adds STAGE_BYTES / 16 to the address field, a k-step adds a constant
@@ -1081,96 +960,335 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
     constexpr uint64_t LOW = (uint64_t)((Cfg::A_BYTES + Cfg::B_BYTES) >> 4);
     constexpr uint64_t A_STEP = (uint64_t)((A_MCONTIG ? (TBM / 32) * 1024 : 32) >> 4);
     constexpr uint64_t B_STEP = (uint64_t)((B_KCONTIG ? 32 : (BN / 32) * 1024) >> 4);
-    long long dbg_wait = 0, dbg_t0 = clock64();
     for (int j = 0; j < ktiles; ++j) {
       const int s = j % S;
-      long long w0 = clock64();
-      if (*failed || !mbar_wait(smem_u32(&ready[s]), (uint32_t)((j / S) & 1))) { *failed = 1; break; }
-      dbg_wait += clock64() - w0;
+      const bool ok = !*failed && mbar_wait(smem_u32(&ready[s]), (uint32_t)((j / S) & 1));
+      if (!__all_sync(0xFFFFFFFFu, ok)) { *failed = 1; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint64_t st = (uint64_t)((s * Cfg::STAGE_BYTES) >> 4);
+      if (elect_one()) {
 #pragma unroll
-      for (int kk = 0; kk < TBK / 8; ++kk) {
-        const uint64_t da = d_a + st + kk * A_STEP, db = d_b + st + kk * B_STEP;
-        umma_tf32(tmem, da, db, idesc, (j | kk) != 0);
-        umma_tf32(tmem, da, db + LOW, idesc, 1);
-        umma_tf32(tmem, da + LOW, db, idesc, 1);
+        for (int kk = 0; kk < TBK / 8; ++kk) {
+          const uint64_t da = d_a + st + kk * A_STEP, db = d_b + st + kk * B_STEP;
+          umma_tf32(tmem, da, db, idesc, (j | kk) != 0);
+          umma_tf32(tmem, da, db + LOW, idesc, 1);
+          umma_tf32(tmem, da + LOW, db, idesc, 1);
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty[s]))
+                     : "memory");
       }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty[s]))
-                   : "memory");
+      __syncwarp();
     }
-    if ((p.debug_skip & 8) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
-      printf("mma    : total %lld cycles, waiting for ready %lld\n", clock64() - dbg_t0, dbg_wait);
   }
 
-  if (warp < 8) {
-    // ------------------------------ epilogue ---------------------------------------------------------------
-    bool ok = !*failed;
-    if (ok && ktiles > 0) {
-      const int last = ktiles - 1;
-      ok = mbar_wait(smem_u32(&empty[last % S]), (uint32_t)((last / S) & 1));
-      if (!ok) *failed = 1;
-    }
-    ok = __all_sync(0xFFFFFFFFu, ok);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-      const int m = m0 + 32 * (warp & 3) + lane;
-#pragma unroll
-      for (int part = 0; part < BN / 64; ++part) {
-        const int col0 = (warp >> 2) * (BN / 2) + part * 32;
-        uint32_t v[32];
-        if (ktiles > 0) {
-          const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)col0;
-          asm volatile(
-              "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-              "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
-              "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-              : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-                "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-                "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-              : "r"(taddr)
-              : "memory");
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        } else {
-#pragma unroll
-          for (int q = 0; q < 32; ++q) v[q] = 0u;
-        }
-        const int nb = n0 + col0;
-        if (m < p.M && nb < p.N) {
-          float* out;
-          bool contiguous;
-          if (p.split_k > 1) {
-            out = partial + ((long long)sp * p.groups + g) * (long long)p.M * p.N + (long long)m * p.N + nb;
-            contiguous = (p.N & 3) == 0;
-          } else {
-            out = C + c_grp[g] + c_row[m] + c_col[nb];
-            contiguous = p.c_vec != 0;
-          }
-          if (contiguous && nb + 32 <= p.N && (((uintptr_t)out) & 15) == 0) {
-#pragma unroll
-            for (int q = 0; q < 32; q += 4)
-              *reinterpret_cast<float4*>(out + q) = make_float4(__uint_as_float(v[q]), __uint_as_float(v[q + 1]),
-                                                                __uint_as_float(v[q + 2]), __uint_as_float(v[q + 3]));
-          } else if (p.split_k > 1) {
-#pragma unroll
-            for (int q = 0; q < 32; ++q)
-              if (nb + q < p.N) out[q] = __uint_as_float(v[q]);
-          } else {
-            float* row = C + c_grp[g] + c_row[m];
-#pragma unroll
-            for (int q = 0; q < 32; ++q)
-              if (nb + q < p.N) row[c_col[nb + q]] = __uint_as_float(v[q]);
-          }
-        }
-      }
-    }
-  }
+  if (warp < 8)
+    store_accumulator<BN>(tmem, warp, lane, m0, n0, g, sp, ktiles, p, C, partial, c_row, c_col, c_grp, failed,
+                          smem_u32(&empty[(ktiles > 0 ? ktiles - 1 : 0) % S]), (uint32_t)(((ktiles > 0 ? ktiles - 1 : 0) / S) & 1));
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (tid == 0 && *failed) atomicExch(error_flag, 1);
   if (warp == MMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Tensor-core path with the A operand in tensor memory (used when both operands gather by whole 128-byte rows,
+// IGemmLaunch::seg). Timelines of the kernel above showed it bound by shared-memory traffic: per 32-deep k-tile
+// the MMA unit read 72 KB of operands (A three times, B three times) next to 72 KB of copies and low-part
+// passes. Here only B lives in shared memory as an MMA operand. A goes global -> shared (raw, cp.async) ->
+// registers of one thread per row -> tensor memory, as a high tile (the raw words: the tensor core reads their
+// TF32 bits) and a low tile (x - tf32(x)), and tcgen05.mma takes it from there; per k-tile the shared memory
+// moves 16 KB + 16 KB for A and (8 + 16 + 24) KB for a 64-wide B instead of 144 KB.
+//   warps 0-3   gather A: lane l owns row l of the warp's 32 tile rows (address + padding mask once per row and
+//               k-tile), copies go out four rows per instruction, eight lanes per row (128-byte cp.async.bulk
+//               copies per row were tried and ran 1.6 times slower)
+//   warps 4-7   gather B the same way
+//   warps 8-15  two groups of four warps alternate k-tiles: thread = one row m of the tile; reads its 32 values
+//               (K-major rows: eight 16-byte reads from the swizzled row; MN-major: 32 words, one per k),
+//               tcgen05.st of the high and the low words into the stage's 64 tensor-memory columns
+//   warps 16-23 low part of the B tile in shared memory
+//   warp 24     one thread issues the 12 MMAs of a k-tile (A hi x B raw, A hi x B lo, A lo x B raw per k-step)
+//               and commits them to the stage's `empty` barrier
+// Tensor memory: all 512 columns; accumulator in [0, BN), A ring from column 128 (64 columns per stage).
+// Every wait is bounded as in the kernels above.
+template <int BN_>
+struct TaCfg {
+  static constexpr int BN = BN_;
+  static constexpr int STAGES = BN_ == 64 ? 6 : 4;
+  static constexpr int A_BYTES = TBM * TBK * 4, B_BYTES = BN_ * TBK * 4;
+  static constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;            // raw A, raw B, low B
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int B_CHUNKS = BN_ * TBK / 4;
+  static constexpr int A_COL0 = 128;                                   // 64 columns per stage: 128 + 6 * 64 = 512
+};
+constexpr int TA_THREADS = 800;
+
+__device__ __forceinline__ void umma_tf32_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, "
+      "%25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+
+template <int BN, bool A_MCONTIG, bool B_KCONTIG, bool MASK>
+__global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
+    const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, const RowEnt* __restrict__ a_row,
+    const ColEnt* __restrict__ a_col, const long long* __restrict__ b_row, const long long* __restrict__ b_col,
+    const long long* __restrict__ c_row, const long long* __restrict__ c_col, const long long* __restrict__ a_grp,
+    const long long* __restrict__ b_grp, const long long* __restrict__ c_grp, float* __restrict__ partial,
+    int* __restrict__ error_flag, IGemmLaunch p) {
+  using Cfg = TaCfg<BN>;
+  constexpr int S = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* landed_a = (uint64_t*)(smem + S * Cfg::STAGE_BYTES);
+  uint64_t* landed_b = landed_a + S;
+  uint64_t* a_ready = landed_b + S;
+  uint64_t* b_ready = a_ready + S;
+  uint64_t* empty = b_ready + S;
+  uint32_t* tmem_slot = (uint32_t*)(empty + S);
+  volatile int* failed = (volatile int*)(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = blockIdx.x * TBM, n0 = blockIdx.y * BN;
+  const int g = blockIdx.z / p.split_k, sp = blockIdx.z % p.split_k;
+  const int kchunk = ((p.K + p.split_k - 1) / p.split_k + TBK - 1) / TBK * TBK;
+  const int kbeg = sp * kchunk, kend = min(p.K, kbeg + kchunk);
+  const int ktiles = kend > kbeg ? (kend - kbeg + TBK - 1) / TBK : 0;
+  constexpr int MMA_WARP = 24;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&landed_a[s]), 128);
+      mbar_init(smem_u32(&landed_b[s]), 128);
+      mbar_init(smem_u32(&a_ready[s]), 128);
+      mbar_init(smem_u32(&b_ready[s]), 256);
+      mbar_init(smem_u32(&empty[s]), 1);
+    }
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == MMA_WARP) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  // lo = x - (TF32 bits of x), exact in fp32; adding half a TF32 unit to its bit pattern turns the tensor core's
+  // truncation of the stored word into round-to-nearest. inf - inf would be NaN: callers track max|x| and redo
+  // a row or tile that saw an infinity with lo1_safe.
+  auto lo1 = [](float x) -> float {
+    const float l = x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+    return __uint_as_float(__float_as_uint(l) + 0x1000u);
+  };
+  auto lo1_safe = [&](float x) -> float { return fabsf(x) == INFINITY ? 0.f : lo1(x); };
+
+  if (warp < 8) {
+    // ------------------------------ gather -----------------------------------------------------------------
+    const int a_sh = (int)p.a_sh, a_sw = (int)p.a_sw;
+    const bool is_a = warp < 4;
+    constexpr int B_ROWS = BN / 4;                   // rows per B warp
+    const int rows = is_a ? 32 : B_ROWS;
+    const int u = is_a ? warp * 32 + lane : (warp - 4) * B_ROWS + (lane % B_ROWS);   // tile row owned by this lane
+    int k_local = 0;                                 // MN-major rows sit at their own k inside the tile
+    uint32_t x_off;                                  // byte offset of the row in the stage (swizzle key folded in)
+    int base_off = -1, h0 = 0, w0 = 0;               // m- or n-dependent part of the address (-1: out of range)
+    const float* src_base;
+    if (is_a) {
+      src_base = A + a_grp[g];
+      int m;
+      // the raw A tile is only read by the converter threads: MN-major rows are stored plainly as [k][128 m],
+      // K-major rows as [m][32 k] with the 16-byte chunks XOR-ed by the row number (conflict-free row reads)
+      if (A_MCONTIG) { k_local = u >> 2; const int mg = u & 3; m = m0 + mg * 32; x_off = (uint32_t)(k_local * 512 + mg * 128); }
+      else { m = m0 + u; x_off = (uint32_t)(u * 128 + ((u & 7) << 4)); }
+      if (m < p.M) { const RowEnt r = a_row[m]; base_off = (int)r.off; h0 = r.h0; w0 = r.w0; }
+    } else {
+      src_base = B + b_grp[g];
+      int n;
+      if (B_KCONTIG) { n = n0 + u; x_off = (uint32_t)((u >> 3) * 1024 + (u & 7) * 128 + ((u & 7) << 4)); }
+      else { k_local = u / (BN / 32); const int ng = u % (BN / 32); n = n0 + ng * 32;
+        x_off = (uint32_t)((((k_local >> 2) * (BN / 32) + ng) << 9) + ((k_local & 3) << 7) + ((k_local & 3) << 5)); }
+      if (n < p.N) base_off = (int)b_col[n];
+      x_off += Cfg::A_BYTES;
+    }
+    const int cl = lane & 7;
+    uint32_t dst[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) dst[q] = __shfl_sync(0xFFFFFFFFu, x_off, (4 * q + (lane >> 3)) % rows) ^ (uint32_t)(cl << 4);
+    src_base += 4 * cl;
+    uint64_t* landed = is_a ? landed_a : landed_b;
+    struct Ent { int off, dh, dw; };
+    // k-dependent table entry of tile j for this lane's row, fetched two tiles ahead into alternating registers
+    auto fetch = [&](int j, Ent& e) {
+      const int k = kbeg + j * TBK + k_local;
+      e.off = -1; e.dh = 0; e.dw = 0;
+      if (j < ktiles && k < kend) {
+        if (is_a) { const ColEnt c = a_col[k]; e.off = (int)c.off; e.dh = c.dh; e.dw = c.dw; }
+        else e.off = (int)b_row[k];
+      }
+    };
+    auto tile = [&](int j, const Ent& e) -> bool {
+      const int s = j % S;
+      bool valid = base_off >= 0 && e.off >= 0;
+      int o = base_off + e.off;
+      if (MASK && is_a) {
+        int ih = h0 + e.dh, iw = w0 + e.dw;
+        valid = valid && ih >= 0 && iw >= 0 && ih < p.Hd && iw < p.Wd;
+        if (p.ldh != 1) { valid = valid && (ih % p.ldh == 0); ih /= p.ldh; }
+        if (p.ldw != 1) { valid = valid && (iw % p.ldw == 0); iw /= p.ldw; }
+        o += ih * a_sh + iw * a_sw;
+      }
+      if (!valid) o = -1;
+      if (j >= S) {
+        // the MMAs of tile j - S were the last readers of this stage (shared memory and tensor memory)
+        if (*failed || !mbar_wait(smem_u32(&empty[s]), (uint32_t)((j / S - 1) & 1))) { *failed = 1; return false; }
+      }
+      const uint32_t x = smem_u32(smem + s * Cfg::STAGE_BYTES);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (4 * q < rows) {
+          const int oq = __shfl_sync(0xFFFFFFFFu, o, 4 * q + (lane >> 3));
+          cp_async16(x + dst[q], oq >= 0 ? src_base + oq : src_base, oq >= 0);
+        }
+      }
+      // this thread's arrival on the barrier fires when its copies above have completed
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&landed[s])) : "memory");
+      return true;
+    };
+    Ent e0, e1;
+    fetch(0, e0);
+    fetch(1, e1);
+    for (int j = 0; j < ktiles; j += 2) {
+      if (!tile(j, e0)) break;
+      fetch(j + 2, e0);
+      if (j + 1 < ktiles) {
+        if (!tile(j + 1, e1)) break;
+        fetch(j + 3, e1);
+      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  } else if (warp < 16) {
+    // ------------------------------ A: shared memory -> registers -> tensor memory ---------------------------
+    const int grp = (warp - 8) >> 2, quad = warp & 3;
+    const int row = 32 * quad + lane;
+    for (int j = grp; j < ktiles; j += 2) {
+      const int s = j % S;
+      if (*failed || !mbar_wait(smem_u32(&landed_a[s]), (uint32_t)((j / S) & 1))) { *failed = 1; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint8_t* raw = smem + s * Cfg::STAGE_BYTES;
+      uint32_t v[32];
+      if (A_MCONTIG) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v[k] = *reinterpret_cast<const uint32_t*>(raw + k * 512 + row * 4);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 t = *reinterpret_cast<const uint4*>(raw + row * 128 + ((c ^ (row & 7)) << 4));
+          v[4 * c] = t.x; v[4 * c + 1] = t.y; v[4 * c + 2] = t.z; v[4 * c + 3] = t.w;
+        }
+      }
+      const uint32_t taddr = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(Cfg::A_COL0 + s * 64);
+      tmem_store32(taddr, v);
+      float mx = 0.f;
+#pragma unroll
+      for (int k = 0; k < 32; ++k) mx = fmaxf(mx, fabsf(__uint_as_float(v[k])));
+      if (mx == INFINITY) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(lo1_safe(__uint_as_float(v[k])));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(lo1(__uint_as_float(v[k])));
+      }
+      tmem_store32(taddr + 32, v);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(smem_u32(&a_ready[s]));
+    }
+  } else if (warp < 24) {
+    // ------------------------------ low part of B ------------------------------------------------------------
+    const int t = tid - 512;
+    for (int j = 0; j < ktiles; ++j) {
+      const int s = j % S;
+      if (*failed || !mbar_wait(smem_u32(&landed_b[s]), (uint32_t)((j / S) & 1))) { *failed = 1; break; }
+      uint8_t* raw = smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES;
+      uint8_t* low = raw + Cfg::B_BYTES;
+      constexpr int NQ = Cfg::B_CHUNKS / 256;
+      float mx = 0.f;
+      float4 v[NQ];
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+        v[q] = *reinterpret_cast<const float4*>(raw + (uint32_t)(t + q * 256) * 16u);
+        mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v[q].x), fabsf(v[q].y))), fmaxf(fabsf(v[q].z), fabsf(v[q].w)));
+      }
+      const bool special = mx == INFINITY;
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+        float4 l;
+        if (special) l = make_float4(lo1_safe(v[q].x), lo1_safe(v[q].y), lo1_safe(v[q].z), lo1_safe(v[q].w));
+        else l = make_float4(lo1(v[q].x), lo1(v[q].y), lo1(v[q].z), lo1(v[q].w));
+        *reinterpret_cast<float4*>(low + (uint32_t)(t + q * 256) * 16u) = l;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(smem_u32(&b_ready[s]));
+    }
+  } else {
+    // ------------------------------ MMA issuer (whole warp, one elected lane issues) --------------------------
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((B_KCONTIG ? 0u : 1u) << 16) |
+                           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
+    const uint32_t base0 = smem_u32(smem) + Cfg::A_BYTES;
+    const uint64_t d_b = B_KCONTIG ? umma_desc(base0) : umma_desc_mn(base0, BN / 32);
+    constexpr uint64_t LOW = (uint64_t)(Cfg::B_BYTES >> 4);
+    constexpr uint64_t B_STEP = (uint64_t)((B_KCONTIG ? 32 : (BN / 32) * 1024) >> 4);
+    for (int j = 0; j < ktiles; ++j) {
+      const int s = j % S;
+      const uint32_t ph = (uint32_t)((j / S) & 1);
+      const bool ok = !*failed && mbar_wait(smem_u32(&a_ready[s]), ph) && mbar_wait(smem_u32(&b_ready[s]), ph);
+      if (!__all_sync(0xFFFFFFFFu, ok)) { *failed = 1; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint64_t st = (uint64_t)((s * Cfg::STAGE_BYTES) >> 4);
+      const uint32_t a_hi = tmem + (uint32_t)(Cfg::A_COL0 + s * 64);
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < TBK / 8; ++kk) {
+          const uint64_t db = d_b + st + kk * B_STEP;
+          umma_tf32_ta(tmem, a_hi + kk * 8, db, idesc, (j | kk) != 0);
+          umma_tf32_ta(tmem, a_hi + kk * 8, db + LOW, idesc, 1);
+          umma_tf32_ta(tmem, a_hi + 32 + kk * 8, db, idesc, 1);
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty[s]))
+                     : "memory");
+      }
+      __syncwarp();
+    }
+  }
+
+  if (warp >= 8 && warp < 16)
+    store_accumulator<BN>(tmem, warp - 8, lane, m0, n0, g, sp, ktiles, p, C, partial, c_row, c_col, c_grp, failed,
+                          smem_u32(&empty[(ktiles > 0 ? ktiles - 1 : 0) % S]), (uint32_t)(((ktiles > 0 ? ktiles - 1 : 0) / S) & 1));
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (tid == 0 && *failed) atomicExch(error_flag, 1);
+  if (warp == MMA_WARP) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
   }
 }
 
@@ -1199,12 +1317,16 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
       configured = true;
     }
     dim3 grid((p.M + TBM - 1) / TBM, (p.N + TBN - 1) / TBN, p.groups * p.split_k);
-    if (p.vec && !p.old_vec) {
+    if (p.vec) {
       static bool configured_w = false;
       if (!configured_w) {
-#define SETATTRW(BN_, AM, BK_, MK)                                                                             \
-  cudaFuncSetAttribute(igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                       WsCfg<BN_>::SMEM)
+#define SETATTRW(BN_, AM, BK_, MK)                                                                                    \
+  cudaFuncSetAttribute(igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                       WsCfg<BN_>::SMEM);                                                                            \
+  cudaFuncSetAttribute(igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                       WsCfg<BN_>::SMEM);                                                                            \
+  cudaFuncSetAttribute(igemm_tf32x3_ta_kernel<BN_, AM, BK_, MK>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                       TaCfg<BN_>::SMEM)
 #define SETALLW(BN_)                                                                                                  \
   SETATTRW(BN_, false, false, false); SETATTRW(BN_, false, false, true); SETATTRW(BN_, false, true, false);           \
   SETATTRW(BN_, false, true, true); SETATTRW(BN_, true, false, false); SETATTRW(BN_, true, false, true);              \
@@ -1218,9 +1340,18 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
       const bool wide = p.N >= 128 && p.wide_n;
       dim3 gridw((p.M + TBM - 1) / TBM, (p.N + (wide ? 128 : 64) - 1) / (wide ? 128 : 64), p.groups * p.split_k);
 #define LAUNCHW(BN_, AM, BK_, MK)                                                                                     \
-  igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK><<<gridw, WS_THREADS, WsCfg<BN_>::SMEM, stream>>>(                          \
-      (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,       \
-      (float*)partial, error_flag, p)
+  if (p.seg && p.tmem_a)                                                                                              \
+    igemm_tf32x3_ta_kernel<BN_, AM, BK_, MK><<<gridw, TA_THREADS, TaCfg<BN_>::SMEM, stream>>>(                        \
+        (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
+        (float*)partial, error_flag, p);                                                                              \
+  else if (p.seg)                                                                                                     \
+    igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK, true><<<gridw, WS_THREADS, WsCfg<BN_>::SMEM, stream>>>(                  \
+        (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
+        (float*)partial, error_flag, p);                                                                              \
+  else                                                                                                                \
+    igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK, false><<<gridw, WS_THREADS, WsCfg<BN_>::SMEM, stream>>>(                 \
+        (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
+        (float*)partial, error_flag, p)
 #define SWITCHW(BN_)                                   \
   switch (v) {                                         \
     case 0: LAUNCHW(BN_, false, false, false); break;  \
@@ -1235,42 +1366,6 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
       if (wide) { SWITCHW(128) } else { SWITCHW(64) }
 #undef SWITCHW
 #undef LAUNCHW
-    } else if (p.vec) {
-      static bool configured_v = false;
-      if (!configured_v) {
-#define SETATTRV(BN_, AM, BK_, MK)                                                                              \
-  cudaFuncSetAttribute(igemm_tf32x3_vec_kernel<BN_, AM, BK_, MK>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                       VecCfg<BN_>::SMEM)
-#define SETALL(BN_)                                                                                                   \
-  SETATTRV(BN_, false, false, false); SETATTRV(BN_, false, false, true); SETATTRV(BN_, false, true, false);           \
-  SETATTRV(BN_, false, true, true); SETATTRV(BN_, true, false, false); SETATTRV(BN_, true, false, true);              \
-  SETATTRV(BN_, true, true, false); SETATTRV(BN_, true, true, true)
-        SETALL(64);
-        SETALL(128);
-#undef SETALL
-#undef SETATTRV
-        configured_v = true;
-      }
-      const bool wide = p.N >= 128 && p.wide_n;
-      dim3 gridv((p.M + TBM - 1) / TBM, (p.N + (wide ? 128 : 64) - 1) / (wide ? 128 : 64), p.groups * p.split_k);
-#define LAUNCHV(BN_, AM, BK_, MK)                                                                                     \
-  igemm_tf32x3_vec_kernel<BN_, AM, BK_, MK><<<gridv, TNT, VecCfg<BN_>::SMEM, stream>>>(                               \
-      (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,       \
-      (float*)partial, error_flag, p)
-#define SWITCHV(BN_)                                   \
-  switch (v) {                                         \
-    case 0: LAUNCHV(BN_, false, false, false); break;  \
-    case 1: LAUNCHV(BN_, false, false, true); break;   \
-    case 2: LAUNCHV(BN_, false, true, false); break;   \
-    case 3: LAUNCHV(BN_, false, true, true); break;    \
-    case 4: LAUNCHV(BN_, true, false, false); break;   \
-    case 5: LAUNCHV(BN_, true, false, true); break;    \
-    case 6: LAUNCHV(BN_, true, true, false); break;    \
-    default: LAUNCHV(BN_, true, true, true); break;    \
-  }
-      if (wide) { SWITCHV(128) } else { SWITCHV(64) }
-#undef SWITCHV
-#undef LAUNCHV
     } else {
 #define LAUNCHT(AM, BK_, MK)                                                                                     \
   igemm_tf32x3_kernel<AM, BK_, MK><<<grid, TNT, TSMEM_BYTES, stream>>>((const float*)A, (const float*)B, (float*)C, \

@@ -11,10 +11,10 @@ struct IGemmLaunch {
   int a_mcontig, b_kcontig, mask;
   int tensor_cores;              // 1: tcgen05 3xTF32 kernel, 0: fp32 FMA kernel
   int vec;                       // operands can be gathered in uniform, aligned 16-byte chunks
+  int seg;                       // vec, and every aligned run of 32 along each operand's contiguous dimension is one 128-byte row
+  int tmem_a;                    // with seg: keep the A operand in tensor memory (igemm_tf32x3_ta_kernel)
   int c_vec;                     // consecutive n are consecutive, 16-byte alignable floats in C
   int wide_n;                    // use 128-wide N tiles when N >= 128
-  int old_vec;                   // use the single-role cp.async kernel instead of the warp-specialised one
-  int debug_skip;                // timing experiments only: 1 = no MMA, 2 = no gather, 4 = no low-part pass
 };
 
 // tables: a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp (device pointers).

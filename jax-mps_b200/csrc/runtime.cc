@@ -538,9 +538,9 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       // tiny products stay on the fp32 FMA kernel; everything else goes to the tensor cores (3xTF32)
       p.vec = s.ig.vec && !getenv("B200_NO_VEC_GATHER");
       p.c_vec = s.ig.c_vec;
+      p.seg = p.vec && s.ig.seg && !getenv("B200_NO_SEG_GATHER");
+      p.tmem_a = getenv("B200_NO_TMEM_A") ? 0 : 1;
       p.wide_n = getenv("B200_NARROW_TILES") ? 0 : 1;
-      p.old_vec = getenv("B200_OLD_VEC") ? 1 : 0;
-      p.debug_skip = getenv("B200_DEBUG_SKIP") ? atoi(getenv("B200_DEBUG_SKIP")) : 0;
       p.tensor_cores = c->tensor_cores && (long long)s.ig.M * s.ig.N * s.ig.K * s.ig.groups >= (1LL << 18) && s.ig.K >= 16;
       const void* tables[9];
       for (int k = 0; k < 9; k++) tables[k] = x.ptrs[s.args[3 + k]];
@@ -623,7 +623,7 @@ b200_error* run_plan(ExecCtx& x, const Plan& plan) {
           t.key = "igemm M=" + std::to_string(s.ig.M) + " N=" + std::to_string(s.ig.N) + " K=" + std::to_string(s.ig.K) +
                   " G=" + std::to_string(s.ig.groups) + " splitK=" + std::to_string(s.ig.split_k) + " a_mcontig=" +
                   std::to_string(s.ig.a_contig) + " b_kcontig=" + std::to_string(s.ig.b_contig) + " mask=" +
-                  std::to_string(s.ig.needs_mask) + " ld=" + std::to_string(s.ig.ldh) + "x" + std::to_string(s.ig.ldw) + " vec=" + std::to_string(s.ig.vec);
+                  std::to_string(s.ig.needs_mask) + " ld=" + std::to_string(s.ig.ldh) + "x" + std::to_string(s.ig.ldw) + " vec=" + std::to_string(s.ig.vec) + " seg=" + std::to_string(s.ig.seg);
           if (!(x.c->tensor_cores && (long long)s.ig.M * s.ig.N * s.ig.K * s.ig.groups >= (1LL << 18) && s.ig.K >= 16))
             t.kind = "igemm_fma";
           break;
