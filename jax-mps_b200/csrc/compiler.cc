@@ -270,12 +270,13 @@ struct Planner {
     v->type = t;
     return v;
   }
-  int add_kernel(const std::string& body_without_name) {
+  // `stem` names the kernel family in profiler listings ("fused", "reduce"); identical bodies share one kernel
+  int add_kernel(const std::string& body_without_name, const char* stem) {
     auto it = kernel_cache.find(body_without_name);
     if (it != kernel_cache.end()) return it->second;
     int id = (int)prog.kernels.size();
     KernelSource ks;
-    ks.name = "k" + std::to_string(id);
+    ks.name = std::string(stem) + "_" + std::to_string(id);
     std::string body = body_without_name;
     auto p = body.find("@NAME@");
     body.replace(p, 6, ks.name);
@@ -470,6 +471,52 @@ struct Planner {
     }
   }
 
+  // Reductions over the same index space that read common inputs (batch-norm statistics sum x / sum x^2, the
+  // two or three sums of its gradient) become one kernel with several accumulators, so the inputs are read
+  // once. Legal when neither kernel has to run after the other (checked at kernel granularity both ways).
+  void merge_sibling_reductions(BlockState& st) {
+    auto inputs_of = [&](Group* g) {
+      std::set<Value*> in;
+      for (Op* m : g->members)
+        for (Value* o : m->operands)
+          if (!(o->def && g->members.count(o->def))) in.insert(o);
+      return in;
+    };
+    std::vector<Group*> reds;
+    for (auto& g : st.groups)
+      if (g.is_reduce && g.roots.size() == 1 && !g.members.empty()) reds.push_back(&g);
+    std::sort(reds.begin(), reds.end(), [](Group* a, Group* b) { return a->max_pos < b->max_pos; });
+    for (size_t i = 0; i < reds.size(); i++) {
+      Group* a = reds[i];
+      if (a->members.empty()) continue;
+      for (size_t j = i + 1; j < reds.size(); j++) {
+        Group* b = reds[j];
+        if (b->members.empty() || b->max_pos - a->max_pos > 4096) continue;
+        Op *ra = a->roots[0], *rb = b->roots[0];
+        if (ra->operands[0]->type.dims != rb->operands[0]->type.dims) continue;
+        if (attr_i64s(ra->attr("dimensions")) != attr_i64s(rb->attr("dimensions"))) continue;
+        if (a->roots.size() + b->roots.size() > 4 || a->members.size() + b->members.size() > 96) continue;
+        auto ia = inputs_of(a), ib = inputs_of(b);
+        bool shared = false;
+        for (Value* v : ia)
+          if (ib.count(v) && v->type.numel() * 4 >= ra->operands[0]->type.numel()) { shared = true; break; }
+        if (!shared) continue;
+        if (reaches({}, {a}, b, st) || reaches({}, {b}, a, st)) continue;
+        // b joins a
+        for (Op* m : b->members) {
+          a->members.insert(m);
+          auto& gs = st.group_of[m];
+          gs.erase(std::remove(gs.begin(), gs.end(), b), gs.end());
+          if (std::find(gs.begin(), gs.end(), a) == gs.end()) gs.push_back(a);
+        }
+        for (Op* r : b->roots) a->roots.push_back(r);
+        a->max_pos = std::max(a->max_pos, b->max_pos);
+        b->members.clear();
+        b->roots.clear();
+      }
+    }
+  }
+
   // ---- kernel generation -----------------------------------------------------
   struct Launch {
     int kernel;
@@ -536,7 +583,7 @@ struct Planner {
     src << em.str();
     src << "  }\n}\n";
     Launch L;
-    L.kernel = add_kernel(src.str());
+    L.kernel = add_kernel(src.str(), "fused");
     int64_t blocks = std::max<int64_t>(1, (n + (int64_t)kThreads * kEPT - 1) / ((int64_t)kThreads * kEPT));
     L.grid[0] = (unsigned)blocks; L.grid[1] = L.grid[2] = 1;
     L.block[0] = kThreads; L.block[1] = L.block[2] = 1;
@@ -548,17 +595,29 @@ struct Planner {
   // A reduction kernel over `in_shape` along `dims`. `operands` are evaluated by
   // the emitter (fusion members inline). Writes `outs` (kept-dims shape) or,
   // when `splits` > 1, partial results laid out [split][kept].
-  struct ReduceGen {
+  // Several reductions over the same index space (same input shape and dimensions) can share one kernel:
+  // each part keeps its own accumulators, initial values and combiner; inputs common to the parts are read once.
+  struct ReducePart {
     std::vector<Value*> operands;      // values reduced
     std::vector<Value*> inits;
-    std::vector<int64_t> in_shape, dims;
     Block* body = nullptr;
     std::vector<DT> dts;
+  };
+  struct ReduceGen {
+    std::vector<ReducePart> parts;
+    std::vector<int64_t> in_shape, dims;
   };
 
   Launch gen_reduce_kernel(const ReduceGen& rg, std::function<bool(Op*)> internal, int splits, bool col,
                            std::vector<Value*> outs) {
-    size_t n = rg.operands.size();
+    size_t n = 0;
+    std::vector<DT> dts;
+    std::vector<Value*> all_inits;
+    for (auto& part : rg.parts) {
+      n += part.operands.size();
+      dts.insert(dts.end(), part.dts.begin(), part.dts.end());
+      all_inits.insert(all_inits.end(), part.inits.begin(), part.inits.end());
+    }
     std::vector<int64_t> kept_dims, kept_shape, red_shape;
     for (size_t d = 0; d < rg.in_shape.size(); d++) {
       if (std::find(rg.dims.begin(), rg.dims.end(), (int64_t)d) == rg.dims.end()) {
@@ -602,28 +661,41 @@ struct Planner {
       }
     }
     std::vector<std::string> vals;
-    for (auto* v : rg.operands) vals.push_back(em.emit(v, oc));
-    // combine(acc, val)
-    std::vector<std::string> args;
-    for (size_t k = 0; k < n; k++) args.push_back("acc" + std::to_string(k));
-    for (size_t k = 0; k < n; k++) args.push_back(vals[k]);
+    for (auto& part : rg.parts)
+      for (auto* v : part.operands) vals.push_back(em.emit(v, oc));
+    // combine(acc, val), part by part
     em.round_small_floats = false;
-    auto comb = em.emit_scalar_region(rg.body, args);
-    for (size_t k = 0; k < n; k++) em.line("acc" + std::to_string(k) + " = " + comb[k] + ";");
+    {
+      size_t base = 0;
+      for (auto& part : rg.parts) {
+        const size_t np = part.operands.size();
+        std::vector<std::string> args;
+        for (size_t k = 0; k < np; k++) args.push_back("acc" + std::to_string(base + k));
+        for (size_t k = 0; k < np; k++) args.push_back(vals[base + k]);
+        auto comb = em.emit_scalar_region(part.body, args);
+        for (size_t k = 0; k < np; k++) em.line("acc" + std::to_string(base + k) + " = " + comb[k] + ";");
+        base += np;
+      }
+    }
     // a second emitter instance renders combine(acc, other) for the cross-thread tree
     auto tree_combine = [&](Emitter& te, const std::string& other_prefix) {
-      std::vector<std::string> a2;
-      for (size_t k = 0; k < n; k++) a2.push_back("acc" + std::to_string(k));
-      for (size_t k = 0; k < n; k++) a2.push_back(other_prefix + std::to_string(k));
       te.round_small_floats = false;
-      auto c2 = te.emit_scalar_region(rg.body, a2);
-      for (size_t k = 0; k < n; k++) te.line("acc" + std::to_string(k) + " = " + c2[k] + ";");
+      size_t base = 0;
+      for (auto& part : rg.parts) {
+        const size_t np = part.operands.size();
+        std::vector<std::string> a2;
+        for (size_t k = 0; k < np; k++) a2.push_back("acc" + std::to_string(base + k));
+        for (size_t k = 0; k < np; k++) a2.push_back(other_prefix + std::to_string(base + k));
+        auto c2 = te.emit_scalar_region(part.body, a2);
+        for (size_t k = 0; k < np; k++) te.line("acc" + std::to_string(base + k) + " = " + c2[k] + ";");
+        base += np;
+      }
     };
     // kernel parameters: outputs, then loop inputs, then init values
     std::vector<Value*> ins = em.inputs;
     std::vector<std::string> init_names;
     for (size_t k = 0; k < n; k++) {
-      Value* iv = rg.inits[k];
+      Value* iv = all_inits[k];
       Op* d = iv->def;
       if (d && d->short_name() == "constant") {
         DenseValue dv = attr_dense(d->attr("value"));
@@ -648,10 +720,10 @@ struct Planner {
       const int TX = 32, TY = 8;
       src << "extern \"C\" __global__ void __launch_bounds__(" << TX * TY << ") @NAME@(" << signature(outs, ins) << ") {\n";
       for (size_t k = 0; k < n; k++)
-        src << "  __shared__ " << c_type(rg.dts[k]) << " sm" << k << "[" << TY << "][" << TX + 1 << "];\n";
+        src << "  __shared__ " << c_type(dts[k]) << " sm" << k << "[" << TY << "][" << TX + 1 << "];\n";
       src << "  const " << it << " o = (" << it << ")blockIdx.x * " << TX << " + threadIdx.x;\n";
       src << "  const bool live = o < (" << it << ")" << Nk << "LL;\n";
-      for (size_t k = 0; k < n; k++) src << "  " << c_type(rg.dts[k]) << " acc" << k << " = " << init_names[k] << ";\n";
+      for (size_t k = 0; k < n; k++) src << "  " << c_type(dts[k]) << " acc" << k << " = " << init_names[k] << ";\n";
       src << "  if (live) {\n" << pe.str();
       src << "    #pragma unroll 4\n";      // independent loads of several rows in flight per thread
       src << "    for (" << it << " r = (" << it << ")blockIdx.y * " << TY << " + threadIdx.y; r < (" << it << ")" << Nr
@@ -663,7 +735,7 @@ struct Planner {
       src << "  if (threadIdx.y == 0 && live) {\n";
       src << "    for (int y = 1; y < " << TY << "; ++y) {\n";
       for (size_t k = 0; k < n; k++)
-        src << "      const " << c_type(rg.dts[k]) << " oth" << k << " = sm" << k << "[y][threadIdx.x];\n";
+        src << "      const " << c_type(dts[k]) << " oth" << k << " = sm" << k << "[y][threadIdx.x];\n";
       Emitter te;
       te.idx_t = em.idx_t;
       te.name_prefix = "t";
@@ -683,11 +755,11 @@ struct Planner {
       int per_block = 256 / T;
       src << "extern \"C\" __global__ void __launch_bounds__(256) @NAME@(" << signature(outs, ins) << ") {\n";
       if (T == 256)
-        for (size_t k = 0; k < n; k++) src << "  __shared__ " << c_type(rg.dts[k]) << " sm" << k << "[8];\n";
+        for (size_t k = 0; k < n; k++) src << "  __shared__ " << c_type(dts[k]) << " sm" << k << "[8];\n";
       src << "  const " << it << " o = (" << it << ")blockIdx.x * " << per_block << " + threadIdx.x / " << T << ";\n";
       src << "  const int lane = threadIdx.x % " << T << ";\n";
       src << "  const bool live = o < (" << it << ")" << Nk << "LL;\n";
-      for (size_t k = 0; k < n; k++) src << "  " << c_type(rg.dts[k]) << " acc" << k << " = " << init_names[k] << ";\n";
+      for (size_t k = 0; k < n; k++) src << "  " << c_type(dts[k]) << " acc" << k << " = " << init_names[k] << ";\n";
       src << "  if (live) {\n" << pe.str();
       src << "    #pragma unroll 4\n";
       src << "    for (" << it << " r = (" << it << ")blockIdx.y * " << T << " + lane; r < (" << it << ")" << Nr
@@ -696,7 +768,7 @@ struct Planner {
       src << "    }\n  }\n";
       src << "  #pragma unroll\n  for (int m = 16; m >= 1; m >>= 1) {\n";
       for (size_t k = 0; k < n; k++)
-        src << "    const " << c_type(rg.dts[k]) << " oth" << k << " = shfl_xor(acc" << k << ", m);\n";
+        src << "    const " << c_type(dts[k]) << " oth" << k << " = shfl_xor(acc" << k << ", m);\n";
       {
         Emitter te;
         te.idx_t = em.idx_t;
@@ -713,7 +785,7 @@ struct Planner {
         src << " }\n  __syncthreads();\n";
         src << "  if (threadIdx.x == 0) {\n    for (int w = 1; w < 8; ++w) {\n";
         for (size_t k = 0; k < n; k++)
-          src << "      const " << c_type(rg.dts[k]) << " oth" << k << " = sm" << k << "[w];\n";
+          src << "      const " << c_type(dts[k]) << " oth" << k << " = sm" << k << "[w];\n";
         Emitter te;
         te.idx_t = em.idx_t;
         te.name_prefix = "u";
@@ -730,7 +802,7 @@ struct Planner {
       L.grid[0] = (unsigned)((Nk + per_block - 1) / per_block); L.grid[1] = (unsigned)splits; L.grid[2] = 1;
       L.block[0] = 256; L.block[1] = L.block[2] = 1;
     }
-    L.kernel = add_kernel(src.str());
+    L.kernel = add_kernel(src.str(), "reduce");
     return L;
   }
 
@@ -750,7 +822,7 @@ struct Planner {
     int split = 1;
     if (tiles < 148 && p.K >= 512) {
       split = (int)std::min<long long>((2 * 148 + tiles - 1) / tiles, (p.K + 255) / 256);
-      split = std::max(1, std::min(split, 64));
+      split = std::max(1, std::min(split, 296));
     }
     p.split_k = split;
   }
@@ -1068,19 +1140,26 @@ struct Planner {
       add_launch(plan, L, group_label(g), st);
       return;
     }
+    // one part per reduce op of the group (sibling reductions over the same index space share the kernel)
     Op* r = g->roots[0];
-    size_t n = r->operands.size() / 2;
     ReduceGen rg;
-    rg.operands.assign(r->operands.begin(), r->operands.begin() + n);
-    rg.inits.assign(r->operands.begin() + n, r->operands.end());
     rg.in_shape = r->operands[0]->type.dims;
     rg.dims = attr_i64s(r->attr("dimensions"));
-    rg.body = r->regions[0].get();
-    for (auto* v : r->results) rg.dts.push_back(v->type.dt);
-    for (auto* iv : rg.inits)
-      if (!(iv->def && iv->def->short_name() == "constant")) {
-        if (!slot_of.count(iv)) throw CompileError("reduce: init value must be a constant or live in memory");
-      }
+    std::vector<Value*> outs;
+    for (Op* root : g->roots) {
+      const size_t np = root->operands.size() / 2;
+      ReducePart part;
+      part.operands.assign(root->operands.begin(), root->operands.begin() + np);
+      part.inits.assign(root->operands.begin() + np, root->operands.end());
+      part.body = root->regions[0].get();
+      for (auto* v : root->results) part.dts.push_back(v->type.dt);
+      for (auto* iv : part.inits)
+        if (!(iv->def && iv->def->short_name() == "constant")) {
+          if (!slot_of.count(iv)) throw CompileError("reduce: init value must be a constant or live in memory");
+        }
+      outs.insert(outs.end(), root->results.begin(), root->results.end());
+      rg.parts.push_back(std::move(part));
+    }
     std::vector<int64_t> kept_shape;
     int64_t Nk = 1, Nr = 1, trailing = 1;
     int last_red = -1;
@@ -1090,7 +1169,6 @@ struct Planner {
       else { Nk *= rg.in_shape[d]; kept_shape.push_back(rg.in_shape[d]); }
     }
     for (size_t d = last_red + 1; d < rg.in_shape.size(); d++) trailing *= rg.in_shape[d];
-    std::vector<Value*> outs(r->results.begin(), r->results.end());
     if (Nk == 0) { for (auto* o : outs) ensure_slot(o, st); return; }
     bool col = trailing >= 16;
     // parallelism: split the reduced range over blockIdx.y when there are few outputs
@@ -1112,26 +1190,31 @@ struct Planner {
       add_launch(plan, L, group_label(g), st);
       return;
     }
-    // pass 1 -> partials [splits, kept...]; pass 2 reduces dim 0 with the same combiner
+    // pass 1 -> partials [splits, kept...]; pass 2 reduces dim 0 with the same combiners
     std::vector<Value*> partials;
-    for (size_t k = 0; k < n; k++) {
-      TensorType t;
-      t.dt = rg.dts[k];
-      t.dims.push_back(splits);
-      for (auto s : kept_shape) t.dims.push_back(s);
-      Value* pv = synth(t);
-      partials.push_back(pv);
+    ReduceGen r2;
+    for (auto& part : rg.parts) {
+      ReducePart p2;
+      for (size_t k = 0; k < part.operands.size(); k++) {
+        TensorType t;
+        t.dt = part.dts[k];
+        t.dims.push_back(splits);
+        for (auto s : kept_shape) t.dims.push_back(s);
+        Value* pv = synth(t);
+        partials.push_back(pv);
+        p2.operands.push_back(pv);
+      }
+      p2.inits = part.inits;
+      p2.body = part.body;
+      p2.dts = part.dts;
+      r2.parts.push_back(std::move(p2));
     }
     Launch L1 = gen_reduce_kernel(rg, internal, splits, col, partials);
     add_launch(plan, L1, group_label(g) + ".partial", st);
-    ReduceGen r2;
-    r2.operands = partials;
-    r2.inits = rg.inits;
     r2.in_shape = partials[0]->type.dims;
     r2.dims = {0};
-    r2.body = rg.body;
-    r2.dts = rg.dts;
-    Launch L2 = gen_reduce_kernel(r2, [](Op*) { return false; }, 1, Nk >= 16, outs);
+    // few outputs: one warp per output walks the partials (a column kernel would run as two or three blocks)
+    Launch L2 = gen_reduce_kernel(r2, [](Op*) { return false; }, 1, Nk >= 2048, outs);
     add_launch(plan, L2, group_label(g) + ".final", st);
   }
 
@@ -1239,6 +1322,7 @@ struct Planner {
     build_groups(st);
     for (auto& g : st.groups)
       for (auto* m : g.members) g.max_pos = std::max(g.max_pos, m->pos);
+    if (opts.fuse) merge_sibling_reductions(st);
 
     // units and their dependencies
     std::vector<Unit> units;
