@@ -1613,6 +1613,15 @@ struct Planner {
     };
     for (size_t i = 0; i < S; i++) {
       Step& s = plan.steps[i];
+      if (s.kind == Step::ALL_REDUCE) {
+        // a run of all-reduces is issued as one NCCL group whose members execute concurrently: every operand
+        // of the run is live over the whole run, so no output can reuse the memory of another member's input
+        size_t b = i, e = i;
+        while (b > 0 && plan.steps[b - 1].kind == Step::ALL_REDUCE) b--;
+        while (e + 1 < S && plan.steps[e + 1].kind == Step::ALL_REDUCE) e++;
+        for (int a : s.args) { touch(a, (int)b); touch(a, (int)e); }
+        continue;
+      }
       for (int a : s.args) touch(a, (int)i);
       for (int a : s.state) touch(a, (int)i);
       for (int a : s.init) touch(a, (int)i);

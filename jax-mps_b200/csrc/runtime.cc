@@ -609,7 +609,37 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
 }
 
 b200_error* run_plan(ExecCtx& x, const Plan& plan) {
-  for (auto& s : plan.steps) {
+  for (size_t si = 0; si < plan.steps.size(); ++si) {
+    const Step& s = plan.steps[si];
+    if (s.kind == Step::ALL_REDUCE && x.c->nprocs > 1) {
+      // consecutive all-reduces (the gradient leaves of a data-parallel step) go out as one NCCL group: one
+      // fused launch instead of one per leaf
+      size_t sj = si;
+      size_t bytes = 0;
+      while (sj < plan.steps.size() && plan.steps[sj].kind == Step::ALL_REDUCE) bytes += plan.steps[sj++].bytes;
+      ExecCtx::Timed t;
+      if (x.c->profiling) {
+        t.kind = "all_reduce";
+        t.key = "all_reduce group of " + std::to_string(sj - si) + ", " + std::to_string(bytes) + " bytes";
+        cudaEventCreate(&t.a);
+        cudaEventCreate(&t.b);
+        cudaEventRecord(t.a, x.c->compute);
+      }
+      const int before = x.launches;
+      nccl().GroupStart();
+      b200_error* err = nullptr;
+      for (size_t k = si; k < sj && !err; ++k) err = run_step(x, plan.steps[k]);
+      ncclResult_t r = nccl().GroupEnd();
+      if (err) return err;
+      if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclGroupEnd failed: ") + nccl().GetErrorString(r));
+      x.launches = before + 1;
+      if (x.c->profiling) {
+        cudaEventRecord(t.b, x.c->compute);
+        x.timed.push_back(t);
+      }
+      si = sj - 1;
+      continue;
+    }
     bool timed = x.c->profiling && s.kind != Step::WHILE && s.kind != Step::CASE;
     ExecCtx::Timed t;
     if (timed) {

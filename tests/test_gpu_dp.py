@@ -1,0 +1,71 @@
+"""Two GPUs, one process each: the data-parallel ResNet step (per-shard body with stablehlo.all_reduce over
+NCCL) against single-device steps on the two shards. With zero initial momentum the update is linear in the
+gradient, so the data-parallel parameters equal the mean of the two single-device results, the loss is the
+mean of the shard losses, and both replicas must hold identical bits afterwards. Skipped with fewer than 2 GPUs."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+CFG = dict(batch=8, image=16, width=8)
+pytestmark = pytest.mark.gpu
+
+
+def _rank_main(rank, world, id_pipe, q):
+    sys.path.insert(0, str(ROOT / "jax-mps_b200"))
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        import b200
+        from b200.shlo import programs
+        if rank == 0:
+            nccl_id = b200.nccl_unique_id()
+            for p in id_pipe:
+                p.send(nccl_id)
+        else:
+            nccl_id = id_pipe.recv()
+        dp = b200.Client(device_ordinal=rank, process_index=rank, num_processes=world, nccl_id=nccl_id)
+        prog = programs.resnet18_train_step(n_partitions=world, **CFG)
+        args = programs.resnet18_inputs(prog, rank=rank)
+        outs = [o.to_numpy() for o in dp.compile(prog.text).execute([dp.buffer_from_host(a) for a in args])]
+        dp.synchronize()
+        single = b200.Client(device_ordinal=rank)
+        prog1 = programs.resnet18_train_step(n_partitions=1, **CFG)
+        outs1 = [o.to_numpy() for o in single.compile(prog1.text).execute([single.buffer_from_host(a) for a in args])]
+        single.synchronize()
+        q.put((rank, outs, outs1))
+    except Exception as e:          # surface the failure instead of leaving the parent to time out
+        q.put((rank, repr(e), None))
+
+
+def test_two_gpu_step_is_the_mean_of_the_shard_steps():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    recv, send = ctx.Pipe(duplex=False)
+    procs = [ctx.Process(target=_rank_main, args=(0, world, [send], q)),
+             ctx.Process(target=_rank_main, args=(1, world, recv, q))]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(world):
+        r, a, b = q.get(timeout=300)
+        assert not isinstance(a, str), f"rank {r} failed: {a}"
+        got[r] = (a, b)
+    for p in procs:
+        p.join(timeout=60)
+    n_leaves = (len(got[0][0]) - 1) // 2
+    np.testing.assert_allclose(got[0][0][0], (got[0][1][0] + got[1][1][0]) / 2, rtol=1e-5)
+    for i in range(1, len(got[0][0])):
+        np.testing.assert_array_equal(got[0][0][i], got[1][0][i], err_msg=f"replicas differ at result {i}")
+        want = (got[0][1][i].astype(np.float64) + got[1][1][i].astype(np.float64)) / 2
+        scale = max(1.0, float(np.max(np.abs(want))))
+        np.testing.assert_allclose(got[0][0][i], want, rtol=1e-4, atol=1e-5 * scale, err_msg=f"result {i}")
+    assert n_leaves == 62
