@@ -576,16 +576,64 @@ struct Planner {
     std::ostringstream src;
     src << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(" << signature(outs, em.inputs)
         << ") {\n";
-    src << "  #pragma unroll\n  for (int e = 0; e < " << kEPT << "; ++e) {\n";
-    src << "    const " << em.idx_t << " lin = ((" << em.idx_t << ")blockIdx.x * " << kEPT << " + e) * " << kThreads
-        << " + threadIdx.x;\n";
-    src << "    if (lin >= (" << em.idx_t << ")" << n << "LL) break;\n";
-    src << em.str();
-    src << "  }\n}\n";
+    // 16-byte accesses: when the element count is a multiple of 4 and every output is a 4-byte type, a thread
+    // takes 4 consecutive elements; inputs read at the kernel's own linear index (same-shaped tensors) are
+    // fetched as one 16-byte load, the outputs leave as one 16-byte store. Other operands (broadcast vectors,
+    // gathers) keep their scalar loads.
+    auto four_bytes = [](DT d) { return d == DT::F32 || d == DT::I32 || d == DT::U32; };
+    bool vec4 = n % 4 == 0 && n >= 4096;
+    for (auto* o : outs) vec4 = vec4 && four_bytes(o->type.dt);
     Launch L;
-    L.kernel = add_kernel(src.str(), "fused");
-    int64_t blocks = std::max<int64_t>(1, (n + (int64_t)kThreads * kEPT - 1) / ((int64_t)kThreads * kEPT));
-    L.grid[0] = (unsigned)blocks; L.grid[1] = L.grid[2] = 1;
+    if (vec4) {
+      std::string body = em.str();
+      auto replace_all = [](std::string& str, const std::string& from, const std::string& to) {
+        size_t pos = 0;
+        bool any = false;
+        while ((pos = str.find(from, pos)) != std::string::npos) {
+          if (pos > 0 && (isalnum((unsigned char)str[pos - 1]) || str[pos - 1] == '_')) { pos += from.size(); continue; }
+          str.replace(pos, from.size(), to);
+          pos += to.size();
+          any = true;
+        }
+        return any;
+      };
+      std::ostringstream loads, stores;
+      for (size_t k = 0; k < em.inputs.size(); k++) {
+        Value* in = em.inputs[k];
+        if (!four_bytes(in->type.dt) || in->type.numel() != n) continue;
+        const std::string nm = "in" + std::to_string(k);
+        if (!replace_all(body, nm + "[lin]", "v" + nm + "[e]")) continue;
+        const char* ct = c_type(in->type.dt);
+        loads << "  __align__(16) " << ct << " v" << nm << "[4];\n  *reinterpret_cast<uint4*>(v" << nm
+              << ") = *reinterpret_cast<const uint4*>(" << nm << " + base);\n";
+      }
+      for (size_t k = 0; k < outs.size(); k++) {
+        const std::string nm = "out" + std::to_string(k);
+        replace_all(body, nm + "[lin]", "v" + nm + "[e]");
+        loads << "  __align__(16) " << c_type(outs[k]->type.dt) << " v" << nm << "[4];\n";
+        stores << "  *reinterpret_cast<uint4*>(" << nm << " + base) = *reinterpret_cast<const uint4*>(v" << nm << ");\n";
+      }
+      src << "  const " << em.idx_t << " base = ((" << em.idx_t << ")blockIdx.x * " << kThreads << " + threadIdx.x) * 4;\n";
+      src << "  if (base >= (" << em.idx_t << ")" << n << "LL) return;\n";
+      src << loads.str();
+      src << "  #pragma unroll\n  for (int e = 0; e < 4; ++e) {\n";
+      src << "    const " << em.idx_t << " lin = base + e;\n";
+      src << body;
+      src << "  }\n" << stores.str() << "}\n";
+      L.kernel = add_kernel(src.str(), "fused");
+      int64_t blocks = std::max<int64_t>(1, (n / 4 + kThreads - 1) / kThreads);
+      L.grid[0] = (unsigned)blocks; L.grid[1] = L.grid[2] = 1;
+    } else {
+      src << "  #pragma unroll\n  for (int e = 0; e < " << kEPT << "; ++e) {\n";
+      src << "    const " << em.idx_t << " lin = ((" << em.idx_t << ")blockIdx.x * " << kEPT << " + e) * " << kThreads
+          << " + threadIdx.x;\n";
+      src << "    if (lin >= (" << em.idx_t << ")" << n << "LL) break;\n";
+      src << em.str();
+      src << "  }\n}\n";
+      L.kernel = add_kernel(src.str(), "fused");
+      int64_t blocks = std::max<int64_t>(1, (n + (int64_t)kThreads * kEPT - 1) / ((int64_t)kThreads * kEPT));
+      L.grid[0] = (unsigned)blocks; L.grid[1] = L.grid[2] = 1;
+    }
     L.block[0] = kThreads; L.block[1] = L.block[2] = 1;
     L.outs = outs;
     L.ins = em.inputs;
