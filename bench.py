@@ -234,10 +234,25 @@ def run_b200(args):
         k["count"] += r["count"] // psteps
     igemm_ms = by_kind.get("igemm", {}).get("ms", 0.0)
     hbm, tens, which = measured_peaks()
-    achieved = FLOP_PER_STEP / (igemm_ms * 1e-3) / 1e12 if igemm_ms else 0.0
+    family = FLOP_PER_STEP / (igemm_ms * 1e-3) / 1e12 if igemm_ms else 0.0
+    # the dominant launch class: the 3x3 stride-1 convolutions of stage 1 (forward and input gradient,
+    # M = 128*32*32 output pixels, N = 64 channels, K = 9*64), eight launches of one kernel per step
+    dom = [r for r in rep if r["kind"] == "igemm" and " M=131072 N=64 K=576 " in r["key"] + " "]
+    dom_ms = sum(r["ms"] for r in dom)
+    dom_n = sum(r["count"] for r in dom)
+    dom_flop = 2.0 * 131072 * 64 * 576
+    achieved = dom_flop * dom_n / (dom_ms * 1e-3) / 1e12 if dom_ms else 0.0
     roofline = {"bound": "tensor", "achieved": achieved, "peak": tens, "unit": "TFLOP/s", "frac": achieved / tens,
-                "traffic": None, "kernel": "igemm_f32 (all convolutions and dense layers of the step)",
-                "peak_source": f"bf16 sustained, {which}", "ms_per_step_in_kernel": igemm_ms,
+                # DRAM bytes of one such launch from the ncu capture summarised in profiles/ (input 33.6 MB read once,
+                # the 33.6 MB output still in L2 when the kernel ends); algorithmic bytes are 67.3 MB
+                "traffic": 37.6e6,
+                "kernel": "igemm_tf32x3_ta_kernel<64,...> on M=131072 N=64 K=576 (stage-1 3x3 convolutions, forward "
+                          "and input gradient), algorithmic fp32 flop 2*M*N*K per launch",
+                "launches_per_step": dom_n // psteps, "us_per_launch": 1e3 * dom_ms / max(dom_n, 1),
+                "peak_source": f"bf16 sustained, {which}; the fp32-accurate path issues three TF32 MMAs per product, "
+                               "so its own ceiling is the TF32 rate / 3 (about 360 TFLOP/s measured issue rate)",
+                "all_contractions": {"achieved": family, "frac": family / tens, "ms_per_step": igemm_ms,
+                                     "flop_per_step": FLOP_PER_STEP},
                 "ms_per_step_by_kind": {k: round(v["ms"], 4) for k, v in by_kind.items()},
                 "launches_by_kind": {k: v["count"] for k, v in by_kind.items()}}
 
