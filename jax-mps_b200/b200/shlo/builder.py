@@ -164,6 +164,8 @@ class Builder:
         if isinstance(rets, Val):
             rets = [rets]
         sub.emit("stablehlo.return", list(rets), [])
+        if not args:                   # a region without block arguments has no block header
+            return "{\n" + "\n".join(sub.lines) + "\n" + " " * self.indent + "}"
         head = " " * (self.indent + 2) + "^bb0(" + ", ".join(f"{a.name}: {a.type}" for a in args) + "):"
         return "{\n" + head + "\n" + "\n".join(sub.lines) + "\n" + " " * self.indent + "}"
 
@@ -605,6 +607,21 @@ class Builder:
                                          "unique_indices": "false"}, regions=[reg])
                 return [dt, None]
             self.record([y], [table, idx], vjp)
+        return y
+
+    def scatter_rows(self, operand: Val, idx: Val, updates: Val, op: str = "add") -> Val:
+        """operand.at[idx].<op>(updates) for integer idx of any shape and updates of shape idx.shape + operand.shape[1:]
+        (`op` in add, multiply, minimum, maximum, or "set"); no gradient."""
+        n = idx.ndim
+        idx2 = self.reshape(idx, (*idx.shape, 1))
+        win = list(range(n, n + operand.ndim - 1))
+        sdn = (f"#stablehlo.scatter<update_window_dims = {win}, inserted_window_dims = [0], "
+               f"scatter_dims_to_operand_dims = [0], index_vector_dim = {n}>")
+        body = (lambda s, a, u: u) if op == "set" else (lambda s, a, u: s._binary(op, a, u))
+        reg = self.region([((), operand.dtype)] * 2, body)
+        (y,) = self.emit("stablehlo.scatter", [operand, idx2, updates], [(operand.shape, operand.dtype)],
+                         props={"scatter_dimension_numbers": sdn, "indices_are_sorted": "false",
+                                "unique_indices": "false"}, regions=[reg])
         return y
 
     def take_along_last(self, x: Val, idx: Val) -> Val:

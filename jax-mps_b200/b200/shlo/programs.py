@@ -204,3 +204,246 @@ def resnet18_inputs(prog: Program, seed_w: int = 0, seed_x: int = 1, rank: int =
         else:
             out.append(rng.integers(0, 10, s).astype(np.int32))
     return out
+
+
+# --------------------------------------------------------------------------
+# Gemma-shaped greedy decoding
+# --------------------------------------------------------------------------
+
+def gemma_param_spec(vocab: int, dim: int, layers: int, heads: int, head_dim: int, hidden: int):
+    """Leaves of the decoder (examples/gemma/model.py:118-296): tied embedding, per layer two RMSNorm weights,
+    q / k / v / o projections with one shared key-value head, and the GeGLU feed-forward."""
+    spec = [("embed", (vocab, dim))]
+    for i in range(layers):
+        p = f"layer{i}."
+        spec += [(p + "attn_norm", (dim,)), (p + "wq", (dim, heads * head_dim)), (p + "wk", (dim, head_dim)),
+                 (p + "wv", (dim, head_dim)), (p + "wo", (heads * head_dim, dim)), (p + "mlp_norm", (dim,)),
+                 (p + "w_gate", (dim, hidden)), (p + "w_up", (dim, hidden)), (p + "w_down", (hidden, dim))]
+    spec.append(("final_norm", (dim,)))
+    return spec
+
+
+def gemma_greedy_decode(vocab: int = 256000, dim: int = 2048, layers: int = 18, heads: int = 8, head_dim: int = 256,
+                        hidden: int = 16384, prompt_len: int = 512, new_tokens: int = 128, cache_len: int = 640,
+                        dtype: str = "bf16") -> Program:
+    """Prompt consumption and greedy generation in one stablehlo.while (the loop of examples/gemma/main.py:109-134
+    moved inside the program): every iteration embeds one token, runs the decoder with a static key-value cache
+    updated in place by dynamic_update_slice, and takes the argmax of the tied-embedding logits. While the
+    position is inside the prompt the next input is the prompt token, afterwards the argmax. Arguments: the
+    weights (bf16), prompt i32[prompt_len]. Results: tokens i32[prompt_len + new_tokens] (prompt followed by the
+    generated ids) and the last step's logits f32[vocab]. Norms, rotary embedding and softmax compute in f32."""
+    spec = gemma_param_spec(vocab, dim, layers, heads, head_dim, hidden)
+    total = prompt_len + new_tokens
+    assert total <= cache_len
+    b = Builder()
+    W = {n: b.arg(s, dtype) for n, s in spec}
+    prompt = b.arg((prompt_len,), "i32")
+    half = head_dim // 2
+    inv_freq = b.const_array((1.0 / (10000.0 ** (np.arange(half, dtype=np.float64) * 2 / head_dim))).astype(np.float32))
+    pos_ids = b.iota((cache_len,), "i32", 0)
+
+    def rms_norm(s, x, w):                           # x f32[dim]; weight stored as (1 + w)
+        ms = s.mean(s.mul(x, x), (0,))
+        inv = s.rsqrt(s.add(ms, s.const(1e-6, "f32")))
+        scale = s.add(s.convert(w, "f32"), s.full((dim,), 1.0, "f32"))
+        return s.mul(s.mul(x, s.bcast(inv, (dim,))), scale)
+
+    def rope(s, x, cos, sin, n):                     # x f32[n, head_dim], rotate-half form
+        x1, x2 = s.slice(x, (0, 0), (n, half)), s.slice(x, (0, half), (n, head_dim))
+        c, sn = s.bcast(cos, (n, half), (1,)), s.bcast(sin, (n, half), (1,))
+        return s.concatenate([s.sub(s.mul(x1, c), s.mul(x2, sn)), s.add(s.mul(x2, c), s.mul(x1, sn))], 1)
+
+    def gelu(s, x):
+        c = s.full(x.shape, math.sqrt(2.0 / math.pi), "f32")
+        inner = s.mul(c, s.add(x, s.mul(s.full(x.shape, 0.044715, "f32"), s.mul(x, s.mul(x, x)))))
+        return s.mul(s.mul(x, s.full(x.shape, 0.5, "f32")), s.add(s.full(x.shape, 1.0, "f32"), s.tanh(inner)))
+
+    def lin(s, x, w):                                # f32[1, k] through a bf16 weight, bf16 product, f32 out
+        return s.convert(s.matmul(s.convert(x, dtype), w), "f32")
+
+    n_state = 3 + 2 * layers
+
+    def cond(s, t, *rest):
+        return s.compare(t, s.const(total, "i32"), "LT")
+
+    def body(s, t, tok, toks, *caches):
+        z = s.const(0, "i32")
+        caches = list(caches)
+        x = s.convert(s.take_rows(W["embed"], s.reshape(tok, (1,))), "f32")            # [1, dim]
+        x = s.reshape(s.mul(x, s.full((1, dim), math.sqrt(dim), "f32")), (dim,))
+        ang = s.mul(s.bcast(s.convert(t, "f32"), (half,)), inv_freq)
+        cos, sin = s.cos(ang), s.sin(ang)
+        for i in range(layers):
+            p = f"layer{i}."
+            h = s.reshape(rms_norm(s, x, W[p + "attn_norm"]), (1, dim))
+            q = rope(s, s.reshape(lin(s, h, W[p + "wq"]), (heads, head_dim)), cos, sin, heads)
+            k = rope(s, lin(s, h, W[p + "wk"]), cos, sin, 1)
+            v = lin(s, h, W[p + "wv"])
+            kc = s.dynamic_update_slice(caches[2 * i], s.convert(k, dtype), [t, z])       # [cache_len, head_dim]
+            vc = s.dynamic_update_slice(caches[2 * i + 1], s.convert(v, dtype), [t, z])
+            caches[2 * i], caches[2 * i + 1] = kc, vc
+            sc = s.convert(s.dot_general(s.convert(q, dtype), kc, ((1,), (1,))), "f32")   # [heads, cache_len]
+            sc = s.mul(sc, s.full(sc.shape, 1.0 / math.sqrt(head_dim), "f32"))
+            visible = s.compare(s.bcast(pos_ids, sc.shape, (1,)), s.bcast(t, sc.shape), "LE")
+            sc = s.select(visible, sc, s.full(sc.shape, -1e30, "f32"))
+            m = s.reduce_max(sc, (1,))
+            e = s.exp(s.sub(sc, s.bcast(m, sc.shape, (0,))))
+            pr = s.div(e, s.bcast(s.reduce_sum(e, (1,)), sc.shape, (0,)))
+            att = s.convert(s.matmul(s.convert(pr, dtype), vc), "f32")                    # [heads, head_dim]
+            o = lin(s, s.reshape(att, (1, heads * head_dim)), W[p + "wo"])
+            x = s.add(x, s.reshape(o, (dim,)))
+            h2 = s.reshape(rms_norm(s, x, W[p + "mlp_norm"]), (1, dim))
+            ff = s.mul(gelu(s, lin(s, h2, W[p + "w_gate"])), lin(s, h2, W[p + "w_up"]))
+            x = s.add(x, s.reshape(lin(s, ff, W[p + "w_down"]), (dim,)))
+        hf = s.convert(s.reshape(rms_norm(s, x, W["final_norm"]), (1, dim)), dtype)
+        logits = s.reshape(s.convert(s.dot_general(hf, W["embed"], ((1,), (1,))), "f32"), (vocab,))
+        best = s.reshape(s.argmax(logits, 0), (1,))
+        t1 = s.add(t, s.const(1, "i32"))
+        # next input: the prompt while inside it, the prediction afterwards
+        idx = s.min(t1, s.const(prompt_len - 1, "i32"))
+        from_prompt = s.dynamic_slice(prompt, [idx], (1,))
+        nxt = s.select(s.reshape(s.compare(t1, s.const(prompt_len, "i32"), "LT"), (1,)), from_prompt, best)
+        toks2 = s.dynamic_update_slice(toks, nxt, [s.min(t1, s.const(total - 1, "i32"))])
+        return [t1, nxt, toks2, *caches, logits]
+
+    tok0 = b.slice(prompt, (0,), (1,))
+    toks0 = b.dynamic_update_slice(b.full((total,), 0, "i32"), tok0, [b.const(0, "i32")])
+    caches0 = [b.full((cache_len, head_dim), 0.0, dtype) for _ in range(2 * layers)]
+    logits0 = b.full((vocab,), 0.0, "f32")
+    init = [b.const(0, "i32"), tok0, toks0, *caches0, logits0]
+    outs = b.while_(init, lambda s, *a: cond(s, *a), lambda s, t, tok, toks, *r: body(s, t, tok, toks, *r[:-1]))
+    text = b.module([outs[2], outs[-1]], name="jit_greedy_decode")
+    args = [(n, s, dtype) for n, s in spec] + [("prompt", (prompt_len,), "i32")]
+    res = [("tokens", (total,), "i32"), ("last_logits", (vocab,), "f32")]
+    return Program("gemma_greedy_decode", text, args, res, 1,
+                   {"vocab": vocab, "dim": dim, "layers": layers, "prompt_len": prompt_len, "new_tokens": new_tokens})
+
+
+def gemma_inputs(prog: Program, seed: int = 0, weight_std: float = 0.02) -> list:
+    """Synthetic arguments: weights ~N(0, weight_std) (norm weights 0, i.e. scale 1), prompt uniform over the
+    vocabulary. Returned as float32 / int32 arrays; float arguments are converted to the program's dtype on upload."""
+    rng = np.random.default_rng(seed)
+    out = []
+    for n, s, d in prog.args:
+        if n == "prompt":
+            out.append(rng.integers(0, prog.meta["vocab"], s).astype(np.int32))
+        elif n.endswith("norm"):
+            out.append(np.zeros(s, np.float32))
+        else:
+            out.append((rng.standard_normal(s) * weight_std).astype(np.float32))
+    return out
+
+
+# --------------------------------------------------------------------------
+# LSTM by scan: one training step
+# --------------------------------------------------------------------------
+
+def lstm_param_spec(in_dim: int = 32, hidden: int = 256):
+    """Two stacked LSTM layers in the concatenated form: gates = [x, h] @ W + b with gate order i, f, g, o."""
+    return [("w1", (in_dim + hidden, 4 * hidden)), ("b1", (4 * hidden,)),
+            ("w2", (2 * hidden, 4 * hidden)), ("b2", (4 * hidden,))]
+
+
+def lstm_scan_train_step(steps: int = 100, batch: int = 64, in_dim: int = 32, hidden: int = 256, lr: float = 1e-3,
+                         beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8) -> Program:
+    """Forward `lax.scan` over `steps` time steps (a stablehlo.while reading xs[t] by dynamic_slice and stacking
+    the carries by dynamic_update_slice), mean-squared error of the last hidden state against `targets`, the
+    reverse scan of its gradient (a second while that recomputes each step from the stacked carries and
+    accumulates the weight gradients), and one Adam update (the first step: bias corrections 1 - beta).
+    The loop structure follows benchmarks/bench_rnn_training.py:63-90 of the reference with LSTM cells.
+    Arguments: 4 parameters, 4 first moments, 4 second moments, xs f32[steps,batch,in_dim], targets
+    f32[batch,hidden]. Results: loss, new parameters, new first moments, new second moments."""
+    spec = lstm_param_spec(in_dim, hidden)
+    H, T, B = hidden, steps, batch
+    b = Builder()
+    P = [b.arg(s, "f32") for _, s in spec]
+    M = [b.arg(s, "f32") for _, s in spec]
+    V = [b.arg(s, "f32") for _, s in spec]
+    xs = b.arg((T, B, in_dim), "f32")
+    targets = b.arg((B, H), "f32")
+
+    def cell(s, x, h, c, w, bias):
+        z = s.add(s.matmul(s.concatenate([x, h], 1), w), s.bcast(bias, (B, 4 * H)))
+        i = s.logistic(s.slice(z, (0, 0), (B, H)))
+        f = s.logistic(s.slice(z, (0, H), (B, 2 * H)))
+        g = s.tanh(s.slice(z, (0, 2 * H), (B, 3 * H)))
+        o = s.logistic(s.slice(z, (0, 3 * H), (B, 4 * H)))
+        c2 = s.add(s.mul(f, c), s.mul(i, g))
+        return s.mul(o, s.tanh(c2)), c2
+
+    def step(s, x, h1, c1, h2, c2, params):
+        w1, b1, w2, b2 = params
+        h1n, c1n = cell(s, x, h1, c1, w1, b1)
+        h2n, c2n = cell(s, h1n, h2, c2, w2, b2)
+        return h1n, c1n, h2n, c2n
+
+    def x_at(s, t):
+        z = s.const(0, "i32")
+        return s.reshape(s.dynamic_slice(xs, [t, z, z], (1, B, in_dim)), (B, in_dim))
+
+    # forward scan: carries entering step t are stacked for the reverse pass
+    def fcond(s, t, *r): return s.compare(t, s.const(T, "i32"), "LT")
+    def fbody(s, t, h1, c1, h2, c2, *stacks):
+        z = s.const(0, "i32")
+        new_stacks = [s.dynamic_update_slice(st, s.reshape(v, (1, B, H)), [t, z, z]) for st, v in zip(stacks, (h1, c1, h2, c2))]
+        out = step(s, x_at(s, t), h1, c1, h2, c2, P)
+        return [s.add(t, s.const(1, "i32")), *out, *new_stacks]
+    zeros = b.full((B, H), 0.0, "f32")
+    stack0 = b.full((T, B, H), 0.0, "f32")
+    fw = b.while_([b.const(0, "i32"), zeros, zeros, zeros, zeros, stack0, stack0, stack0, stack0], fcond, fbody)
+    h2_last, stacks = fw[3], fw[5:9]
+    diff = b.sub(h2_last, targets)
+    loss = b.mean(b.mul(diff, diff), (0, 1))
+    d_h2 = b.mul(diff, b.full((B, H), 2.0 / (B * H), "f32"))
+
+    # reverse scan
+    def bcond(s, k, *r): return s.compare(k, s.const(T, "i32"), "LT")
+    def bbody(s, k, dh1, dc1, dh2, dc2, *gacc):
+        z = s.const(0, "i32")
+        t = s.sub(s.const(T - 1, "i32"), k)
+        carry = [s.reshape(s.dynamic_slice(st, [t, z, z], (1, B, H)), (B, H)) for st in stacks]
+        x = x_at(s, t)
+        s.root.taping = True
+        try:
+            outs = step(s, x, *carry, P)
+            total = None
+            for o, d in zip(outs, (dh1, dc1, dh2, dc2)):
+                term = s.reduce_sum(s.mul(o, d), (0, 1))
+                total = term if total is None else s.add(total, term)
+            grads = s.grad(total, [*carry, *P])
+        finally:
+            s.root.taping = False
+        return [s.add(k, s.const(1, "i32")), *grads[:4], *[s.add(a, g) for a, g in zip(gacc, grads[4:])]]
+    bw = b.while_([b.const(0, "i32"), zeros, zeros, d_h2, zeros, *[b.full(s_, 0.0, "f32") for _, s_ in spec]], bcond, bbody)
+    grads = bw[5:9]
+    b.root.taping = False
+    new_p, new_m, new_v = [], [], []
+    for (n, s_), p, m, v, g in zip(spec, P, M, V, grads):
+        m2 = b.add(b.mul(m, b.full(s_, beta1, "f32")), b.mul(g, b.full(s_, 1.0 - beta1, "f32")))
+        v2 = b.add(b.mul(v, b.full(s_, beta2, "f32")), b.mul(b.mul(g, g), b.full(s_, 1.0 - beta2, "f32")))
+        mhat = b.div(m2, b.full(s_, 1.0 - beta1, "f32"))
+        vhat = b.div(v2, b.full(s_, 1.0 - beta2, "f32"))
+        new_p.append(b.sub(p, b.div(b.mul(mhat, b.full(s_, lr, "f32")), b.add(b.sqrt(vhat), b.full(s_, eps, "f32")))))
+        new_m.append(m2)
+        new_v.append(v2)
+    text = b.module([loss, *new_p, *new_m, *new_v], name="jit_lstm_train_step")
+    args = ([("p." + n, s_, "f32") for n, s_ in spec] + [("m." + n, s_, "f32") for n, s_ in spec] +
+            [("v." + n, s_, "f32") for n, s_ in spec] + [("xs", (T, B, in_dim), "f32"), ("targets", (B, H), "f32")])
+    res = ([("loss", (), "f32")] + [("p." + n, s_, "f32") for n, s_ in spec] + [("m." + n, s_, "f32") for n, s_ in spec] +
+           [("v." + n, s_, "f32") for n, s_ in spec])
+    return Program("lstm_scan_train_step", text, args, res, 1, {"steps": T, "batch": B, "in_dim": in_dim, "hidden": H})
+
+
+def lstm_inputs(prog: Program, seed: int = 0) -> list:
+    """Glorot-uniform weights, zero biases and moments, xs and targets ~N(0,1)."""
+    rng = np.random.default_rng(seed)
+    out = []
+    for n, s, _ in prog.args:
+        if n.startswith("p.w"):
+            lim = math.sqrt(6.0 / (s[0] + s[1]))
+            out.append(rng.uniform(-lim, lim, s).astype(np.float32))
+        elif n in ("xs", "targets"):
+            out.append(rng.standard_normal(s).astype(np.float32))
+        else:
+            out.append(np.zeros(s, np.float32))
+    return out

@@ -160,6 +160,43 @@ struct Inliner {
         return;
       }
     }
+    // dot_general / convolution on bf16 or f16 operands: computed as the f32 contraction of the converted
+    // operands and rounded once at the end. Products of two bf16 (or f16) numbers and their fp32 accumulation
+    // are what XLA's CPU backend computes for these types; the converts fuse into neighbouring kernels.
+    if ((sh == "dot_general" || sh == "convolution") && op->operands.size() == 2 && op->results.size() == 1) {
+      auto half = [](DT d) { return d == DT::BF16 || d == DT::F16; };
+      if (half(op->operands[0]->type.dt) || half(op->operands[1]->type.dt) || half(op->results[0]->type.dt)) {
+        auto convert_to = [&](Value* v, DT to, Value* into) -> Value* {
+          auto c = std::make_unique<Op>();
+          c->name = "stablehlo.convert";
+          c->operands.push_back(v);
+          TensorType t = v->type;
+          t.dt = to;
+          Value* nv = into ? into : m.new_value(t, "");
+          nv->def = c.get();
+          nv->def_index = 0;
+          c->results.push_back(nv);
+          c->parent = b;
+          b->ops.push_back(std::move(c));
+          return nv;
+        };
+        for (auto& o : op->operands)
+          if (half(o->type.dt)) o = convert_to(o, DT::F32, nullptr);
+        Value* orig = op->results[0];
+        if (half(orig->type.dt)) {
+          TensorType t = orig->type;
+          t.dt = DT::F32;
+          Value* wide = m.new_value(t, "");
+          wide->def = op.get();
+          wide->def_index = 0;
+          op->results[0] = wide;
+          op->parent = b;
+          b->ops.push_back(std::move(op));
+          convert_to(wide, orig->type.dt, orig);
+          return;
+        }
+      }
+    }
     for (auto& reg : op->regions) run(reg.get());
     op->parent = b;
     b->ops.push_back(std::move(op));
@@ -558,7 +595,7 @@ struct Planner {
       if (o->type.dims != rt.dims) throw CompileError("internal: fused outputs of different shapes");
     int64_t n = rt.numel();
     Emitter em;
-    em.is_internal = [&](Op* o) { return g->members.count(o) || (is_dup(o) && !st.dup_materialize.count(o)); };
+    em.is_internal = [&](Op* o) { return g->members.count(o) || (is_dup(o) && !st.dup_materialize.count(o) && !slot_of.count(o->results[0])); };
     std::vector<Value*> all;
     for (auto* m : g->members) {
       all.push_back(m->results[0]);
@@ -1147,6 +1184,59 @@ struct Planner {
     return s;
   }
 
+  // stablehlo.scatter in its row form (what jnp.take's gradient and x.at[idx].add(rows) lower to): the index
+  // vector holds one coordinate along operand dimension 0 and every update is a whole row. Updates are applied
+  // in update order per row with an fp32 accumulator, so the result is deterministic (src/pjrt_plugin/ops/gather_scatter.cc:296-699 handles the general form).
+  Step lower_scatter(Op* op, BlockState& st) {
+    if (op->operands.size() != 3 || op->results.size() != 1)
+      throw CompileError("stablehlo.scatter: only one operand / one update tensor is supported");
+    Value *operand = op->operands[0], *indices = op->operands[1], *updates = op->operands[2], *out = op->results[0];
+    auto f = attr_struct(op->attr("scatter_dimension_numbers"));
+    const int ivd = f.count("index_vector_dim") && !f["index_vector_dim"].empty() ? (int)f["index_vector_dim"][0] : indices->type.rank() - 1;
+    const auto uwd = f["update_window_dims"], iwd = f["inserted_window_dims"], sdo = f["scatter_dims_to_operand_dims"];
+    const int R = operand->type.rank();
+    bool ok = R >= 1 && iwd.size() == 1 && iwd[0] == 0 && sdo.size() == 1 && sdo[0] == 0 && f["input_batching_dims"].empty() &&
+              ivd == indices->type.rank() - 1 && indices->type.dims.back() == 1 && (int)uwd.size() == R - 1;
+    const int n_scatter = updates->type.rank() - (R - 1);
+    for (int k = 0; ok && k < R - 1; k++)
+      ok = uwd[k] == n_scatter + k && updates->type.dims[n_scatter + k] == operand->type.dims[k + 1];
+    long long U = 1;
+    for (int k = 0; ok && k < n_scatter; k++) {
+      ok = k < indices->type.rank() - 1 && indices->type.dims[k] == updates->type.dims[k];
+      U *= updates->type.dims[k];
+    }
+    if (!ok) throw CompileError("stablehlo.scatter: only the row form is supported (one index along dimension 0, "
+                                "whole-row update windows); got " + op->attr("scatter_dimension_numbers"));
+    Block* body = op->regions[0].get();
+    int kind = -1;                                    // 0 assign, 1 add, 2 multiply, 3 minimum, 4 maximum
+    if (body->ops.size() == 1 && body->ops[0]->operands.size() == 1 && body->ops[0]->operands[0] == body->args[1]) kind = 0;
+    else if (body->ops.size() == 2) {
+      const std::string sh = body->ops[0]->short_name();
+      kind = sh == "add" ? 1 : sh == "multiply" ? 2 : sh == "minimum" ? 3 : sh == "maximum" ? 4 : -1;
+    }
+    DT dt = operand->type.dt;
+    if (kind < 0 || !(dt == DT::F32 || dt == DT::BF16 || dt == DT::I32))
+      throw CompileError("stablehlo.scatter: update computation or element type not supported (add/multiply/minimum/"
+                         "maximum/assign on f32, bf16, i32)");
+    if (indices->type.dt != DT::I32 && indices->type.dt != DT::I64) throw CompileError("stablehlo.scatter: indices must be i32 or i64");
+    ensure_slot(out, st);
+    for (auto* o : op->operands)
+      if (!slot_of.count(o)) throw CompileError("internal: operand of scatter has no storage");
+    Step s;
+    s.kind = Step::SCATTER;
+    s.label = op->name;
+    s.dtype = dt;
+    s.bytes = operand->type.bytes();
+    const long long rows = operand->type.dims[0];
+    const long long row_elems = rows ? operand->type.numel() / rows : 0;
+    s.iparams = {rows, row_elems, U, indices->type.dt == DT::I64 ? 8 : 4, kind};
+    TensorType t;
+    t.dt = DT::I32;
+    t.dims = {2 * std::max<long long>(U, 1)};
+    s.args = {slot_of.at(operand), slot_of.at(indices), slot_of.at(updates), slot_of.at(out), new_slot(Slot::TEMP, t, st.arena)};
+    return s;
+  }
+
   // ---- block -> steps ----------------------------------------------------------------
   void ensure_slot(Value* v, BlockState& st) {
     if (slot_of.count(v)) return;
@@ -1243,7 +1333,7 @@ struct Planner {
       splits = std::max(1, std::min(splits, 1024));
     }
     auto internal = [this, g, &st](Op* o) {
-      return (g->members.count(o) && categorize(o) != Cat::REDUCE) || (is_dup(o) && !st.dup_materialize.count(o));
+      return (g->members.count(o) && categorize(o) != Cat::REDUCE) || (is_dup(o) && !st.dup_materialize.count(o) && !slot_of.count(o->results[0]));
     };
     if (splits == 1) {
       Launch L = gen_reduce_kernel(rg, internal, 1, col, outs);
@@ -1620,6 +1710,56 @@ struct Planner {
           plan.steps.push_back(std::move(s));
           break;
         }
+        case Cat::CASE: {
+          // lax.cond / lax.switch: the index is read back by the host, the chosen branch's plan runs and its
+          // results are copied into the op's result slots (src/pjrt_plugin/ops/control_flow.cc:702-1317;
+          // an index outside [0, branches) selects the last branch)
+          Step s;
+          s.kind = Step::CASE;
+          s.label = op->name;
+          s.pred = slot_of.at(op->operands[0]);
+          for (auto* r : op->results) {
+            ensure_slot(r, st);
+            s.state.push_back(slot_of.at(r));
+          }
+          for (auto& reg : op->regions) {
+            int a_br = (int)prog.arena_bytes.size();
+            prog.arena_bytes.push_back(0);
+            auto pb = std::make_unique<Plan>();
+            pb->arena = a_br;
+            Op* ret = reg->ops.back().get();
+            plan_block(reg.get(), *pb, a_br, ret->operands);
+            for (size_t k = 0; k < op->results.size(); k++) {
+              int src = slot_of.at(ret->operands[k]);
+              persistent.insert(src);
+              Step c;
+              c.kind = Step::MEMCPY;
+              c.label = "case result";
+              c.args = {s.state[k], src};
+              c.bytes = prog.slots[src].type.bytes();
+              pb->steps.push_back(std::move(c));
+            }
+            s.sub.push_back(std::move(pb));
+          }
+          std::set<int> used;
+          std::function<void(const Plan&)> collect = [&](const Plan& p) {
+            for (auto& q : p.steps) {
+              for (int a : q.args) used.insert(a);
+              for (int a : q.init) used.insert(a);
+              for (auto& sp : q.sub) collect(*sp);
+            }
+          };
+          for (auto& sp : s.sub) collect(*sp);
+          s.args.push_back(s.pred);
+          for (int a : used)
+            if (prog.slots[a].arena == arena && prog.slots[a].kind == Slot::TEMP) s.args.push_back(a);
+          plan.steps.push_back(std::move(s));
+          break;
+        }
+        case Cat::SCATTER: {
+          plan.steps.push_back(lower_scatter(op, st));
+          break;
+        }
         case Cat::TOKEN: {
           ensure_slot(op->results[0], st);
           break;
@@ -1727,6 +1867,8 @@ void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& o
         break;
       case Step::MEMCPY: os << "memcpy " << s.bytes; break;
       case Step::WHILE: os << "while trip=" << s.trip_count; break;
+      case Step::CASE: os << "case branches=" << s.sub.size(); break;
+      case Step::SCATTER: os << "scatter rows=" << s.iparams[0] << " row_elems=" << s.iparams[1] << " updates=" << s.iparams[2]; break;
       case Step::ALL_REDUCE: os << "all_reduce " << s.bytes << " bytes"; break;
       default: os << "step";
     }
@@ -1818,11 +1960,12 @@ std::unique_ptr<CompiledProgram> compile_module(Module& m, const CompileOptions&
       long long n = 0;
       for (auto& s : p.steps) {
         if (s.kind == Step::KERNEL || s.kind == Step::ALL_REDUCE) n += 1;
+        else if (s.kind == Step::SCATTER) n += 2;
         else if (s.kind == Step::IGEMM) n += s.ig.split_k > 1 ? 2 : 1;
         else if (s.kind == Step::WHILE) {
           if (s.trip_count < 0) { dynamic = true; continue; }
           n += (s.trip_count + 1) * count(*s.sub[0]) + s.trip_count * count(*s.sub[1]);
-        }
+        } else if (s.kind == Step::CASE) dynamic = true;
       }
       return n;
     };

@@ -1292,6 +1292,69 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------
+// Row scatter, deterministic: updates are ranked by (row index, update number) with an all-pairs count, then one
+// block per run of equal row indices applies the run's updates in update order, accumulating in fp32 and rounding
+// to the element type once (the same result whatever the launch order). Out-of-range indices are dropped.
+template <typename I>
+__global__ void __launch_bounds__(256) scatter_rank_kernel(const I* __restrict__ idx, int U, long long rows, int* __restrict__ key,
+                                                         int* __restrict__ order) {
+  const int u = blockIdx.x * 256 + threadIdx.x;
+  if (u >= U) return;
+  auto key_of = [&](int v) -> long long {
+    const long long r = (long long)idx[v];
+    return (r < 0 || r >= rows) ? rows : r;            // dropped updates sort to the end
+  };
+  const long long mine = key_of(u);
+  int rank = 0;
+  for (int v = 0; v < U; ++v) {
+    const long long kv = key_of(v);
+    rank += (kv < mine || (kv == mine && v < u)) ? 1 : 0;
+  }
+  order[rank] = u;
+  key[rank] = (int)mine;
+}
+
+__device__ __forceinline__ float scatter_load(const float* p) { return *p; }
+__device__ __forceinline__ float scatter_load(const unsigned short* p) { return __uint_as_float((uint32_t)*p << 16); }
+__device__ __forceinline__ int scatter_load(const int* p) { return *p; }
+__device__ __forceinline__ void scatter_store(float* p, float v) { *p = v; }
+__device__ __forceinline__ void scatter_store(int* p, int v) { *p = v; }
+__device__ __forceinline__ unsigned short bf16_round(float v) {
+  uint32_t u = __float_as_uint(v);
+  if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (unsigned short)((u >> 16) | 0x40);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return (unsigned short)(u >> 16);
+}
+__device__ __forceinline__ void scatter_store(unsigned short* p, float v) { *p = bf16_round(v); }
+
+template <typename T, typename A>
+__global__ void __launch_bounds__(256) scatter_apply_kernel(T* __restrict__ out, const T* __restrict__ upd, const int* __restrict__ key,
+                                                          const int* __restrict__ order, int U, long long rows,
+                                                          long long row_elems, int kind) {
+  const int p = blockIdx.x;
+  const int row = key[p];
+  if (row >= rows || (p > 0 && key[p - 1] == row)) return;      // not the start of a run
+  int end = p + 1;
+  while (end < U && key[end] == row) ++end;
+  for (long long d = (long long)blockIdx.y * 256 + threadIdx.x; d < row_elems; d += 256ll * gridDim.y) {
+    A acc = scatter_load(out + (long long)row * row_elems + d);
+    for (int q = p; q < end; ++q) {
+      const A v = scatter_load(upd + (long long)order[q] * row_elems + d);
+      A r;
+      switch (kind) {
+        case 0: r = v; break;
+        case 1: r = acc + v; break;
+        case 2: r = acc * v; break;
+        case 3: r = (v < acc || v != v) ? v : acc; break;
+        default: r = (v > acc || v != v) ? v : acc; break;
+      }
+      acc = r;
+    }
+    scatter_store(out + (long long)row * row_elems + d, acc);
+  }
+}
+
 }  // namespace
 
 cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B, void* C, const void* const* tables,
@@ -1520,6 +1583,31 @@ cudaError_t matmul_f32_static_scratch(const float* A, const float* B, float* C, 
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   splitk_sum_static_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, stream>>>(scratch, C, mn, splits);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_rows(int elem_kind, int index_bytes, int kind, long long rows, long long row_elems, int updates,
+                                void* out, const void* indices, const void* upd, int* scratch, cudaStream_t stream,
+                                int* launches) {
+  if (updates <= 0 || rows <= 0 || row_elems <= 0) return cudaSuccess;
+  int* key = scratch;
+  int* order = scratch + updates;
+  const unsigned rb = (unsigned)((updates + 255) / 256);
+  if (index_bytes == 8)
+    scatter_rank_kernel<long long><<<rb, 256, 0, stream>>>((const long long*)indices, updates, rows, key, order);
+  else
+    scatter_rank_kernel<int><<<rb, 256, 0, stream>>>((const int*)indices, updates, rows, key, order);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  dim3 grid((unsigned)updates, (unsigned)std::min<long long>(64, (row_elems + 255) / 256));
+  if (elem_kind == 0)
+    scatter_apply_kernel<float, float><<<grid, 256, 0, stream>>>((float*)out, (const float*)upd, key, order, updates, rows, row_elems, kind);
+  else if (elem_kind == 1)
+    scatter_apply_kernel<unsigned short, float><<<grid, 256, 0, stream>>>((unsigned short*)out, (const unsigned short*)upd, key, order,
+                                                                          updates, rows, row_elems, kind);
+  else
+    scatter_apply_kernel<int, int><<<grid, 256, 0, stream>>>((int*)out, (const int*)upd, key, order, updates, rows, row_elems, kind);
+  *launches += 2;
   return cudaGetLastError();
 }
 

@@ -27,6 +27,13 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
 }  // namespace b200
 
 namespace b200 {
+// Row scatter (stablehlo.scatter with one index along dimension 0 and whole-row updates), deterministic.
+// elem_kind: 0 f32, 1 bf16, 2 i32; kind: 0 assign, 1 add, 2 multiply, 3 minimum, 4 maximum. `out` already holds
+// the operand; `scratch` has room for 2 * updates ints.
+cudaError_t launch_scatter_rows(int elem_kind, int index_bytes, int kind, long long rows, long long row_elems, int updates,
+                                void* out, const void* indices, const void* upd, int* scratch, cudaStream_t stream,
+                                int* launches);
+
 // Split-K fp32 product C[M,N] = A[M,K] * B[K,N] (dense row-major device pointers) whose partial sums go to a
 // file-scope device array instead of allocated memory. `*why` explains a refusal. The first call on a device
 // resolves the array's device address (cudaGetSymbolAddress); make it before any stream capture.

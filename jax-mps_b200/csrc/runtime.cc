@@ -603,6 +603,24 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       }
       return nullptr;
     }
+    case Step::SCATTER: {
+      void *operand = x.ptrs[s.args[0]], *out = x.ptrs[s.args[3]];
+      if (operand != out && s.bytes) CUDA_TRY(cudaMemcpyAsync(out, operand, s.bytes, cudaMemcpyDeviceToDevice, st));
+      const int ek = s.dtype == DT::F32 ? 0 : s.dtype == DT::BF16 ? 1 : 2;
+      cudaError_t e = launch_scatter_rows(ek, (int)s.iparams[3], (int)s.iparams[4], s.iparams[0], s.iparams[1], (int)s.iparams[2], out,
+                                          x.ptrs[s.args[1]], x.ptrs[s.args[2]], (int*)x.ptrs[s.args[4]], st, &x.launches);
+      if (e != cudaSuccess) return make_error(B200_INTERNAL, "launch of " + s.label + " failed: " + cudaGetErrorString(e));
+      return nullptr;
+    }
+    case Step::CASE: {
+      int32_t index = 0;
+      CUDA_TRY(cudaMemcpyAsync(c->pred_host, x.ptrs[s.pred], 4, cudaMemcpyDeviceToHost, st));
+      CUDA_TRY(cudaStreamSynchronize(st));
+      memcpy(&index, c->pred_host, 4);
+      const int n = (int)s.sub.size();
+      if (index < 0 || index >= n) index = n - 1;
+      return run_plan(x, *s.sub[index]);
+    }
     default:
       return make_error(B200_UNIMPLEMENTED, "plan step kind not implemented: " + s.label);
   }

@@ -107,3 +107,37 @@ class ResNet18Stepper:
                 self.m[n].mul_(self.mu).add_(g)
                 self.p[n].sub_(self.lr * self.m[n])
         return float(loss)
+
+
+def lstm_train_step(params, xs, targets, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, dtype=None):
+    """PyTorch twin of b200.shlo.programs.lstm_scan_train_step (two stacked LSTM layers in the concatenated
+    form, gate order i, f, g, o; MSE of the last hidden state; first Adam step from zero moments) by autograd.
+    `params` = [w1, b1, w2, b2] as numpy arrays. Returns loss, new params, first moments, second moments."""
+    import numpy as np
+    import torch
+    dtype = dtype or torch.float64
+    P = [torch.tensor(np.asarray(a), dtype=dtype, requires_grad=True) for a in params]
+    xs = torch.tensor(np.asarray(xs), dtype=dtype)
+    tg = torch.tensor(np.asarray(targets), dtype=dtype)
+    B, H = tg.shape
+
+    def cell(x, h, c, w, b):
+        z = torch.cat([x, h], 1) @ w + b
+        i, f, g, o = torch.sigmoid(z[:, :H]), torch.sigmoid(z[:, H:2 * H]), torch.tanh(z[:, 2 * H:3 * H]), torch.sigmoid(z[:, 3 * H:])
+        c2 = f * c + i * g
+        return o * torch.tanh(c2), c2
+
+    h1 = c1 = h2 = c2 = torch.zeros(B, H, dtype=dtype)
+    for t in range(xs.shape[0]):
+        h1, c1 = cell(xs[t], h1, c1, P[0], P[1])
+        h2, c2 = cell(h1, h2, c2, P[2], P[3])
+    loss = ((h2 - tg) ** 2).mean()
+    loss.backward()
+    new_p, ms, vs = [], [], []
+    for p in P:
+        g = p.grad.numpy()
+        m, v = (1 - beta1) * g, (1 - beta2) * g * g
+        new_p.append(p.detach().numpy() - lr * (m / (1 - beta1)) / (np.sqrt(v / (1 - beta2)) + eps))
+        ms.append(m)
+        vs.append(v)
+    return float(loss), new_p, ms, vs

@@ -232,6 +232,17 @@ DOT_CASES = [
 ]
 
 
+def test_bf16_contractions(client):
+    """bf16 dot_general and convolution: bf16 products accumulated in fp32 and rounded once (what a CPU backend
+    computes); compared at bf16 resolution."""
+    b = Builder()
+    x, w = b.arg((96, 160), "bf16"), b.arg((160, 72), "bf16")
+    img, ker = b.arg((4, 12, 12, 32), "bf16"), b.arg((3, 3, 32, 48), "bf16")
+    outs = [b.matmul(x, w), b.dot_general(x, w, ((1,), (0,)), out_dtype="f32"), b.conv(img, ker, padding=((1, 1), (1, 1)))]
+    check(client, b.module(outs), [f32(96, 160), f32(160, 72), f32(4, 12, 12, 32), f32(3, 3, 32, 48)],
+          rtol=1e-2, atol=1e-2, scale_atol=True, dtypes=["bf16"] * 4)
+
+
 @pytest.mark.parametrize("ls,rs,contract,batch", DOT_CASES)
 def test_dot_general(client, ls, rs, contract, batch):
     b = Builder()
@@ -357,6 +368,56 @@ def test_scan_with_dynamic_slices(client):
         return [s.add(t, s.const(1, "i32")), h2, ys2]
     outs = b.while_([b.const(0, "i32"), h0, ys0], cond, body)
     check(client, b.module(outs), [f32(T, N), f32(N)], rtol=2e-5)
+
+
+def test_row_scatter(client):
+    """Row scatter with repeated and out-of-range indices: add in f32 and bf16 (update order, fp32 accumulator),
+    multiply / minimum / maximum / set, i64 indices, and the embedding-gradient form."""
+    rng = np.random.default_rng(3)
+    idx = rng.integers(0, 12, (5, 7)).astype(np.int32)
+    idx[0, 0], idx[1, 1] = 40, -2                      # dropped
+    for dt, tol in [("f32", 1e-6), ("bf16", 1e-2)]:
+        for op in ["add", "multiply", "minimum", "maximum", "set"]:
+            b = Builder()
+            t, i, u = b.arg((12, 3, 10), dt), b.arg((5, 7), "i32"), b.arg((5, 7, 3, 10), dt)
+            if op == "set":                            # duplicates make "set" order-dependent: keep indices unique
+                ii = np.arange(35, dtype=np.int32).reshape(5, 7) % 12
+                ii[2:] = 100
+                args = [f32(12, 3, 10), ii, f32(5, 7, 3, 10)]
+            else:
+                args = [f32(12, 3, 10), idx, f32(5, 7, 3, 10)]
+            check(client, b.module([b.scatter_rows(t, i, u, op)]), args, rtol=tol, atol=tol, dtypes=[dt, None, dt])
+    b = Builder()
+    t, i, u = b.arg((9, 4), "i32"), b.arg((6,), "i64"), b.arg((6, 4), "i32")
+    check(client, b.module([b.scatter_rows(t, i, u, "add")]),
+          [rng.integers(-5, 5, (9, 4)).astype(np.int32), np.array([3, 3, 0, 8, 3, 0], np.int64), rng.integers(-5, 5, (6, 4)).astype(np.int32)])
+    b = Builder()
+    table, ids, g = b.arg((50, 8), "f32"), b.arg((3, 4), "i32"), b.arg((3, 4, 8), "f32")
+    y = b.take_rows(table, ids)
+    (dtab,) = b.grad(b.reduce_sum(b.mul(y, g), (0, 1, 2)), [table])
+    check(client, b.module([y, dtab]), [f32(50, 8), rng.integers(0, 50, (3, 4)).astype(np.int32), f32(3, 4, 8)], rtol=1e-6, atol=1e-6)
+
+
+def test_case_branches(client):
+    """lax.cond / lax.switch lowerings: branches capture outer values; an index outside [0, n) runs the last
+    branch; a case inside a while body."""
+    b = Builder()
+    idx, x, y = b.arg((), "i32"), b.arg((6, 5), "f32"), b.arg((6, 5), "f32")
+    outs = b.case(idx, [lambda s: [s.add(x, y), s.reduce_sum(x, (0,))],
+                        lambda s: [s.mul(x, y), s.reduce_sum(y, (0,))],
+                        lambda s: [s.tanh(s.sub(x, y)), s.reduce_max(x, (0,))]],
+                  [((6, 5), "f32"), ((5,), "f32")])
+    text = b.module([outs[0], b.exp(outs[1])])
+    for i in [0, 1, 2, 7, -3]:
+        check(client, text, [np.int32(i), f32(6, 5), f32(6, 5)])
+    b = Builder()
+    v = b.arg((4,), "f32")
+    def cond(s, i, a): return s.compare(i, s.const(5, "i32"), "LT")
+    def body(s, i, a):
+        r = s.case(s.rem(i, s.const(2, "i32")), [lambda q: [q.add(a, q.full((4,), 1.0, "f32"))],
+                                                  lambda q: [q.mul(a, q.full((4,), 2.0, "f32"))]], [((4,), "f32")])
+        return [s.add(i, s.const(1, "i32")), r[0]]
+    check(client, b.module(b.while_([b.const(0, "i32"), v], cond, body)), [f32(4)])
 
 
 def test_loop_carried_swap(client):

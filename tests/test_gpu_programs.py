@@ -178,3 +178,40 @@ def test_memory_stats_and_device_info(client):
     assert st.bytes_limit_is_set and st.bytes_limit > 100e9
     assert st.peak_bytes_in_use >= st.bytes_in_use >= 0
     assert "B200" in client.device_kind() and client.platform == "b200"
+
+
+GEMMA_TINY = dict(vocab=384, dim=64, layers=2, heads=4, head_dim=16, hidden=128, prompt_len=5, new_tokens=6, cache_len=16)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", [0, 1])
+def test_gemma_shaped_greedy_decode_matches_oracle(client, seed):
+    """Prompt consumption and greedy generation inside one stablehlo.while: bf16 weights, key-value caches
+    updated by dynamic_update_slice, rotary embedding, softmax in f32, argmax over the tied-embedding logits.
+    Token ids must be identical; the last logits agree at bf16 resolution."""
+    prog = programs.gemma_greedy_decode(**GEMMA_TINY)
+    args = programs.gemma_inputs(prog, seed=seed, weight_std=0.3)
+    dtypes = [d for _, _, d in prog.args]
+    got, exe = run_gpu(client, prog.text, args, dtypes)
+    want = interp.run_text(prog.text, args)
+    total = GEMMA_TINY["prompt_len"] + GEMMA_TINY["new_tokens"]
+    assert got[0].shape == (total,) and list(got[0][:5]) == list(args[-1])
+    np.testing.assert_array_equal(got[0], want[0])
+    compare(got[1], want[1], rtol=2e-2, atol=2e-2, what="last logits", scale_atol=True)
+    assert "while trip=11" in exe.plan_text()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("steps,batch,in_dim,hidden", [(6, 4, 8, 16), (12, 8, 32, 64)])
+def test_lstm_scan_train_step_matches_oracle(client, steps, batch, in_dim, hidden):
+    """LSTM by scan: two counted stablehlo.while loops (forward with stacked carries, reverse with per-step
+    recomputation and gradient accumulation) and an Adam update; every result against the oracle."""
+    prog = programs.lstm_scan_train_step(steps=steps, batch=batch, in_dim=in_dim, hidden=hidden)
+    args = programs.lstm_inputs(prog, seed=1)
+    got, exe = run_gpu(client, prog.text, args)
+    want = interp.run_text(prog.text, args, wide=True)
+    assert exe.plan_text().count(f"while trip={steps}") == 2
+    for (name, _, _), g, w in zip(prog.results, got, want):
+        # second moments are squares of gradients: compare them relative to their own scale
+        scale = float(np.max(np.abs(w))) or 1.0
+        np.testing.assert_allclose(g, w, rtol=2e-4, atol=2e-5 * scale, err_msg=name)

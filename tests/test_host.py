@@ -131,3 +131,19 @@ module @m attributes {mhlo.num_partitions = 1 : i32} { func.func public @main(%a
 } }"""
     plan, _ = b200.compile_to_plan(text)
     assert plan.count("kernel ") == 1
+
+
+def test_lstm_scan_program_matches_autograd_twin():
+    """The LSTM-by-scan training step (forward while, reverse while with per-step recomputation, Adam) run in
+    the float64 oracle against PyTorch autograd on the same weights: pins the program the GPU tests execute."""
+    from b200.shlo import programs
+    from oracle import interp, twins
+    prog = programs.lstm_scan_train_step(steps=6, batch=4, in_dim=5, hidden=8)
+    args = programs.lstm_inputs(prog, seed=2)
+    outs = interp.run_text(prog.text, args, wide=True)
+    loss, new_p, ms, vs = twins.lstm_train_step(args[:4], args[-2], args[-1])
+    assert abs(float(outs[0]) - loss) < 1e-9
+    for k in range(4):
+        np.testing.assert_allclose(outs[1 + k], new_p[k], rtol=1e-6, atol=1e-9)
+        np.testing.assert_allclose(outs[5 + k], ms[k], rtol=1e-6, atol=1e-12)
+        np.testing.assert_allclose(outs[9 + k], vs[k], rtol=1e-6, atol=1e-15)
