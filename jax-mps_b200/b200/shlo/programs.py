@@ -447,3 +447,110 @@ def lstm_inputs(prog: Program, seed: int = 0) -> list:
         else:
             out.append(np.zeros(s, np.float32))
     return out
+
+
+# --------------------------------------------------------------------------
+# DistilBERT-shaped masked-language-model step (forward + backward)
+# --------------------------------------------------------------------------
+
+def distilbert_param_spec(vocab: int, max_pos: int, dim: int, layers: int, ffn: int):
+    """Leaves per examples/distilbert/model.py:11-94: word and position embeddings with their LayerNorm, per layer
+    q/k/v/out projections, two LayerNorms and the two feed-forward matrices, then the MLM head (transform,
+    LayerNorm, output bias; the projector is tied to the word embedding)."""
+    spec = [("word_emb", (vocab, dim)), ("pos_emb", (max_pos, dim)), ("emb_ln.scale", (dim,)), ("emb_ln.bias", (dim,))]
+    for i in range(layers):
+        p = f"layer{i}."
+        for n in ("q", "k", "v", "o"):
+            spec += [(p + n + ".w", (dim, dim)), (p + n + ".b", (dim,))]
+        spec += [(p + "attn_ln.scale", (dim,)), (p + "attn_ln.bias", (dim,)), (p + "ff1.w", (dim, ffn)), (p + "ff1.b", (ffn,)),
+                 (p + "ff2.w", (ffn, dim)), (p + "ff2.b", (dim,)), (p + "out_ln.scale", (dim,)), (p + "out_ln.bias", (dim,))]
+    spec += [("head.w", (dim, dim)), ("head.b", (dim,)), ("head_ln.scale", (dim,)), ("head_ln.bias", (dim,)), ("vocab_bias", (vocab,))]
+    return spec
+
+
+def distilbert_mlm_step(batch: int = 32, seq: int = 128, vocab: int = 30522, dim: int = 768, layers: int = 6, heads: int = 12,
+                        ffn: int = 3072, dtype: str = "bf16") -> Program:
+    """Loss and the gradient of every leaf for one masked-language-model batch. Weights and activations are
+    `dtype`; LayerNorm, softmax and the log-softmax of the logits compute in f32. Arguments: the leaves, ids
+    i32[batch,seq], weights f32[batch,seq] (1 at masked positions). Labels are the ids themselves. Results: loss f32
+    and one gradient per leaf (in the leaf's dtype). The embedding gradient is a row scatter-add."""
+    spec = distilbert_param_spec(vocab, seq, dim, layers, ffn)
+    b = Builder()
+    W = {n: b.arg(s, dtype) for n, s in spec}
+    ids = b.arg((batch, seq), "i32")
+    mask_w = b.arg((batch, seq), "f32")
+    N, hd = batch * seq, dim // heads
+
+    def layer_norm(x, scale, bias):                       # x dtype[N, dim] -> dtype[N, dim], f32 statistics
+        xf = b.convert(x, "f32")
+        mu = b.mean(xf, (1,))
+        xc = b.sub(xf, b.bcast(mu, xf.shape, (0,)))
+        var = b.mean(b.mul(xc, xc), (1,))
+        inv = b.rsqrt(b.add(var, b.full(var.shape, 1e-12, "f32")))
+        y = b.mul(xc, b.bcast(inv, xf.shape, (0,)))
+        y = b.add(b.mul(y, b.bcast(b.convert(scale, "f32"), xf.shape, (1,))), b.bcast(b.convert(bias, "f32"), xf.shape, (1,)))
+        return b.convert(y, dtype)
+
+    def linear(x, w, bias):
+        y = b.matmul(x, w)
+        return b.add(y, b.bcast(bias, y.shape, (1,)))
+
+    def gelu(x):
+        xf = b.convert(x, "f32")
+        c = b.full(xf.shape, math.sqrt(2.0 / math.pi), "f32")
+        inner = b.mul(c, b.add(xf, b.mul(b.full(xf.shape, 0.044715, "f32"), b.mul(xf, b.mul(xf, xf)))))
+        y = b.mul(b.mul(xf, b.full(xf.shape, 0.5, "f32")), b.add(b.full(xf.shape, 1.0, "f32"), b.tanh(inner)))
+        return b.convert(y, dtype)
+
+    x = b.take_rows(W["word_emb"], b.reshape(ids, (N,)))                                   # [N, dim]
+    pos = b.reshape(b.bcast(W["pos_emb"], (batch, seq, dim), (1, 2)), (N, dim))
+    x = layer_norm(b.add(x, pos), W["emb_ln.scale"], W["emb_ln.bias"])
+    for i in range(layers):
+        p = f"layer{i}."
+        def split(t):                                     # [N, dim] -> [batch, heads, seq, hd]
+            return b.transpose(b.reshape(t, (batch, seq, heads, hd)), (0, 2, 1, 3))
+        q, k, v = (split(linear(x, W[p + n + ".w"], W[p + n + ".b"])) for n in ("q", "k", "v"))
+        sc = b.convert(b.dot_general(q, k, ((3,), (3,)), ((0, 1), (0, 1))), "f32")          # [batch, heads, seq, seq]
+        sc = b.mul(sc, b.full(sc.shape, 1.0 / math.sqrt(hd), "f32"))
+        m = b.stop_gradient(b.reduce_max(sc, (3,)))
+        e = b.exp(b.sub(sc, b.bcast(m, sc.shape, (0, 1, 2))))
+        pr = b.convert(b.div(e, b.bcast(b.reduce_sum(e, (3,)), sc.shape, (0, 1, 2))), dtype)
+        ctx = b.dot_general(pr, v, ((3,), (2,)), ((0, 1), (0, 1)))                            # [batch, heads, seq, hd]
+        ctx = b.reshape(b.transpose(ctx, (0, 2, 1, 3)), (N, dim))
+        x = layer_norm(b.add(x, linear(ctx, W[p + "o.w"], W[p + "o.b"])), W[p + "attn_ln.scale"], W[p + "attn_ln.bias"])
+        ff = linear(gelu(linear(x, W[p + "ff1.w"], W[p + "ff1.b"])), W[p + "ff2.w"], W[p + "ff2.b"])
+        x = layer_norm(b.add(x, ff), W[p + "out_ln.scale"], W[p + "out_ln.bias"])
+    h = layer_norm(gelu(linear(x, W["head.w"], W["head.b"])), W["head_ln.scale"], W["head_ln.bias"])
+    logits = b.convert(b.dot_general(h, W["word_emb"], ((1,), (1,))), "f32")                 # [N, vocab], tied projector
+    logits = b.add(logits, b.bcast(b.convert(W["vocab_bias"], "f32"), logits.shape, (1,)))
+    mx = b.stop_gradient(b.reduce_max(logits, (1,)))
+    sh = b.sub(logits, b.bcast(mx, logits.shape, (0,)))
+    lse = b.log(b.reduce_sum(b.exp(sh), (1,)))
+    picked = b.take_along_last(sh, b.reshape(ids, (N,)))
+    nll = b.sub(lse, picked)                                                                 # [N]
+    wv = b.reshape(mask_w, (N,))
+    denom = b.max(b.reduce_sum(wv, (0,)), b.const(1.0, "f32"))
+    loss = b.div(b.reduce_sum(b.mul(nll, wv), (0,)), denom)
+    grads = b.grad(loss, [W[n] for n, _ in spec])
+    text = b.module([loss, *grads], name="jit_mlm_step")
+    args = [(n, s, dtype) for n, s in spec] + [("ids", (batch, seq), "i32"), ("mask", (batch, seq), "f32")]
+    res = [("loss", (), "f32")] + [("g." + n, s, dtype) for n, s in spec]
+    return Program("distilbert_mlm_step", text, args, res, 1, {"vocab": vocab, "batch": batch, "seq": seq, "dim": dim})
+
+
+def distilbert_inputs(prog: Program, seed: int = 0, weight_std: float = 0.02, mask_rate: float = 0.15) -> list:
+    """Weights ~N(0, weight_std), LayerNorm scale 1 / bias 0, ids uniform over the vocabulary, mask Bernoulli."""
+    rng = np.random.default_rng(seed)
+    out = []
+    for n, s, d in prog.args:
+        if n == "ids":
+            out.append(rng.integers(0, prog.meta["vocab"], s).astype(np.int32))
+        elif n == "mask":
+            out.append((rng.random(s) < mask_rate).astype(np.float32))
+        elif n.endswith("ln.scale"):
+            out.append(np.ones(s, np.float32))
+        elif n.endswith(".bias") or n.endswith(".b") or n == "vocab_bias":
+            out.append(np.zeros(s, np.float32))
+        else:
+            out.append((rng.standard_normal(s) * weight_std).astype(np.float32))
+    return out

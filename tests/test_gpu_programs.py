@@ -215,3 +215,26 @@ def test_lstm_scan_train_step_matches_oracle(client, steps, batch, in_dim, hidde
         # second moments are squares of gradients: compare them relative to their own scale
         scale = float(np.max(np.abs(w))) or 1.0
         np.testing.assert_allclose(g, w, rtol=2e-4, atol=2e-5 * scale, err_msg=name)
+
+
+BERT_TINY = dict(batch=2, seq=16, vocab=160, dim=64, layers=2, heads=4, ffn=128)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,rtol,atol", [("f32", 2e-4, 2e-5), ("bf16", 3e-2, 3e-2)])
+def test_distilbert_shaped_mlm_step_matches_oracle(client, dtype, rtol, atol):
+    """Embedding gather, attention with batched dot_general, LayerNorm / softmax in f32, tied-projector logits,
+    label pick by gather, and the gradient of every leaf (the embedding gradient is a row scatter-add)."""
+    prog = programs.distilbert_mlm_step(**BERT_TINY, dtype=dtype)
+    args = programs.distilbert_inputs(prog, seed=3, weight_std=0.1, mask_rate=0.3)
+    dtypes = [d for _, _, d in prog.args]
+    got, exe = run_gpu(client, prog.text, args, dtypes)
+    want = interp.run_text(prog.text, args)
+    assert "scatter rows=160" in exe.plan_text()
+    assert abs(float(got[0]) - float(want[0])) < (1e-4 if dtype == "f32" else 3e-2) * abs(float(want[0]))
+    # the key-bias gradients are zero in exact arithmetic (softmax is invariant to a shift of all keys): leaves are
+    # held to their own scale, but never below a thousandth (bf16: a hundredth) of the largest gradient of the step
+    top = max(float(np.max(np.abs(w))) for w in want[1:])
+    for (name, _, _), g, w in zip(prog.results[1:], got[1:], want[1:]):
+        scale = max(float(np.max(np.abs(w))), (1e-3 if dtype == "f32" else 1e-2) * top)
+        np.testing.assert_allclose(np.asarray(g, np.float64), np.asarray(w, np.float64), rtol=rtol, atol=atol * scale, err_msg=name)

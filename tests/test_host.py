@@ -147,3 +147,23 @@ def test_lstm_scan_program_matches_autograd_twin():
         np.testing.assert_allclose(outs[1 + k], new_p[k], rtol=1e-6, atol=1e-9)
         np.testing.assert_allclose(outs[5 + k], ms[k], rtol=1e-6, atol=1e-12)
         np.testing.assert_allclose(outs[9 + k], vs[k], rtol=1e-6, atol=1e-15)
+
+
+def test_distilbert_program_gradients_match_finite_differences():
+    """The DistilBERT-shaped masked-language-model step in f32, run in the float64 oracle: the program's
+    gradients against central differences of its own loss on a few leaves of every kind."""
+    from b200.shlo import programs
+    from oracle import interp
+    prog = programs.distilbert_mlm_step(batch=2, seq=8, vocab=96, dim=32, layers=2, heads=4, ffn=64, dtype="f32")
+    args = [a.astype(np.float64) if a.dtype == np.float32 else a for a in programs.distilbert_inputs(prog, weight_std=0.1, mask_rate=0.4)]
+    outs = interp.run_text(prog.text, args, wide=True)
+    names = [n for n, _, _ in prog.args]
+    for nm in ["word_emb", "pos_emb", "layer0.q.w", "layer1.ff2.b", "head_ln.scale", "vocab_bias"]:
+        k = names.index(nm)
+        idx = tuple(np.unravel_index(3, args[k].shape))
+        h = 1e-5
+        up, dn = [x.copy() for x in args], [x.copy() for x in args]
+        up[k][idx] += h
+        dn[k][idx] -= h
+        fd = (float(interp.run_text(prog.text, up, wide=True)[0]) - float(interp.run_text(prog.text, dn, wide=True)[0])) / (2 * h)
+        assert abs(fd - float(outs[1 + k][idx])) < 1e-6 * max(1.0, abs(fd)), nm
