@@ -607,7 +607,7 @@ struct WsCfg {
   static constexpr int STAGES = BN_ == 64 ? 4 : 3;
   static constexpr int A_BYTES = TBM * TBK * 4, B_BYTES = BN_ * TBK * 4;
   static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);          // raw A, raw B, low A, low B
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 512;
   static constexpr int A_CHUNKS = TBM * TBK / 4, B_CHUNKS = BN_ * TBK / 4;
 };
 // role sizes: chunk gather 512 + 256 low-part threads, segment gather 256 + 512; one more warp issues the MMAs
@@ -711,7 +711,8 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
   uint64_t* landed = (uint64_t*)(smem + S * Cfg::STAGE_BYTES);
   uint64_t* ready = landed + S;
   uint64_t* empty = ready + S;
-  uint32_t* tmem_slot = (uint32_t*)(empty + S);
+  uint64_t* done = empty + S;                      // completes once, when every MMA of the CTA has retired
+  uint32_t* tmem_slot = (uint32_t*)(done + 1);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -728,6 +729,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
       mbar_init(smem_u32(&ready[s]), WS_LOW);
       mbar_init(smem_u32(&empty[s]), 1);
     }
+    mbar_init(smem_u32(done), 1);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -979,11 +981,16 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
       }
       __syncwarp();
     }
+    // the read-back warps may be several k-tiles ahead of the MMAs, so they wait on a barrier of its own that a
+    // last commit completes exactly once (a parity wait on a stage barrier is only unambiguous within one phase)
+    if (elect_one())
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(done)) : "memory");
+    __syncwarp();
   }
 
   if (warp < 8)
     store_accumulator<BN>(tmem, warp, lane, m0, n0, g, sp, ktiles, p, C, partial, c_row, c_col, c_grp, failed,
-                          smem_u32(&empty[(ktiles > 0 ? ktiles - 1 : 0) % S]), (uint32_t)(((ktiles > 0 ? ktiles - 1 : 0) / S) & 1));
+                          smem_u32(done), 0u);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (tid == 0 && *failed) atomicExch(error_flag, 1);
@@ -1000,14 +1007,14 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
 // registers of one thread per row -> tensor memory, as a high tile (the raw words: the tensor core reads their
 // TF32 bits) and a low tile (x - tf32(x)), and tcgen05.mma takes it from there; per k-tile the shared memory
 // moves 16 KB + 16 KB for A and (8 + 16 + 24) KB for a 64-wide B instead of 144 KB.
-//   warps 0-3   gather A: lane l owns row l of the warp's 32 tile rows (address + padding mask once per row and
-//               k-tile), copies go out four rows per instruction, eight lanes per row (128-byte cp.async.bulk
-//               copies per row were tried and ran 1.6 times slower)
-//   warps 4-7   gather B the same way
-//   warps 8-15  two groups of four warps alternate k-tiles: thread = one row m of the tile; reads its 32 values
+//   warps 0-7   gather A, two groups of four warps alternating k-tiles: lane l owns row l of the warp's 32 tile
+//               rows (address + padding mask once per row and k-tile), copies go out four rows per instruction,
+//               eight lanes per row (128-byte cp.async.bulk copies per row were tried and ran 1.6 times slower)
+//   warps 8-11  gather B the same way, every k-tile
+//   warps 12-19 two groups of four warps alternate k-tiles: thread = one row m of the tile; reads its 32 values
 //               (K-major rows: eight 16-byte reads from the swizzled row; MN-major: 32 words, one per k),
 //               tcgen05.st of the high and the low words into the stage's 64 tensor-memory columns
-//   warps 16-23 low part of the B tile in shared memory
+//   warps 20-23 low part of the B tile in shared memory
 //   warp 24     one thread issues the 12 MMAs of a k-tile (A hi x B raw, A hi x B lo, A lo x B raw per k-step)
 //               and commits them to the stage's `empty` barrier
 // Tensor memory: all 512 columns; accumulator in [0, BN), A ring from column 128 (64 columns per stage).
@@ -1018,7 +1025,7 @@ struct TaCfg {
   static constexpr int STAGES = BN_ == 64 ? 6 : 4;
   static constexpr int A_BYTES = TBM * TBK * 4, B_BYTES = BN_ * TBK * 4;
   static constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;            // raw A, raw B, low B
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 512;
   static constexpr int B_CHUNKS = BN_ * TBK / 4;
   static constexpr int A_COL0 = 128;                                   // 64 columns per stage: 128 + 6 * 64 = 512
 };
@@ -1061,7 +1068,8 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
   uint64_t* a_ready = landed_b + S;
   uint64_t* b_ready = a_ready + S;
   uint64_t* empty = b_ready + S;
-  uint32_t* tmem_slot = (uint32_t*)(empty + S);
+  uint64_t* done = empty + S;                      // completes once, when every MMA of the CTA has retired
+  uint32_t* tmem_slot = (uint32_t*)(done + 1);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -1077,9 +1085,10 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
       mbar_init(smem_u32(&landed_a[s]), 128);
       mbar_init(smem_u32(&landed_b[s]), 128);
       mbar_init(smem_u32(&a_ready[s]), 128);
-      mbar_init(smem_u32(&b_ready[s]), 256);
+      mbar_init(smem_u32(&b_ready[s]), 128);
       mbar_init(smem_u32(&empty[s]), 1);
     }
+    mbar_init(smem_u32(done), 1);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -1102,13 +1111,15 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
   };
   auto lo1_safe = [&](float x) -> float { return fabsf(x) == INFINITY ? 0.f : lo1(x); };
 
-  if (warp < 8) {
+  if (warp < 12) {
     // ------------------------------ gather -----------------------------------------------------------------
+    // warps 0-3 and 4-7: two groups that take the A tiles of even and odd k-tiles; warps 8-11: every B tile
     const int a_sh = (int)p.a_sh, a_sw = (int)p.a_sw;
-    const bool is_a = warp < 4;
+    const bool is_a = warp < 8;
+    const int first = is_a ? (warp >> 2) : 0, stride = is_a ? 2 : 1;     // k-tiles first, first + stride, ...
     constexpr int B_ROWS = BN / 4;                   // rows per B warp
     const int rows = is_a ? 32 : B_ROWS;
-    const int u = is_a ? warp * 32 + lane : (warp - 4) * B_ROWS + (lane % B_ROWS);   // tile row owned by this lane
+    const int u = is_a ? (warp & 3) * 32 + lane : (warp - 8) * B_ROWS + (lane % B_ROWS);   // tile row owned by this lane
     int k_local = 0;                                 // MN-major rows sit at their own k inside the tile
     uint32_t x_off;                                  // byte offset of the row in the stage (swizzle key folded in)
     int base_off = -1, h0 = 0, w0 = 0;               // m- or n-dependent part of the address (-1: out of range)
@@ -1175,20 +1186,20 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
       return true;
     };
     Ent e0, e1;
-    fetch(0, e0);
-    fetch(1, e1);
-    for (int j = 0; j < ktiles; j += 2) {
+    fetch(first, e0);
+    fetch(first + stride, e1);
+    for (int j = first; j < ktiles; j += 2 * stride) {
       if (!tile(j, e0)) break;
-      fetch(j + 2, e0);
-      if (j + 1 < ktiles) {
-        if (!tile(j + 1, e1)) break;
-        fetch(j + 3, e1);
+      fetch(j + 2 * stride, e0);
+      if (j + stride < ktiles) {
+        if (!tile(j + stride, e1)) break;
+        fetch(j + 3 * stride, e1);
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
-  } else if (warp < 16) {
+  } else if (warp < 20) {
     // ------------------------------ A: shared memory -> registers -> tensor memory ---------------------------
-    const int grp = (warp - 8) >> 2, quad = warp & 3;
+    const int grp = (warp - 12) >> 2, quad = warp & 3;
     const int row = 32 * quad + lane;
     for (int j = grp; j < ktiles; j += 2) {
       const int s = j % S;
@@ -1225,18 +1236,18 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
     }
   } else if (warp < 24) {
     // ------------------------------ low part of B ------------------------------------------------------------
-    const int t = tid - 512;
+    const int t = tid - 640;
     for (int j = 0; j < ktiles; ++j) {
       const int s = j % S;
       if (*failed || !mbar_wait(smem_u32(&landed_b[s]), (uint32_t)((j / S) & 1))) { *failed = 1; break; }
       uint8_t* raw = smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES;
       uint8_t* low = raw + Cfg::B_BYTES;
-      constexpr int NQ = Cfg::B_CHUNKS / 256;
+      constexpr int NQ = Cfg::B_CHUNKS / 128;
       float mx = 0.f;
       float4 v[NQ];
 #pragma unroll
       for (int q = 0; q < NQ; ++q) {
-        v[q] = *reinterpret_cast<const float4*>(raw + (uint32_t)(t + q * 256) * 16u);
+        v[q] = *reinterpret_cast<const float4*>(raw + (uint32_t)(t + q * 128) * 16u);
         mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v[q].x), fabsf(v[q].y))), fmaxf(fabsf(v[q].z), fabsf(v[q].w)));
       }
       const bool special = mx == INFINITY;
@@ -1245,7 +1256,7 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
         float4 l;
         if (special) l = make_float4(lo1_safe(v[q].x), lo1_safe(v[q].y), lo1_safe(v[q].z), lo1_safe(v[q].w));
         else l = make_float4(lo1(v[q].x), lo1(v[q].y), lo1(v[q].z), lo1(v[q].w));
-        *reinterpret_cast<float4*>(low + (uint32_t)(t + q * 256) * 16u) = l;
+        *reinterpret_cast<float4*>(low + (uint32_t)(t + q * 128) * 16u) = l;
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(smem_u32(&b_ready[s]));
@@ -1279,11 +1290,16 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
       }
       __syncwarp();
     }
+    // The read-back warps may reach their wait several k-tiles early, so they cannot use a stage barrier (a
+    // parity wait is only unambiguous within one phase): a last commit completes `done` exactly once.
+    if (elect_one())
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(done)) : "memory");
+    __syncwarp();
   }
 
-  if (warp >= 8 && warp < 16)
-    store_accumulator<BN>(tmem, warp - 8, lane, m0, n0, g, sp, ktiles, p, C, partial, c_row, c_col, c_grp, failed,
-                          smem_u32(&empty[(ktiles > 0 ? ktiles - 1 : 0) % S]), (uint32_t)(((ktiles > 0 ? ktiles - 1 : 0) / S) & 1));
+  if (warp >= 12 && warp < 20)
+    store_accumulator<BN>(tmem, warp - 12, lane, m0, n0, g, sp, ktiles, p, C, partial, c_row, c_col, c_grp, failed,
+                          smem_u32(done), 0u);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (tid == 0 && *failed) atomicExch(error_flag, 1);

@@ -232,6 +232,18 @@ DOT_CASES = [
 ]
 
 
+def test_contraction_results_are_reproducible(client):
+    """Run-to-run bit equality on a split-K convolution with many k-tiles per CTA (the shape on which reading the
+    accumulator before the last MMAs had retired once showed up as sporadic errors in single output tiles)."""
+    b = Builder()
+    x, w = b.arg((128, 4, 4, 512), "f32"), b.arg((3, 3, 512, 512), "f32")
+    exe = client.compile(b.module([b.conv(x, w, padding=((1, 1), (1, 1)))]))
+    bufs = [client.buffer_from_host(f32(128, 4, 4, 512)), client.buffer_from_host(f32(3, 3, 512, 512))]
+    ref = exe.execute(bufs)[0].to_numpy()
+    for _ in range(12):
+        np.testing.assert_array_equal(exe.execute(bufs)[0].to_numpy(), ref)
+
+
 def test_bf16_contractions(client):
     """bf16 dot_general and convolution: bf16 products accumulated in fp32 and rounded once (what a CPU backend
     computes); compared at bf16 resolution."""
