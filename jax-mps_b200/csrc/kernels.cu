@@ -1007,14 +1007,15 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
 // registers of one thread per row -> tensor memory, as a high tile (the raw words: the tensor core reads their
 // TF32 bits) and a low tile (x - tf32(x)), and tcgen05.mma takes it from there; per k-tile the shared memory
 // moves 16 KB + 16 KB for A and (8 + 16 + 24) KB for a 64-wide B instead of 144 KB.
-//   warps 0-7   gather A, two groups of four warps alternating k-tiles: lane l owns row l of the warp's 32 tile
-//               rows (address + padding mask once per row and k-tile), copies go out four rows per instruction,
-//               eight lanes per row (128-byte cp.async.bulk copies per row were tried and ran 1.6 times slower)
-//   warps 8-11  gather B the same way, every k-tile
-//   warps 12-19 two groups of four warps alternate k-tiles: thread = one row m of the tile; reads its 32 values
-//               (K-major rows: eight 16-byte reads from the swizzled row; MN-major: 32 words, one per k),
+// Roles, 64-wide tile (128-wide tile in brackets):
+//   warps 0-7 [0-3]    gather A, two groups of four warps alternating k-tiles [one group]: lane l owns row l of the
+//               warp's 32 tile rows (address + padding mask once per row and k-tile), copies go out four rows per
+//               instruction, eight lanes per row (128-byte cp.async.bulk row copies were tried: 1.6 times slower)
+//   warps 8-11 [4-7]   gather B the same way, every k-tile
+//   warps 12-19 [8-15] two groups of four warps alternate k-tiles: thread = one row m of the tile; reads its 32
+//               values (K-major rows: eight 16-byte reads from the swizzled row; MN-major: 32 words, one per k),
 //               tcgen05.st of the high and the low words into the stage's 64 tensor-memory columns
-//   warps 20-23 low part of the B tile in shared memory
+//   warps 20-23 [16-23] low part of the B tile in shared memory
 //   warp 24     one thread issues the 12 MMAs of a k-tile (A hi x B raw, A hi x B lo, A lo x B raw per k-step)
 //               and commits them to the stage's `empty` barrier
 // Tensor memory: all 512 columns; accumulator in [0, BN), A ring from column 128 (64 columns per stage).
@@ -1079,13 +1080,17 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
   const int kbeg = sp * kchunk, kend = min(p.K, kbeg + kchunk);
   const int ktiles = kend > kbeg ? (kend - kbeg + TBK - 1) / TBK : 0;
   constexpr int MMA_WARP = 24;
+  // warp roles: A gather (one group of four warps, or two groups alternating k-tiles for the 64-wide tile, where
+  // A is two thirds of the gather work), B gather, A converters, low part of B (the warps that remain)
+  constexpr int A_GROUPS = BN == 64 ? 2 : 1;
+  constexpr int W_B = 4 * A_GROUPS, W_CONV = W_B + 4, W_LOW = W_CONV + 8, N_LOW = (MMA_WARP - W_LOW) * 32;
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&landed_a[s]), 128);
       mbar_init(smem_u32(&landed_b[s]), 128);
       mbar_init(smem_u32(&a_ready[s]), 128);
-      mbar_init(smem_u32(&b_ready[s]), 128);
+      mbar_init(smem_u32(&b_ready[s]), N_LOW);
       mbar_init(smem_u32(&empty[s]), 1);
     }
     mbar_init(smem_u32(done), 1);
@@ -1111,15 +1116,15 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
   };
   auto lo1_safe = [&](float x) -> float { return fabsf(x) == INFINITY ? 0.f : lo1(x); };
 
-  if (warp < 12) {
+  if (warp < W_CONV) {
     // ------------------------------ gather -----------------------------------------------------------------
-    // warps 0-3 and 4-7: two groups that take the A tiles of even and odd k-tiles; warps 8-11: every B tile
+    // A groups take the A tiles of k-tiles group, group + A_GROUPS, ...; the B warps take every B tile
     const int a_sh = (int)p.a_sh, a_sw = (int)p.a_sw;
-    const bool is_a = warp < 8;
-    const int first = is_a ? (warp >> 2) : 0, stride = is_a ? 2 : 1;     // k-tiles first, first + stride, ...
+    const bool is_a = warp < W_B;
+    const int first = is_a ? (warp >> 2) : 0, stride = is_a ? A_GROUPS : 1;     // k-tiles first, first + stride, ...
     constexpr int B_ROWS = BN / 4;                   // rows per B warp
     const int rows = is_a ? 32 : B_ROWS;
-    const int u = is_a ? (warp & 3) * 32 + lane : (warp - 8) * B_ROWS + (lane % B_ROWS);   // tile row owned by this lane
+    const int u = is_a ? (warp & 3) * 32 + lane : (warp - W_B) * B_ROWS + (lane % B_ROWS);   // tile row owned by this lane
     int k_local = 0;                                 // MN-major rows sit at their own k inside the tile
     uint32_t x_off;                                  // byte offset of the row in the stage (swizzle key folded in)
     int base_off = -1, h0 = 0, w0 = 0;               // m- or n-dependent part of the address (-1: out of range)
@@ -1197,9 +1202,9 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
-  } else if (warp < 20) {
+  } else if (warp < W_LOW) {
     // ------------------------------ A: shared memory -> registers -> tensor memory ---------------------------
-    const int grp = (warp - 12) >> 2, quad = warp & 3;
+    const int grp = (warp - W_CONV) >> 2, quad = warp & 3;
     const int row = 32 * quad + lane;
     for (int j = grp; j < ktiles; j += 2) {
       const int s = j % S;
@@ -1236,18 +1241,18 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
     }
   } else if (warp < 24) {
     // ------------------------------ low part of B ------------------------------------------------------------
-    const int t = tid - 640;
+    const int t = tid - W_LOW * 32;
     for (int j = 0; j < ktiles; ++j) {
       const int s = j % S;
       if (*failed || !mbar_wait(smem_u32(&landed_b[s]), (uint32_t)((j / S) & 1))) { *failed = 1; break; }
       uint8_t* raw = smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES;
       uint8_t* low = raw + Cfg::B_BYTES;
-      constexpr int NQ = Cfg::B_CHUNKS / 128;
+      constexpr int NQ = Cfg::B_CHUNKS / N_LOW;
       float mx = 0.f;
       float4 v[NQ];
 #pragma unroll
       for (int q = 0; q < NQ; ++q) {
-        v[q] = *reinterpret_cast<const float4*>(raw + (uint32_t)(t + q * 128) * 16u);
+        v[q] = *reinterpret_cast<const float4*>(raw + (uint32_t)(t + q * N_LOW) * 16u);
         mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v[q].x), fabsf(v[q].y))), fmaxf(fabsf(v[q].z), fabsf(v[q].w)));
       }
       const bool special = mx == INFINITY;
@@ -1256,7 +1261,7 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
         float4 l;
         if (special) l = make_float4(lo1_safe(v[q].x), lo1_safe(v[q].y), lo1_safe(v[q].z), lo1_safe(v[q].w));
         else l = make_float4(lo1(v[q].x), lo1(v[q].y), lo1(v[q].z), lo1(v[q].w));
-        *reinterpret_cast<float4*>(low + (uint32_t)(t + q * 128) * 16u) = l;
+        *reinterpret_cast<float4*>(low + (uint32_t)(t + q * N_LOW) * 16u) = l;
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(smem_u32(&b_ready[s]));
@@ -1297,8 +1302,8 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
     __syncwarp();
   }
 
-  if (warp >= 12 && warp < 20)
-    store_accumulator<BN>(tmem, warp - 12, lane, m0, n0, g, sp, ktiles, p, C, partial, c_row, c_col, c_grp, failed,
+  if (warp >= W_CONV && warp < W_LOW)
+    store_accumulator<BN>(tmem, warp - W_CONV, lane, m0, n0, g, sp, ktiles, p, C, partial, c_row, c_col, c_grp, failed,
                           smem_u32(done), 0u);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
