@@ -910,12 +910,15 @@ struct Planner {
     const int bn = p.N >= 128 ? 128 : 64;
     const long long tiles = (long long)((p.M + 127) / 128) * ((p.N + bn - 1) / bn) * p.groups;
     const long long ktiles = (p.K + 31) / 32;
-    const double tile_us = bn == 128 ? 0.9 : 0.6;
+    // the scalar-gather kernel (operands without 16-byte structure) spends about 10 us per k-tile and runs two
+    // CTAs per SM; the row-gather kernels one CTA per SM
+    const double tile_us = !p.vec ? 10.0 : (bn == 128 ? 0.9 : 0.6);
+    const long long per_wave = p.vec ? 148 : 296;
     int best = 1;
     double best_cost = 1e30;
-    const int max_split = (int)std::min<long long>(296, std::max<long long>(1, ktiles / 8));
+    const int max_split = (int)std::min<long long>(592, std::max<long long>(1, ktiles / 8));
     for (int split = 1; split <= max_split; split++) {
-      const long long waves = (tiles * split + 147) / 148;
+      const long long waves = (tiles * split + per_wave - 1) / per_wave;
       const long long kt = (ktiles + split - 1) / split;
       double cost = (double)waves * ((double)kt * tile_us + 6.0);
       if (split > 1) cost += 3.0 + 2.0 * split * (double)p.M * p.N * p.groups * 4.0 / 3e6;
@@ -1023,7 +1026,6 @@ struct Planner {
     }
     p.a_contig = (sl[lf] == 1 && Cg > 1) ? 0 : (batch_fastest ? 1 : 0);
     p.b_contig = sr[ro] == 1 ? 0 : 1;
-    choose_split_k(p);
     return make_igemm(op, p, lhs, rhs, out, arow, acol, bcol, bn, crow, cn, ag, bg, cg, st);
   }
 
@@ -1077,7 +1079,6 @@ struct Planner {
     for (int64_t g = 0; g < G; g++) cg[g] = g * M * N;
     p.a_contig = (K > 1 && ak[1] == 1) ? 0 : ((M > 1 && am[1] == 1) ? 1 : 0);
     p.b_contig = (N > 1 && bn[1] == 1) ? 0 : 1;
-    choose_split_k(p);
     return make_igemm(op, p, lhs, rhs, out, arow, acol, bk, bn, crow, cn, ag, bg, cg, st);
   }
 
@@ -1165,6 +1166,7 @@ struct Planner {
     }
     p.c_vec = 1;
     for (size_t n = 1; n < cn.size(); n++) if (cn[n] != cn[0] + (long long)n) p.c_vec = 0;
+    choose_split_k(p);
     Step s;
     s.kind = Step::IGEMM;
     s.label = op->name;
