@@ -1166,6 +1166,12 @@ struct Planner {
     }
     p.c_vec = 1;
     for (size_t n = 1; n < cn.size(); n++) if (cn[n] != cn[0] + (long long)n) p.c_vec = 0;
+    if (p.c_vec) {                                   // 2: every row of C also starts on a multiple of four floats
+      bool al = !cn.empty() && cn[0] % 4 == 0;
+      for (auto v : crow) al = al && v % 4 == 0;
+      for (auto v : cg) al = al && v % 4 == 0;
+      if (al) p.c_vec = 2;
+    }
     choose_split_k(p);
     Step s;
     s.kind = Step::IGEMM;

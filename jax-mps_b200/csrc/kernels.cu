@@ -199,20 +199,62 @@ __global__ void __launch_bounds__(NT) igemm_f32_kernel(const float* __restrict__
   }
 }
 
+// Sum of the split-K partial tiles, in a fixed order. Threads (32, KY), or (256, 1) when KY = 1: thread x owns one output (or four consecutive
+// n when VEC), row y adds the splits y, y + KY, ... with four independent accumulators so that several loads are in
+// flight; the KY rows are then added in order by row 0.
+template <int KY, bool VEC>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ C,
-                                                            const long long* __restrict__ c_row,
-                                                            const long long* __restrict__ c_col,
-                                                            const long long* __restrict__ c_grp, int M, int N, int groups,
-                                                            int split_k) {
-  long long total = (long long)groups * M * N;
-  long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+                                                                const long long* __restrict__ c_row,
+                                                                const long long* __restrict__ c_col,
+                                                                const long long* __restrict__ c_grp, int M, int N, int groups,
+                                                                int split_k) {
+  constexpr int W = VEC ? 4 : 1;
+  __shared__ float sm[KY][32 * W + 1];
+  const long long total = (long long)groups * M * N;
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * W;     // blockDim.x is 32 when KY > 1
+  float acc[4][W];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int w = 0; w < W; ++w) acc[a][w] = 0.f;
+  if (i < total) {
+    int k = threadIdx.y;
+    for (; k + 3 * KY < split_k; k += 4 * KY) {
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const float* src = partial + (long long)(k + a * KY) * total + i;
+        if (VEC) { const float4 v = *reinterpret_cast<const float4*>(src); acc[a][0] += v.x; acc[a][W > 1 ? 1 : 0] += v.y; acc[a][W > 2 ? 2 : 0] += v.z; acc[a][W > 3 ? 3 : 0] += v.w; }
+        else acc[a][0] += *src;
+      }
+    }
+    for (; k < split_k; k += KY) {
+      const float* src = partial + (long long)k * total + i;
+      if (VEC) { const float4 v = *reinterpret_cast<const float4*>(src); acc[0][0] += v.x; acc[0][W > 1 ? 1 : 0] += v.y; acc[0][W > 2 ? 2 : 0] += v.z; acc[0][W > 3 ? 3 : 0] += v.w; }
+      else acc[0][0] += *src;
+    }
+  }
+  float s[W];
+#pragma unroll
+  for (int w = 0; w < W; ++w) s[w] = (acc[0][w] + acc[1][w]) + (acc[2][w] + acc[3][w]);
+  if (KY > 1) {
+#pragma unroll
+    for (int w = 0; w < W; ++w) sm[threadIdx.y][threadIdx.x * W + w] = s[w];
+    __syncthreads();
+    if (threadIdx.y != 0) return;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      float t = sm[0][threadIdx.x * W + w];
+      for (int y = 1; y < KY; ++y) t += sm[y][threadIdx.x * W + w];
+      s[w] = t;
+    }
+  }
   if (i >= total) return;
-  float s = 0.f;
-  for (int k = 0; k < split_k; k++) s += partial[(long long)k * total + i];
-  int n = (int)(i % N);
-  int m = (int)((i / N) % M);
-  int g = (int)(i / ((long long)M * N));
-  C[c_grp[g] + c_row[m] + c_col[n]] = s;
+  const int n = (int)(i % N);
+  const int m = (int)((i / N) % M);
+  const int g = (int)(i / ((long long)M * N));
+  float* out = C + c_grp[g] + c_row[m] + c_col[n];
+  if (VEC) *reinterpret_cast<float4*>(out) = make_float4(s[0], s[W > 1 ? 1 : 0], s[W > 2 ? 2 : 0], s[W > 3 ? 3 : 0]);
+  else *out = s[0];
 }
 
 
@@ -1492,8 +1534,18 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
   if (e != cudaSuccess) return e;
   if (p.split_k > 1) {
     long long total = (long long)p.groups * p.M * p.N;
-    splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const float*)partial, (float*)C, c_row,
-                                                                              c_col, c_grp, p.M, p.N, p.groups, p.split_k);
+    // four consecutive n per thread when they are four consecutive, 16-byte aligned floats of C; the splits are
+    // spread over 8 thread rows when there are many of them and few outputs
+    const float* pp = (const float*)partial;
+    float* cc = (float*)C;
+    const bool vec = p.c_vec == 2 && p.N % 4 == 0 && (((uintptr_t)C) & 15) == 0 && (((uintptr_t)partial) & 15) == 0;
+    const long long items = vec ? total / 4 : total;
+    const bool tall = p.split_k >= 16;
+    const unsigned blocks = (unsigned)(tall ? (items + 31) / 32 : (items + 255) / 256);
+    if (vec && tall) splitk_reduce_kernel<8, true><<<blocks, dim3(32, 8), 0, stream>>>(pp, cc, c_row, c_col, c_grp, p.M, p.N, p.groups, p.split_k);
+    else if (vec) splitk_reduce_kernel<1, true><<<blocks, dim3(256, 1), 0, stream>>>(pp, cc, c_row, c_col, c_grp, p.M, p.N, p.groups, p.split_k);
+    else if (tall) splitk_reduce_kernel<8, false><<<blocks, dim3(32, 8), 0, stream>>>(pp, cc, c_row, c_col, c_grp, p.M, p.N, p.groups, p.split_k);
+    else splitk_reduce_kernel<1, false><<<blocks, dim3(256, 1), 0, stream>>>(pp, cc, c_row, c_col, c_grp, p.M, p.N, p.groups, p.split_k);
     if (launches) (*launches)++;
     e = cudaGetLastError();
   }

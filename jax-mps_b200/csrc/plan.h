@@ -42,7 +42,7 @@ struct IGemmParams {
   int needs_mask = 0;
   int vec = 0;                               // both operands gather in uniform, aligned 16-byte chunks
   int seg = 0;                               // vec, and aligned runs of 32 along the contiguous dimensions are uniform
-  int c_vec = 0;                             // consecutive n are consecutive floats in C
+  int c_vec = 0;                             // consecutive n are consecutive floats in C (2: and rows start on multiples of four floats)
 };
 
 struct Plan;
