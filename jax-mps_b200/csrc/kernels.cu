@@ -1062,17 +1062,21 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
 //               and commits them to the stage's `empty` barrier
 // Tensor memory: all 512 columns; accumulator in [0, BN), A ring from column 128 (64 columns per stage).
 // Every wait is bounded as in the kernels above.
-template <int BN_>
+// HALF: a CTA of 13 warps with three stages and 256 tensor-memory columns, two of which share an SM, so that the
+// launch, pipeline fill and read-back of one overlap the main loop of the other (used for 64-wide tiles when the
+// grid has several waves of CTAs).
+template <int BN_, bool HALF>
 struct TaCfg {
   static constexpr int BN = BN_;
-  static constexpr int STAGES = BN_ == 64 ? 6 : 4;
+  static constexpr int STAGES = HALF ? 3 : (BN_ == 64 ? 6 : 4);
   static constexpr int A_BYTES = TBM * TBK * 4, B_BYTES = BN_ * TBK * 4;
   static constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;            // raw A, raw B, low B
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 512;
   static constexpr int B_CHUNKS = BN_ * TBK / 4;
-  static constexpr int A_COL0 = 128;                                   // 64 columns per stage: 128 + 6 * 64 = 512
+  static constexpr int TMEM_COLS = HALF ? 256 : 512;
+  static constexpr int A_COL0 = HALF ? 64 : 128;                       // 64 columns per stage after the accumulator
+  static constexpr int THREADS = HALF ? 416 : 800;
 };
-constexpr int TA_THREADS = 800;
 
 __device__ __forceinline__ void umma_tf32_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -1095,14 +1099,14 @@ __device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&v)
       : "memory");
 }
 
-template <int BN, bool A_MCONTIG, bool B_KCONTIG, bool MASK>
-__global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
+template <int BN, bool A_MCONTIG, bool B_KCONTIG, bool MASK, bool HALF>
+__global__ void __launch_bounds__((TaCfg<BN, HALF>::THREADS), (HALF ? 2 : 1)) igemm_tf32x3_ta_kernel(
     const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, const RowEnt* __restrict__ a_row,
     const ColEnt* __restrict__ a_col, const long long* __restrict__ b_row, const long long* __restrict__ b_col,
     const long long* __restrict__ c_row, const long long* __restrict__ c_col, const long long* __restrict__ a_grp,
     const long long* __restrict__ b_grp, const long long* __restrict__ c_grp, float* __restrict__ partial,
     int* __restrict__ error_flag, IGemmLaunch p) {
-  using Cfg = TaCfg<BN>;
+  using Cfg = TaCfg<BN, HALF>;
   constexpr int S = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -1121,16 +1125,18 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
   const int kchunk = ((p.K + p.split_k - 1) / p.split_k + TBK - 1) / TBK * TBK;
   const int kbeg = sp * kchunk, kend = min(p.K, kbeg + kchunk);
   const int ktiles = kend > kbeg ? (kend - kbeg + TBK - 1) / TBK : 0;
-  constexpr int MMA_WARP = 24;
+  constexpr int MMA_WARP = Cfg::THREADS / 32 - 1;
   // warp roles: A gather (one group of four warps, or two groups alternating k-tiles for the 64-wide tile, where
   // A is two thirds of the gather work), B gather, A converters, low part of B (the warps that remain)
-  constexpr int A_GROUPS = BN == 64 ? 2 : 1;
-  constexpr int W_B = 4 * A_GROUPS, W_CONV = W_B + 4, W_LOW = W_CONV + 8, N_LOW = (MMA_WARP - W_LOW) * 32;
+  constexpr int A_GROUPS = (BN == 64 && !HALF) ? 2 : 1;
+  constexpr int NBW = HALF ? 2 : 4;                  // B gather warps
+  constexpr int CONV_GROUPS = HALF ? 1 : 2;          // groups of four converter warps
+  constexpr int W_B = 4 * A_GROUPS, W_CONV = W_B + NBW, W_LOW = W_CONV + 4 * CONV_GROUPS, N_LOW = (MMA_WARP - W_LOW) * 32;
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&landed_a[s]), 128);
-      mbar_init(smem_u32(&landed_b[s]), 128);
+      mbar_init(smem_u32(&landed_b[s]), NBW * 32);
       mbar_init(smem_u32(&a_ready[s]), 128);
       mbar_init(smem_u32(&b_ready[s]), N_LOW);
       mbar_init(smem_u32(&empty[s]), 1);
@@ -1140,7 +1146,7 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -1164,7 +1170,7 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
     const int a_sh = (int)p.a_sh, a_sw = (int)p.a_sw;
     const bool is_a = warp < W_B;
     const int first = is_a ? (warp >> 2) : 0, stride = is_a ? A_GROUPS : 1;     // k-tiles first, first + stride, ...
-    constexpr int B_ROWS = BN / 4;                   // rows per B warp
+    constexpr int B_ROWS = BN / NBW;                 // rows per B warp
     const int rows = is_a ? 32 : B_ROWS;
     const int u = is_a ? (warp & 3) * 32 + lane : (warp - W_B) * B_ROWS + (lane % B_ROWS);   // tile row owned by this lane
     int k_local = 0;                                 // MN-major rows sit at their own k inside the tile
@@ -1248,7 +1254,7 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
     // ------------------------------ A: shared memory -> registers -> tensor memory ---------------------------
     const int grp = (warp - W_CONV) >> 2, quad = warp & 3;
     const int row = 32 * quad + lane;
-    for (int j = grp; j < ktiles; j += 2) {
+    for (int j = grp; j < ktiles; j += CONV_GROUPS) {
       const int s = j % S;
       if (*failed || !mbar_wait(smem_u32(&landed_a[s]), (uint32_t)((j / S) & 1))) { *failed = 1; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -1281,7 +1287,7 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(smem_u32(&a_ready[s]));
     }
-  } else if (warp < 24) {
+  } else if (warp < MMA_WARP) {
     // ------------------------------ low part of B ------------------------------------------------------------
     const int t = tid - W_LOW * 32;
     for (int j = 0; j < ktiles; ++j) {
@@ -1344,14 +1350,20 @@ __global__ void __launch_bounds__(TA_THREADS, 1) igemm_tf32x3_ta_kernel(
     __syncwarp();
   }
 
-  if (warp >= W_CONV && warp < W_LOW)
-    store_accumulator<BN>(tmem, warp - W_CONV, lane, m0, n0, g, sp, ktiles, p, C, partial, c_row, c_col, c_grp, failed,
+  if (warp >= W_CONV && warp < W_LOW) {
+    // a warp can only read the tensor-memory lanes of quadrant warp % 4; the converter group picks the column half
+    const int ew = (warp & 3) + 4 * ((warp - W_CONV) >> 2);
+    store_accumulator<BN>(tmem, ew, lane, m0, n0, g, sp, ktiles, p, C, partial, c_row, c_col, c_grp, failed,
                           smem_u32(done), 0u);
+    if (CONV_GROUPS == 1)                            // four read-back warps: each also takes the second column half
+      store_accumulator<BN>(tmem, ew + 4, lane, m0, n0, g, sp, ktiles, p, C, partial, c_row, c_col, c_grp, failed,
+                            smem_u32(done), 0u);
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (tid == 0 && *failed) atomicExch(error_flag, 1);
   if (warp == MMA_WARP) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::TMEM_COLS) : "memory");
   }
 }
 
@@ -1451,8 +1463,10 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
                        WsCfg<BN_>::SMEM);                                                                            \
   cudaFuncSetAttribute(igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                        WsCfg<BN_>::SMEM);                                                                            \
-  cudaFuncSetAttribute(igemm_tf32x3_ta_kernel<BN_, AM, BK_, MK>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
-                       TaCfg<BN_>::SMEM)
+  cudaFuncSetAttribute(igemm_tf32x3_ta_kernel<BN_, AM, BK_, MK, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                       TaCfg<BN_, false>::SMEM);                                                                     \
+  cudaFuncSetAttribute(igemm_tf32x3_ta_kernel<64, AM, BK_, MK, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                       TaCfg<64, true>::SMEM)
 #define SETALLW(BN_)                                                                                                  \
   SETATTRW(BN_, false, false, false); SETATTRW(BN_, false, false, true); SETATTRW(BN_, false, true, false);           \
   SETATTRW(BN_, false, true, true); SETATTRW(BN_, true, false, false); SETATTRW(BN_, true, false, true);              \
@@ -1464,10 +1478,17 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
         configured_w = true;
       }
       const bool wide = p.N >= 128 && p.wide_n;
+      // two half-size CTAs per SM for 64-wide tiles once the grid has more than two waves of full-size CTAs
+      const long long ctas64 = (long long)((p.M + TBM - 1) / TBM) * ((p.N + 63) / 64) * p.groups * p.split_k;
+      const bool half = !wide && p.half_ctas && ctas64 > 2 * 148;
       dim3 gridw((p.M + TBM - 1) / TBM, (p.N + (wide ? 128 : 64) - 1) / (wide ? 128 : 64), p.groups * p.split_k);
 #define LAUNCHW(BN_, AM, BK_, MK)                                                                                     \
-  if (p.seg && p.tmem_a)                                                                                              \
-    igemm_tf32x3_ta_kernel<BN_, AM, BK_, MK><<<gridw, TA_THREADS, TaCfg<BN_>::SMEM, stream>>>(                        \
+  if (p.seg && p.tmem_a && half)                                                                                      \
+    igemm_tf32x3_ta_kernel<64, AM, BK_, MK, true><<<gridw, TaCfg<64, true>::THREADS, TaCfg<64, true>::SMEM, stream>>>( \
+        (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
+        (float*)partial, error_flag, p);                                                                              \
+  else if (p.seg && p.tmem_a)                                                                                         \
+    igemm_tf32x3_ta_kernel<BN_, AM, BK_, MK, false><<<gridw, TaCfg<BN_, false>::THREADS, TaCfg<BN_, false>::SMEM, stream>>>( \
         (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
         (float*)partial, error_flag, p);                                                                              \
   else if (p.seg)                                                                                                     \

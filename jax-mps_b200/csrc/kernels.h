@@ -13,6 +13,7 @@ struct IGemmLaunch {
   int vec;                       // operands can be gathered in uniform, aligned 16-byte chunks
   int seg;                       // vec, and every aligned run of 32 along each operand's contiguous dimension is one 128-byte row
   int tmem_a;                    // with seg: keep the A operand in tensor memory (igemm_tf32x3_ta_kernel)
+  int half_ctas;                 // allow the two-CTAs-per-SM variant of the tensor-memory kernel
   int c_vec;                     // consecutive n are consecutive floats in C (2: and rows start on multiples of four floats)
   int wide_n;                    // use 128-wide N tiles when N >= 128
 };

@@ -540,6 +540,7 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       p.c_vec = s.ig.c_vec;
       p.seg = p.vec && s.ig.seg && !getenv("B200_NO_SEG_GATHER");
       p.tmem_a = getenv("B200_NO_TMEM_A") ? 0 : 1;
+      p.half_ctas = getenv("B200_NO_HALF_CTAS") ? 0 : 1;
       p.wide_n = getenv("B200_NARROW_TILES") ? 0 : 1;
       p.tensor_cores = c->tensor_cores && (long long)s.ig.M * s.ig.N * s.ig.K * s.ig.groups >= (1LL << 18) && s.ig.K >= 16;
       const void* tables[9];

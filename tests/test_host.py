@@ -167,3 +167,34 @@ def test_distilbert_program_gradients_match_finite_differences():
         dn[k][idx] -= h
         fd = (float(interp.run_text(prog.text, up, wide=True)[0]) - float(interp.run_text(prog.text, dn, wide=True)[0])) / (2 * h)
         assert abs(fd - float(outs[1 + k][idx])) < 1e-6 * max(1.0, abs(fd)), nm
+
+
+def test_plans_of_case_scatter_and_half_precision_contractions():
+    """Compile-only checks (no GPU): a case becomes one step with a sub-plan per branch, the row scatter one
+    scatter step, a bf16 dot_general an f32 implicit GEMM between converts; an unsupported scatter form is a
+    compile error that names the restriction."""
+    b = Builder()
+    idx, x = b.arg((), "i32"), b.arg((4, 4), "f32")
+    outs = b.case(idx, [lambda s: [s.exp(x)], lambda s: [s.neg(x)]], [((4, 4), "f32")])
+    plan, _ = b200.compile_to_plan(b.module(outs))
+    assert "case branches=2" in plan
+
+    b = Builder()
+    t, i, u = b.arg((12, 8), "bf16"), b.arg((5,), "i32"), b.arg((5, 8), "bf16")
+    plan, _ = b200.compile_to_plan(b.module([b.scatter_rows(t, i, u, "add")]))
+    assert "scatter rows=12 row_elems=8 updates=5" in plan
+
+    b = Builder()
+    p, q = b.arg((64, 64), "bf16"), b.arg((64, 64), "bf16")
+    plan, src = b200.compile_to_plan(b.module([b.matmul(p, q)]))
+    assert "igemm M=64 N=64 K=64" in plan and plan.count("convert") >= 2
+
+    b = Builder()
+    t, i, u = b.arg((12, 8), "f32"), b.arg((5, 2), "i32"), b.arg((5,), "f32")
+    sdn = ("#stablehlo.scatter<update_window_dims = [], inserted_window_dims = [0, 1], "
+           "scatter_dims_to_operand_dims = [0, 1], index_vector_dim = 1>")
+    reg = b.region([((), "f32")] * 2, lambda s, a, c: s.add(a, c))
+    (y,) = b.emit("stablehlo.scatter", [t, i, u], [((12, 8), "f32")],
+                  props={"scatter_dimension_numbers": sdn, "indices_are_sorted": "false", "unique_indices": "false"}, regions=[reg])
+    with pytest.raises(b200.B200Error, match="row form"):
+        b200.compile_to_plan(b.module([y]))
