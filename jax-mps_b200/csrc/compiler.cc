@@ -912,8 +912,10 @@ struct Planner {
     const long long ktiles = (p.K + 31) / 32;
     // the scalar-gather kernel (operands without 16-byte structure) spends about 10 us per k-tile and runs two
     // CTAs per SM; the row-gather kernels one CTA per SM
-    const double tile_us = !p.vec ? 10.0 : (bn == 128 ? 0.9 : 0.6);
-    const long long per_wave = p.vec ? 148 : 296;
+    // 64-wide row-gather tiles run as two half-size CTAs per SM (about 1 us per k-tile each, two at a time)
+    const bool half = p.vec && p.seg && bn == 64;
+    const double tile_us = !p.vec ? 10.0 : (bn == 128 ? 0.9 : (half ? 1.0 : 0.6));
+    const long long per_wave = (!p.vec || half) ? 296 : 148;
     int best = 1;
     double best_cost = 1e30;
     const int max_split = (int)std::min<long long>(592, std::max<long long>(1, ktiles / 8));

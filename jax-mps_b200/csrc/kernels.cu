@@ -1478,9 +1478,9 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
         configured_w = true;
       }
       const bool wide = p.N >= 128 && p.wide_n;
-      // two half-size CTAs per SM for 64-wide tiles once the grid has more than two waves of full-size CTAs
+      // two half-size CTAs per SM for 64-wide tiles once the grid has more than one wave of full-size CTAs
       const long long ctas64 = (long long)((p.M + TBM - 1) / TBM) * ((p.N + 63) / 64) * p.groups * p.split_k;
-      const bool half = !wide && p.half_ctas && ctas64 > 2 * 148;
+      const bool half = !wide && p.half_ctas && ctas64 > 148;
       dim3 gridw((p.M + TBM - 1) / TBM, (p.N + (wide ? 128 : 64) - 1) / (wide ? 128 : 64), p.groups * p.split_k);
 #define LAUNCHW(BN_, AM, BK_, MK)                                                                                     \
   if (p.seg && p.tmem_a && half)                                                                                      \
