@@ -1049,16 +1049,20 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
 // registers of one thread per row -> tensor memory, as a high tile (the raw words: the tensor core reads their
 // TF32 bits) and a low tile (x - tf32(x)), and tcgen05.mma takes it from there; per k-tile the shared memory
 // moves 16 KB + 16 KB for A and (8 + 16 + 24) KB for a 64-wide B instead of 144 KB.
-// Roles, 64-wide tile (128-wide tile in brackets):
-//   warps 0-7 [0-3]    gather A, two groups of four warps alternating k-tiles [one group]: lane l owns row l of the
-//               warp's 32 tile rows (address + padding mask once per row and k-tile), copies go out four rows per
-//               instruction, eight lanes per row (128-byte cp.async.bulk row copies were tried: 1.6 times slower)
-//   warps 8-11 [4-7]   gather B the same way, every k-tile
-//   warps 12-19 [8-15] two groups of four warps alternate k-tiles: thread = one row m of the tile; reads its 32
-//               values (K-major rows: eight 16-byte reads from the swizzled row; MN-major: 32 words, one per k),
-//               tcgen05.st of the high and the low words into the stage's 64 tensor-memory columns
-//   warps 20-23 [16-23] low part of the B tile in shared memory
-//   warp 24     one thread issues the 12 MMAs of a k-tile (A hi x B raw, A hi x B lo, A lo x B raw per k-step)
+// Roles (warp ranges for the 64-wide tile | the 128-wide tile | the half-size CTA):
+//   gather A    0-7 | 0-7 | 0-3    groups of four warps alternating k-tiles (one group in the half-size CTA): lane l owns
+//               row l of the warp's 32 tile rows (address + padding mask once per row and k-tile), copies go out four
+//               rows per instruction, eight lanes per row (128-byte cp.async.bulk row copies were tried: 1.6x slower)
+//   gather B    8-11 | 8-11 | 4-5  the same way, every k-tile
+//   convert A   12-19 | 12-15 | 6-9  groups of four warps (two groups alternating k-tiles for the 64-wide tile): thread
+//               = one row m of the tile; reads its 32 values (K-major rows: eight 16-byte reads from the swizzled row;
+//               MN-major: 32 words, one per k), tcgen05.st of the high and the low words into the stage's 64
+//               tensor-memory columns; the same warps read the accumulator back at the end
+//   low part B  20-23 | 16-23 | 10-11  in shared memory
+// Every producer warp needs about a thousand cycles per k-tile whatever its share of the work (dependent chains), so
+// the split gives each role as many independent chains as its share of the critical path needs; the numbers above
+// are the fastest of the splits measured.
+//   last warp   one thread issues the 12 MMAs of a k-tile (A hi x B raw, A hi x B lo, A lo x B raw per k-step)
 //               and commits them to the stage's `empty` barrier
 // Tensor memory: all 512 columns; accumulator in [0, BN), A ring from column 128 (64 columns per stage).
 // Every wait is bounded as in the kernels above.
@@ -1126,11 +1130,10 @@ __global__ void __launch_bounds__((TaCfg<BN, HALF>::THREADS), (HALF ? 2 : 1)) ig
   const int kbeg = sp * kchunk, kend = min(p.K, kbeg + kchunk);
   const int ktiles = kend > kbeg ? (kend - kbeg + TBK - 1) / TBK : 0;
   constexpr int MMA_WARP = Cfg::THREADS / 32 - 1;
-  // warp roles: A gather (one group of four warps, or two groups alternating k-tiles for the 64-wide tile, where
-  // A is two thirds of the gather work), B gather, A converters, low part of B (the warps that remain)
-  constexpr int A_GROUPS = (BN == 64 && !HALF) ? 2 : 1;
+  // warp roles in order: A gather groups, B gather, A converter groups, low part of B (the warps that remain), MMA
+  constexpr int A_GROUPS = HALF ? 1 : 2;
   constexpr int NBW = HALF ? 2 : 4;                  // B gather warps
-  constexpr int CONV_GROUPS = HALF ? 1 : 2;          // groups of four converter warps
+  constexpr int CONV_GROUPS = (HALF || BN == 128) ? 1 : 2;          // groups of four converter warps
   constexpr int W_B = 4 * A_GROUPS, W_CONV = W_B + NBW, W_LOW = W_CONV + 4 * CONV_GROUPS, N_LOW = (MMA_WARP - W_LOW) * 32;
 
   if (tid == 0) {
