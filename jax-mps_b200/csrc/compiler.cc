@@ -1011,6 +1011,24 @@ struct Planner {
       arow[m] = {n * sl[lb], (int)(oh * stride[0] - pad[0]), (int)(ow * stride[1] - pad[2])};
       crow[m] = n * so[ob] + oh * so[o0] + ow * so1;
     }
+    if (p.ldh > 1 || p.ldw > 1) {
+      // Input dilation (the input gradient of a strided convolution): a window position only meets real input where
+      // (h0 + dh) is a multiple of the dilation, so rows of one phase (h0 mod ldh, w0 mod ldw) share their live
+      // window positions. Rows are visited phase by phase, which lets whole k-tiles be skipped per row tile
+      // (make_igemm builds the list); the output addresses follow the rows, so the result is unchanged.
+      auto phase = [&](const RowEnt& r) {
+        const int ph = ((r.h0 % p.ldh) + p.ldh) % p.ldh, pw = ((r.w0 % p.ldw) + p.ldw) % p.ldw;
+        return ph * p.ldw + pw;
+      };
+      std::vector<int64_t> order(p.M);
+      for (int64_t m = 0; m < p.M; m++) order[m] = m;
+      std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return phase(arow[a]) < phase(arow[b]); });
+      std::vector<RowEnt> ar2(p.M);
+      std::vector<long long> cr2(p.M);
+      for (int64_t m = 0; m < p.M; m++) { ar2[m] = arow[order[m]]; cr2[m] = crow[order[m]]; }
+      arow.swap(ar2);
+      crow.swap(cr2);
+    }
     std::vector<ColEnt> acol(p.K);
     std::vector<long long> bcol(p.K);
     for (int64_t k = 0; k < p.K; k++) {
@@ -1190,6 +1208,32 @@ struct Planner {
       t.dt = DT::F32;
       t.dims = {(int64_t)p.split_k, (int64_t)p.groups, (int64_t)p.M, (int64_t)p.N};
       s.args.push_back(new_slot(Slot::TEMP, t, st.arena));
+    }
+    if (p.seg && p.needs_mask && p.a_contig == 0 && p.split_k == 1 && p.groups == 1 && (p.ldh > 1 || p.ldw > 1)) {
+      // per 128-row tile: the k-tiles in which at least one row meets real input (all 32 k of a tile share one
+      // window position when the row gather applies)
+      const int mtiles = (p.M + 127) / 128, ktiles = p.K / 32;
+      std::vector<int> table((size_t)mtiles * (ktiles + 1), 0);
+      long long kept = 0;
+      for (int mt = 0; mt < mtiles; mt++) {
+        int* row = &table[(size_t)mt * (ktiles + 1)];
+        int cnt = 0;
+        for (int kt = 0; kt < ktiles; kt++) {
+          const ColEnt& c = acol[(size_t)kt * 32];
+          bool live = false;
+          for (int m = mt * 128; m < std::min(p.M, (mt + 1) * 128) && !live; m++) {
+            const int ih = arow[m].h0 + c.dh, iw = arow[m].w0 + c.dw;
+            live = ih >= 0 && iw >= 0 && ih < p.Hd && iw < p.Wd && ih % p.ldh == 0 && iw % p.ldw == 0;
+          }
+          if (live) row[1 + cnt++] = kt;
+        }
+        row[0] = cnt;
+        kept += cnt;
+      }
+      if (kept < (long long)mtiles * ktiles) {
+        s.ig.kt_stride = ktiles;
+        s.args.push_back(tab(table.data(), table.size() * sizeof(int)));
+      }
     }
     return s;
   }
@@ -1873,7 +1917,7 @@ void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& o
         break;
       case Step::IGEMM:
         os << "igemm M=" << s.ig.M << " N=" << s.ig.N << " K=" << s.ig.K << " G=" << s.ig.groups << " splitK=" << s.ig.split_k
-           << " a_contig=" << s.ig.a_contig << " b_contig=" << s.ig.b_contig << " vec=" << s.ig.vec << " seg=" << s.ig.seg << " " << s.label;
+           << " a_contig=" << s.ig.a_contig << " b_contig=" << s.ig.b_contig << " vec=" << s.ig.vec << " seg=" << s.ig.seg << (s.ig.kt_stride ? " ktlist" : "") << " " << s.label;
         break;
       case Step::MEMCPY: os << "memcpy " << s.bytes; break;
       case Step::WHILE: os << "while trip=" << s.trip_count; break;

@@ -1109,7 +1109,7 @@ __global__ void __launch_bounds__((TaCfg<BN, HALF>::THREADS), (HALF ? 2 : 1)) ig
     const ColEnt* __restrict__ a_col, const long long* __restrict__ b_row, const long long* __restrict__ b_col,
     const long long* __restrict__ c_row, const long long* __restrict__ c_col, const long long* __restrict__ a_grp,
     const long long* __restrict__ b_grp, const long long* __restrict__ c_grp, float* __restrict__ partial,
-    int* __restrict__ error_flag, IGemmLaunch p) {
+    const int* __restrict__ kt_table, int* __restrict__ error_flag, IGemmLaunch p) {
   using Cfg = TaCfg<BN, HALF>;
   constexpr int S = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -1128,7 +1128,11 @@ __global__ void __launch_bounds__((TaCfg<BN, HALF>::THREADS), (HALF ? 2 : 1)) ig
   const int g = blockIdx.z / p.split_k, sp = blockIdx.z % p.split_k;
   const int kchunk = ((p.K + p.split_k - 1) / p.split_k + TBK - 1) / TBK * TBK;
   const int kbeg = sp * kchunk, kend = min(p.K, kbeg + kchunk);
-  const int ktiles = kend > kbeg ? (kend - kbeg + TBK - 1) / TBK : 0;
+  // with a k-tile list (input-dilated convolutions: most window positions of a row tile fall on holes) only the
+  // listed k-tiles are visited; j below counts visited tiles, kt_of(j) is the k-tile itself
+  const int* kt_list = kt_table ? kt_table + (size_t)blockIdx.x * (p.kt_stride + 1) : nullptr;
+  const int ktiles = kt_list ? kt_list[0] : (kend > kbeg ? (kend - kbeg + TBK - 1) / TBK : 0);
+  auto kt_of = [&](int j) { return kt_list ? kt_list[1 + j] : j; };
   constexpr int MMA_WARP = Cfg::THREADS / 32 - 1;
   // warp roles in order: A gather groups, B gather, A converter groups, low part of B (the warps that remain), MMA
   constexpr int A_GROUPS = HALF ? 1 : 2;
@@ -1206,8 +1210,8 @@ __global__ void __launch_bounds__((TaCfg<BN, HALF>::THREADS), (HALF ? 2 : 1)) ig
     struct Ent { int off, dh, dw; };
     // k-dependent table entry of tile j for this lane's row, fetched two tiles ahead into alternating registers
     auto fetch = [&](int j, Ent& e) {
-      const int k = kbeg + j * TBK + k_local;
       e.off = -1; e.dh = 0; e.dw = 0;
+      const int k = j < ktiles ? kbeg + kt_of(j) * TBK + k_local : kend;
       if (j < ktiles && k < kend) {
         if (is_a) { const ColEnt c = a_col[k]; e.off = (int)c.off; e.dh = c.dh; e.dw = c.dw; }
         else e.off = (int)b_row[k];
@@ -1436,7 +1440,7 @@ __global__ void __launch_bounds__(256) scatter_apply_kernel(T* __restrict__ out,
 }  // namespace
 
 cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B, void* C, const void* const* tables,
-                             void* partial, int* error_flag, cudaStream_t stream, int* launches) {
+                             void* partial, const int* kt_table, int* error_flag, cudaStream_t stream, int* launches) {
   auto a_row = (const RowEnt*)tables[0];
   auto a_col = (const ColEnt*)tables[1];
   auto b_row = (const long long*)tables[2];
@@ -1489,11 +1493,11 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
   if (p.seg && p.tmem_a && half)                                                                                      \
     igemm_tf32x3_ta_kernel<64, AM, BK_, MK, true><<<gridw, TaCfg<64, true>::THREADS, TaCfg<64, true>::SMEM, stream>>>( \
         (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
-        (float*)partial, error_flag, p);                                                                              \
+        (float*)partial, kt_table, error_flag, p);                                                                    \
   else if (p.seg && p.tmem_a)                                                                                         \
     igemm_tf32x3_ta_kernel<BN_, AM, BK_, MK, false><<<gridw, TaCfg<BN_, false>::THREADS, TaCfg<BN_, false>::SMEM, stream>>>( \
         (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
-        (float*)partial, error_flag, p);                                                                              \
+        (float*)partial, kt_table, error_flag, p);                                                                    \
   else if (p.seg)                                                                                                     \
     igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK, true><<<gridw, WS_THREADS, WsCfg<BN_>::SMEM, stream>>>(                  \
         (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \

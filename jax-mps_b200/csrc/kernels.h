@@ -13,6 +13,7 @@ struct IGemmLaunch {
   int vec;                       // operands can be gathered in uniform, aligned 16-byte chunks
   int seg;                       // vec, and every aligned run of 32 along each operand's contiguous dimension is one 128-byte row
   int tmem_a;                    // with seg: keep the A operand in tensor memory (igemm_tf32x3_ta_kernel)
+  int kt_stride;                 // > 0: kt_table holds, per 128-row tile, a count and the k-tiles to visit
   int half_ctas;                 // allow the two-CTAs-per-SM variant of the tensor-memory kernel
   int c_vec;                     // consecutive n are consecutive floats in C (2: and rows start on multiples of four floats)
   int wide_n;                    // use 128-wide N tiles when N >= 128
@@ -22,8 +23,10 @@ struct IGemmLaunch {
 // `partial` is the split-K scratch ([split_k][groups][M][N] floats) or null when split_k == 1.
 // `error_flag` (device int) is set by the tensor-core kernel when one of its bounded waits expires.
 // Adds the number of kernels launched to *launches.
+// `kt_table` (device, may be null): per 128-row tile of M, [count, k-tile indices...] with row length 1 + kt_stride;
+// k-tiles outside the list contribute nothing (their rows all fall on padding or dilation holes) and are skipped.
 cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B, void* C, const void* const* tables,
-                             void* partial, int* error_flag, cudaStream_t stream, int* launches);
+                             void* partial, const int* kt_table, int* error_flag, cudaStream_t stream, int* launches);
 
 }  // namespace b200
 

@@ -41,6 +41,7 @@ struct IGemmParams {
   int split_k = 1;
   int needs_mask = 0;
   int vec = 0;                               // both operands gather in uniform, aligned 16-byte chunks
+  int kt_stride = 0;                         // > 0: the last igemm arg is a table [m-tile][1 + kt_stride] of k-tiles to visit
   int seg = 0;                               // vec, and aligned runs of 32 along the contiguous dimensions are uniform
   int c_vec = 0;                             // consecutive n are consecutive floats in C (2: and rows start on multiples of four floats)
 };

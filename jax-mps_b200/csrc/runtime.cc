@@ -546,8 +546,10 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       const void* tables[9];
       for (int k = 0; k < 9; k++) tables[k] = x.ptrs[s.args[3 + k]];
       void* partial = s.ig.split_k > 1 ? x.ptrs[s.args[12]] : nullptr;
+      p.kt_stride = s.ig.kt_stride;
+      const int* kt_table = s.ig.kt_stride > 0 ? (const int*)x.ptrs[s.args.back()] : nullptr;
       cudaError_t e = launch_igemm_f32(p, x.ptrs[s.args[0]], x.ptrs[s.args[1]], x.ptrs[s.args[2]], tables, partial,
-                                       c->error_flag, st, &x.launches);
+                                       kt_table, c->error_flag, st, &x.launches);
       if (e != cudaSuccess) return make_error(B200_INTERNAL, "launch of " + s.label + " failed: " + cudaGetErrorString(e));
       return nullptr;
     }

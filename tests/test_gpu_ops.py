@@ -232,6 +232,21 @@ DOT_CASES = [
 ]
 
 
+def test_strided_convolution_input_gradient_with_skipped_k_tiles(client):
+    """Input gradient of stride-2 convolutions with 32-aligned channels: an input-dilated convolution whose rows
+    are visited phase by phase and whose dead k-tiles (window positions that only meet dilation holes) are
+    skipped; 3x3 and 1x1 kernels, odd and even extents."""
+    for (n, h, w, ci, co, k, pad) in [(4, 16, 16, 64, 64, 3, 1), (2, 15, 13, 32, 96, 3, 1), (8, 8, 8, 64, 128, 1, 0),
+                                      (96, 16, 16, 64, 64, 3, 1)]:
+        b = Builder()
+        x, wt = b.arg((n, h, w, ci), "f32"), b.arg((k, k, ci, co), "f32")
+        y = b.conv(x, wt, strides=(2, 2), padding=((pad, pad), (pad, pad)))
+        g = b.arg(y.shape, "f32")
+        dx, dw = b.grad(b.reduce_sum(b.mul(y, g), (0, 1, 2, 3)), [x, wt])
+        check(client, b.module([dx, dw]), [f32(n, h, w, ci), f32(k, k, ci, co), f32(*y.shape)],
+              rtol=1e-5, atol=1e-5, scale_atol=True)
+
+
 def test_contraction_results_are_reproducible(client):
     """Run-to-run bit equality on a split-K convolution with many k-tiles per CTA (the shape on which reading the
     accumulator before the last MMAs had retired once showed up as sporadic errors in single output tiles)."""

@@ -104,6 +104,8 @@ def test_resnet_full_size_step_properties(client):
     prog = programs.resnet18_train_step(batch=128)
     args = programs.resnet18_inputs(prog)
     outs, exe = run_gpu(client, prog.text, args)
+    # the input gradients of the three strided stages run with phase-ordered rows and k-tile lists
+    assert exe.plan_text().count("ktlist") == 6
     names = [n for n, _, _ in prog.args]
     P = {n[2:]: a for n, a in zip(names, args) if n.startswith("p.")}
     M = {n[2:]: a for n, a in zip(names, args) if n.startswith("m.")}
