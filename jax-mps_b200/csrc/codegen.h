@@ -42,6 +42,7 @@ class Emitter {
 
   std::string emit(Value* v, Ctx c);
   std::string input_name(Value* v);
+  void seed_inputs(const std::vector<Value*>& vs) { for (Value* v : vs) input_name(v); }   // fix the first parameters
   void line(const std::string& s);
   std::string fresh(const char* prefix);
   void ensure_idx(Ctx& c);

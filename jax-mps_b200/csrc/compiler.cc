@@ -693,8 +693,12 @@ struct Planner {
     std::vector<int64_t> in_shape, dims;
   };
 
+  // `epilogue`: pointwise groups over the kept index space that are evaluated by the thread holding the final
+  // value of each output (second pass of a split reduction only); `bound_results` are the reduce results their
+  // expressions refer to, in accumulator order.
   Launch gen_reduce_kernel(const ReduceGen& rg, std::function<bool(Op*)> internal, int splits, bool col,
-                           std::vector<Value*> outs) {
+                           std::vector<Value*> outs, const std::vector<Group*>* epilogue = nullptr,
+                           const std::vector<Value*>* bound_results = nullptr, BlockState* est = nullptr) {
     size_t n = 0;
     std::vector<DT> dts;
     std::vector<Value*> all_inits;
@@ -795,6 +799,33 @@ struct Planner {
         init_names.push_back(e);
       }
     }
+    // epilogue code (before the signature is printed: it adds outputs and inputs)
+    std::string epi;
+    if (epilogue && !epilogue->empty()) {
+      Emitter ee;
+      ee.idx_t = em.idx_t;
+      ee.name_prefix = "e";
+      ee.indent_ = 4;
+      ee.seed_inputs(ins);
+      for (size_t k = 0; k < bound_results->size(); k++) ee.bound[(*bound_results)[k]] = "acc" + std::to_string(k);
+      ee.is_internal = [&](Op* o) {
+        for (Group* eg : *epilogue) if (eg->members.count(o)) return true;
+        return is_dup(o) && !est->dup_materialize.count(o) && !slot_of.count(o->results[0]);
+      };
+      Ctx ec;
+      ec.shape = kept_shape;
+      ec.lin = "o";
+      ee.ensure_idx(ec);
+      std::vector<std::pair<Value*, std::string>> stores;
+      for (Group* eg : *epilogue)
+        for (Op* r : eg->roots) stores.push_back({r->results[0], ee.emit(r->results[0], ec)});
+      for (auto& st2 : stores) {
+        ee.line("out" + std::to_string(outs.size()) + "[o] = " + store_expr(st2.first->type.dt, st2.second) + ";");
+        outs.push_back(st2.first);
+      }
+      epi = ee.str();
+      ins = ee.inputs;
+    }
     std::ostringstream src;
     const char* it = em.idx_t.c_str();
     Launch L;
@@ -831,6 +862,7 @@ struct Planner {
       for (size_t k = 0; k < n; k++)
         src << "    out" << k << "[(" << it << ")blockIdx.y * " << Nk << " + o] = "
             << store_expr(outs[k]->type.dt, "acc" + std::to_string(k)) << ";\n";
+      src << epi;
       src << "  }\n}\n";
       L.grid[0] = (unsigned)((Nk + TX - 1) / TX); L.grid[1] = (unsigned)splits; L.grid[2] = 1;
       L.block[0] = TX; L.block[1] = TY; L.block[2] = 1;
@@ -883,6 +915,7 @@ struct Planner {
       for (size_t k = 0; k < n; k++)
         src << "    out" << k << "[(" << it << ")blockIdx.y * " << Nk << " + o] = "
             << store_expr(outs[k]->type.dt, "acc" + std::to_string(k)) << ";\n";
+      src << epi;
       src << "  }\n}\n";
       L.grid[0] = (unsigned)((Nk + per_block - 1) / per_block); L.grid[1] = (unsigned)splits; L.grid[2] = 1;
       L.block[0] = 256; L.block[1] = L.block[2] = 1;
@@ -1417,9 +1450,57 @@ struct Planner {
     add_launch(plan, L1, group_label(g) + ".partial", st);
     r2.in_shape = partials[0]->type.dims;
     r2.dims = {0};
+    // Pointwise kernels over the reduced shape whose inputs are all at hand once the sums exist (the per-channel
+    // statistics, scale and shift of a batch norm, the gradient updates of its scale and bias) are evaluated by the
+    // thread that holds the final sums instead of being launched on their own.
+    std::vector<Group*> epi;
+    std::string epi_label;
+    if (opts.fuse && Nk <= 65536) {
+      bool all_f32 = true;
+      for (auto* o : outs) all_f32 = all_f32 && o->type.dt == DT::F32;
+      std::set<Value*> at_hand(outs.begin(), outs.end());
+      std::function<bool(Value*)> avail = [&](Value* v) -> bool {
+        if (at_hand.count(v) || slot_of.count(v)) return true;
+        Op* d = v->def;
+        if (!d || d->parent != st.block) return false;
+        if (is_dup(d) && !st.dup_materialize.count(d)) {
+          for (auto* o : d->operands) if (!avail(o)) return false;
+          return true;
+        }
+        return false;
+      };
+      bool grew = all_f32;
+      while (grew && epi.size() < 6) {
+        grew = false;
+        for (auto& cand : st.groups) {
+          Group* e = &cand;
+          if (e->is_reduce || e->members.empty() || emitted.count(e) || absorbed.count(e) || e->members.size() > 48) continue;
+          bool ok = true;
+          for (Op* r : e->roots) ok = ok && r->results.size() == 1 && r->results[0]->type.dims == outs[0]->type.dims &&
+                                       categorize(r) == Cat::ELEMENTWISE;
+          bool uses_result = false;
+          for (Op* m : e->members) {
+            if (!ok) break;
+            if (categorize(m) != Cat::ELEMENTWISE && !is_dup(m)) { ok = false; break; }
+            for (Value* o : m->operands) {
+              if (o->def && e->members.count(o->def)) continue;
+              if (at_hand.count(o)) uses_result = true;
+              if (!avail(o)) { ok = false; break; }
+            }
+          }
+          if (!ok || !uses_result) continue;
+          epi.push_back(e);
+          absorbed.insert(e);
+          for (Op* r : e->roots) at_hand.insert(r->results[0]);
+          epi_label += "+" + group_label(e);
+          grew = true;
+          if (epi.size() >= 6) break;
+        }
+      }
+    }
     // few outputs: one warp per output walks the partials (a column kernel would run as two or three blocks)
-    Launch L2 = gen_reduce_kernel(r2, [](Op*) { return false; }, 1, Nk >= 2048, outs);
-    add_launch(plan, L2, group_label(g) + ".final", st);
+    Launch L2 = gen_reduce_kernel(r2, [](Op*) { return false; }, 1, Nk >= 2048, outs, &epi, &outs, &st);
+    add_launch(plan, L2, group_label(g) + ".final" + epi_label, st);
   }
 
   void materialize_dup(Op* op, Plan& plan, BlockState& st) {
@@ -1660,7 +1741,11 @@ struct Planner {
 
     for (int ui : order) {
       Unit& u = units[ui];
-      if (u.kind == Unit::GROUP) { emit_group(u.group, plan, st); continue; }
+      if (u.kind == Unit::GROUP) {
+        if (!absorbed.count(u.group)) emit_group(u.group, plan, st);
+        emitted.insert(u.group);
+        continue;
+      }
       if (u.kind == Unit::CONST_MAT) { materialize_dup(u.op, plan, st); continue; }
       Op* op = u.op;
       Cat c = categorize(op);
@@ -1905,6 +1990,7 @@ struct Planner {
   }
 
   std::set<int> persistent;
+  std::set<Group*> absorbed, emitted;     // pointwise groups folded into a reduction's second pass / groups already planned
 };
 
 void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& os, int indent) {
