@@ -160,6 +160,36 @@ struct Inliner {
         return;
       }
     }
+    // convolution whose kernel is a stablehlo.reverse over kernel-spatial dimensions (the input gradient of a
+    // convolution): the reversal is folded into the B index table instead of materialising the flipped kernel
+    if (sh == "convolution" && op->operands.size() == 2 && op->operands[1]->def &&
+        op->operands[1]->def->short_name() == "reverse" && !op->has("b200.rhs_reversed")) {
+      Op* rev = op->operands[1]->def;
+      const std::string& dn = op->attr("dimension_numbers");
+      size_t a1 = dn.find(']'), b0 = dn.find('[', a1), b1 = dn.find(']', b0);
+      if (a1 != std::string::npos && b0 != std::string::npos && b1 != std::string::npos) {
+        std::vector<int64_t> spatial;          // kernel dimensions labelled with a digit
+        int64_t d = 0;
+        std::string cur;
+        for (size_t k = b0 + 1; k <= b1; k++) {
+          char ch = dn[k];
+          if (ch == ',' || ch == ']') {
+            if (!cur.empty() && isdigit((unsigned char)cur[0])) spatial.push_back(d);
+            cur.clear();
+            d++;
+          } else if (!isspace((unsigned char)ch)) cur += ch;
+        }
+        std::vector<int64_t> rd = attr_i64s(rev->attr("dimensions"));
+        bool ok = !rd.empty();
+        for (auto x : rd) ok = ok && std::find(spatial.begin(), spatial.end(), x) != spatial.end();
+        if (ok) {
+          std::string txt = "[";
+          for (size_t k = 0; k < rd.size(); k++) txt += (k ? ", " : "") + std::to_string(rd[k]);
+          op->attrs["b200.rhs_reversed"] = txt + "]";
+          op->operands[1] = res(rev->operands[0]);
+        }
+      }
+    }
     // dot_general / convolution on bf16 or f16 operands: computed as the f32 contraction of the converted
     // operands and rounded once at the end. Products of two bf16 (or f16) numbers and their fp32 accumulation
     // are what XLA's CPU backend computes for these types; the converts fuse into neighbouring kernels.
@@ -1064,10 +1094,13 @@ struct Planner {
     }
     std::vector<ColEnt> acol(p.K);
     std::vector<long long> bcol(p.K);
+    bool rev0 = false, rev1 = false;              // kernel-spatial dimensions read back to front (folded stablehlo.reverse)
+    if (op->has("b200.rhs_reversed"))
+      for (auto d : attr_i64s(op->attr("b200.rhs_reversed"))) { rev0 = rev0 || d == r0; rev1 = rev1 || (!one_d && d == r1); }
     for (int64_t k = 0; k < p.K; k++) {
       int64_t c = k % Cg, kw = (k / Cg) % KW, kh = k / (Cg * KW);
       acol[k] = {c * sl[lf], (int)(kh * rdil[0]), (int)(kw * rdil[1])};
-      bcol[k] = c * sr[ri] + kh * sr[r0] + kw * sr1;
+      bcol[k] = c * sr[ri] + (rev0 ? KH - 1 - kh : kh) * sr[r0] + (rev1 ? KW - 1 - kw : kw) * sr1;
     }
     std::vector<long long> bn(p.N), cn(p.N), ag(groups), bg(groups), cg(groups);
     for (int64_t n = 0; n < p.N; n++) { bn[n] = n * sr[ro]; cn[n] = n * so[of]; }
