@@ -17,6 +17,7 @@
 #include <functional>
 #include <queue>
 #include <set>
+#include <tuple>
 #include <sstream>
 
 #include "codegen.h"
@@ -190,6 +191,107 @@ struct Inliner {
         }
       }
     }
+    // Convolutions whose innermost input dimension is a small channel count that is not a multiple of four (an RGB
+    // stem, forward and weight gradient) cannot be gathered 16 bytes at a time. The input is zero-padded to four
+    // channels (and the kernel's input-feature dimension with it, or the weight gradient sliced back), which moves
+    // them from the scalar-gather kernel to the vector paths.
+    if (sh == "convolution" && op->operands.size() == 2 && op->results.size() == 1 &&
+        (!op->has("feature_group_count") || attr_int(op->attr("feature_group_count")) == 1) &&
+        (!op->has("batch_group_count") || attr_int(op->attr("batch_group_count")) == 1)) {
+      const std::string& dn = op->attr("dimension_numbers");
+      auto spec = [&](size_t from, size_t& end) {
+        std::vector<std::string> toks;
+        size_t b0 = dn.find('[', from), b1 = dn.find(']', b0);
+        end = b1;
+        if (b0 == std::string::npos || b1 == std::string::npos) return toks;
+        std::string cur;
+        for (size_t k = b0 + 1; k <= b1; k++) {
+          if (dn[k] == ',' || dn[k] == ']') { toks.push_back(cur); cur.clear(); }
+          else if (!isspace((unsigned char)dn[k])) cur += dn[k];
+        }
+        return toks;
+      };
+      size_t e1 = 0, e2 = 0, e3 = 0;
+      auto ls = spec(0, e1);
+      auto rs = e1 != std::string::npos ? spec(e1, e2) : std::vector<std::string>{};
+      auto os = e2 != std::string::npos ? spec(e2, e3) : std::vector<std::string>{};
+      auto pos = [](const std::vector<std::string>& v, const char* c) { for (size_t k = 0; k < v.size(); k++) if (v[k] == c) return (int)k; return -1; };
+      Value *lhs = op->operands[0], *rhs = op->operands[1];
+      const int rank = lhs->type.rank();
+      const int lb = pos(ls, "b"), lf = pos(ls, "f"), ri = pos(rs, "i"), ob = pos(os, "b");
+      auto pad_dim = [&](Value* v, int dim, int64_t to) -> Value* {
+        auto key = std::make_tuple(v, dim, to);
+        auto it = padded.find(key);
+        if (it != padded.end()) return it->second;
+        TensorType st;
+        st.dt = v->type.dt;
+        auto zc = std::make_unique<Op>();
+        zc->name = "stablehlo.constant";
+        zc->attrs["value"] = "dense<0.000000e+00> : " + st.str();
+        Value* zero = m.new_value(st, "");
+        zero->def = zc.get();
+        zero->def_index = 0;
+        zc->results.push_back(zero);
+        zc->parent = b;
+        b->ops.push_back(std::move(zc));
+        auto pd = std::make_unique<Op>();
+        pd->name = "stablehlo.pad";
+        pd->operands = {v, zero};
+        std::string lo = "array<i64: ", hi = "array<i64: ";
+        for (int k = 0; k < v->type.rank(); k++) {
+          lo += std::string(k ? ", " : "") + "0";
+          hi += std::string(k ? ", " : "") + std::to_string(k == dim ? to - v->type.dims[k] : 0);
+        }
+        pd->attrs["edge_padding_low"] = lo + ">";
+        pd->attrs["edge_padding_high"] = hi + ">";
+        pd->attrs["interior_padding"] = lo + ">";
+        TensorType pt = v->type;
+        pt.dims[dim] = to;
+        Value* out = m.new_value(pt, "");
+        out->def = pd.get();
+        out->def_index = 0;
+        pd->results.push_back(out);
+        pd->parent = b;
+        b->ops.push_back(std::move(pd));
+        padded[key] = out;
+        return out;
+      };
+      if (rank >= 3 && lb >= 0 && lf >= 0 && ri >= 0 && ob >= 0 && (int)ls.size() == rank && dt_is_float(lhs->type.dt)) {
+        const int64_t Cin = lhs->type.dims[lf], Nb = lhs->type.dims[lb];
+        if (lf == rank - 1 && Cin % 4 != 0 && Cin < 16 && rhs->type.dims[ri] == Cin) {
+          const int64_t to = (Cin + 3) / 4 * 4;
+          op->operands[0] = pad_dim(lhs, lf, to);
+          op->operands[1] = pad_dim(rhs, ri, to);
+        } else if (lb == rank - 1 && Nb % 4 != 0 && Nb < 16 && op->results[0]->type.dims[ob] == Nb) {
+          const int64_t to = (Nb + 3) / 4 * 4;
+          op->operands[0] = pad_dim(lhs, lb, to);
+          // the convolution now yields `to` slices along the output's batch dimension; the first Nb are the result
+          Value* orig = op->results[0];
+          TensorType wt = orig->type;
+          wt.dims[ob] = to;
+          Value* wide = m.new_value(wt, "");
+          wide->def = op.get();
+          wide->def_index = 0;
+          op->results[0] = wide;
+          auto sl = std::make_unique<Op>();
+          sl->name = "stablehlo.slice";
+          sl->operands = {wide};
+          std::string st0 = "array<i64: ", lim = "array<i64: ", one = "array<i64: ";
+          for (int k = 0; k < orig->type.rank(); k++) {
+            st0 += std::string(k ? ", " : "") + "0";
+            lim += std::string(k ? ", " : "") + std::to_string(orig->type.dims[k]);
+            one += std::string(k ? ", " : "") + "1";
+          }
+          sl->attrs["start_indices"] = st0 + ">";
+          sl->attrs["limit_indices"] = lim + ">";
+          sl->attrs["strides"] = one + ">";
+          orig->def = sl.get();
+          orig->def_index = 0;
+          sl->results.push_back(orig);
+          deferred.push_back(std::move(sl));
+        }
+      }
+    }
     // dot_general / convolution on bf16 or f16 operands: computed as the f32 contraction of the converted
     // operands and rounded once at the end. Products of two bf16 (or f16) numbers and their fp32 accumulation
     // are what XLA's CPU backend computes for these types; the converts fuse into neighbouring kernels.
@@ -223,6 +325,8 @@ struct Inliner {
           op->parent = b;
           b->ops.push_back(std::move(op));
           convert_to(wide, orig->type.dt, orig);
+          for (auto& d : deferred) { d->parent = b; b->ops.push_back(std::move(d)); }
+          deferred.clear();
           return;
         }
       }
@@ -230,7 +334,11 @@ struct Inliner {
     for (auto& reg : op->regions) run(reg.get());
     op->parent = b;
     b->ops.push_back(std::move(op));
+    for (auto& d : deferred) { d->parent = b; b->ops.push_back(std::move(d)); }
+    deferred.clear();
   }
+  std::map<std::tuple<Value*, int, int64_t>, Value*> padded;   // zero-padded copies made for convolutions
+  std::vector<std::unique_ptr<Op>> deferred;                   // ops to place right after the one being processed
 };
 
 void fix_region_operands(Block* b, Inliner& inl) {

@@ -247,6 +247,18 @@ def test_strided_convolution_input_gradient_with_skipped_k_tiles(client):
               rtol=1e-5, atol=1e-5, scale_atol=True)
 
 
+@pytest.mark.parametrize("ci", [1, 3, 5, 7])
+def test_small_channel_convolution_and_gradients(client, ci):
+    """Convolutions whose input has a few channels (not a multiple of 4): forward, input gradient and weight
+    gradient; the compiler pads the channels with zeros to reach the 16-byte gather paths."""
+    b = Builder()
+    x, wt = b.arg((6, 10, 9, ci), "f32"), b.arg((3, 3, ci, 24), "f32")
+    y = b.conv(x, wt, padding=((1, 1), (1, 1)))
+    g = b.arg(y.shape, "f32")
+    dx, dw = b.grad(b.reduce_sum(b.mul(y, g), (0, 1, 2, 3)), [x, wt])
+    check(client, b.module([y, dx, dw]), [f32(6, 10, 9, ci), f32(3, 3, ci, 24), f32(*y.shape)], rtol=1e-5, atol=1e-5, scale_atol=True)
+
+
 def test_contraction_results_are_reproducible(client):
     """Run-to-run bit equality on a split-K convolution with many k-tiles per CTA (the shape on which reading the
     accumulator before the last MMAs had retired once showed up as sporadic errors in single output tiles)."""
