@@ -815,6 +815,62 @@ struct Planner {
     return L;
   }
 
+  // dynamic_update_slice of a loop-carried tensor written back to the same position of the loop state: the result
+  // shares the state's memory and the kernel stores only the update window (one thread per update element)
+  // instead of rewriting the whole tensor every iteration. Start indices are clamped as in the general form.
+  Launch gen_window_update(Group* g, BlockState& st) {
+    Op* d = g->roots[0];
+    Value* out = d->results[0];
+    Value* u = d->operands[1];
+    const std::vector<int64_t>& od = out->type.dims;
+    const int64_t n = u->type.numel();
+    Emitter em;
+    em.is_internal = [&](Op* o) {
+      return (o != d && g->members.count(o)) || (is_dup(o) && !st.dup_materialize.count(o) && !slot_of.count(o->results[0]));
+    };
+    std::vector<Value*> all{out};
+    for (auto* m : g->members) {
+      all.push_back(m->results[0]);
+      for (auto* o : m->operands) all.push_back(o);
+    }
+    em.idx_t = idx_type_for(all, n + kThreads * kEPT);
+    Ctx uc;
+    uc.shape = u->type.dims;
+    uc.lin = "lin";
+    em.ensure_idx(uc);
+    std::string dst;
+    int64_t stride = 1;
+    std::vector<int64_t> strides(od.size());
+    for (size_t i = od.size(); i-- > 0;) { strides[i] = stride; stride *= od[i]; }
+    for (size_t i = 0; i < od.size(); i++) {
+      Ctx sc;
+      sc.lin = "0";
+      std::string sv = em.emit(d->operands[2 + i], sc);
+      std::string nv = em.fresh("s");
+      em.line("const " + em.idx_t + " " + nv + " = (" + em.idx_t + ")min(max((i64)" + sv + ", (i64)0), (i64)" +
+              std::to_string(od[i] - u->type.dims[i]) + ");");
+      dst += std::string(i ? " + " : "") + "(" + nv + " + " + uc.idx[i] + ") * (" + em.idx_t + ")" + std::to_string(strides[i]) + "LL";
+    }
+    std::string val = em.emit(u, uc);
+    em.line("out0[" + dst + "] = " + store_expr(out->type.dt, val) + ";");
+    std::ostringstream src;
+    src << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(" << signature({out}, em.inputs) << ") {\n";
+    src << "  #pragma unroll\n  for (int e = 0; e < " << kEPT << "; ++e) {\n";
+    src << "    const " << em.idx_t << " lin = ((" << em.idx_t << ")blockIdx.x * " << kEPT << " + e) * " << kThreads
+        << " + threadIdx.x;\n";
+    src << "    if (lin >= (" << em.idx_t << ")" << n << "LL) break;\n";
+    src << em.str();
+    src << "  }\n}\n";
+    Launch L;
+    L.kernel = add_kernel(src.str(), "fused");
+    int64_t blocks = std::max<int64_t>(1, (n + (int64_t)kThreads * kEPT - 1) / ((int64_t)kThreads * kEPT));
+    L.grid[0] = (unsigned)blocks; L.grid[1] = L.grid[2] = 1;
+    L.block[0] = kThreads; L.block[1] = L.block[2] = 1;
+    L.outs = {out};
+    L.ins = em.inputs;
+    return L;
+  }
+
   // A reduction kernel over `in_shape` along `dims`. `operands` are evaluated by
   // the emitter (fusion members inline). Writes `outs` (kept-dims shape) or,
   // when `splits` > 1, partial results laid out [split][kept].
@@ -1514,6 +1570,13 @@ struct Planner {
         for (auto* r : g->roots) ensure_slot(r->results[0], st);
         return;
       }
+      if (g->roots.size() == 1 && window_updates.count(g->roots[0])) {
+        Op* d = g->roots[0];
+        slot_of[d->results[0]] = slot_of.at(d->operands[0]);
+        Launch L = gen_window_update(g, st);
+        add_launch(plan, L, group_label(g) + ".window", st);
+        return;
+      }
       Launch L = gen_pointwise(g, st);
       add_launch(plan, L, group_label(g), st);
       return;
@@ -1952,6 +2015,24 @@ struct Planner {
           pc->arena = a_cond;
           pb->arena = a_body;
           plan_block(cond, *pc, a_cond, cret->operands);
+          for (size_t k = 0; k < n; k++) {
+            // state k is only ever updated in a window and handed back at position k: update it in place
+            Value* r = bret->operands[k];
+            Op* d = r->def;
+            if (!d || d->parent != body || d->short_name() != "dynamic_update_slice" || d->operands[0] != body->args[k]) continue;
+            std::function<int(Block*, Value*)> uses = [&](Block* blk, Value* v) {
+              int c = 0;
+              for (auto& o : blk->ops) {
+                c += (int)std::count(o->operands.begin(), o->operands.end(), v);
+                for (auto& reg : o->regions) c += uses(reg.get(), v);
+              }
+              return c;
+            };
+            // the old tensor has no other reader and the new one goes nowhere but back into the loop state
+            if (uses(body, body->args[k]) != 1 || uses(body, r) != 1) continue;
+            if (r->type.dims.empty() || r->type.numel() == 0 || getenv("B200_NO_WINDOW_UPDATE")) continue;
+            window_updates.insert(d);
+          }
           plan_block(body, *pb, a_body, bret->operands);
           s.pred = slot_of.at(cret->operands[0]);
           persistent.insert(s.pred);
@@ -1971,6 +2052,19 @@ struct Planner {
             }
             persistent.insert(ns);
             s.next.push_back(ns);
+          }
+          // A carried value whose next value is a temporary of the body written once per iteration needs no copy:
+          // the runtime exchanges the two pointers after each iteration. The body temporary then holds the state
+          // during the following iteration, so it owns its memory for the whole body.
+          s.swap.assign(n, 0);
+          for (size_t k = 0; k < n; k++) {
+            const int ns = s.next[k];
+            const Slot& sn = prog.slots[ns];
+            if (ns == s.state[k] || sn.kind != Slot::TEMP || sn.arena != a_body) continue;
+            if (sn.bytes != prog.slots[s.state[k]].bytes || sn.bytes == 0) continue;
+            if (std::count(s.next.begin(), s.next.end(), ns) != 1) continue;
+            s.swap[k] = 1;
+            whole_plan.insert(ns);
           }
           s.sub.push_back(std::move(pc));
           s.sub.push_back(std::move(pb));
@@ -2099,6 +2193,8 @@ struct Planner {
     // slots marked persistent (results of nested blocks) live to the end
     for (int ps : persistent)
       if (live.count(ps)) live[ps].second = (int)S;
+    for (int ps : whole_plan)
+      if (live.count(ps)) live[ps] = {0, (int)S};
     for (auto& sub_steps : plan.steps)
       for (auto& sp : sub_steps.sub) layout_arena(*sp);
     // greedy first-fit by start time
@@ -2131,6 +2227,8 @@ struct Planner {
   }
 
   std::set<int> persistent;
+  std::set<Op*> window_updates;       // dynamic_update_slice ops of loop bodies that update their loop state in place
+  std::set<int> whole_plan;           // slots that own their memory for their whole plan (exchanged loop state)
   std::set<Group*> absorbed, emitted;     // pointwise groups folded into a reduction's second pass / groups already planned
 };
 
@@ -2147,7 +2245,9 @@ void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& o
            << " a_contig=" << s.ig.a_contig << " b_contig=" << s.ig.b_contig << " vec=" << s.ig.vec << " seg=" << s.ig.seg << (s.ig.kt_stride ? " ktlist" : "") << " " << s.label;
         break;
       case Step::MEMCPY: os << "memcpy " << s.bytes; break;
-      case Step::WHILE: os << "while trip=" << s.trip_count; break;
+      case Step::WHILE:
+        os << "while trip=" << s.trip_count << " exchanged=" << std::count(s.swap.begin(), s.swap.end(), (char)1) << "/" << s.state.size();
+        break;
       case Step::CASE: os << "case branches=" << s.sub.size(); break;
       case Step::SCATTER: os << "scatter rows=" << s.iparams[0] << " row_elems=" << s.iparams[1] << " updates=" << s.iparams[2]; break;
       case Step::ALL_REDUCE: os << "all_reduce " << s.bytes << " bytes"; break;

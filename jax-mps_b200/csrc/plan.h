@@ -63,6 +63,7 @@ struct Step {
   // CASE: sub = branches; args = {index}; branch_results[b][i] copied to results[i]
   std::vector<std::unique_ptr<Plan>> sub;
   std::vector<int> state, init, next;
+  std::vector<char> swap;             // WHILE: per carried value, exchange the state and next pointers instead of copying
   std::vector<std::vector<int>> branch_results;
   std::vector<int> results;
   int pred = -1;

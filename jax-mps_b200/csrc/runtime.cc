@@ -581,12 +581,34 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
         size_t b = x.lp->prog->slots[s.state[k]].type.bytes();
         if (d != src && b) CUDA_TRY(cudaMemcpyAsync(d, src, b, cudaMemcpyDeviceToDevice, st));
       }
+      // carried values marked for exchange trade pointers with their next value after every iteration; when the
+      // loop ends the pointers go back and a value left in the other buffer is copied home once
+      std::vector<void*> home_state(n), home_next(n);
+      for (size_t k = 0; k < n; k++) {
+        home_state[k] = x.ptrs[s.state[k]];
+        home_next[k] = x.ptrs[s.next[k]];
+      }
       auto iterate = [&]() -> b200_error* {
         if (auto* e = run_plan(x, *s.sub[1])) return e;
         for (size_t k = 0; k < n; k++) {
+          if (k < s.swap.size() && s.swap[k]) {
+            std::swap(x.ptrs[s.state[k]], x.ptrs[s.next[k]]);
+            continue;
+          }
           void *d = x.ptrs[s.state[k]], *src = x.ptrs[s.next[k]];
           size_t b = x.lp->prog->slots[s.state[k]].type.bytes();
           if (d != src && b) CUDA_TRY(cudaMemcpyAsync(d, src, b, cudaMemcpyDeviceToDevice, st));
+        }
+        return nullptr;
+      };
+      auto finish = [&]() -> b200_error* {
+        for (size_t k = 0; k < n; k++) {
+          if (!(k < s.swap.size() && s.swap[k])) continue;
+          void* cur = x.ptrs[s.state[k]];
+          x.ptrs[s.state[k]] = home_state[k];
+          x.ptrs[s.next[k]] = home_next[k];
+          size_t b = x.lp->prog->slots[s.state[k]].type.bytes();
+          if (cur != home_state[k] && b) CUDA_TRY(cudaMemcpyAsync(home_state[k], cur, b, cudaMemcpyDeviceToDevice, st));
         }
         return nullptr;
       };
@@ -595,7 +617,7 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
         // (the reference's counted path, src/pjrt_plugin/ops/control_flow.cc:476-503)
         for (long long i = 0; i < s.trip_count; i++)
           if (auto* e = iterate()) return e;
-        return nullptr;
+        return finish();
       }
       for (long long it = 0;; it++) {
         if (auto* e = run_plan(x, *s.sub[0])) return e;
@@ -604,7 +626,7 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
         if (!*c->pred_host) break;
         if (auto* e = iterate()) return e;
       }
-      return nullptr;
+      return finish();
     }
     case Step::SCATTER: {
       void *operand = x.ptrs[s.args[0]], *out = x.ptrs[s.args[3]];

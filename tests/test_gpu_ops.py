@@ -406,7 +406,46 @@ def test_scan_with_dynamic_slices(client):
         ys2 = s.dynamic_update_slice(ys, s.reshape(h2, (1, N)), [t, z])
         return [s.add(t, s.const(1, "i32")), h2, ys2]
     outs = b.while_([b.const(0, "i32"), h0, ys0], cond, body)
-    check(client, b.module(outs), [f32(T, N), f32(N)], rtol=2e-5)
+    _, exe = check(client, b.module(outs), [f32(T, N), f32(N)], rtol=2e-5)
+    assert ".window" in exe.plan_text()      # ys is updated in place, one window per iteration
+
+
+def test_in_place_window_update_clamps(client):
+    """A loop-carried tensor updated in place through a two-row window whose start runs from below zero to past
+    the end: the start is clamped like the general dynamic_update_slice (src/pjrt_plugin/ops/slice.cc:80-107)."""
+    T, N = 9, 40
+    b = Builder()
+    ys0, u0 = b.arg((T, N), "f32"), b.arg((2, N), "f32")
+    def cond(s, t, u, ys): return s.compare(t, s.const(8, "i32"), "LT")
+    def body(s, t, u, ys):
+        start = s.sub(s.mul(t, s.const(2, "i32")), s.const(3, "i32"))
+        u2 = s.add(u, s.full((2, N), 1.0, "f32"))
+        ys2 = s.dynamic_update_slice(ys, s.mul(u, s.full((2, N), 0.5, "f32")), [start, s.const(0, "i32")])
+        return [s.add(t, s.const(1, "i32")), u2, ys2]
+    outs = b.while_([b.const(0, "i32"), u0, ys0], cond, body)
+    _, exe = check(client, b.module(outs), [f32(T, N), f32(2, N)], rtol=1e-6)
+    assert ".window" in exe.plan_text()
+
+
+def test_loop_state_pointer_exchange(client):
+    """Carried values trade buffers with their next values instead of being copied. The body reads a carried
+    value late (after temporaries have come and gone), returns one value at two positions and passes one through;
+    odd and even trip counts leave the final values in either buffer."""
+    N = 4096
+    for trips in (1, 6, 7):
+        b = Builder()
+        x, y = b.arg((N,), "f32"), b.arg((N,), "f32")
+        def cond(s, i, a, c, d, e): return s.compare(i, s.const(trips, "i32"), "LT")
+        def body(s, i, a, c, d, e):
+            t1 = s.tanh(s.add(a, c))
+            t2 = s.reduce_sum(s.mul(t1, t1), [0])
+            t3 = s.mul(t1, s.broadcast_in_dim(t2, (N,), []))
+            a2 = s.add(s.mul(t3, s.full((N,), 1e-3, "f32")), c)
+            c2 = s.sub(a2, s.mul(a, s.full((N,), 0.5, "f32")))       # reads the old state after a2 exists
+            return [s.add(i, s.const(1, "i32")), a2, c2, c2, e]
+        outs = b.while_([b.const(0, "i32"), x, y, y, x], cond, body)
+        _, exe = check(client, b.module(outs), [f32(N), f32(N)], rtol=1e-4)
+        assert "exchanged=" in exe.plan_text()
 
 
 def test_row_scatter(client):
