@@ -282,7 +282,13 @@ struct LoadedProgram {
   std::vector<void*> const_ptrs;
   std::vector<void*> arenas;
   void* const_block = nullptr;
+  // Instantiated CUDA graphs of counted-loop bodies (two iterations each), per loop step and per set of slot
+  // addresses the graph was captured with.
+  struct LoopGraph { const void* step; std::vector<void*> ptrs; cudaGraphExec_t exec; int launches; };
+  std::vector<LoopGraph> loop_graphs;
   ~LoadedProgram() {
+    for (auto& g : loop_graphs)
+      if (g.exec) cudaGraphExecDestroy(g.exec);
     for (auto* a : arenas)
       if (a) cudaFree(a);
     if (const_block) cudaFree(const_block);
@@ -506,6 +512,21 @@ struct ExecCtx {
 
 b200_error* run_plan(ExecCtx& x, const Plan& plan);
 
+// A plan can be recorded into a CUDA graph when it only launches kernels and device copies: no host round trip
+// (data-dependent loops, case), no collective.
+bool graph_safe(const Plan& plan) {
+  for (const Step& s : plan.steps) {
+    switch (s.kind) {
+      case Step::KERNEL: case Step::IGEMM: case Step::MEMCPY: break;
+      case Step::WHILE:
+        if (s.trip_count < 0 || !graph_safe(*s.sub[1])) return false;
+        break;
+      default: return false;
+    }
+  }
+  return true;
+}
+
 b200_error* run_step(ExecCtx& x, const Step& s) {
   b200_client* c = x.c;
   cudaStream_t st = c->compute;
@@ -615,7 +636,60 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       if (s.trip_count >= 0) {
         // counted loop: trip count known at compile time, no host round trip
         // (the reference's counted path, src/pjrt_plugin/ops/control_flow.cc:476-503)
-        for (long long i = 0; i < s.trip_count; i++)
+        long long done = 0;
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        CUDA_TRY(cudaStreamIsCapturing(st, &capturing));
+        if (s.trip_count >= 4 && !c->profiling && capturing == cudaStreamCaptureStatusNone && graph_safe(*s.sub[1]) &&
+            !getenv("B200_NO_LOOP_GRAPHS")) {
+          // Two iterations (after which exchanged pointers are back where they started) are recorded once as a
+          // CUDA graph and replayed: the host issues one launch per pair instead of one per kernel, and the
+          // dependent kernels of a latency-bound body follow each other without a host round trip.
+          const long long pairs = s.trip_count / 2;
+          long long replayed = 0;
+          LoadedProgram::LoopGraph* hit = nullptr;
+          for (auto& g : x.lp->loop_graphs)
+            if (g.step == &s && g.ptrs == x.ptrs) { hit = &g; break; }
+          if (!hit) {
+            if (x.lp->loop_graphs.size() >= 16) {
+              // bounded cache: let the device finish with the oldest graph before it goes
+              CUDA_TRY(cudaStreamSynchronize(st));
+              cudaGraphExecDestroy(x.lp->loop_graphs.front().exec);
+              x.lp->loop_graphs.erase(x.lp->loop_graphs.begin());
+            }
+            const std::vector<void*> at_start = x.ptrs;
+            // the first pair runs directly, so that every kernel of the body has been loaded and configured
+            // before anything is recorded
+            if (auto* e = iterate()) return e;
+            if (auto* e = iterate()) return e;
+            replayed = 1;
+            const int before = x.launches;
+            CUDA_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed));
+            b200_error* err = iterate();
+            if (!err) err = iterate();
+            cudaGraph_t graph = nullptr;
+            cudaError_t ce = cudaStreamEndCapture(st, &graph);
+            if (err) {
+              if (graph) cudaGraphDestroy(graph);
+              return err;
+            }
+            CUDA_TRY(ce);
+            cudaGraphExec_t exec = nullptr;
+            ce = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            CUDA_TRY(ce);
+            if (x.ptrs != at_start) {
+              cudaGraphExecDestroy(exec);
+              return make_error(B200_INTERNAL, "loop state pointers did not return after two iterations");
+            }
+            x.lp->loop_graphs.push_back({&s, at_start, exec, x.launches - before});
+            x.launches = before;
+            hit = &x.lp->loop_graphs.back();
+          }
+          for (long long i = replayed; i < pairs; i++) CUDA_TRY(cudaGraphLaunch(hit->exec, st));
+          x.launches += (int)(hit->launches * (pairs - replayed));
+          done = 2 * pairs;
+        }
+        for (long long i = done; i < s.trip_count; i++)
           if (auto* e = iterate()) return e;
         return finish();
       }
