@@ -409,6 +409,7 @@ struct Planner {
   Module& mod;
   std::map<Value*, int> slot_of;
   std::map<std::string, int> kernel_cache;
+  std::vector<std::string> kernel_text;       // un-named source of every generated kernel, by kernel id
   std::deque<Value> synth_values;
   std::ostringstream dump;
   int next_group_id = 0;
@@ -453,11 +454,11 @@ struct Planner {
     KernelSource ks;
     ks.name = std::string(stem) + "_" + std::to_string(id);
     std::string body = body_without_name;
-    auto p = body.find("@NAME@");
-    body.replace(p, 6, ks.name);
+    for (auto p = body.find("@NAME@"); p != std::string::npos; p = body.find("@NAME@", p)) body.replace(p, 6, ks.name);
     ks.body = body;
     prog.kernels.push_back(ks);
     kernel_cache[body_without_name] = id;
+    kernel_text.push_back(body_without_name);
     return id;
   }
 
@@ -1145,7 +1146,10 @@ struct Planner {
     const long long per_wave = (!p.vec || half) ? 296 : 148;
     int best = 1;
     double best_cost = 1e30;
-    const int max_split = (int)std::min<long long>(592, std::max<long long>(1, ktiles / 8));
+    // a split keeps at least 8 k-tiles, except when the output has so few tiles that even then most of the GPU
+    // would idle (the small products of a recurrent cell): those go down to 2 k-tiles per CTA
+    const long long min_kt = tiles * 8 <= per_wave ? 2 : 8;
+    const int max_split = (int)std::min<long long>(592, std::max<long long>(1, ktiles / min_kt));
     for (int split = 1; split <= max_split; split++) {
       const long long waves = (tiles * split + per_wave - 1) / per_wave;
       const long long kt = (ktiles + split - 1) / split;
@@ -1540,6 +1544,7 @@ struct Planner {
     s.label = label;
     for (int k = 0; k < 3; k++) { s.grid[k] = L.grid[k]; s.block[k] = L.block[k]; }
     for (auto* o : L.outs) { ensure_slot(o, st); s.args.push_back(slot_of.at(o)); }
+    s.n_outs = (int)L.outs.size();
     for (auto* i : L.ins) {
       if (!slot_of.count(i)) throw CompileError("internal: kernel input without storage: " + i->name + " (" + label + ")");
       s.args.push_back(slot_of.at(i));
@@ -2155,6 +2160,107 @@ struct Planner {
       if (v->def && v->def->parent == block && is_dup(v->def)) { materialize_dup(v->def, plan, st); continue; }
       throw CompileError("internal: returned value without storage: " + v->name);
     }
+    bundle_independent_kernels(plan);
+  }
+
+  // ---- bundling of independent pointwise kernels --------------------------------------
+  // Adjacent pointwise launches that do not depend on one another (the window updates of a scan body, the
+  // accumulations at its end, optimizer updates of small parameters) become one launch: the bundle's grid is the
+  // concatenation of the parts' grids and each block runs the part its index falls into. The parts keep their code
+  // unchanged as device functions. Latency-bound plans pay per launch, so this is where their time goes.
+  struct BundlePart { int kernel; unsigned grid; };
+
+  int bundle_kernel(const std::vector<BundlePart>& parts) {
+    std::ostringstream fns, sig, body;
+    std::map<int, std::string> fn_of;
+    int pi = 0;
+    unsigned first = 0;
+    body << "  unsigned bid = blockIdx.x;\n";
+    for (size_t k = 0; k < parts.size(); k++) {
+      const std::string& text = kernel_text[parts[k].kernel];
+      const size_t name_at = text.find("@NAME@(");
+      const size_t sig_end = text.find(") {\n", name_at);
+      if (name_at == std::string::npos || sig_end == std::string::npos) return -1;
+      const std::string params = text.substr(name_at + 7, sig_end - name_at - 7);
+      if (!fn_of.count(parts[k].kernel)) {
+        std::string fn = "@NAME@_p" + std::to_string(fn_of.size());
+        std::string rest = text.substr(sig_end);          // ") {\n body }"
+        for (auto p = rest.find("blockIdx.x"); p != std::string::npos; p = rest.find("blockIdx.x", p)) rest.replace(p, 10, "bid");
+        fns << "static __device__ __forceinline__ void " << fn << "(const unsigned bid, " << params << rest << "\n";
+        fn_of[parts[k].kernel] = fn;
+      }
+      // parameter types of the part, renamed for the bundle's own signature
+      std::vector<std::string> names;
+      size_t at = 0;
+      while (at < params.size()) {
+        size_t comma = params.find(", ", at);
+        std::string one = params.substr(at, comma == std::string::npos ? std::string::npos : comma - at);
+        size_t sp = one.find_last_of(' ');
+        if (sp == std::string::npos) return -1;
+        std::string nm = "a" + std::to_string(pi++);
+        sig << (names.empty() && k == 0 ? "" : ", ") << one.substr(0, sp + 1) << nm;
+        names.push_back(nm);
+        if (comma == std::string::npos) break;
+        at = comma + 2;
+      }
+      body << "  if (bid < " << first + parts[k].grid << "u) { " << fn_of[parts[k].kernel] << "(bid - " << first << "u";
+      for (auto& nm : names) body << ", " << nm;
+      body << "); return; }\n";
+      first += parts[k].grid;
+    }
+    std::ostringstream src;
+    src << fns.str() << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(" << sig.str() << ") {\n"
+        << body.str() << "}\n";
+    return add_kernel(src.str(), "bundle");
+  }
+
+  void bundle_independent_kernels(Plan& plan) {
+    if (getenv("B200_NO_BUNDLES")) return;
+    auto eligible = [&](const Step& s) {
+      return s.kind == Step::KERNEL && s.block[0] == (unsigned)kThreads && s.block[1] == 1 && s.block[2] == 1 && s.grid[1] == 1 &&
+             s.grid[2] == 1 && s.n_outs > 0 && prog.kernels[s.kernel].name.rfind("fused_", 0) == 0;
+    };
+    std::vector<Step> out;
+    size_t i = 0;
+    while (i < plan.steps.size()) {
+      if (!eligible(plan.steps[i])) { out.push_back(std::move(plan.steps[i++])); continue; }
+      std::set<int> written, read;
+      size_t j = i, nargs = 0;
+      unsigned blocks = 0;
+      for (; j < plan.steps.size() && j - i < 16; j++) {
+        const Step& s = plan.steps[j];
+        if (!eligible(s) || nargs + s.args.size() > 256 || (uint64_t)blocks + s.grid[0] > (1u << 30)) break;
+        bool clash = false;
+        for (size_t a = 0; a < s.args.size(); a++) {
+          const bool w = (int)a < s.n_outs;
+          if (written.count(s.args[a]) || (w && read.count(s.args[a]))) clash = true;
+        }
+        if (clash) break;
+        for (size_t a = 0; a < s.args.size(); a++) ((int)a < s.n_outs ? written : read).insert(s.args[a]);
+        nargs += s.args.size();
+        blocks += s.grid[0];
+      }
+      int id = -1;
+      if (j - i >= 2) {
+        std::vector<BundlePart> parts;
+        for (size_t k = i; k < j; k++) parts.push_back({plan.steps[k].kernel, plan.steps[k].grid[0]});
+        id = bundle_kernel(parts);
+      }
+      if (id < 0) { out.push_back(std::move(plan.steps[i++])); continue; }
+      Step b;
+      b.kind = Step::KERNEL;
+      b.kernel = id;
+      b.grid[0] = blocks;
+      b.block[0] = kThreads;
+      b.n_outs = 0;                    // outputs and inputs interleave per part; bundles are not bundled again
+      for (size_t k = i; k < j; k++) {
+        b.label += (k > i ? " + " : "") + plan.steps[k].label;
+        b.args.insert(b.args.end(), plan.steps[k].args.begin(), plan.steps[k].args.end());
+      }
+      out.push_back(std::move(b));
+      i = j;
+    }
+    plan.steps = std::move(out);
   }
 
   int partition_id = 0;
@@ -2334,6 +2440,19 @@ std::unique_ptr<CompiledProgram> compile_module(Module& m, const CompileOptions&
     prog->results.push_back(ri);
   }
   pl.layout_arena(prog->main);
+  // kernels that ended up inside bundles only are not compiled on their own
+  {
+    std::set<int> used;
+    std::function<void(const Plan&)> mark = [&](const Plan& p) {
+      for (auto& s : p.steps) {
+        if (s.kind == Step::KERNEL) used.insert(s.kernel);
+        for (auto& sp : s.sub) mark(*sp);
+      }
+    };
+    mark(prog->main);
+    for (size_t k = 0; k < prog->kernels.size(); k++)
+      if (!used.count((int)k)) prog->kernels[k].body = "extern \"C\" __global__ void " + prog->kernels[k].name + "() {}\n";
+  }
   // static launch count
   {
     bool dynamic = false;
@@ -2345,7 +2464,7 @@ std::unique_ptr<CompiledProgram> compile_module(Module& m, const CompileOptions&
         else if (s.kind == Step::IGEMM) n += s.ig.split_k > 1 ? 2 : 1;
         else if (s.kind == Step::WHILE) {
           if (s.trip_count < 0) { dynamic = true; continue; }
-          n += (s.trip_count + 1) * count(*s.sub[0]) + s.trip_count * count(*s.sub[1]);
+          n += s.trip_count * count(*s.sub[1]);      // a counted loop never evaluates its condition
         } else if (s.kind == Step::CASE) dynamic = true;
       }
       return n;

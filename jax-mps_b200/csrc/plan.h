@@ -55,6 +55,7 @@ struct Step {
   int kernel = -1;                    // index into Executable::kernels
   unsigned grid[3] = {1, 1, 1}, block[3] = {1, 1, 1};
   std::vector<int> args;              // slot ids, in kernel-parameter order
+  int n_outs = 0;                     // KERNEL: the first n_outs args are written, the rest only read
   // IGEMM: args = {A, B, C, a_row, a_col, b_row(k), b_col(n), c_row(m), c_col(n), a_grp, b_grp, c_grp, [split-K scratch]}
   IGemmParams ig;
   // MEMCPY: args = {dst, src}; MEMSET: args = {dst}
