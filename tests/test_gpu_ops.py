@@ -448,6 +448,40 @@ def test_loop_state_pointer_exchange(client):
         assert "exchanged=" in exe.plan_text()
 
 
+def test_bundled_pointwise_kernels(client):
+    """Independent pointwise results of different shapes leave as one launch; a later kernel that reads one of
+    them stays separate. Values must equal the unbundled evaluation (the oracle)."""
+    b = Builder()
+    x, y, z = b.arg((1000,), "f32"), b.arg((7, 33), "f32"), b.arg((5000,), "f32")
+    a1 = b.tanh(x)
+    a2 = b.mul(y, y)
+    a3 = b.add(z, b.full((5000,), 2.0, "f32"))
+    s1 = b.reduce_sum(a3, [0])                       # forces a3 into memory before the dependent kernel
+    a4 = b.mul(a3, b.broadcast_in_dim(s1, (5000,), []))
+    _, exe = check(client, b.module([a1, a2, a3, a4]), [f32(1000), f32(7, 33), f32(5000)], rtol=1e-5)
+    plan = exe.plan_text()
+    assert "bundle_" in plan and plan.count("kernel ") < 6
+
+
+def test_counted_loop_graph_replay_odd_and_even(client):
+    """Counted loops of four or more iterations replay a recorded pair of iterations; odd counts run the last
+    iteration directly. Executing twice reuses the recorded graph."""
+    for trips in (4, 5, 11, 130):
+        b = Builder()
+        x = b.arg((300,), "f32")
+        def cond(s, i, v, w): return s.compare(i, s.const(trips, "i32"), "LT")
+        def body(s, i, v, w):
+            v2 = s.add(s.mul(v, s.full((300,), 0.9, "f32")), w)
+            return [s.add(i, s.const(1, "i32")), v2, s.mul(w, s.full((300,), 1.01, "f32"))]
+        text = b.module(b.while_([b.const(0, "i32"), x, x], cond, body))
+        xin = f32(300)
+        got, exe = check(client, text, [xin], rtol=1e-4)
+        assert int(got[0]) == trips
+        again = [o.to_numpy() for o in exe.execute([client.buffer_from_host(xin)])]
+        for g, a in zip(got, again):
+            assert np.array_equal(np.asarray(g), a)
+
+
 def test_row_scatter(client):
     """Row scatter with repeated and out-of-range indices: add in f32 and bf16 (update order, fp32 accumulator),
     multiply / minimum / maximum / set, i64 indices, and the embedding-gradient form."""

@@ -101,6 +101,18 @@ def test_counted_loop_is_recognised():
     assert "while trip=130" in plan
 
 
+def test_scan_body_plan_has_no_copies():
+    """The LSTM scan step: stacked carries are updated through a window in place, every other carried value trades
+    pointers with its next value, independent pointwise kernels of a body share a launch, and the generated
+    source of the whole plan compiles."""
+    prog = programs.lstm_scan_train_step(steps=6, batch=8, in_dim=8, hidden=16)
+    plan, _ = b200.compile_to_plan(prog.text, validate=True)
+    loops = [l for l in plan.splitlines() if l.strip().startswith("while trip=6")]
+    assert len(loops) == 2
+    assert "exchanged=5/9" in loops[0] and "exchanged=9/9" in loops[1]
+    assert plan.count(".window") >= 4 and "bundle_" in plan and "memcpy" not in plan
+
+
 def test_custom_assembly_and_generic_form_give_the_same_plan():
     pretty = """
 module @m { func.func public @main(%arg0: tensor<8x4xf32>, %arg1: tensor<4xf32>) -> tensor<8xf32> {
