@@ -1063,7 +1063,9 @@ struct Planner {
       L.block[0] = TX; L.block[1] = TY; L.block[2] = 1;
     } else {
       // T threads cooperate on one output; the reduced range is contiguous-ish along threads
-      int T = Nr >= 1024 ? 256 : 32;
+      // a block per output from 128 reduced elements on: second passes over a few hundred partial rows are latency-
+      // bound, and 256 threads fetch them in one or two rounds of loads where a warp would need ten to twenty
+      int T = Nr >= 128 ? 256 : 32;
       int per_block = 256 / T;
       src << "extern \"C\" __global__ void __launch_bounds__(256) @NAME@(" << signature(outs, ins) << ") {\n";
       if (T == 256)
