@@ -210,11 +210,18 @@ def run_b200(args):
         outs[0].to_host_async(loss_pin.numpy()).wait()
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        xb, yb = client.buffer_from_host(x_pin.numpy()), client.buffer_from_host(y_pin.numpy())
+    # input double-buffering, as a training loop's loader does it: the copy of the next step's batch is issued
+    # (copy stream) before the loss of the current step is awaited; every step still copies its own batch up and
+    # reads its own loss back inside the timed region
+    nxt = (client.buffer_from_host(x_pin.numpy()), client.buffer_from_host(y_pin.numpy()))
+    for i in range(args.steps):
+        xb, yb = nxt
         outs = exe.execute(state + [xb, yb])
         state = outs[1:]
-        outs[0].to_host_async(loss_pin.numpy()).wait()
+        pending = outs[0].to_host_async(loss_pin.numpy())
+        if i + 1 < args.steps:
+            nxt = (client.buffer_from_host(x_pin.numpy()), client.buffer_from_host(y_pin.numpy()))
+        pending.wait()
     barrier()
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
     e2e_value = world * args.steps / (e2e_ms / 1e3)
