@@ -2305,9 +2305,42 @@ struct Planner {
       if (live.count(ps)) live[ps] = {0, (int)S};
     for (auto& sub_steps : plan.steps)
       for (auto& sp : sub_steps.sub) layout_arena(*sp);
+    // The operands of a run of all-reduces (the gradient leaves of a data-parallel step) are laid out back to back,
+    // inputs in one block and outputs in another, so that the runtime can reduce the whole run with one call over
+    // one flat buffer instead of one operation per leaf. A pack is placed as a single block that lives from the
+    // first member's first use to the last member's last use.
+    std::map<int, std::vector<int>> packs;    // leader slot -> members in order (leader first)
+    std::set<int> packed;
+    for (size_t i = 0; i < S;) {
+      if (plan.steps[i].kind != Step::ALL_REDUCE) { i++; continue; }
+      size_t e = i;
+      while (e + 1 < S && plan.steps[e + 1].kind == Step::ALL_REDUCE) e++;
+      std::vector<int> ins, outs;
+      bool ok = e > i;
+      std::set<int> seen;
+      for (size_t k = i; k <= e && ok; k++) {
+        const Step& q = plan.steps[k];
+        ok = q.dtype == plan.steps[i].dtype && q.bytes > 0;
+        for (int a : q.args) ok = ok && live.count(a) && !packed.count(a) && seen.insert(a).second && !whole_plan.count(a);
+        ins.push_back(q.args[0]);
+        outs.push_back(q.args[1]);
+      }
+      if (ok && !getenv("B200_NO_FLAT_ALL_REDUCE")) {
+        for (auto* v : {&ins, &outs}) {
+          packs[(*v)[0]] = *v;
+          for (int a : *v) {
+            packed.insert(a);
+            live[(*v)[0]].first = std::min(live[(*v)[0]].first, live[a].first);
+            live[(*v)[0]].second = std::max(live[(*v)[0]].second, live[a].second);
+          }
+        }
+      }
+      i = e + 1;
+    }
     // greedy first-fit by start time
     std::vector<std::pair<int, int>> order;   // (first, slot)
-    for (auto& kv : live) order.push_back({kv.second.first, kv.first});
+    for (auto& kv : live)
+      if (!packed.count(kv.first) || packs.count(kv.first)) order.push_back({kv.second.first, kv.first});
     std::sort(order.begin(), order.end());
     struct Blk { size_t off, size; int last; };
     std::vector<Blk> active;
@@ -2319,6 +2352,11 @@ struct Planner {
       int slot = pr.second;
       int first = pr.first, last = live[slot].second;
       size_t need = (prog.slots[slot].bytes + 255) & ~(size_t)255;
+      auto pk = packs.find(slot);
+      if (pk != packs.end()) {
+        need = 0;
+        for (int m : pk->second) need += (prog.slots[m].bytes + 255) & ~(size_t)255;
+      }
       // drop blocks that ended before `first`
       active.erase(std::remove_if(active.begin(), active.end(), [&](const Blk& b) { return b.last < first; }), active.end());
       std::sort(active.begin(), active.end(), [](const Blk& a, const Blk& b) { return a.off < b.off; });
@@ -2328,6 +2366,13 @@ struct Planner {
         off = std::max(off, b.off + b.size);
       }
       prog.slots[slot].offset = off;
+      if (pk != packs.end()) {
+        size_t at = off;
+        for (int m : pk->second) {
+          prog.slots[m].offset = at;
+          at += (prog.slots[m].bytes + 255) & ~(size_t)255;
+        }
+      }
       active.push_back({off, need, last});
       peak = std::max(peak, off + need);
     }
@@ -2358,7 +2403,9 @@ void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& o
         break;
       case Step::CASE: os << "case branches=" << s.sub.size(); break;
       case Step::SCATTER: os << "scatter rows=" << s.iparams[0] << " row_elems=" << s.iparams[1] << " updates=" << s.iparams[2]; break;
-      case Step::ALL_REDUCE: os << "all_reduce " << s.bytes << " bytes"; break;
+      case Step::ALL_REDUCE:
+        os << "all_reduce " << s.bytes << " bytes in@" << prog.slots[s.args[0]].offset << " out@" << prog.slots[s.args[1]].offset;
+        break;
       default: os << "step";
     }
     os << " args=[";

@@ -742,6 +742,32 @@ b200_error* run_plan(ExecCtx& x, const Plan& plan) {
         cudaEventCreate(&t.b);
         cudaEventRecord(t.a, x.c->compute);
       }
+      // the compiler lays the run's inputs and outputs out back to back (256-byte granules): when it did, the run
+      // is one all-reduce over one flat buffer; the padding between leaves is summed along and never read
+      {
+        bool flat = sj - si >= 2;
+        size_t total = 0;
+        const Step& f = plan.steps[si];
+        char *in0 = (char*)x.ptrs[f.args[0]], *out0 = (char*)x.ptrs[f.args[1]];
+        for (size_t k = si; k < sj && flat; ++k) {
+          const Step& q = plan.steps[k];
+          flat = q.dtype == f.dtype && (char*)x.ptrs[q.args[0]] == in0 + total && (char*)x.ptrs[q.args[1]] == out0 + total;
+          total += (q.bytes + 255) & ~(size_t)255;
+        }
+        bool ok = false;
+        ncclDataType_t nt = nccl_type(f.dtype, &ok);
+        if (flat && ok) {
+          ncclResult_t r = nccl().AllReduce(in0, out0, total / dt_size(f.dtype), nt, ncclSum, x.c->comm, x.c->compute);
+          if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclAllReduce failed: ") + nccl().GetErrorString(r));
+          x.launches += 1;
+          if (x.c->profiling) {
+            cudaEventRecord(t.b, x.c->compute);
+            x.timed.push_back(t);
+          }
+          si = sj - 1;
+          continue;
+        }
+      }
       const int before = x.launches;
       nccl().GroupStart();
       b200_error* err = nullptr;

@@ -90,6 +90,13 @@ def test_resnet_plan_shape():
     dp = programs.resnet18_train_step(batch=4, image=8, width=8, n_partitions=2)
     plan2, _ = b200.compile_to_plan(dp.text, num_processes=2, process_index=1)
     assert plan2.count("all_reduce") == 63                  # 62 gradient leaves + the loss
+    # the leaves lie back to back in 256-byte granules (inputs in one block, outputs in another): the runtime
+    # reduces the run with one call over the flat buffer
+    rows = [re.search(r"all_reduce (\d+) bytes in@(\d+) out@(\d+)", l) for l in plan2.splitlines() if "all_reduce" in l]
+    rows = [tuple(int(g) for g in m.groups()) for m in rows]
+    for (b0, i0, o0), (_, i1, o1) in zip(rows, rows[1:]):
+        step = (b0 + 255) // 256 * 256
+        assert i1 == i0 + step and o1 == o0 + step
 
 
 def test_counted_loop_is_recognised():
