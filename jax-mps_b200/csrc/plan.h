@@ -49,7 +49,7 @@ struct IGemmParams {
 struct Plan;
 
 struct Step {
-  enum Kind { KERNEL, IGEMM, MEMCPY, MEMSET, WHILE, CASE, ALL_REDUCE, SCATTER } kind = KERNEL;
+  enum Kind { KERNEL, IGEMM, MEMCPY, MEMSET, WHILE, CASE, ALL_REDUCE, SCATTER, JOIN } kind = KERNEL;
   std::string label;                  // op names, for profiling and error text
   // KERNEL
   int kernel = -1;                    // index into Executable::kernels
@@ -69,7 +69,9 @@ struct Step {
   std::vector<int> results;
   int pred = -1;
   long long trip_count = -1;          // statically known trip count of a counted loop
-  // ALL_REDUCE: args = {in0.., out0..}
+  // ALL_REDUCE: args = {in, out}; overlapped = issued on the collective stream, the next JOIN step makes the
+  // compute stream wait for it
+  bool overlapped = false;
   DT dtype = DT::F32;
   // SCATTER: args = {operand, indices, updates, result, scratch...}
   std::vector<long long> iparams;

@@ -300,6 +300,8 @@ struct LoadedProgram {
 struct b200_client {
   int ordinal = 0, rank = 0, nprocs = 1;
   cudaStream_t compute = nullptr, h2d = nullptr, d2h = nullptr;
+  cudaStream_t coll = nullptr;                      // collectives that overlap with compute (created with the communicator)
+  cudaEvent_t coll_ready = nullptr, coll_done = nullptr;
   cudaMemPool_t pool = nullptr;
   ncclComm_t comm = nullptr;
   std::recursive_mutex mu;
@@ -506,6 +508,8 @@ struct ExecCtx {
   LoadedProgram* lp;
   std::vector<void*> ptrs;
   int launches = 0;
+  bool coll_pending = false;            // work on the collective stream that the compute stream has not waited for yet
+  cudaStream_t coll_stream = nullptr;   // set while the members of an all-reduce group are issued
   struct Timed { std::string kind, key; cudaEvent_t a, b; };
   std::vector<Timed> timed;
 };
@@ -590,7 +594,7 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       bool ok;
       ncclDataType_t t = nccl_type(s.dtype, &ok);
       if (!ok) return make_error(B200_UNIMPLEMENTED, "all_reduce of this element type");
-      ncclResult_t r = nccl().AllReduce(in, out, s.bytes / dt_size(s.dtype), t, ncclSum, c->comm, st);
+      ncclResult_t r = nccl().AllReduce(in, out, s.bytes / dt_size(s.dtype), t, ncclSum, c->comm, x.coll_stream ? x.coll_stream : st);
       if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclAllReduce failed: ") + nccl().GetErrorString(r));
       x.launches++;
       return nullptr;
@@ -728,6 +732,14 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
 b200_error* run_plan(ExecCtx& x, const Plan& plan) {
   for (size_t si = 0; si < plan.steps.size(); ++si) {
     const Step& s = plan.steps[si];
+    if (s.kind == Step::JOIN) {
+      // the compute stream waits for everything issued on the collective stream so far
+      if (x.c->nprocs > 1 && x.coll_pending) {
+        CUDA_TRY(cudaStreamWaitEvent(x.c->compute, x.c->coll_done, 0));
+        x.coll_pending = false;
+      }
+      continue;
+    }
     if (s.kind == Step::ALL_REDUCE && x.c->nprocs > 1) {
       // consecutive all-reduces (the gradient leaves of a data-parallel step) go out as one NCCL group: one
       // fused launch instead of one per leaf
@@ -744,6 +756,21 @@ b200_error* run_plan(ExecCtx& x, const Plan& plan) {
       }
       // the compiler lays the run's inputs and outputs out back to back (256-byte granules): when it did, the run
       // is one all-reduce over one flat buffer; the padding between leaves is summed along and never read
+      // an overlapped run goes to the collective stream behind everything the compute stream has been given so far
+      cudaStream_t cst = x.c->compute;
+      const bool overlapped = s.overlapped && x.c->coll && !x.c->profiling;
+      if (overlapped) {
+        cst = x.c->coll;
+        CUDA_TRY(cudaEventRecord(x.c->coll_ready, x.c->compute));
+        CUDA_TRY(cudaStreamWaitEvent(cst, x.c->coll_ready, 0));
+      }
+      auto after_issue = [&]() -> b200_error* {
+        if (overlapped) {
+          CUDA_TRY(cudaEventRecord(x.c->coll_done, cst));
+          x.coll_pending = true;
+        }
+        return nullptr;
+      };
       {
         bool flat = sj - si >= 2;
         size_t total = 0;
@@ -757,8 +784,9 @@ b200_error* run_plan(ExecCtx& x, const Plan& plan) {
         bool ok = false;
         ncclDataType_t nt = nccl_type(f.dtype, &ok);
         if (flat && ok) {
-          ncclResult_t r = nccl().AllReduce(in0, out0, total / dt_size(f.dtype), nt, ncclSum, x.c->comm, x.c->compute);
+          ncclResult_t r = nccl().AllReduce(in0, out0, total / dt_size(f.dtype), nt, ncclSum, x.c->comm, cst);
           if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclAllReduce failed: ") + nccl().GetErrorString(r));
+          if (auto* e = after_issue()) return e;
           x.launches += 1;
           if (x.c->profiling) {
             cudaEventRecord(t.b, x.c->compute);
@@ -771,10 +799,13 @@ b200_error* run_plan(ExecCtx& x, const Plan& plan) {
       const int before = x.launches;
       nccl().GroupStart();
       b200_error* err = nullptr;
+      x.coll_stream = cst;
       for (size_t k = si; k < sj && !err; ++k) err = run_step(x, plan.steps[k]);
+      x.coll_stream = nullptr;
       ncclResult_t r = nccl().GroupEnd();
       if (err) return err;
       if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclGroupEnd failed: ") + nccl().GetErrorString(r));
+      if (auto* e = after_issue()) return e;
       x.launches = before + 1;
       if (x.c->profiling) {
         cudaEventRecord(t.b, x.c->compute);
@@ -897,6 +928,13 @@ b200_error* b200_client_create(const b200_client_options* o, b200_client** out) 
     memcpy(&id, o->nccl_unique_id, sizeof id);
     ncclResult_t r = n.CommInitRank(&c->comm, c->nprocs, id, c->rank);
     if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclCommInitRank: ") + n.GetErrorString(r));
+    // collectives that overlap with compute run on a stream of their own, at the highest priority so that their
+    // few CTAs find a place as soon as compute CTAs retire
+    int lo = 0, hi = 0;
+    CUDA_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    CUDA_TRY(cudaStreamCreateWithPriority(&c->coll, cudaStreamNonBlocking, hi));
+    CUDA_TRY(cudaEventCreateWithFlags(&c->coll_ready, cudaEventDisableTiming));
+    CUDA_TRY(cudaEventCreateWithFlags(&c->coll_done, cudaEventDisableTiming));
   }
   *out = c.release();
   return nullptr;
@@ -914,6 +952,9 @@ b200_error* b200_client_destroy(b200_client* c) {
   }
   if (c->pred_host) cudaFreeHost(c->pred_host);
   if (c->error_flag) cudaFree(c->error_flag);
+  if (c->coll) cudaStreamDestroy(c->coll);
+  if (c->coll_ready) cudaEventDestroy(c->coll_ready);
+  if (c->coll_done) cudaEventDestroy(c->coll_done);
   cudaStreamDestroy(c->compute);
   cudaStreamDestroy(c->h2d);
   cudaStreamDestroy(c->d2h);
@@ -1394,6 +1435,7 @@ b200_error* b200_executable_execute(b200_executable* exe, b200_buffer* const* ar
     }
   }
   b200_error* err = run_plan(x, p.main);
+  if (x.coll_pending) cudaStreamWaitEvent(c->compute, c->coll_done, 0);   // a plan that ended early still joins
   c->launches += x.launches;
   if (!x.timed.empty()) {
     cudaStreamSynchronize(c->compute);

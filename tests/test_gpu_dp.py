@@ -15,9 +15,11 @@ CFG = dict(batch=8, image=16, width=8)
 pytestmark = pytest.mark.gpu
 
 
-def _rank_main(rank, world, id_pipe, q):
+def _rank_main(rank, world, id_pipe, q, overlap):
     sys.path.insert(0, str(ROOT / "jax-mps_b200"))
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    if overlap:
+        os.environ["B200_ALL_REDUCE_OVERLAP"] = "1"     # buckets of the all-reduce issued inside the backward pass
     try:
         import b200
         from b200.shlo import programs
@@ -41,7 +43,8 @@ def _rank_main(rank, world, id_pipe, q):
         q.put((rank, repr(e), None))
 
 
-def test_two_gpu_step_is_the_mean_of_the_shard_steps():
+@pytest.mark.parametrize("overlap", [False, True])
+def test_two_gpu_step_is_the_mean_of_the_shard_steps(overlap):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -50,8 +53,8 @@ def test_two_gpu_step_is_the_mean_of_the_shard_steps():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     recv, send = ctx.Pipe(duplex=False)
-    procs = [ctx.Process(target=_rank_main, args=(0, world, [send], q)),
-             ctx.Process(target=_rank_main, args=(1, world, recv, q))]
+    procs = [ctx.Process(target=_rank_main, args=(0, world, [send], q, overlap)),
+             ctx.Process(target=_rank_main, args=(1, world, recv, q, overlap))]
     for p in procs:
         p.start()
     got = {}

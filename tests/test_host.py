@@ -1,6 +1,7 @@
 """CPU: host-side logic — the C-ABI library loads and exports every declared
 symbol, the parser and the plan compiler behave (fusion shape, error text for
 unsupported operations, custom assembly), and nothing computes without a GPU."""
+import os
 import re
 from pathlib import Path
 
@@ -90,13 +91,40 @@ def test_resnet_plan_shape():
     dp = programs.resnet18_train_step(batch=4, image=8, width=8, n_partitions=2)
     plan2, _ = b200.compile_to_plan(dp.text, num_processes=2, process_index=1)
     assert plan2.count("all_reduce") == 63                  # 62 gradient leaves + the loss
-    # the leaves lie back to back in 256-byte granules (inputs in one block, outputs in another): the runtime
-    # reduces the run with one call over the flat buffer
-    rows = [re.search(r"all_reduce (\d+) bytes in@(\d+) out@(\d+)", l) for l in plan2.splitlines() if "all_reduce" in l]
-    rows = [tuple(int(g) for g in m.groups()) for m in rows]
-    for (b0, i0, o0), (_, i1, o1) in zip(rows, rows[1:]):
-        step = (b0 + 255) // 256 * 256
-        assert i1 == i0 + step and o1 == o0 + step
+    assert "join" not in plan2 and "overlapped" not in plan2
+    check_runs(plan2, overlapped=False)
+    os.environ["B200_ALL_REDUCE_OVERLAP"] = "1"
+    try:
+        plan3, _ = b200.compile_to_plan(dp.text, num_processes=2, process_index=1)
+    finally:
+        del os.environ["B200_ALL_REDUCE_OVERLAP"]
+    assert plan3.count("all_reduce") == 63
+    check_runs(plan3, overlapped=True)
+
+
+def check_runs(plan2, overlapped):
+    # Each run of consecutive all-reduces lies back to back in 256-byte granules (inputs in one block, outputs in
+    # another): the runtime reduces a run with one call over the flat buffer. Runs whose gradients exist early are
+    # moved up into the backward pass and issued on the collective stream; a join follows the last run.
+    lines = plan2.splitlines()
+    runs, prev = [], None
+    for i, l in enumerate(lines):
+        m = re.search(r"all_reduce (\d+) bytes in@(\d+) out@(\d+)", l)
+        if not m:
+            continue
+        assert ("overlapped" in l) == overlapped
+        if prev != i - 1:
+            runs.append([])
+        runs[-1].append(tuple(int(g) for g in m.groups()))
+        prev = i
+    assert len(runs) >= 2 if overlapped else len(runs) == 1
+    for run in runs:
+        for (b0, i0, o0), (_, i1, o1) in zip(run, run[1:]):
+            step = (b0 + 255) // 256 * 256
+            assert i1 == i0 + step and o1 == o0 + step
+    join = [i for i, l in enumerate(lines) if l.strip().startswith("join")]
+    if overlapped:
+        assert len(join) == 1 and join[0] == prev + 1
 
 
 def test_counted_loop_is_recognised():
