@@ -68,15 +68,20 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self) -> dict:
+    def count(self, t0: float, t1: float) -> int:
+        return sum(1 for t, _ in self.lines if t0 <= t <= t1)
+
+    def stop(self, t0: float, t1: float) -> dict:
+        """Summary of the samples that arrived between t0 and t1 (perf_counter times)."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
         self.proc.terminate()
         sm, mx, reasons = [], None, set()
-        for ln in self.lines:
+        for t, ln in self.lines:
+            if not (t0 <= t <= t1):
+                continue
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -175,14 +180,17 @@ def run_b200(args):
     # ---- device-resident loop: parameters and momentum stay in HBM, outputs feed the next step -------
     bufs = [client.buffer_from_host(a) for a in host_args]
     state, xy = bufs[:n_state], bufs[n_state:]
+    # the sampler starts ahead of the warm-up so that nvidia-smi is up and reporting when the timed region begins;
+    # only samples that arrive inside the window below are used
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         outs = exe.execute(state + xy)
         state = outs[1:]
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     launches0 = client.launch_count()
+    t_begin = time.perf_counter()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         ev0.record()
@@ -194,8 +202,21 @@ def run_b200(args):
     barrier()
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     launches = client.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
     loss = float(outs[0].to_numpy())
+    # A short timed region (30 steps are 0.16 s) can end before nvidia-smi has reported a few times: every rank then
+    # keeps running the same steps, untimed, until 0.6 s of load have passed since the region began, and the
+    # sampling window covers them too (ms_total is the maximum over ranks, so all ranks run the same count).
+    window = "timed region"
+    if ms_total < 600.0:
+        for _ in range(int((600.0 - ms_total) / (ms_total / args.steps)) + 1):
+            o2 = exe.execute(state + xy)
+            state = o2[1:]
+        window = "timed region and further identical steps, untimed, up to 0.6 s of load"
+    barrier()
+    clocks = None
+    if rank == 0:
+        clocks = sampler.stop(t_begin, time.perf_counter())
+        clocks["window"] = window
     ms_step = ms_total / args.steps
     value = world * args.steps / (ms_total / 1e3)
 
