@@ -335,6 +335,7 @@ struct b200_buffer {
   b200_dtype dtype = B200_INVALID;
   std::vector<int64_t> dims;
   cudaEvent_t ready = nullptr;                 // recorded on the producing stream
+  cudaStream_t ready_on = nullptr;             // that stream: work issued to it later needs no wait
   std::vector<cudaEvent_t> reads;              // pending reads on other streams
   bool deleted = false;
 };
@@ -1261,6 +1262,7 @@ b200_error* b200_buffer_from_host(b200_client* c, const void* data, b200_dtype d
   }
   CUDA_TRY(cudaEventCreateWithFlags(&b->ready, cudaEventDisableTiming));
   CUDA_TRY(cudaEventRecord(b->ready, c->h2d));
+  b->ready_on = c->h2d;
   if (done) {
     if (host_ready_now) *done = new b200_event();
     else {
@@ -1334,7 +1336,8 @@ b200_error* b200_buffer_delete(b200_buffer* b) {
   if (auto* e = set_device(c)) return e;
   b->deleted = true;
   if (b->ptr) {
-    if (b->ready) cudaStreamWaitEvent(c->compute, b->ready, 0);
+    // the free is ordered on the compute stream: only a producer on another stream needs a wait
+    if (b->ready && b->ready_on != c->compute) cudaStreamWaitEvent(c->compute, b->ready, 0);
     for (auto ev : b->reads) {
       cudaStreamWaitEvent(c->compute, ev, 0);
       cudaEventDestroy(ev);
@@ -1372,6 +1375,7 @@ b200_error* b200_buffer_copy(b200_buffer* b, b200_buffer** out) {
   if (b->bytes) CUDA_TRY(cudaMemcpyAsync(n->ptr, b->ptr, b->bytes, cudaMemcpyDeviceToDevice, c->compute));
   CUDA_TRY(cudaEventCreateWithFlags(&n->ready, cudaEventDisableTiming));
   CUDA_TRY(cudaEventRecord(n->ready, c->compute));
+  n->ready_on = c->compute;
   *out = n.release();
   return nullptr;
 }
@@ -1403,7 +1407,9 @@ b200_error* b200_executable_execute(b200_executable* exe, b200_buffer* const* ar
   x.c = c;
   x.lp = exe->lp.get();
   x.ptrs.assign(p.slots.size(), nullptr);
-  for (size_t k = 0; k < num_args; k++) CUDA_TRY(cudaStreamWaitEvent(c->compute, args[k]->ready, 0));
+  // arguments produced on the compute stream itself (the outputs of earlier executions) are ordered already
+  for (size_t k = 0; k < num_args; k++)
+    if (args[k]->ready_on != c->compute) CUDA_TRY(cudaStreamWaitEvent(c->compute, args[k]->ready, 0));
   std::vector<std::unique_ptr<b200_buffer>> outs(p.results.size());
   std::vector<int> donated_from(p.results.size(), -1);
   std::vector<bool> arg_taken(num_args, false);
@@ -1458,6 +1464,7 @@ b200_error* b200_executable_execute(b200_executable* exe, b200_buffer* const* ar
   for (size_t k = 0; k < outs.size(); k++) {
     CUDA_TRY(cudaEventCreateWithFlags(&outs[k]->ready, cudaEventDisableTiming));
     CUDA_TRY(cudaEventRecord(outs[k]->ready, c->compute));
+    outs[k]->ready_on = c->compute;
   }
   if (donate) {
     // donated arguments are consumed (PJRT semantics): their memory returns to the pool in stream order
