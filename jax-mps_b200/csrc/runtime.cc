@@ -336,6 +336,8 @@ struct b200_buffer {
   std::vector<int64_t> dims;
   cudaEvent_t ready = nullptr;                 // recorded on the producing stream
   cudaStream_t ready_on = nullptr;             // that stream: work issued to it later needs no wait
+  struct Block { void* base; int refs; };      // one device allocation shared by several results of an execution
+  Block* block = nullptr;                      // non-null: ptr lies inside block->base, freed with its last buffer
   std::vector<cudaEvent_t> reads;              // pending reads on other streams
   bool deleted = false;
 };
@@ -1343,7 +1345,15 @@ b200_error* b200_buffer_delete(b200_buffer* b) {
       cudaEventDestroy(ev);
     }
     b->reads.clear();
-    cudaFreeAsync(b->ptr, c->compute);
+    if (b->block) {
+      if (--b->block->refs == 0) {
+        cudaFreeAsync(b->block->base, c->compute);
+        delete b->block;
+      }
+      b->block = nullptr;
+    } else {
+      cudaFreeAsync(b->ptr, c->compute);
+    }
     c->note_free(std::max<size_t>(b->bytes, 16));
     b->ptr = nullptr;
   }
@@ -1428,8 +1438,48 @@ b200_error* b200_executable_execute(b200_executable* exe, b200_buffer* const* ar
       arg_taken[da] = true;
       donated_from[k] = da;
     }
-    if (auto* e = device_alloc(c, b->bytes, c->compute, &b->ptr)) return e;
     outs[k] = std::move(b);
+  }
+  // Results come out of two allocations per execution instead of one each: one block for the small results (under
+  // 64 KB: scalars, statistics vectors) and one for the large ones (parameters, optimizer state), each freed when
+  // its last buffer is deleted. A scalar that the caller keeps (a loss) therefore pins the small block only.
+  {
+    size_t total[2] = {0, 0};
+    int count[2] = {0, 0};
+    auto cls = [](size_t bytes) { return bytes < 65536 ? 0 : 1; };
+    auto padded = [](size_t bytes) { return (std::max<size_t>(bytes, 16) + 255) & ~(size_t)255; };
+    for (auto& b : outs) { total[cls(b->bytes)] += padded(b->bytes); count[cls(b->bytes)]++; }
+    b200_buffer::Block* blocks[2] = {nullptr, nullptr};
+    for (int g = 0; g < 2; g++) {
+      if (count[g] < 2) continue;
+      void* base = nullptr;
+      cudaError_t e = cudaMallocAsync(&base, total[g], c->compute);
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        if (blocks[0]) { cudaFreeAsync(blocks[0]->base, c->compute); delete blocks[0]; }
+        return make_error(B200_RESOURCE_EXHAUSTED, "device allocation of " + std::to_string(total[g]) + " bytes for " +
+                                                       std::to_string(count[g]) + " results failed: " + cudaGetErrorString(e));
+      }
+      blocks[g] = new b200_buffer::Block{base, 0};
+    }
+    size_t at[2] = {0, 0};
+    for (auto& b : outs) {
+      const int g = cls(b->bytes);
+      if (!blocks[g]) continue;
+      b->block = blocks[g];
+      b->ptr = (char*)blocks[g]->base + at[g];
+      at[g] += padded(b->bytes);
+      blocks[g]->refs++;
+      c->note_alloc(std::max<size_t>(b->bytes, 16));
+    }
+    for (auto& b : outs) {
+      if (b->ptr) continue;
+      if (auto* e = device_alloc(c, b->bytes, c->compute, &b->ptr)) {
+        for (auto& o : outs)
+          if (o->ptr) b200_buffer_delete(o.get());
+        return e;
+      }
+    }
   }
   for (size_t s = 0; s < p.slots.size(); s++) {
     const Slot& sl = p.slots[s];
@@ -1458,7 +1508,7 @@ b200_error* b200_executable_execute(b200_executable* exe, b200_buffer* const* ar
   }
   if (err) {
     for (auto& b : outs)
-      if (b && b->ptr) { cudaFreeAsync(b->ptr, c->compute); c->note_free(std::max<size_t>(b->bytes, 16)); }
+      if (b && b->ptr) b200_buffer_delete(b.get());
     return err;
   }
   for (size_t k = 0; k < outs.size(); k++) {
