@@ -482,6 +482,36 @@ def test_counted_loop_graph_replay_odd_and_even(client):
             assert np.array_equal(np.asarray(g), a)
 
 
+def test_results_share_blocks_and_outlive_their_siblings(client):
+    """The results of one execution come out of two shared allocations (small and large results). A result that is
+    kept while its siblings are deleted stays valid, later executions do not disturb it, and the accounted bytes
+    return to where they were once everything is deleted."""
+    b = Builder()
+    x = b.arg((40000,), "f32")
+    big1 = b.add(x, b.full((40000,), 1.0, "f32"))
+    big2 = b.mul(x, b.full((40000,), 2.0, "f32"))
+    s1 = b.reduce_sum(x, [0])
+    s2 = b.reduce_sum(b.mul(x, x), [0])
+    exe = client.compile(b.module([big1, big2, s1, s2]))
+    xin = f32(40000)
+    import gc
+    gc.collect()                                         # buffers of earlier tests go first
+    before = client.memory_stats().bytes_in_use
+    xb = client.buffer_from_host(xin)
+    outs = exe.execute([xb])
+    keep_big, keep_small = outs[1], outs[2]
+    outs[0].delete(); outs[3].delete()
+    del outs
+    for _ in range(3):                                   # further executions reuse the pool
+        for o in exe.execute([xb]):
+            o.delete()
+    np.testing.assert_allclose(keep_big.to_numpy(), xin * 2.0, rtol=1e-6)
+    np.testing.assert_allclose(float(keep_small.to_numpy()), float(xin.astype(np.float64).sum()), rtol=1e-4, atol=1e-3)
+    keep_big.delete(); keep_small.delete(); xb.delete()
+    client.synchronize()
+    assert client.memory_stats().bytes_in_use == before
+
+
 def test_row_scatter(client):
     """Row scatter with repeated and out-of-range indices: add in f32 and bf16 (update order, fp32 accumulator),
     multiply / minimum / maximum / set, i64 indices, and the embedding-gradient form."""
