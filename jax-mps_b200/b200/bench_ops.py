@@ -3,6 +3,11 @@ captures summarised under profiles/, and handy when tuning a kernel):
 
     python -m b200.bench_ops conv --case s1 [--reps 10]
     python -m b200.bench_ops reduce --shape 128,32,32,64 --dims 0,1,2
+    python -m b200.bench_ops scan [--reps 10]
+
+`scan` times the full-size LSTM-by-scan training step (100 time steps, batch 64, 32 -> 256 -> 256, Adam: a forward
+and a reverse counted loop, 200 dependent iterations) and, beside it, the floor of one dependent kernel launch
+inside a replayed loop (a counted loop of 2000 iterations whose body is one tiny kernel).
 
 Convolution cases are the ResNet18 (batch 128) layer shapes: s1..s4 = the 3x3
 stride-1 convolution of stage 1..4 (forward form).
@@ -10,6 +15,7 @@ stride-1 convolution of stage 1..4 (forward form).
 from __future__ import annotations
 
 import argparse
+import time
 
 import numpy as np
 
@@ -34,9 +40,41 @@ def time_program(client, text, arrays, reps):
     return sum(r["ms"] for r in rep) / reps, rep
 
 
+def wall_ms(client, exe, bufs, reps):
+    for _ in range(3):
+        exe.execute(bufs)
+    client.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        exe.execute(bufs)
+    client.synchronize()
+    return (time.perf_counter() - t0) * 1e3 / reps
+
+
+def scan(client, reps):
+    from b200.shlo import programs
+    prog = programs.lstm_scan_train_step()
+    exe = client.compile(prog.text)
+    bufs = [client.buffer_from_host(a) for a in programs.lstm_inputs(prog, seed=0)]
+    ms = wall_ms(client, exe, bufs, reps)
+    print(f"lstm scan step: {ms:.2f} ms = {ms * 1e3 / 200:.1f} us per scan iteration (200 dependent iterations, "
+          f"{exe.launches_per_execute} launches per step)")
+    b = Builder()
+    x = b.arg((16,), "f32")
+    trips = 2000
+    outs = b.while_([b.const(0, "i32"), x], lambda s, i, v: s.compare(i, s.const(trips, "i32"), "LT"),
+                    lambda s, i, v: [s.add(i, s.const(1, "i32")),
+                                     s.add(s.mul(v, s.full((16,), 0.99, "f32")), s.full((16,), 0.01, "f32"))])
+    e2 = client.compile(b.module(outs))
+    ms2 = wall_ms(client, e2, [client.buffer_from_host(np.ones(16, np.float32))], reps)
+    per = e2.launches_per_execute / trips
+    print(f"dependent-kernel floor: {ms2 * 1e3 / e2.launches_per_execute:.2f} us per launch "
+          f"({per:.0f} launch per iteration, {trips} iterations)")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["conv", "reduce"])
+    ap.add_argument("what", choices=["conv", "reduce", "scan"])
     ap.add_argument("--case", default="s1")
     ap.add_argument("--shape", default="128,32,32,64")
     ap.add_argument("--dims", default="0,1,2")
@@ -45,6 +83,9 @@ def main():
     client = b200.Client()
     rng = np.random.default_rng(0)
     b = Builder()
+    if a.what == "scan":
+        scan(client, a.reps)
+        return
     if a.what == "conv":
         xs, ws = CONV_CASES[a.case]
         x, w = b.arg(xs, "f32"), b.arg(ws, "f32")
