@@ -181,7 +181,9 @@ typedef struct {
                                 and the argument buffer is left deleted */
 } b200_execute_options;
 /* `outputs` is a caller-allocated array of b200_executable_num_outputs pointers. `done` (may be NULL)
- * becomes ready when all outputs are computed. The call returns after enqueueing. */
+ * becomes ready when all outputs are computed. The call returns after enqueueing. The outputs of one call share
+ * two device allocations (small and large results); each is deleted on its own and a shared allocation is
+ * released with its last output. */
 b200_error* b200_executable_execute(b200_executable* exe, b200_buffer* const* args, size_t num_args,
                                     b200_buffer** outputs, b200_event** done, const b200_execute_options* options);
 
