@@ -148,6 +148,17 @@ def test_scan_body_plan_has_no_copies():
     assert plan.count(".window") >= 4 and "bundle_" in plan and "memcpy" not in plan
 
 
+@pytest.mark.parametrize("dt", ["f32", "f64", "i32", "bf16"])
+def test_column_reduction_source_compiles(dt):
+    """The four-indices-per-thread column reduction and its block-per-output second pass are generated for every
+    element type and pass NVRTC (compile only, no device)."""
+    b = Builder()
+    x = b.arg((4096, 128), dt)
+    plan, src = b200.compile_to_plan(b.module([b.reduce_sum(x, [0]), b.reduce_sum(b.mul(x, x), [0])]), validate=True)
+    assert "block=32x8" in plan and ".final" in plan
+    assert "acc0[q]" in src
+
+
 def test_custom_assembly_and_generic_form_give_the_same_plan():
     pretty = """
 module @m { func.func public @main(%arg0: tensor<8x4xf32>, %arg1: tensor<4xf32>) -> tensor<8xf32> {
