@@ -300,6 +300,25 @@ struct Inliner {
       auto half = [](DT d) { return d == DT::BF16 || d == DT::F16; };
       if (half(op->operands[0]->type.dt) || half(op->operands[1]->type.dt) || half(op->results[0]->type.dt)) {
         auto convert_to = [&](Value* v, DT to, Value* into) -> Value* {
+          // The widened copy of an operand that comes from outside a `while` (weights read by a decode loop) is
+          // made once in front of the loop instead of in every iteration: the convert moves out through every
+          // enclosing loop region that does not define the operand.
+          Block* tb = b;
+          if (!into && !getenv("B200_NO_HOIST")) {
+            for (size_t lvl = enclosing.size(); lvl-- > 0;) {
+              auto& en = enclosing[lvl];
+              const bool defined_here = v->def ? v->def->parent == tb : v->owner == tb;
+              if (defined_here || en.second->short_name() != "while") break;
+              bool is_region = false;
+              for (auto& reg : en.second->regions) is_region = is_region || reg.get() == tb;
+              if (!is_region) break;
+              tb = en.first;
+            }
+            if (tb != b) {
+              auto hit = hoisted.find({v, (int)to});
+              if (hit != hoisted.end()) return hit->second;
+            }
+          }
           auto c = std::make_unique<Op>();
           c->name = "stablehlo.convert";
           c->operands.push_back(v);
@@ -309,8 +328,9 @@ struct Inliner {
           nv->def = c.get();
           nv->def_index = 0;
           c->results.push_back(nv);
-          c->parent = b;
-          b->ops.push_back(std::move(c));
+          c->parent = tb;
+          tb->ops.push_back(std::move(c));
+          if (tb != b) hoisted[{v, (int)to}] = nv;
           return nv;
         };
         for (auto& o : op->operands)
@@ -332,12 +352,16 @@ struct Inliner {
         }
       }
     }
+    enclosing.push_back({b, op.get()});
     for (auto& reg : op->regions) run(reg.get());
+    enclosing.pop_back();
     op->parent = b;
     b->ops.push_back(std::move(op));
     for (auto& d : deferred) { d->parent = b; b->ops.push_back(std::move(d)); }
     deferred.clear();
   }
+  std::vector<std::pair<Block*, Op*>> enclosing;               // (block, op) pairs around the region being processed
+  std::map<std::pair<Value*, int>, Value*> hoisted;            // widened copies already placed in front of a loop
   std::map<std::tuple<Value*, int, int64_t>, Value*> padded;   // zero-padded copies made for convolutions
   std::vector<std::unique_ptr<Op>> deferred;                   // ops to place right after the one being processed
 };

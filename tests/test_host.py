@@ -159,6 +159,25 @@ def test_column_reduction_source_compiles(dt):
     assert "acc0[q]" in src
 
 
+def test_weight_widening_is_hoisted_out_of_the_decode_loop():
+    """bf16 contractions run as f32 contractions of widened operands. Weights come from outside the decode loop:
+    their widened copies are made once in front of the `while`, not in every iteration."""
+    prog = programs.gemma_greedy_decode(vocab=64, dim=32, layers=2, heads=2, head_dim=16, hidden=64, prompt_len=4,
+                                        new_tokens=4, cache_len=8)
+    def split(plan):
+        lines = plan.splitlines()
+        w = next(i for i, l in enumerate(lines) if l.strip().startswith("while"))
+        return lines[1:w], [l for l in lines[w + 1:] if l.startswith("    ")]
+    before, body = split(b200.compile_to_plan(prog.text, validate=True)[0])
+    os.environ["B200_NO_HOIST"] = "1"
+    try:
+        before0, body0 = split(b200.compile_to_plan(prog.text)[0])
+    finally:
+        del os.environ["B200_NO_HOIST"]
+    count = lambda ls: sum(l.count("convert") for l in ls)
+    assert count(before) > count(before0) and count(body) < count(body0)
+
+
 def test_custom_assembly_and_generic_form_give_the_same_plan():
     pretty = """
 module @m { func.func public @main(%arg0: tensor<8x4xf32>, %arg1: tensor<4xf32>) -> tensor<8xf32> {
