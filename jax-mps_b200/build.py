@@ -11,7 +11,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "b200" / "libb200core.so"
-SOURCES = ["parser.cc", "codegen.cc", "compiler.cc", "runtime.cc", "kernels.cu"]
+SOURCES = ["parser.cc", "codegen.cc", "compiler.cc", "runtime.cc", "kernels.cu", "gemm16.cu"]
 
 
 def _nccl_include() -> str:
@@ -29,7 +29,7 @@ def needs_build() -> bool:
     if not OUT.exists():
         return True
     t = OUT.stat().st_mtime
-    deps = list(CSRC.glob("*.cc")) + list(CSRC.glob("*.cu")) + list(CSRC.glob("*.h")) + list(CSRC.glob("*.inc")) + \
+    deps = list(CSRC.glob("*.cc")) + list(CSRC.glob("*.cu")) + list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.inc")) + \
         [HERE.parent / "include" / "b200_core.h"]
     return any(d.stat().st_mtime > t for d in deps)
 

@@ -36,6 +36,94 @@ const char* codegen_prelude() {
 namespace {
 
 // ---------------------------------------------------------------------------
+// dot_general on two 16-bit floating-point operands of one type: geometry for the native kernels (gemm16.cu)
+// ---------------------------------------------------------------------------
+// Each operand must be a strided matrix per batch group: its batch, free and contracting dimensions each collapse
+// to one stride, and m or k (n or k) is contiguous. An operand whose row stride is not a multiple of 16 bytes
+// (a vocabulary of 30522 columns) is copied once into rows padded to a multiple of eight elements, which TMA can
+// address; what the padding holds never matters, the copy engine reads zeros outside the declared extent.
+struct Dot16 {
+  Gemm16Launch g;
+  struct Repack { bool needed = false; long long rows = 0, cols = 0, src_ld = 0, dst_ld = 0; } ra, rb;
+};
+
+bool dot16_geometry(Op* op, Dot16& d) {
+  if (op->operands.size() != 2 || op->results.size() != 1 || getenv("B200_NO_GEMM16")) return false;
+  Value *lhs = op->operands[0], *rhs = op->operands[1], *out = op->results[0];
+  const DT dt = lhs->type.dt;
+  if (dt != rhs->type.dt || !(dt == DT::BF16 || dt == DT::F16)) return false;
+  if (!(out->type.dt == dt || out->type.dt == DT::F32)) return false;
+  if (!op->has("dot_dimension_numbers")) return false;
+  auto f = attr_struct(op->attr("dot_dimension_numbers"));
+  auto lbd = f["lhs_batching_dimensions"], rbd = f["rhs_batching_dimensions"];
+  auto lcd = f["lhs_contracting_dimensions"], rcd = f["rhs_contracting_dimensions"];
+  auto in = [](const std::vector<int64_t>& v, int64_t x) { return std::find(v.begin(), v.end(), x) != v.end(); };
+  std::vector<int64_t> lfree, rfree;
+  for (int k = 0; k < lhs->type.rank(); k++) if (!in(lbd, k) && !in(lcd, k)) lfree.push_back(k);
+  for (int k = 0; k < rhs->type.rank(); k++) if (!in(rbd, k) && !in(rcd, k)) rfree.push_back(k);
+  auto strides = [](const std::vector<int64_t>& dims) {
+    std::vector<int64_t> s(dims.size());
+    int64_t st = 1;
+    for (int k = (int)dims.size() - 1; k >= 0; k--) { s[k] = st; st *= dims[k]; }
+    return s;
+  };
+  // the row-major multi-index over `which` as extent and a single stride (false when it does not collapse)
+  auto collapse = [](const std::vector<int64_t>& dims, const std::vector<int64_t>& s, const std::vector<int64_t>& which,
+                     long long& extent, long long& stride) {
+    extent = 1;
+    stride = 0;
+    bool have = false;
+    for (int q = (int)which.size() - 1; q >= 0; q--) {
+      const int64_t dsz = dims[which[q]];
+      if (dsz == 1) continue;
+      if (!have) { stride = s[which[q]]; have = true; }
+      else if (s[which[q]] != stride * extent) return false;
+      extent *= dsz;
+    }
+    return true;
+  };
+  auto sl = strides(lhs->type.dims), sr = strides(rhs->type.dims);
+  long long G, G2, M, N, K, K2;
+  Gemm16Launch& g = d.g;
+  if (!collapse(lhs->type.dims, sl, lbd, G, g.a_gs) || !collapse(rhs->type.dims, sr, rbd, G2, g.b_gs) ||
+      !collapse(lhs->type.dims, sl, lfree, M, g.a_ms) || !collapse(rhs->type.dims, sr, rfree, N, g.b_ns) ||
+      !collapse(lhs->type.dims, sl, lcd, K, g.a_ks) || !collapse(rhs->type.dims, sr, rcd, K2, g.b_ks))
+    return false;
+  if (G != G2 || K != K2 || G <= 0 || M <= 0 || N <= 0 || K < 8) return false;
+  if (G > 65535 || M >= (1LL << 31) || N >= (1LL << 31) || K >= (1LL << 31)) return false;
+  // an index of extent 1 has no stride of its own: give it the one that makes the operand a plain matrix
+  if (K == 1) return false;
+  if (M == 1) g.a_ms = g.a_ks == 1 ? K : 1;
+  if (N == 1) g.b_ns = g.b_ks == 1 ? K : 1;
+  g.M = (int)M; g.N = (int)N; g.K = (int)K; g.G = (int)G;
+  g.in_fmt = dt == DT::BF16 ? 1 : 0;
+  g.c_kind = out->type.dt == DT::F32 ? 2 : g.in_fmt;
+  if (!((g.a_ks == 1 || g.a_ms == 1) && (g.b_ks == 1 || g.b_ns == 1))) return false;
+  if (M <= 8) {
+    Gemm16Launch t = g;
+    if (gemm16_plan(t, false) && t.path != 0) { g = t; return true; }
+  }
+  // tensor-core tiles: TMA needs 16-byte strides
+  auto fix = [&](long long& ld, long long& gs, long long outer, long long inner, Dot16::Repack& r) {
+    if (ld % 8 == 0 && (G == 1 || gs % 8 == 0)) return true;
+    if (!(G == 1 || gs == outer * ld)) return false;        // groups must continue the rows
+    r.needed = true;
+    r.rows = G * outer;
+    r.cols = inner;
+    r.src_ld = ld;
+    r.dst_ld = (inner + 7) / 8 * 8;
+    ld = r.dst_ld;
+    gs = outer * r.dst_ld;
+    return true;
+  };
+  if (g.a_ks == 1) { if (!fix(g.a_ms, g.a_gs, M, K, d.ra)) return false; }
+  else if (!fix(g.a_ks, g.a_gs, K, M, d.ra)) return false;
+  if (g.b_ks == 1) { if (!fix(g.b_ns, g.b_gs, N, K, d.rb)) return false; }
+  else if (!fix(g.b_ks, g.b_gs, K, N, d.rb)) return false;
+  return gemm16_plan(g, true);
+}
+
+// ---------------------------------------------------------------------------
 // pass 1: inlining and pass-through removal
 // ---------------------------------------------------------------------------
 struct Inliner {
@@ -293,12 +381,15 @@ struct Inliner {
         }
       }
     }
-    // dot_general / convolution on bf16 or f16 operands: computed as the f32 contraction of the converted
+    // dot_general on two bf16 (or two f16) operands in matrix form goes to the native 16-bit kernels (lower_dot16).
+    // Any other dot_general / convolution on bf16 or f16 operands: computed as the f32 contraction of the converted
     // operands and rounded once at the end. Products of two bf16 (or f16) numbers and their fp32 accumulation
     // are what XLA's CPU backend computes for these types; the converts fuse into neighbouring kernels.
     if ((sh == "dot_general" || sh == "convolution") && op->operands.size() == 2 && op->results.size() == 1) {
       auto half = [](DT d) { return d == DT::BF16 || d == DT::F16; };
-      if (half(op->operands[0]->type.dt) || half(op->operands[1]->type.dt) || half(op->results[0]->type.dt)) {
+      Dot16 native;
+      const bool is_native = sh == "dot_general" && dot16_geometry(op.get(), native);
+      if (!is_native && (half(op->operands[0]->type.dt) || half(op->operands[1]->type.dt) || half(op->results[0]->type.dt))) {
         auto convert_to = [&](Value* v, DT to, Value* into) -> Value* {
           // The widened copy of an operand that comes from outside a `while` (weights read by a decode loop) is
           // made once in front of the loop instead of in every iteration: the convert moves out through every
@@ -1365,6 +1456,51 @@ struct Planner {
     return make_igemm(op, p, lhs, rhs, out, arow, acol, bcol, bn, crow, cn, ag, bg, cg, st);
   }
 
+  // dot_general on 16-bit operands: optional row repacks, then one GEMM16 step (args: A, B, C, [fp32 scratch],
+  // [counters]; iparams: which of the two optional arguments are present).
+  void lower_dot16(Op* op, const Dot16& d, Plan& plan, BlockState& st) {
+    Value *lhs = op->operands[0], *rhs = op->operands[1], *out = op->results[0];
+    auto operand = [&](Value* v, const Dot16::Repack& r) -> int {
+      if (!r.needed) return slot_of.at(v);
+      auto key = std::make_tuple(st.block, v, r.dst_ld);
+      auto it = repacked.find(key);
+      if (it != repacked.end()) return it->second;
+      TensorType t;
+      t.dt = v->type.dt;
+      t.dims = {(int64_t)r.rows, (int64_t)r.dst_ld};
+      const int tmp = new_slot(Slot::TEMP, t, st.arena);
+      Step c;
+      c.kind = Step::REPACK16;
+      c.label = "row repack for " + op->name;
+      c.args = {tmp, slot_of.at(v)};
+      c.iparams = {r.rows, r.cols, r.dst_ld, r.src_ld};
+      plan.steps.push_back(std::move(c));
+      repacked[key] = tmp;
+      return tmp;
+    };
+    Step s;
+    s.kind = Step::GEMM16;
+    s.label = op->name;
+    s.g16 = d.g;
+    const int a = operand(lhs, d.ra), b = operand(rhs, d.rb);
+    s.args = {a, b, slot_of.at(out)};
+    s.iparams = {0, 0};
+    if (d.g.scratch_floats > 0) {
+      TensorType t;
+      t.dt = DT::F32;
+      t.dims = {(int64_t)d.g.scratch_floats};
+      s.args.push_back(new_slot(Slot::TEMP, t, st.arena));
+      s.iparams[0] = 1;
+    }
+    if (d.g.counters > 0) {
+      std::vector<int> zeros((size_t)d.g.counters, 0);
+      s.args.push_back(table_slot(zeros.data(), zeros.size() * sizeof(int)));
+      s.iparams[1] = 1;
+    }
+    plan.steps.push_back(std::move(s));
+  }
+  std::map<std::tuple<Block*, Value*, long long>, int> repacked;   // padded copies of operands, per block
+
   Step lower_dot(Op* op, BlockState& st) {
     Value *lhs = op->operands[0], *rhs = op->operands[1], *out = op->results[0];
     if (lhs->type.dt != DT::F32 || rhs->type.dt != DT::F32 || out->type.dt != DT::F32)
@@ -2046,6 +2182,8 @@ struct Planner {
           for (auto* o : op->operands)
             if (!slot_of.count(o)) throw CompileError("internal: operand of " + op->name + " has no storage");
           if (op->results[0]->type.numel() == 0) break;
+          Dot16 native;
+          if (c == Cat::DOT && dot16_geometry(op, native)) { lower_dot16(op, native, plan, st); break; }
           Step s = c == Cat::CONV ? lower_conv(op, st) : lower_dot(op, st);
           plan.steps.push_back(std::move(s));
           break;
@@ -2565,6 +2703,12 @@ void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& o
            << " a_contig=" << s.ig.a_contig << " b_contig=" << s.ig.b_contig << " vec=" << s.ig.vec << " seg=" << s.ig.seg << (s.ig.kt_stride ? " ktlist" : "") << " " << s.label;
         break;
       case Step::MEMCPY: os << "memcpy " << s.bytes; break;
+      case Step::GEMM16:
+        os << (s.g16.path == 0 ? "gemm16" : s.g16.path == 1 ? "gemv16_nc" : "gemv16_kc") << " M=" << s.g16.M << " N=" << s.g16.N
+           << " K=" << s.g16.K << " G=" << s.g16.G << " a_kcontig=" << (s.g16.a_ks == 1) << " b_kcontig=" << (s.g16.b_ks == 1)
+           << " bn=" << s.g16.bn << " splitK=" << s.g16.split_k << " out=" << (s.g16.c_kind == 2 ? "f32" : "16") << " " << s.label;
+        break;
+      case Step::REPACK16: os << "repack16 rows=" << s.iparams[0] << " cols=" << s.iparams[1] << " ld " << s.iparams[3] << "->" << s.iparams[2]; break;
       case Step::WHILE:
         os << "while trip=" << s.trip_count << " exchanged=" << std::count(s.swap.begin(), s.swap.end(), (char)1) << "/" << s.state.size();
         break;
@@ -2680,6 +2824,8 @@ std::unique_ptr<CompiledProgram> compile_module(Module& m, const CompileOptions&
         if (s.kind == Step::KERNEL || s.kind == Step::ALL_REDUCE) n += 1;
         else if (s.kind == Step::SCATTER) n += 2;
         else if (s.kind == Step::IGEMM) n += s.ig.split_k > 1 ? 2 : 1;
+        else if (s.kind == Step::GEMM16) n += (s.g16.path == 0 && s.g16.split_k > 1) ? 2 : 1;
+        else if (s.kind == Step::REPACK16) n += (s.iparams[0] + 65534) / 65535;
         else if (s.kind == Step::WHILE) {
           if (s.trip_count < 0) { dynamic = true; continue; }
           n += s.trip_count * count(*s.sub[1]);      // a counted loop never evaluates its condition

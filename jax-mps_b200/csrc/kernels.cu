@@ -21,6 +21,7 @@
 #include <cstdio>
 
 #include "kernels.h"
+#include "tc_util.cuh"
 
 namespace b200 {
 
@@ -281,33 +282,6 @@ constexpr int TBM = 128, TBN = 64, TBK = 32, TSTAGES = 2, TNT = 256;
 constexpr int TA_BYTES = TBM * TBK * 4, TB_BYTES = TBN * TBK * 4;
 constexpr int TSTAGE_BYTES = 2 * TA_BYTES + 2 * TB_BYTES;
 constexpr int TSMEM_BYTES = TSTAGES * TSTAGE_BYTES + 1024 + 64;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-// Bounded wait: false when the phase did not complete within the budget.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int spin = 0; spin < (1 << 22); ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-  // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart (SBO), LBO unused (1), descriptor version 1
-  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
-         (2ull << 61);
-}
 
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -654,19 +628,6 @@ struct WsCfg {
 };
 // role sizes: chunk gather 512 + 256 low-part threads, segment gather 256 + 512; one more warp issues the MMAs
 constexpr int WS_THREADS = 768 + 32;
-
-// One lane of a converged warp. The MMA warps run their loops with all 32 lanes (so that descriptor arithmetic
-// stays warp-uniform) and only the elected lane issues tcgen05.mma / tcgen05.commit: issued from a loop that a
-// single thread runs alone, the same instruction stream feeds the tensor core at two thirds of the rate.
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-  return pred != 0;
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 
 // Accumulator read-back shared by the tensor-core kernels: eight warps; warp `ew` reads TMEM lanes 32 * (ew & 3) ..
 // (row m0 + lane of that quadrant) and the column half ew >> 2, waits (bounded) for the MMAs of the last k-tile

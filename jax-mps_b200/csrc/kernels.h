@@ -2,6 +2,8 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include "gemm16.h"
+
 namespace b200 {
 
 struct IGemmLaunch {
@@ -44,4 +46,25 @@ cudaError_t launch_scatter_rows(int elem_kind, int index_bytes, int kind, long l
 cudaError_t matmul_f32_static_scratch(const float* A, const float* B, float* C, int M, int N, int K, cudaStream_t stream,
                                       const char** why);
 size_t static_scratch_bytes();
+}  // namespace b200
+
+namespace b200 {
+// Contractions of 16-bit floating-point operands (bf16 or f16) with fp32 accumulation and one rounding to the
+// result type: C[g][m][n] = sum_k A(g, m, k) * B(g, k, n), C dense row-major [G][M][N]. Each operand is a strided
+// matrix per group with one of its two strides equal to 1 (the reference forwards these to MLX matmul / einsum:
+// src/pjrt_plugin/ops/linalg.cc:89-250). Three kernels:
+//   path 0  gemm16_tma_kernel : persistent tcgen05.mma kind::f16 tiles of 128 x {64, 128, 256}, operands moved by TMA
+//                               tiled copies into 128-byte-swizzled shared memory, accumulators double-buffered in
+//                               tensor memory; needs 16-byte aligned bases and strides
+//   path 1  gemv16_nc_kernel  : M <= 8 and n contiguous in B: every element of B is read once with 128-bit loads,
+//                               K split over warps and CTAs, the last CTA of a column panel adds the splits in order
+//   path 2  gemv16_kc_kernel  : M <= 8 and k contiguous in B: one warp per group of output columns, warp-shuffle tree
+// `scratch` (fp32, g.scratch_floats) and `counters` may be null when the plan needs none.
+cudaError_t launch_gemm16(const Gemm16Launch& g, const void* A, const void* B, void* C, float* scratch, int* counters,
+                          int* error_flag, cudaStream_t stream, int* launches, const char** why);
+
+// dst[r][0..cols) = src[r][0..cols) for `rows` rows of 16-bit elements with row strides dst_ld / src_ld (elements): makes
+// an operand whose row stride is not a multiple of 16 bytes readable by TMA.
+cudaError_t launch_repack_rows16(void* dst, const void* src, long long rows, long long cols, long long dst_ld,
+                                 long long src_ld, cudaStream_t stream, int* launches);
 }  // namespace b200

@@ -12,6 +12,7 @@
 #include <string>
 #include <vector>
 
+#include "gemm16.h"
 #include "ir.h"
 
 namespace b200 {
@@ -49,7 +50,7 @@ struct IGemmParams {
 struct Plan;
 
 struct Step {
-  enum Kind { KERNEL, IGEMM, MEMCPY, MEMSET, WHILE, CASE, ALL_REDUCE, SCATTER, JOIN } kind = KERNEL;
+  enum Kind { KERNEL, IGEMM, MEMCPY, MEMSET, WHILE, CASE, ALL_REDUCE, SCATTER, JOIN, GEMM16, REPACK16 } kind = KERNEL;
   std::string label;                  // op names, for profiling and error text
   // KERNEL
   int kernel = -1;                    // index into Executable::kernels
@@ -58,6 +59,9 @@ struct Step {
   int n_outs = 0;                     // KERNEL: the first n_outs args are written, the rest only read
   // IGEMM: args = {A, B, C, a_row, a_col, b_row(k), b_col(n), c_row(m), c_col(n), a_grp, b_grp, c_grp, [split-K scratch]}
   IGemmParams ig;
+  // GEMM16: args = {A, B, C, [fp32 scratch], [counters]}; iparams = {has scratch, has counters}
+  // REPACK16: args = {dst, src}; iparams = {rows, cols, dst_ld, src_ld}
+  Gemm16Launch g16;
   // MEMCPY: args = {dst, src}; MEMSET: args = {dst}
   size_t bytes = 0;
   // WHILE: sub[0] = cond, sub[1] = body; state/init/next slot lists; pred slot

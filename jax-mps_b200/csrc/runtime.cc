@@ -524,7 +524,7 @@ b200_error* run_plan(ExecCtx& x, const Plan& plan);
 bool graph_safe(const Plan& plan) {
   for (const Step& s : plan.steps) {
     switch (s.kind) {
-      case Step::KERNEL: case Step::IGEMM: case Step::MEMCPY: break;
+      case Step::KERNEL: case Step::IGEMM: case Step::MEMCPY: case Step::GEMM16: case Step::REPACK16: break;
       case Step::WHILE:
         if (s.trip_count < 0 || !graph_safe(*s.sub[1])) return false;
         break;
@@ -578,6 +578,23 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       const int* kt_table = s.ig.kt_stride > 0 ? (const int*)x.ptrs[s.args.back()] : nullptr;
       cudaError_t e = launch_igemm_f32(p, x.ptrs[s.args[0]], x.ptrs[s.args[1]], x.ptrs[s.args[2]], tables, partial,
                                        kt_table, c->error_flag, st, &x.launches);
+      if (e != cudaSuccess) return make_error(B200_INTERNAL, "launch of " + s.label + " failed: " + cudaGetErrorString(e));
+      return nullptr;
+    }
+    case Step::GEMM16: {
+      size_t next = 3;
+      float* scratch = s.iparams[0] ? (float*)x.ptrs[s.args[next++]] : nullptr;
+      int* counters = s.iparams[1] ? (int*)x.ptrs[s.args[next++]] : nullptr;
+      const char* why = nullptr;
+      cudaError_t e = launch_gemm16(s.g16, x.ptrs[s.args[0]], x.ptrs[s.args[1]], x.ptrs[s.args[2]], scratch, counters,
+                                    c->error_flag, st, &x.launches, &why);
+      if (e != cudaSuccess)
+        return make_error(B200_INTERNAL, "launch of " + s.label + " failed: " + (why ? why : cudaGetErrorString(e)));
+      return nullptr;
+    }
+    case Step::REPACK16: {
+      cudaError_t e = launch_repack_rows16(x.ptrs[s.args[0]], x.ptrs[s.args[1]], s.iparams[0], s.iparams[1], s.iparams[2],
+                                           s.iparams[3], st, &x.launches);
       if (e != cudaSuccess) return make_error(B200_INTERNAL, "launch of " + s.label + " failed: " + cudaGetErrorString(e));
       return nullptr;
     }
@@ -835,6 +852,12 @@ b200_error* run_plan(ExecCtx& x, const Plan& plan) {
             t.kind = "igemm_fma";
           break;
         case Step::ALL_REDUCE: t.kind = "all_reduce"; t.key = "all_reduce " + std::to_string(s.bytes); break;
+        case Step::GEMM16:
+          t.kind = s.g16.path == 0 ? "gemm16" : "gemv16";
+          t.key = t.kind + " M=" + std::to_string(s.g16.M) + " N=" + std::to_string(s.g16.N) + " K=" + std::to_string(s.g16.K) +
+                  " G=" + std::to_string(s.g16.G) + " a_kcontig=" + std::to_string(s.g16.a_ks == 1) + " b_kcontig=" +
+                  std::to_string(s.g16.b_ks == 1) + " bn=" + std::to_string(s.g16.bn) + " splitK=" + std::to_string(s.g16.split_k);
+          break;
         default: t.kind = "copy"; t.key = s.label; break;
       }
       cudaEventCreate(&t.a);
