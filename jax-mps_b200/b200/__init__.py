@@ -394,11 +394,13 @@ class Client:
     compile_and_load = compile
 
     def buffer_from_host(self, array, dtype: str | None = None) -> Buffer:
-        """Host array -> device buffer. `dtype='bf16'` converts float32 input to bfloat16 on the host."""
+        """Host array -> device buffer. `dtype='bf16'` converts float32 input to bfloat16 on the host (a uint16 array
+        is taken as bfloat16 bit patterns as it is)."""
         a = np.asarray(array)
         if dtype == "bf16":
-            from .shlo.builder import f32_to_bf16_bits
-            a = f32_to_bf16_bits(a.astype(np.float32)).reshape(a.shape)
+            if a.dtype != np.uint16:                      # uint16 input is taken as bfloat16 bit patterns
+                from .shlo.builder import f32_to_bf16_bits
+                a = f32_to_bf16_bits(a.astype(np.float32)).reshape(a.shape)
             code = BF16
         else:
             if dtype is not None:

@@ -4,6 +4,13 @@ captures summarised under profiles/, and handy when tuning a kernel):
     python -m b200.bench_ops conv --case s1 [--reps 10]
     python -m b200.bench_ops reduce --shape 128,32,32,64 --dims 0,1,2
     python -m b200.bench_ops scan [--reps 10]
+    python -m b200.bench_ops gemma [--layers 18] [--reps 3] [--profile]
+    python -m b200.bench_ops distilbert [--reps 5] [--profile]
+    python -m b200.bench_ops gemm --shape M,N,K [--reps 20]
+
+`gemma` times the Gemma-2B-shaped prefill (512 prompt tokens in one pass) and the 128-step greedy decode loop (bf16
+weights resident in HBM); `distilbert` the DistilBERT-base-shaped masked-LM step (forward + backward, bf16); `gemm` one
+bf16 product [M,K] x [K,N]. `--profile` prints the device time per kernel class from CUDA events around every plan step.
 
 `scan` times the full-size LSTM-by-scan training step (100 time steps, batch 64, 32 -> 256 -> 256, Adam: a forward
 and a reverse counted loop, 200 dependent iterations) and, beside it, the floor of one dependent kernel launch
@@ -72,9 +79,154 @@ def scan(client, reps):
           f"({per:.0f} launch per iteration, {trips} iterations)")
 
 
+def _events(client):
+    """(record, elapsed_ms) timing with CUDA events on the client's own compute stream."""
+    import torch
+    stream = torch.cuda.ExternalStream(client.compute_stream())
+    def record():
+        ev = torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            ev.record()
+        return ev
+    return record
+
+
+def _by_kind(rep, reps=1):
+    out = {}
+    for r in rep:
+        k = out.setdefault(r["kind"], {"ms": 0.0, "count": 0})
+        k["ms"] += r["ms"] / reps
+        k["count"] += r["count"] // reps
+    return out
+
+
+def gemma_decode(client, reps=3, profile=False, hbm_gbs=6546.2, verbose=False, **shape):
+    """Prefill once, then the decode loop `reps` times from the prefilled caches. Returns times, tokens per second and
+    the fraction of the HBM roofline (bytes of weights read per token / time per token / copy bandwidth)."""
+    from b200.shlo import programs
+    pre = programs.gemma_prefill(**{k: v for k, v in shape.items() if k not in ("start", "new_tokens")})
+    kw = dict(shape)
+    kw.pop("prompt_len", None)
+    dec = programs.gemma_decode_loop(start=pre.meta["prompt_len"], **kw)
+    n_w = len(pre.args) - 1
+    weights = programs.gemma_weights([(n, s) for n, s, _ in pre.args[:n_w]], seed=0, as_bits=True)
+    wb = [client.buffer_from_host(w, dtype="bf16") for w in weights]
+    del weights
+    prompt = np.random.default_rng(1).integers(0, pre.meta["vocab"], pre.meta["prompt_len"]).astype(np.int32)
+    pb = client.buffer_from_host(prompt)
+    e_pre, e_dec = client.compile(pre.text), client.compile(dec.text)
+    record = _events(client)
+    outs = e_pre.execute(wb + [pb])
+    client.synchronize()
+    a = record()
+    outs = e_pre.execute(wb + [pb])
+    b = record()
+    client.synchronize()
+    prefill_ms = a.elapsed_time(b)
+    tok, caches = outs[0], outs[2:]
+    d = e_dec.execute(wb + [tok] + caches)          # first run records the loop's graph
+    client.synchronize()
+    times = []
+    for _ in range(reps):
+        a = record()
+        d = e_dec.execute(wb + [tok] + caches)
+        b = record()
+        client.synchronize()
+        times.append(a.elapsed_time(b))
+    n_new = dec.meta["new_tokens"]
+    ms = sorted(times)[len(times) // 2]
+    res = {"prefill_ms": prefill_ms, "decode_ms": ms, "decode_ms_all": times, "new_tokens": n_new,
+           "tok_s": n_new / (ms * 1e-3), "ms_per_token": ms / n_new, "weight_bytes_per_token": dec.meta["weight_bytes"],
+           "hbm_frac": dec.meta["weight_bytes"] / (ms / n_new * 1e-3) / (hbm_gbs * 1e9),
+           "launches_per_token": e_dec.launches_per_execute / n_new, "tokens": d[0].to_numpy().tolist()}
+    if profile:
+        client.set_profiling(True)
+        e_dec.execute(wb + [tok] + caches)
+        client.set_profiling(False)
+        rep = client.profile_report()
+        res["decode_by_kind"] = {k: {"ms_per_token": v["ms"] / n_new, "per_token": v["count"] / n_new} for k, v in _by_kind(rep).items()}
+        if verbose:
+            for r in sorted(rep, key=lambda r: -r["ms"])[:25]:
+                print(f"  {r['ms'] / n_new * 1e3:9.1f} us/token x{r['count'] // n_new:<3d} {r['kind']:8s} {r['key'][:110]}")
+        client.set_profiling(True)
+        e_pre.execute(wb + [pb])
+        client.set_profiling(False)
+        rep = client.profile_report()
+        res["prefill_by_kind"] = {k: {"ms": v["ms"], "count": v["count"]} for k, v in _by_kind(rep).items()}
+        if verbose:
+            for r in sorted(rep, key=lambda r: -r["ms"])[:20]:
+                print(f"  {r['ms'] * 1e3:9.1f} us x{r['count']:<3d} {r['kind']:8s} {r['key'][:110]}")
+    return res
+
+
+def distilbert_step(client, reps=5, profile=False, verbose=False, **shape):
+    """The DistilBERT-base-shaped masked-LM step (loss and every gradient, bf16). FLOP: 2 * 3 * 67.7 M multiply-adds per
+    token over 4096 tokens (six layers and the tied-projector head, forward and two backward products)."""
+    from b200.shlo import programs
+    prog = programs.distilbert_mlm_step(**shape)
+    args = programs.distilbert_inputs(prog, seed=0)
+    dtypes = [d for _, _, d in prog.args]
+    bufs = [client.buffer_from_host(a, dtype=(d if d == "bf16" else None)) for a, d in zip(args, dtypes)]
+    exe = client.compile(prog.text)
+    record = _events(client)
+    for _ in range(3):
+        outs = exe.execute(bufs)
+    client.synchronize()
+    times = []
+    for _ in range(reps):
+        a = record()
+        outs = exe.execute(bufs)
+        b = record()
+        client.synchronize()
+        times.append(a.elapsed_time(b))
+    ms = sorted(times)[len(times) // 2]
+    m = prog.meta
+    tokens = m["batch"] * m["seq"]
+    layers, dim, vocab = shape.get("layers", 6), m["dim"], m["vocab"]
+    ffn, seq = shape.get("ffn", 3072), m["seq"]
+    mac_per_token = layers * (4 * dim * dim + 2 * dim * ffn + 2 * seq * dim) + dim * dim + dim * vocab
+    flop = 2.0 * 3 * mac_per_token * tokens
+    res = {"step_ms": ms, "step_ms_all": times, "flop": flop, "tflops": flop / (ms * 1e-3) / 1e12,
+           "loss": float(outs[0].to_numpy()), "launches": exe.launches_per_execute}
+    if profile:
+        client.set_profiling(True)
+        exe.execute(bufs)
+        client.set_profiling(False)
+        rep = client.profile_report()
+        res["by_kind"] = {k: {"ms": v["ms"], "count": v["count"]} for k, v in _by_kind(rep).items()}
+        if verbose:
+            for r in sorted(rep, key=lambda r: -r["ms"])[:40]:
+                print(f"  {r['ms'] * 1e3:9.1f} us x{r['count']:<3d} {r['kind']:8s} {r['key'][:120]}")
+    return res
+
+
+def gemm(client, m, n, k, reps):
+    b = Builder()
+    x, w = b.arg((m, k), "bf16"), b.arg((k, n), "bf16")
+    text = b.module([b.matmul(x, w)])
+    rng = np.random.default_rng(0)
+    exe = client.compile(text)
+    bufs = [client.buffer_from_host(rng.standard_normal((m, k)).astype(np.float32), dtype="bf16"),
+            client.buffer_from_host(rng.standard_normal((k, n)).astype(np.float32), dtype="bf16")]
+    record = _events(client)
+    for _ in range(3):
+        exe.execute(bufs)
+    client.synchronize()
+    a = record()
+    for _ in range(reps):
+        exe.execute(bufs)
+    e = record()
+    client.synchronize()
+    ms = a.elapsed_time(e) / reps
+    print(f"gemm bf16 {m}x{n}x{k}: {ms * 1e3:.1f} us, {2.0 * m * n * k / ms / 1e9:.1f} TFLOP/s; plan: "
+          + " | ".join(l.strip()[:90] for l in exe.plan_text().splitlines()[1:]))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["conv", "reduce", "scan"])
+    ap.add_argument("what", choices=["conv", "reduce", "scan", "gemma", "distilbert", "gemm"])
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--profile", action="store_true")
     ap.add_argument("--case", default="s1")
     ap.add_argument("--shape", default="128,32,32,64")
     ap.add_argument("--dims", default="0,1,2")
@@ -85,6 +237,22 @@ def main():
     b = Builder()
     if a.what == "scan":
         scan(client, a.reps)
+        return
+    if a.what == "gemma":
+        import json
+        kw = {"layers": a.layers} if a.layers else {}
+        res = gemma_decode(client, reps=min(a.reps, 5), profile=a.profile, verbose=True, **kw)
+        res.pop("tokens")
+        print(json.dumps(res))
+        return
+    if a.what == "distilbert":
+        import json
+        kw = {"layers": a.layers} if a.layers else {}
+        print(json.dumps(distilbert_step(client, reps=a.reps, profile=a.profile, verbose=True, **kw)))
+        return
+    if a.what == "gemm":
+        m, n, k = (int(v) for v in a.shape.split(","))
+        gemm(client, m, n, k, a.reps)
         return
     if a.what == "conv":
         xs, ws = CONV_CASES[a.case]

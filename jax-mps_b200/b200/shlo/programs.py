@@ -319,6 +319,192 @@ def gemma_greedy_decode(vocab: int = 256000, dim: int = 2048, layers: int = 18, 
                    {"vocab": vocab, "dim": dim, "layers": layers, "prompt_len": prompt_len, "new_tokens": new_tokens})
 
 
+def _gemma_ops(dim: int, heads: int, head_dim: int, dtype: str):
+    """Building blocks shared by the prefill and the decode-loop programs (examples/gemma/model.py:118-296 of the
+    reference): RMSNorm with the weight stored as (1 + w), rotate-half rotary embedding, tanh GELU, and a linear
+    layer that rounds its input to `dtype`, multiplies by a `dtype` weight and returns f32."""
+    half = head_dim // 2
+
+    def rms_norm(s, x, w):                           # x f32[rows, dim]
+        rows = x.shape[0]
+        ms = s.mean(s.mul(x, x), (1,))
+        inv = s.rsqrt(s.add(ms, s.full((rows,), 1e-6, "f32")))
+        scale = s.add(s.convert(w, "f32"), s.full((dim,), 1.0, "f32"))
+        return s.mul(s.mul(x, s.bcast(inv, x.shape, (0,))), s.bcast(scale, x.shape, (1,)))
+
+    def rope(s, x, cos, sin):                        # x f32[rows, n, head_dim]; cos, sin f32[rows, half]
+        rows, n = x.shape[0], x.shape[1]
+        x1, x2 = s.slice(x, (0, 0, 0), (rows, n, half)), s.slice(x, (0, 0, half), (rows, n, head_dim))
+        c, sn = s.bcast(cos, (rows, n, half), (0, 2)), s.bcast(sin, (rows, n, half), (0, 2))
+        return s.concatenate([s.sub(s.mul(x1, c), s.mul(x2, sn)), s.add(s.mul(x2, c), s.mul(x1, sn))], 2)
+
+    def gelu(s, x):
+        c = s.full(x.shape, math.sqrt(2.0 / math.pi), "f32")
+        inner = s.mul(c, s.add(x, s.mul(s.full(x.shape, 0.044715, "f32"), s.mul(x, s.mul(x, x)))))
+        return s.mul(s.mul(x, s.full(x.shape, 0.5, "f32")), s.add(s.full(x.shape, 1.0, "f32"), s.tanh(inner)))
+
+    def lin(s, x, w):                                # f32[rows, k] through a `dtype` weight, `dtype` product, f32 out
+        return s.convert(s.matmul(s.convert(x, dtype), w), "f32")
+
+    return rms_norm, rope, gelu, lin
+
+
+def gemma_prefill(vocab: int = 256000, dim: int = 2048, layers: int = 18, heads: int = 8, head_dim: int = 256,
+                  hidden: int = 16384, prompt_len: int = 512, cache_len: int = 640, dtype: str = "bf16") -> Program:
+    """The whole prompt in one pass (the `prefill` jit of examples/gemma/main.py:109-123 of the reference): every
+    projection is a product with `prompt_len` rows, attention is causal over the prompt with the one key-value head
+    shared by all query heads, and the keys (after the rotary embedding) and values are written into static caches
+    of `cache_len` positions. Arguments: the weights, prompt i32[prompt_len]. Results: the first generated token
+    i32[1], the logits f32[vocab] of the last prompt position, then for every layer the key and the value cache
+    `dtype`[cache_len, head_dim]."""
+    spec = gemma_param_spec(vocab, dim, layers, heads, head_dim, hidden)
+    T, H, half = prompt_len, heads, head_dim // 2
+    assert T <= cache_len
+    b = Builder()
+    W = {n: b.arg(s, dtype) for n, s in spec}
+    prompt = b.arg((T,), "i32")
+    rms_norm, rope, gelu, lin = _gemma_ops(dim, heads, head_dim, dtype)
+    inv_freq = b.const_array((1.0 / (10000.0 ** (np.arange(half, dtype=np.float64) * 2 / head_dim))).astype(np.float32))
+    pos = b.convert(b.iota((T,), "i32", 0), "f32")
+    ang = b.mul(b.bcast(pos, (T, half), (0,)), b.bcast(inv_freq, (T, half), (1,)))
+    cos, sin = b.cos(ang), b.sin(ang)
+    x = b.convert(b.take_rows(W["embed"], prompt), "f32")                             # [T, dim]
+    x = b.mul(x, b.full((T, dim), math.sqrt(dim), "f32"))
+    qi, kj = b.iota((H, T, T), "i32", 1), b.iota((H, T, T), "i32", 2)
+    visible = b.compare(kj, qi, "LE")
+    zero = b.const(0.0, dtype)
+    caches = []
+    for i in range(layers):
+        p = f"layer{i}."
+        h = rms_norm(b, x, W[p + "attn_norm"])
+        q = rope(b, b.reshape(lin(b, h, W[p + "wq"]), (T, H, head_dim)), cos, sin)       # [T, H, hd]
+        k = b.reshape(rope(b, b.reshape(lin(b, h, W[p + "wk"]), (T, 1, head_dim)), cos, sin), (T, head_dim))
+        v = lin(b, h, W[p + "wv"])
+        kb, vb = b.convert(k, dtype), b.convert(v, dtype)
+        caches += [b.pad(kb, zero, (0, 0), (cache_len - T, 0)), b.pad(vb, zero, (0, 0), (cache_len - T, 0))]
+        qb = b.convert(b.reshape(b.transpose(q, (1, 0, 2)), (H * T, head_dim)), dtype)
+        sc = b.convert(b.dot_general(qb, kb, ((1,), (1,))), "f32")                    # [H * T, T]
+        sc = b.reshape(b.mul(sc, b.full(sc.shape, 1.0 / math.sqrt(head_dim), "f32")), (H, T, T))
+        sc = b.select(visible, sc, b.full(sc.shape, -1e30, "f32"))
+        m = b.reduce_max(sc, (2,))
+        e = b.exp(b.sub(sc, b.bcast(m, sc.shape, (0, 1))))
+        pr = b.div(e, b.bcast(b.reduce_sum(e, (2,)), sc.shape, (0, 1)))
+        att = b.convert(b.matmul(b.convert(b.reshape(pr, (H * T, T)), dtype), vb), "f32")   # [H * T, hd]
+        att = b.reshape(b.transpose(b.reshape(att, (H, T, head_dim)), (1, 0, 2)), (T, H * head_dim))
+        x = b.add(x, lin(b, att, W[p + "wo"]))
+        h2 = rms_norm(b, x, W[p + "mlp_norm"])
+        ff = b.mul(gelu(b, lin(b, h2, W[p + "w_gate"])), lin(b, h2, W[p + "w_up"]))
+        x = b.add(x, lin(b, ff, W[p + "w_down"]))
+    last = b.slice(x, (T - 1, 0), (T, dim))
+    hf = b.convert(rms_norm(b, last, W["final_norm"]), dtype)
+    logits = b.reshape(b.convert(b.dot_general(hf, W["embed"], ((1,), (1,))), "f32"), (vocab,))
+    best = b.reshape(b.argmax(logits, 0), (1,))
+    text = b.module([best, logits, *caches], name="jit_prefill")
+    args = [(n, s, dtype) for n, s in spec] + [("prompt", (T,), "i32")]
+    res = [("token", (1,), "i32"), ("logits", (vocab,), "f32")]
+    for i in range(layers):
+        res += [(f"layer{i}.k_cache", (cache_len, head_dim), dtype), (f"layer{i}.v_cache", (cache_len, head_dim), dtype)]
+    return Program("gemma_prefill", text, args, res, 1,
+                   {"vocab": vocab, "dim": dim, "layers": layers, "prompt_len": T, "cache_len": cache_len})
+
+
+def gemma_decode_loop(vocab: int = 256000, dim: int = 2048, layers: int = 18, heads: int = 8, head_dim: int = 256,
+                      hidden: int = 16384, start: int = 512, new_tokens: int = 128, cache_len: int = 640,
+                      dtype: str = "bf16") -> Program:
+    """`new_tokens` greedy decode steps in one stablehlo.while (the decode loop of examples/gemma/main.py:125-134 of
+    the reference moved inside the program): every iteration embeds the current token, runs the decoder at position
+    `start + i` against the static key-value caches (updated in place by dynamic_update_slice) and takes the argmax
+    of the tied-embedding logits as the next token. Arguments: the weights, the current token i32[1], the caches as
+    `gemma_prefill` returns them. Results: the generated ids i32[new_tokens], the logits f32[vocab] of the last
+    step, the caches."""
+    spec = gemma_param_spec(vocab, dim, layers, heads, head_dim, hidden)
+    assert start + new_tokens <= cache_len
+    half = head_dim // 2
+    b = Builder()
+    W = {n: b.arg(s, dtype) for n, s in spec}
+    tok_in = b.arg((1,), "i32")
+    caches_in = [b.arg((cache_len, head_dim), dtype) for _ in range(2 * layers)]
+    rms_norm, rope, gelu, lin = _gemma_ops(dim, heads, head_dim, dtype)
+    inv_freq = b.const_array((1.0 / (10000.0 ** (np.arange(half, dtype=np.float64) * 2 / head_dim))).astype(np.float32))
+    pos_ids = b.iota((cache_len,), "i32", 0)
+    end = start + new_tokens
+
+    def cond(s, t, *rest):
+        return s.compare(t, s.const(end, "i32"), "LT")
+
+    def body(s, t, tok, toks, *caches):
+        z = s.const(0, "i32")
+        caches = list(caches)
+        x = s.convert(s.take_rows(W["embed"], tok), "f32")                              # [1, dim]
+        x = s.mul(x, s.full((1, dim), math.sqrt(dim), "f32"))
+        ang = s.reshape(s.mul(s.bcast(s.convert(t, "f32"), (half,)), inv_freq), (1, half))
+        cos, sin = s.cos(ang), s.sin(ang)
+        for i in range(layers):
+            p = f"layer{i}."
+            h = rms_norm(s, x, W[p + "attn_norm"])
+            q = s.reshape(rope(s, s.reshape(lin(s, h, W[p + "wq"]), (1, heads, head_dim)), cos, sin), (heads, head_dim))
+            k = s.reshape(rope(s, s.reshape(lin(s, h, W[p + "wk"]), (1, 1, head_dim)), cos, sin), (1, head_dim))
+            v = lin(s, h, W[p + "wv"])
+            kc = s.dynamic_update_slice(caches[2 * i], s.convert(k, dtype), [t, z])
+            vc = s.dynamic_update_slice(caches[2 * i + 1], s.convert(v, dtype), [t, z])
+            caches[2 * i], caches[2 * i + 1] = kc, vc
+            sc = s.convert(s.dot_general(s.convert(q, dtype), kc, ((1,), (1,))), "f32")   # [heads, cache_len]
+            sc = s.mul(sc, s.full(sc.shape, 1.0 / math.sqrt(head_dim), "f32"))
+            visible = s.compare(s.bcast(pos_ids, sc.shape, (1,)), s.bcast(t, sc.shape), "LE")
+            sc = s.select(visible, sc, s.full(sc.shape, -1e30, "f32"))
+            m = s.reduce_max(sc, (1,))
+            e = s.exp(s.sub(sc, s.bcast(m, sc.shape, (0,))))
+            pr = s.div(e, s.bcast(s.reduce_sum(e, (1,)), sc.shape, (0,)))
+            att = s.convert(s.matmul(s.convert(pr, dtype), vc), "f32")                    # [heads, head_dim]
+            x = s.add(x, lin(s, s.reshape(att, (1, heads * head_dim)), W[p + "wo"]))
+            h2 = rms_norm(s, x, W[p + "mlp_norm"])
+            ff = s.mul(gelu(s, lin(s, h2, W[p + "w_gate"])), lin(s, h2, W[p + "w_up"]))
+            x = s.add(x, lin(s, ff, W[p + "w_down"]))
+        hf = s.convert(rms_norm(s, x, W["final_norm"]), dtype)
+        logits = s.reshape(s.convert(s.dot_general(hf, W["embed"], ((1,), (1,))), "f32"), (vocab,))
+        best = s.reshape(s.argmax(logits, 0), (1,))
+        toks2 = s.dynamic_update_slice(toks, best, [s.sub(t, s.const(start, "i32"))])
+        return [s.add(t, s.const(1, "i32")), best, toks2, *caches, logits]
+
+    init = [b.const(start, "i32"), tok_in, b.full((new_tokens,), 0, "i32"), *caches_in, b.full((vocab,), 0.0, "f32")]
+    outs = b.while_(init, lambda s, *a: cond(s, *a), lambda s, t, tok, toks, *r: body(s, t, tok, toks, *r[:-1]))
+    text = b.module([outs[2], outs[-1], *outs[3:-1]], name="jit_decode_loop")
+    args = [(n, s, dtype) for n, s in spec] + [("token", (1,), "i32")]
+    res = [("tokens", (new_tokens,), "i32"), ("last_logits", (vocab,), "f32")]
+    for i in range(layers):
+        kv = [(f"layer{i}.k_cache", (cache_len, head_dim), dtype), (f"layer{i}.v_cache", (cache_len, head_dim), dtype)]
+        args += kv
+        res += kv
+    return Program("gemma_decode_loop", text, args, res, 1,
+                   {"vocab": vocab, "dim": dim, "layers": layers, "start": start, "new_tokens": new_tokens,
+                    "cache_len": cache_len, "weight_bytes": sum(int(np.prod(s)) for n, s in spec) * 2})
+
+
+def gemma_weights(spec, seed: int = 0, weight_std: float = 0.02, tile: int = 1 << 24, as_bits: bool = False) -> list:
+    """Weights ~N(0, weight_std) rounded to bfloat16 (norm weights 0, i.e. scale 1), as float32 arrays or, with
+    `as_bits`, as uint16 bit patterns. Tensors larger than `tile` elements are filled by repeating one block of `tile`
+    normal samples from a per-tensor random offset: drawing 2.5 billion samples one by one takes minutes, and neither
+    timing nor parity depends on independence across far-apart entries."""
+    from .builder import f32_to_bf16_bits
+    rng = np.random.default_rng(seed)
+    def bits(a): return f32_to_bf16_bits(a.astype(np.float32)).reshape(a.shape)
+    def back(b): return (b.astype(np.uint32) << 16).view(np.float32)
+    block = bits(rng.standard_normal(tile) * weight_std)
+    out = []
+    for n, s in spec:
+        size = int(np.prod(s))
+        if n.endswith("norm"):
+            w = np.zeros(s, np.uint16)
+        elif size <= tile:
+            w = bits(rng.standard_normal(s) * weight_std)
+        else:
+            off = int(rng.integers(0, tile))
+            reps = (size + off + tile - 1) // tile
+            w = np.tile(block, reps)[off:off + size].reshape(s)
+        out.append(w if as_bits else back(w))
+    return out
+
+
 def gemma_inputs(prog: Program, seed: int = 0, weight_std: float = 0.02) -> list:
     """Synthetic arguments: weights ~N(0, weight_std) (norm weights 0, i.e. scale 1), prompt uniform over the
     vocabulary. Returned as float32 / int32 arrays; float arguments are converted to the program's dtype on upload."""

@@ -141,3 +141,112 @@ def lstm_train_step(params, xs, targets, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e
         ms.append(m)
         vs.append(v)
     return float(loss), new_p, ms, vs
+
+
+class GemmaTwin:
+    """PyTorch-CPU twin of b200.shlo.programs.gemma_prefill / gemma_decode_loop (the decoder of
+    examples/gemma/model.py:118-296 of the reference: RMSNorm with weight 1 + w, rotate-half rotary embedding, one
+    shared key-value head, GeGLU feed-forward, tied embedding scaled by sqrt(dim)). Weights arrive as float32 arrays
+    holding bfloat16 values. Every product takes operands rounded to bfloat16, accumulates in fp32 and rounds its
+    result to bfloat16 once; norms, rotary embedding and softmax run in fp32: the rounding points of the program."""
+
+    def __init__(self, weights: dict, heads: int, head_dim: int, cache_len: int):
+        self.w = {k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in weights.items()}
+        self.layers = sum(1 for k in self.w if k.endswith(".wq"))
+        self.heads, self.hd, self.cache_len = heads, head_dim, cache_len
+        self.dim = self.w["embed"].shape[1]
+        half = head_dim // 2
+        self.inv_freq = torch.from_numpy((1.0 / (10000.0 ** (np.arange(half, dtype=np.float64) * 2 / head_dim))).astype(np.float32))
+        self.k = [torch.zeros(cache_len, head_dim) for _ in range(self.layers)]
+        self.v = [torch.zeros(cache_len, head_dim) for _ in range(self.layers)]
+
+    @staticmethod
+    def bf(x):
+        return x.to(torch.bfloat16).to(torch.float32)
+
+    def lin(self, x, w):
+        return self.bf(self.bf(x) @ w)
+
+    def rms(self, x, w):
+        inv = torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6)
+        return x * inv * (w + 1.0)
+
+    def rope(self, x, pos):                           # x [rows, n, hd], pos float32 [rows]
+        ang = pos[:, None] * self.inv_freq[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        half = self.hd // 2
+        x1, x2 = x[..., :half], x[..., half:]
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
+
+    @staticmethod
+    def gelu(x):
+        return 0.5 * x * (1.0 + torch.tanh(np.float32(np.sqrt(2.0 / np.pi)) * (x + np.float32(0.044715) * x * x * x)))
+
+    def forward(self, tokens: np.ndarray, start: int) -> torch.Tensor:
+        """Runs positions start .. start + len(tokens) - 1 (causal among themselves, attending to the caches before
+        them), writes their keys and values into the caches and returns the fp32 logits of the last position."""
+        with torch.no_grad():
+            T, H, hd = len(tokens), self.heads, self.hd
+            pos = torch.arange(start, start + T, dtype=torch.float32)
+            x = self.w["embed"][torch.from_numpy(np.asarray(tokens, np.int64))] * np.float32(np.sqrt(self.dim))
+            end = start + T
+            visible = torch.arange(end)[None, :] <= torch.arange(start, end)[:, None]        # [T, end]
+            for i in range(self.layers):
+                p = f"layer{i}."
+                h = self.rms(x, self.w[p + "attn_norm"])
+                q = self.rope(self.lin(h, self.w[p + "wq"]).reshape(T, H, hd), pos)
+                k = self.rope(self.lin(h, self.w[p + "wk"]).reshape(T, 1, hd), pos).reshape(T, hd)
+                v = self.lin(h, self.w[p + "wv"])
+                self.k[i][start:end] = self.bf(k)
+                self.v[i][start:end] = self.bf(v)
+                kc, vc = self.k[i][:end], self.v[i][:end]
+                sc = self.bf(torch.einsum("thd,sd->hts", self.bf(q), kc)) * np.float32(1.0 / np.sqrt(hd))
+                sc = torch.where(visible[None], sc, torch.tensor(-1e30))
+                pr = torch.softmax(sc, -1)
+                att = self.bf(torch.einsum("hts,sd->thd", self.bf(pr), vc)).reshape(T, H * hd)
+                x = x + self.lin(att, self.w[p + "wo"])
+                h2 = self.rms(x, self.w[p + "mlp_norm"])
+                ff = self.gelu(self.lin(h2, self.w[p + "w_gate"])) * self.lin(h2, self.w[p + "w_up"])
+                x = x + self.lin(ff, self.w[p + "w_down"])
+            hf = self.bf(self.rms(x[-1:], self.w["final_norm"]))
+            return self.bf(hf @ self.w["embed"].T)[0]
+
+
+def distilbert_loss_and_grads(weights: dict, ids: np.ndarray, mask: np.ndarray, heads: int, dtype=torch.float32):
+    """PyTorch autograd twin of b200.shlo.programs.distilbert_mlm_step (examples/distilbert/model.py:11-94 of the
+    reference: post-LayerNorm encoder, tanh GELU, tied-projector masked-LM head, labels = ids, loss averaged over the
+    masked positions) in `dtype` arithmetic without intermediate rounding: the reference value a bfloat16 execution is
+    held against. Returns the loss and one gradient per weight, in the order of `weights`."""
+    W = {k: torch.tensor(np.asarray(v), dtype=dtype, requires_grad=True) for k, v in weights.items()}
+    B, S = ids.shape
+    N, dim = B * S, W["word_emb"].shape[1]
+    hd = dim // heads
+    layers = sum(1 for k in W if k.endswith(".q.w"))
+    idt = torch.from_numpy(ids.reshape(-1).astype(np.int64))
+
+    def ln(x, s, b):
+        mu = x.mean(-1, keepdim=True)
+        xc = x - mu
+        return xc * torch.rsqrt((xc * xc).mean(-1, keepdim=True) + 1e-12) * s + b
+
+    def gelu(x):
+        return 0.5 * x * (1.0 + torch.tanh(np.sqrt(2.0 / np.pi) * (x + 0.044715 * x * x * x)))
+
+    x = W["word_emb"][idt] + W["pos_emb"][:S].repeat(B, 1)
+    x = ln(x, W["emb_ln.scale"], W["emb_ln.bias"])
+    for i in range(layers):
+        p = f"layer{i}."
+        def split(t): return t.reshape(B, S, heads, hd).permute(0, 2, 1, 3)
+        q, k, v = (split(x @ W[p + n + ".w"] + W[p + n + ".b"]) for n in ("q", "k", "v"))
+        pr = torch.softmax(q @ k.transpose(-1, -2) / np.sqrt(hd), -1)
+        ctx = (pr @ v).permute(0, 2, 1, 3).reshape(N, dim)
+        x = ln(x + ctx @ W[p + "o.w"] + W[p + "o.b"], W[p + "attn_ln.scale"], W[p + "attn_ln.bias"])
+        ff = gelu(x @ W[p + "ff1.w"] + W[p + "ff1.b"]) @ W[p + "ff2.w"] + W[p + "ff2.b"]
+        x = ln(x + ff, W[p + "out_ln.scale"], W[p + "out_ln.bias"])
+    h = ln(gelu(x @ W["head.w"] + W["head.b"]), W["head_ln.scale"], W["head_ln.bias"])
+    logits = h @ W["word_emb"].T + W["vocab_bias"]
+    nll = F.cross_entropy(logits, idt, reduction="none")
+    wv = torch.tensor(np.asarray(mask).reshape(-1), dtype=dtype)
+    loss = (nll * wv).sum() / torch.clamp(wv.sum(), min=1.0)
+    grads = torch.autograd.grad(loss, [W[k] for k in weights])
+    return float(loss.detach()), [g.numpy() for g in grads]
