@@ -443,6 +443,23 @@ struct Inliner {
         }
       }
     }
+    // Common subexpressions: an operation without regions or side effects that repeats an earlier one of the same
+    // block (same name, operands, attributes and result types) is dropped and its results renamed. Generators and
+    // jax alike emit the same convert or broadcast once per use (the bf16 copy of a normalised activation feeding
+    // three projections); without this every copy becomes its own kernel launch.
+    if (op->regions.empty() && deferred.empty() && cse_candidate(op.get())) {
+      std::string key = op->name;
+      for (auto* o : op->operands) { char buf[32]; snprintf(buf, sizeof buf, "|%p", (void*)o); key += buf; }
+      for (auto& kv : op->attrs) key += "|" + kv.first + "=" + kv.second;
+      for (auto* r : op->results) key += "|" + r->type.str();
+      auto& table = seen_ops[b];
+      auto it = table.find(key);
+      if (it != table.end()) {
+        for (size_t k = 0; k < op->results.size(); k++) remap[op->results[k]] = it->second->results[k];
+        return;
+      }
+      table[key] = op.get();
+    }
     enclosing.push_back({b, op.get()});
     for (auto& reg : op->regions) run(reg.get());
     enclosing.pop_back();
@@ -451,6 +468,17 @@ struct Inliner {
     for (auto& d : deferred) { d->parent = b; b->ops.push_back(std::move(d)); }
     deferred.clear();
   }
+  static bool cse_candidate(Op* op) {
+    if (getenv("B200_NO_CSE")) return false;
+    const std::string sh = op->short_name();
+    if (op->name.rfind("stablehlo.", 0) != 0 && op->name.rfind("chlo.", 0) != 0) return false;
+    if (is_elementwise_op(sh)) return true;
+    static const char* pure[] = {"broadcast_in_dim", "reshape", "transpose", "reverse", "slice", "pad", "concatenate", "dynamic_slice",
+                                 "iota", "gather", "dot_general", "convolution", "convert", "bitcast_convert", "dynamic_update_slice"};
+    for (const char* p2 : pure) if (sh == p2) return true;
+    return false;
+  }
+  std::map<Block*, std::map<std::string, Op*>> seen_ops;         // per block: key of an operation -> its first occurrence
   std::vector<std::pair<Block*, Op*>> enclosing;               // (block, op) pairs around the region being processed
   std::map<std::pair<Value*, int>, Value*> hoisted;            // widened copies already placed in front of a loop
   std::map<std::tuple<Value*, int, int64_t>, Value*> padded;   // zero-padded copies made for convolutions
@@ -463,6 +491,158 @@ void fix_region_operands(Block* b, Inliner& inl) {
     for (auto& r : op->regions) fix_region_operands(r.get(), inl);
   }
 }
+
+// ---------------------------------------------------------------------------
+// pass 1b: weights of skinny products inside loops
+// ---------------------------------------------------------------------------
+// A decode loop multiplies one or a few rows by weight matrices that come from outside the loop, once per iteration:
+// the rate is the rate at which the weights stream from HBM. A 16-bit weight stored [k][n] (n contiguous) needs a K
+// split across CTAs to give the GPU enough independent loads, and the split costs a reduction pass; stored [n][k]
+// every output column is one contiguous row that a warp streams with 128-bit loads and finishes with a shuffle tree.
+// So for every such product the transposed weight is made once in front of the loop, and products that share their
+// left operand (the query / key / value projections, the gate and up projections) read one concatenated weight and
+// become one product whose result is sliced. What it costs: one pass over the weights per execution and a second
+// copy of them in HBM.
+struct SkinnyWeightHoist {
+  Module& m;
+  explicit SkinnyWeightHoist(Module& mod) : m(mod) {}
+
+  static std::string i64_array(const std::vector<int64_t>& v) {
+    std::string s = "array<i64: ";
+    for (size_t k = 0; k < v.size(); k++) s += (k ? ", " : "") + std::to_string(v[k]);
+    return s + ">";
+  }
+  Value* make(std::unique_ptr<Op>& op, const TensorType& t, Block* parent) {
+    Value* v = m.new_value(t, "");
+    v->def = op.get();
+    v->def_index = 0;
+    op->results.push_back(v);
+    op->parent = parent;
+    return v;
+  }
+  static bool defined_in(Value* v, Block* b) {
+    if (v->def) {
+      for (Block* p = v->def->parent; p; p = p->parent_op ? p->parent_op->parent : nullptr)
+        if (p == b) return true;
+      return false;
+    }
+    for (Block* p = v->owner; p; p = p->parent_op ? p->parent_op->parent : nullptr)
+      if (p == b) return true;
+    return false;
+  }
+
+  void run(Block* b) {
+    for (size_t i = 0; i < b->ops.size(); i++) {
+      Op* op = b->ops[i].get();
+      for (auto& r : op->regions) run(r.get());
+      if (op->short_name() != "while" || op->regions.size() != 2 || getenv("B200_NO_WEIGHT_HOIST")) continue;
+      std::vector<std::unique_ptr<Op>> front;          // operations to place in front of the loop
+      rewrite(op->regions[1].get(), b, front);
+      const size_t n = front.size();
+      for (size_t k = 0; k < n; k++) b->ops.insert(b->ops.begin() + i + k, std::move(front[k]));
+      i += n;
+    }
+  }
+
+  void rewrite(Block* body, Block* outer, std::vector<std::unique_ptr<Op>>& front) {
+    struct Cand { Op* op; Value* lhs; Value* rhs; int64_t K, N; };
+    std::map<Value*, std::vector<Cand>> by_lhs;
+    std::vector<Value*> order;
+    for (auto& up : body->ops) {
+      Op* op = up.get();
+      if (op->short_name() != "dot_general" || op->operands.size() != 2 || !op->has("dot_dimension_numbers")) continue;
+      Value *lhs = op->operands[0], *rhs = op->operands[1];
+      const DT dt = lhs->type.dt;
+      if (dt != rhs->type.dt || !(dt == DT::BF16 || dt == DT::F16) || rhs->type.rank() != 2 || lhs->type.rank() < 1) continue;
+      if (defined_in(rhs, body)) continue;             // not loop-invariant
+      auto f = attr_struct(op->attr("dot_dimension_numbers"));
+      if (!f["lhs_batching_dimensions"].empty() || !f["rhs_batching_dimensions"].empty()) continue;
+      auto lcd = f["lhs_contracting_dimensions"], rcd = f["rhs_contracting_dimensions"];
+      if (lcd.size() != 1 || rcd.size() != 1 || lcd[0] != lhs->type.rank() - 1 || rcd[0] != 0) continue;
+      const int64_t K = rhs->type.dims[0], N = rhs->type.dims[1];
+      const int64_t M = lhs->type.numel() / std::max<int64_t>(K, 1);
+      if (M > 8 || K % 8 || K * N < (1 << 16) || M * K * 2 > 96 * 1024) continue;
+      if (!by_lhs.count(lhs)) order.push_back(lhs);
+      by_lhs[lhs].push_back({op, lhs, rhs, K, N});
+    }
+    for (Value* lhs : order) {
+      auto& group = by_lhs[lhs];
+      // transposed (and concatenated) weight in front of the loop
+      std::vector<Value*> parts;
+      int64_t total = 0;
+      const int64_t K = group[0].K;
+      for (auto& c : group) {
+        auto key = std::make_pair(c.rhs, outer);
+        Value* t;
+        auto tr = std::make_unique<Op>();
+        tr->name = "stablehlo.transpose";
+        tr->operands = {c.rhs};
+        tr->attrs["permutation"] = i64_array({1, 0});
+        TensorType tt = c.rhs->type;
+        tt.dims = {c.N, c.K};
+        t = make(tr, tt, outer);
+        front.push_back(std::move(tr));
+        (void)key;
+        parts.push_back(t);
+        total += c.N;
+      }
+      Value* weight = parts[0];
+      if (parts.size() > 1) {
+        auto cat = std::make_unique<Op>();
+        cat->name = "stablehlo.concatenate";
+        cat->operands = parts;
+        cat->attrs["dimension"] = "0 : i64";
+        TensorType ct = parts[0]->type;
+        ct.dims = {total, K};
+        weight = make(cat, ct, outer);
+        front.push_back(std::move(cat));
+      }
+      Op* first = group[0].op;
+      const int lrank = lhs->type.rank();
+      if (group.size() == 1) {
+        // a product on its own keeps its place and result and reads the transposed weight
+        first->operands[1] = weight;
+        first->attrs["dot_dimension_numbers"] = "#stablehlo.dot<lhs_batching_dimensions = [], rhs_batching_dimensions = [], "
+                                                "lhs_contracting_dimensions = [" + std::to_string(lrank - 1) +
+                                                "], rhs_contracting_dimensions = [1]>";
+        continue;
+      }
+      // one product against the whole weight, in the place of the group's first product; the others become slices
+      std::vector<int64_t> out_dims(lhs->type.dims.begin(), lhs->type.dims.end() - 1);
+      out_dims.push_back(total);
+      auto dot = std::make_unique<Op>();
+      dot->name = "stablehlo.dot_general";
+      dot->operands = {lhs, weight};
+      dot->attrs = first->attrs;
+      dot->attrs["dot_dimension_numbers"] = "#stablehlo.dot<lhs_batching_dimensions = [], rhs_batching_dimensions = [], "
+                                            "lhs_contracting_dimensions = [" + std::to_string(lrank - 1) +
+                                            "], rhs_contracting_dimensions = [1]>";
+      TensorType dt2 = first->results[0]->type;
+      dt2.dims = out_dims;
+      Value* whole = make(dot, dt2, body);
+      // position of the first product in the body
+      size_t at = 0;
+      while (at < body->ops.size() && body->ops[at].get() != first) at++;
+      int64_t off = 0;
+      std::vector<std::unique_ptr<Op>> slices;
+      for (auto& c : group) {
+        // the old product turns into a slice of the new one (same result value, so users need no change)
+        Op* old = c.op;
+        std::vector<int64_t> st(lrank, 0), lim = out_dims, one(lrank, 1);
+        st[lrank - 1] = off;
+        lim[lrank - 1] = off + c.N;
+        old->name = "stablehlo.slice";
+        old->operands = {whole};
+        old->attrs.clear();
+        old->attrs["start_indices"] = i64_array(st);
+        old->attrs["limit_indices"] = i64_array(lim);
+        old->attrs["strides"] = i64_array(one);
+        off += c.N;
+      }
+      body->ops.insert(body->ops.begin() + at, std::move(dot));
+    }
+  }
+};
 
 // ---------------------------------------------------------------------------
 // op classification
@@ -725,7 +905,16 @@ struct Planner {
       if (ext.empty() && !returned && gs.size() > 1 && cheap_to_duplicate(op)) {
         bool small = true;
         for (auto* g : gs) small &= g->members.size() < 48;
+        // a chain of duplicated operations (the residual stream of a deep network: x4 = x3 + o3 = x2 + o2 + o3 ...)
+        // would be re-evaluated from ever more inputs by every later kernel: after four links the value is written
+        int depth = 1;
+        for (auto* u : st.users[v]) {
+          auto du = dup_depth.find(u);
+          if (du != dup_depth.end()) depth = std::max(depth, du->second + 1);
+        }
+        if (depth > 8) small = false;
         if (small) {
+          dup_depth[op] = depth;
           for (auto* g : gs) join(g, false);
           continue;
         }
@@ -1779,6 +1968,80 @@ struct Planner {
     return s + "}";
   }
 
+  // A large transpose that moves the innermost dimension, standing alone (or several of them concatenated along
+  // dimension 0, what the weights of a decode loop become): moved by the tiled kernel that stages 32 x 32 (64 x 64)
+  // tiles through shared memory, so that reads and writes are both whole lines. The index-rewriting form inside a
+  // fused kernel reads or writes with a stride. Input dims A ++ X ++ Y, output dims A ++ Y ++ X.
+  bool lower_tiled_transpose(Group* g, Plan& plan, BlockState& st) {
+    if (g->roots.size() != 1 || getenv("B200_NO_TILED_TRANSPOSE")) return false;
+    Op* root = g->roots[0];
+    Value* out = root->results[0];
+    const size_t es = dt_size(out->type.dt);
+    if ((es != 2 && es != 4) || out->type.numel() < (1 << 16)) return false;
+    struct Part { Value* src; long long B, R, C, dst_off; };
+    std::vector<Part> parts;
+    auto canonical = [&](Op* t, Part& p) -> bool {
+      if (t->short_name() != "transpose") return false;
+      Value* src = t->operands[0];
+      if (!slot_of.count(src) || (src->def && is_dup(src->def) && !st.dup_materialize.count(src->def))) return false;
+      auto perm = attr_i64s(t->attr("permutation"));
+      const int n = (int)perm.size();
+      for (int a = 0; a < n - 1; a++) {
+        bool ok = true;
+        for (int i = 0; i < a && ok; i++) ok = perm[i] == i;
+        if (!ok) break;
+        for (int x = 1; a + x < n; x++) {
+          const int y = n - a - x;
+          bool match = true;
+          for (int i = 0; i < y && match; i++) match = perm[a + i] == a + x + i;
+          for (int i = 0; i < x && match; i++) match = perm[a + y + i] == a + i;
+          if (!match) continue;
+          p.src = src;
+          p.B = p.R = p.C = 1;
+          for (int i = 0; i < a; i++) p.B *= src->type.dims[i];
+          for (int i = a; i < a + x; i++) p.R *= src->type.dims[i];
+          for (int i = a + x; i < n; i++) p.C *= src->type.dims[i];
+          return p.B <= 65535 && p.R > 1 && p.C > 1 && (es == 4 || (p.R % 2 == 0 && p.C % 2 == 0)) && (p.R + 31) / 32 <= 65535;
+        }
+      }
+      return false;
+    };
+    long long dst_ld = 0, dst_bs = 0;
+    if (g->members.size() == 1) {
+      Part p;
+      if (!canonical(root, p)) return false;
+      p.dst_off = 0;
+      dst_ld = p.R;
+      dst_bs = p.R * p.C;
+      parts.push_back(p);
+    } else {
+      // concatenate along dimension 0 of rank-2 transposes
+      if (root->short_name() != "concatenate" || attr_int(root->attr("dimension")) != 0 || out->type.rank() != 2) return false;
+      if (g->members.size() != root->operands.size() + 1) return false;
+      long long off = 0;
+      for (Value* o : root->operands) {
+        Part p;
+        if (!o->def || !g->members.count(o->def) || o->type.rank() != 2 || !canonical(o->def, p) || p.B != 1) return false;
+        p.dst_off = off * out->type.dims[1];
+        off += o->type.dims[0];
+        parts.push_back(p);
+      }
+      dst_ld = out->type.dims[1];
+      dst_bs = 0;
+      for (auto& p : parts) if (p.R != dst_ld) return false;
+    }
+    ensure_slot(out, st);
+    for (auto& p : parts) {
+      Step s;
+      s.kind = Step::TRANSPOSE;
+      s.label = "tiled transpose";
+      s.args = {slot_of.at(out), slot_of.at(p.src)};
+      s.iparams = {(long long)es, p.B, p.R, p.C, dst_ld, dst_bs, p.dst_off};
+      plan.steps.push_back(std::move(s));
+    }
+    return true;
+  }
+
   void emit_group(Group* g, Plan& plan, BlockState& st) {
     if (!g->is_reduce) {
       // a lone reshape of a value that already lives in memory is a view
@@ -1793,6 +2056,7 @@ struct Planner {
         for (auto* r : g->roots) ensure_slot(r->results[0], st);
         return;
       }
+      if (lower_tiled_transpose(g, plan, st)) return;
       if (g->roots.size() == 1 && window_updates.count(g->roots[0])) {
         Op* d = g->roots[0];
         slot_of[d->results[0]] = slot_of.at(d->operands[0]);
@@ -1836,7 +2100,8 @@ struct Planner {
     if (Nk == 0) { for (auto* o : outs) ensure_slot(o, st); return; }
     bool col = trailing >= 16;
     // parallelism: split the reduced range over blockIdx.y when there are few outputs
-    int64_t blocks = col ? (Nk + 31) / 32 : (Nk + (Nr >= 1024 ? 0 : 7)) / (Nr >= 1024 ? 1 : 8);
+    // (the row strategy gives an output a whole block from 128 reduced elements on, a warp below)
+    int64_t blocks = col ? (Nk + 31) / 32 : (Nr >= 128 ? Nk : (Nk + 7) / 8);
     // enough blocks to fill 148 SMs with 2048 threads each (1184 blocks of 256 threads), each split keeping
     // at least a few unrolled iterations per thread
     int64_t per_split_min = col ? 64 : (Nr >= 1024 ? 2048 : 256);
@@ -1846,6 +2111,8 @@ struct Planner {
       splits = (int)std::min<int64_t>((target_blocks + blocks - 1) / blocks, (Nr + per_split_min - 1) / per_split_min);
       splits = std::max(1, std::min(splits, 1024));
     }
+    // a few thousand elements in all: a second launch costs more than the parallelism of a split returns
+    if (Nk * Nr <= 32768) splits = 1;
     auto internal = [this, g, &st](Op* o) {
       return (g->members.count(o) && categorize(o) != Cat::REDUCE) || (is_dup(o) && !st.dup_materialize.count(o) && !slot_of.count(o->results[0]));
     };
@@ -2253,8 +2520,9 @@ struct Planner {
               }
               return c;
             };
-            // the old tensor has no other reader and the new one goes nowhere but back into the loop state
-            if (uses(body, body->args[k]) != 1 || uses(body, r) != 1) continue;
+            // the old tensor has no other reader; the new one shares the state's memory, so whoever else reads it
+            // (the attention product reading an updated key cache) finds it there
+            if (uses(body, body->args[k]) != 1) continue;
             if (r->type.dims.empty() || r->type.numel() == 0 || getenv("B200_NO_WINDOW_UPDATE")) continue;
             window_updates.insert(d);
           }
@@ -2685,6 +2953,7 @@ struct Planner {
   }
 
   std::set<int> persistent;
+  std::map<Op*, int> dup_depth;       // cheap operations evaluated in several kernels: links of duplicated users above them
   std::set<Op*> window_updates;       // dynamic_update_slice ops of loop bodies that update their loop state in place
   std::set<int> whole_plan;           // slots that own their memory for their whole plan (exchanged loop state)
   std::set<Group*> absorbed, emitted;     // pointwise groups folded into a reduction's second pass / groups already planned
@@ -2707,6 +2976,10 @@ void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& o
         os << (s.g16.path == 0 ? "gemm16" : s.g16.path == 1 ? "gemv16_nc" : "gemv16_kc") << " M=" << s.g16.M << " N=" << s.g16.N
            << " K=" << s.g16.K << " G=" << s.g16.G << " a_kcontig=" << (s.g16.a_ks == 1) << " b_kcontig=" << (s.g16.b_ks == 1)
            << " bn=" << s.g16.bn << " splitK=" << s.g16.split_k << " out=" << (s.g16.c_kind == 2 ? "f32" : "16") << " " << s.label;
+        break;
+      case Step::TRANSPOSE:
+        os << "transpose batch=" << s.iparams[1] << " rows=" << s.iparams[2] << " cols=" << s.iparams[3] << " bytes=" << s.iparams[0]
+           << " dst_off=" << s.iparams[6];
         break;
       case Step::REPACK16: os << "repack16 rows=" << s.iparams[0] << " cols=" << s.iparams[1] << " ld " << s.iparams[3] << "->" << s.iparams[2]; break;
       case Step::WHILE:
@@ -2744,6 +3017,7 @@ std::unique_ptr<CompiledProgram> compile_module(Module& m, const CompileOptions&
   Inliner inl(m);
   inl.run(f->body.get());
   fix_region_operands(f->body.get(), inl);
+  SkinnyWeightHoist(m).run(f->body.get());
   // unsupported-op check names every offender at once (src/pjrt_plugin/stablehlo_parser.cc:167-184)
   std::set<std::string> bad;
   collect_unsupported(f->body.get(), bad, false);
@@ -2826,6 +3100,7 @@ std::unique_ptr<CompiledProgram> compile_module(Module& m, const CompileOptions&
         else if (s.kind == Step::IGEMM) n += s.ig.split_k > 1 ? 2 : 1;
         else if (s.kind == Step::GEMM16) n += (s.g16.path == 0 && s.g16.split_k > 1) ? 2 : 1;
         else if (s.kind == Step::REPACK16) n += (s.iparams[0] + 65534) / 65535;
+        else if (s.kind == Step::TRANSPOSE) n += 1;
         else if (s.kind == Step::WHILE) {
           if (s.trip_count < 0) { dynamic = true; continue; }
           n += s.trip_count * count(*s.sub[1]);      // a counted loop never evaluates its condition

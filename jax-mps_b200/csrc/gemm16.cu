@@ -330,6 +330,46 @@ __global__ void __launch_bounds__(256) repack_rows16_kernel(uint16_t* __restrict
     dst[r * dst_ld + c] = src[r * src_ld + c];
 }
 
+// Batched two-dimensional transpose dst[b][c][r] = src[b][r][c] staged through shared memory, so that both the reads
+// (along c) and the writes (along r) are whole 128-byte lines. 4-byte elements: 32 x 32 tiles; 2-byte elements:
+// 64 x 64 tiles moved as pairs (R and C even). Block (32, 8), grid (tiles along c, tiles along r, b).
+__global__ void __launch_bounds__(256) transpose32_kernel(uint32_t* __restrict__ dst, const uint32_t* __restrict__ src, int R, int C,
+                                                         long long dst_ld, long long src_bs, long long dst_bs) {
+  __shared__ uint32_t tile[32][33];
+  const long long sb = (long long)blockIdx.z * src_bs, db = (long long)blockIdx.z * dst_bs;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+#pragma unroll
+  for (int j = threadIdx.y; j < 32; j += 8)
+    if (r0 + j < R && c0 + threadIdx.x < C) tile[j][threadIdx.x] = src[sb + (long long)(r0 + j) * C + c0 + threadIdx.x];
+  __syncthreads();
+#pragma unroll
+  for (int j = threadIdx.y; j < 32; j += 8)
+    if (c0 + j < C && r0 + threadIdx.x < R) dst[db + (long long)(c0 + j) * dst_ld + r0 + threadIdx.x] = tile[threadIdx.x][j];
+}
+
+__global__ void __launch_bounds__(256) transpose16_kernel(uint16_t* __restrict__ dst, const uint16_t* __restrict__ src, int R, int C,
+                                                         long long dst_ld, long long src_bs, long long dst_bs) {
+  __shared__ uint32_t tile[64][33];                   // 64 rows of 64 16-bit values (32 words) + 1 word of padding
+  const long long sb = (long long)blockIdx.z * src_bs, db = (long long)blockIdx.z * dst_bs;
+  const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+#pragma unroll
+  for (int j = threadIdx.y; j < 64; j += 8) {
+    const int r = r0 + j, c = c0 + 2 * threadIdx.x;
+    if (r < R && c < C) tile[j][threadIdx.x] = *reinterpret_cast<const uint32_t*>(src + sb + (long long)r * C + c);
+  }
+  __syncthreads();
+  // output row c (64 of them), pairs of r: words of two source rows, the same half of each
+#pragma unroll
+  for (int j = threadIdx.y; j < 64; j += 8) {
+    const int c = c0 + j, r = r0 + 2 * threadIdx.x;
+    if (c < C && r < R) {
+      const uint32_t w0 = tile[2 * threadIdx.x][j >> 1], w1 = tile[2 * threadIdx.x + 1][j >> 1];
+      const uint32_t lo = (j & 1) ? (w0 >> 16) : (w0 & 0xFFFFu), hi = (j & 1) ? (w1 >> 16) : (w1 & 0xFFFFu);
+      *reinterpret_cast<uint32_t*>(dst + db + (long long)c * dst_ld + r) = lo | (hi << 16);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // Skinny products (M <= 8).
 struct GemvParams {
@@ -448,18 +488,40 @@ __global__ void __launch_bounds__(256) gemv16_nc_kernel(const uint16_t* __restri
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  if (nn < p.N) {
-    for (int m = 0; m < p.M; ++m) {
-      float s = 0.f;
-      for (int q = 0; q < p.splits; ++q) s += __ldcg(scratch + (((long long)g * p.splits + q) * p.M + m) * p.N + nn);
-      store_c(C, ((long long)g * p.M + m) * p.N + nn, s, p.c_kind);
+  // warp w adds the splits w, w + 8, ... for the eight columns of each of its lanes (independent loads, several in
+  // flight), then the eight warps' sums are added in warp order: a fixed order whichever CTA came last
+  const bool vec4 = (p.N & 3) == 0;
+  for (int m = 0; m < p.M; ++m) {
+    float t[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = 0.f;
+#pragma unroll 4
+    for (int q = warp; q < p.splits; q += 8) {
+      const float* src = scratch + (((long long)g * p.splits + q) * p.M + m) * p.N + n;
+      if (vec4 && n + 8 <= p.N) {
+        const float4 v0 = __ldcg(reinterpret_cast<const float4*>(src)), v1 = __ldcg(reinterpret_cast<const float4*>(src) + 1);
+        t[0] += v0.x; t[1] += v0.y; t[2] += v0.z; t[3] += v0.w;
+        t[4] += v1.x; t[5] += v1.y; t[6] += v1.z; t[7] += v1.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (n + j < p.N) t[j] += __ldcg(src + j);
+      }
     }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[warp * 256 + lane * 8 + j] = t[j];
+    __syncthreads();
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += red[w * 256 + tid];
+    if (nn < p.N) store_c(C, ((long long)g * p.M + m) * p.N + nn, s, p.c_kind);
   }
 }
 
-// k contiguous in B (a tied-embedding logits product, scores against a key cache). Grid (CTAs, groups), 256 threads;
-// a warp takes NW output columns at a time, its lanes stride over k with 128-bit loads (K a multiple of 8), A sits in
-// shared memory as 16-bit values, per-lane sums meet in a warp-shuffle tree.
+// k contiguous in B (a tied-embedding logits product, scores against a key cache, a weight transposed in front of a
+// decode loop). Grid (CTAs, groups), 256 threads; a warp takes NW output columns at a time, its lanes stride over k with
+// 128-bit loads (K a multiple of 8), A sits in shared memory as 16-bit values, per-lane sums meet in a warp-shuffle tree.
 template <int MAXM, bool BF16, int NW>
 __global__ void __launch_bounds__(256) gemv16_kc_kernel(const uint16_t* __restrict__ A, const uint16_t* __restrict__ B,
                                                        void* __restrict__ C, GemvParams p) {
@@ -474,6 +536,8 @@ __global__ void __launch_bounds__(256) gemv16_kc_kernel(const uint16_t* __restri
     a_s[i] = Ag[m * p.a_ms + (long long)k * p.a_ks];
   }
   __syncthreads();
+  // UNR chunks of 8 k per column are loaded before any is used: NW * UNR independent 16-byte loads in flight per lane
+  constexpr int UNR = NW == 1 ? 8 : 2;
   const int tasks = (p.N + NW - 1) / NW;
   for (int task = blockIdx.x * 8 + warp; task < tasks; task += gridDim.x * 8) {
     const int n0 = task * NW;
@@ -482,25 +546,35 @@ __global__ void __launch_bounds__(256) gemv16_kc_kernel(const uint16_t* __restri
     for (int q = 0; q < NW; ++q)
 #pragma unroll
       for (int m = 0; m < MAXM; ++m) acc[q][m] = 0.f;
-    for (int k = lane * 8; k < p.K; k += 256) {
-      uint4 b[NW];
+    for (int k0 = lane * 8; k0 < p.K; k0 += 256 * UNR) {
+      uint4 b[UNR][NW];
 #pragma unroll
-      for (int q = 0; q < NW; ++q)
-        b[q] = n0 + q < p.N ? __ldcs(reinterpret_cast<const uint4*>(Bg + (long long)(n0 + q) * p.b_ld + k)) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int m = 0; m < MAXM; ++m) {
-        if (m >= p.M) break;
-        const uint4 a = *reinterpret_cast<const uint4*>(a_s + m * p.K + k);
-        const float a0 = lo16<BF16>(a.x), a1 = hi16<BF16>(a.x), a2 = lo16<BF16>(a.y), a3 = hi16<BF16>(a.y);
-        const float a4 = lo16<BF16>(a.z), a5 = hi16<BF16>(a.z), a6 = lo16<BF16>(a.w), a7 = hi16<BF16>(a.w);
+      for (int u = 0; u < UNR; ++u)
 #pragma unroll
         for (int q = 0; q < NW; ++q) {
-          float s = acc[q][m];
-          s = fmaf(a0, lo16<BF16>(b[q].x), s); s = fmaf(a1, hi16<BF16>(b[q].x), s);
-          s = fmaf(a2, lo16<BF16>(b[q].y), s); s = fmaf(a3, hi16<BF16>(b[q].y), s);
-          s = fmaf(a4, lo16<BF16>(b[q].z), s); s = fmaf(a5, hi16<BF16>(b[q].z), s);
-          s = fmaf(a6, lo16<BF16>(b[q].w), s); s = fmaf(a7, hi16<BF16>(b[q].w), s);
-          acc[q][m] = s;
+          const int k = k0 + 256 * u;
+          b[u][q] = (n0 + q < p.N && k < p.K) ? __ldcs(reinterpret_cast<const uint4*>(Bg + (long long)(n0 + q) * p.b_ld + k))
+                                              : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int k = k0 + 256 * u;
+        if (k >= p.K) break;
+#pragma unroll
+        for (int m = 0; m < MAXM; ++m) {
+          if (m >= p.M) break;
+          const uint4 a = *reinterpret_cast<const uint4*>(a_s + m * p.K + k);
+          const float a0 = lo16<BF16>(a.x), a1 = hi16<BF16>(a.x), a2 = lo16<BF16>(a.y), a3 = hi16<BF16>(a.y);
+          const float a4 = lo16<BF16>(a.z), a5 = hi16<BF16>(a.z), a6 = lo16<BF16>(a.w), a7 = hi16<BF16>(a.w);
+#pragma unroll
+          for (int q = 0; q < NW; ++q) {
+            float s = acc[q][m];
+            s = fmaf(a0, lo16<BF16>(b[u][q].x), s); s = fmaf(a1, hi16<BF16>(b[u][q].x), s);
+            s = fmaf(a2, lo16<BF16>(b[u][q].y), s); s = fmaf(a3, hi16<BF16>(b[u][q].y), s);
+            s = fmaf(a4, lo16<BF16>(b[u][q].z), s); s = fmaf(a5, hi16<BF16>(b[u][q].z), s);
+            s = fmaf(a6, lo16<BF16>(b[u][q].w), s); s = fmaf(a7, hi16<BF16>(b[u][q].w), s);
+            acc[q][m] = s;
+          }
         }
       }
     }
@@ -575,7 +649,8 @@ bool gemm16_plan(Gemm16Launch& g, bool aligned) {
       // every element of B once: column panels of 256 times K splits should give each SM several CTAs
       g.path = 1;
       const int panels = (g.N + 255) / 256;
-      long long want = (SMS * 6 + (long long)panels * g.G - 1) / ((long long)panels * g.G);
+      // one wave of CTAs (four of these CTAs fit an SM), each with at least 64 rows of K
+      long long want = ((long long)SMS * 4) / ((long long)panels * g.G);
       want = std::max<long long>(1, std::min<long long>(want, (g.K + 63) / 64));
       int kc = (int)((g.K + want - 1) / want);
       kc = (kc + 7) / 8 * 8;
@@ -626,6 +701,29 @@ bool gemm16_plan(Gemm16Launch& g, bool aligned) {
     }
   }
   return true;
+}
+
+cudaError_t launch_transpose2d(void* dst, const void* src, int elem_bytes, long long batch, long long rows, long long cols,
+                               long long dst_ld, long long dst_batch_stride, cudaStream_t stream, int* launches) {
+  if (batch <= 0 || rows <= 0 || cols <= 0) return cudaSuccess;
+  if (batch > 65535 || rows >= (1LL << 31) || cols >= (1LL << 31)) return cudaErrorInvalidValue;
+  dim3 block(32, 8);
+  if (elem_bytes == 4) {
+    dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32), (unsigned)batch);
+    if (grid.y > 65535) return cudaErrorInvalidValue;
+    transpose32_kernel<<<grid, block, 0, stream>>>((uint32_t*)dst, (const uint32_t*)src, (int)rows, (int)cols, dst_ld, rows * cols,
+                                                   dst_batch_stride);
+  } else if (elem_bytes == 2 && rows % 2 == 0 && cols % 2 == 0 && dst_ld % 2 == 0 && dst_batch_stride % 2 == 0 &&
+             (((uintptr_t)dst | (uintptr_t)src) & 3) == 0) {
+    dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64), (unsigned)batch);
+    if (grid.y > 65535) return cudaErrorInvalidValue;
+    transpose16_kernel<<<grid, block, 0, stream>>>((uint16_t*)dst, (const uint16_t*)src, (int)rows, (int)cols, dst_ld, rows * cols,
+                                                   dst_batch_stride);
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  if (launches) (*launches)++;
+  return cudaGetLastError();
 }
 
 cudaError_t launch_repack_rows16(void* dst, const void* src, long long rows, long long cols, long long dst_ld, long long src_ld,

@@ -63,6 +63,13 @@ namespace b200 {
 cudaError_t launch_gemm16(const Gemm16Launch& g, const void* A, const void* B, void* C, float* scratch, int* counters,
                           int* error_flag, cudaStream_t stream, int* launches, const char** why);
 
+// dst[b][c][r] = src[b][r][c]: dense source [batch][rows][cols], destination rows `dst_ld` elements apart and batches
+// `dst_batch_stride` elements apart (so that several transposes can fill one concatenated tensor), through shared
+// memory. Element size 4, or 2 with even extents and 4-byte aligned pointers; anything else returns
+// cudaErrorInvalidValue without launching (the caller checks the same conditions when it plans the step).
+cudaError_t launch_transpose2d(void* dst, const void* src, int elem_bytes, long long batch, long long rows, long long cols,
+                               long long dst_ld, long long dst_batch_stride, cudaStream_t stream, int* launches);
+
 // dst[r][0..cols) = src[r][0..cols) for `rows` rows of 16-bit elements with row strides dst_ld / src_ld (elements): makes
 // an operand whose row stride is not a multiple of 16 bytes readable by TMA.
 cudaError_t launch_repack_rows16(void* dst, const void* src, long long rows, long long cols, long long dst_ld,

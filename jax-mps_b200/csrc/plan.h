@@ -50,7 +50,7 @@ struct IGemmParams {
 struct Plan;
 
 struct Step {
-  enum Kind { KERNEL, IGEMM, MEMCPY, MEMSET, WHILE, CASE, ALL_REDUCE, SCATTER, JOIN, GEMM16, REPACK16 } kind = KERNEL;
+  enum Kind { KERNEL, IGEMM, MEMCPY, MEMSET, WHILE, CASE, ALL_REDUCE, SCATTER, JOIN, GEMM16, REPACK16, TRANSPOSE } kind = KERNEL;
   std::string label;                  // op names, for profiling and error text
   // KERNEL
   int kernel = -1;                    // index into Executable::kernels
@@ -61,6 +61,7 @@ struct Step {
   IGemmParams ig;
   // GEMM16: args = {A, B, C, [fp32 scratch], [counters]}; iparams = {has scratch, has counters}
   // REPACK16: args = {dst, src}; iparams = {rows, cols, dst_ld, src_ld}
+  // TRANSPOSE: args = {dst, src}; iparams = {element bytes, batch, rows, cols, dst_ld, dst batch stride, dst offset (elements)}
   Gemm16Launch g16;
   // MEMCPY: args = {dst, src}; MEMSET: args = {dst}
   size_t bytes = 0;

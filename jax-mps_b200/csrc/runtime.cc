@@ -524,7 +524,7 @@ b200_error* run_plan(ExecCtx& x, const Plan& plan);
 bool graph_safe(const Plan& plan) {
   for (const Step& s : plan.steps) {
     switch (s.kind) {
-      case Step::KERNEL: case Step::IGEMM: case Step::MEMCPY: case Step::GEMM16: case Step::REPACK16: break;
+      case Step::KERNEL: case Step::IGEMM: case Step::MEMCPY: case Step::GEMM16: case Step::REPACK16: case Step::TRANSPOSE: break;
       case Step::WHILE:
         if (s.trip_count < 0 || !graph_safe(*s.sub[1])) return false;
         break;
@@ -590,6 +590,13 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
                                     c->error_flag, st, &x.launches, &why);
       if (e != cudaSuccess)
         return make_error(B200_INTERNAL, "launch of " + s.label + " failed: " + (why ? why : cudaGetErrorString(e)));
+      return nullptr;
+    }
+    case Step::TRANSPOSE: {
+      char* dst = (char*)x.ptrs[s.args[0]] + s.iparams[6] * s.iparams[0];
+      cudaError_t e = launch_transpose2d(dst, x.ptrs[s.args[1]], (int)s.iparams[0], s.iparams[1], s.iparams[2], s.iparams[3],
+                                         s.iparams[4], s.iparams[5], st, &x.launches);
+      if (e != cudaSuccess) return make_error(B200_INTERNAL, "launch of " + s.label + " failed: " + cudaGetErrorString(e));
       return nullptr;
     }
     case Step::REPACK16: {

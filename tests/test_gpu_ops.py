@@ -6,9 +6,12 @@ reference's catalogue (tests/configs/{conv,matmul,slice,reduction,control_flow}.
 import math
 
 import numpy as np
+
+import b200
 import pytest
 
 from b200.shlo.builder import Builder
+from oracle import interp
 from tests.util import check, compare, run_gpu
 
 pytestmark = pytest.mark.gpu
@@ -140,6 +143,43 @@ def test_big_transpose(client):
     b = Builder()
     x = b.arg((96, 200, 33), "f32")
     check(client, b.module([b.transpose(x, (2, 1, 0)), b.transpose(x, (1, 0, 2))]), [f32(96, 200, 33)])
+
+
+@pytest.mark.parametrize("shape,perm,dt", [
+    ((1000, 520), (1, 0), "f32"), ((1000, 520), (1, 0), "bf16"), ((514, 300), (1, 0), "i32"),
+    ((6, 200, 136), (0, 2, 1), "f32"), ((6, 200, 136), (0, 2, 1), "bf16"),
+    ((4, 16, 64, 40), (0, 1, 3, 2), "f32"),           # two batch dimensions
+    ((40, 8, 512), (2, 0, 1), "bf16"),                # [X0, X1, Y] -> [Y, X0, X1]
+    ((512, 40, 8), (1, 2, 0), "f32"),                 # [X, Y0, Y1] -> [Y0, Y1, X]
+])
+def test_tiled_transpose(client, shape, perm, dt):
+    """Large transposes that move the innermost dimension go through the shared-memory tile kernel (plan step
+    `transpose`); values must be the input's, bit for bit."""
+    b = Builder()
+    x = b.arg(shape, dt)
+    text = b.module([b.transpose(x, perm)])
+    plan, _ = b200.compile_to_plan(text)
+    assert "transpose batch=" in plan and "kernel " not in plan, plan
+    a = (np.random.default_rng(5).standard_normal(shape) * 100).astype(np.float32)
+    if dt == "i32":
+        a = a.astype(np.int32)
+    got, _ = run_gpu(client, text, [a], dtypes=[dt])
+    want = interp.run_text(text, [a])
+    np.testing.assert_array_equal(got[0], want[0])
+
+
+def test_transposes_concatenated_along_rows(client):
+    """concatenate(transpose(a), transpose(b)) along dimension 0 (the form the weights of a decode loop take): each
+    part is one tiled transpose into its rows of the result."""
+    b = Builder()
+    x, y = b.arg((256, 384), "bf16"), b.arg((256, 130), "bf16")
+    text = b.module([b.concatenate([b.transpose(x, (1, 0)), b.transpose(y, (1, 0))], 0)])
+    plan, _ = b200.compile_to_plan(text)
+    assert plan.count("transpose batch=") == 2 and "kernel " not in plan, plan
+    a0, a1 = f32(256, 384), f32(256, 130)
+    got, _ = run_gpu(client, text, [a0, a1], dtypes=["bf16", "bf16"])
+    want = interp.run_text(text, [a0, a1])
+    np.testing.assert_array_equal(got[0], want[0])
 
 
 def test_slice_pad_concat(client):
@@ -440,7 +480,8 @@ def test_loop_state_pointer_exchange(client):
             t1 = s.tanh(s.add(a, c))
             t2 = s.reduce_sum(s.mul(t1, t1), [0])
             t3 = s.mul(t1, s.broadcast_in_dim(t2, (N,), []))
-            a2 = s.add(s.mul(t3, s.full((N,), 1e-3, "f32")), c)
+            # (the factor keeps the map contractive: rounding differences of the sum must not grow over the iterations)
+            a2 = s.add(s.mul(t3, s.full((N,), 1e-4, "f32")), c)
             c2 = s.sub(a2, s.mul(a, s.full((N,), 0.5, "f32")))       # reads the old state after a2 exists
             return [s.add(i, s.const(1, "i32")), a2, c2, c2, e]
         outs = b.while_([b.const(0, "i32"), x, y, y, x], cond, body)

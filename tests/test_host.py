@@ -159,23 +159,75 @@ def test_column_reduction_source_compiles(dt):
     assert "acc0[q]" in src
 
 
+def _split_at_while(plan):
+    lines = plan.splitlines()
+    w = next(i for i, l in enumerate(lines) if l.strip().startswith("while"))
+    return lines[1:w], [l for l in lines[w + 1:] if l.startswith("    ")]
+
+
 def test_weight_widening_is_hoisted_out_of_the_decode_loop():
-    """bf16 contractions run as f32 contractions of widened operands. Weights come from outside the decode loop:
-    their widened copies are made once in front of the `while`, not in every iteration."""
+    """Where the native 16-bit kernels do not apply (here: switched off), bf16 contractions run as f32 contractions
+    of widened operands. Weights come from outside the decode loop: their widened copies are made once in front of
+    the `while`, not in every iteration."""
     prog = programs.gemma_greedy_decode(vocab=64, dim=32, layers=2, heads=2, head_dim=16, hidden=64, prompt_len=4,
                                         new_tokens=4, cache_len=8)
-    def split(plan):
-        lines = plan.splitlines()
-        w = next(i for i, l in enumerate(lines) if l.strip().startswith("while"))
-        return lines[1:w], [l for l in lines[w + 1:] if l.startswith("    ")]
-    before, body = split(b200.compile_to_plan(prog.text, validate=True)[0])
-    os.environ["B200_NO_HOIST"] = "1"
+    os.environ["B200_NO_GEMM16"] = "1"
     try:
-        before0, body0 = split(b200.compile_to_plan(prog.text)[0])
+        before, body = _split_at_while(b200.compile_to_plan(prog.text, validate=True)[0])
+        os.environ["B200_NO_HOIST"] = "1"
+        before0, body0 = _split_at_while(b200.compile_to_plan(prog.text)[0])
     finally:
-        del os.environ["B200_NO_HOIST"]
+        os.environ.pop("B200_NO_HOIST", None)
+        del os.environ["B200_NO_GEMM16"]
     count = lambda ls: sum(l.count("convert") for l in ls)
     assert count(before) > count(before0) and count(body) < count(body0)
+
+
+def test_bf16_decode_loop_reads_its_weights_in_place():
+    """With the native 16-bit kernels the decode loop multiplies by the bf16 weights as they are: no widened copy in
+    front of the loop, every product of the body a skinny 16-bit kernel, the key-value caches updated in their
+    windows, and one copy of the normalised activation for the projections that share it."""
+    prog = programs.gemma_decode_loop(vocab=64, dim=32, layers=2, heads=2, head_dim=16, hidden=64, start=4, new_tokens=4,
+                                      cache_len=8)
+    plan = b200.compile_to_plan(prog.text, validate=True)[0]
+    before, body = _split_at_while(plan)
+    assert not any("convert" in l for l in before) and "igemm" not in plan
+    assert sum("gemv16" in l for l in body) == 2 * 9 + 1
+    assert sum(l.count(".window") for l in body) >= 2 * 2
+    # q, k and v projections read one converted activation (args[0] of three consecutive products is one slot)
+    prods = [l for l in body if "gemv16" in l]
+    first = [l.split("args=[")[1].split(",")[0] for l in prods[:3]]
+    assert len(set(first)) == 1
+
+
+def test_loop_invariant_weights_of_skinny_products_are_transposed_once_and_merged():
+    """Weights large enough to matter are transposed (and, for products sharing their left operand, concatenated) in
+    front of the decode loop; the loop then runs one k-contiguous product for q / k / v and one for gate / up."""
+    prog = programs.gemma_decode_loop(vocab=512, dim=256, layers=2, heads=2, head_dim=128, hidden=512, start=4, new_tokens=4,
+                                      cache_len=8)
+    plan = b200.compile_to_plan(prog.text, validate=True)[0]
+    before, body = _split_at_while(plan)
+    assert sum(l.count("transpose batch=") for l in before) == 2 * 7       # seven weights per layer, tiled kernel
+    prods = [l for l in body if "gemv16" in l]
+    assert sum("N=512 K=256" in l and "gemv16_kc" in l for l in prods) == 2        # q | k | v: 256 + 128 + 128 columns
+    assert sum("N=1024 K=256" in l and "gemv16_kc" in l for l in prods) == 2       # gate | up
+    assert len(prods) == 2 * 6 + 1
+    os.environ["B200_NO_WEIGHT_HOIST"] = "1"
+    try:
+        plan0 = b200.compile_to_plan(prog.text)[0]
+    finally:
+        del os.environ["B200_NO_WEIGHT_HOIST"]
+    assert sum("gemv16" in l for l in plan0.splitlines()) == 2 * 9 + 1
+
+
+def test_common_subexpressions_are_computed_once():
+    b = Builder()
+    x = b.arg((64, 32), "f32")
+    w1, w2 = b.arg((32, 16), "bf16"), b.arg((32, 8), "bf16")
+    y1 = b.matmul(b.convert(b.tanh(x), "bf16"), w1)
+    y2 = b.matmul(b.convert(b.tanh(x), "bf16"), w2)
+    plan = b200.compile_to_plan(b.module([y1, y2]))[0]
+    assert plan.count("kernel ") == 1, plan
 
 
 def test_custom_assembly_and_generic_form_give_the_same_plan():
@@ -264,7 +316,17 @@ def test_plans_of_case_scatter_and_half_precision_contractions():
     b = Builder()
     p, q = b.arg((64, 64), "bf16"), b.arg((64, 64), "bf16")
     plan, src = b200.compile_to_plan(b.module([b.matmul(p, q)]))
-    assert "igemm M=64 N=64 K=64" in plan and plan.count("convert") >= 2
+    assert "gemm16 M=64 N=64 K=64" in plan and "convert" not in plan          # native 16-bit tiles, no widened copies
+    # a bf16 operand against an f32 one has no native kernel: both sides go through f32
+    b = Builder()
+    p, q = b.arg((64, 64), "bf16"), b.arg((64, 64), "f32")
+    plan, src = b200.compile_to_plan(b.module([b.dot_general(b.convert(p, "f32"), q, ((1,), (0,)))]))
+    assert "igemm M=64 N=64 K=64" in plan
+    # an operand whose row stride is not a multiple of 16 bytes is copied into padded rows first
+    b = Builder()
+    p, q = b.arg((64, 100), "bf16"), b.arg((100, 30), "bf16")
+    plan, src = b200.compile_to_plan(b.module([b.matmul(p, q)]))
+    assert plan.count("repack16") == 2 and "ld 100->104" in plan and "ld 30->32" in plan and "gemm16 M=64 N=30 K=100" in plan
 
     b = Builder()
     t, i, u = b.arg((12, 8), "f32"), b.arg((5, 2), "i32"), b.arg((5,), "f32")
