@@ -203,14 +203,13 @@ def test_bf16_decode_loop_reads_its_weights_in_place():
 def test_loop_invariant_weights_of_skinny_products_are_transposed_once_and_merged():
     """Weights large enough to matter are transposed (and, for products sharing their left operand, concatenated) in
     front of the decode loop; the loop then runs one k-contiguous product for q / k / v and one for gate / up."""
-    prog = programs.gemma_decode_loop(vocab=512, dim=256, layers=2, heads=2, head_dim=128, hidden=512, start=4, new_tokens=4,
+    prog = programs.gemma_decode_loop(vocab=512, dim=256, layers=2, heads=2, head_dim=256, hidden=512, start=4, new_tokens=4,
                                       cache_len=8)
     plan = b200.compile_to_plan(prog.text, validate=True)[0]
     before, body = _split_at_while(plan)
     assert sum(l.count("transpose batch=") for l in before) == 2 * 7       # seven weights per layer, tiled kernel
     prods = [l for l in body if "gemv16" in l]
-    assert sum("N=512 K=256" in l and "gemv16_kc" in l for l in prods) == 2        # q | k | v: 256 + 128 + 128 columns
-    assert sum("N=1024 K=256" in l and "gemv16_kc" in l for l in prods) == 2       # gate | up
+    assert sum("N=1024 K=256" in l and "gemv16_kc" in l for l in prods) == 2 * 2   # q | k | v (512 + 256 + 256) and gate | up
     assert len(prods) == 2 * 6 + 1
     os.environ["B200_NO_WEIGHT_HOIST"] = "1"
     try:
