@@ -7,6 +7,7 @@ captures summarised under profiles/, and handy when tuning a kernel):
     python -m b200.bench_ops gemma [--layers 18] [--reps 3] [--profile]
     python -m b200.bench_ops distilbert [--reps 5] [--profile]
     python -m b200.bench_ops gemm --shape M,N,K [--reps 20]
+    python -m b200.bench_ops gemv --shape M,N,K --layout kc|nc [--reps 50]
 
 `gemma` times the Gemma-2B-shaped prefill (512 prompt tokens in one pass) and the 128-step greedy decode loop (bf16
 weights resident in HBM); `distilbert` the DistilBERT-base-shaped masked-LM step (forward + backward, bf16); `gemm` one
@@ -222,9 +223,39 @@ def gemm(client, m, n, k, reps):
           + " | ".join(l.strip()[:90] for l in exe.plan_text().splitlines()[1:]))
 
 
+def gemv(client, m, n, k, layout, reps, hbm_gbs=6546.2):
+    """One skinny bf16 product x[m,k] . W with W stored [k,n] (`nc`) or [n,k] (`kc`), timed over `reps` launches that
+    rotate through enough distinct weight buffers to exceed the 126 MB L2 (so every launch streams from HBM)."""
+    b = Builder()
+    x = b.arg((m, k), "bf16")
+    w = b.arg((k, n) if layout == "nc" else (n, k), "bf16")
+    text = b.module([b.dot_general(x, w, ((1,), (0,) if layout == "nc" else (1,)))])
+    exe = client.compile(text)
+    rng = np.random.default_rng(0)
+    nbuf = max(2, int(300e6 // (2 * n * k)) + 1)
+    wshape = (k, n) if layout == "nc" else (n, k)
+    ws = [client.buffer_from_host(rng.integers(0, 1 << 14, wshape, dtype=np.uint16), dtype="bf16") for _ in range(min(nbuf, 64))]
+    xb = client.buffer_from_host(rng.standard_normal((m, k)).astype(np.float32), dtype="bf16")
+    record = _events(client)
+    for i in range(3):
+        exe.execute([xb, ws[i % len(ws)]])
+    client.synchronize()
+    a = record()
+    for i in range(reps):
+        exe.execute([xb, ws[i % len(ws)]])
+    e = record()
+    client.synchronize()
+    us = a.elapsed_time(e) * 1e3 / reps
+    gbs = 2.0 * n * k / us / 1e3
+    print(f"gemv bf16 {layout} M={m} N={n} K={k}: {us:.1f} us per launch, {gbs:.0f} GB/s of weights = {gbs / hbm_gbs:.2f} of the "
+          f"measured copy bandwidth ({len(ws)} rotating weight buffers); plan: " +
+          " | ".join(l.strip()[:80] for l in exe.plan_text().splitlines()[1:]))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["conv", "reduce", "scan", "gemma", "distilbert", "gemm"])
+    ap.add_argument("what", choices=["conv", "reduce", "scan", "gemma", "distilbert", "gemm", "gemv"])
+    ap.add_argument("--layout", default="kc", choices=["kc", "nc"])
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--profile", action="store_true")
     ap.add_argument("--case", default="s1")
@@ -249,6 +280,10 @@ def main():
         import json
         kw = {"layers": a.layers} if a.layers else {}
         print(json.dumps(distilbert_step(client, reps=a.reps, profile=a.profile, verbose=True, **kw)))
+        return
+    if a.what == "gemv":
+        m, n, k = (int(v) for v in a.shape.split(","))
+        gemv(client, m, n, k, a.layout, a.reps)
         return
     if a.what == "gemm":
         m, n, k = (int(v) for v in a.shape.split(","))

@@ -223,6 +223,23 @@ struct Inliner {
                            "compile the per-shard (manual) program instead");
       }
     }
+    // convert(convert(x, wider type), type of x) -> x when the first conversion is exact (bf16 -> f32 -> bf16 between two
+    // products of a bf16 network)
+    if (sh == "convert" && op->operands.size() == 1 && op->operands[0]->def && op->operands[0]->def->short_name() == "convert") {
+      Value* inner = op->operands[0]->def->operands[0];
+      const DT a = inner->type.dt, mid = op->operands[0]->type.dt;
+      auto widens = [](DT from, DT to) {
+        if ((from == DT::BF16 || from == DT::F16) && (to == DT::F32 || to == DT::F64)) return true;
+        if (from == DT::F32 && to == DT::F64) return true;
+        if (dt_is_signed(from) && dt_is_signed(to) && dt_size(to) > dt_size(from)) return true;
+        if (dt_is_unsigned(from) && dt_is_int(to) && dt_size(to) > dt_size(from)) return true;
+        return false;
+      };
+      if (inner->type == op->results[0]->type && widens(a, mid)) {
+        remap[op->results[0]] = res(inner);
+        return;
+      }
+    }
     // x + broadcast(0), x * broadcast(1), x - broadcast(0), x / broadcast(1) -> x
     // (src/pjrt_plugin/passes/canonicalize_broadcast_identity.cc)
     if ((sh == "add" || sh == "multiply" || sh == "subtract" || sh == "divide") && op->operands.size() == 2 &&
@@ -537,11 +554,65 @@ struct SkinnyWeightHoist {
       for (auto& r : op->regions) run(r.get());
       if (op->short_name() != "while" || op->regions.size() != 2 || getenv("B200_NO_WEIGHT_HOIST")) continue;
       std::vector<std::unique_ptr<Op>> front;          // operations to place in front of the loop
+      hoist_invariants(op->regions[1].get(), b, front);
       rewrite(op->regions[1].get(), b, front);
       const size_t n = front.size();
       for (size_t k = 0; k < n; k++) b->ops.insert(b->ops.begin() + i + k, std::move(front[k]));
       i += n;
     }
+  }
+
+  // Loop-invariant code motion: a pure elementwise or indexing operation of the body whose operands all come from
+  // outside the loop (or from operations moved before it) is computed once in front of the loop: the (1 + w) scale of
+  // every norm of a decode loop, a mask built from constants. Constants, iotas and broadcasts stay where they are (their
+  // users evaluate them inline for free) and are copied in front of the loop only where a moved operation needs them.
+  void hoist_invariants(Block* body, Block* outer, std::vector<std::unique_ptr<Op>>& front) {
+    if (getenv("B200_NO_LICM")) return;
+    std::set<Value*> moved;                           // results now defined in front of the loop
+    std::map<Op*, Value*> dup_copy;                   // duplicable operations copied in front of the loop
+    std::function<bool(Value*, int)> invariant = [&](Value* v, int depth) -> bool {
+      if (moved.count(v) || !defined_in(v, body)) return true;
+      Op* d = v->def;
+      if (!d || d->parent != body || depth > 8) return false;
+      const std::string sh = d->short_name();
+      if (sh == "constant" || sh == "iota") return true;
+      if (sh == "broadcast_in_dim") return invariant(d->operands[0], depth + 1);
+      return false;
+    };
+    std::function<Value*(Value*)> outside = [&](Value* v) -> Value* {
+      if (moved.count(v) || !defined_in(v, body)) return v;
+      Op* d = v->def;                                 // a constant, iota or broadcast: copy it
+      auto it = dup_copy.find(d);
+      if (it != dup_copy.end()) return it->second;
+      auto c = std::make_unique<Op>();
+      c->name = d->name;
+      c->attrs = d->attrs;
+      for (Value* o : d->operands) c->operands.push_back(outside(o));
+      Value* nv = make(c, v->type, outer);
+      front.push_back(std::move(c));
+      dup_copy[d] = nv;
+      return nv;
+    };
+    std::vector<std::unique_ptr<Op>> kept;
+    for (auto& up : body->ops) {
+      Op* op = up.get();
+      const std::string sh = op->short_name();
+      static const std::set<std::string> indexing = {"reshape", "transpose", "reverse", "slice", "pad", "concatenate", "convert"};
+      const bool pure = op->regions.empty() && op->results.size() == 1 && (op->name.rfind("stablehlo.", 0) == 0) &&
+                        (is_elementwise_op(sh) || indexing.count(sh));
+      bool ok = pure && !op->operands.empty() && op->results[0]->type.numel() <= (1 << 24);
+      bool any_real = false;                          // reads something that is not a constant: worth a kernel of its own
+      for (Value* o : op->operands) {
+        ok = ok && invariant(o, 0);
+        any_real = any_real || moved.count(o) || !defined_in(o, body);
+      }
+      if (!ok || !any_real) { kept.push_back(std::move(up)); continue; }
+      for (auto& o : op->operands) o = outside(o);
+      op->parent = outer;
+      moved.insert(op->results[0]);
+      front.push_back(std::move(up));
+    }
+    body->ops = std::move(kept);
   }
 
   void rewrite(Block* body, Block* outer, std::vector<std::unique_ptr<Op>>& front) {
@@ -1968,6 +2039,320 @@ struct Planner {
     return s + "}";
   }
 
+
+  // ---- row chains ------------------------------------------------------------------------
+  // softmax, RMSNorm, LayerNorm and their gradients are chains of reductions over the trailing dimensions of one
+  // tensor ("rows") and pointwise kernels over the same tensor that read the reductions' results through a broadcast
+  // along the row (the reference matches these as named fusions: src/pjrt_plugin/passes/fuse_softmax.cc,
+  // fuse_layer_norm.cc, fuse_rms_norm.cc). Such a chain becomes one kernel: a warp (rows under 128 elements) or a block
+  // owns a row and runs the stages one after the other over it; a reduction's result stays in a register of every
+  // thread, a pointwise value that only later stages read is recomputed instead of stored, and the row's operands come
+  // from L1 / L2 after the first pass. Launches and round trips through memory drop by the length of the chain.
+  struct RowChain {
+    std::vector<Group*> stages;
+    std::vector<int64_t> in_shape, kept_shape, red_shape;
+    int64_t Nk = 1, Nr = 1;
+  };
+
+  bool row_form(Group* g, RowChain& rc) {
+    if (!g->is_reduce || g->roots.empty()) return false;
+    Op* r = g->roots[0];
+    const auto& shape = r->operands[0]->type.dims;
+    auto dims = attr_i64s(r->attr("dimensions"));
+    std::sort(dims.begin(), dims.end());
+    const int n = (int)shape.size(), nd = (int)dims.size();
+    if (nd == 0 || nd > n) return false;
+    for (int i = 0; i < nd; i++) if (dims[i] != n - nd + i) return false;      // a suffix of the dimensions
+    rc.in_shape = shape;
+    rc.kept_shape.assign(shape.begin(), shape.begin() + (n - nd));
+    rc.red_shape.assign(shape.begin() + (n - nd), shape.end());
+    rc.Nk = rc.Nr = 1;
+    for (auto v : rc.kept_shape) rc.Nk *= v;
+    for (auto v : rc.red_shape) rc.Nr *= v;
+    if (rc.Nr < 32 || rc.Nr > 16384 || rc.Nk < 1 || rc.Nk * rc.Nr >= (1LL << 31)) return false;
+    for (Op* root : g->roots) {
+      if (root->operands[0]->type.dims != shape) return false;
+      auto d2 = attr_i64s(root->attr("dimensions"));
+      std::sort(d2.begin(), d2.end());
+      if (d2 != dims) return false;
+      const size_t np = root->operands.size() / 2;
+      for (size_t k = np; k < root->operands.size(); k++) {
+        Op* d = root->operands[k]->def;
+        if (!(d && d->short_name() == "constant")) return false;
+      }
+    }
+    return true;
+  }
+
+  // Can stage `g` run inside the chain? Every path from its outputs to a reduction result of the chain must keep the
+  // row: elementwise operations at the full index, then one broadcast along the row from the kept shape.
+  bool row_safe(Group* g, const RowChain& rc, const std::set<Op*>& members, const std::set<Value*>& reduced, BlockState& st) {
+    enum { FULL, KEPT, OTHER };
+    std::map<std::pair<Value*, int>, bool> memo;
+    std::function<bool(Value*, int)> chk = [&](Value* v, int state) -> bool {
+      if (reduced.count(v)) return state == KEPT || rc.Nk == 1;
+      auto key = std::make_pair(v, state);
+      auto it = memo.find(key);
+      if (it != memo.end()) return it->second;
+      memo[key] = true;
+      Op* d = v->def;
+      const bool internal = d && d->parent == st.block &&
+                            (members.count(d) || (is_dup(d) && !st.dup_materialize.count(d) && !slot_of.count(v)));
+      if (!internal) return true;                       // read from memory
+      if (categorize(d) == Cat::REDUCE) return memo[key] = false;
+      const std::string sh = d->short_name();
+      bool ok = true;
+      if (is_elementwise_op(sh)) {
+        for (Value* o : d->operands) ok = ok && chk(o, o->type.dims == v->type.dims ? state : OTHER);
+      } else if (sh == "broadcast_in_dim") {
+        Value* o = d->operands[0];
+        auto bd = attr_i64s(d->attr("broadcast_dimensions"));
+        bool prefix = state == FULL && v->type.dims == rc.in_shape && o->type.dims == rc.kept_shape;
+        for (size_t i = 0; i < bd.size() && prefix; i++) prefix = bd[i] == (int64_t)i;
+        ok = chk(o, prefix ? KEPT : OTHER);
+      } else {
+        for (Value* o : d->operands) ok = ok && chk(o, OTHER);
+      }
+      return memo[key] = ok;
+    };
+    if (g->is_reduce) {
+      for (Op* root : g->roots) {
+        const size_t np = root->operands.size() / 2;
+        for (size_t k = 0; k < np; k++) if (!chk(root->operands[k], FULL)) return false;
+      }
+      return true;
+    }
+    // a pointwise stage lives on the full index space or (the scalar arithmetic between a sum and its use) on the rows
+    const bool kept = g->roots[0]->results[0]->type.dims != rc.in_shape;
+    for (Op* root : g->roots) {
+      if (root->results[0]->type.dims != (kept ? rc.kept_shape : rc.in_shape)) return false;
+      if (!chk(root->results[0], kept ? KEPT : FULL)) return false;
+    }
+    return true;
+  }
+
+  // does `g` read (through its own members) a value of `produced`?
+  bool reads_any(Group* g, const std::set<Value*>& produced, BlockState& st) {
+    std::set<Value*> seen;
+    std::function<bool(Value*)> walk = [&](Value* v) -> bool {
+      if (produced.count(v)) return true;
+      if (!seen.insert(v).second) return false;
+      Op* d = v->def;
+      if (!d || d->parent != st.block) return false;
+      if (!(g->members.count(d) || (is_dup(d) && !st.dup_materialize.count(d) && !slot_of.count(v)))) return false;
+      if (categorize(d) == Cat::REDUCE && !g->is_reduce) return false;
+      for (Value* o : d->operands) if (walk(o)) return true;
+      return false;
+    };
+    for (Op* m : g->members)
+      for (Value* o : m->operands) if (walk(o)) return true;
+    return false;
+  }
+
+  void emit_row_chain(const RowChain& rc, Plan& plan, BlockState& st) {
+    const int64_t Nk = rc.Nk, Nr = rc.Nr;
+    const int T = Nr >= 128 ? 256 : 32, per_block = 256 / T;
+    const std::string it = "int";
+    std::set<Op*> chain_members;
+    for (Group* g : rc.stages) chain_members.insert(g->members.begin(), g->members.end());
+    // a value needs memory when somebody outside the chain reads it (looking through the broadcasts and other
+    // duplicable operations that are evaluated inline by their users)
+    std::function<bool(Value*)> stored = [&](Value* v) -> bool {
+      if (st.returned.count(v)) return true;
+      for (Op* u : st.users[v]) {
+        if (chain_members.count(u)) {
+          // a cheap operation can be evaluated by several kernels: all of them must be stages of this chain
+          bool all_inside = true;
+          auto gi = st.group_of.find(u);
+          if (gi != st.group_of.end())
+            for (Group* ug : gi->second) all_inside = all_inside && std::find(rc.stages.begin(), rc.stages.end(), ug) != rc.stages.end();
+          if (all_inside) continue;
+          return true;
+        }
+        if (is_dup(u) && !st.dup_materialize.count(u) && !slot_of.count(u->results[0])) {
+          if (stored(u->results[0])) return true;
+          continue;
+        }
+        return true;
+      }
+      return false;
+    };
+    // kept index decomposition, shared by all stages
+    Emitter pe;
+    pe.is_internal = [](Op*) { return false; };
+    pe.idx_t = it;
+    pe.name_prefix = "k";
+    pe.indent_ = 2;
+    Ctx kc;
+    kc.shape = rc.kept_shape;
+    kc.lin = "o";
+    pe.ensure_idx(kc);
+    std::vector<Value*> ins, outs;
+    std::ostringstream decl, body;
+    std::set<Op*> members_so_far;
+    std::map<Value*, std::string> bound;
+    std::string label = "row{";
+    int stage_no = 0;
+    for (Group* g : rc.stages) {
+      label += (stage_no ? " > " : "") + group_label(g);
+      members_so_far.insert(g->members.begin(), g->members.end());
+      Emitter em;
+      em.idx_t = it;
+      em.name_prefix = std::string(1, (char)('a' + stage_no));
+      em.indent_ = 6;
+      em.seed_inputs(ins);
+      em.bound = bound;
+      const std::set<Op*> ms = members_so_far;
+      em.is_internal = [this, ms, &st](Op* o) {
+        return (ms.count(o) && categorize(o) != Cat::REDUCE) || (is_dup(o) && !st.dup_materialize.count(o) && !slot_of.count(o->results[0]));
+      };
+      Ctx rctx;
+      rctx.shape = rc.red_shape;
+      rctx.lin = "r";
+      em.ensure_idx(rctx);
+      Ctx oc;
+      oc.shape = rc.in_shape;
+      oc.idx = kc.idx;
+      oc.idx.insert(oc.idx.end(), rctx.idx.begin(), rctx.idx.end());
+      oc.lin = "lin";
+      const std::string loop = "    for (" + it + " r = lane; r < " + std::to_string(Nr) + "; r += " + std::to_string(T) + ") {\n      const " +
+                               it + " lin = o * " + std::to_string(Nr) + " + r;\n";
+      if (g->is_reduce) {
+        std::vector<Value*> operands, results;
+        std::vector<std::string> inits;
+        std::vector<DT> dts;
+        struct Part { Block* body; size_t n; };
+        std::vector<Part> parts;
+        for (Op* root : g->roots) {
+          const size_t np = root->operands.size() / 2;
+          for (size_t k = 0; k < np; k++) {
+            operands.push_back(root->operands[k]);
+            DenseValue dv = attr_dense(root->operands[np + k]->def->attr("value"));
+            inits.push_back(literal(dv.type.dt, dv.data.data()));
+            results.push_back(root->results[k]);
+            dts.push_back(root->results[k]->type.dt);
+          }
+          parts.push_back({root->regions[0].get(), np});
+        }
+        const size_t n = operands.size();
+        std::vector<std::string> vals;
+        for (Value* v : operands) vals.push_back(em.emit(v, oc));
+        em.round_small_floats = false;
+        auto combine = [&](Emitter& e, const std::string& other, bool from_vals) {
+          size_t base = 0;
+          for (auto& part : parts) {
+            std::vector<std::string> a;
+            for (size_t k = 0; k < part.n; k++) a.push_back("acc" + std::to_string(base + k));
+            for (size_t k = 0; k < part.n; k++) a.push_back(from_vals ? vals[base + k] : other + std::to_string(base + k));
+            auto c = e.emit_scalar_region(part.body, a);
+            for (size_t k = 0; k < part.n; k++) e.line("acc" + std::to_string(base + k) + " = " + c[k] + ";");
+            base += part.n;
+          }
+        };
+        combine(em, "", true);
+        const std::string sn = std::to_string(stage_no);
+        for (size_t k = 0; k < n; k++) {
+          decl << "  " << c_type(dts[k]) << " S" << sn << "_" << k << ";\n";
+          if (T == 256) decl << "  __shared__ " << c_type(dts[k]) << " sm" << sn << "_" << k << "[8];\n";
+        }
+        body << "  {\n";
+        for (size_t k = 0; k < n; k++) body << "    " << c_type(dts[k]) << " acc" << k << " = " << inits[k] << ";\n";
+        body << "    {\n  " << loop << em.str() << "      }\n    }\n";
+        body << "    #pragma unroll\n    for (int m = 16; m >= 1; m >>= 1) {\n";
+        for (size_t k = 0; k < n; k++) body << "      const " << c_type(dts[k]) << " oth" << k << " = shfl_xor(acc" << k << ", m);\n";
+        {
+          Emitter te;
+          te.idx_t = it;
+          te.name_prefix = em.name_prefix + "t";
+          te.indent_ = 6;
+          te.round_small_floats = false;
+          combine(te, "oth", false);
+          body << te.str();
+        }
+        body << "    }\n";
+        if (T == 256) {
+          body << "    if ((threadIdx.x & 31) == 0) {";
+          for (size_t k = 0; k < n; k++) body << " sm" << sn << "_" << k << "[threadIdx.x >> 5] = acc" << k << ";";
+          body << " }\n    __syncthreads();\n";
+          for (size_t k = 0; k < n; k++) body << "    acc" << k << " = sm" << sn << "_" << k << "[0];\n";
+          body << "    for (int w = 1; w < 8; ++w) {\n";
+          for (size_t k = 0; k < n; k++) body << "      const " << c_type(dts[k]) << " oth" << k << " = sm" << sn << "_" << k << "[w];\n";
+          Emitter te;
+          te.idx_t = it;
+          te.name_prefix = em.name_prefix + "u";
+          te.indent_ = 6;
+          te.round_small_floats = false;
+          combine(te, "oth", false);
+          body << te.str() << "    }\n";
+        }
+        for (size_t k = 0; k < n; k++) body << "    S" << sn << "_" << k << " = acc" << k << ";\n";
+        body << "  }\n";
+        for (size_t k = 0; k < n; k++) {
+          bound[results[k]] = "S" + sn + "_" + std::to_string(k);
+          if (stored(results[k])) {
+            body << "  if (lane == 0 && live) out" << outs.size() << "[o] = " << store_expr(dts[k], "S" + sn + "_" + std::to_string(k)) << ";\n";
+            outs.push_back(results[k]);
+          }
+        }
+      } else if (g->roots[0]->results[0]->type.dims != rc.in_shape) {
+        // arithmetic on the rows' own values (a mean turned into a reciprocal root): every thread computes it
+        Emitter ke;
+        ke.idx_t = it;
+        ke.name_prefix = em.name_prefix + "k";
+        ke.indent_ = 2;
+        ke.seed_inputs(ins);
+        ke.bound = bound;
+        ke.is_internal = em.is_internal;
+        Ctx kctx = kc;
+        for (Op* root : g->roots) {
+          Value* v = root->results[0];
+          const std::string e = ke.emit(v, kctx);
+          const std::string nm = "K" + std::to_string(stage_no) + "_" + std::to_string(bound.size());
+          ke.line(std::string("const ") + c_type(v->type.dt) + " " + nm + " = " + e + ";");
+          bound[v] = nm;
+          if (stored(v)) {
+            ke.line("if (lane == 0 && live) out" + std::to_string(outs.size()) + "[o] = " + store_expr(v->type.dt, nm) + ";");
+            outs.push_back(v);
+          }
+        }
+        body << ke.str();
+        ins = ke.inputs;
+        stage_no++;
+        continue;
+      } else {
+        std::vector<std::pair<Value*, std::string>> stores;
+        for (Op* root : g->roots)
+          if (stored(root->results[0])) stores.push_back({root->results[0], em.emit(root->results[0], oc)});
+        if (!stores.empty()) {
+          for (auto& sv : stores) {
+            em.line("out" + std::to_string(outs.size()) + "[lin] = " + store_expr(sv.first->type.dt, sv.second) + ";");
+            outs.push_back(sv.first);
+          }
+          body << "  if (live) {\n" << loop << em.str() << "    }\n  }\n";
+        }
+      }
+      ins = em.inputs;
+      stage_no++;
+    }
+    label += "}";
+    std::ostringstream src;
+    src << "extern \"C\" __global__ void __launch_bounds__(256) @NAME@(" << signature(outs, ins) << ") {\n";
+    // rows past the end (the last block of the warp-per-row form) work on the last row and store nothing
+    src << "  const " << it << " o_raw = (" << it << ")blockIdx.x * " << per_block << " + threadIdx.x / " << T << ";\n";
+    src << "  const bool live = o_raw < " << Nk << ";\n";
+    src << "  const " << it << " o = live ? o_raw : " << Nk - 1 << ";\n";
+    src << "  const int lane = threadIdx.x % " << T << ";\n";
+    src << pe.str() << decl.str() << body.str() << "}\n";
+    Launch L;
+    L.kernel = add_kernel(src.str(), "row");
+    L.grid[0] = (unsigned)((Nk + per_block - 1) / per_block); L.grid[1] = L.grid[2] = 1;
+    L.block[0] = 256; L.block[1] = L.block[2] = 1;
+    L.outs = outs;
+    L.ins = ins;
+    if (outs.empty()) return;
+    add_launch(plan, L, label, st);
+  }
+
   // A large transpose that moves the innermost dimension, standing alone (or several of them concatenated along
   // dimension 0, what the weights of a decode loop become): moved by the tiled kernel that stages 32 x 32 (64 x 64)
   // tiles through shared memory, so that reads and writes are both whole lines. The index-rewriting form inside a
@@ -2433,9 +2818,83 @@ struct Planner {
       throw CompileError(msg);
     }
 
-    for (int ui : order) {
+    for (size_t oi = 0; oi < order.size(); oi++) {
+      const int ui = order[oi];
       Unit& u = units[ui];
       if (u.kind == Unit::GROUP) {
+        // a reduction over rows followed by kernels over the same rows: one launch for the chain
+        RowChain rc;
+        if (opts.fuse && !absorbed.count(u.group) && !getenv("B200_NO_ROW_FUSION") && row_form(u.group, rc)) {
+          std::set<Op*> members;
+          std::set<Value*> reduced, produced;
+          auto take = [&](Group* g) {
+            rc.stages.push_back(g);
+            members.insert(g->members.begin(), g->members.end());
+            const bool kept = g->is_reduce || g->roots[0]->results[0]->type.dims != rc.in_shape;
+            for (Op* r : g->roots)
+              for (Value* v : r->results) { produced.insert(v); if (kept) reduced.insert(v); }
+          };
+          if (row_safe(u.group, rc, u.group->members, reduced, st)) {
+            take(u.group);
+            // units that stand between the stages but read nothing of the chain (a constant, the scale vector of a
+            // norm) go out in front of it
+            std::vector<size_t> before;
+            size_t last_stage = oi, n_before_at_last = 0;
+            const bool dbg = getenv("B200_DEBUG_ROWS") != nullptr;
+            for (size_t oj = oi + 1; oj < order.size() && oj < oi + 16 && rc.stages.size() < 8; oj++) {
+              Unit& nu = units[order[oj]];
+              if (nu.kind == Unit::CONST_MAT) {
+                std::set<Value*> seen;
+                std::function<bool(Value*)> dep = [&](Value* v) -> bool {
+                  if (produced.count(v)) return true;
+                  if (!seen.insert(v).second || !v->def || v->def->parent != block || !is_dup(v->def)) return false;
+                  for (Value* o : v->def->operands) if (dep(o)) return true;
+                  return false;
+                };
+                bool d = false;
+                for (Value* o : nu.op->operands) d = d || dep(o);
+                if (d) break;
+                before.push_back(oj);
+                continue;
+              }
+              if (nu.kind != Unit::GROUP || absorbed.count(nu.group) || nu.group->roots.empty()) {
+                if (dbg) fprintf(stderr, "row chain stops: next unit is %s\n", nu.kind == Unit::GROUP ? "an absorbed or empty group" : nu.op->name.c_str());
+                break;
+              }
+              Group* g = nu.group;
+              if (g->roots.size() == 1 && window_updates.count(g->roots[0])) break;
+              if (!reads_any(g, produced, st)) { before.push_back(oj); continue; }
+              if (g->is_reduce) {
+                RowChain r2;
+                if (!row_form(g, r2) || r2.in_shape != rc.in_shape || r2.kept_shape != rc.kept_shape) {
+                  if (dbg) fprintf(stderr, "row chain stops: %s has another row form\n", group_label(g).c_str());
+                  break;
+                }
+              }
+              std::set<Op*> m2 = members;
+              m2.insert(g->members.begin(), g->members.end());
+              if (!row_safe(g, rc, m2, reduced, st)) {
+                if (dbg) fprintf(stderr, "row chain stops: %s is not row safe\n", group_label(g).c_str());
+                break;
+              }
+              take(g);
+              last_stage = oj;
+              n_before_at_last = before.size();
+            }
+            if (rc.stages.size() >= 2) {
+              before.resize(n_before_at_last);
+              for (size_t ob : before) {
+                Unit& bu = units[order[ob]];
+                if (bu.kind == Unit::CONST_MAT) materialize_dup(bu.op, plan, st);
+                else { emit_group(bu.group, plan, st); emitted.insert(bu.group); }
+              }
+              emit_row_chain(rc, plan, st);
+              for (Group* g : rc.stages) emitted.insert(g);
+              oi = last_stage;
+              continue;
+            }
+          }
+        }
         if (!absorbed.count(u.group)) emit_group(u.group, plan, st);
         emitted.insert(u.group);
         continue;

@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(256) gemv16_nc_kernel(const uint16_t* __restri
   extern __shared__ float gemv_smem[];
   float* a_s = gemv_smem;                              // [MAXM][kc_pad]
   const int kc_pad = p.kc + 8 * UNROLL;
-  float* red = a_s + MAXM * kc_pad;                    // [8][256]
+  float* red = a_s + MAXM * kc_pad;                    // [8 warps][MAXM][256]
   __shared__ int is_last;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int panel = blockIdx.x, sp = blockIdx.y, g = blockIdx.z;
@@ -460,20 +460,28 @@ __global__ void __launch_bounds__(256) gemv16_nc_kernel(const uint16_t* __restri
       }
     }
   }
-  const int nn = panel * 256 + tid;                    // the column this thread finishes
+  // the eight warps' sums of all M rows meet in shared memory at once: thread t finishes column t of every row
+  const int nn = panel * 256 + tid;
+  __syncthreads();
+#pragma unroll
+  for (int m = 0; m < MAXM; ++m)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[(warp * MAXM + m) * 256 + lane * 8 + j] = acc[m][j];
+  __syncthreads();
+  float fin[MAXM];
 #pragma unroll
   for (int m = 0; m < MAXM; ++m) {
-    if (m >= p.M) break;
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < 8; ++j) red[warp * 256 + lane * 8 + j] = acc[m][j];
-    __syncthreads();
     float s = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) s += red[w * 256 + tid];
-    if (nn < p.N) {
-      if (p.splits == 1) store_c(C, ((long long)g * p.M + m) * p.N + nn, s, p.c_kind);
-      else scratch[(((long long)g * p.splits + sp) * p.M + m) * p.N + nn] = s;
+    for (int w = 0; w < 8; ++w) s += red[(w * MAXM + m) * 256 + tid];
+    fin[m] = s;
+  }
+  if (nn < p.N) {
+#pragma unroll
+    for (int m = 0; m < MAXM; ++m) {
+      if (m >= p.M) break;
+      if (p.splits == 1) store_c(C, ((long long)g * p.M + m) * p.N + nn, fin[m], p.c_kind);
+      else scratch[(((long long)g * p.splits + sp) * p.M + m) * p.N + nn] = fin[m];
     }
   }
   if (p.splits == 1) return;
@@ -488,34 +496,47 @@ __global__ void __launch_bounds__(256) gemv16_nc_kernel(const uint16_t* __restri
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // warp w adds the splits w, w + 8, ... for the eight columns of each of its lanes (independent loads, several in
-  // flight), then the eight warps' sums are added in warp order: a fixed order whichever CTA came last
+  // The last CTA to arrive adds the splits: warp w takes the splits w, w + 8, ... for the eight columns of each of its
+  // lanes and every row (independent loads, several in flight), then the eight warps' sums are added in warp order: a
+  // fixed order whichever CTA came last.
   const bool vec4 = (p.N & 3) == 0;
-  for (int m = 0; m < p.M; ++m) {
-    float t[8];
+  float t[MAXM][8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) t[j] = 0.f;
-#pragma unroll 4
-    for (int q = warp; q < p.splits; q += 8) {
+  for (int m = 0; m < MAXM; ++m)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[m][j] = 0.f;
+#pragma unroll 2
+  for (int q = warp; q < p.splits; q += 8) {
+#pragma unroll
+    for (int m = 0; m < MAXM; ++m) {
+      if (m >= p.M) break;
       const float* src = scratch + (((long long)g * p.splits + q) * p.M + m) * p.N + n;
       if (vec4 && n + 8 <= p.N) {
         const float4 v0 = __ldcg(reinterpret_cast<const float4*>(src)), v1 = __ldcg(reinterpret_cast<const float4*>(src) + 1);
-        t[0] += v0.x; t[1] += v0.y; t[2] += v0.z; t[3] += v0.w;
-        t[4] += v1.x; t[5] += v1.y; t[6] += v1.z; t[7] += v1.w;
+        t[m][0] += v0.x; t[m][1] += v0.y; t[m][2] += v0.z; t[m][3] += v0.w;
+        t[m][4] += v1.x; t[m][5] += v1.y; t[m][6] += v1.z; t[m][7] += v1.w;
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          if (n + j < p.N) t[j] += __ldcg(src + j);
+          if (n + j < p.N) t[m][j] += __ldcg(src + j);
       }
     }
-    __syncthreads();
+  }
+  __syncthreads();
 #pragma unroll
-    for (int j = 0; j < 8; ++j) red[warp * 256 + lane * 8 + j] = t[j];
-    __syncthreads();
-    float s = 0.f;
+  for (int m = 0; m < MAXM; ++m)
 #pragma unroll
-    for (int w = 0; w < 8; ++w) s += red[w * 256 + tid];
-    if (nn < p.N) store_c(C, ((long long)g * p.M + m) * p.N + nn, s, p.c_kind);
+    for (int j = 0; j < 8; ++j) red[(warp * MAXM + m) * 256 + lane * 8 + j] = t[m][j];
+  __syncthreads();
+  if (nn < p.N) {
+#pragma unroll
+    for (int m = 0; m < MAXM; ++m) {
+      if (m >= p.M) break;
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) s += red[(w * MAXM + m) * 256 + tid];
+      store_c(C, ((long long)g * p.M + m) * p.N + nn, s, p.c_kind);
+    }
   }
 }
 
@@ -531,9 +552,17 @@ __global__ void __launch_bounds__(256) gemv16_kc_kernel(const uint16_t* __restri
   const int g = blockIdx.y;
   const uint16_t* Ag = A + (long long)g * p.a_gs;
   const uint16_t* Bg = B + (long long)g * p.b_gs;
-  for (int i = tid; i < p.M * p.K; i += 256) {
-    const int m = i / p.K, k = i % p.K;
-    a_s[i] = Ag[m * p.a_ms + (long long)k * p.a_ks];
+  if (p.a_ks == 1 && (p.a_ms & 7) == 0 && (p.a_gs & 7) == 0 && (((uintptr_t)A) & 15) == 0) {
+    const int chunks = p.K >> 3;                        // rows of A are whole 16-byte chunks (K % 8 == 0)
+    for (int i = tid; i < p.M * chunks; i += 256) {
+      const int m = i / chunks, c = i - m * chunks;
+      reinterpret_cast<uint4*>(a_s)[i] = *reinterpret_cast<const uint4*>(Ag + m * p.a_ms + 8 * c);
+    }
+  } else {
+    for (int i = tid; i < p.M * p.K; i += 256) {
+      const int m = i / p.K, k = i % p.K;
+      a_s[i] = Ag[m * p.a_ms + (long long)k * p.a_ks];
+    }
   }
   __syncthreads();
   // UNR chunks of 8 k per column are loaded before any is used: NW * UNR independent 16-byte loads in flight per lane
@@ -654,7 +683,7 @@ bool gemm16_plan(Gemm16Launch& g, bool aligned) {
       want = std::max<long long>(1, std::min<long long>(want, (g.K + 63) / 64));
       int kc = (int)((g.K + want - 1) / want);
       kc = (kc + 7) / 8 * 8;
-      kc = std::min(kc, 2048);                       // the K range's slice of A must fit shared memory (8 rows of fp32)
+      kc = std::min(kc, g.M == 1 ? 2048 : 512);      // the K range's slice of A (fp32) shares shared memory with the sums
       g.gemv_kc = kc;
       g.split_k = (g.K + kc - 1) / kc;
       if (g.split_k > 1) {
@@ -763,12 +792,12 @@ cudaError_t launch_gemm16(const Gemm16Launch& g, const void* A, const void* B, v
       dim3 grid((g.N + 255) / 256, g.split_k, g.G);
       static bool configured = false;
       if (!configured) {
-        cudaFuncSetAttribute(gemv16_nc_kernel<8, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * (2048 + 32) * 4 + 8192);
-        cudaFuncSetAttribute(gemv16_nc_kernel<8, false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * (2048 + 32) * 4 + 8192);
+        cudaFuncSetAttribute(gemv16_nc_kernel<8, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * (2048 + 32) * 4 + 65536);
+        cudaFuncSetAttribute(gemv16_nc_kernel<8, false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * (2048 + 32) * 4 + 65536);
         configured = true;
       }
       const int unroll = maxm == 1 ? 8 : 4;
-      const size_t smem = (size_t)maxm * (g.gemv_kc + 8 * unroll) * 4 + 8 * 256 * 4;
+      const size_t smem = (size_t)maxm * (g.gemv_kc + 8 * unroll) * 4 + (size_t)maxm * 8 * 256 * 4;
       if (maxm == 1 && bf16) gemv16_nc_kernel<1, true, 8><<<grid, 256, smem, stream>>>((const uint16_t*)A, (const uint16_t*)B, C, scratch, counters, p);
       else if (maxm == 1) gemv16_nc_kernel<1, false, 8><<<grid, 256, smem, stream>>>((const uint16_t*)A, (const uint16_t*)B, C, scratch, counters, p);
       else if (bf16) gemv16_nc_kernel<8, true, 4><<<grid, 256, smem, stream>>>((const uint16_t*)A, (const uint16_t*)B, C, scratch, counters, p);
