@@ -116,24 +116,65 @@ def cpu_twin_steps(steps: int, warmup: int, threads: int):
     return 1.0 / dt, dt * 1e3
 
 
+def extra_configs(client, hbm_gbs, tensor_tflops, which):
+    """The other single-GPU configurations of the benchmark, beside the headline: Gemma-2B-shaped greedy decoding
+    (tokens per second of the 128-step loop, bf16 weights resident in HBM; its roofline is the bytes of weights a
+    token has to read over the measured copy bandwidth) and the DistilBERT-base-shaped masked-LM step (bf16)."""
+    from b200 import bench_ops
+    out = {}
+    try:
+        g = bench_ops.gemma_decode(client, reps=3, hbm_gbs=hbm_gbs)
+        per_token = g["weight_bytes_per_token"]
+        ach = per_token / (g["ms_per_token"] * 1e-3) / 1e9
+        out["gemma_decode_tok_s"] = {
+            "value": g["tok_s"], "unit": "tokens/s (batch 1, greedy, 128 new tokens after a 512-token prompt)",
+            "ms_per_token": g["ms_per_token"], "decode_ms_all": g["decode_ms_all"], "prefill_ms": g["prefill_ms"],
+            "launches_per_token": g["launches_per_token"], "dtype": "bf16",
+            "config": {"workload": "gemma_2b_shaped_decode_18l_d2048_h8kv1_hd256_ffn16384_v256000_prompt512_new128"},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": hbm_gbs, "unit": "GB/s", "frac": ach / hbm_gbs, "traffic": None,
+                         "bytes_per_token": per_token, "peak_source": f"copy bandwidth, {which}",
+                         "note": "algorithmic bytes = every bf16 weight once per token (2 506 M parameters); the whole "
+                                 "token step is timed, not one kernel"}}
+    except Exception as e:
+        out["gemma_decode_tok_s"] = {"error": str(e)[:300]}
+    try:
+        d = bench_ops.distilbert_step(client, reps=5)
+        ach = d["tflops"]
+        out["distilbert_step_ms"] = {
+            "value": d["step_ms"], "unit": "ms per masked-LM step (batch 32 x 128 tokens, forward + backward)",
+            "step_ms_all": d["step_ms_all"], "launches": d["launches"], "dtype": "bf16", "loss": d["loss"],
+            "config": {"workload": "distilbert_base_shaped_mlm_step_6l_d768_h12_ffn3072_v30522_b32_s128"},
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": tensor_tflops, "unit": "TFLOP/s", "frac": ach / tensor_tflops,
+                         "traffic": None, "flop_per_step": d["flop"], "peak_source": f"bf16 sustained, {which}"}}
+    except Exception as e:
+        out["distilbert_step_ms"] = {"error": str(e)[:300]}
+    return out
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    steps = max(1, min(args.steps, 8))          # a CPU step takes around a second: keep the run bounded
-    warm = max(1, min(args.warmup, 2))
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    world = max(1, args.gpus)
     sps, ms = cpu_twin_steps(steps, warm, threads)
-    sample = f"{steps} steps after {warm} warm-up, batch {BATCH}, PyTorch-CPU twin, {threads} threads"
+    # The unit counts steps of one batch-128 shard. With N GPUs the job's step is a global batch of 128 * N, which this
+    # one host runs as N shard steps one after the other: its rate in shard steps per second is the same at every N
+    # (the timed sample is one shard's step), and a global step takes N times as long.
+    value = sps
+    sample = (f"{steps} steps after {warm} warm-up of one batch-{BATCH} shard, PyTorch-CPU twin, {threads} threads" +
+              (f"; a global step of {world} shards counted as {world} such steps" if world > 1 else ""))
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": sps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warm, "ms_per_step": ms * world, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": "resnet18_cifar_b128_fp32_sgd_momentum_train_step", "batch_per_gpu": BATCH,
-                   "global_batch": BATCH, "note": "CPU arm: the reference's Metal path cannot run on Linux and jaxlib "
+                   "global_batch": BATCH * world, "parallelism": f"dp{world}",
+                   "note": "CPU arm: the reference's Metal path cannot run on Linux and jaxlib "
                    "(its CPU comparison backend) is not installable here; PyTorch-CPU stand-in of the same step"},
-        "cpu_baseline": {"value": sps, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": sps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
@@ -189,29 +230,48 @@ def run_b200(args):
         outs = exe.execute(state + xy)
         state = outs[1:]
     barrier()
-    launches0 = client.launch_count()
     t_begin = time.perf_counter()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        ev0.record()
-    for _ in range(args.steps):
-        outs = exe.execute(state + xy)
-        state = outs[1:]
-    with torch.cuda.stream(stream):
-        ev1.record()
-    barrier()
-    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
-    launches = client.launch_count() - launches0
+    # the timed region (exactly `steps` steps between two events on the launching stream, a barrier on both sides)
+    # is repeated; the reported figure is the median repeat, every repeat is listed
+    repeats_ms, own_ms = [], []
+    for rep in range(max(1, args.repeats)):
+        launches0 = client.launch_count()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            ev0.record()
+        for _ in range(args.steps):
+            outs = exe.execute(state + xy)
+            state = outs[1:]
+        with torch.cuda.stream(stream):
+            ev1.record()
+        barrier()
+        own_ms.append(ev0.elapsed_time(ev1))
+        repeats_ms.append(max_over_ranks(own_ms[-1]))
+        launches = client.launch_count() - launches0
+    ms_total = statistics.median(repeats_ms)
     loss = float(outs[0].to_numpy())
+    # replicas must agree: every rank holds the same parameter bits after the same number of steps
+    consistency = None
+    if world > 1:
+        import hashlib
+        h = hashlib.sha256()
+        for buf in state[:8] + state[n_state // 2 - 4:n_state // 2]:
+            h.update(buf.to_numpy().tobytes())
+        digests = [None] * world
+        dist.all_gather_object(digests, (h.hexdigest(), loss, statistics.median(own_ms)))
+        if len({d[0] for d in digests}) != 1 or len({d[1] for d in digests}) != 1:
+            raise SystemExit(f"replicas diverged: {digests}")
+        consistency = {"replicas_bit_identical": True, "leaves_hashed": 12, "loss_identical": True,
+                       "rank_ms_per_step": [round(d[2] / args.steps, 4) for d in digests]}
     # A short timed region (30 steps are 0.16 s) can end before nvidia-smi has reported a few times: every rank then
     # keeps running the same steps, untimed, until 0.6 s of load have passed since the region began, and the
     # sampling window covers them too (ms_total is the maximum over ranks, so all ranks run the same count).
-    window = "timed region"
-    if ms_total < 600.0:
-        for _ in range(int((600.0 - ms_total) / (ms_total / args.steps)) + 1):
+    window = "all repeats of the timed region"
+    if sum(repeats_ms) < 600.0:
+        for _ in range(int((600.0 - sum(repeats_ms)) / (ms_total / args.steps)) + 1):
             o2 = exe.execute(state + xy)
             state = o2[1:]
-        window = "timed region and further identical steps, untimed, up to 0.6 s of load"
+        window = "all repeats of the timed region and further identical steps, untimed, up to 0.6 s of load"
     barrier()
     clocks = None
     if rank == 0:
@@ -270,10 +330,20 @@ def run_b200(args):
     dom_n = sum(r["count"] for r in dom)
     dom_flop = 2.0 * 131072 * 64 * 576
     achieved = dom_flop * dom_n / (dom_ms * 1e-3) / 1e12 if dom_ms else 0.0
+    try:
+        tf32_rate = client.probe_tf32_mma_rate()
+    except Exception as e:          # the probe is an aid, not part of the measurement
+        tf32_rate = None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": tens, "unit": "TFLOP/s", "frac": achieved / tens,
-                # DRAM bytes of one such launch from the ncu capture summarised in profiles/ (input 33.6 MB read once,
-                # the 33.6 MB output still in L2 when the kernel ends); algorithmic bytes are 67.3 MB
+                # DRAM bytes of one such launch (input 33.6 MB read once, the 33.6 MB output still in L2 when the kernel
+                # ends); algorithmic bytes are 67.3 MB
                 "traffic": 37.6e6,
+                "traffic_source": "ncu capture of this kernel on this shape, profiles/igemm_tf32x3_ta_kernel_conv3x3_stage1_stage3.md "
+                                  "(dram__bytes_read.sum + dram__bytes_write.sum per launch); not re-measured by this run",
+                "own_ceiling": {"tf32_mma_tflops": tf32_rate, "fp32_accurate_tflops": tf32_rate / 3.0 if tf32_rate else None,
+                                "frac": achieved / (tf32_rate / 3.0) if tf32_rate else None,
+                                "how": "tcgen05.mma.kind::tf32 issue loop, one CTA per SM, measured in this run; the kernel "
+                                       "issues three such MMAs per fp32 product"},
                 "kernel": "igemm_tf32x3_ta_kernel<64,...> on M=131072 N=64 K=576 (stage-1 3x3 convolutions, forward "
                           "and input gradient), algorithmic fp32 flop 2*M*N*K per launch",
                 "launches_per_step": dom_n // psteps, "us_per_launch": 1e3 * dom_ms / max(dom_n, 1),
@@ -283,6 +353,34 @@ def run_b200(args):
                                      "flop_per_step": FLOP_PER_STEP},
                 "ms_per_step_by_kind": {k: round(v["ms"], 4) for k, v in by_kind.items()},
                 "launches_by_kind": {k: v["count"] for k, v in by_kind.items()}}
+
+    # ---- strong scaling: a global batch of 1024 split over the GPUs (an extra key beside the weak-scaling headline) ----
+    strong = None
+    if args.strong:
+        per = 1024 // world
+        sprog = programs.resnet18_train_step(batch=per, n_partitions=world)
+        sargs = programs.resnet18_inputs(sprog, seed_w=0, seed_x=1, rank=rank)
+        sexe = client.compile(sprog.text)
+        sb = [client.buffer_from_host(a) for a in sargs]
+        sstate, sxy = sb[:len(sargs) - 2], sb[len(sargs) - 2:]
+        for _ in range(3):
+            o = sexe.execute(sstate + sxy)
+            sstate = o[1:]
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record()
+        ssteps = max(5, args.steps // 2)
+        for _ in range(ssteps):
+            o = sexe.execute(sstate + sxy)
+            sstate = o[1:]
+        with torch.cuda.stream(stream):
+            e1.record()
+        barrier()
+        sms = max_over_ranks(e0.elapsed_time(e1)) / ssteps
+        strong = {"global_batch": 1024, "batch_per_gpu": per, "ms_per_step": sms, "steps_per_s": 1e3 / sms,
+                  "images_per_s": 1024 * 1e3 / sms, "steps": ssteps}
+        del sb, sstate, sxy, o
 
     if rank != 0:
         if world > 1:
@@ -309,7 +407,15 @@ def run_b200(args):
                 "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": int(launches), "launches_per_step": exe.launches_per_execute,
         "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "final_loss": loss,
+        "repeats": {"count": len(repeats_ms), "ms_per_step_all": [round(m / args.steps, 4) for m in repeats_ms],
+                    "reported": "median"},
+        "comm_ms_per_step": by_kind.get("all_reduce", {}).get("ms") if world > 1 else 0.0,
+        "replica_consistency": consistency,
     }
+    if strong is not None:
+        line["strong_scaling"] = strong
+    if world == 1 and not args.no_extras:
+        line.update(extra_configs(client, hbm, tens, which))
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -322,6 +428,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--repeats", type=int, default=5, help="repeats of the timed region; the median is reported")
+    ap.add_argument("--no-extras", action="store_true", help="skip the Gemma decode and DistilBERT extra keys (N = 1)")
+    ap.add_argument("--no-strong", dest="strong", action="store_false", help="skip the strong-scaling extra measurement")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

@@ -205,6 +205,11 @@ void* b200_client_compute_stream(b200_client* client);
  * {"kind","key","ms","count"} accumulated since the last report (release with b200_string_free). */
 b200_error* b200_client_set_profiling(b200_client* client, int enabled);
 b200_error* b200_client_profile_report(b200_client* client, char** json);
+/* Measures the rate of tcgen05.mma.kind::tf32 on the client's device (TFLOP/s; issue loop alone, operands resident in
+ * shared memory). The fp32-accurate contraction kernels issue three such MMAs per product: their ceiling is a third of
+ * this figure. A measurement aid with no counterpart in the reference (its numbers come from MPS_PROFILE,
+ * src/pjrt_plugin/mlx_executable.cc:381-454). */
+b200_error* b200_client_probe_tf32_mma_rate(b200_client* client, double* tflops);
 /* Total kernels launched by this client since creation (generated + static + collectives). */
 int64_t b200_client_launch_count(const b200_client* client);
 

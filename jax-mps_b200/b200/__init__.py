@@ -125,6 +125,7 @@ SIGNATURES = {
     "b200_client_synchronize": (_P, [_P]),
     "b200_client_compute_stream": (_P, [_P]),
     "b200_client_launch_count": (C.c_int64, [_P]),
+    "b200_client_probe_tf32_mma_rate": (_P, [_P, C.POINTER(C.c_double)]),
     "b200_client_set_profiling": (_P, [_P, C.c_int]),
     "b200_client_profile_report": (_P, [_P, C.POINTER(_P)]),
     "b200_matmul_f32_static_scratch": (_P, [_P, _P, _P, C.c_int64, C.c_int64, C.c_int64, _P]),
@@ -437,6 +438,12 @@ class Client:
         txt = C.string_at(out.value).decode()
         lib.b200_string_free(out)
         return json.loads(txt)
+
+    def probe_tf32_mma_rate(self) -> float:
+        """TFLOP/s of the TF32 tensor-core MMA on this device (issue loop alone); the 3xTF32 fp32 path tops out at a third."""
+        out = C.c_double(0.0)
+        _check(load_library().b200_client_probe_tf32_mma_rate(self._h, C.byref(out)))
+        return out.value
 
     def launch_count(self) -> int:
         return load_library().b200_client_launch_count(self._h)

@@ -1648,6 +1648,79 @@ cudaError_t matmul_f32_static_scratch(const float* A, const float* B, float* C, 
   return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------
+// Probe: the rate at which the tensor cores retire tcgen05.mma.kind::tf32 on this GPU, measured with the issue loop
+// alone (operands resident in shared memory, nothing to load): the ceiling of the three-MMA fp32-accurate scheme is a
+// third of it. One CTA per SM, 128 x 128 x 8 MMAs, `iters` groups of 12 per CTA.
+namespace {
+__global__ void __launch_bounds__(128, 1) tf32_mma_rate_kernel(int iters, int* __restrict__ error_flag) {
+  extern __shared__ uint8_t probe_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)probe_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t bars[2];
+  __shared__ uint32_t tmem_slot;
+  constexpr int A_BYTES = 128 * 32 * 4, B_BYTES = 128 * 32 * 4;
+  const int tid = threadIdx.x;
+  float* f = (float*)smem;
+  for (int i = tid; i < (A_BYTES + B_BYTES) / 4; i += 128) f[i] = 1.0f + (i % 7) * 0.125f;
+  if (tid == 0) {
+    mbar_init(smem_u32(&bars[0]), 1);
+    mbar_init(smem_u32(&bars[1]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (tid < 32) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(128) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_slot;
+  if (tid == 0) {
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    const uint64_t d_a = umma_desc(smem_u32(smem)), d_b = umma_desc(smem_u32(smem) + A_BYTES);
+    for (int j = 0; j < iters; ++j) {
+#pragma unroll
+      for (int q = 0; q < 12; ++q) umma_tf32(tmem, d_a + (uint64_t)((q & 3) * 2), d_b + (uint64_t)((q & 3) * 2), idesc, (j | q) != 0);
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[j == iters - 1]))
+                   : "memory");
+    }
+    if (!mbar_wait(smem_u32(&bars[1]), 0)) atomicExch(error_flag, 1);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (tid < 32) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128) : "memory");
+}
+}  // namespace
+
+cudaError_t probe_tf32_mma_rate(int* error_flag, cudaStream_t stream, double* tflops) {
+  *tflops = 0.0;
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return e;
+  constexpr int SMEM = 2 * 128 * 32 * 4 + 1024;
+  e = cudaFuncSetAttribute(tf32_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  if (e != cudaSuccess) return e;
+  cudaEvent_t a, b;
+  cudaEventCreate(&a);
+  cudaEventCreate(&b);
+  const int iters = 4000;
+  tf32_mma_rate_kernel<<<sms, 128, SMEM, stream>>>(100, error_flag);
+  cudaEventRecord(a, stream);
+  tf32_mma_rate_kernel<<<sms, 128, SMEM, stream>>>(iters, error_flag);
+  cudaEventRecord(b, stream);
+  e = cudaStreamSynchronize(stream);
+  float ms = 0.f;
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, a, b);
+  cudaEventDestroy(a);
+  cudaEventDestroy(b);
+  if (e != cudaSuccess) return e;
+  *tflops = 2.0 * 128 * 128 * 8 * 12.0 * iters * sms / (ms * 1e-3) / 1e12;
+  return cudaGetLastError();
+}
+
 cudaError_t launch_scatter_rows(int elem_kind, int index_bytes, int kind, long long rows, long long row_elems, int updates,
                                 void* out, const void* indices, const void* upd, int* scratch, cudaStream_t stream,
                                 int* launches) {

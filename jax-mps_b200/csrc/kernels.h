@@ -46,6 +46,10 @@ cudaError_t launch_scatter_rows(int elem_kind, int index_bytes, int kind, long l
 cudaError_t matmul_f32_static_scratch(const float* A, const float* B, float* C, int M, int N, int K, cudaStream_t stream,
                                       const char** why);
 size_t static_scratch_bytes();
+
+// TFLOP/s of tcgen05.mma.kind::tf32 (128 x 128 x 8, one CTA per SM, operands resident in shared memory) measured on
+// the current device: the fp32-accurate contraction issues three of these per product, so its ceiling is a third.
+cudaError_t probe_tf32_mma_rate(int* error_flag, cudaStream_t stream, double* tflops);
 }  // namespace b200
 
 namespace b200 {

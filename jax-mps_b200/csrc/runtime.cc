@@ -1608,6 +1608,15 @@ b200_error* b200_event_destroy(b200_event* e) {
   return nullptr;
 }
 
+b200_error* b200_client_probe_tf32_mma_rate(b200_client* c, double* tflops) {
+  if (!c || !tflops) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  if (auto* e = set_device(c)) return e;
+  cudaError_t e = b200::probe_tf32_mma_rate(c->error_flag, c->compute, tflops);
+  if (e != cudaSuccess) return make_error(B200_INTERNAL, std::string("tensor-core rate probe failed: ") + cudaGetErrorString(e));
+  return nullptr;
+}
+
 b200_error* b200_matmul_f32_static_scratch(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                                            void* cuda_stream) {
   if (!a || !b || !c) return make_error(B200_INVALID_ARGUMENT, "null operand pointer");
