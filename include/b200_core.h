@@ -177,11 +177,14 @@ void* b200_buffer_device_pointer(const b200_buffer* buffer);
 /* ---- execute: PJRT_LoadedExecutable_Execute (pjrt_executable.cc:178-258) ---- */
 typedef struct {
   size_t struct_size;
-  int donate_arguments;      /* honour tf.aliasing_output: a donated argument's storage becomes the result
-                                and the argument buffer is left deleted */
+  int donate_arguments;      /* honour tf.aliasing_output: a donated argument is consumed. Its buffer is left deleted
+                                and its memory returns to the stream-ordered pool behind this execution; results
+                                are fresh allocations (they never share storage with an argument) */
 } b200_execute_options;
 /* `outputs` is a caller-allocated array of b200_executable_num_outputs pointers. `done` (may be NULL)
- * becomes ready when all outputs are computed. The call returns after enqueueing. The outputs of one call share
+ * becomes ready when all outputs are computed. The call returns after enqueueing. Device-side waits are bounded: if
+ * one runs out during the execution, b200_event_await / _error / _on_ready of `done`, and of the events of reads of
+ * its outputs (b200_buffer_to_host, b200_buffer_ready_event), report B200_INTERNAL once the work has finished. The outputs of one call share
  * two device allocations (small and large results); each is deleted on its own and a shared allocation is
  * released with its last output. */
 b200_error* b200_executable_execute(b200_executable* exe, b200_buffer* const* args, size_t num_args,
@@ -205,6 +208,10 @@ void* b200_client_compute_stream(b200_client* client);
  * {"kind","key","ms","count"} accumulated since the last report (release with b200_string_free). */
 b200_error* b200_client_set_profiling(b200_client* client, int enabled);
 b200_error* b200_client_profile_report(b200_client* client, char** json);
+/* Test hook: the next execution on this client starts with a kernel that waits, with a budget of `polls` polls, on a
+ * barrier nothing arrives at. The wait runs out (nothing hangs, nothing faults) and the execution reports the failure
+ * the way an expired tensor-core pipeline wait does. No counterpart in the reference. */
+b200_error* b200_client_debug_arm_wait_expiry(b200_client* client, int polls);
 /* Measures the rate of tcgen05.mma.kind::tf32 on the client's device (TFLOP/s; issue loop alone, operands resident in
  * shared memory). The fp32-accurate contraction kernels issue three such MMAs per product: their ceiling is a third of
  * this figure. A measurement aid with no counterpart in the reference (its numbers come from MPS_PROFILE,

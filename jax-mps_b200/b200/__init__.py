@@ -126,6 +126,7 @@ SIGNATURES = {
     "b200_client_compute_stream": (_P, [_P]),
     "b200_client_launch_count": (C.c_int64, [_P]),
     "b200_client_probe_tf32_mma_rate": (_P, [_P, C.POINTER(C.c_double)]),
+    "b200_client_debug_arm_wait_expiry": (_P, [_P, C.c_int]),
     "b200_client_set_profiling": (_P, [_P, C.c_int]),
     "b200_client_profile_report": (_P, [_P, C.POINTER(_P)]),
     "b200_matmul_f32_static_scratch": (_P, [_P, _P, _P, C.c_int64, C.c_int64, C.c_int64, _P]),
@@ -203,6 +204,28 @@ class Event:
 
     def wait(self):
         _check(load_library().b200_event_await(self._h))
+
+    def error(self):
+        """None, or the B200Error the event completed with (PJRT_Event_Error)."""
+        try:
+            _check(load_library().b200_event_error(self._h))
+        except B200Error as e:
+            return e
+        return None
+
+    def on_ready(self, fn):
+        """Calls fn(error_or_None) on the completion thread once the event is ready (PJRT_Event_OnReady). The event
+        must stay alive until the callback has run."""
+        lib = load_library()
+
+        def tramp(err, _arg):
+            exc = None
+            if err:
+                exc = B200Error(lib.b200_error_message(err).decode(), lib.b200_error_get_code(err))
+                lib.b200_error_destroy(err)
+            fn(exc)
+        self._cb = EVENT_CALLBACK(tramp)              # keep the trampoline alive with the event
+        _check(lib.b200_event_on_ready(self._h, self._cb, None))
 
     def __del__(self):
         if getattr(self, "_h", None):
@@ -322,15 +345,18 @@ class Executable:
         _check(load_library().b200_executable_output_info(self._h, i, C.byref(dt), C.byref(dims), C.byref(nd)))
         return _DT_NAMES[dt.value], tuple(int(dims[k]) for k in range(nd.value))
 
-    def execute(self, args, donate: bool = False) -> list:
-        """Enqueue one execution; returns the output buffers without waiting."""
+    def execute(self, args, donate: bool = False, with_event: bool = False):
+        """Enqueue one execution; returns the output buffers without waiting (with `with_event`: the buffers and the
+        completion event of the execution)."""
         lib = load_library()
         n = len(args)
         arr = (_P * max(n, 1))(*[a._h for a in args])
         outs = (_P * max(self.num_outputs, 1))()
         opts = _ExecuteOptions(C.sizeof(_ExecuteOptions), 1 if donate else 0)
-        _check(lib.b200_executable_execute(self._h, arr, n, outs, None, C.byref(opts)))
-        return [Buffer(self.client, outs[k]) for k in range(self.num_outputs)]
+        done = _P()
+        _check(lib.b200_executable_execute(self._h, arr, n, outs, C.byref(done) if with_event else None, C.byref(opts)))
+        bufs = [Buffer(self.client, outs[k]) for k in range(self.num_outputs)]
+        return (bufs, Event(done.value)) if with_event else bufs
 
     def __call__(self, *arrays):
         bufs = [a if isinstance(a, Buffer) else self.client.buffer_from_host(a) for a in arrays]
@@ -438,6 +464,10 @@ class Client:
         txt = C.string_at(out.value).decode()
         lib.b200_string_free(out)
         return json.loads(txt)
+
+    def debug_arm_wait_expiry(self, polls: int = 1000):
+        """Test hook: the next execution starts with a bounded device-side wait that runs out."""
+        _check(load_library().b200_client_debug_arm_wait_expiry(self._h, polls))
 
     def probe_tf32_mma_rate(self) -> float:
         """TFLOP/s of the TF32 tensor-core MMA on this device (issue loop alone); the 3xTF32 fp32 path tops out at a third."""

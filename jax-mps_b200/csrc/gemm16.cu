@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm16_tma_kernel(const __grid_c
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (tid == 0 && *failed) atomicExch(error_flag, 1);
+  if (tid == 0 && *failed) atomicAdd(error_flag, 1);
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::TMEM_COLS) : "memory");
   }

@@ -519,7 +519,7 @@ __global__ void __launch_bounds__(TNT, 2) igemm_tf32x3_kernel(const float* __res
   ok = __syncthreads_and(ok);
   if (!ok && tid == 0) {
     *failed = 1;
-    atomicExch(error_flag, 1);
+    atomicAdd(error_flag, 1);
   }
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
@@ -996,7 +996,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
                           smem_u32(done), 0u);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (tid == 0 && *failed) atomicExch(error_flag, 1);
+  if (tid == 0 && *failed) atomicAdd(error_flag, 1);
   if (warp == MMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
   }
@@ -1329,7 +1329,7 @@ __global__ void __launch_bounds__((TaCfg<BN, HALF>::THREADS), (HALF ? 2 : 1)) ig
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (tid == 0 && *failed) atomicExch(error_flag, 1);
+  if (tid == 0 && *failed) atomicAdd(error_flag, 1);
   if (warp == MMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::TMEM_COLS) : "memory");
   }
@@ -1685,13 +1685,44 @@ __global__ void __launch_bounds__(128, 1) tf32_mma_rate_kernel(int iters, int* _
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[j == iters - 1]))
                    : "memory");
     }
-    if (!mbar_wait(smem_u32(&bars[1]), 0)) atomicExch(error_flag, 1);
+    if (!mbar_wait(smem_u32(&bars[1]), 0)) atomicAdd(error_flag, 1);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (tid < 32) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128) : "memory");
 }
 }  // namespace
+
+namespace {
+// Test hook: a wait on an mbarrier that nothing ever arrives at, with a small poll budget. It runs out, and the
+// kernel reports it exactly as the tensor-core kernels report an expired pipeline wait: it counts up the error word
+// and returns. Nothing hangs and nothing faults.
+__global__ void expiring_wait_kernel(int polls, int* __restrict__ error_flag) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    bool done = false;
+    for (int spin = 0; spin < polls && !done; ++spin) {
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(smem_u32(&bar)), "r"(0u)
+          : "memory");
+      done = ok != 0;
+    }
+    if (!done) atomicAdd(error_flag, 1);
+  }
+}
+}  // namespace
+
+cudaError_t launch_expiring_wait(int polls, int* error_flag, cudaStream_t stream) {
+  expiring_wait_kernel<<<1, 32, 0, stream>>>(polls < 1 ? 1 : polls, error_flag);
+  return cudaGetLastError();
+}
 
 cudaError_t probe_tf32_mma_rate(int* error_flag, cudaStream_t stream, double* tflops) {
   *tflops = 0.0;

@@ -23,7 +23,7 @@ struct IGemmLaunch {
 
 // tables: a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp (device pointers).
 // `partial` is the split-K scratch ([split_k][groups][M][N] floats) or null when split_k == 1.
-// `error_flag` (device int) is set by the tensor-core kernel when one of its bounded waits expires.
+// `error_flag` (device int) is counted up by the tensor-core kernel when one of its bounded waits expires.
 // Adds the number of kernels launched to *launches.
 // `kt_table` (device, may be null): per 128-row tile of M, [count, k-tile indices...] with row length 1 + kt_stride;
 // k-tiles outside the list contribute nothing (their rows all fall on padding or dilation holes) and are skipped.
@@ -46,6 +46,9 @@ cudaError_t launch_scatter_rows(int elem_kind, int index_bytes, int kind, long l
 cudaError_t matmul_f32_static_scratch(const float* A, const float* B, float* C, int M, int N, int K, cudaStream_t stream,
                                       const char** why);
 size_t static_scratch_bytes();
+
+// Test hook: one kernel whose bounded mbarrier wait (budget `polls`) runs out and counts up *error_flag.
+cudaError_t launch_expiring_wait(int polls, int* error_flag, cudaStream_t stream);
 
 // TFLOP/s of tcgen05.mma.kind::tf32 (128 x 128 x 8, one CTA per SM, operands resident in shared memory) measured on
 // the current device: the fp32-accurate contraction issues three of these per product, so its ceiling is a third.

@@ -258,9 +258,20 @@ Completion& completion() {
 
 }  // namespace
 
+// Error counter of the device as one execution saw it: the word before its first kernel and after its last, copied
+// into pinned memory on the compute stream. The execution failed (a bounded device-side wait ran out) when the two
+// differ once the copies have landed.
+struct ExecStatus {
+  volatile int* pair = nullptr;   // pinned: [0] before, [1] after
+  std::function<void(volatile int*)> release;
+  ~ExecStatus() { if (release && pair) release(pair); }
+  bool failed() const { return pair && pair[1] != pair[0]; }
+};
+
 struct b200_event {
   cudaEvent_t ev = nullptr;       // null: ready at creation
   int device = 0;
+  std::shared_ptr<ExecStatus> status;   // set on events of an execution and of reads of its results
   std::string error;              // non-empty: the event completed with an error
   b200_error_code code = B200_OK;
   ~b200_event() {
@@ -313,6 +324,11 @@ struct b200_client {
   int* error_flag = nullptr;            // device word raised by kernels whose bounded waits expire
   bool tensor_cores = true;
   bool profiling = false;
+  int reported_errors = 0;              // value of the error word at the last b200_client_synchronize
+  int armed_wait_polls = 0;             // test hook: the next execution starts with a wait that runs out
+  int* status_block = nullptr;          // pinned pairs handed to executions
+  std::vector<int> free_status;         // free pair indices
+  static constexpr int kStatusPairs = 4096;
   struct ProfEntry { std::string kind; double ms = 0; long long count = 0; };
   std::map<std::string, ProfEntry> profile;
   int64_t total_mem = 0;
@@ -330,6 +346,7 @@ struct b200_client {
 
 struct b200_buffer {
   b200_client* client = nullptr;
+  std::shared_ptr<ExecStatus> status;          // the execution that produced this buffer
   void* ptr = nullptr;
   size_t bytes = 0;
   b200_dtype dtype = B200_INVALID;
@@ -951,6 +968,9 @@ b200_error* b200_client_create(const b200_client_options* o, b200_client** out) 
   CUDA_TRY(cudaMallocHost((void**)&c->pred_host, 64));
   CUDA_TRY(cudaMalloc((void**)&c->error_flag, sizeof(int)));
   CUDA_TRY(cudaMemset(c->error_flag, 0, sizeof(int)));
+  CUDA_TRY(cudaMallocHost((void**)&c->status_block, 2 * sizeof(int) * b200_client::kStatusPairs));
+  memset(c->status_block, 0, 2 * sizeof(int) * b200_client::kStatusPairs);
+  for (int k = b200_client::kStatusPairs - 1; k >= 0; k--) c->free_status.push_back(k);
   if (const char* e2 = getenv("B200_NO_TENSOR_CORES")) c->tensor_cores = atoi(e2) == 0;
   if (!driver().ok) return make_error(B200_FAILED_PRECONDITION, driver().error);
   if (c->nprocs > 1) {
@@ -984,6 +1004,7 @@ b200_error* b200_client_destroy(b200_client* c) {
     cudaEventDestroy(b.ev);
   }
   if (c->pred_host) cudaFreeHost(c->pred_host);
+  if (c->status_block) cudaFreeHost(c->status_block);
   if (c->error_flag) cudaFree(c->error_flag);
   if (c->coll) cudaStreamDestroy(c->coll);
   if (c->coll_ready) cudaEventDestroy(c->coll_ready);
@@ -1057,8 +1078,9 @@ b200_error* b200_client_synchronize(b200_client* c) {
   CUDA_TRY(cudaStreamSynchronize(c->d2h));
   int flag = 0;
   CUDA_TRY(cudaMemcpy(&flag, c->error_flag, sizeof(int), cudaMemcpyDeviceToHost));
-  if (flag) {
-    cudaMemset(c->error_flag, 0, sizeof(int));
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  if (flag != c->reported_errors) {
+    c->reported_errors = flag;
     return make_error(B200_INTERNAL, "a kernel gave up on a bounded wait (tensor-core pipeline did not complete); "
                                      "results of the affected execution are invalid");
   }
@@ -1334,8 +1356,11 @@ b200_error* b200_buffer_to_host(b200_buffer* b, void* dst, size_t* dst_size, b20
     b200_error* err = nullptr;
     *event = new_event_on(c, c->d2h, &err);
     if (err) return err;
+    (*event)->status = b->status;
   } else {
     CUDA_TRY(cudaStreamSynchronize(c->d2h));
+    if (b->status && b->status->failed())
+      return make_error(B200_INTERNAL, "the execution that produced this buffer gave up on a bounded device-side wait; its results are invalid");
   }
   return nullptr;
 }
@@ -1358,6 +1383,7 @@ b200_error* b200_buffer_ready_event(b200_buffer* b, b200_event** event) {
   CUDA_TRY(cudaStreamWaitEvent(c->d2h, b->ready, 0));
   b200_error* err = nullptr;
   *event = new_event_on(c, c->d2h, &err);
+  if (*event) (*event)->status = b->status;
   return err;
 }
 
@@ -1451,23 +1477,35 @@ b200_error* b200_executable_execute(b200_executable* exe, b200_buffer* const* ar
   for (size_t k = 0; k < num_args; k++)
     if (args[k]->ready_on != c->compute) CUDA_TRY(cudaStreamWaitEvent(c->compute, args[k]->ready, 0));
   std::vector<std::unique_ptr<b200_buffer>> outs(p.results.size());
-  std::vector<int> donated_from(p.results.size(), -1);
+  // Donation (tf.aliasing_output on an argument): the argument is consumed. Its buffer is left deleted and its memory
+  // goes back to the stream-ordered pool behind this execution, where the next allocation of the stream finds it; the
+  // results themselves are fresh allocations (the kernels are free to write a result before they have read all of
+  // the argument, so the two never share storage).
   std::vector<bool> arg_taken(num_args, false);
+  // the error counter as this execution sees it before its first and after its last kernel
+  auto status = std::make_shared<ExecStatus>();
+  if (!c->free_status.empty()) {
+    const int slot = c->free_status.back();
+    c->free_status.pop_back();
+    status->pair = c->status_block + 2 * slot;
+    status->pair[0] = status->pair[1] = 0;
+    status->release = [c, slot](volatile int*) { std::lock_guard<std::recursive_mutex> l(c->mu); c->free_status.push_back(slot); };
+    CUDA_TRY(cudaMemcpyAsync((void*)&status->pair[0], c->error_flag, sizeof(int), cudaMemcpyDeviceToHost, c->compute));
+  }
+  if (c->armed_wait_polls > 0) {
+    cudaError_t he = b200::launch_expiring_wait(c->armed_wait_polls, c->error_flag, c->compute);
+    c->armed_wait_polls = 0;
+    if (he != cudaSuccess) return make_error(B200_INTERNAL, std::string("test hook launch failed: ") + cudaGetErrorString(he));
+  }
   for (size_t k = 0; k < p.results.size(); k++) {
     auto b = std::make_unique<b200_buffer>();
     b->client = c;
     b->dtype = to_api(p.results[k].type.dt);
     b->dims = p.results[k].type.dims;
     b->bytes = p.results[k].type.bytes();
+    b->status = status;
     int da = p.results[k].donated_arg;
-    if (donate && da >= 0 && (size_t)da < num_args && !arg_taken[da] && args[da]->bytes == b->bytes &&
-        args[da]->reads.empty()) {
-      // the result takes over the argument's storage; fused kernels read element i before writing
-      // element i, so in-place reuse is safe only for results written by such kernels: restrict to
-      // same-shape elementwise updates, which is what optimizer steps produce
-      arg_taken[da] = true;
-      donated_from[k] = da;
-    }
+    if (donate && da >= 0 && (size_t)da < num_args) arg_taken[da] = true;
     outs[k] = std::move(b);
   }
   // Results come out of two allocations per execution instead of one each: one block for the small results (under
@@ -1551,10 +1589,13 @@ b200_error* b200_executable_execute(b200_executable* exe, b200_buffer* const* ar
     for (size_t k = 0; k < num_args; k++)
       if (arg_taken[k]) b200_buffer_delete(args[k]);
   }
+  if (status->pair)
+    CUDA_TRY(cudaMemcpyAsync((void*)&status->pair[1], c->error_flag, sizeof(int), cudaMemcpyDeviceToHost, c->compute));
   if (done) {
     b200_error* e2 = nullptr;
     *done = new_event_on(c, c->compute, &e2);
     if (e2) return e2;
+    (*done)->status = status;
   }
   for (size_t k = 0; k < outs.size(); k++) outputs[k] = outs[k].release();
   return nullptr;
@@ -1579,7 +1620,12 @@ b200_error* b200_event_await(b200_event* e) {
 }
 
 b200_error* b200_event_error(b200_event* e) {
-  if (!e || e->error.empty()) return nullptr;
+  if (!e) return nullptr;
+  if (e->error.empty() && e->status && e->status->failed() && (!e->ev || cudaEventQuery(e->ev) == cudaSuccess)) {
+    e->error = "the execution gave up on a bounded device-side wait (a tensor-core pipeline did not complete); its results are invalid";
+    e->code = B200_INTERNAL;
+  }
+  if (e->error.empty()) return nullptr;
   return make_error(e->code, e->error);
 }
 
@@ -1591,13 +1637,16 @@ b200_error* b200_event_on_ready(b200_event* e, b200_event_callback cb, void* use
   }
   cudaEvent_t ev = e->ev;
   int dev = e->device;
+  std::shared_ptr<ExecStatus> status = e->status;
   // The waiter needs its own handle on completion: record-independent wait through a second event
   // is not possible, so the callback thread synchronises on the same CUDA event; destroying the
   // b200_event before the callback fired is therefore not allowed (same rule as PJRT).
-  completion().post([ev, dev, cb, user_arg] {
+  completion().post([ev, dev, cb, user_arg, status] {
     cudaSetDevice(dev);
     cudaError_t r = cudaEventSynchronize(ev);
     b200_error* err = r == cudaSuccess ? nullptr : make_error(B200_INTERNAL, std::string("device work failed: ") + cudaGetErrorString(r));
+    if (!err && status && status->failed())
+      err = make_error(B200_INTERNAL, "the execution gave up on a bounded device-side wait; its results are invalid");
     cb(err, user_arg);
   });
   return nullptr;
@@ -1605,6 +1654,13 @@ b200_error* b200_event_on_ready(b200_event* e, b200_event_callback cb, void* use
 
 b200_error* b200_event_destroy(b200_event* e) {
   delete e;
+  return nullptr;
+}
+
+b200_error* b200_client_debug_arm_wait_expiry(b200_client* c, int polls) {
+  if (!c || polls <= 0) return make_error(B200_INVALID_ARGUMENT, "client and a positive poll budget are required");
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  c->armed_wait_polls = polls;
   return nullptr;
 }
 

@@ -32,6 +32,14 @@ def test_resnet_step_matches_torch_twin_golden(client):
     assert exe.launches_per_execute > 0
 
 
+def fraction_within(got, want, rtol=1e-4, atol_scale=1e-5):
+    """Share of the elements of a leaf within the plugin's fp32 bar: rtol 1e-4, atol 1e-5 of the leaf's largest
+    magnitude (a gradient is a sum over batch * pixels terms: its rounding error scales with the terms, not the sum)."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    tol = rtol * np.abs(want) + atol_scale * max(float(np.max(np.abs(want))), 1e-30)
+    return float(np.mean(np.abs(got - want) <= tol))
+
+
 def relu_margin(batch, image, width, args):
     """Smallest |x| over every ReLU input of the forward pass (float64 oracle). A ReLU input within float32
     rounding of zero makes the gradient mask, and with it every upstream gradient, differ between any two
@@ -75,6 +83,10 @@ def test_resnet_step_matches_oracle(client, batch, image, width):
         compare(o, r, rtol=1e-4, atol=1e-5, what=name, scale_atol=True)
 
 
+# lowest share of a leaf's elements within the fp32 bar that a step with flipped ReLU masks may show
+MASK_FLIP_FLOOR = 0.98
+
+
 @pytest.mark.parametrize("batch,image,width", [(16, 16, 16), (32, 32, 8), (32, 16, 16)])
 def test_resnet_step_robust_to_mask_flips(client, batch, image, width):
     """Larger steps always contain ReLU inputs within float32 rounding of zero (about 1e-6 of the inputs
@@ -86,12 +98,17 @@ def test_resnet_step_robust_to_mask_flips(client, batch, image, width):
     outs, _ = run_gpu(client, prog.text, args)
     ref = interp.run_text(prog.text, args, wide=True)
     compare(outs[0], ref[0], rtol=1e-4, atol=1e-5, what="loss")
+    fractions = {}
     for (name, _, _), o, r in zip(prog.results[1:], outs[1:], ref[1:]):
         o, r = o.astype(np.float64), np.asarray(r, np.float64)
         if name.startswith("m.") and np.linalg.norm(r) > 1e-6:
             cos = float(o.reshape(-1) @ r.reshape(-1) / (np.linalg.norm(o) * np.linalg.norm(r)))
             assert cos > 1 - 1e-3, (name, cos)
             assert abs(np.linalg.norm(o) / np.linalg.norm(r) - 1) < 2e-2, name
+            fractions[name] = fraction_within(o, r)
+    # element by element: a flipped mask perturbs the leaves upstream of it, everything else sits at the fp32 bar
+    worst = min(fractions, key=fractions.get)
+    assert np.median(list(fractions.values())) >= 0.9999 and fractions[worst] >= MASK_FLIP_FLOOR, (worst, fractions[worst])
 
 
 def test_resnet_full_size_step_properties(client):
@@ -112,6 +129,7 @@ def test_resnet_full_size_step_properties(client):
     loss, new_p, new_m, grads = twins.resnet18_train_step(P, M, args[-2], args[-1], dtype=torch.float32)
     assert abs(float(outs[0]) - loss) <= 1e-4 * abs(loss) + 1e-5
     k = len(P)
+    fractions = {}
     for i, (name, _, _) in enumerate(prog.results[1:1 + k]):
         w_new, m_new, w_old = outs[1 + i], outs[1 + k + i], args[i]
         np.testing.assert_allclose(w_new, w_old - np.float32(0.1) * m_new, rtol=1e-6, atol=1e-7, err_msg=name)
@@ -120,6 +138,12 @@ def test_resnet_full_size_step_properties(client):
         cos = float(g @ g_ref / (np.linalg.norm(g) * np.linalg.norm(g_ref) + 1e-30))
         assert cos > 1 - 1e-4, (name, cos)                      # a few hundred ReLU-mask flips among 10^8 inputs
         assert abs(np.linalg.norm(g) / np.linalg.norm(g_ref) - 1) < 5e-3, name
+        fractions[name] = fraction_within(m_new, grads[name[2:]])
+    # element by element against the fp32 twin (itself an fp32 implementation with its own mask flips)
+    worst = min(fractions, key=fractions.get)
+    report = {"median": float(np.median(list(fractions.values()))), "worst": (worst, fractions[worst])}
+    print("share of elements within rtol 1e-4 / atol 1e-5 max|leaf|:", report)
+    assert report["median"] >= 0.9999 and fractions[worst] >= MASK_FLIP_FLOOR, report
 
 
 def test_resnet_two_steps_feed_outputs_back(client):
@@ -223,7 +247,7 @@ BERT_TINY = dict(batch=2, seq=16, vocab=160, dim=64, layers=2, heads=4, ffn=128)
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("dtype,rtol,atol", [("f32", 2e-4, 2e-5), ("bf16", 3e-2, 3e-2)])
+@pytest.mark.parametrize("dtype,rtol,atol", [("f32", 2e-4, 2e-5), ("bf16", 2e-2, 2e-2)])
 def test_distilbert_shaped_mlm_step_matches_oracle(client, dtype, rtol, atol):
     """Embedding gather, attention with batched dot_general, LayerNorm / softmax in f32, tied-projector logits,
     label pick by gather, and the gradient of every leaf (the embedding gradient is a row scatter-add)."""
@@ -233,7 +257,7 @@ def test_distilbert_shaped_mlm_step_matches_oracle(client, dtype, rtol, atol):
     got, exe = run_gpu(client, prog.text, args, dtypes)
     want = interp.run_text(prog.text, args)
     assert "scatter rows=160" in exe.plan_text()
-    assert abs(float(got[0]) - float(want[0])) < (1e-4 if dtype == "f32" else 3e-2) * abs(float(want[0]))
+    assert abs(float(got[0]) - float(want[0])) < (1e-4 if dtype == "f32" else 2e-2) * abs(float(want[0]))
     # the key-bias gradients are zero in exact arithmetic (softmax is invariant to a shift of all keys): leaves are
     # held to their own scale, but never below a thousandth (bf16: a hundredth) of the largest gradient of the step
     top = max(float(np.max(np.abs(w))) for w in want[1:])
