@@ -82,7 +82,7 @@ def test_donated_arguments_are_consumed(client):
     """tf.aliasing_output marks the parameter as donated: after an execution with donation its buffer is deleted and
     its memory is back in the pool; the result is right and the bytes in use do not grow from step to step."""
     b = Builder()
-    p = b.arg((1024, 256), "f32", attrs="{tf.aliasing_output = 0 : i32}")
+    p = b.arg((1024, 256), "f32", attrs="tf.aliasing_output = 0 : i32")
     g = b.arg((1024, 256), "f32")
     text = b.module([b.sub(p, b.mul(g, b.full((1024, 256), 0.1, "f32")))])
     exe = client.compile(text)
