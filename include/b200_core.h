@@ -114,6 +114,60 @@ typedef struct {
 } b200_memory_stats;
 b200_error* b200_device_memory_stats(b200_client* client, b200_memory_stats* stats);   /* PJRT_Device_MemoryStats */
 
+/* ---- memory spaces: pjrt_memory.cc:10-48, PJRT_Device_AddressableMemories / _DefaultMemory (pjrt_device.cc:88-109),
+ *      PJRT_Client_AddressableMemories. Every device has one memory space, its HBM, of kind "device". ---- */
+int b200_device_num_memories(const b200_client* client);                     /* 1 */
+int b200_memory_id(const b200_client* client, int memory_index);             /* PJRT_Memory_Id: == the device's id */
+const char* b200_memory_kind(const b200_client* client, int memory_index);   /* PJRT_Memory_Kind: "device" */
+int b200_memory_kind_id(const b200_client* client, int memory_index);        /* PJRT_Memory_Kind_Id */
+const char* b200_memory_debug_string(const b200_client* client, int memory_index);   /* PJRT_Memory_DebugString */
+const char* b200_memory_to_string(const b200_client* client, int memory_index);      /* PJRT_Memory_ToString */
+/* PJRT_Memory_AddressableByDevices: writes the ids of the devices that address the memory (one: its own device). */
+b200_error* b200_memory_addressable_by_devices(const b200_client* client, int memory_index, int* device_ids, size_t capacity,
+                                               size_t* num_devices);
+
+/* ---- topology: PJRT_Client_TopologyDescription and PJRT_TopologyDescription_* (pjrt_topology.cc:10-70) ---- */
+const char* b200_topology_platform_name(const b200_client* client);
+const char* b200_topology_platform_version(const b200_client* client);
+int b200_topology_num_devices(const b200_client* client);                    /* all processes of the job */
+/* Device `index` of the job: its id (== index), the process that drives it, kind and debug string (owned by the client). */
+b200_error* b200_topology_device_description(const b200_client* client, int index, int* id, int* process_index,
+                                             const char** kind, const char** debug_string);
+/* PJRT_TopologyDescription_Fingerprint: a hash of platform, device kind and device count (the reference returns a
+ * constant for its one device); jax's compilation cache keys on it. */
+uint64_t b200_topology_fingerprint(const b200_client* client);
+/* PJRT_TopologyDescription_Serialize: B200_UNIMPLEMENTED, as in the reference. */
+b200_error* b200_topology_serialize(const b200_client* client, char** bytes, size_t* size);
+
+/* ---- device assignment: PJRT_Client_DefaultDeviceAssignment (pjrt_client.cc:259-265),
+ *      PJRT_LoadedExecutable_GetDeviceAssignment (pjrt_executable.cc:290-313) ---- */
+/* Fills assignment[replica * num_partitions + partition] with device ids 0, 1, ... in that order; fails when the job
+ * has fewer devices than replicas * partitions. */
+b200_error* b200_client_default_device_assignment(const b200_client* client, int num_replicas, int num_partitions,
+                                                  int* assignment, size_t assignment_size);
+/* Serialized xla.DeviceAssignmentProto (src/proto/device_assignment.proto:9-17) of the executable: replica_count,
+ * computation_count (the partitions) and one ComputationDevice per partition listing the device of every replica.
+ * `*bytes` is malloc'd: release it with b200_string_free. */
+b200_error* b200_executable_device_assignment(const b200_executable* exe, char** bytes, size_t* size);
+/* The same encoding for any assignment (device_ids[computation * replica_count + replica]); needs no device. */
+b200_error* b200_encode_device_assignment(int replica_count, int computation_count, const int64_t* device_ids, char** bytes,
+                                          size_t* size);
+/* PJRT_Executable_OutputMemoryKinds (pjrt_executable.cc:66-99): one kind string per output ("device"); the arrays are
+ * owned by the executable. */
+b200_error* b200_executable_output_memory_kinds(const b200_executable* exe, const char* const** kinds, const size_t** kind_sizes,
+                                                size_t* num_outputs);
+
+/* ---- profiler extension stub: pjrt_profiler.cc:17-125. jaxlib probes the plugin for a profiler; like the reference this
+ *      one accepts create / start / stop and hands back an empty trace. Device timings come from
+ *      b200_client_set_profiling. ---- */
+typedef struct b200_profiler b200_profiler;
+b200_error* b200_profiler_create(const char* options, size_t options_size, b200_profiler** profiler);
+b200_error* b200_profiler_start(b200_profiler* profiler);
+b200_error* b200_profiler_stop(b200_profiler* profiler);
+/* buffer == NULL: only *size is written (0: nothing was collected). */
+b200_error* b200_profiler_collect_data(b200_profiler* profiler, void* buffer, size_t* size);
+b200_error* b200_profiler_destroy(b200_profiler* profiler);
+
 /* ---- compile: PJRT_Client_Compile (pjrt_client.cc:179-257) ---- */
 typedef struct {
   size_t struct_size;
@@ -166,6 +220,7 @@ size_t b200_buffer_num_dims(const b200_buffer* buffer);
 const int64_t* b200_buffer_dims(const b200_buffer* buffer);
 size_t b200_buffer_on_device_size(const b200_buffer* buffer);
 int b200_buffer_device(const b200_buffer* buffer);
+int b200_buffer_memory(const b200_buffer* buffer);                              /* PJRT_Buffer_Memory: the memory's id */
 b200_error* b200_buffer_ready_event(b200_buffer* buffer, b200_event** event);   /* PJRT_Buffer_ReadyEvent */
 b200_error* b200_buffer_copy(b200_buffer* buffer, b200_buffer** copy);          /* PJRT_Buffer_CopyToDevice (same device) */
 b200_error* b200_buffer_delete(b200_buffer* buffer);                            /* PJRT_Buffer_Delete: frees device memory */

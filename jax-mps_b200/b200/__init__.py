@@ -127,6 +127,31 @@ SIGNATURES = {
     "b200_client_launch_count": (C.c_int64, [_P]),
     "b200_client_probe_tf32_mma_rate": (_P, [_P, C.POINTER(C.c_double)]),
     "b200_client_debug_arm_wait_expiry": (_P, [_P, C.c_int]),
+    "b200_device_num_memories": (C.c_int, [_P]),
+    "b200_memory_id": (C.c_int, [_P, C.c_int]),
+    "b200_memory_kind": (C.c_char_p, [_P, C.c_int]),
+    "b200_memory_kind_id": (C.c_int, [_P, C.c_int]),
+    "b200_memory_debug_string": (C.c_char_p, [_P, C.c_int]),
+    "b200_memory_to_string": (C.c_char_p, [_P, C.c_int]),
+    "b200_memory_addressable_by_devices": (_P, [_P, C.c_int, C.POINTER(C.c_int), C.c_size_t, C.POINTER(C.c_size_t)]),
+    "b200_buffer_memory": (C.c_int, [_P]),
+    "b200_topology_platform_name": (C.c_char_p, [_P]),
+    "b200_topology_platform_version": (C.c_char_p, [_P]),
+    "b200_topology_num_devices": (C.c_int, [_P]),
+    "b200_topology_device_description": (_P, [_P, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_char_p),
+                                              C.POINTER(C.c_char_p)]),
+    "b200_topology_fingerprint": (C.c_uint64, [_P]),
+    "b200_topology_serialize": (_P, [_P, C.POINTER(_P), C.POINTER(C.c_size_t)]),
+    "b200_client_default_device_assignment": (_P, [_P, C.c_int, C.c_int, C.POINTER(C.c_int), C.c_size_t]),
+    "b200_executable_device_assignment": (_P, [_P, C.POINTER(_P), C.POINTER(C.c_size_t)]),
+    "b200_encode_device_assignment": (_P, [C.c_int, C.c_int, C.POINTER(C.c_int64), C.POINTER(_P), C.POINTER(C.c_size_t)]),
+    "b200_executable_output_memory_kinds": (_P, [_P, C.POINTER(C.POINTER(C.c_char_p)), C.POINTER(C.POINTER(C.c_size_t)),
+                                                 C.POINTER(C.c_size_t)]),
+    "b200_profiler_create": (_P, [C.c_char_p, C.c_size_t, C.POINTER(_P)]),
+    "b200_profiler_start": (_P, [_P]),
+    "b200_profiler_stop": (_P, [_P]),
+    "b200_profiler_collect_data": (_P, [_P, _P, C.POINTER(C.c_size_t)]),
+    "b200_profiler_destroy": (_P, [_P]),
     "b200_client_set_profiling": (_P, [_P, C.c_int]),
     "b200_client_profile_report": (_P, [_P, C.POINTER(_P)]),
     "b200_matmul_f32_static_scratch": (_P, [_P, _P, _P, C.c_int64, C.c_int64, C.c_int64, _P]),
@@ -187,6 +212,86 @@ def compile_to_plan(text: str | bytes, num_processes: int = 1, process_index: in
     lib.b200_string_free(plan)
     lib.b200_string_free(src)
     return out
+
+
+def encode_device_assignment(device_ids) -> bytes:
+    """Serialized xla.DeviceAssignmentProto for device_ids[computation][replica] (needs no device)."""
+    comps = [list(row) for row in device_ids]
+    reps = len(comps[0]) if comps else 0
+    flat = [int(v) for row in comps for v in row]
+    arr = (C.c_int64 * max(len(flat), 1))(*flat)
+    out, size = _P(), C.c_size_t(0)
+    lib = load_library()
+    _check(lib.b200_encode_device_assignment(reps, len(comps), arr, C.byref(out), C.byref(size)))
+    data = C.string_at(out.value, size.value)
+    lib.b200_string_free(out)
+    return data
+
+
+def decode_device_assignment(data: bytes):
+    """Reads a serialized xla.DeviceAssignmentProto back: (replica_count, computation_count, device_ids[computation][replica])."""
+    def varint(buf, i):
+        v, shift = 0, 0
+        while True:
+            b = buf[i]; i += 1
+            v |= (b & 0x7F) << shift
+            shift += 7
+            if not b & 0x80:
+                return v, i
+    reps = comps = 0
+    rows = []
+    i = 0
+    while i < len(data):
+        tag, i = varint(data, i)
+        field, wire = tag >> 3, tag & 7
+        if wire == 0:
+            v, i = varint(data, i)
+            if field == 1: reps = v
+            elif field == 2: comps = v
+        elif wire == 2:
+            n, i = varint(data, i)
+            sub, i = data[i:i + n], i + n
+            if field == 3:
+                row, j = [], 0
+                while j < len(sub):
+                    t, j = varint(sub, j)
+                    if t == 0x0A:
+                        m, j = varint(sub, j)
+                        end = j + m
+                        while j < end:
+                            v, j = varint(sub, j)
+                            row.append(v)
+                    elif t == 0x08:
+                        v, j = varint(sub, j)
+                        row.append(v)
+                    else:
+                        raise ValueError("unexpected field in ComputationDevice")
+                rows.append(row)
+        else:
+            raise ValueError("unexpected wire type")
+    return reps, comps, rows
+
+
+class Profiler:
+    """The profiler-extension stub (PJRT_Profiler_Extension): start / stop are accepted, the trace is empty."""
+
+    def __init__(self, options: bytes = b""):
+        h = _P()
+        _check(load_library().b200_profiler_create(options, len(options), C.byref(h)))
+        self._h = h.value
+
+    def start(self): _check(load_library().b200_profiler_start(self._h))
+    def stop(self): _check(load_library().b200_profiler_stop(self._h))
+
+    def collect(self) -> bytes:
+        size = C.c_size_t(0)
+        _check(load_library().b200_profiler_collect_data(self._h, None, C.byref(size)))
+        return b"" if size.value == 0 else bytes(size.value)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            load_library().b200_profiler_destroy(self._h)
+            self._h = None
 
 
 def nccl_unique_id() -> bytes:
@@ -340,6 +445,20 @@ class Executable:
     def plan_text(self) -> str:
         return load_library().b200_executable_plan_text(self._h).decode()
 
+    def device_assignment(self):
+        """(replica_count, computation_count, device_ids[computation][replica]) decoded from the serialized proto."""
+        out, size = _P(), C.c_size_t(0)
+        lib = load_library()
+        _check(lib.b200_executable_device_assignment(self._h, C.byref(out), C.byref(size)))
+        data = C.string_at(out.value, size.value)
+        lib.b200_string_free(out)
+        return decode_device_assignment(data)
+
+    def output_memory_kinds(self) -> list:
+        kinds, sizes, n = C.POINTER(C.c_char_p)(), C.POINTER(C.c_size_t)(), C.c_size_t(0)
+        _check(load_library().b200_executable_output_memory_kinds(self._h, C.byref(kinds), C.byref(sizes), C.byref(n)))
+        return [kinds[k][:sizes[k]].decode() for k in range(n.value)]
+
     def output_info(self, i: int):
         dt, dims, nd = C.c_int(), C.POINTER(C.c_int64)(), C.c_size_t()
         _check(load_library().b200_executable_output_info(self._h, i, C.byref(dt), C.byref(dims), C.byref(nd)))
@@ -464,6 +583,35 @@ class Client:
         txt = C.string_at(out.value).decode()
         lib.b200_string_free(out)
         return json.loads(txt)
+
+    def memories(self) -> list:
+        """[{id, kind, debug_string, to_string, devices}] for the memory spaces of this client's device."""
+        lib = load_library()
+        out = []
+        for k in range(lib.b200_device_num_memories(self._h)):
+            ids, n = (C.c_int * 8)(), C.c_size_t(0)
+            _check(lib.b200_memory_addressable_by_devices(self._h, k, ids, 8, C.byref(n)))
+            out.append({"id": lib.b200_memory_id(self._h, k), "kind": lib.b200_memory_kind(self._h, k).decode(),
+                        "debug_string": lib.b200_memory_debug_string(self._h, k).decode(),
+                        "to_string": lib.b200_memory_to_string(self._h, k).decode(), "devices": list(ids[:n.value])})
+        return out
+
+    def topology(self) -> dict:
+        lib = load_library()
+        devs = []
+        for k in range(lib.b200_topology_num_devices(self._h)):
+            i, p, kind, dbg = C.c_int(), C.c_int(), C.c_char_p(), C.c_char_p()
+            _check(lib.b200_topology_device_description(self._h, k, C.byref(i), C.byref(p), C.byref(kind), C.byref(dbg)))
+            devs.append({"id": i.value, "process_index": p.value, "kind": kind.value.decode(), "debug_string": dbg.value.decode()})
+        return {"platform_name": lib.b200_topology_platform_name(self._h).decode(),
+                "platform_version": lib.b200_topology_platform_version(self._h).decode(),
+                "fingerprint": lib.b200_topology_fingerprint(self._h), "devices": devs}
+
+    def default_device_assignment(self, num_replicas: int, num_partitions: int) -> list:
+        n = num_replicas * num_partitions
+        arr = (C.c_int * max(n, 1))()
+        _check(load_library().b200_client_default_device_assignment(self._h, num_replicas, num_partitions, arr, n))
+        return [[arr[r * num_partitions + p] for p in range(num_partitions)] for r in range(num_replicas)]
 
     def debug_arm_wait_expiry(self, polls: int = 1000):
         """Test hook: the next execution starts with a bounded device-side wait that runs out."""

@@ -288,6 +288,8 @@ struct PinnedBlock {
 
 struct LoadedProgram {
   std::unique_ptr<CompiledProgram> prog;
+  std::vector<const char*> output_kinds;       // PJRT_Executable_OutputMemoryKinds
+  std::vector<size_t> output_kind_sizes;
   std::vector<CUmodule> modules;
   std::vector<CUfunction> functions;
   std::vector<void*> const_ptrs;
@@ -316,7 +318,8 @@ struct b200_client {
   cudaMemPool_t pool = nullptr;
   ncclComm_t comm = nullptr;
   std::recursive_mutex mu;
-  std::string kind, debug, version;
+  std::string kind, debug, version, memory_debug, memory_string;
+  std::vector<std::string> topology_strings;
   std::atomic<int64_t> bytes_in_use{0}, peak_bytes{0}, num_allocs{0}, largest_alloc{0}, launches{0};
   std::map<std::string, std::shared_ptr<LoadedProgram>> cache;    // program text hash -> loaded plan
   std::vector<PinnedBlock> pinned;
@@ -357,6 +360,10 @@ struct b200_buffer {
   Block* block = nullptr;                      // non-null: ptr lies inside block->base, freed with its last buffer
   std::vector<cudaEvent_t> reads;              // pending reads on other streams
   bool deleted = false;
+};
+
+struct b200_profiler {
+  bool running = false;
 };
 
 struct b200_executable {
@@ -952,6 +959,8 @@ b200_error* b200_client_create(const b200_client_options* o, b200_client** out) 
   CUDA_TRY(cudaGetDeviceProperties(&prop, ord));
   c->kind = prop.name;
   c->total_mem = (int64_t)prop.totalGlobalMem;
+  c->memory_debug = "B200 HBM of device " + std::to_string(c->rank) + " (" + std::to_string(prop.totalGlobalMem >> 20) + " MiB)";
+  c->memory_string = "B200Memory(id=" + std::to_string(c->rank) + ", kind=device)";
   c->debug = "B200:" + std::to_string(c->rank) + " (cuda:" + std::to_string(ord) + ", sm_" + std::to_string(prop.major) +
              std::to_string(prop.minor) + ")";
   int rtv = 0;
@@ -1657,6 +1666,133 @@ b200_error* b200_event_destroy(b200_event* e) {
   return nullptr;
 }
 
+// ---- memory spaces, topology, device assignment, profiler stub ---------------------------------------------------
+int b200_device_num_memories(const b200_client*) { return 1; }
+int b200_memory_id(const b200_client* c, int) { return c->rank; }
+const char* b200_memory_kind(const b200_client*, int) { return "device"; }
+int b200_memory_kind_id(const b200_client*, int) { return 0; }
+const char* b200_memory_debug_string(const b200_client* c, int) { return c->memory_debug.c_str(); }
+const char* b200_memory_to_string(const b200_client* c, int) { return c->memory_string.c_str(); }
+int b200_buffer_memory(const b200_buffer* b) { return b->client->rank; }
+
+b200_error* b200_memory_addressable_by_devices(const b200_client* c, int memory_index, int* device_ids, size_t capacity,
+                                               size_t* num_devices) {
+  if (!c || !num_devices) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  if (memory_index != 0) return make_error(B200_INVALID_ARGUMENT, "a device has one memory space (index 0)");
+  *num_devices = 1;
+  if (device_ids && capacity >= 1) device_ids[0] = c->rank;
+  return nullptr;
+}
+
+const char* b200_topology_platform_name(const b200_client*) { return "b200"; }
+const char* b200_topology_platform_version(const b200_client* c) { return c->version.c_str(); }
+int b200_topology_num_devices(const b200_client* c) { return c->nprocs; }
+
+b200_error* b200_topology_device_description(const b200_client* c, int index, int* id, int* process_index, const char** kind,
+                                             const char** debug_string) {
+  if (!c) return make_error(B200_INVALID_ARGUMENT, "null client");
+  if (index < 0 || index >= c->nprocs) return make_error(B200_INVALID_ARGUMENT, "device index out of range");
+  if (id) *id = index;
+  if (process_index) *process_index = index;          // one process drives one device
+  if (kind) *kind = c->kind.c_str();
+  if (debug_string) {
+    std::lock_guard<std::recursive_mutex> lock(const_cast<b200_client*>(c)->mu);
+    auto& cache = const_cast<b200_client*>(c)->topology_strings;
+    if ((int)cache.size() < c->nprocs) cache.resize(c->nprocs);
+    if (cache[index].empty()) cache[index] = "B200:" + std::to_string(index) + (index == c->rank ? " (this process)" : " (process " + std::to_string(index) + ")");
+    *debug_string = cache[index].c_str();
+  }
+  return nullptr;
+}
+
+uint64_t b200_topology_fingerprint(const b200_client* c) {
+  const std::string text = std::string("b200|") + c->kind + "|" + std::to_string(c->nprocs);
+  return hash_text(text.data(), text.size(), 0x42323030ull);
+}
+
+b200_error* b200_topology_serialize(const b200_client*, char**, size_t*) {
+  return make_error(B200_UNIMPLEMENTED, "TopologyDescription_Serialize is not implemented");
+}
+
+b200_error* b200_client_default_device_assignment(const b200_client* c, int num_replicas, int num_partitions, int* assignment,
+                                                  size_t assignment_size) {
+  if (!c || !assignment) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  if (num_replicas < 1 || num_partitions < 1) return make_error(B200_INVALID_ARGUMENT, "replica and partition counts must be positive");
+  const size_t n = (size_t)num_replicas * (size_t)num_partitions;
+  if (assignment_size < n) return make_error(B200_INVALID_ARGUMENT, "assignment array is too small");
+  if (n > (size_t)c->nprocs)
+    return make_error(B200_INVALID_ARGUMENT, "the job has " + std::to_string(c->nprocs) + " devices, " + std::to_string(n) + " were asked for");
+  for (size_t k = 0; k < n; k++) assignment[k] = (int)k;
+  return nullptr;
+}
+
+namespace {
+void put_varint(std::string& out, uint64_t v) {
+  while (v >= 0x80) { out.push_back((char)((v & 0x7F) | 0x80)); v >>= 7; }
+  out.push_back((char)v);
+}
+// xla.DeviceAssignmentProto by hand: 1 replica_count, 2 computation_count, 3 repeated ComputationDevice
+// { 1 repeated int64 replica_device_ids (packed) }; proto3 leaves out scalars that are zero.
+std::string encode_device_assignment(int replicas, int computations, const int64_t* ids) {
+  std::string out;
+  if (replicas) { out.push_back(0x08); put_varint(out, (uint64_t)replicas); }
+  if (computations) { out.push_back(0x10); put_varint(out, (uint64_t)computations); }
+  for (int cidx = 0; cidx < computations; cidx++) {
+    std::string packed;
+    for (int r = 0; r < replicas; r++) put_varint(packed, (uint64_t)ids[(size_t)cidx * replicas + r]);
+    std::string msg;
+    if (!packed.empty()) { msg.push_back(0x0A); put_varint(msg, packed.size()); msg += packed; }
+    out.push_back(0x1A);
+    put_varint(out, msg.size());
+    out += msg;
+  }
+  return out;
+}
+b200_error* hand_out(const std::string& data, char** bytes, size_t* size) {
+  char* p = (char*)malloc(std::max<size_t>(data.size(), 1));
+  if (!p) return make_error(B200_RESOURCE_EXHAUSTED, "out of host memory");
+  memcpy(p, data.data(), data.size());
+  *bytes = p;
+  *size = data.size();
+  return nullptr;
+}
+}  // namespace
+
+b200_error* b200_encode_device_assignment(int replica_count, int computation_count, const int64_t* device_ids, char** bytes,
+                                          size_t* size) {
+  if (!bytes || !size || (!device_ids && replica_count * computation_count > 0)) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  if (replica_count < 0 || computation_count < 0) return make_error(B200_INVALID_ARGUMENT, "negative count");
+  return hand_out(encode_device_assignment(replica_count, computation_count, device_ids), bytes, size);
+}
+
+b200_error* b200_executable_device_assignment(const b200_executable* e, char** bytes, size_t* size) {
+  if (!e || !bytes || !size) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  const int replicas = std::max(1, e->lp->prog->num_replicas);
+  const int parts = std::max(1, e->client->nprocs > 1 ? e->client->nprocs : e->lp->prog->num_partitions);
+  std::vector<int64_t> ids((size_t)replicas * parts);
+  for (int p2 = 0; p2 < parts; p2++)
+    for (int r = 0; r < replicas; r++) ids[(size_t)p2 * replicas + r] = (int64_t)p2 * replicas + r;
+  if (parts == 1 && replicas == 1) ids[0] = e->client->rank;
+  return hand_out(encode_device_assignment(replicas, parts, ids.data()), bytes, size);
+}
+
+b200_error* b200_executable_output_memory_kinds(const b200_executable* e, const char* const** kinds, const size_t** kind_sizes,
+                                                size_t* num_outputs) {
+  if (!e || !num_outputs) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  static const char* const kDevice = "device";
+  std::lock_guard<std::recursive_mutex> lock(e->client->mu);
+  auto& lp = *e->lp;
+  const size_t n = lp.prog->results.size();
+  if (lp.output_kinds.size() != n) {
+    lp.output_kinds.assign(n, kDevice);
+    lp.output_kind_sizes.assign(n, 6);
+  }
+  *num_outputs = n;
+  if (kinds) *kinds = lp.output_kinds.data();
+  if (kind_sizes) *kind_sizes = lp.output_kind_sizes.data();
+  return nullptr;
+}
+
 b200_error* b200_client_debug_arm_wait_expiry(b200_client* c, int polls) {
   if (!c || polls <= 0) return make_error(B200_INVALID_ARGUMENT, "client and a positive poll budget are required");
   std::lock_guard<std::recursive_mutex> lock(c->mu);
@@ -1670,6 +1806,34 @@ b200_error* b200_client_probe_tf32_mma_rate(b200_client* c, double* tflops) {
   if (auto* e = set_device(c)) return e;
   cudaError_t e = b200::probe_tf32_mma_rate(c->error_flag, c->compute, tflops);
   if (e != cudaSuccess) return make_error(B200_INTERNAL, std::string("tensor-core rate probe failed: ") + cudaGetErrorString(e));
+  return nullptr;
+}
+
+// profiler extension stub (pjrt_profiler.cc:17-125)
+b200_error* b200_profiler_create(const char*, size_t, b200_profiler** profiler) {
+  if (!profiler) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  *profiler = new b200_profiler();
+  return nullptr;
+}
+b200_error* b200_profiler_start(b200_profiler* p) {
+  if (!p) return make_error(B200_INVALID_ARGUMENT, "null profiler");
+  if (p->running) return make_error(B200_FAILED_PRECONDITION, "profiler already started");
+  p->running = true;
+  return nullptr;
+}
+b200_error* b200_profiler_stop(b200_profiler* p) {
+  if (!p) return make_error(B200_INVALID_ARGUMENT, "null profiler");
+  if (!p->running) return make_error(B200_FAILED_PRECONDITION, "profiler was not started");
+  p->running = false;
+  return nullptr;
+}
+b200_error* b200_profiler_collect_data(b200_profiler* p, void*, size_t* size) {
+  if (!p || !size) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  *size = 0;
+  return nullptr;
+}
+b200_error* b200_profiler_destroy(b200_profiler* p) {
+  delete p;
   return nullptr;
 }
 

@@ -105,3 +105,29 @@ def test_donated_arguments_are_consumed(client):
     # without donation the argument stays
     (nb,) = exe.execute([pb, gb])
     assert not pb.is_deleted()
+
+
+def test_memory_spaces_topology_and_device_assignment(client):
+    """The descriptors jaxlib asks a plugin for at start-up (pjrt_memory.cc:10-48, pjrt_device.cc:88-109,
+    pjrt_topology.cc:10-70, pjrt_client.cc:259-265, pjrt_executable.cc:66-99,290-313 of the reference)."""
+    mems = client.memories()
+    assert len(mems) == 1 and mems[0]["kind"] == "device" and mems[0]["devices"] == [0] and mems[0]["id"] == 0
+    assert "HBM" in mems[0]["debug_string"] and "kind=device" in mems[0]["to_string"]
+    topo = client.topology()
+    assert topo["platform_name"] == "b200" and topo["platform_version"] == client.platform_version
+    assert [d["id"] for d in topo["devices"]] == [0] and "B200" in topo["devices"][0]["kind"]
+    assert topo["fingerprint"] == client.topology()["fingerprint"] != 0
+    assert client.default_device_assignment(1, 1) == [[0]]
+    with pytest.raises(b200.B200Error):
+        client.default_device_assignment(2, 1)              # one device in this job
+    lib = b200.load_library()
+    import ctypes as C
+    out, size = C.c_void_p(), C.c_size_t(0)
+    err = lib.b200_topology_serialize(client._h, C.byref(out), C.byref(size))
+    assert err and lib.b200_error_get_code(err) == 12        # UNIMPLEMENTED, as in the reference
+    lib.b200_error_destroy(err)
+    exe = client.compile(_matmul_program(64))
+    assert exe.device_assignment() == (1, 1, [[0]])
+    assert exe.output_memory_kinds() == ["device"]
+    buf = client.buffer_from_host(np.zeros(4, np.float32))
+    assert lib.b200_buffer_memory(buf._h) == 0 == lib.b200_buffer_device(buf._h)

@@ -338,3 +338,26 @@ def test_plans_of_case_scatter_and_half_precision_contractions():
                   props={"scatter_dimension_numbers": sdn, "indices_are_sorted": "false", "unique_indices": "false"}, regions=[reg])
     with pytest.raises(b200.B200Error, match="row form"):
         b200.compile_to_plan(b.module([y]))
+
+
+def test_device_assignment_proto_round_trip():
+    """The hand-encoded xla.DeviceAssignmentProto (src/proto/device_assignment.proto:9-17 of the reference) decodes back
+    to what went in; the single-device case is byte for byte what protobuf writes for the reference's 1 x 1 assignment
+    (pjrt_executable.cc:290-313: replica_count 1, computation_count 1, one ComputationDevice [0])."""
+    assert b200.encode_device_assignment([[0]]) == bytes([0x08, 1, 0x10, 1, 0x1A, 3, 0x0A, 1, 0])
+    for ids in ([[0, 1, 2, 3, 4, 5, 6, 7]], [[k] for k in range(8)], [[0, 1], [2, 3], [300, 70000]]):
+        data = b200.encode_device_assignment(ids)
+        reps, comps, rows = b200.decode_device_assignment(data)
+        assert (reps, comps) == (len(ids[0]), len(ids)) and rows == [list(r) for r in ids]
+
+
+def test_profiler_stub_accepts_a_session_and_returns_an_empty_trace():
+    """Like the reference's stub (src/pjrt_plugin/pjrt_profiler.cc:17-125): create, start, stop, collect nothing."""
+    p = b200.Profiler(b"options")
+    p.start()
+    with pytest.raises(b200.B200Error):
+        p.start()
+    p.stop()
+    with pytest.raises(b200.B200Error):
+        p.stop()
+    assert p.collect() == b""
