@@ -245,6 +245,26 @@ typedef struct {
 b200_error* b200_executable_execute(b200_executable* exe, b200_buffer* const* args, size_t num_args,
                                     b200_buffer** outputs, b200_event** done, const b200_execute_options* options);
 
+/* ---- several GPUs as the devices of one process: the per-device lists of PJRT_LoadedExecutable_Execute
+ *      (pjrt_executable.cc:178-258: argument_lists[d], output_lists[d], device_complete_events[d]; the reference reads
+ *      index 0 only, it has one device) ---- */
+typedef struct b200_device_group b200_device_group;
+/* One client per listed CUDA ordinal (NULL: 0 .. num_devices - 1), their NCCL communicators made together in this
+ * process. Device d of the group has id d. Buffers are made through b200_device_group_client(group, d). */
+b200_error* b200_device_group_create(const int* ordinals, int num_devices, b200_device_group** group);
+int b200_device_group_size(const b200_device_group* group);
+b200_client* b200_device_group_client(const b200_device_group* group, int device);      /* owned by the group */
+b200_error* b200_device_group_destroy(b200_device_group* group);
+/* Compiles the module once per device (partition d of num_devices); `executables` has room for one per device. */
+b200_error* b200_device_group_compile(b200_device_group* group, const char* code, size_t code_size, const char* format,
+                                      const b200_compile_options* options, b200_executable** executables);
+/* argument_lists[d][i] is argument i on device d, output_lists[d] a caller-allocated array of
+ * b200_executable_num_outputs pointers, device_complete_events[d] (the array may be NULL) the completion event of
+ * device d. Returns after every device's plan has been enqueued. */
+b200_error* b200_device_group_execute(b200_device_group* group, b200_executable* const* executables,
+                                      b200_buffer* const* const* argument_lists, size_t num_args, b200_buffer** const* output_lists,
+                                      b200_event** device_complete_events, const b200_execute_options* options);
+
 /* ---- events: pjrt_event.cc:101-193 ---- */
 int b200_event_is_ready(b200_event* event);
 b200_error* b200_event_await(b200_event* event);

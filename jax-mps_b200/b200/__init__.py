@@ -147,6 +147,13 @@ SIGNATURES = {
     "b200_encode_device_assignment": (_P, [C.c_int, C.c_int, C.POINTER(C.c_int64), C.POINTER(_P), C.POINTER(C.c_size_t)]),
     "b200_executable_output_memory_kinds": (_P, [_P, C.POINTER(C.POINTER(C.c_char_p)), C.POINTER(C.POINTER(C.c_size_t)),
                                                  C.POINTER(C.c_size_t)]),
+    "b200_device_group_create": (_P, [C.POINTER(C.c_int), C.c_int, C.POINTER(_P)]),
+    "b200_device_group_size": (C.c_int, [_P]),
+    "b200_device_group_client": (_P, [_P, C.c_int]),
+    "b200_device_group_destroy": (_P, [_P]),
+    "b200_device_group_compile": (_P, [_P, C.c_char_p, C.c_size_t, C.c_char_p, C.POINTER(_CompileOptions), C.POINTER(_P)]),
+    "b200_device_group_execute": (_P, [_P, C.POINTER(_P), C.POINTER(C.POINTER(_P)), C.c_size_t, C.POINTER(C.POINTER(_P)),
+                                       C.POINTER(_P), C.POINTER(_ExecuteOptions)]),
     "b200_profiler_create": (_P, [C.c_char_p, C.c_size_t, C.POINTER(_P)]),
     "b200_profiler_start": (_P, [_P]),
     "b200_profiler_stop": (_P, [_P]),
@@ -494,6 +501,15 @@ class Client:
     """One process, one B200 (PJRT_Client). For data-parallel jobs every
     process passes its rank, the world size and the shared NCCL id."""
 
+    _owned = True
+
+    @classmethod
+    def _wrap(cls, handle) -> "Client":
+        """A client owned by somebody else (a device of a DeviceGroup)."""
+        c = cls.__new__(cls)
+        c._h, c._id, c._owned = handle, None, False
+        return c
+
     def __init__(self, device_ordinal: int = -1, process_index: int = 0, num_processes: int = 1,
                  nccl_id: bytes | None = None):
         lib = load_library()
@@ -639,6 +655,58 @@ class Client:
                                                              out.device_pointer(), m, n, k, self.compute_stream()))
 
     def close(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and self._owned:
             load_library().b200_client_destroy(self._h)
             self._h = None
+
+
+class DeviceGroup:
+    """Several local GPUs as the devices of this one process (the per-device lists of PJRT_LoadedExecutable_Execute):
+    `devices[d]` is the client of device d (make buffers through it), `compile` gives one executable per device and
+    `execute` takes one argument list per device."""
+
+    def __init__(self, ordinals=None, num_devices: int | None = None):
+        lib = load_library()
+        n = len(ordinals) if ordinals is not None else int(num_devices)
+        arr = (C.c_int * n)(*ordinals) if ordinals is not None else None
+        h = _P()
+        _check(lib.b200_device_group_create(arr, n, C.byref(h)))
+        self._h = h.value
+        self.devices = [Client._wrap(lib.b200_device_group_client(self._h, d)) for d in range(n)]
+
+    def compile(self, text: str | bytes) -> list:
+        code = text.encode() if isinstance(text, str) else text
+        opts = _CompileOptions(C.sizeof(_CompileOptions), 0, 0)
+        n = len(self.devices)
+        exes = (_P * n)()
+        _check(load_library().b200_device_group_compile(self._h, code, len(code), b"mlir", C.byref(opts), exes))
+        return [Executable(self.devices[d], exes[d]) for d in range(n)]
+
+    def execute(self, exes, argument_lists, donate: bool = False):
+        """argument_lists[d][i]: argument i on device d. Returns (output_lists[d][k], device_complete_events[d])."""
+        n = len(self.devices)
+        num_args = len(argument_lists[0]) if argument_lists else 0
+        exe_arr = (_P * n)(*[e._h for e in exes])
+        arg_rows = [(_P * max(num_args, 1))(*[a._h for a in argument_lists[d]]) for d in range(n)]
+        args = (C.POINTER(_P) * n)(*[C.cast(r, C.POINTER(_P)) for r in arg_rows])
+        num_out = exes[0].num_outputs
+        out_rows = [(_P * max(num_out, 1))() for _ in range(n)]
+        outs = (C.POINTER(_P) * n)(*[C.cast(r, C.POINTER(_P)) for r in out_rows])
+        events = (_P * n)()
+        opts = _ExecuteOptions(C.sizeof(_ExecuteOptions), 1 if donate else 0)
+        _check(load_library().b200_device_group_execute(self._h, exe_arr, args, num_args, outs, events, C.byref(opts)))
+        return ([[Buffer(self.devices[d], out_rows[d][k]) for k in range(num_out)] for d in range(n)],
+                [Event(events[d]) for d in range(n)])
+
+    def close(self):
+        if getattr(self, "_h", None):
+            load_library().b200_device_group_destroy(self._h)
+            self._h = None
+            for c in self.devices:
+                c._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -790,11 +790,10 @@ cudaError_t launch_gemm16(const Gemm16Launch& g, const void* A, const void* B, v
     if (g.path == 1) {
       if (g.split_k > 1 && (!scratch || !counters)) { *why = "skinny product without its scratch"; return cudaErrorInvalidValue; }
       dim3 grid((g.N + 255) / 256, g.split_k, g.G);
-      static bool configured = false;
-      if (!configured) {
+      static bool configured[64] = {};
+      if (first_use_on_this_device(configured)) {
         cudaFuncSetAttribute(gemv16_nc_kernel<8, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * (2048 + 32) * 4 + 65536);
         cudaFuncSetAttribute(gemv16_nc_kernel<8, false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * (2048 + 32) * 4 + 65536);
-        configured = true;
       }
       const int unroll = maxm == 1 ? 8 : 4;
       const size_t smem = (size_t)maxm * (g.gemv_kc + 8 * unroll) * 4 + (size_t)maxm * 8 * 256 * 4;
@@ -804,13 +803,12 @@ cudaError_t launch_gemm16(const Gemm16Launch& g, const void* A, const void* B, v
       else gemv16_nc_kernel<8, false, 4><<<grid, 256, smem, stream>>>((const uint16_t*)A, (const uint16_t*)B, C, scratch, counters, p);
     } else {
       if (!p.vec) { *why = "skinny product: B is not 16-byte aligned"; return cudaErrorInvalidValue; }
-      static bool configured = false;
-      if (!configured) {
+      static bool configured[64] = {};
+      if (first_use_on_this_device(configured)) {
 #define SETKC(MM, BF, NW_) cudaFuncSetAttribute(gemv16_kc_kernel<MM, BF, NW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)
         SETKC(1, true, 1); SETKC(1, true, 4); SETKC(1, false, 1); SETKC(1, false, 4);
         SETKC(8, true, 1); SETKC(8, true, 4); SETKC(8, false, 1); SETKC(8, false, 4);
 #undef SETKC
-        configured = true;
       }
       const int tasks = (g.N + g.nw - 1) / g.nw;
       dim3 grid((unsigned)std::max(1, std::min((tasks + 7) / 8, sm_count() * 8)), g.G);
@@ -849,12 +847,11 @@ cudaError_t launch_gemm16(const Gemm16Launch& g, const void* A, const void* B, v
     else ok = make_map(&tm_b, B, g.in_fmt, g.N, g.K, g.G, g.b_ks, g.b_gs, 64, 64);
   }
   if (!ok) { *why = "cuTensorMapEncodeTiled refused an operand (alignment or extent)"; return cudaErrorInvalidValue; }
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};
+  if (first_use_on_this_device(configured)) {
     cudaFuncSetAttribute(gemm16_tma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, G16Cfg<64>::SMEM);
     cudaFuncSetAttribute(gemm16_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, G16Cfg<128>::SMEM);
     cudaFuncSetAttribute(gemm16_tma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, G16Cfg<256>::SMEM);
-    configured = true;
   }
   const long long tiles = (long long)p.mtiles * p.ntiles * p.G * p.split_k;
   const unsigned grid = (unsigned)std::min<long long>(tiles, sm_count());

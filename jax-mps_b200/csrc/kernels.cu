@@ -1413,19 +1413,18 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
   auto c_grp = (const long long*)tables[8];
   int v = (p.a_mcontig ? 4 : 0) | (p.b_kcontig ? 2 : 0) | (p.mask ? 1 : 0);
   if (p.tensor_cores) {
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};
+    if (first_use_on_this_device(configured)) {
 #define SETATTR(AM, BK_, MK) \
   cudaFuncSetAttribute(igemm_tf32x3_kernel<AM, BK_, MK>, cudaFuncAttributeMaxDynamicSharedMemorySize, TSMEM_BYTES)
       SETATTR(false, false, false); SETATTR(false, false, true); SETATTR(false, true, false); SETATTR(false, true, true);
       SETATTR(true, false, false); SETATTR(true, false, true); SETATTR(true, true, false); SETATTR(true, true, true);
 #undef SETATTR
-      configured = true;
     }
     dim3 grid((p.M + TBM - 1) / TBM, (p.N + TBN - 1) / TBN, p.groups * p.split_k);
     if (p.vec) {
-      static bool configured_w = false;
-      if (!configured_w) {
+      static bool configured_w[64] = {};
+      if (first_use_on_this_device(configured_w)) {
 #define SETATTRW(BN_, AM, BK_, MK)                                                                                    \
   cudaFuncSetAttribute(igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                        WsCfg<BN_>::SMEM);                                                                            \
@@ -1443,7 +1442,6 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
         SETALLW(128);
 #undef SETALLW
 #undef SETATTRW
-        configured_w = true;
       }
       const bool wide = p.N >= 128 && p.wide_n;
       // two half-size CTAs per SM for 64-wide tiles once the grid has more than one wave of full-size CTAs

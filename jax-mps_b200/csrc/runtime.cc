@@ -150,6 +150,7 @@ NvrtcApi& nvrtc() {
 struct NcclApi {
   ncclResult_t (*GetUniqueId)(ncclUniqueId*);
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+  ncclResult_t (*CommInitAll)(ncclComm_t*, int, const int*);
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
   ncclResult_t (*CommDestroy)(ncclComm_t);
   ncclResult_t (*CommAbort)(ncclComm_t);
@@ -184,6 +185,7 @@ NcclApi& nccl() {
     };
     get("ncclGetUniqueId", (void**)&api.GetUniqueId);
     get("ncclCommInitRank", (void**)&api.CommInitRank);
+    get("ncclCommInitAll", (void**)&api.CommInitAll);
     get("ncclAllReduce", (void**)&api.AllReduce);
     get("ncclCommDestroy", (void**)&api.CommDestroy);
     get("ncclCommAbort", (void**)&api.CommAbort);
@@ -932,7 +934,16 @@ b200_error* b200_nccl_unique_id(char out[B200_NCCL_ID_BYTES]) {
   return nullptr;
 }
 
-b200_error* b200_client_create(const b200_client_options* o, b200_client** out) {
+namespace {
+b200_error* create_client(const b200_client_options* o, ncclComm_t given_comm, b200_client** out);
+}
+
+b200_error* b200_client_create(const b200_client_options* o, b200_client** out) { return create_client(o, nullptr, out); }
+
+namespace {
+// `given_comm`: a communicator made for this device by ncclCommInitAll (several devices in one process); otherwise
+// a job of several processes builds its own from the shared unique id.
+b200_error* create_client(const b200_client_options* o, ncclComm_t given_comm, b200_client** out) {
   if (!out) return make_error(B200_INVALID_ARGUMENT, "client out-pointer is null");
   *out = nullptr;
   int count = 0;
@@ -983,13 +994,16 @@ b200_error* b200_client_create(const b200_client_options* o, b200_client** out) 
   if (const char* e2 = getenv("B200_NO_TENSOR_CORES")) c->tensor_cores = atoi(e2) == 0;
   if (!driver().ok) return make_error(B200_FAILED_PRECONDITION, driver().error);
   if (c->nprocs > 1) {
-    if (!o->nccl_unique_id) return make_error(B200_INVALID_ARGUMENT, "num_processes > 1 needs nccl_unique_id");
     NcclApi& n = nccl();
     if (!n.ok) return make_error(B200_FAILED_PRECONDITION, n.error);
-    ncclUniqueId id;
-    memcpy(&id, o->nccl_unique_id, sizeof id);
-    ncclResult_t r = n.CommInitRank(&c->comm, c->nprocs, id, c->rank);
-    if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclCommInitRank: ") + n.GetErrorString(r));
+    if (given_comm) c->comm = given_comm;
+    else {
+      if (!o->nccl_unique_id) return make_error(B200_INVALID_ARGUMENT, "num_processes > 1 needs nccl_unique_id");
+      ncclUniqueId id;
+      memcpy(&id, o->nccl_unique_id, sizeof id);
+      ncclResult_t r = n.CommInitRank(&c->comm, c->nprocs, id, c->rank);
+      if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclCommInitRank: ") + n.GetErrorString(r));
+    }
     // collectives that overlap with compute run on a stream of their own, at the highest priority so that their
     // few CTAs find a place as soon as compute CTAs retire
     int lo = 0, hi = 0;
@@ -1001,6 +1015,7 @@ b200_error* b200_client_create(const b200_client_options* o, b200_client** out) 
   *out = c.release();
   return nullptr;
 }
+}  // namespace
 
 b200_error* b200_client_destroy(b200_client* c) {
   if (!c) return nullptr;
@@ -1791,6 +1806,117 @@ b200_error* b200_executable_output_memory_kinds(const b200_executable* e, const 
   if (kinds) *kinds = lp.output_kinds.data();
   if (kind_sizes) *kind_sizes = lp.output_kind_sizes.data();
   return nullptr;
+}
+
+// ---- several GPUs as the devices of one process ------------------------------------------------------------------
+// PJRT_LoadedExecutable_Execute hands the plugin one argument list per addressable device
+// (src/pjrt_plugin/pjrt_executable.cc:178-258 reads argument_lists[0] only: the reference has one device). A device
+// group is that shape on this side: one client per local GPU, their NCCL communicators made together in this process
+// (ncclCommInitAll), one executable per device compiled from the same module, and an execute call that takes
+// per-device argument and output lists and returns one completion event per device. Each device's plan is issued
+// by a thread of its own, so that the collectives of the plans meet the way they do between processes.
+struct b200_device_group {
+  std::vector<b200_client*> clients;
+};
+
+b200_error* b200_device_group_create(const int* ordinals, int num_devices, b200_device_group** out) {
+  if (!out || num_devices < 1) return make_error(B200_INVALID_ARGUMENT, "a device group needs at least one device");
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    return make_error(B200_FAILED_PRECONDITION, "no CUDA device available (this plugin has no CPU fallback)");
+  }
+  std::vector<int> devs(num_devices);
+  for (int d = 0; d < num_devices; d++) {
+    devs[d] = ordinals ? ordinals[d] : d;
+    if (devs[d] < 0 || devs[d] >= count) return make_error(B200_INVALID_ARGUMENT, "device ordinal " + std::to_string(devs[d]) + " out of range");
+    for (int q = 0; q < d; q++) if (devs[q] == devs[d]) return make_error(B200_INVALID_ARGUMENT, "a device appears twice in the group");
+  }
+  std::vector<ncclComm_t> comms(num_devices, nullptr);
+  if (num_devices > 1) {
+    NcclApi& n = nccl();
+    if (!n.ok) return make_error(B200_FAILED_PRECONDITION, n.error);
+    ncclResult_t r = n.CommInitAll(comms.data(), num_devices, devs.data());
+    if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclCommInitAll: ") + n.GetErrorString(r));
+  }
+  auto g = std::make_unique<b200_device_group>();
+  for (int d = 0; d < num_devices; d++) {
+    b200_client_options o;
+    memset(&o, 0, sizeof o);
+    o.struct_size = sizeof o;
+    o.device_ordinal = devs[d];
+    o.process_index = d;
+    o.num_processes = num_devices;
+    b200_client* c = nullptr;
+    if (auto* e = create_client(&o, comms[d], &c)) {
+      for (auto* made : g->clients) b200_client_destroy(made);
+      return e;
+    }
+    g->clients.push_back(c);
+  }
+  *out = g.release();
+  return nullptr;
+}
+
+int b200_device_group_size(const b200_device_group* g) { return g ? (int)g->clients.size() : 0; }
+b200_client* b200_device_group_client(const b200_device_group* g, int device) {
+  return (g && device >= 0 && device < (int)g->clients.size()) ? g->clients[device] : nullptr;
+}
+
+b200_error* b200_device_group_destroy(b200_device_group* g) {
+  if (!g) return nullptr;
+  for (auto* c : g->clients) b200_client_destroy(c);
+  delete g;
+  return nullptr;
+}
+
+b200_error* b200_device_group_compile(b200_device_group* g, const char* code, size_t code_size, const char* format,
+                                      const b200_compile_options* options, b200_executable** executables) {
+  if (!g || !executables) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  const size_t n = g->clients.size();
+  std::vector<b200_error*> errs(n, nullptr);
+  std::vector<std::thread> threads;
+  for (size_t d = 0; d < n; d++) {
+    executables[d] = nullptr;
+    threads.emplace_back([&, d] { errs[d] = b200_client_compile(g->clients[d], code, code_size, format, options, &executables[d]); });
+  }
+  for (auto& t : threads) t.join();
+  b200_error* first = nullptr;
+  for (size_t d = 0; d < n; d++) {
+    if (!errs[d]) continue;
+    if (!first) first = errs[d];
+    else b200_error_destroy(errs[d]);
+  }
+  if (first)
+    for (size_t d = 0; d < n; d++)
+      if (executables[d]) { b200_executable_destroy(executables[d]); executables[d] = nullptr; }
+  return first;
+}
+
+b200_error* b200_device_group_execute(b200_device_group* g, b200_executable* const* executables,
+                                      b200_buffer* const* const* argument_lists, size_t num_args, b200_buffer** const* output_lists,
+                                      b200_event** device_complete_events, const b200_execute_options* options) {
+  if (!g || !executables || !output_lists || (num_args && !argument_lists)) return make_error(B200_INVALID_ARGUMENT, "null argument");
+  const size_t n = g->clients.size();
+  for (size_t d = 0; d < n; d++)
+    if (!executables[d] || executables[d]->client != g->clients[d])
+      return make_error(B200_INVALID_ARGUMENT, "executable " + std::to_string(d) + " does not belong to device " + std::to_string(d) + " of the group");
+  std::vector<b200_error*> errs(n, nullptr);
+  std::vector<std::thread> threads;
+  for (size_t d = 0; d < n; d++)
+    threads.emplace_back([&, d] {
+      errs[d] = b200_executable_execute(executables[d], num_args ? argument_lists[d] : nullptr, num_args, output_lists[d],
+                                        device_complete_events ? &device_complete_events[d] : nullptr, options);
+    });
+  for (auto& t : threads) t.join();
+  b200_error* first = nullptr;
+  for (size_t d = 0; d < n; d++) {
+    if (!errs[d]) continue;
+    if (!first) first = make_error(errs[d]->code, "device " + std::to_string(d) + ": " + errs[d]->message);
+    b200_error_destroy(errs[d]);
+  }
+  return first;
 }
 
 b200_error* b200_client_debug_arm_wait_expiry(b200_client* c, int polls) {

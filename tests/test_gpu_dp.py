@@ -72,3 +72,57 @@ def test_two_gpu_step_is_the_mean_of_the_shard_steps(overlap):
         scale = max(1.0, float(np.max(np.abs(want))))
         np.testing.assert_allclose(got[0][0][i], want, rtol=1e-4, atol=1e-5 * scale, err_msg=f"result {i}")
     assert n_leaves == 62
+
+
+def _group_main(q):
+    """One process driving both GPUs through a device group (run in a child so that NVLS stays off for it)."""
+    sys.path.insert(0, str(ROOT / "jax-mps_b200"))
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        import b200
+        from b200.shlo import programs
+        world = 2
+        group = b200.DeviceGroup(num_devices=world)
+        prog = programs.resnet18_train_step(n_partitions=world, **CFG)
+        exes = group.compile(prog.text)
+        shard_args = [programs.resnet18_inputs(prog, rank=d) for d in range(world)]
+        arg_lists = [[group.devices[d].buffer_from_host(a) for a in shard_args[d]] for d in range(world)]
+        outs, events = group.execute(exes, arg_lists)
+        for e in events:
+            e.wait()
+        dp = [[o.to_numpy() for o in outs[d]] for d in range(world)]
+        devs = [outs[d][1].client is group.devices[d] for d in range(world)]
+        assign = exes[0].device_assignment()
+        topo = [d["id"] for d in group.devices[0].topology()["devices"]]
+        prog1 = programs.resnet18_train_step(n_partitions=1, **CFG)
+        single = b200.Client(device_ordinal=0)
+        exe1 = single.compile(prog1.text)
+        ones = [[o.to_numpy() for o in exe1.execute([single.buffer_from_host(a) for a in shard_args[d]])] for d in range(world)]
+        q.put((dp, ones, devs, assign, topo))
+    except Exception as e:
+        import traceback
+        q.put((repr(e) + traceback.format_exc(), None, None, None, None))
+
+
+def test_one_process_drives_two_devices_through_per_device_argument_lists():
+    """Both GPUs as devices of one process: argument_lists[d] / output_lists[d] / one completion event per device. The
+    result must be the mean of the two single-device shard steps and identical on both devices."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_group_main, args=(q,))
+    p.start()
+    dp, ones, devs, assign, topo = q.get(timeout=300)
+    p.join(timeout=60)
+    assert not isinstance(dp, str), dp
+    assert devs == [True, True] and topo == [0, 1]
+    assert assign == (1, 2, [[0], [1]])
+    np.testing.assert_allclose(dp[0][0], (ones[0][0] + ones[1][0]) / 2, rtol=1e-5)
+    for i in range(1, len(dp[0])):
+        np.testing.assert_array_equal(dp[0][i], dp[1][i], err_msg=f"devices differ at result {i}")
+        want = (ones[0][i].astype(np.float64) + ones[1][i].astype(np.float64)) / 2
+        scale = max(1.0, float(np.max(np.abs(want))))
+        np.testing.assert_allclose(dp[0][i], want, rtol=1e-4, atol=1e-5 * scale, err_msg=f"result {i}")
