@@ -678,6 +678,16 @@ class Builder:
             outs.append(y)
         return outs
 
+    def all_gather(self, x: Val, n_devices: int, dim: int = 0, channel: int = 100) -> Val:
+        """lax.all_gather(..., tiled=True) over all partitions of a fully-manual shard_map body: the operands of the
+        partitions concatenated along `dim` in partition order."""
+        groups = f"dense<[{list(range(n_devices))}]> : tensor<1x{n_devices}xi64>"
+        shape = tuple(d * n_devices if i == dim else d for i, d in enumerate(x.shape))
+        (y,) = self.emit("stablehlo.all_gather", [x], [(shape, x.dtype)],
+                         props={"all_gather_dim": f"{dim} : i64", "replica_groups": groups, "use_global_device_ids": "unit",
+                                "channel_handle": f"#stablehlo.channel_handle<handle = {channel}, type = 1>"})
+        return y
+
     def partition_id(self) -> Val:
         return self.emit("stablehlo.partition_id", [], [((), "ui32")])[0]
 

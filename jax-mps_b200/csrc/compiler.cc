@@ -718,7 +718,7 @@ struct SkinnyWeightHoist {
 // ---------------------------------------------------------------------------
 // op classification
 // ---------------------------------------------------------------------------
-enum class Cat { ELEMENTWISE, DUP, INDEXING, REDUCE, DOT, CONV, SCATTER, WHILE, CASE, ALL_REDUCE, RETURN, TOKEN, PARTITION_ID, UNSUPPORTED };
+enum class Cat { ELEMENTWISE, DUP, INDEXING, REDUCE, DOT, CONV, SCATTER, WHILE, CASE, ALL_REDUCE, ALL_GATHER, RETURN, TOKEN, PARTITION_ID, UNSUPPORTED };
 
 Cat categorize(Op* op) {
   const std::string sh = op->short_name();
@@ -737,6 +737,7 @@ Cat categorize(Op* op) {
   if (sh == "while") return Cat::WHILE;
   if (sh == "case") return Cat::CASE;
   if (sh == "all_reduce") return Cat::ALL_REDUCE;
+  if (sh == "all_gather") return Cat::ALL_GATHER;
   if (sh == "create_token" || sh == "after_all") return Cat::TOKEN;
   if (sh == "partition_id" || sh == "replica_id") return Cat::PARTITION_ID;
   return Cat::UNSUPPORTED;
@@ -746,7 +747,7 @@ void collect_unsupported(Block* b, std::set<std::string>& out, bool in_combiner)
   for (auto& op : b->ops) {
     Cat c = categorize(op.get());
     if (c == Cat::UNSUPPORTED) out.insert(op->name);
-    bool comb = c == Cat::REDUCE || c == Cat::SCATTER || c == Cat::ALL_REDUCE;
+    bool comb = c == Cat::REDUCE || c == Cat::SCATTER || c == Cat::ALL_REDUCE || c == Cat::ALL_GATHER;
     for (auto& r : op->regions) collect_unsupported(r.get(), out, comb);
   }
 }
@@ -2662,7 +2663,7 @@ struct Planner {
       for (int i = (int)st.ops.size() - 1; i >= 0; i--) {
         Op* op = st.ops[i];
         Cat c = categorize(op);
-        bool keep = c == Cat::RETURN || c == Cat::ALL_REDUCE;
+        bool keep = c == Cat::RETURN || c == Cat::ALL_REDUCE || c == Cat::ALL_GATHER;
         for (auto* r : op->results) {
           if (st.returned.count(r)) keep = true;
           for (auto* u : st.users[r])
@@ -2935,6 +2936,38 @@ struct Planner {
             s.bytes = op->operands[k]->type.bytes();
             ensure_slot(op->results[k], st);
             s.args = {slot_of.at(op->operands[k]), slot_of.at(op->results[k])};
+            plan.steps.push_back(std::move(s));
+          }
+          break;
+        }
+        case Cat::ALL_GATHER: {
+          // every partition contributes its operand; the result concatenates them along all_gather_dim in partition
+          // order (one group spanning all partitions, as for all_reduce). The reference has no collective beyond
+          // src/pjrt_plugin/ops/collectives.cc:20-78; a shard_map program over N devices needs this one too.
+          const int64_t dim = attr_int(op->attr("all_gather_dim"));
+          if (op->has("replica_groups")) {
+            DenseValue rg = attr_dense(op->attr("replica_groups"));
+            if (rg.type.rank() != 2) throw CompileError("all_gather: replica_groups must be rank 2");
+            int64_t groups = rg.type.dims[0], gsize = rg.type.dims[1];
+            if (groups > 1 || (gsize != opts.num_partitions && gsize != 0 && !(gsize == 1 && opts.num_partitions == 1)))
+              throw CompileError("all_gather: only one group spanning all " + std::to_string(opts.num_partitions) + " partitions is supported");
+          }
+          for (size_t k = 0; k < op->operands.size(); k++) {
+            Value *in = op->operands[k], *out = op->results[k];
+            if (dim < 0 || dim >= in->type.rank() || out->type.dims[dim] != in->type.dims[dim] * opts.num_partitions)
+              throw CompileError("all_gather: result extent along all_gather_dim must be " + std::to_string(opts.num_partitions) + " times the operand's");
+            ensure_slot(out, st);
+            if (in->type.numel() == 0) continue;
+            Step s;
+            s.kind = Step::ALL_GATHER;
+            s.label = op->name;
+            s.dtype = in->type.dt;
+            s.bytes = in->type.bytes();
+            int64_t outer = 1;
+            for (int64_t d = 0; d < dim; d++) outer *= in->type.dims[d];
+            s.iparams = {outer, (long long)(in->type.bytes() / std::max<int64_t>(outer, 1))};    // rows, bytes per row of the operand
+            s.args = {slot_of.at(in), slot_of.at(out)};
+            if (outer > 1 && opts.num_partitions > 1) s.args.push_back(new_slot(Slot::TEMP, out->type, st.arena));   // [partition][operand]
             plan.steps.push_back(std::move(s));
           }
           break;
@@ -3447,6 +3480,7 @@ void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& o
       case Step::CASE: os << "case branches=" << s.sub.size(); break;
       case Step::SCATTER: os << "scatter rows=" << s.iparams[0] << " row_elems=" << s.iparams[1] << " updates=" << s.iparams[2]; break;
       case Step::JOIN: os << "join"; break;
+      case Step::ALL_GATHER: os << "all_gather " << s.bytes << " bytes per partition, rows=" << s.iparams[0]; break;
       case Step::ALL_REDUCE:
         os << (s.overlapped ? "overlapped " : "") << "all_reduce " << s.bytes << " bytes in@" << prog.slots[s.args[0]].offset << " out@" << prog.slots[s.args[1]].offset;
         break;
@@ -3554,7 +3588,7 @@ std::unique_ptr<CompiledProgram> compile_module(Module& m, const CompileOptions&
     std::function<long long(const Plan&)> count = [&](const Plan& p) -> long long {
       long long n = 0;
       for (auto& s : p.steps) {
-        if (s.kind == Step::KERNEL || s.kind == Step::ALL_REDUCE) n += 1;
+        if (s.kind == Step::KERNEL || s.kind == Step::ALL_REDUCE || s.kind == Step::ALL_GATHER) n += 1;
         else if (s.kind == Step::SCATTER) n += 2;
         else if (s.kind == Step::IGEMM) n += s.ig.split_k > 1 ? 2 : 1;
         else if (s.kind == Step::GEMM16) n += (s.g16.path == 0 && s.g16.split_k > 1) ? 2 : 1;

@@ -50,7 +50,7 @@ struct IGemmParams {
 struct Plan;
 
 struct Step {
-  enum Kind { KERNEL, IGEMM, MEMCPY, MEMSET, WHILE, CASE, ALL_REDUCE, SCATTER, JOIN, GEMM16, REPACK16, TRANSPOSE } kind = KERNEL;
+  enum Kind { KERNEL, IGEMM, MEMCPY, MEMSET, WHILE, CASE, ALL_REDUCE, SCATTER, JOIN, GEMM16, REPACK16, TRANSPOSE, ALL_GATHER } kind = KERNEL;
   std::string label;                  // op names, for profiling and error text
   // KERNEL
   int kernel = -1;                    // index into Executable::kernels
@@ -78,6 +78,7 @@ struct Step {
   // compute stream wait for it
   bool overlapped = false;
   DT dtype = DT::F32;
+  // ALL_GATHER: args = {in, out, [staging]}; bytes = operand bytes; iparams = {rows before all_gather_dim, bytes per such row}
   // SCATTER: args = {operand, indices, updates, result, scratch...}
   std::vector<long long> iparams;
 };

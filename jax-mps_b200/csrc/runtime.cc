@@ -152,6 +152,7 @@ struct NcclApi {
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
   ncclResult_t (*CommInitAll)(ncclComm_t*, int, const int*);
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
   ncclResult_t (*CommDestroy)(ncclComm_t);
   ncclResult_t (*CommAbort)(ncclComm_t);
   ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*);
@@ -187,6 +188,7 @@ NcclApi& nccl() {
     get("ncclCommInitRank", (void**)&api.CommInitRank);
     get("ncclCommInitAll", (void**)&api.CommInitAll);
     get("ncclAllReduce", (void**)&api.AllReduce);
+    get("ncclAllGather", (void**)&api.AllGather);
     get("ncclCommDestroy", (void**)&api.CommDestroy);
     get("ncclCommAbort", (void**)&api.CommAbort);
     get("ncclCommGetAsyncError", (void**)&api.CommGetAsyncError);
@@ -650,6 +652,27 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       ncclResult_t r = nccl().AllReduce(in, out, s.bytes / dt_size(s.dtype), t, ncclSum, c->comm, x.coll_stream ? x.coll_stream : st);
       if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclAllReduce failed: ") + nccl().GetErrorString(r));
       x.launches++;
+      return nullptr;
+    }
+    case Step::ALL_GATHER: {
+      void *in = x.ptrs[s.args[0]], *out = x.ptrs[s.args[1]];
+      if (c->nprocs == 1) {
+        if (in != out && s.bytes) CUDA_TRY(cudaMemcpyAsync(out, in, s.bytes, cudaMemcpyDeviceToDevice, st));
+        return nullptr;
+      }
+      // bytes move as they are: gathered as unsigned bytes whatever the element type
+      const long long rows = s.iparams[0], row_bytes = s.iparams[1];
+      void* dst = rows > 1 ? x.ptrs[s.args[2]] : out;
+      ncclResult_t r = nccl().AllGather(in, dst, s.bytes, ncclUint8, c->comm, st);
+      if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclAllGather failed: ") + nccl().GetErrorString(r));
+      x.launches++;
+      if (rows > 1) {
+        // staging holds [partition][row][row_bytes]; the result wants [row][partition][row_bytes]
+        for (int p2 = 0; p2 < c->nprocs; p2++)
+          CUDA_TRY(cudaMemcpy2DAsync((char*)out + (size_t)p2 * row_bytes, (size_t)c->nprocs * row_bytes,
+                                     (char*)dst + (size_t)p2 * s.bytes, (size_t)row_bytes, (size_t)row_bytes, (size_t)rows,
+                                     cudaMemcpyDeviceToDevice, st));
+      }
       return nullptr;
     }
     case Step::WHILE: {

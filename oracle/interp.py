@@ -185,9 +185,10 @@ def _int_pow(a, b):
 
 class Interp:
     def __init__(self, module: Module | str, collective=None, partition_id: int = 0, conv_f64: bool = False,
-                 wide: bool = False):
+                 wide: bool = False, gather=None):
         self.m = mt.parse_module(module) if isinstance(module, str) else module
         self.collective = collective          # callable(list[np.ndarray]) -> list (sum over partitions)
+        self.gather = gather                  # callable(np.ndarray) -> list of every partition's array, in partition order
         self.partition_id = partition_id
         self.conv_f64 = conv_f64 or wide
         self.wide = wide
@@ -654,11 +655,11 @@ class Interp:
 
     def op_call(self, op, x, env):
         callee = op.attrs["callee"].strip().lstrip("@")
-        return Interp(self.m, self.collective, self.partition_id, self.conv_f64, self.wide).run(x, callee)
+        return Interp(self.m, self.collective, self.partition_id, self.conv_f64, self.wide, self.gather).run(x, callee)
 
     def op_composite(self, op, x, env):
         callee = op.attrs["decomposition"].strip().lstrip("@")
-        return Interp(self.m, self.collective, self.partition_id, self.conv_f64, self.wide).run(x, callee)
+        return Interp(self.m, self.collective, self.partition_id, self.conv_f64, self.wide, self.gather).run(x, callee)
 
     def op_optimization_barrier(self, op, x, env):
         return list(x)
@@ -680,6 +681,13 @@ class Interp:
         if self.collective is None:
             return list(x)                  # one partition: identity (src/pjrt_plugin/ops/collectives.cc:41-47)
         return self.collective(list(x))
+
+    def op_all_gather(self, op, x, env):
+        # every partition's operand, concatenated along all_gather_dim in partition order
+        dim = mt.attr_int(op.attrs["all_gather_dim"])
+        if self.gather is None:
+            return list(x)                  # one partition
+        return [np.concatenate(self.gather(v), axis=dim) for v in x]
 
     def op_partition_id(self, op, x, env):
         return [np.uint32(self.partition_id)]

@@ -126,3 +126,50 @@ def test_one_process_drives_two_devices_through_per_device_argument_lists():
         want = (ones[0][i].astype(np.float64) + ones[1][i].astype(np.float64)) / 2
         scale = max(1.0, float(np.max(np.abs(want))))
         np.testing.assert_allclose(dp[0][i], want, rtol=1e-4, atol=1e-5 * scale, err_msg=f"result {i}")
+
+
+def _gather_main(q):
+    sys.path.insert(0, str(ROOT / "jax-mps_b200"))
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        import b200
+        from b200.shlo.builder import Builder
+        world = 2
+        group = b200.DeviceGroup(num_devices=world)
+        b = Builder()
+        x, y = b.arg((6, 5), "f32"), b.arg((4, 3, 8), "bf16")
+        s_ = b.all_reduce_sum([x], world)[0]
+        text = b.module([b.all_gather(x, world, 0), b.all_gather(x, world, 1), b.all_gather(y, world, 1), s_], num_partitions=world)
+        exes = group.compile(text)
+        xs = [np.arange(30, dtype=np.float32).reshape(6, 5) + 100 * d for d in range(world)]
+        ys = [(np.arange(96, dtype=np.float32).reshape(4, 3, 8) - 40 * d) for d in range(world)]
+        args = [[group.devices[d].buffer_from_host(xs[d]), group.devices[d].buffer_from_host(ys[d], dtype="bf16")] for d in range(world)]
+        outs, events = group.execute(exes, args)
+        for e in events:
+            e.wait()
+        q.put(([[o.to_numpy() for o in outs[d]] for d in range(world)], xs, ys))
+    except Exception as e:
+        import traceback
+        q.put((repr(e) + traceback.format_exc(), None, None))
+
+
+def test_all_gather_over_two_devices():
+    """stablehlo.all_gather over NCCL: along the outermost dimension (gathered in place) and along inner dimensions
+    (gathered into a staging buffer and laid out by strided copies), f32 and bf16, beside an all_reduce of the same job;
+    both devices must hold the concatenation in partition order."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_gather_main, args=(q,))
+    p.start()
+    outs, xs, ys = q.get(timeout=300)
+    p.join(timeout=60)
+    assert not isinstance(outs, str), outs
+    for d in range(2):
+        np.testing.assert_array_equal(outs[d][0], np.concatenate(xs, 0))
+        np.testing.assert_array_equal(outs[d][1], np.concatenate(xs, 1))
+        np.testing.assert_array_equal(outs[d][2], np.concatenate(ys, 1))
+        np.testing.assert_array_equal(outs[d][3], xs[0] + xs[1])

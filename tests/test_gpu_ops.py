@@ -182,6 +182,20 @@ def test_transposes_concatenated_along_rows(client):
     np.testing.assert_array_equal(got[0], want[0])
 
 
+def test_collectives_on_one_partition_are_identities(client):
+    """all_reduce, all_gather and partition_id with one partition (src/pjrt_plugin/ops/collectives.cc:41-78)."""
+    b = Builder()
+    x = b.arg((7, 3), "f32")
+    outs = [b.all_gather(x, 1, 1), b.all_reduce_sum([x], 1)[0], b.convert(b.partition_id(), "i32")]
+    got, _ = run_gpu(client, b.module(outs), [f32(7, 3)])
+    want = interp.run_text(b.module(outs), [f32(7, 3)])
+    a = f32(7, 3)
+    got, _ = run_gpu(client, b.module(outs), [a])
+    np.testing.assert_array_equal(got[0], a)
+    np.testing.assert_array_equal(got[1], a)
+    assert int(got[2]) == 0
+
+
 def test_slice_pad_concat(client):
     """Negative and interior padding (src/pjrt_plugin/ops/slice.cc:202-276)."""
     b = Builder()

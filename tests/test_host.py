@@ -361,3 +361,25 @@ def test_profiler_stub_accepts_a_session_and_returns_an_empty_trace():
     with pytest.raises(b200.B200Error):
         p.stop()
     assert p.collect() == b""
+
+
+def test_all_gather_plans_and_oracle():
+    """stablehlo.all_gather over all partitions: one NCCL step per operand (with a staging buffer when the gathered
+    dimension is not the outermost); one partition is the identity; the interpreter concatenates what its `gather`
+    callable returns."""
+    from oracle import interp
+    b = Builder()
+    x = b.arg((6, 5), "f32")
+    text = b.module([b.all_gather(x, 4, 0), b.all_gather(x, 4, 1)], num_partitions=4)
+    plan = b200.compile_to_plan(text, num_processes=4, process_index=1)[0]
+    assert plan.count("all_gather 120 bytes per partition") == 2 and "rows=1" in plan and "rows=6" in plan
+    with pytest.raises(b200.B200Error):
+        b200.compile_to_plan(text, num_processes=2)           # the group must span the job
+    shards = [np.arange(30, dtype=np.float32).reshape(6, 5) + 100 * r for r in range(4)]
+    outs = interp.Interp(text, gather=lambda v: shards, partition_id=1).run([shards[1]])
+    np.testing.assert_array_equal(outs[0], np.concatenate(shards, 0))
+    np.testing.assert_array_equal(outs[1], np.concatenate(shards, 1))
+    b = Builder()
+    x = b.arg((6, 5), "f32")
+    one = b.module([b.all_gather(x, 1, 1)])
+    np.testing.assert_array_equal(interp.run_text(one, [shards[0]])[0], shards[0])
