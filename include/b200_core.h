@@ -301,8 +301,10 @@ int64_t b200_client_launch_count(const b200_client* client);
  * code inside a memory-pool callback or under a framework allocator's lock, and loops that may not take the
  * driver's allocation lock. The partial sums of the K splits live in an 8 MiB array inside the library image (held
  * by every GPU that loads the library, until exit), so 2 * m * n floats must fit in 8 MiB (m * n <= 1048576);
- * larger products are refused with B200_INVALID_ARGUMENT. The first call on each device looks up the array's
- * device address; make that call before any stream capture. All calls share the array and it keeps the last
+ * larger products are refused with B200_INVALID_ARGUMENT. The first call on each device loads the
+ * library's device image (with the array) and looks up the array's device address, which does take the driver's
+ * locks: make that call ahead of time, before entering the context that may not allocate and before any stream
+ * capture. All calls share the array and it keeps the last
  * call's contents (each call overwrites the part it reads, nothing needs to start at zero): calls that overlap
  * in time on one device, from different streams or threads, race - serialise them. */
 b200_error* b200_matmul_f32_static_scratch(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,

@@ -1622,7 +1622,7 @@ cudaError_t matmul_f32_static_scratch(const float* A, const float* B, float* C, 
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) { *why = "device ordinal out of range"; return cudaErrorInvalidDevice; }
-  std::lock_guard<std::mutex> lock(mu);     // also keeps two host threads from launching into the array at once
+  std::lock_guard<std::mutex> lock(mu);     // guards the address cache and serialises the enqueueing; launches that overlap on the GPU still race
   if (!resolved[dev]) {
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_static_scratch);

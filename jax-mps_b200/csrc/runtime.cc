@@ -292,6 +292,7 @@ struct PinnedBlock {
 
 struct LoadedProgram {
   std::unique_ptr<CompiledProgram> prog;
+  std::string text;                            // the module this plan was compiled from
   std::vector<const char*> output_kinds;       // PJRT_Executable_OutputMemoryKinds
   std::vector<size_t> output_kind_sizes;
   std::vector<CUmodule> modules;
@@ -325,12 +326,18 @@ struct b200_client {
   std::string kind, debug, version, memory_debug, memory_string;
   std::vector<std::string> topology_strings;
   std::atomic<int64_t> bytes_in_use{0}, peak_bytes{0}, num_allocs{0}, largest_alloc{0}, launches{0};
-  std::map<std::string, std::shared_ptr<LoadedProgram>> cache;    // program text hash -> loaded plan
+  // program text hash -> loaded plan. Entries are weak: the last executable handle releases the plan's arenas,
+  // constants, modules and loop graphs (as PJRT_LoadedExecutable_Destroy does in the reference). A hit is confirmed
+  // by comparing the text itself.
+  std::map<std::string, std::weak_ptr<LoadedProgram>> cache;
   std::vector<PinnedBlock> pinned;
   unsigned char* pred_host = nullptr;   // pinned byte for while-loop predicates
   int* error_flag = nullptr;            // device word raised by kernels whose bounded waits expire
   bool tensor_cores = true;
   bool profiling = false;
+  // debugging switches of the contraction kernels and the loop executor, read from the environment once at creation
+  struct Switches { bool no_vec_gather = false, no_seg_gather = false, no_tmem_a = false, no_half_ctas = false, narrow_tiles = false,
+                    no_loop_graphs = false; } sw;
   int reported_errors = 0;              // value of the error word at the last b200_client_synchronize
   int armed_wait_polls = 0;             // test hook: the next execution starts with a wait that runs out
   int* status_block = nullptr;          // pinned pairs handed to executions
@@ -592,12 +599,12 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       p.a_sh = s.ig.a_sh; p.a_sw = s.ig.a_sw;
       p.a_mcontig = s.ig.a_contig; p.b_kcontig = s.ig.b_contig; p.mask = s.ig.needs_mask;
       // tiny products stay on the fp32 FMA kernel; everything else goes to the tensor cores (3xTF32)
-      p.vec = s.ig.vec && !getenv("B200_NO_VEC_GATHER");
+      p.vec = s.ig.vec && !c->sw.no_vec_gather;
       p.c_vec = s.ig.c_vec;
-      p.seg = p.vec && s.ig.seg && !getenv("B200_NO_SEG_GATHER");
-      p.tmem_a = getenv("B200_NO_TMEM_A") ? 0 : 1;
-      p.half_ctas = getenv("B200_NO_HALF_CTAS") ? 0 : 1;
-      p.wide_n = getenv("B200_NARROW_TILES") ? 0 : 1;
+      p.seg = p.vec && s.ig.seg && !c->sw.no_seg_gather;
+      p.tmem_a = c->sw.no_tmem_a ? 0 : 1;
+      p.half_ctas = c->sw.no_half_ctas ? 0 : 1;
+      p.wide_n = c->sw.narrow_tiles ? 0 : 1;
       p.tensor_cores = c->tensor_cores && (long long)s.ig.M * s.ig.N * s.ig.K * s.ig.groups >= (1LL << 18) && s.ig.K >= 16;
       const void* tables[9];
       for (int k = 0; k < 9; k++) tables[k] = x.ptrs[s.args[3 + k]];
@@ -720,7 +727,7 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
         cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
         CUDA_TRY(cudaStreamIsCapturing(st, &capturing));
         if (s.trip_count >= 4 && !c->profiling && capturing == cudaStreamCaptureStatusNone && graph_safe(*s.sub[1]) &&
-            !getenv("B200_NO_LOOP_GRAPHS")) {
+            !c->sw.no_loop_graphs) {
           // Two iterations (after which exchanged pointers are back where they started) are recorded once as a
           // CUDA graph and replayed: the host issues one launch per pair instead of one per kernel, and the
           // dependent kernels of a latency-bound body follow each other without a host round trip.
@@ -855,7 +862,9 @@ b200_error* run_plan(ExecCtx& x, const Plan& plan) {
         for (size_t k = si; k < sj && flat; ++k) {
           const Step& q = plan.steps[k];
           flat = q.dtype == f.dtype && (char*)x.ptrs[q.args[0]] == in0 + total && (char*)x.ptrs[q.args[1]] == out0 + total;
-          total += (q.bytes + 255) & ~(size_t)255;
+          // leaves sit in 256-byte granules; the last one counts with its own size, so that the reduction never
+          // reaches past the end of the last allocation
+          total += k + 1 < sj ? (q.bytes + 255) & ~(size_t)255 : q.bytes;
         }
         bool ok = false;
         ncclDataType_t nt = nccl_type(f.dtype, &ok);
@@ -1015,6 +1024,12 @@ b200_error* create_client(const b200_client_options* o, ncclComm_t given_comm, b
   memset(c->status_block, 0, 2 * sizeof(int) * b200_client::kStatusPairs);
   for (int k = b200_client::kStatusPairs - 1; k >= 0; k--) c->free_status.push_back(k);
   if (const char* e2 = getenv("B200_NO_TENSOR_CORES")) c->tensor_cores = atoi(e2) == 0;
+  c->sw.no_vec_gather = getenv("B200_NO_VEC_GATHER") != nullptr;
+  c->sw.no_seg_gather = getenv("B200_NO_SEG_GATHER") != nullptr;
+  c->sw.no_tmem_a = getenv("B200_NO_TMEM_A") != nullptr;
+  c->sw.no_half_ctas = getenv("B200_NO_HALF_CTAS") != nullptr;
+  c->sw.narrow_tiles = getenv("B200_NARROW_TILES") != nullptr;
+  c->sw.no_loop_graphs = getenv("B200_NO_LOOP_GRAPHS") != nullptr;
   if (!driver().ok) return make_error(B200_FAILED_PRECONDITION, driver().error);
   if (c->nprocs > 1) {
     NcclApi& n = nccl();
@@ -1153,13 +1168,27 @@ b200_error* b200_client_compile(b200_client* c, const char* code, size_t code_si
   co.partition_id = c->rank;
   co.num_partitions = c->nprocs;
   char key[64];
-  snprintf(key, sizeof key, "%016llx-%d-%d-%d", (unsigned long long)hash_text(code, code_size, 0), (int)co.fuse, c->rank,
-           c->nprocs);
+  // planning switches read from the environment are part of the key (a plan made with one setting must not answer
+  // for another)
+  unsigned env_bits = 0;
+  {
+    static const char* names[] = {"B200_NO_WINDOW_UPDATE", "B200_NO_FLAT_ALL_REDUCE", "B200_NO_GEMM16", "B200_NO_ROW_FUSION",
+                                  "B200_NO_WEIGHT_HOIST", "B200_NO_LICM", "B200_NO_CSE", "B200_NO_HOIST", "B200_NO_BUNDLES",
+                                  "B200_NO_TILED_TRANSPOSE", "B200_ALL_REDUCE_OVERLAP", "B200_DEBUG_NO_REUSE", "B200_NO_COL4"};
+    for (size_t k = 0; k < sizeof names / sizeof names[0]; k++)
+      if (getenv(names[k])) env_bits |= 1u << k;
+  }
+  snprintf(key, sizeof key, "%016llx-%d-%d-%d-%x", (unsigned long long)hash_text(code, code_size, 0), (int)co.fuse, c->rank,
+           c->nprocs, env_bits);
   auto hit = c->cache.find(key);
   std::shared_ptr<LoadedProgram> lp;
-  if (hit != c->cache.end()) lp = hit->second;
-  else {
+  if (hit != c->cache.end()) {
+    lp = hit->second.lock();
+    if (lp && (lp->text.size() != code_size || memcmp(lp->text.data(), code, code_size) != 0)) lp.reset();   // same hash, other text
+  }
+  if (!lp) {
     lp = std::make_shared<LoadedProgram>();
+    lp->text.assign(code, code_size);
     try {
       auto m = parse_module(code, code_size);
       int np = (o && o->num_partitions > 0) ? o->num_partitions : 0;
@@ -1263,6 +1292,14 @@ b200_error* b200_compile_to_plan(const char* code, size_t code_size, const b200_
 }
 
 b200_error* b200_executable_destroy(b200_executable* e) {
+  if (!e) return nullptr;
+  b200_client* c = e->client;
+  std::lock_guard<std::recursive_mutex> lock(c->mu);
+  if (e->lp.use_count() == 1) {
+    // the last handle: the device must be done with the plan's memory before it is freed
+    cudaSetDevice(c->ordinal);
+    cudaStreamSynchronize(c->compute);
+  }
   delete e;
   return nullptr;
 }
@@ -1989,7 +2026,8 @@ b200_error* b200_profiler_destroy(b200_profiler* p) {
 b200_error* b200_matmul_f32_static_scratch(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                                            void* cuda_stream) {
   if (!a || !b || !c) return make_error(B200_INVALID_ARGUMENT, "null operand pointer");
-  if (m <= 0 || n <= 0 || k <= 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX || m * k > INT32_MAX * 64ll ||
+  // (the kernel rounds K up to whole chunks in 32-bit arithmetic: keep a margin below INT32_MAX)
+  if (m <= 0 || n <= 0 || k <= 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX - 4096 || m * k > INT32_MAX * 64ll ||
       k * n > INT32_MAX * 64ll)
     return make_error(B200_INVALID_ARGUMENT, "matrix extents must be positive and fit the kernel's index range");
   const char* why = nullptr;

@@ -39,7 +39,8 @@ def initialize() -> None:
         raise B200PluginError("jax is not installed; use the `b200.Client` API directly") from e
     lib = _find_library()
     if lib is None:
-        raise B200PluginError(f"{_LIB_NAME} not found: build the PJRT adapter against xla/pjrt/c/pjrt_c_api.h "
-                              "(see INTEGRATION.md) or set B200_PJRT_LIBRARY_PATH")
+        raise B200PluginError(f"{_LIB_NAME} not found: compile the PJRT function-table adapter (one forwarding function per "
+                              "entry of include/b200_core.h, built against xla/pjrt/c/pjrt_c_api.h) and place it beside this "
+                              "file, or point B200_PJRT_LIBRARY_PATH at it")
     # The plugin executes per-shard programs itself; there is no SPMD partitioner behind it.
     xb.register_plugin("b200", priority=500, library_path=lib, options=None)

@@ -51,3 +51,22 @@ def test_products_beyond_the_static_scratch_are_refused(client):
     out = client.buffer_from_host(np.zeros((2048, 1024), np.float32))
     with pytest.raises(b200.B200Error, match="static scratch"):
         client.matmul_static_scratch(a, w, out)
+
+
+def test_a_call_allocates_no_device_memory(client):
+    """After a first call on the device (which loads the library image and looks up the array's address), a call leaves
+    the client's allocation counters and the device's free memory where they were."""
+    import torch
+    rng = np.random.default_rng(11)
+    a = client.buffer_from_host(rng.standard_normal((128, 512)).astype(np.float32))
+    w = client.buffer_from_host(rng.standard_normal((512, 96)).astype(np.float32))
+    out = client.buffer_from_host(np.zeros((128, 96), np.float32))
+    client.matmul_static_scratch(a, w, out)             # warm-up
+    client.synchronize()
+    before, free_before = client.memory_stats(), torch.cuda.mem_get_info(0)[0]
+    for _ in range(3):
+        client.matmul_static_scratch(a, w, out)
+    client.synchronize()
+    after, free_after = client.memory_stats(), torch.cuda.mem_get_info(0)[0]
+    assert (after.num_allocs, after.bytes_in_use) == (before.num_allocs, before.bytes_in_use)
+    assert free_after == free_before
