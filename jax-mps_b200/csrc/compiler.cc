@@ -1714,6 +1714,24 @@ struct Planner {
     }
     p.a_contig = (sl[lf] == 1 && Cg > 1) ? 0 : (batch_fastest ? 1 : 0);
     p.b_contig = sr[ro] == 1 ? 0 : 1;
+    // TMA feed of A: stride-1 two-dimensional convolution without input dilation over a dense NHWC input with a
+    // multiple of 32 channels, output rows dividing the 128-row tile (make_igemm drops it again where the row gather
+    // kernel with A in tensor memory is not the one that runs)
+    if (!one_d && groups == 1 && stride[0] == 1 && stride[1] == 1 && p.ldh == 1 && p.ldw == 1 && !batch_fastest &&
+        sl[lf] == 1 && sl1 == Cin && sl[l0] == W * Cin && sl[lb] == H * W * Cin && Cin % 32 == 0 && OW >= 1 && 128 % OW == 0 &&
+        OW <= 256 && !getenv("B200_NO_TMA_A")) {
+      const int64_t rows_per_tile = 128 / OW;                    // output rows in a tile
+      const int64_t box_h = std::min<int64_t>(OH, rows_per_tile);
+      const int64_t box_n = std::max<int64_t>(1, rows_per_tile / OH);
+      const bool whole = OH % box_h == 0 && (box_n == 1 || OH * OW * box_n == 128) && (box_n == 1 || rows_per_tile % OH == 0);
+      if (whole && box_h <= 256 && box_n <= 256 && H < (1 << 15) && W < (1 << 15)) {
+        p.a_tma = 1;
+        p.tma_c = (int)Cin; p.tma_w = (int)W; p.tma_h = (int)H; p.tma_n = (int)Nb;
+        p.tma_ow = (int)OW; p.tma_oh = (int)OH; p.tma_box_h = (int)box_h; p.tma_box_n = (int)box_n;
+        p.tma_kw = (int)KW; p.tma_pad_h = (int)pad[0]; p.tma_pad_w = (int)pad[2];
+        p.tma_rdil_h = (int)rdil[0]; p.tma_rdil_w = (int)rdil[1];
+      }
+    }
     return make_igemm(op, p, lhs, rhs, out, arow, acol, bcol, bn, crow, cn, ag, bg, cg, st);
   }
 
@@ -1905,6 +1923,7 @@ struct Planner {
       for (auto v : cg) al = al && v % 4 == 0;
       if (al) p.c_vec = 2;
     }
+    if (!(p.seg && p.a_contig == 0)) p.a_tma = 0;
     choose_split_k(p);
     Step s;
     s.kind = Step::IGEMM;
@@ -1944,6 +1963,7 @@ struct Planner {
         kept += cnt;
       }
       if (kept < (long long)mtiles * ktiles) {
+        s.ig.a_tma = 0;
         s.ig.kt_stride = ktiles;
         s.args.push_back(tab(table.data(), table.size() * sizeof(int)));
       }
@@ -3461,7 +3481,7 @@ void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& o
         break;
       case Step::IGEMM:
         os << "igemm M=" << s.ig.M << " N=" << s.ig.N << " K=" << s.ig.K << " G=" << s.ig.groups << " splitK=" << s.ig.split_k
-           << " a_contig=" << s.ig.a_contig << " b_contig=" << s.ig.b_contig << " vec=" << s.ig.vec << " seg=" << s.ig.seg << (s.ig.kt_stride ? " ktlist" : "") << " " << s.label;
+           << " a_contig=" << s.ig.a_contig << " b_contig=" << s.ig.b_contig << " vec=" << s.ig.vec << " seg=" << s.ig.seg << (s.ig.kt_stride ? " ktlist" : "") << (s.ig.a_tma ? " tmaA" : "") << " " << s.label;
         break;
       case Step::MEMCPY: os << "memcpy " << s.bytes; break;
       case Step::GEMM16:

@@ -655,6 +655,24 @@ bool make_map(CUtensorMap* map, const void* base, int in_fmt, long long inner, l
   return r == CUDA_SUCCESS;
 }
 
+}  // namespace
+
+// Tiled tensor map with the 128-byte swizzle over this GPU's memory: `kind` 0 f16, 1 bf16, 2 f32; dims[0] is the
+// contiguous dimension; strides (bytes) belong to dims[1..]. False when the driver refuses (alignment, extents).
+bool encode_tensor_map(void* map, int kind, int rank, const void* base, const unsigned long long* dims,
+                       const unsigned long long* strides_bytes, const unsigned* box) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc || rank < 1 || rank > 5) return false;
+  cuuint64_t d[5], st[5];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; i++) { d[i] = dims[i]; bx[i] = box[i]; es[i] = 1; if (i + 1 < rank) st[i] = strides_bytes[i]; }
+  const CUtensorMapDataType dt = kind == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : (kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  return enc((CUtensorMap*)map, dt, (cuuint32_t)rank, (void*)base, d, st, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+namespace {
+
 int sm_count() {
   static int n = 0;
   if (!n) {

@@ -14,11 +14,13 @@
 //     0 <= ih < Hd, 0 <= iw < Wd, ih % ldh == 0 and iw % ldw == 0   (dilate, then pad: linalg.cc:508-532)
 //   B address = b_grp[g] + b_row[k] + b_col[n]
 //   C address = c_grp[g] + c_row[m] + c_col[n]
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <algorithm>
 #include <mutex>
 #include <cstdio>
+#include <cstring>
 
 #include "kernels.h"
 #include "tc_util.cuh"
@@ -1070,7 +1072,7 @@ __global__ void __launch_bounds__((TaCfg<BN, HALF>::THREADS), (HALF ? 2 : 1)) ig
     const ColEnt* __restrict__ a_col, const long long* __restrict__ b_row, const long long* __restrict__ b_col,
     const long long* __restrict__ c_row, const long long* __restrict__ c_col, const long long* __restrict__ a_grp,
     const long long* __restrict__ b_grp, const long long* __restrict__ c_grp, float* __restrict__ partial,
-    const int* __restrict__ kt_table, int* __restrict__ error_flag, IGemmLaunch p) {
+    const int* __restrict__ kt_table, int* __restrict__ error_flag, const __grid_constant__ CUtensorMap tm_a, IGemmLaunch p) {
   using Cfg = TaCfg<BN, HALF>;
   constexpr int S = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -1103,7 +1105,7 @@ __global__ void __launch_bounds__((TaCfg<BN, HALF>::THREADS), (HALF ? 2 : 1)) ig
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(smem_u32(&landed_a[s]), 128);
+      mbar_init(smem_u32(&landed_a[s]), p.a_tma ? 1 : 128);      // one arrival that announces the copy's bytes, or 128 gather threads
       mbar_init(smem_u32(&landed_b[s]), NBW * 32);
       mbar_init(smem_u32(&a_ready[s]), 128);
       mbar_init(smem_u32(&b_ready[s]), N_LOW);
@@ -1132,7 +1134,37 @@ __global__ void __launch_bounds__((TaCfg<BN, HALF>::THREADS), (HALF ? 2 : 1)) ig
   };
   auto lo1_safe = [&](float x) -> float { return fabsf(x) == INFINITY ? 0.f : lo1(x); };
 
-  if (warp < W_CONV) {
+  if (p.a_tma && warp < W_B) {
+    // ------------------------------ A by TMA ------------------------------------------------------------------
+    // A stride-1 convolution over a dense NHWC input: the 128 rows of this tile are whole output rows, so the A tile
+    // of a k-tile (32 channels at one filter tap) is one box of the input, 32 channels x OW pixels x rows x images,
+    // and arrives by a single tiled copy in the swizzled row layout the converter threads read; taps that reach
+    // outside the image read zeros. One lane of the first warp issues the copies; the other gather warps rest.
+    if (warp == 0) {
+      const int pixels = p.tma_oh * p.tma_ow;
+      const int n0 = m0 / pixels, oh0 = (m0 % pixels) / p.tma_ow;
+      const int c_tiles = p.tma_c / TBK;
+      for (int j = 0; j < ktiles; ++j) {
+        const int s = j % S;
+        bool ok = true;
+        if (j >= S) ok = !*failed && mbar_wait(smem_u32(&empty[s]), (uint32_t)((j / S - 1) & 1));
+        if (!__all_sync(0xFFFFFFFFu, ok)) { *failed = 1; break; }
+        if (elect_one()) {
+          const int kt = kbeg / TBK + j;
+          const int tap = kt / c_tiles, c0 = (kt - tap * c_tiles) * TBK;
+          const int kh = tap / p.tma_kw, kw = tap - kh * p.tma_kw;
+          const uint32_t bar = smem_u32(&landed_a[s]);
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)Cfg::A_BYTES) : "memory");
+          asm volatile(
+              "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+              ::"r"(smem_u32(smem + s * Cfg::STAGE_BYTES)), "l"(&tm_a), "r"(bar), "r"(c0), "r"(kw * p.tma_rdil_w - p.tma_pad_w),
+                "r"(oh0 + kh * p.tma_rdil_h - p.tma_pad_h), "r"(n0)
+              : "memory");
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp < W_CONV) {
     // ------------------------------ gather -----------------------------------------------------------------
     // A groups take the A tiles of k-tiles group, group + A_GROUPS, ...; the B warps take every B tile
     const int a_sh = (int)p.a_sh, a_sw = (int)p.a_sw;
@@ -1443,6 +1475,16 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
 #undef SETALLW
 #undef SETATTRW
       }
+      alignas(64) CUtensorMap tm_a;
+      memset(&tm_a, 0, sizeof tm_a);
+      IGemmLaunch pl = p;
+      if (p.a_tma && p.seg && p.tmem_a) {
+        const unsigned long long dims[4] = {(unsigned long long)p.tma_c, (unsigned long long)p.tma_w, (unsigned long long)p.tma_h,
+                                            (unsigned long long)p.tma_n};
+        const unsigned long long strides[3] = {4ull * p.tma_c, 4ull * p.tma_c * p.tma_w, 4ull * p.tma_c * p.tma_w * p.tma_h};
+        const unsigned box[4] = {(unsigned)TBK, (unsigned)p.tma_ow, (unsigned)p.tma_box_h, (unsigned)p.tma_box_n};
+        if (!encode_tensor_map(&tm_a, 2, 4, A, dims, strides, box)) pl.a_tma = 0;      // fall back to the gather
+      } else pl.a_tma = 0;
       const bool wide = p.N >= 128 && p.wide_n;
       // two half-size CTAs per SM for 64-wide tiles once the grid has more than one wave of full-size CTAs
       const long long ctas64 = (long long)((p.M + TBM - 1) / TBM) * ((p.N + 63) / 64) * p.groups * p.split_k;
@@ -1452,11 +1494,11 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
   if (p.seg && p.tmem_a && half)                                                                                      \
     igemm_tf32x3_ta_kernel<64, AM, BK_, MK, true><<<gridw, TaCfg<64, true>::THREADS, TaCfg<64, true>::SMEM, stream>>>( \
         (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
-        (float*)partial, kt_table, error_flag, p);                                                                    \
+        (float*)partial, kt_table, error_flag, tm_a, pl);                                                             \
   else if (p.seg && p.tmem_a)                                                                                         \
     igemm_tf32x3_ta_kernel<BN_, AM, BK_, MK, false><<<gridw, TaCfg<BN_, false>::THREADS, TaCfg<BN_, false>::SMEM, stream>>>( \
         (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
-        (float*)partial, kt_table, error_flag, p);                                                                    \
+        (float*)partial, kt_table, error_flag, tm_a, pl);                                                             \
   else if (p.seg)                                                                                                     \
     igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK, true><<<gridw, WS_THREADS, WsCfg<BN_>::SMEM, stream>>>(                  \
         (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \

@@ -19,6 +19,10 @@ struct IGemmLaunch {
   int half_ctas;                 // allow the two-CTAs-per-SM variant of the tensor-memory kernel
   int c_vec;                     // consecutive n are consecutive floats in C (2: and rows start on multiples of four floats)
   int wide_n;                    // use 128-wide N tiles when N >= 128
+  // A by TMA (IGemmParams::a_tma): input extents, output row geometry, filter tap geometry
+  int a_tma = 0;
+  int tma_c = 0, tma_w = 0, tma_h = 0, tma_n = 0, tma_ow = 0, tma_oh = 0, tma_box_h = 0, tma_box_n = 0;
+  int tma_kw = 0, tma_pad_h = 0, tma_pad_w = 0, tma_rdil_h = 1, tma_rdil_w = 1;
 };
 
 // tables: a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp (device pointers).
@@ -66,6 +70,11 @@ namespace b200 {
 //   path 1  gemv16_nc_kernel  : M <= 8 and n contiguous in B: every element of B is read once with 128-bit loads,
 //                               K split over warps and CTAs, the last CTA of a column panel adds the splits in order
 //   path 2  gemv16_kc_kernel  : M <= 8 and k contiguous in B: one warp per group of output columns, warp-shuffle tree
+// Tiled tensor map (128-byte swizzle) over this GPU's memory for TMA copies: `kind` 0 f16, 1 bf16, 2 f32; dims[0] is
+// the contiguous dimension, strides_bytes[i] the stride of dims[i + 1]; `map` points at 128 bytes aligned to 64.
+bool encode_tensor_map(void* map, int kind, int rank, const void* base, const unsigned long long* dims,
+                       const unsigned long long* strides_bytes, const unsigned* box);
+
 // `scratch` (fp32, g.scratch_floats) and `counters` may be null when the plan needs none.
 cudaError_t launch_gemm16(const Gemm16Launch& g, const void* A, const void* B, void* C, float* scratch, int* counters,
                           int* error_flag, cudaStream_t stream, int* launches, const char** why);

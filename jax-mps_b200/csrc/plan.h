@@ -45,6 +45,13 @@ struct IGemmParams {
   int kt_stride = 0;                         // > 0: the last igemm arg is a table [m-tile][1 + kt_stride] of k-tiles to visit
   int seg = 0;                               // vec, and aligned runs of 32 along the contiguous dimensions are uniform
   int c_vec = 0;                             // consecutive n are consecutive floats in C (2: and rows start on multiples of four floats)
+  // A operand of a stride-1 convolution over a dense NHWC input whose 128-row tiles are whole output rows: every
+  // k-tile of A is one box of the input (32 channels x OW pixels x rows x images at one filter tap), fetched by a
+  // single TMA tiled copy with zero fill outside the image instead of a table-driven gather.
+  int a_tma = 0;
+  int tma_c = 0, tma_w = 0, tma_h = 0, tma_n = 0;        // input extents (channels, width, height, images)
+  int tma_ow = 0, tma_oh = 0, tma_box_h = 0, tma_box_n = 0;
+  int tma_kw = 0, tma_pad_h = 0, tma_pad_w = 0, tma_rdil_h = 1, tma_rdil_w = 1;
 };
 
 struct Plan;

@@ -337,7 +337,7 @@ struct b200_client {
   bool profiling = false;
   // debugging switches of the contraction kernels and the loop executor, read from the environment once at creation
   struct Switches { bool no_vec_gather = false, no_seg_gather = false, no_tmem_a = false, no_half_ctas = false, narrow_tiles = false,
-                    no_loop_graphs = false; } sw;
+                    no_loop_graphs = false, no_tma_a = false; } sw;
   int reported_errors = 0;              // value of the error word at the last b200_client_synchronize
   int armed_wait_polls = 0;             // test hook: the next execution starts with a wait that runs out
   int* status_block = nullptr;          // pinned pairs handed to executions
@@ -610,6 +610,11 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       for (int k = 0; k < 9; k++) tables[k] = x.ptrs[s.args[3 + k]];
       void* partial = s.ig.split_k > 1 ? x.ptrs[s.args[12]] : nullptr;
       p.kt_stride = s.ig.kt_stride;
+      p.a_tma = s.ig.a_tma && p.seg && p.tmem_a && !c->sw.no_tma_a;
+      p.tma_c = s.ig.tma_c; p.tma_w = s.ig.tma_w; p.tma_h = s.ig.tma_h; p.tma_n = s.ig.tma_n;
+      p.tma_ow = s.ig.tma_ow; p.tma_oh = s.ig.tma_oh; p.tma_box_h = s.ig.tma_box_h; p.tma_box_n = s.ig.tma_box_n;
+      p.tma_kw = s.ig.tma_kw; p.tma_pad_h = s.ig.tma_pad_h; p.tma_pad_w = s.ig.tma_pad_w;
+      p.tma_rdil_h = s.ig.tma_rdil_h; p.tma_rdil_w = s.ig.tma_rdil_w;
       const int* kt_table = s.ig.kt_stride > 0 ? (const int*)x.ptrs[s.args.back()] : nullptr;
       cudaError_t e = launch_igemm_f32(p, x.ptrs[s.args[0]], x.ptrs[s.args[1]], x.ptrs[s.args[2]], tables, partial,
                                        kt_table, c->error_flag, st, &x.launches);
@@ -1030,6 +1035,7 @@ b200_error* create_client(const b200_client_options* o, ncclComm_t given_comm, b
   c->sw.no_half_ctas = getenv("B200_NO_HALF_CTAS") != nullptr;
   c->sw.narrow_tiles = getenv("B200_NARROW_TILES") != nullptr;
   c->sw.no_loop_graphs = getenv("B200_NO_LOOP_GRAPHS") != nullptr;
+  c->sw.no_tma_a = getenv("B200_NO_TMA_A") != nullptr;
   if (!driver().ok) return make_error(B200_FAILED_PRECONDITION, driver().error);
   if (c->nprocs > 1) {
     NcclApi& n = nccl();

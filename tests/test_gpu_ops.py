@@ -301,6 +301,30 @@ def test_strided_convolution_input_gradient_with_skipped_k_tiles(client):
               rtol=1e-5, atol=1e-5, scale_atol=True)
 
 
+@pytest.mark.parametrize("n,h,w,ci,co,k,pad,rdil", [
+    (4, 32, 32, 64, 64, 3, 1, 1),        # four output rows per tile
+    (6, 16, 16, 32, 96, 3, 1, 1),        # eight rows per tile
+    (3, 8, 8, 64, 128, 3, 1, 1),         # two images per tile, a ragged last tile (192 rows)
+    (20, 4, 4, 96, 64, 3, 1, 1),         # eight images per tile
+    (5, 16, 16, 64, 32, 1, 0, 1),        # 1 x 1
+    (2, 16, 16, 32, 64, 5, 2, 1),        # 5 x 5
+    (2, 16, 16, 32, 64, 3, 2, 2),        # kernel dilation 2, same size
+    (4, 18, 18, 32, 64, 3, 0, 1),        # no padding: 16 x 16 outputs from an 18 x 18 input (its input gradient has 18-pixel rows: gathered)
+])
+def test_stride_one_convolution_with_tma_fed_operand(client, n, h, w, ci, co, k, pad, rdil):
+    """Stride-1 convolutions over NHWC inputs with a multiple of 32 channels whose 128-row tiles are whole output rows:
+    the A operand arrives by TMA boxes (plan tag `tmaA`), forward and input gradient, against the oracle."""
+    b = Builder()
+    x, wt = b.arg((n, h, w, ci), "f32"), b.arg((k, k, ci, co), "f32")
+    y = b.conv(x, wt, padding=((pad, pad), (pad, pad)), rhs_dilation=(rdil, rdil))
+    g = b.arg(y.shape, "f32")
+    dx, dw = b.grad(b.reduce_sum(b.mul(y, g), (0, 1, 2, 3)), [x, wt])
+    text = b.module([y, dx, dw])
+    plan, _ = b200.compile_to_plan(text)
+    assert plan.count("tmaA") == (1 if pad == 0 and k > 1 else 2), plan
+    check(client, text, [f32(n, h, w, ci), f32(k, k, ci, co), f32(*y.shape)], rtol=1e-5, atol=1e-5, scale_atol=True)
+
+
 @pytest.mark.parametrize("ci", [1, 3, 5, 7])
 def test_small_channel_convolution_and_gradients(client, ci):
     """Convolutions whose input has a few channels (not a multiple of 4): forward, input gradient and weight
