@@ -824,7 +824,8 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
       if (!valid) o = -1;
       if (j >= S) {
         // the MMAs of tile j - S were the last readers of this stage
-        if (*failed || !mbar_wait(smem_u32(&empty[s]), (uint32_t)((j / S - 1) & 1))) { *failed = 1; return false; }
+        // the warp leaves together: the shuffles below name every lane
+        if (!__all_sync(0xFFFFFFFFu, !*failed && mbar_wait(smem_u32(&empty[s]), (uint32_t)((j / S - 1) & 1)))) { *failed = 1; return false; }
       }
       const uint32_t x = smem_u32(smem + s * Cfg::STAGE_BYTES);
 #pragma unroll
@@ -1224,7 +1225,8 @@ __global__ void __launch_bounds__((TaCfg<BN, HALF>::THREADS), (HALF ? 2 : 1)) ig
       if (!valid) o = -1;
       if (j >= S) {
         // the MMAs of tile j - S were the last readers of this stage (shared memory and tensor memory)
-        if (*failed || !mbar_wait(smem_u32(&empty[s]), (uint32_t)((j / S - 1) & 1))) { *failed = 1; return false; }
+        // the warp leaves together: the shuffles below name every lane
+        if (!__all_sync(0xFFFFFFFFu, !*failed && mbar_wait(smem_u32(&empty[s]), (uint32_t)((j / S - 1) & 1)))) { *failed = 1; return false; }
       }
       const uint32_t x = smem_u32(smem + s * Cfg::STAGE_BYTES);
 #pragma unroll
