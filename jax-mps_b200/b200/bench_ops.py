@@ -8,6 +8,12 @@ captures summarised under profiles/, and handy when tuning a kernel):
     python -m b200.bench_ops distilbert [--reps 5] [--profile]
     python -m b200.bench_ops gemm --shape M,N,K [--reps 20]
     python -m b200.bench_ops gemv --shape M,N,K --layout kc|nc [--reps 50]
+    python -m b200.bench_ops pointwise | transpose | softmax | gather | scatter [--dtype f32|bf16] [--reps 20]
+
+`pointwise` is a batch-norm apply + residual + ReLU over a stage-1 activation (three tensors read, one written);
+`transpose` a 2-D transpose of 8192 x 6144 elements (the tiled shared-memory kernel); `softmax` the attention softmax
+of the DistilBERT-shaped step (49 152 rows of 128, one generated row kernel); `gather` / `scatter` the word-embedding
+lookup of 4096 rows of 768 and its gradient (deterministic scatter-add into 30 522 rows).
 
 `gemma` times the Gemma-2B-shaped prefill (512 prompt tokens in one pass) and the 128-step greedy decode loop (bf16
 weights resident in HBM); `distilbert` the DistilBERT-base-shaped masked-LM step (forward + backward, bf16); `gemm` one
@@ -252,9 +258,66 @@ def gemv(client, m, n, k, layout, reps, hbm_gbs=6546.2):
           " | ".join(l.strip()[:80] for l in exe.plan_text().splitlines()[1:]))
 
 
+def simple(client, what, dtype, reps):
+    """One-operation programs of the HBM-bound kernel classes; prints microseconds per execution and the algorithmic
+    bytes (inputs read once + outputs written once) per second."""
+    rng = np.random.default_rng(0)
+    b = Builder()
+    es = 4 if dtype == "f32" else 2
+    f = lambda shape: rng.standard_normal(shape).astype(np.float32)
+    if what == "pointwise":
+        shape = (128, 32, 32, 64)
+        x, r, sc, sh = b.arg(shape, dtype), b.arg(shape, dtype), b.arg((64,), dtype), b.arg((64,), dtype)
+        y = b.add(b.mul(x, b.broadcast_in_dim(sc, shape, (3,))), b.broadcast_in_dim(sh, shape, (3,)))
+        y = b.max(b.add(y, r), b.full(shape, 0.0, dtype))
+        text, arrays = b.module([y]), [f(shape), f(shape), f((64,)), f((64,))]
+        nbytes = 3 * int(np.prod(shape)) * es
+    elif what == "transpose":
+        shape = (8192, 6144)
+        x = b.arg(shape, dtype)
+        text, arrays = b.module([b.transpose(x, (1, 0))]), [f(shape)]
+        nbytes = 2 * int(np.prod(shape)) * es
+    elif what == "softmax":
+        shape = (32 * 12 * 128, 128)
+        x = b.arg(shape, dtype)
+        xf = b.convert(x, "f32") if dtype != "f32" else x
+        m = b.reduce_max(xf, (1,))
+        e = b.exp(b.sub(xf, b.broadcast_in_dim(m, shape, (0,))))
+        p = b.div(e, b.broadcast_in_dim(b.reduce_sum(e, (1,)), shape, (0,)))
+        text, arrays = b.module([b.convert(p, dtype) if dtype != "f32" else p]), [f(shape)]
+        nbytes = 2 * int(np.prod(shape)) * es
+    elif what == "gather":
+        table, idx = b.arg((30522, 768), dtype), b.arg((4096,), "i32")
+        text = b.module([b.take_rows(table, idx)])
+        arrays = [f((30522, 768)), rng.integers(0, 30522, (4096,)).astype(np.int32)]
+        nbytes = 2 * 4096 * 768 * es
+    else:
+        table, idx, upd = b.arg((30522, 768), dtype), b.arg((4096,), "i32"), b.arg((4096, 768), dtype)
+        text = b.module([b.scatter_rows(table, idx, upd, "add")])
+        arrays = [f((30522, 768)), rng.integers(0, 30522, (4096,)).astype(np.int32), f((4096, 768))]
+        nbytes = (2 * 30522 * 768 + 2 * 4096 * 768) * es          # operand copied to the result, updates read and added
+    exe = client.compile(text)
+    dts = [dtype if a.dtype == np.float32 else "i32" for a in arrays]
+    bufs = [client.buffer_from_host(a, dtype=d) for a, d in zip(arrays, dts)]
+    record = _events(client)
+    for _ in range(3):
+        exe.execute(bufs)
+    client.synchronize()
+    a = record()
+    for _ in range(reps):
+        exe.execute(bufs)
+    e = record()
+    client.synchronize()
+    us = a.elapsed_time(e) * 1e3 / reps
+    print(f"{what} {dtype}: {us:.1f} us per execution, {nbytes / us / 1e3:.0f} GB/s of algorithmic bytes ({nbytes / 1e6:.1f} MB); plan: "
+          + " | ".join(l.strip()[:100] for l in exe.plan_text().splitlines()[1:]))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["conv", "reduce", "scan", "gemma", "distilbert", "gemm", "gemv"])
+    ap.add_argument("what", choices=["conv", "reduce", "scan", "gemma", "distilbert", "gemm", "gemv", "pointwise", "transpose",
+                                     "softmax", "gather", "scatter"])
+    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--layout", default="kc", choices=["kc", "nc"])
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--profile", action="store_true")
@@ -268,6 +331,9 @@ def main():
     b = Builder()
     if a.what == "scan":
         scan(client, a.reps)
+        return
+    if a.what in ("pointwise", "transpose", "softmax", "gather", "scatter"):
+        simple(client, a.what, a.dtype, a.reps)
         return
     if a.what == "gemma":
         import json

@@ -1117,7 +1117,7 @@ struct Planner {
       all.push_back(m->results[0]);
       for (auto* o : m->operands) all.push_back(o);
     }
-    em.idx_t = idx_type_for(all, n + kThreads * kEPT);
+    em.idx_t = idx_type_for(all, n + kThreads * 8);
     Ctx root;
     root.shape = rt.dims;
     root.lin = "lin";
@@ -1129,13 +1129,26 @@ struct Planner {
     std::ostringstream src;
     src << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(" << signature(outs, em.inputs)
         << ") {\n";
-    // 16-byte accesses: when the element count is a multiple of 4 and every output is a 4-byte type, a thread
-    // takes 4 consecutive elements; inputs read at the kernel's own linear index (same-shaped tensors) are
-    // fetched as one 16-byte load, the outputs leave as one 16-byte store. Other operands (broadcast vectors,
-    // gathers) keep their scalar loads.
-    auto four_bytes = [](DT d) { return d == DT::F32 || d == DT::I32 || d == DT::U32; };
-    bool vec4 = n % 4 == 0 && n >= 4096;
-    for (auto* o : outs) vec4 = vec4 && four_bytes(o->type.dt);
+    // Wide accesses: a thread takes W consecutive elements (8 when a 2-byte type is among the outputs and the element
+    // count allows it, else 4). Inputs read at the kernel's own linear index (same-shaped tensors) are fetched with
+    // 16-byte loads (one for 8 two-byte or 4 four-byte elements, two for 8 four-byte ones), the outputs leave the
+    // same way. Other operands (broadcast vectors, gathers) keep their scalar loads.
+    auto esize = [](DT d) -> int {
+      switch (d) {
+        case DT::F32: case DT::I32: case DT::U32: return 4;
+        case DT::BF16: case DT::F16: case DT::I16: case DT::U16: return 2;
+        case DT::PRED: case DT::I8: case DT::U8: return 1;
+        default: return 0;
+      }
+    };
+    bool two_byte_out = false, wide_ok = n >= 4096;
+    for (auto* o : outs) {
+      wide_ok = wide_ok && esize(o->type.dt) != 0;
+      two_byte_out = two_byte_out || esize(o->type.dt) == 2;
+    }
+    const int W = (two_byte_out && n % 8 == 0) ? 8 : 4;
+    for (auto* o : outs) wide_ok = wide_ok && (W * esize(o->type.dt)) % 4 == 0;
+    const bool vec4 = wide_ok && n % W == 0 && !getenv("B200_NO_WIDE_POINTWISE");
     Launch L;
     if (vec4) {
       std::string body = em.str();
@@ -1150,31 +1163,43 @@ struct Planner {
         }
         return any;
       };
+      // moves W elements of `es` bytes between the thread's array and memory in the widest aligned pieces
+      auto mover = [&](const std::string& arr, const std::string& ptr, int es, bool is_load) {
+        std::ostringstream o;
+        const int bytes = W * es;
+        const char* piece = bytes >= 16 ? "uint4" : (bytes == 8 ? "uint2" : "unsigned int");
+        const int pb = bytes >= 16 ? 16 : bytes;
+        for (int q = 0; q < bytes / pb; q++) {
+          const std::string mem = "reinterpret_cast<" + std::string(is_load ? "const " : "") + piece + "*>(" + ptr + " + base)[" + std::to_string(q) + "]";
+          const std::string loc = "reinterpret_cast<" + std::string(is_load ? "" : "const ") + piece + "*>(" + arr + ")[" + std::to_string(q) + "]";
+          o << "  " << (is_load ? loc + " = " + mem : mem + " = " + loc) << ";\n";
+        }
+        return o.str();
+      };
       std::ostringstream loads, stores;
       for (size_t k = 0; k < em.inputs.size(); k++) {
         Value* in = em.inputs[k];
-        if (!four_bytes(in->type.dt) || in->type.numel() != n) continue;
+        const int es = esize(in->type.dt);
+        if (es == 0 || (W * es) % 4 != 0 || in->type.numel() != n) continue;
         const std::string nm = "in" + std::to_string(k);
         if (!replace_all(body, nm + "[lin]", "v" + nm + "[e]")) continue;
-        const char* ct = c_type(in->type.dt);
-        loads << "  __align__(16) " << ct << " v" << nm << "[4];\n  *reinterpret_cast<uint4*>(v" << nm
-              << ") = *reinterpret_cast<const uint4*>(" << nm << " + base);\n";
+        loads << "  __align__(16) " << s_type(in->type.dt) << " v" << nm << "[" << W << "];\n" << mover("v" + nm, nm, es, true);
       }
       for (size_t k = 0; k < outs.size(); k++) {
         const std::string nm = "out" + std::to_string(k);
         replace_all(body, nm + "[lin]", "v" + nm + "[e]");
-        loads << "  __align__(16) " << c_type(outs[k]->type.dt) << " v" << nm << "[4];\n";
-        stores << "  *reinterpret_cast<uint4*>(" << nm << " + base) = *reinterpret_cast<const uint4*>(v" << nm << ");\n";
+        loads << "  __align__(16) " << s_type(outs[k]->type.dt) << " v" << nm << "[" << W << "];\n";
+        stores << mover("v" + nm, nm, esize(outs[k]->type.dt), false);
       }
-      src << "  const " << em.idx_t << " base = ((" << em.idx_t << ")blockIdx.x * " << kThreads << " + threadIdx.x) * 4;\n";
+      src << "  const " << em.idx_t << " base = ((" << em.idx_t << ")blockIdx.x * " << kThreads << " + threadIdx.x) * " << W << ";\n";
       src << "  if (base >= (" << em.idx_t << ")" << n << "LL) return;\n";
       src << loads.str();
-      src << "  #pragma unroll\n  for (int e = 0; e < 4; ++e) {\n";
+      src << "  #pragma unroll\n  for (int e = 0; e < " << W << "; ++e) {\n";
       src << "    const " << em.idx_t << " lin = base + e;\n";
       src << body;
       src << "  }\n" << stores.str() << "}\n";
       L.kernel = add_kernel(src.str(), "fused");
-      int64_t blocks = std::max<int64_t>(1, (n / 4 + kThreads - 1) / kThreads);
+      int64_t blocks = std::max<int64_t>(1, (n / W + kThreads - 1) / kThreads);
       L.grid[0] = (unsigned)blocks; L.grid[1] = L.grid[2] = 1;
     } else {
       src << "  #pragma unroll\n  for (int e = 0; e < " << kEPT << "; ++e) {\n";
@@ -2172,7 +2197,9 @@ struct Planner {
 
   void emit_row_chain(const RowChain& rc, Plan& plan, BlockState& st) {
     const int64_t Nk = rc.Nk, Nr = rc.Nr;
-    const int T = Nr >= 128 ? 256 : 32, per_block = 256 / T;
+    // rows of up to 512 elements: a warp per row, eight rows per block (a block per row leaves most of its threads
+    // without an element and pays a block-wide exchange per reduction); longer rows: a block per row
+    const int T = Nr > 512 ? 256 : 32, per_block = 256 / T;
     const std::string it = "int";
     std::set<Op*> chain_members;
     for (Group* g : rc.stages) chain_members.insert(g->members.begin(), g->members.end());
