@@ -2044,7 +2044,7 @@ struct Planner {
     s.iparams = {rows, row_elems, U, indices->type.dt == DT::I64 ? 8 : 4, kind};
     TensorType t;
     t.dt = DT::I32;
-    t.dims = {2 * std::max<long long>(U, 1)};
+    t.dims = {scatter_rows_scratch_ints(rows, U)};
     s.args = {slot_of.at(operand), slot_of.at(indices), slot_of.at(updates), slot_of.at(out), new_slot(Slot::TEMP, t, st.arena)};
     return s;
   }
@@ -2197,9 +2197,11 @@ struct Planner {
 
   void emit_row_chain(const RowChain& rc, Plan& plan, BlockState& st) {
     const int64_t Nk = rc.Nk, Nr = rc.Nr;
-    // rows of up to 512 elements: a warp per row, eight rows per block (a block per row leaves most of its threads
+    // rows of up to 1024 elements: a warp per row, eight rows per block (a block per row leaves most of its threads
     // without an element and pays a block-wide exchange per reduction); longer rows: a block per row
-    const int T = Nr > 512 ? 256 : 32, per_block = 256 / T;
+    const char* wm = getenv("B200_ROW_WARP_MAX");
+    const int64_t warp_max = wm ? atoll(wm) : 1024;
+    const int T = Nr > warp_max ? 256 : 32, per_block = 256 / T;
     const std::string it = "int";
     std::set<Op*> chain_members;
     for (Group* g : rc.stages) chain_members.insert(g->members.begin(), g->members.end());
@@ -3636,7 +3638,7 @@ std::unique_ptr<CompiledProgram> compile_module(Module& m, const CompileOptions&
       long long n = 0;
       for (auto& s : p.steps) {
         if (s.kind == Step::KERNEL || s.kind == Step::ALL_REDUCE || s.kind == Step::ALL_GATHER) n += 1;
-        else if (s.kind == Step::SCATTER) n += 2;
+        else if (s.kind == Step::SCATTER) n += scatter_rows_launches(s.iparams[0], s.iparams[2]);
         else if (s.kind == Step::IGEMM) n += s.ig.split_k > 1 ? 2 : 1;
         else if (s.kind == Step::GEMM16) n += (s.g16.path == 0 && s.g16.split_k > 1) ? 2 : 1;
         else if (s.kind == Step::REPACK16) n += (s.iparams[0] + 65534) / 65535;

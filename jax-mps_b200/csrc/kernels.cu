@@ -1392,6 +1392,84 @@ __global__ void __launch_bounds__(256) scatter_rank_kernel(const I* __restrict__
   key[rank] = (int)mine;
 }
 
+// The same ranking for many updates: a stable least-significant-digit radix sort of (row index, update number) with
+// 8-bit digits, 1024 elements per block. Per pass: digit histograms per block, one exclusive scan over (digit, block),
+// then every element goes to scan[digit][block] + the number of earlier elements of its block with the same digit
+// (within a warp by matching lanes, across the block's warps by a table of per-warp counts): equal keys keep their
+// update order, which is what makes the accumulation order, and so the result, independent of the launch.
+template <typename I>
+__global__ void __launch_bounds__(256) scatter_keys_kernel(const I* __restrict__ idx, int U, long long rows, int* __restrict__ key,
+                                                         int* __restrict__ val) {
+  const int u = blockIdx.x * 256 + threadIdx.x;
+  if (u >= U) return;
+  const long long r = (long long)idx[u];
+  key[u] = (r < 0 || r >= rows) ? (int)rows : (int)r;          // dropped updates sort to the end
+  val[u] = u;
+}
+
+__global__ void __launch_bounds__(1024) radix_hist_kernel(const int* __restrict__ key, int U, int shift, int* __restrict__ hist, int nblocks) {
+  __shared__ int h[256];
+  if (threadIdx.x < 256) h[threadIdx.x] = 0;
+  __syncthreads();
+  const int e = blockIdx.x * 1024 + threadIdx.x;
+  if (e < U) atomicAdd(&h[((unsigned)key[e] >> shift) & 255u], 1);
+  __syncthreads();
+  if (threadIdx.x < 256) hist[threadIdx.x * nblocks + blockIdx.x] = h[threadIdx.x];
+}
+
+// exclusive scan of n integers in place by one block: a contiguous chunk per thread, the chunk sums scanned in shared memory
+__global__ void __launch_bounds__(1024) radix_scan_kernel(int* __restrict__ hist, int n) {
+  __shared__ int sums[1024];
+  const int per = (n + 1023) / 1024;
+  const int lo = min(n, (int)threadIdx.x * per), hi = min(n, lo + per);
+  int s = 0;
+  for (int i = lo; i < hi; ++i) s += hist[i];
+  sums[threadIdx.x] = s;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const int v = threadIdx.x >= off ? sums[threadIdx.x - off] : 0;
+    __syncthreads();
+    sums[threadIdx.x] += v;
+    __syncthreads();
+  }
+  int run = sums[threadIdx.x] - s;
+  for (int i = lo; i < hi; ++i) {
+    const int v = hist[i];
+    hist[i] = run;
+    run += v;
+  }
+}
+
+__global__ void __launch_bounds__(1024) radix_scatter_kernel(const int* __restrict__ key_in, const int* __restrict__ val_in,
+                                                           int* __restrict__ key_out, int* __restrict__ val_out, int U, int shift,
+                                                           const int* __restrict__ offsets, int nblocks) {
+  __shared__ int cnt[32][256];
+  for (int q = threadIdx.x; q < 32 * 256; q += 1024) (&cnt[0][0])[q] = 0;
+  __syncthreads();
+  const int e = blockIdx.x * 1024 + threadIdx.x, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool valid = e < U;
+  const int k = valid ? key_in[e] : 0, v = valid ? val_in[e] : 0;
+  const int d = valid ? (int)(((unsigned)k >> shift) & 255u) : -1 - lane;     // lanes past the end match nobody
+  const unsigned peers = __match_any_sync(0xFFFFFFFFu, d);
+  const int rank = __popc(peers & ((1u << lane) - 1u));
+  if (valid && rank == 0) cnt[w][d] = __popc(peers);
+  __syncthreads();
+  if (threadIdx.x < 256) {
+    int run = offsets[threadIdx.x * nblocks + blockIdx.x];
+    for (int q = 0; q < 32; ++q) {
+      const int c = cnt[q][threadIdx.x];
+      cnt[q][threadIdx.x] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  if (valid) {
+    const int pos = cnt[w][d] + rank;
+    key_out[pos] = k;
+    val_out[pos] = v;
+  }
+}
+
 __device__ __forceinline__ float scatter_load(const float* p) { return *p; }
 __device__ __forceinline__ float scatter_load(const unsigned short* p) { return __uint_as_float((uint32_t)*p << 16); }
 __device__ __forceinline__ int scatter_load(const int* p) { return *p; }
@@ -1794,6 +1872,9 @@ cudaError_t probe_tf32_mma_rate(int* error_flag, cudaStream_t stream, double* tf
   return cudaGetLastError();
 }
 
+constexpr int kScatterAllPairsMax = 1024;          // up to here the all-pairs ranking (one launch) is the quicker one
+static int scatter_radix_passes(long long rows);
+
 cudaError_t launch_scatter_rows(int elem_kind, int index_bytes, int kind, long long rows, long long row_elems, int updates,
                                 void* out, const void* indices, const void* upd, int* scratch, cudaStream_t stream,
                                 int* launches) {
@@ -1801,10 +1882,31 @@ cudaError_t launch_scatter_rows(int elem_kind, int index_bytes, int kind, long l
   int* key = scratch;
   int* order = scratch + updates;
   const unsigned rb = (unsigned)((updates + 255) / 256);
-  if (index_bytes == 8)
-    scatter_rank_kernel<long long><<<rb, 256, 0, stream>>>((const long long*)indices, updates, rows, key, order);
-  else
-    scatter_rank_kernel<int><<<rb, 256, 0, stream>>>((const int*)indices, updates, rows, key, order);
+  if (updates <= kScatterAllPairsMax) {
+    if (index_bytes == 8)
+      scatter_rank_kernel<long long><<<rb, 256, 0, stream>>>((const long long*)indices, updates, rows, key, order);
+    else
+      scatter_rank_kernel<int><<<rb, 256, 0, stream>>>((const int*)indices, updates, rows, key, order);
+    *launches += 1;
+  } else {
+    int* key_b = scratch + 2 * (long long)updates;
+    int* order_b = scratch + 3 * (long long)updates;
+    int* hist = scratch + 4 * (long long)updates;
+    const int nblocks = (updates + 1023) / 1024;
+    if (index_bytes == 8)
+      scatter_keys_kernel<long long><<<rb, 256, 0, stream>>>((const long long*)indices, updates, rows, key, order);
+    else
+      scatter_keys_kernel<int><<<rb, 256, 0, stream>>>((const int*)indices, updates, rows, key, order);
+    const int passes = scatter_radix_passes(rows);
+    for (int pass = 0; pass < passes; ++pass) {
+      radix_hist_kernel<<<nblocks, 1024, 0, stream>>>(key, updates, 8 * pass, hist, nblocks);
+      radix_scan_kernel<<<1, 1024, 0, stream>>>(hist, 256 * nblocks);
+      radix_scatter_kernel<<<nblocks, 1024, 0, stream>>>(key, order, key_b, order_b, updates, 8 * pass, hist, nblocks);
+      std::swap(key, key_b);
+      std::swap(order, order_b);
+    }
+    *launches += 1 + 3 * passes;
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)updates, (unsigned)std::min<long long>(64, (row_elems + 255) / 256));
@@ -1815,8 +1917,24 @@ cudaError_t launch_scatter_rows(int elem_kind, int index_bytes, int kind, long l
                                                                           updates, rows, row_elems, kind);
   else
     scatter_apply_kernel<int, int><<<grid, 256, 0, stream>>>((int*)out, (const int*)upd, key, order, updates, rows, row_elems, kind);
-  *launches += 2;
+  *launches += 1;
   return cudaGetLastError();
+}
+
+static int scatter_radix_passes(long long rows) {
+  int bits = 1;
+  while (bits < 32 && (1ll << bits) <= rows) ++bits;          // keys lie in [0, rows]
+  return (bits + 7) / 8;
+}
+
+long long scatter_rows_scratch_ints(long long rows, long long updates) {
+  updates = std::max<long long>(updates, 1);
+  if (updates <= kScatterAllPairsMax) return 2 * updates;
+  return 4 * updates + 256 * ((updates + 1023) / 1024);
+}
+
+int scatter_rows_launches(long long rows, long long updates) {
+  return updates <= kScatterAllPairsMax ? 2 : 2 + 3 * scatter_radix_passes(rows);
 }
 
 }  // namespace b200

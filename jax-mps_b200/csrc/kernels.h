@@ -39,7 +39,8 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
 namespace b200 {
 // Row scatter (stablehlo.scatter with one index along dimension 0 and whole-row updates), deterministic.
 // elem_kind: 0 f32, 1 bf16, 2 i32; kind: 0 assign, 1 add, 2 multiply, 3 minimum, 4 maximum. `out` already holds
-// the operand; `scratch` has room for 2 * updates ints.
+// the operand; `scratch` has room for scatter_rows_scratch_ints(rows, updates) ints. Updates are ranked by (row, update
+// number): all pairs up to 1024 updates, a stable radix sort above.
 cudaError_t launch_scatter_rows(int elem_kind, int index_bytes, int kind, long long rows, long long row_elems, int updates,
                                 void* out, const void* indices, const void* upd, int* scratch, cudaStream_t stream,
                                 int* launches);

@@ -56,6 +56,10 @@ struct IGemmParams {
 
 struct Plan;
 
+// Row scatter (kernels.cu): ints of scratch and kernel launches for `updates` updates into `rows` rows.
+long long scatter_rows_scratch_ints(long long rows, long long updates);
+int scatter_rows_launches(long long rows, long long updates);
+
 struct Step {
   enum Kind { KERNEL, IGEMM, MEMCPY, MEMSET, WHILE, CASE, ALL_REDUCE, SCATTER, JOIN, GEMM16, REPACK16, TRANSPOSE, ALL_GATHER } kind = KERNEL;
   std::string label;                  // op names, for profiling and error text

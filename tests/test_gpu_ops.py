@@ -619,6 +619,30 @@ def test_row_scatter(client):
     check(client, b.module([y, dtab]), [f32(50, 8), rng.integers(0, 50, (3, 4)).astype(np.int32), f32(3, 4, 8)], rtol=1e-6, atol=1e-6)
 
 
+def test_row_scatter_with_many_updates(client):
+    """Above 1024 updates the (row, update number) ranking is a stable radix sort: one, two and three 8-bit passes
+    (rows below 2^8, 2^16, 2^24), heavy duplication, dropped indices, i64 indices; integer results are exact, the
+    f32 sums follow update order (one accumulator per row), and two executions agree bit for bit."""
+    rng = np.random.default_rng(11)
+    for rows, U, idt in [(200, 5000, "i32"), (30522, 4096, "i32"), (70000, 3000, "i64"), (300, 2049, "i32")]:
+        idx = rng.integers(0, rows, (U,)).astype(np.int64 if idt == "i64" else np.int32)
+        idx[::97] = rows + 5                            # dropped
+        idx[1::131] = -1                                # dropped
+        b = Builder()
+        t, i, u = b.arg((rows, 8), "i32"), b.arg((U,), idt), b.arg((U, 8), "i32")
+        check(client, b.module([b.scatter_rows(t, i, u, "add")]),
+              [rng.integers(-9, 9, (rows, 8)).astype(np.int32), idx, rng.integers(-9, 9, (U, 8)).astype(np.int32)])
+        b = Builder()
+        t, i, u = b.arg((rows, 8), "f32"), b.arg((U,), idt), b.arg((U, 8), "f32")
+        text = b.module([b.scatter_rows(t, i, u, "add")])
+        args = [f32(rows, 8), idx, f32(U, 8)]
+        check(client, text, args, rtol=1e-6, atol=1e-5)
+        exe = client.compile(text)
+        bufs = [client.buffer_from_host(a) for a in args]
+        first = exe.execute(bufs)[0].to_numpy()
+        np.testing.assert_array_equal(exe.execute(bufs)[0].to_numpy(), first)
+
+
 def test_case_branches(client):
     """lax.cond / lax.switch lowerings: branches capture outer values; an index outside [0, n) runs the last
     branch; a case inside a while body."""
