@@ -398,6 +398,106 @@ struct Inliner {
         }
       }
     }
+    // dot_general on integers and booleans: exact integer arithmetic (wrapping like any integer multiply and add; the
+    // reference casts through f32, src/pjrt_plugin/ops/linalg.cc:110-119, which is exact only below 2^24). The product
+    // is written as what it means, result[b, i, j] = sum over k of lhs[b, i, k] * rhs[b, k, j]: both operands broadcast
+    // to [batch, lhs free, rhs free, contracted], multiplied and reduced over the trailing dimensions. The broadcasts
+    // and the multiply are evaluated inside the reduction kernel; nothing of the large shape is stored.
+    if (sh == "dot_general" && op->operands.size() == 2 && op->results.size() == 1 && op->has("dot_dimension_numbers")) {
+      auto integral = [](DT d) { return d == DT::PRED || dt_is_signed(d) || dt_is_unsigned(d); };
+      const TensorType rt = op->results[0]->type;
+      if (integral(rt.dt) && integral(op->operands[0]->type.dt) && integral(op->operands[1]->type.dt)) {
+        auto f = attr_struct(op->attr("dot_dimension_numbers"));
+        const auto lb = f["lhs_batching_dimensions"], rb = f["rhs_batching_dimensions"];
+        const auto lc = f["lhs_contracting_dimensions"], rc = f["rhs_contracting_dimensions"];
+        Value* ops2[2] = {op->operands[0], op->operands[1]};
+        auto new_op = [&](const char* name, std::vector<Value*> ins, const TensorType& t, std::map<std::string, std::string> attrs,
+                          Value* into = nullptr) -> std::unique_ptr<Op> {
+          auto o = std::make_unique<Op>();
+          o->name = std::string("stablehlo.") + name;
+          o->operands = std::move(ins);
+          o->attrs = std::move(attrs);
+          Value* v = into ? into : m.new_value(t, "");
+          v->def = o.get();
+          v->def_index = 0;
+          o->results.push_back(v);
+          return o;
+        };
+        auto run1 = [&](std::unique_ptr<Op> o) -> Value* {
+          Value* v = o->results[0];
+          process(std::move(o), b);
+          return res(v);
+        };
+        auto pos_in = [](const std::vector<int64_t>& v, int64_t x) { for (size_t k = 0; k < v.size(); k++) if (v[k] == x) return (int)k; return -1; };
+        std::vector<int64_t> full = rt.dims;
+        for (auto d : lc) full.push_back(ops2[0]->type.dims[d]);
+        const int nb = (int)lb.size(), nres = (int)rt.dims.size();
+        int nlf = 0;
+        for (int d = 0; d < ops2[0]->type.rank(); d++) if (pos_in(lb, d) < 0 && pos_in(lc, d) < 0) nlf++;
+        Value* wide[2];
+        for (int side = 0; side < 2; side++) {
+          Value* v = ops2[side];
+          const auto& bd = side == 0 ? lb : rb;
+          const auto& cd = side == 0 ? lc : rc;
+          if (v->type.dt != rt.dt) {
+            TensorType ct = v->type;
+            ct.dt = rt.dt;
+            v = run1(new_op("convert", {v}, ct, {}));
+          }
+          std::string map = "[";
+          int free_seen = 0;
+          for (int d = 0; d < v->type.rank(); d++) {
+            int to;
+            if (pos_in(bd, d) >= 0) to = pos_in(bd, d);
+            else if (pos_in(cd, d) >= 0) to = nres + pos_in(cd, d);
+            else to = nb + (side == 0 ? 0 : nlf) + free_seen++;
+            map += (d ? ", " : "") + std::to_string(to);
+          }
+          map += "]";
+          TensorType ft;
+          ft.dt = rt.dt;
+          ft.dims = full;
+          wide[side] = run1(new_op("broadcast_in_dim", {v}, ft, {{"broadcast_dimensions", map}}));
+        }
+        TensorType ft;
+        ft.dt = rt.dt;
+        ft.dims = full;
+        const bool boolean = rt.dt == DT::PRED;
+        if (lc.empty()) {
+          process(new_op(boolean ? "and" : "multiply", {wide[0], wide[1]}, rt, {}, op->results[0]), b);
+          return;
+        }
+        Value* prod = run1(new_op(boolean ? "and" : "multiply", {wide[0], wide[1]}, ft, {}));
+        TensorType st;
+        st.dt = rt.dt;
+        Value* init = run1(new_op("constant", {}, st, {{"value", std::string("dense<") + (boolean ? "false" : "0") + "> : " + st.str()}}));
+        std::string dims = "[";
+        for (size_t k = 0; k < lc.size(); k++) dims += (k ? ", " : "") + std::to_string(nres + (int)k);
+        dims += "]";
+        auto red = new_op("reduce", {prod, init}, rt, {{"dimensions", dims}}, op->results[0]);
+        auto body = std::make_unique<Block>();
+        body->parent_op = red.get();
+        Value* a0 = m.new_value(st, "%acc");
+        Value* a1 = m.new_value(st, "%val");
+        for (Value* v : {a0, a1}) { v->owner = body.get(); v->arg_index = (int)body->args.size(); body->args.push_back(v); }
+        auto inner = std::make_unique<Op>();
+        inner->name = boolean ? "stablehlo.or" : "stablehlo.add";
+        inner->operands = {a0, a1};
+        inner->parent = body.get();
+        Value* r = m.new_value(st, "%red");
+        r->def = inner.get();
+        inner->results.push_back(r);
+        auto ret = std::make_unique<Op>();
+        ret->name = "stablehlo.return";
+        ret->operands = {r};
+        ret->parent = body.get();
+        body->ops.push_back(std::move(inner));
+        body->ops.push_back(std::move(ret));
+        red->regions.push_back(std::move(body));
+        process(std::move(red), b);
+        return;
+      }
+    }
     // dot_general on two bf16 (or two f16) operands in matrix form goes to the native 16-bit kernels (lower_dot16).
     // Any other dot_general / convolution on bf16 or f16 operands: computed as the f32 contraction of the converted
     // operands and rounded once at the end. Products of two bf16 (or f16) numbers and their fp32 accumulation
@@ -1100,6 +1200,33 @@ struct Planner {
     return s;
   }
 
+  // replaces `from` by `to` where `from` does not continue an identifier; true when anything was replaced
+  static bool replace_word(std::string& str, const std::string& from, const std::string& to) {
+    size_t pos = 0;
+    bool any = false;
+    while ((pos = str.find(from, pos)) != std::string::npos) {
+      if (pos > 0 && (isalnum((unsigned char)str[pos - 1]) || str[pos - 1] == '_')) { pos += from.size(); continue; }
+      str.replace(pos, from.size(), to);
+      pos += to.size();
+      any = true;
+    }
+    return any;
+  }
+
+  // moves W elements of `es` bytes between a thread's array `arr` and `ptr + base` in the widest aligned pieces
+  static std::string wide_move(const std::string& arr, const std::string& ptr, int W, int es, bool is_load, int indent = 2) {
+    std::ostringstream o;
+    const int bytes = W * es;
+    const char* piece = bytes >= 16 ? "uint4" : (bytes == 8 ? "uint2" : "unsigned int");
+    const int pb = bytes >= 16 ? 16 : bytes;
+    for (int q = 0; q < bytes / pb; q++) {
+      const std::string mem = "reinterpret_cast<" + std::string(is_load ? "const " : "") + piece + "*>(" + ptr + " + base)[" + std::to_string(q) + "]";
+      const std::string loc = "reinterpret_cast<" + std::string(is_load ? "" : "const ") + piece + "*>(" + arr + ")[" + std::to_string(q) + "]";
+      o << std::string(indent, ' ') << (is_load ? loc + " = " + mem : mem + " = " + loc) << ";\n";
+    }
+    return o.str();
+  }
+
   static constexpr int kEPT = 4;       // elements per thread of a pointwise kernel
   static constexpr int kThreads = 256;
 
@@ -1152,44 +1279,20 @@ struct Planner {
     Launch L;
     if (vec4) {
       std::string body = em.str();
-      auto replace_all = [](std::string& str, const std::string& from, const std::string& to) {
-        size_t pos = 0;
-        bool any = false;
-        while ((pos = str.find(from, pos)) != std::string::npos) {
-          if (pos > 0 && (isalnum((unsigned char)str[pos - 1]) || str[pos - 1] == '_')) { pos += from.size(); continue; }
-          str.replace(pos, from.size(), to);
-          pos += to.size();
-          any = true;
-        }
-        return any;
-      };
-      // moves W elements of `es` bytes between the thread's array and memory in the widest aligned pieces
-      auto mover = [&](const std::string& arr, const std::string& ptr, int es, bool is_load) {
-        std::ostringstream o;
-        const int bytes = W * es;
-        const char* piece = bytes >= 16 ? "uint4" : (bytes == 8 ? "uint2" : "unsigned int");
-        const int pb = bytes >= 16 ? 16 : bytes;
-        for (int q = 0; q < bytes / pb; q++) {
-          const std::string mem = "reinterpret_cast<" + std::string(is_load ? "const " : "") + piece + "*>(" + ptr + " + base)[" + std::to_string(q) + "]";
-          const std::string loc = "reinterpret_cast<" + std::string(is_load ? "" : "const ") + piece + "*>(" + arr + ")[" + std::to_string(q) + "]";
-          o << "  " << (is_load ? loc + " = " + mem : mem + " = " + loc) << ";\n";
-        }
-        return o.str();
-      };
       std::ostringstream loads, stores;
       for (size_t k = 0; k < em.inputs.size(); k++) {
         Value* in = em.inputs[k];
         const int es = esize(in->type.dt);
         if (es == 0 || (W * es) % 4 != 0 || in->type.numel() != n) continue;
         const std::string nm = "in" + std::to_string(k);
-        if (!replace_all(body, nm + "[lin]", "v" + nm + "[e]")) continue;
-        loads << "  __align__(16) " << s_type(in->type.dt) << " v" << nm << "[" << W << "];\n" << mover("v" + nm, nm, es, true);
+        if (!replace_word(body, nm + "[lin]", "v" + nm + "[e]")) continue;
+        loads << "  __align__(16) " << s_type(in->type.dt) << " v" << nm << "[" << W << "];\n" << wide_move("v" + nm, nm, W, es, true);
       }
       for (size_t k = 0; k < outs.size(); k++) {
         const std::string nm = "out" + std::to_string(k);
-        replace_all(body, nm + "[lin]", "v" + nm + "[e]");
+        replace_word(body, nm + "[lin]", "v" + nm + "[e]");
         loads << "  __align__(16) " << s_type(outs[k]->type.dt) << " v" << nm << "[" << W << "];\n";
-        stores << mover("v" + nm, nm, esize(outs[k]->type.dt), false);
+        stores << wide_move("v" + nm, nm, W, esize(outs[k]->type.dt), false);
       }
       src << "  const " << em.idx_t << " base = ((" << em.idx_t << ")blockIdx.x * " << kThreads << " + threadIdx.x) * " << W << ";\n";
       src << "  if (base >= (" << em.idx_t << ")" << n << "LL) return;\n";
@@ -2199,9 +2302,23 @@ struct Planner {
     const int64_t Nk = rc.Nk, Nr = rc.Nr;
     // rows of up to 1024 elements: a warp per row, eight rows per block (a block per row leaves most of its threads
     // without an element and pays a block-wide exchange per reduction); longer rows: a block per row
+    // (with few rows a block per row is what spreads the work over the SMs)
     const char* wm = getenv("B200_ROW_WARP_MAX");
     const int64_t warp_max = wm ? atoll(wm) : 1024;
-    const int T = Nr > warp_max ? 256 : 32, per_block = 256 / T;
+    const int T = (Nr <= 64 || (Nr <= warp_max && Nk >= 1184)) ? 32 : 256, per_block = 256 / T;
+    // V consecutive elements of the row per thread and round, moved with 16-byte accesses where a tensor is read or
+    // written at the row element's own position: 8 when the row's tensors include 2-byte types, else 4
+    int V = 1;
+    if (!getenv("B200_NO_WIDE_ROWS")) {
+      bool two = false;
+      for (Group* g : rc.stages)
+        for (Op* mop : g->members) {
+          two = two || dt_size(mop->results[0]->type.dt) == 2;
+          for (Value* ov : mop->operands) two = two || (ov->type.numel() == Nk * Nr && dt_size(ov->type.dt) == 2);
+        }
+      if (two && Nr % 8 == 0) V = 8;
+      else if (Nr % 4 == 0) V = 4;
+    }
     const std::string it = "int";
     std::set<Op*> chain_members;
     for (Group* g : rc.stages) chain_members.insert(g->members.begin(), g->members.end());
@@ -2265,8 +2382,35 @@ struct Planner {
       oc.idx = kc.idx;
       oc.idx.insert(oc.idx.end(), rctx.idx.begin(), rctx.idx.end());
       oc.lin = "lin";
-      const std::string loop = "    for (" + it + " r = lane; r < " + std::to_string(Nr) + "; r += " + std::to_string(T) + ") {\n      const " +
-                               it + " lin = o * " + std::to_string(Nr) + " + r;\n";
+      // the loop over the row's elements around a stage's code; `stage_outs` are the (output number, value) pairs the
+      // stage stores at the element's own position
+      auto row_loop = [&](Emitter& e2, const std::vector<std::pair<size_t, Value*>>& stage_outs) -> std::string {
+        std::string inner = e2.str();
+        if (V == 1)
+          return "    for (" + it + " r = lane; r < " + std::to_string(Nr) + "; r += " + std::to_string(T) + ") {\n      const " + it +
+                 " lin = o * " + std::to_string(Nr) + " + r;\n" + inner + "    }\n";
+        std::ostringstream pre, post;
+        for (size_t k = 0; k < e2.inputs.size(); k++) {
+          Value* in = e2.inputs[k];
+          const int es = dt_size(in->type.dt);
+          if (in->type.numel() != Nk * Nr || (es != 1 && es != 2 && es != 4) || (V * es) % 4 != 0) continue;
+          const std::string nm = "in" + std::to_string(k);
+          if (!replace_word(inner, nm + "[lin]", "v" + nm + "[e]")) continue;
+          pre << "      __align__(16) " << s_type(in->type.dt) << " v" << nm << "[" << V << "];\n" << wide_move("v" + nm, nm, V, es, true, 6);
+        }
+        for (auto& so : stage_outs) {
+          const int es = dt_size(so.second->type.dt);
+          if ((es != 1 && es != 2 && es != 4) || (V * es) % 4 != 0) continue;
+          const std::string nm = "out" + std::to_string(so.first);
+          if (!replace_word(inner, nm + "[lin]", "v" + nm + "[e]")) continue;
+          pre << "      __align__(16) " << s_type(so.second->type.dt) << " v" << nm << "[" << V << "];\n";
+          post << wide_move("v" + nm, nm, V, es, false, 6);
+        }
+        return "    for (" + it + " rb = lane * " + std::to_string(V) + "; rb < " + std::to_string(Nr) + "; rb += " + std::to_string(T * V) +
+               ") {\n      const " + it + " base = o * " + std::to_string(Nr) + " + rb;\n" + pre.str() +
+               "      #pragma unroll\n      for (int e = 0; e < " + std::to_string(V) + "; ++e) {\n      const " + it + " r = rb + e;\n      const " +
+               it + " lin = base + e;\n" + inner + "      }\n" + post.str() + "    }\n";
+      };
       if (g->is_reduce) {
         std::vector<Value*> operands, results;
         std::vector<std::string> inits;
@@ -2307,7 +2451,7 @@ struct Planner {
         }
         body << "  {\n";
         for (size_t k = 0; k < n; k++) body << "    " << c_type(dts[k]) << " acc" << k << " = " << inits[k] << ";\n";
-        body << "    {\n  " << loop << em.str() << "      }\n    }\n";
+        body << "    {\n" << row_loop(em, {}) << "    }\n";
         body << "    #pragma unroll\n    for (int m = 16; m >= 1; m >>= 1) {\n";
         for (size_t k = 0; k < n; k++) body << "      const " << c_type(dts[k]) << " oth" << k << " = shfl_xor(acc" << k << ", m);\n";
         {
@@ -2374,11 +2518,13 @@ struct Planner {
         for (Op* root : g->roots)
           if (stored(root->results[0])) stores.push_back({root->results[0], em.emit(root->results[0], oc)});
         if (!stores.empty()) {
+          std::vector<std::pair<size_t, Value*>> stage_outs;
           for (auto& sv : stores) {
             em.line("out" + std::to_string(outs.size()) + "[lin] = " + store_expr(sv.first->type.dt, sv.second) + ";");
+            stage_outs.push_back({outs.size(), sv.first});
             outs.push_back(sv.first);
           }
-          body << "  if (live) {\n" << loop << em.str() << "    }\n  }\n";
+          body << "  if (live) {\n" << row_loop(em, stage_outs) << "  }\n";
         }
       }
       ins = em.inputs;

@@ -619,6 +619,41 @@ def test_row_scatter(client):
     check(client, b.module([y, dtab]), [f32(50, 8), rng.integers(0, 50, (3, 4)).astype(np.int32), f32(3, 4, 8)], rtol=1e-6, atol=1e-6)
 
 
+@pytest.mark.parametrize("dt,out", [("i32", None), ("i8", "i32"), ("ui8", None), ("i64", None), ("ui32", None), ("i16", "i32")])
+def test_integer_dot_general_is_exact(client, dt, out):
+    """dot_general on integers: exact integer products and sums (wrapping in the result type), the layouts of the
+    reference's matmul cases (tests/configs/matmul.py:19-141 of the reference): plain, transposed, batched, several
+    free and several contracting dimensions, and a contraction of length 300 whose partial sums pass 2^24 (where the
+    reference's cast through f32, src/pjrt_plugin/ops/linalg.cc:110-119, stops being exact)."""
+    rng = np.random.default_rng(5)
+    npdt = {"i32": np.int32, "i8": np.int8, "ui8": np.uint8, "i64": np.int64, "ui32": np.uint32, "i16": np.int16}[dt]
+    lo, hi = (0, 200) if dt.startswith("u") else (-100, 100)
+    big = dt in ("i32", "i64", "ui32")
+    cases = [((6, 5), (5, 7), ((1,), (0,)), ((), ())),
+             ((5, 6), (7, 5), ((0,), (1,)), ((), ())),
+             ((3, 4, 9), (3, 9, 5), ((2,), (1,)), ((0,), (0,))),
+             ((2, 3, 4, 6), (6, 5), ((3,), (0,)), ((), ())),
+             ((4, 3, 5), (3, 5, 6), ((1, 2), (0, 1)), ((), ())),
+             ((8, 300), (300, 9), ((1,), (0,)), ((), ())),
+             ((7,), (7,), ((0,), (0,)), ((), ()))]
+    for ls, rs, contract, batch in cases:
+        b = Builder()
+        x, y = b.arg(ls, dt), b.arg(rs, dt)
+        text = b.module([b.dot_general(x, y, contract, batch, out_dtype=out)])
+        scale = 20000 if big and ls == (8, 300) else 1
+        args = [(rng.integers(lo, hi, ls) * scale).astype(npdt), (rng.integers(lo, hi, rs) * scale).astype(npdt)]
+        check(client, text, args)
+
+
+def test_boolean_dot_general(client):
+    """dot_general on i1: and / or."""
+    rng = np.random.default_rng(6)
+    b = Builder()
+    x, y = b.arg((9, 40), "i1"), b.arg((40, 11), "i1")
+    text = b.module([b.dot_general(x, y, ((1,), (0,)))])
+    check(client, text, [rng.random((9, 40)) < 0.05, rng.random((40, 11)) < 0.05])
+
+
 def test_row_scatter_with_many_updates(client):
     """Above 1024 updates the (row, update number) ranking is a stable radix sort: one, two and three 8-bit passes
     (rows below 2^8, 2^16, 2^24), heavy duplication, dropped indices, i64 indices; integer results are exact, the
