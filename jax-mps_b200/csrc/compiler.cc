@@ -923,6 +923,13 @@ struct Planner {
     ks.name = std::string(stem) + "_" + std::to_string(id);
     std::string body = body_without_name;
     for (auto p = body.find("@NAME@"); p != std::string::npos; p = body.find("@NAME@", p)) body.replace(p, 6, ks.name);
+    // every generated kernel can be launched with programmatic stream serialization: it lets the next kernel be
+    // scheduled, then waits for everything in front of it before it touches memory
+    {
+      const size_t sig = body.find("__global__");
+      const size_t open = sig == std::string::npos ? std::string::npos : body.find(") {\n", sig);
+      if (open != std::string::npos) body.insert(open + 4, "  pdl_prologue();\n");
+    }
     ks.body = body;
     prog.kernels.push_back(ks);
     kernel_cache[body_without_name] = id;

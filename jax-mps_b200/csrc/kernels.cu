@@ -28,6 +28,24 @@
 namespace b200 {
 
 namespace {
+// Launch with programmatic stream serialization (the product kernels and their split-K sum start with pdl_prologue).
+bool g_igemm_programmatic_launch = true;
+
+template <typename... P, typename... A>
+cudaError_t launch_k(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_igemm_programmatic_launch ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<A>(args)...);
+}
+
 
 constexpr int BM = 128, BN = 64, BK = 16, NT = 256;
 constexpr int TM = 8, TN = 4;
@@ -47,6 +65,7 @@ __global__ void __launch_bounds__(NT) igemm_f32_kernel(const float* __restrict__
                                                        const long long* __restrict__ b_grp,
                                                        const long long* __restrict__ c_grp, float* __restrict__ partial,
                                                        IGemmLaunch p) {
+  pdl_prologue();
   __shared__ __align__(16) float As[BK][BM + 4];
   __shared__ __align__(16) float Bs[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -211,6 +230,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
                                                                 const long long* __restrict__ c_col,
                                                                 const long long* __restrict__ c_grp, int M, int N, int groups,
                                                                 int split_k) {
+  pdl_prologue();
   constexpr int W = VEC ? 4 : 1;
   __shared__ float sm[KY][32 * W + 1];
   const long long total = (long long)groups * M * N;
@@ -322,6 +342,7 @@ __global__ void __launch_bounds__(TNT, 2) igemm_tf32x3_kernel(const float* __res
                                                              const long long* __restrict__ c_grp,
                                                              float* __restrict__ partial, int* __restrict__ error_flag,
                                                              IGemmLaunch p) {
+  pdl_prologue();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + TSTAGES * TSTAGE_BYTES);      // one mbarrier per stage
@@ -708,6 +729,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) igemm_tf32x3_ws_kernel(
     const long long* __restrict__ c_row, const long long* __restrict__ c_col, const long long* __restrict__ a_grp,
     const long long* __restrict__ b_grp, const long long* __restrict__ c_grp, float* __restrict__ partial,
     int* __restrict__ error_flag, IGemmLaunch p) {
+  pdl_prologue();
   using Cfg = WsCfg<BN>;
   constexpr int S = Cfg::STAGES;
   constexpr int WS_GATHER = SEG ? 256 : 512, WS_LOW = 768 - WS_GATHER;
@@ -1074,6 +1096,7 @@ __global__ void __launch_bounds__((TaCfg<BN, HALF>::THREADS), (HALF ? 2 : 1)) ig
     const long long* __restrict__ c_row, const long long* __restrict__ c_col, const long long* __restrict__ a_grp,
     const long long* __restrict__ b_grp, const long long* __restrict__ c_grp, float* __restrict__ partial,
     const int* __restrict__ kt_table, int* __restrict__ error_flag, const __grid_constant__ CUtensorMap tm_a, IGemmLaunch p) {
+  pdl_prologue();
   using Cfg = TaCfg<BN, HALF>;
   constexpr int S = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -1572,19 +1595,19 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
       dim3 gridw((p.M + TBM - 1) / TBM, (p.N + (wide ? 128 : 64) - 1) / (wide ? 128 : 64), p.groups * p.split_k);
 #define LAUNCHW(BN_, AM, BK_, MK)                                                                                     \
   if (p.seg && p.tmem_a && half)                                                                                      \
-    igemm_tf32x3_ta_kernel<64, AM, BK_, MK, true><<<gridw, TaCfg<64, true>::THREADS, TaCfg<64, true>::SMEM, stream>>>( \
+    launch_k(igemm_tf32x3_ta_kernel<64, AM, BK_, MK, true>, gridw, TaCfg<64, true>::THREADS, TaCfg<64, true>::SMEM, stream,  \
         (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
         (float*)partial, kt_table, error_flag, tm_a, pl);                                                             \
   else if (p.seg && p.tmem_a)                                                                                         \
-    igemm_tf32x3_ta_kernel<BN_, AM, BK_, MK, false><<<gridw, TaCfg<BN_, false>::THREADS, TaCfg<BN_, false>::SMEM, stream>>>( \
+    launch_k(igemm_tf32x3_ta_kernel<BN_, AM, BK_, MK, false>, gridw, TaCfg<BN_, false>::THREADS, TaCfg<BN_, false>::SMEM, stream,  \
         (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
         (float*)partial, kt_table, error_flag, tm_a, pl);                                                             \
   else if (p.seg)                                                                                                     \
-    igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK, true><<<gridw, WS_THREADS, WsCfg<BN_>::SMEM, stream>>>(                  \
+    launch_k(igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK, true>, gridw, WS_THREADS, WsCfg<BN_>::SMEM, stream,                   \
         (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
         (float*)partial, error_flag, p);                                                                              \
   else                                                                                                                \
-    igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK, false><<<gridw, WS_THREADS, WsCfg<BN_>::SMEM, stream>>>(                 \
+    launch_k(igemm_tf32x3_ws_kernel<BN_, AM, BK_, MK, false>, gridw, WS_THREADS, WsCfg<BN_>::SMEM, stream,                  \
         (const float*)A, (const float*)B, (float*)C, a_row, a_col, b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,     \
         (float*)partial, error_flag, p)
 #define SWITCHW(BN_)                                   \
@@ -1603,7 +1626,7 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
 #undef LAUNCHW
     } else {
 #define LAUNCHT(AM, BK_, MK)                                                                                     \
-  igemm_tf32x3_kernel<AM, BK_, MK><<<grid, TNT, TSMEM_BYTES, stream>>>((const float*)A, (const float*)B, (float*)C, \
+  launch_k(igemm_tf32x3_kernel<AM, BK_, MK>, grid, TNT, TSMEM_BYTES, stream, (const float*)A, (const float*)B, (float*)C, \
                                                                         a_row, a_col, b_row, b_col, c_row, c_col,   \
                                                                         a_grp, b_grp, c_grp, (float*)partial,       \
                                                                         error_flag, p)
@@ -1623,7 +1646,7 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
     dim3 grid((p.M + BM - 1) / BM, (p.N + BN - 1) / BN, p.groups * p.split_k);
     dim3 block(NT);
 #define LAUNCH(AM, BK_, MK)                                                                                          \
-  igemm_f32_kernel<AM, BK_, MK><<<grid, block, 0, stream>>>((const float*)A, (const float*)B, (float*)C, a_row, a_col, \
+  launch_k(igemm_f32_kernel<AM, BK_, MK>, grid, block, 0, stream, (const float*)A, (const float*)B, (float*)C, a_row, a_col, \
                                                             b_row, b_col, c_row, c_col, a_grp, b_grp, c_grp,           \
                                                             (float*)partial, p)
     switch (v) {
@@ -1651,10 +1674,10 @@ cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B,
     const long long items = vec ? total / 4 : total;
     const bool tall = p.split_k >= 16;
     const unsigned blocks = (unsigned)(tall ? (items + 31) / 32 : (items + 255) / 256);
-    if (vec && tall) splitk_reduce_kernel<8, true><<<blocks, dim3(32, 8), 0, stream>>>(pp, cc, c_row, c_col, c_grp, p.M, p.N, p.groups, p.split_k);
-    else if (vec) splitk_reduce_kernel<1, true><<<blocks, dim3(256, 1), 0, stream>>>(pp, cc, c_row, c_col, c_grp, p.M, p.N, p.groups, p.split_k);
-    else if (tall) splitk_reduce_kernel<8, false><<<blocks, dim3(32, 8), 0, stream>>>(pp, cc, c_row, c_col, c_grp, p.M, p.N, p.groups, p.split_k);
-    else splitk_reduce_kernel<1, false><<<blocks, dim3(256, 1), 0, stream>>>(pp, cc, c_row, c_col, c_grp, p.M, p.N, p.groups, p.split_k);
+    if (vec && tall) launch_k(splitk_reduce_kernel<8, true>, blocks, dim3(32, 8), 0, stream, pp, cc, c_row, c_col, c_grp, p.M, p.N, p.groups, p.split_k);
+    else if (vec) launch_k(splitk_reduce_kernel<1, true>, blocks, dim3(256, 1), 0, stream, pp, cc, c_row, c_col, c_grp, p.M, p.N, p.groups, p.split_k);
+    else if (tall) launch_k(splitk_reduce_kernel<8, false>, blocks, dim3(32, 8), 0, stream, pp, cc, c_row, c_col, c_grp, p.M, p.N, p.groups, p.split_k);
+    else launch_k(splitk_reduce_kernel<1, false>, blocks, dim3(256, 1), 0, stream, pp, cc, c_row, c_col, c_grp, p.M, p.N, p.groups, p.split_k);
     if (launches) (*launches)++;
     e = cudaGetLastError();
   }
@@ -1936,5 +1959,7 @@ long long scatter_rows_scratch_ints(long long rows, long long updates) {
 int scatter_rows_launches(long long rows, long long updates) {
   return updates <= kScatterAllPairsMax ? 2 : 2 + 3 * scatter_radix_passes(rows);
 }
+
+void set_igemm_programmatic_launch(bool on) { g_igemm_programmatic_launch = on; }
 
 }  // namespace b200

@@ -52,6 +52,10 @@ cudaError_t matmul_f32_static_scratch(const float* A, const float* B, float* C, 
                                       const char** why);
 size_t static_scratch_bytes();
 
+// Programmatic stream serialization for the 16-bit product, transpose and repack kernels (on by default).
+void set_programmatic_launch(bool on);
+void set_igemm_programmatic_launch(bool on);
+
 // Test hook: one kernel whose bounded mbarrier wait (budget `polls`) runs out and counts up *error_flag.
 cudaError_t launch_expiring_wait(int polls, int* error_flag, cudaStream_t stream);
 

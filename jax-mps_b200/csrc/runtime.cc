@@ -75,6 +75,7 @@ struct DriverApi {
   CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
                            void**, void**) = nullptr;
+  CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;   // optional
   CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
   std::string error;
   bool ok = false;
@@ -96,6 +97,10 @@ DriverApi& driver() {
     api.ok = get("cuModuleLoadData", (void**)&api.ModuleLoadData) && get("cuModuleUnload", (void**)&api.ModuleUnload) &&
              get("cuModuleGetFunction", (void**)&api.ModuleGetFunction) &&
              get("cuLaunchKernel", (void**)&api.LaunchKernel) && get("cuGetErrorString", (void**)&api.GetErrorString);
+    if (api.ok) {
+      const std::string keep = api.error;
+      if (!get("cuLaunchKernelEx", (void**)&api.LaunchKernelEx)) { api.LaunchKernelEx = nullptr; api.error = keep; }
+    }
   });
   return api;
 }
@@ -337,7 +342,7 @@ struct b200_client {
   bool profiling = false;
   // debugging switches of the contraction kernels and the loop executor, read from the environment once at creation
   struct Switches { bool no_vec_gather = false, no_seg_gather = false, no_tmem_a = false, no_half_ctas = false, narrow_tiles = false,
-                    no_loop_graphs = false, no_tma_a = false; } sw;
+                    no_loop_graphs = false, no_tma_a = false, no_pdl = false; } sw;
   int reported_errors = 0;              // value of the error word at the last b200_client_synchronize
   int armed_wait_polls = 0;             // test hook: the next execution starts with a wait that runs out
   int* status_block = nullptr;          // pinned pairs handed to executions
@@ -582,8 +587,25 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
         vals[k] = x.ptrs[s.args[k]];
         argv[k] = &vals[k];
       }
-      CUresult r = driver().LaunchKernel(x.lp->functions[s.kernel], s.grid[0], s.grid[1], s.grid[2], s.block[0], s.block[1],
-                                         s.block[2], 0, (CUstream)st, argv, nullptr);
+      CUresult r;
+      if (driver().LaunchKernelEx && !c->sw.no_pdl) {
+        // programmatic stream serialization: the kernel is scheduled while the one in front of it drains, and waits for
+        // it (first statement of every generated kernel) before it reads or writes anything
+        CUlaunchConfig cfg = {};
+        cfg.gridDimX = s.grid[0]; cfg.gridDimY = s.grid[1]; cfg.gridDimZ = s.grid[2];
+        cfg.blockDimX = s.block[0]; cfg.blockDimY = s.block[1]; cfg.blockDimZ = s.block[2];
+        cfg.sharedMemBytes = 0;
+        cfg.hStream = (CUstream)st;
+        CUlaunchAttribute attr[1];
+        attr[0].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr[0].value.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        r = driver().LaunchKernelEx(&cfg, x.lp->functions[s.kernel], argv, nullptr);
+      } else {
+        r = driver().LaunchKernel(x.lp->functions[s.kernel], s.grid[0], s.grid[1], s.grid[2], s.block[0], s.block[1], s.block[2], 0,
+                                  (CUstream)st, argv, nullptr);
+      }
       if (r != CUDA_SUCCESS) {
         const char* msg = nullptr;
         driver().GetErrorString(r, &msg);
@@ -1036,6 +1058,9 @@ b200_error* create_client(const b200_client_options* o, ncclComm_t given_comm, b
   c->sw.narrow_tiles = getenv("B200_NARROW_TILES") != nullptr;
   c->sw.no_loop_graphs = getenv("B200_NO_LOOP_GRAPHS") != nullptr;
   c->sw.no_tma_a = getenv("B200_NO_TMA_A") != nullptr;
+  c->sw.no_pdl = getenv("B200_NO_PDL") != nullptr;
+  set_programmatic_launch(!c->sw.no_pdl);
+  set_igemm_programmatic_launch(!c->sw.no_pdl && !getenv("B200_NO_IGEMM_PDL"));
   if (!driver().ok) return make_error(B200_FAILED_PRECONDITION, driver().error);
   if (c->nprocs > 1) {
     NcclApi& n = nccl();

@@ -28,6 +28,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
+// First statement of a kernel that may be launched with programmatic stream serialization: the kernel is scheduled
+// while the one in front of it drains, and waits here until everything in front of it has completed and its memory
+// is visible. Without the launch attribute this is a no-op. (Letting dependents start earlier still, with
+// griddepcontrol.launch_dependents, lost time on the measured programs: 6.42 -> 6.73 ms on the DistilBERT-shaped step.)
+__device__ __forceinline__ void pdl_prologue() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
   // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart (SBO), LBO unused (1), descriptor version 1
   return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
