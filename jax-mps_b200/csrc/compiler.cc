@@ -1896,6 +1896,19 @@ struct Planner {
     s.kind = Step::GEMM16;
     s.label = op->name;
     s.g16 = d.g;
+    // B may be read ahead of the wait for the kernel in front when that kernel cannot be its writer: B is a program
+    // input, or it was made in front of the loop whose body this is and a kernel of the body already precedes this one
+    {
+      bool is_static = false;
+      if (!d.rb.needed) {
+        if (!rhs->def) is_static = rhs->owner && rhs->owner->parent_op == nullptr;
+        else if (rhs->def->parent != st.block) {
+          for (auto& prev : plan.steps)
+            if (prev.kind == Step::KERNEL || prev.kind == Step::GEMM16 || prev.kind == Step::IGEMM) { is_static = true; break; }
+        }
+      }
+      s.g16.b_static = is_static ? 1 : 0;
+    }
     const int a = operand(lhs, d.ra), b = operand(rhs, d.rb);
     s.args = {a, b, slot_of.at(out)};
     s.iparams = {0, 0};
@@ -3667,9 +3680,9 @@ void dump_plan(const CompiledProgram& prog, const Plan& p, std::ostringstream& o
         break;
       case Step::MEMCPY: os << "memcpy " << s.bytes; break;
       case Step::GEMM16:
-        os << (s.g16.path == 0 ? "gemm16" : s.g16.path == 1 ? "gemv16_nc" : "gemv16_kc") << " M=" << s.g16.M << " N=" << s.g16.N
+        os << (s.g16.path == 0 ? "gemm16" : s.g16.path == 1 ? "gemv16_nc" : s.g16.path == 3 ? "gemv16_nc_small" : "gemv16_kc") << " M=" << s.g16.M << " N=" << s.g16.N
            << " K=" << s.g16.K << " G=" << s.g16.G << " a_kcontig=" << (s.g16.a_ks == 1) << " b_kcontig=" << (s.g16.b_ks == 1)
-           << " bn=" << s.g16.bn << " splitK=" << s.g16.split_k << " out=" << (s.g16.c_kind == 2 ? "f32" : "16") << " " << s.label;
+           << " bn=" << s.g16.bn << " splitK=" << s.g16.split_k << (s.g16.b_static ? " staticB" : "") << " out=" << (s.g16.c_kind == 2 ? "f32" : "16") << " " << s.label;
         break;
       case Step::TRANSPOSE:
         os << "transpose batch=" << s.iparams[1] << " rows=" << s.iparams[2] << " cols=" << s.iparams[3] << " bytes=" << s.iparams[0]

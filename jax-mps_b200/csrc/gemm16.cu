@@ -402,6 +402,7 @@ struct GemvParams {
   int M, N, K, G;
   long long a_ms, a_ks, a_gs, b_ld, b_gs;      // b_ld: stride of k (nc) or of n (kc)
   int kc, splits, c_kind, vec;                 // vec: 128-bit loads of B are aligned
+  int b_static;                                // B may be read before the wait for the kernel in front
 };
 
 template <bool BF16>
@@ -431,7 +432,6 @@ template <int MAXM, bool BF16, int UNROLL>
 __global__ void __launch_bounds__(256) gemv16_nc_kernel(const uint16_t* __restrict__ A, const uint16_t* __restrict__ B,
                                                        void* __restrict__ C, float* __restrict__ scratch,
                                                        int* __restrict__ counters, GemvParams p) {
-  pdl_prologue();
   extern __shared__ float gemv_smem[];
   float* a_s = gemv_smem;                              // [MAXM][kc_pad]
   const int kc_pad = p.kc + 8 * UNROLL;
@@ -442,20 +442,10 @@ __global__ void __launch_bounds__(256) gemv16_nc_kernel(const uint16_t* __restri
   const int kbeg = sp * p.kc, kend = min(p.K, kbeg + p.kc);
   const uint16_t* Ag = A + (long long)g * p.a_gs;
   const uint16_t* Bg = B + (long long)g * p.b_gs;
-  for (int i = tid; i < MAXM * kc_pad; i += 256) {
-    const int m = i / kc_pad, kk = i % kc_pad;
-    a_s[i] = (m < p.M && kbeg + kk < kend) ? one16<BF16>(Ag[m * p.a_ms + (long long)(kbeg + kk) * p.a_ks]) : 0.f;
-  }
-  __syncthreads();
   const int n = panel * 256 + lane * 8;
-  float acc[MAXM][8];
-#pragma unroll
-  for (int m = 0; m < MAXM; ++m)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[m][j] = 0.f;
   const bool vec = p.vec && n + 8 <= p.N;
-  for (int k = kbeg + warp; k < kend; k += 8 * UNROLL) {
-    uint4 v[UNROLL];
+  uint4 v[UNROLL];
+  auto load_rows = [&](int k) {
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int kk = k + 8 * u;
@@ -472,6 +462,24 @@ __global__ void __launch_bounds__(256) gemv16_nc_kernel(const uint16_t* __restri
         }
       }
     }
+  };
+  // The first rows of B are on their way before the slice of A is staged; when nothing in flight writes B they are
+  // requested even before the wait for the kernel in front, whose tail then overlaps the first HBM round trip.
+  if (p.b_static) load_rows(kbeg + warp);
+  pdl_prologue();
+  if (!p.b_static) load_rows(kbeg + warp);
+  for (int i = tid; i < MAXM * kc_pad; i += 256) {
+    const int m = i / kc_pad, kk = i % kc_pad;
+    a_s[i] = (m < p.M && kbeg + kk < kend) ? one16<BF16>(Ag[m * p.a_ms + (long long)(kbeg + kk) * p.a_ks]) : 0.f;
+  }
+  __syncthreads();
+  float acc[MAXM][8];
+#pragma unroll
+  for (int m = 0; m < MAXM; ++m)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[m][j] = 0.f;
+  for (int k = kbeg + warp; k < kend; k += 8 * UNROLL) {
+    if (k != kbeg + warp) load_rows(k);
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const float b0 = lo16<BF16>(v[u].x), b1 = hi16<BF16>(v[u].x), b2 = lo16<BF16>(v[u].y), b3 = hi16<BF16>(v[u].y);
@@ -567,19 +575,126 @@ __global__ void __launch_bounds__(256) gemv16_nc_kernel(const uint16_t* __restri
   }
 }
 
+// n contiguous in B, a small B (probabilities against a value cache: a few hundred rows of a few hundred columns). The
+// whole product is one round trip to memory: a CTA owns 32 columns and all of K, its 64 groups of four lanes take the
+// rows k = slot, slot + 64, ... (up to 16 independent 16-byte loads per lane, all issued before any is used), the
+// sums of the groups meet by warp shuffles and once through shared memory in warp order. No K split across CTAs, so no
+// scratch, no counter and no second pass.
+template <int MAXM, bool BF16>
+__global__ void __launch_bounds__(256) gemv16_nc_small_kernel(const uint16_t* __restrict__ A, const uint16_t* __restrict__ B,
+                                                             void* __restrict__ C, GemvParams p) {
+  constexpr int R = 16;
+  extern __shared__ float gemv_smem[];
+  float* a_s = gemv_smem;                              // [MAXM][K]
+  float* red = a_s + MAXM * p.K;                       // [8 warps][MAXM][32]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = blockIdx.y, cg = lane & 3, slot = warp * 8 + (lane >> 2);
+  const uint16_t* Ag = A + (long long)g * p.a_gs;
+  const uint16_t* Bg = B + (long long)g * p.b_gs;
+  const int n = blockIdx.x * 32 + cg * 8;
+  const bool vec = p.vec && n + 8 <= p.N;
+  uint4 v[R];
+  auto load_rows = [&]() {
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      const int k = slot + 64 * j;
+      v[j] = make_uint4(0, 0, 0, 0);
+      if (k < p.K) {
+        const uint16_t* src = Bg + (long long)k * p.b_ld + n;
+        if (vec) v[j] = *reinterpret_cast<const uint4*>(src);
+        else if (n < p.N) {
+          uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            if (n + q < p.N) w[q >> 1] |= (uint32_t)src[q] << (16 * (q & 1));
+          v[j] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+  };
+  if (p.b_static) load_rows();
+  pdl_prologue();
+  if (!p.b_static) load_rows();
+  for (int i = tid; i < MAXM * p.K; i += 256) {
+    const int m = i / p.K, k = i - m * p.K;
+    a_s[i] = m < p.M ? one16<BF16>(Ag[m * p.a_ms + (long long)k * p.a_ks]) : 0.f;
+  }
+  __syncthreads();
+  float acc[MAXM][8];
+#pragma unroll
+  for (int m = 0; m < MAXM; ++m)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[m][q] = 0.f;
+#pragma unroll
+  for (int j = 0; j < R; ++j) {
+    const int k = slot + 64 * j;
+    if (k >= p.K) break;
+    const float b0 = lo16<BF16>(v[j].x), b1 = hi16<BF16>(v[j].x), b2 = lo16<BF16>(v[j].y), b3 = hi16<BF16>(v[j].y);
+    const float b4 = lo16<BF16>(v[j].z), b5 = hi16<BF16>(v[j].z), b6 = lo16<BF16>(v[j].w), b7 = hi16<BF16>(v[j].w);
+#pragma unroll
+    for (int m = 0; m < MAXM; ++m) {
+      const float a = a_s[m * p.K + k];
+      acc[m][0] = fmaf(a, b0, acc[m][0]); acc[m][1] = fmaf(a, b1, acc[m][1]);
+      acc[m][2] = fmaf(a, b2, acc[m][2]); acc[m][3] = fmaf(a, b3, acc[m][3]);
+      acc[m][4] = fmaf(a, b4, acc[m][4]); acc[m][5] = fmaf(a, b5, acc[m][5]);
+      acc[m][6] = fmaf(a, b6, acc[m][6]); acc[m][7] = fmaf(a, b7, acc[m][7]);
+    }
+  }
+  // the eight row slots of a warp (lanes with equal lane & 3) by shuffles, then the eight warps in warp order
+#pragma unroll
+  for (int m = 0; m < MAXM; ++m)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      float s = acc[m][q];
+      s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
+      s += __shfl_xor_sync(0xFFFFFFFFu, s, 8);
+      s += __shfl_xor_sync(0xFFFFFFFFu, s, 16);
+      if (lane < 4) red[(warp * MAXM + m) * 32 + cg * 8 + q] = s;
+    }
+  __syncthreads();
+  for (int t = tid; t < MAXM * 32; t += 256) {
+    const int m = t >> 5, c = t & 31, nn = blockIdx.x * 32 + c;
+    if (m < p.M && nn < p.N) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) s += red[(w * MAXM + m) * 32 + c];
+      store_c(C, ((long long)g * p.M + m) * p.N + nn, s, p.c_kind);
+    }
+  }
+}
+
 // k contiguous in B (a tied-embedding logits product, scores against a key cache, a weight transposed in front of a
 // decode loop). Grid (CTAs, groups), 256 threads; a warp takes NW output columns at a time, its lanes stride over k with
 // 128-bit loads (K a multiple of 8), A sits in shared memory as 16-bit values, per-lane sums meet in a warp-shuffle tree.
 template <int MAXM, bool BF16, int NW>
 __global__ void __launch_bounds__(256) gemv16_kc_kernel(const uint16_t* __restrict__ A, const uint16_t* __restrict__ B,
                                                        void* __restrict__ C, GemvParams p) {
-  pdl_prologue();
   extern __shared__ float gemv_smem[];
   uint16_t* a_s = (uint16_t*)gemv_smem;                // [M][K], 16-byte aligned rows (K % 8 == 0)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = blockIdx.y;
   const uint16_t* Ag = A + (long long)g * p.a_gs;
   const uint16_t* Bg = B + (long long)g * p.b_gs;
+  // UNR chunks of 8 k per column are loaded before any is used: NW * UNR independent 16-byte loads in flight per lane
+  constexpr int UNR = NW == 1 ? 8 : 2;
+  const int tasks = (p.N + NW - 1) / NW;
+  uint4 b[UNR][NW];
+  auto load_cols = [&](int n0, int k0) {
+#pragma unroll
+    for (int u = 0; u < UNR; ++u)
+#pragma unroll
+      for (int q = 0; q < NW; ++q) {
+        const int k = k0 + 256 * u;
+        b[u][q] = (n0 + q < p.N && k < p.K) ? __ldcs(reinterpret_cast<const uint4*>(Bg + (long long)(n0 + q) * p.b_ld + k))
+                                            : make_uint4(0, 0, 0, 0);
+      }
+  };
+  // The warp's first loads of B are on their way before A is staged; when nothing in flight writes B they are requested
+  // even before the wait for the kernel in front, whose tail then overlaps the first HBM round trip.
+  const int first_task = blockIdx.x * 8 + warp;
+  if (p.b_static && first_task < tasks) load_cols(first_task * NW, lane * 8);
+  pdl_prologue();
+  if (!p.b_static && first_task < tasks) load_cols(first_task * NW, lane * 8);
   if (p.a_ks == 1 && (p.a_ms & 7) == 0 && (p.a_gs & 7) == 0 && (((uintptr_t)A) & 15) == 0) {
     const int chunks = p.K >> 3;                        // rows of A are whole 16-byte chunks (K % 8 == 0)
     for (int i = tid; i < p.M * chunks; i += 256) {
@@ -593,10 +708,7 @@ __global__ void __launch_bounds__(256) gemv16_kc_kernel(const uint16_t* __restri
     }
   }
   __syncthreads();
-  // UNR chunks of 8 k per column are loaded before any is used: NW * UNR independent 16-byte loads in flight per lane
-  constexpr int UNR = NW == 1 ? 8 : 2;
-  const int tasks = (p.N + NW - 1) / NW;
-  for (int task = blockIdx.x * 8 + warp; task < tasks; task += gridDim.x * 8) {
+  for (int task = first_task; task < tasks; task += gridDim.x * 8) {
     const int n0 = task * NW;
     float acc[NW][MAXM];
 #pragma unroll
@@ -604,15 +716,7 @@ __global__ void __launch_bounds__(256) gemv16_kc_kernel(const uint16_t* __restri
 #pragma unroll
       for (int m = 0; m < MAXM; ++m) acc[q][m] = 0.f;
     for (int k0 = lane * 8; k0 < p.K; k0 += 256 * UNR) {
-      uint4 b[UNR][NW];
-#pragma unroll
-      for (int u = 0; u < UNR; ++u)
-#pragma unroll
-        for (int q = 0; q < NW; ++q) {
-          const int k = k0 + 256 * u;
-          b[u][q] = (n0 + q < p.N && k < p.K) ? __ldcs(reinterpret_cast<const uint4*>(Bg + (long long)(n0 + q) * p.b_ld + k))
-                                              : make_uint4(0, 0, 0, 0);
-        }
+      if (task != first_task || k0 != lane * 8) load_cols(n0, k0);
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
         const int k = k0 + 256 * u;
@@ -720,6 +824,10 @@ bool gemm16_plan(Gemm16Launch& g, bool aligned) {
   g.split_k = 1;
   const int SMS = 148;
   if (g.M <= 8) {
+    if (g.b_ns == 1 && g.K <= 1024 && (long long)g.K * g.N <= (1 << 20)) {
+      g.path = 3;                                    // a small B: one round trip, no K split across CTAs
+      return true;
+    }
     if (g.b_ns == 1) {
       // every element of B once: column panels of 256 times K splits should give each SM several CTAs
       g.path = 1;
@@ -824,16 +932,24 @@ cudaError_t launch_gemm16(const Gemm16Launch& g, const void* A, const void* B, v
                           int* error_flag, cudaStream_t stream, int* launches, const char** why) {
   *why = nullptr;
   const bool bf16 = g.in_fmt == 1;
-  if (g.path == 1 || g.path == 2) {
+  if (g.path == 1 || g.path == 2 || g.path == 3) {
     GemvParams p;
     p.M = g.M; p.N = g.N; p.K = g.K; p.G = g.G;
     p.a_ms = g.a_ms; p.a_ks = g.a_ks; p.a_gs = g.a_gs;
-    p.b_ld = g.path == 1 ? g.b_ks : g.b_ns;
+    p.b_ld = g.path == 2 ? g.b_ns : g.b_ks;
     p.b_gs = g.b_gs;
     p.kc = g.gemv_kc; p.splits = g.split_k; p.c_kind = g.c_kind;
     p.vec = (((uintptr_t)B) & 15) == 0 && p.b_ld % 8 == 0 && g.b_gs % 8 == 0;
+    p.b_static = g.b_static;
     const int maxm = g.M == 1 ? 1 : 8;
-    if (g.path == 1) {
+    if (g.path == 3) {
+      dim3 grid((g.N + 31) / 32, g.G);
+      const size_t smem = (size_t)maxm * g.K * 4 + (size_t)8 * maxm * 32 * 4;
+      if (maxm == 1 && bf16) launch_k(gemv16_nc_small_kernel<1, true>, grid, 256, smem, stream, (const uint16_t*)A, (const uint16_t*)B, C, p);
+      else if (maxm == 1) launch_k(gemv16_nc_small_kernel<1, false>, grid, 256, smem, stream, (const uint16_t*)A, (const uint16_t*)B, C, p);
+      else if (bf16) launch_k(gemv16_nc_small_kernel<8, true>, grid, 256, smem, stream, (const uint16_t*)A, (const uint16_t*)B, C, p);
+      else launch_k(gemv16_nc_small_kernel<8, false>, grid, 256, smem, stream, (const uint16_t*)A, (const uint16_t*)B, C, p);
+    } else if (g.path == 1) {
       if (g.split_k > 1 && (!scratch || !counters)) { *why = "skinny product without its scratch"; return cudaErrorInvalidValue; }
       dim3 grid((g.N + 255) / 256, g.split_k, g.G);
       static bool configured[64] = {};

@@ -9,6 +9,9 @@ struct Gemm16Launch {
   long long b_ks = 0, b_ns = 0, b_gs = 0;   // element strides of k, n and the group in B
   int in_fmt = 1;                           // operands: 0 f16, 1 bf16
   int c_kind = 1;                           // result: 0 f16, 1 bf16, 2 f32
+  int b_static = 0;                         // B is not written by the kernel in front of this one (a program input, or made
+                                            // in front of the loop whose body this product belongs to): the skinny
+                                            // kernels may fetch it before they wait for that kernel
   // filled by gemm16_plan (the compiler sizes the scratch from it, the launcher follows it)
   int path = 0, bn = 128, split_k = 1, kt_per_split = 0, gemv_kc = 0, nw = 1;
   long long scratch_floats = 0;             // fp32 partial sums
