@@ -418,6 +418,49 @@ __device__ __forceinline__ float hi16(uint32_t w) {
 template <bool BF16>
 __device__ __forceinline__ float one16(uint16_t h) { return lo16<BF16>((uint32_t)h); }
 
+// A[m][k0 .. k0 + len) of M rows -> dst[m][pad] as fp32 (zero past `len`), by 16-byte loads issued four at a time per
+// thread when the rows allow it (k contiguous, 16-byte aligned starts): a loop of dependent scalar loads costs one
+// memory round trip per iteration, which is what a skinny product's time is made of.
+template <bool BF16>
+__device__ __forceinline__ void stage_a_f32(float* __restrict__ dst, const uint16_t* __restrict__ Ag, int M, int rows, int pad,
+                                            int len, long long a_ms, long long a_ks, int k0, int tid) {
+  const bool wide = a_ks == 1 && (a_ms & 7) == 0 && (k0 & 7) == 0 && ((((uintptr_t)Ag) & 15) == 0) && (pad & 7) == 0;
+  if (wide) {
+    const int cpr = pad >> 3, chunks = rows * cpr;     // 8-element chunks per staged row
+    for (int i0 = tid; i0 < chunks; i0 += 256 * 4) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + 256 * u;
+        v[u] = make_uint4(0, 0, 0, 0);
+        if (i < chunks) {
+          const int m = i / cpr, c = i - m * cpr;
+          if (m < M && 8 * c + 8 <= len) v[u] = *reinterpret_cast<const uint4*>(Ag + m * a_ms + k0 + 8 * c);
+          else if (m < M && 8 * c < len) {
+            uint32_t w[4] = {0, 0, 0, 0};
+            for (int q = 0; q < 8 && 8 * c + q < len; ++q) w[q >> 1] |= (uint32_t)Ag[m * a_ms + k0 + 8 * c + q] << (16 * (q & 1));
+            v[u] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + 256 * u;
+        if (i < chunks) {
+          float* d = dst + 8 * i;
+          d[0] = lo16<BF16>(v[u].x); d[1] = hi16<BF16>(v[u].x); d[2] = lo16<BF16>(v[u].y); d[3] = hi16<BF16>(v[u].y);
+          d[4] = lo16<BF16>(v[u].z); d[5] = hi16<BF16>(v[u].z); d[6] = lo16<BF16>(v[u].w); d[7] = hi16<BF16>(v[u].w);
+        }
+      }
+    }
+  } else {
+    for (int i = tid; i < rows * pad; i += 256) {
+      const int m = i / pad, kk = i - m * pad;
+      dst[i] = (m < M && kk < len) ? one16<BF16>(Ag[m * a_ms + (long long)(k0 + kk) * a_ks]) : 0.f;
+    }
+  }
+}
+
 __device__ __forceinline__ void store_c(void* C, long long i, float v, int c_kind) {
   if (c_kind == 2) ((float*)C)[i] = v;
   else ((uint16_t*)C)[i] = (uint16_t)to16(v, c_kind);
@@ -468,10 +511,7 @@ __global__ void __launch_bounds__(256) gemv16_nc_kernel(const uint16_t* __restri
   if (p.b_static) load_rows(kbeg + warp);
   pdl_prologue();
   if (!p.b_static) load_rows(kbeg + warp);
-  for (int i = tid; i < MAXM * kc_pad; i += 256) {
-    const int m = i / kc_pad, kk = i % kc_pad;
-    a_s[i] = (m < p.M && kbeg + kk < kend) ? one16<BF16>(Ag[m * p.a_ms + (long long)(kbeg + kk) * p.a_ks]) : 0.f;
-  }
+  stage_a_f32<BF16>(a_s, Ag, p.M, MAXM, kc_pad, kend - kbeg, p.a_ms, p.a_ks, kbeg, tid);
   __syncthreads();
   float acc[MAXM][8];
 #pragma unroll
@@ -615,10 +655,7 @@ __global__ void __launch_bounds__(256) gemv16_nc_small_kernel(const uint16_t* __
   if (p.b_static) load_rows();
   pdl_prologue();
   if (!p.b_static) load_rows();
-  for (int i = tid; i < MAXM * p.K; i += 256) {
-    const int m = i / p.K, k = i - m * p.K;
-    a_s[i] = m < p.M ? one16<BF16>(Ag[m * p.a_ms + (long long)k * p.a_ks]) : 0.f;
-  }
+  stage_a_f32<BF16>(a_s, Ag, p.M, MAXM, p.K, p.K, p.a_ms, p.a_ks, 0, tid);
   __syncthreads();
   float acc[MAXM][8];
 #pragma unroll
@@ -697,9 +734,21 @@ __global__ void __launch_bounds__(256) gemv16_kc_kernel(const uint16_t* __restri
   if (!p.b_static && first_task < tasks) load_cols(first_task * NW, lane * 8);
   if (p.a_ks == 1 && (p.a_ms & 7) == 0 && (p.a_gs & 7) == 0 && (((uintptr_t)A) & 15) == 0) {
     const int chunks = p.K >> 3;                        // rows of A are whole 16-byte chunks (K % 8 == 0)
-    for (int i = tid; i < p.M * chunks; i += 256) {
-      const int m = i / chunks, c = i - m * chunks;
-      reinterpret_cast<uint4*>(a_s)[i] = *reinterpret_cast<const uint4*>(Ag + m * p.a_ms + 8 * c);
+    for (int i0 = tid; i0 < p.M * chunks; i0 += 256 * 4) {
+      uint4 v[4];                                       // four loads in flight per thread
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + 256 * u;
+        if (i < p.M * chunks) {
+          const int m = i / chunks, c = i - m * chunks;
+          v[u] = *reinterpret_cast<const uint4*>(Ag + m * p.a_ms + 8 * c);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + 256 * u;
+        if (i < p.M * chunks) reinterpret_cast<uint4*>(a_s)[i] = v[u];
+      }
     }
   } else {
     for (int i = tid; i < p.M * p.K; i += 256) {
