@@ -287,6 +287,13 @@ b200_error* b200_client_profile_report(b200_client* client, char** json);
  * barrier nothing arrives at. The wait runs out (nothing hangs, nothing faults) and the execution reports the failure
  * the way an expired tensor-core pipeline wait does. No counterpart in the reference. */
 b200_error* b200_client_debug_arm_wait_expiry(b200_client* client, int polls);
+/* How many times executions on this client have synchronised the compute stream to read a `while` predicate or a
+ * `case` index back to the host (the reference does so on every iteration of a data-dependent loop,
+ * src/pjrt_plugin/ops/control_flow.cc:505-536). Loops and cases whose bodies only launch kernels and device copies run
+ * as conditional CUDA-graph nodes from their second execution on and add nothing here. A data-dependent loop that is
+ * resident on the device ends with an error (reported like an expired device-side wait) once it has run for
+ * B200_WHILE_TIME_LIMIT_S seconds (default 30). */
+long long b200_client_host_syncs(const b200_client* client);
 /* Measures the rate of tcgen05.mma.kind::tf32 on the client's device (TFLOP/s; issue loop alone, operands resident in
  * shared memory). The fp32-accurate contraction kernels issue three such MMAs per product: their ceiling is a third of
  * this figure. A measurement aid with no counterpart in the reference (its numbers come from MPS_PROFILE,

@@ -127,6 +127,7 @@ SIGNATURES = {
     "b200_client_launch_count": (C.c_int64, [_P]),
     "b200_client_probe_tf32_mma_rate": (_P, [_P, C.POINTER(C.c_double)]),
     "b200_client_debug_arm_wait_expiry": (_P, [_P, C.c_int]),
+    "b200_client_host_syncs": (C.c_longlong, [_P]),
     "b200_device_num_memories": (C.c_int, [_P]),
     "b200_memory_id": (C.c_int, [_P, C.c_int]),
     "b200_memory_kind": (C.c_char_p, [_P, C.c_int]),
@@ -632,6 +633,10 @@ class Client:
     def debug_arm_wait_expiry(self, polls: int = 1000):
         """Test hook: the next execution starts with a bounded device-side wait that runs out."""
         _check(load_library().b200_client_debug_arm_wait_expiry(self._h, polls))
+
+    def host_syncs(self) -> int:
+        """Stream synchronisations inside executions so far (predicates of `while` / indices of `case` read by the host)."""
+        return int(load_library().b200_client_host_syncs(self._h))
 
     def probe_tf32_mma_rate(self) -> float:
         """TFLOP/s of the TF32 tensor-core MMA on this device (issue loop alone); the 3xTF32 fp32 path tops out at a third."""

@@ -1862,6 +1862,42 @@ __global__ void expiring_wait_kernel(int polls, int* __restrict__ error_flag) {
 }
 }  // namespace
 
+// ---------------------------------------------------------------------------
+// Conditional graph nodes: the kernels that set a node's handle from a value on the device, so that a data-dependent
+// `while` or `case` needs no host round trip. The while form is bounded in time: `*started` holds the loop's start
+// (written when `first`), and once `limit_ns` has passed the loop ends and the error counter goes up.
+namespace {
+__global__ void while_handle_kernel(cudaGraphConditionalHandle handle, const unsigned char* __restrict__ pred,
+                                    unsigned long long* __restrict__ started, unsigned long long limit_ns, int first,
+                                    int* __restrict__ error_flag) {
+  unsigned long long now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+  if (first) *started = now;
+  unsigned int go = *pred != 0 ? 1u : 0u;
+  if (go && now - *started > limit_ns) {
+    go = 0u;
+    atomicAdd(error_flag, 1);
+  }
+  cudaGraphSetConditional(handle, go);
+}
+__global__ void switch_handle_kernel(cudaGraphConditionalHandle handle, const int* __restrict__ index, int branches) {
+  const int i = *index;
+  cudaGraphSetConditional(handle, (unsigned int)((i < 0 || i >= branches) ? branches - 1 : i));   // out of range: the last branch
+}
+}  // namespace
+
+cudaError_t launch_while_handle(unsigned long long handle, const void* pred, unsigned long long* started, double limit_seconds,
+                                bool first, int* error_flag, cudaStream_t stream) {
+  while_handle_kernel<<<1, 1, 0, stream>>>((cudaGraphConditionalHandle)handle, (const unsigned char*)pred, started,
+                                           (unsigned long long)(limit_seconds * 1e9), first ? 1 : 0, error_flag);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_switch_handle(unsigned long long handle, const void* index, int branches, cudaStream_t stream) {
+  switch_handle_kernel<<<1, 1, 0, stream>>>((cudaGraphConditionalHandle)handle, (const int*)index, branches);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_expiring_wait(int polls, int* error_flag, cudaStream_t stream) {
   expiring_wait_kernel<<<1, 32, 0, stream>>>(polls < 1 ? 1 : polls, error_flag);
   return cudaGetLastError();

@@ -56,6 +56,13 @@ size_t static_scratch_bytes();
 void set_programmatic_launch(bool on);
 void set_igemm_programmatic_launch(bool on);
 
+// One-thread kernels that set the handle of a conditional graph node from device memory: `pred` (one byte) for a while
+// node, bounded by `limit_seconds` from the loop's first evaluation (`first` stores the start in *started; when the
+// limit passes the loop ends and *error_flag goes up); `index` (i32, out of range = last branch) for a switch node.
+cudaError_t launch_while_handle(unsigned long long handle, const void* pred, unsigned long long* started, double limit_seconds,
+                                bool first, int* error_flag, cudaStream_t stream);
+cudaError_t launch_switch_handle(unsigned long long handle, const void* index, int branches, cudaStream_t stream);
+
 // Test hook: one kernel whose bounded mbarrier wait (budget `polls`) runs out and counts up *error_flag.
 cudaError_t launch_expiring_wait(int polls, int* error_flag, cudaStream_t stream);
 

@@ -309,8 +309,13 @@ struct LoadedProgram {
   // addresses the graph was captured with.
   struct LoopGraph { const void* step; std::vector<void*> ptrs; cudaGraphExec_t exec; int launches; };
   std::vector<LoopGraph> loop_graphs;
+  // Graphs of data-dependent loops and cases (conditional nodes), per step and per set of addresses of the slots the
+  // step and everything below it touches.
+  std::vector<LoopGraph> cond_graphs;
   ~LoadedProgram() {
     for (auto& g : loop_graphs)
+      if (g.exec) cudaGraphExecDestroy(g.exec);
+    for (auto& g : cond_graphs)
       if (g.exec) cudaGraphExecDestroy(g.exec);
     for (auto* a : arenas)
       if (a) cudaFree(a);
@@ -338,11 +343,14 @@ struct b200_client {
   std::vector<PinnedBlock> pinned;
   unsigned char* pred_host = nullptr;   // pinned byte for while-loop predicates
   int* error_flag = nullptr;            // device word raised by kernels whose bounded waits expire
+  unsigned long long* loop_guard = nullptr;   // device: start time of the data-dependent loop that is running
+  double while_limit_s = 30.0;          // a device-resident data-dependent loop ends with an error after this long
+  long long host_syncs = 0;             // stream synchronisations inside executions (predicates read back by the host)
   bool tensor_cores = true;
   bool profiling = false;
   // debugging switches of the contraction kernels and the loop executor, read from the environment once at creation
   struct Switches { bool no_vec_gather = false, no_seg_gather = false, no_tmem_a = false, no_half_ctas = false, narrow_tiles = false,
-                    no_loop_graphs = false, no_tma_a = false, no_pdl = false; } sw;
+                    no_loop_graphs = false, no_tma_a = false, no_pdl = false, no_device_cf = false; } sw;
   int reported_errors = 0;              // value of the error word at the last b200_client_synchronize
   int armed_wait_polls = 0;             // test hook: the next execution starts with a wait that runs out
   int* status_block = nullptr;          // pinned pairs handed to executions
@@ -551,6 +559,7 @@ struct ExecCtx {
   LoadedProgram* lp;
   std::vector<void*> ptrs;
   int launches = 0;
+  bool plain_launch = false;            // while the bodies of conditional graph nodes are recorded: no programmatic launches
   bool coll_pending = false;            // work on the collective stream that the compute stream has not waited for yet
   cudaStream_t coll_stream = nullptr;   // set while the members of an all-reduce group are issued
   struct Timed { std::string kind, key; cudaEvent_t a, b; };
@@ -574,6 +583,17 @@ bool graph_safe(const Plan& plan) {
   return true;
 }
 
+// Addresses of every slot a step and the plans below it refer to, in a fixed order.
+void touched_addresses(const ExecCtx& x, const Step& s, std::vector<void*>& out, bool top = true) {
+  for (int a : s.args) out.push_back(x.ptrs[a]);
+  for (int a : s.state) out.push_back(x.ptrs[a]);
+  if (!top) for (int a : s.init) out.push_back(x.ptrs[a]);      // the outermost loop's initial values are copied in front of the graph
+  for (int a : s.next) out.push_back(x.ptrs[a]);
+  if (s.pred >= 0) out.push_back(x.ptrs[s.pred]);
+  for (auto& p : s.sub)
+    if (p) for (const Step& t : p->steps) touched_addresses(x, t, out, false);
+}
+
 b200_error* run_step(ExecCtx& x, const Step& s) {
   b200_client* c = x.c;
   cudaStream_t st = c->compute;
@@ -588,7 +608,7 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
         argv[k] = &vals[k];
       }
       CUresult r;
-      if (driver().LaunchKernelEx && !c->sw.no_pdl) {
+      if (driver().LaunchKernelEx && !c->sw.no_pdl && !x.plain_launch) {
         // programmatic stream serialization: the kernel is scheduled while the one in front of it drains, and waits for
         // it (first statement of every generated kernel) before it reads or writes anything
         CUlaunchConfig cfg = {};
@@ -807,14 +827,121 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
           if (auto* e = iterate()) return e;
         return finish();
       }
+      // Data-dependent loop. On the device when condition and body only launch kernels and device copies: a CUDA graph
+      // of [condition, handle] -> while node { body, copies of the carried values, condition, handle }, where
+      // `handle` is a one-thread kernel that sets the node's handle from the predicate (the reference pays a host
+      // read-back per iteration, src/pjrt_plugin/ops/control_flow.cc:505-536). Inside the graph carried values are
+      // copied, not exchanged (the addresses are part of the recording). The first execution of a loop with a given
+      // set of addresses runs through the host, which also loads every kernel; the graph is recorded after it.
+      cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+      CUDA_TRY(cudaStreamIsCapturing(st, &capturing));
+      const bool on_device = !c->sw.no_device_cf && !c->profiling && capturing == cudaStreamCaptureStatusNone &&
+                             graph_safe(*s.sub[0]) && graph_safe(*s.sub[1]);
+      std::vector<void*> touched;
+      if (on_device) {
+        touched_addresses(x, s, touched);
+        for (auto& g : x.lp->cond_graphs)
+          if (g.step == &s && g.ptrs == touched) {
+            CUDA_TRY(cudaGraphLaunch(g.exec, st));
+            x.launches += g.launches;
+            return nullptr;
+          }
+      }
+      const std::vector<void*> at_start = x.ptrs;
+      long long trips = 0;
       for (long long it = 0;; it++) {
         if (auto* e = run_plan(x, *s.sub[0])) return e;
         CUDA_TRY(cudaMemcpyAsync(c->pred_host, x.ptrs[s.pred], 1, cudaMemcpyDeviceToHost, st));
         CUDA_TRY(cudaStreamSynchronize(st));
+        c->host_syncs++;
         if (!*c->pred_host) break;
         if (auto* e = iterate()) return e;
+        trips++;
       }
-      return finish();
+      if (auto* e = finish()) return e;
+      if (on_device && trips > 0 && x.ptrs == at_start) {
+        if (x.lp->cond_graphs.size() >= 16) {
+          CUDA_TRY(cudaStreamSynchronize(st));
+          cudaGraphExecDestroy(x.lp->cond_graphs.front().exec);
+          x.lp->cond_graphs.erase(x.lp->cond_graphs.begin());
+        }
+        // the loop has just run with these addresses: recording changes nothing on the device
+        const int before = x.launches;
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+        b200_error* err = nullptr;
+        auto fail = [&](cudaError_t ce, const char* what) {
+          if (!err) err = make_error(B200_INTERNAL, std::string("recording a device-resident loop: ") + what + ": " + cudaGetErrorString(ce));
+        };
+        x.plain_launch = true;
+        set_programmatic_launch(false);
+        set_igemm_programmatic_launch(false);
+        cudaError_t ce = cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed);
+        if (ce != cudaSuccess) fail(ce, "begin capture");
+        else {
+          cudaStreamCaptureStatus status;
+          const cudaGraphNode_t* deps = nullptr;
+          size_t ndeps = 0;
+          cudaGraphConditionalHandle handle = 0;
+          cudaGraph_t body = nullptr;
+          ce = cudaStreamGetCaptureInfo(st, &status, nullptr, &graph, &deps, &ndeps);
+          if (ce != cudaSuccess) fail(ce, "capture info");
+          if (!err && (ce = cudaGraphConditionalHandleCreate(&handle, graph, 0, cudaGraphCondAssignDefault)) != cudaSuccess) fail(ce, "handle");
+          if (!err) err = run_plan(x, *s.sub[0]);
+          if (!err && (ce = launch_while_handle(handle, x.ptrs[s.pred], c->loop_guard, c->while_limit_s, true, c->error_flag, st)) != cudaSuccess)
+            fail(ce, "handle kernel");
+          if (!err && (ce = cudaStreamGetCaptureInfo(st, &status, nullptr, nullptr, &deps, &ndeps)) != cudaSuccess) fail(ce, "capture info");
+          if (!err) {
+            cudaGraphNodeParams np = {};
+            np.type = cudaGraphNodeTypeConditional;
+            np.conditional.handle = handle;
+            np.conditional.type = cudaGraphCondTypeWhile;
+            np.conditional.size = 1;
+            cudaGraphNode_t node = nullptr;
+            if ((ce = cudaGraphAddNode(&node, graph, deps, ndeps, &np)) != cudaSuccess) fail(ce, "while node");
+            else {
+              body = np.conditional.phGraph_out[0];
+              if ((ce = cudaStreamUpdateCaptureDependencies(st, &node, 1, cudaStreamSetCaptureDependencies)) != cudaSuccess) fail(ce, "dependencies");
+            }
+          }
+          cudaGraph_t ended = nullptr;
+          ce = cudaStreamEndCapture(st, &ended);
+          if (ce != cudaSuccess) fail(ce, "end capture");
+          graph = ended;                              // null when the capture was invalidated: nothing to destroy then
+          if (!err && body) {
+            if ((ce = cudaStreamBeginCaptureToGraph(st, body, nullptr, nullptr, 0, cudaStreamCaptureModeRelaxed)) != cudaSuccess) fail(ce, "begin body");
+            else {
+              err = run_plan(x, *s.sub[1]);
+              for (size_t k = 0; k < n && !err; k++) {
+                void *d = x.ptrs[s.state[k]], *src = x.ptrs[s.next[k]];
+                size_t b = x.lp->prog->slots[s.state[k]].type.bytes();
+                if (d != src && b && (ce = cudaMemcpyAsync(d, src, b, cudaMemcpyDeviceToDevice, st)) != cudaSuccess) fail(ce, "state copy");
+              }
+              if (!err) err = run_plan(x, *s.sub[0]);
+              if (!err && (ce = launch_while_handle(handle, x.ptrs[s.pred], c->loop_guard, c->while_limit_s, false, c->error_flag, st)) != cudaSuccess)
+                fail(ce, "handle kernel");
+              ce = cudaStreamEndCapture(st, nullptr);
+              if (ce != cudaSuccess) fail(ce, "end body");
+            }
+          }
+          if (!err && (ce = cudaGraphInstantiate(&exec, graph, 0)) != cudaSuccess) fail(ce, "instantiate");
+        }
+        x.plain_launch = false;
+        set_programmatic_launch(!c->sw.no_pdl);
+        set_igemm_programmatic_launch(!c->sw.no_pdl && !getenv("B200_NO_IGEMM_PDL"));
+        if (graph) cudaGraphDestroy(graph);
+        const int recorded = x.launches - before;
+        x.launches = before;
+        if (err) {
+          // a loop that cannot be recorded keeps the host path (the result of this execution is already complete)
+          logf(1, "%s", err->message.c_str());
+          b200_error_destroy(err);
+          cudaGetLastError();
+        } else {
+          x.lp->cond_graphs.push_back({&s, touched, exec, recorded});
+        }
+      }
+      return nullptr;
     }
     case Step::SCATTER: {
       void *operand = x.ptrs[s.args[0]], *out = x.ptrs[s.args[3]];
@@ -826,13 +953,97 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       return nullptr;
     }
     case Step::CASE: {
+      const int n = (int)s.sub.size();
+      // On the device when every branch only launches generated kernels and device copies: a switch node whose handle
+      // a one-thread kernel sets from the index (out of range selects the last branch, as on the host path;
+      // src/pjrt_plugin/ops/control_flow.cc:600-699). Recorded after the first execution through the host.
+      cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+      CUDA_TRY(cudaStreamIsCapturing(st, &capturing));
+      bool on_device = !c->sw.no_device_cf && !c->profiling && capturing == cudaStreamCaptureStatusNone && n >= 1;
+      for (int b = 0; b < n && on_device; b++)
+        for (const Step& bs : s.sub[b]->steps) on_device = on_device && (bs.kind == Step::KERNEL || bs.kind == Step::MEMCPY);
+      std::vector<void*> touched;
+      if (on_device) {
+        touched_addresses(x, s, touched);
+        for (auto& g : x.lp->cond_graphs)
+          if (g.step == &s && g.ptrs == touched) {
+            CUDA_TRY(cudaGraphLaunch(g.exec, st));
+            x.launches += g.launches;
+            return nullptr;
+          }
+      }
       int32_t index = 0;
       CUDA_TRY(cudaMemcpyAsync(c->pred_host, x.ptrs[s.pred], 4, cudaMemcpyDeviceToHost, st));
       CUDA_TRY(cudaStreamSynchronize(st));
+      c->host_syncs++;
       memcpy(&index, c->pred_host, 4);
-      const int n = (int)s.sub.size();
       if (index < 0 || index >= n) index = n - 1;
-      return run_plan(x, *s.sub[index]);
+      if (auto* e = run_plan(x, *s.sub[index])) return e;
+      if (on_device) {
+        if (x.lp->cond_graphs.size() >= 16) {
+          CUDA_TRY(cudaStreamSynchronize(st));
+          cudaGraphExecDestroy(x.lp->cond_graphs.front().exec);
+          x.lp->cond_graphs.erase(x.lp->cond_graphs.begin());
+        }
+        const int before = x.launches;
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+        b200_error* err = nullptr;
+        auto fail = [&](cudaError_t ce, const char* what) {
+          if (!err) err = make_error(B200_INTERNAL, std::string("recording a device-resident case: ") + what + ": " + cudaGetErrorString(ce));
+        };
+        x.plain_launch = true;
+        std::vector<cudaGraph_t> bodies;
+        cudaError_t ce = cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed);
+        if (ce != cudaSuccess) fail(ce, "begin capture");
+        else {
+          cudaStreamCaptureStatus status;
+          const cudaGraphNode_t* deps = nullptr;
+          size_t ndeps = 0;
+          cudaGraphConditionalHandle handle = 0;
+          ce = cudaStreamGetCaptureInfo(st, &status, nullptr, &graph, &deps, &ndeps);
+          if (ce != cudaSuccess) fail(ce, "capture info");
+          if (!err && (ce = cudaGraphConditionalHandleCreate(&handle, graph, 0, cudaGraphCondAssignDefault)) != cudaSuccess) fail(ce, "handle");
+          if (!err && (ce = launch_switch_handle(handle, x.ptrs[s.pred], n, st)) != cudaSuccess) fail(ce, "handle kernel");
+          if (!err && (ce = cudaStreamGetCaptureInfo(st, &status, nullptr, nullptr, &deps, &ndeps)) != cudaSuccess) fail(ce, "capture info");
+          if (!err) {
+            cudaGraphNodeParams np = {};
+            np.type = cudaGraphNodeTypeConditional;
+            np.conditional.handle = handle;
+            np.conditional.type = cudaGraphCondTypeSwitch;
+            np.conditional.size = (unsigned)n;
+            cudaGraphNode_t node = nullptr;
+            if ((ce = cudaGraphAddNode(&node, graph, deps, ndeps, &np)) != cudaSuccess) fail(ce, "switch node");
+            else {
+              for (int b = 0; b < n; b++) bodies.push_back(np.conditional.phGraph_out[b]);
+              if ((ce = cudaStreamUpdateCaptureDependencies(st, &node, 1, cudaStreamSetCaptureDependencies)) != cudaSuccess) fail(ce, "dependencies");
+            }
+          }
+          cudaGraph_t ended = nullptr;
+          ce = cudaStreamEndCapture(st, &ended);
+          if (ce != cudaSuccess) fail(ce, "end capture");
+          graph = ended;
+          for (int b = 0; b < n && !err && (int)bodies.size() == n; b++) {
+            if ((ce = cudaStreamBeginCaptureToGraph(st, bodies[b], nullptr, nullptr, 0, cudaStreamCaptureModeRelaxed)) != cudaSuccess) { fail(ce, "begin branch"); break; }
+            err = run_plan(x, *s.sub[b]);
+            ce = cudaStreamEndCapture(st, nullptr);
+            if (ce != cudaSuccess) fail(ce, "end branch");
+          }
+          if (!err && (ce = cudaGraphInstantiate(&exec, graph, 0)) != cudaSuccess) fail(ce, "instantiate");
+        }
+        x.plain_launch = false;
+        if (graph) cudaGraphDestroy(graph);
+        const int recorded = n > 0 ? (x.launches - before) / n : 0;
+        x.launches = before;
+        if (err) {
+          logf(1, "%s", err->message.c_str());
+          b200_error_destroy(err);
+          cudaGetLastError();
+        } else {
+          x.lp->cond_graphs.push_back({&s, touched, exec, recorded});
+        }
+      }
+      return nullptr;
     }
     default:
       return make_error(B200_UNIMPLEMENTED, "plan step kind not implemented: " + s.label);
@@ -1046,6 +1257,7 @@ b200_error* create_client(const b200_client_options* o, ncclComm_t given_comm, b
   CUDA_TRY(cudaMemPoolSetAttribute(c->pool, cudaMemPoolAttrReleaseThreshold, &thr));
   CUDA_TRY(cudaMallocHost((void**)&c->pred_host, 64));
   CUDA_TRY(cudaMalloc((void**)&c->error_flag, sizeof(int)));
+  CUDA_TRY(cudaMalloc((void**)&c->loop_guard, sizeof(unsigned long long)));
   CUDA_TRY(cudaMemset(c->error_flag, 0, sizeof(int)));
   CUDA_TRY(cudaMallocHost((void**)&c->status_block, 2 * sizeof(int) * b200_client::kStatusPairs));
   memset(c->status_block, 0, 2 * sizeof(int) * b200_client::kStatusPairs);
@@ -1059,6 +1271,8 @@ b200_error* create_client(const b200_client_options* o, ncclComm_t given_comm, b
   c->sw.no_loop_graphs = getenv("B200_NO_LOOP_GRAPHS") != nullptr;
   c->sw.no_tma_a = getenv("B200_NO_TMA_A") != nullptr;
   c->sw.no_pdl = getenv("B200_NO_PDL") != nullptr;
+  c->sw.no_device_cf = getenv("B200_NO_DEVICE_CONTROL_FLOW") != nullptr;
+  if (const char* lim = getenv("B200_WHILE_TIME_LIMIT_S")) c->while_limit_s = std::max(0.001, atof(lim));
   set_programmatic_launch(!c->sw.no_pdl);
   set_igemm_programmatic_launch(!c->sw.no_pdl && !getenv("B200_NO_IGEMM_PDL"));
   if (!driver().ok) return make_error(B200_FAILED_PRECONDITION, driver().error);
@@ -1097,6 +1311,7 @@ b200_error* b200_client_destroy(b200_client* c) {
     cudaEventDestroy(b.ev);
   }
   if (c->pred_host) cudaFreeHost(c->pred_host);
+  if (c->loop_guard) cudaFree(c->loop_guard);
   if (c->status_block) cudaFreeHost(c->status_block);
   if (c->error_flag) cudaFree(c->error_flag);
   if (c->coll) cudaStreamDestroy(c->coll);
@@ -2016,6 +2231,8 @@ b200_error* b200_client_debug_arm_wait_expiry(b200_client* c, int polls) {
   c->armed_wait_polls = polls;
   return nullptr;
 }
+
+long long b200_client_host_syncs(const b200_client* c) { return c ? c->host_syncs : 0; }
 
 b200_error* b200_client_probe_tf32_mma_rate(b200_client* c, double* tflops) {
   if (!c || !tflops) return make_error(B200_INVALID_ARGUMENT, "null argument");

@@ -469,6 +469,45 @@ def test_dynamic_while_and_zero_trip(client):
         check(client, text, [np.float32(start), np.float32(limit)])
 
 
+def test_data_dependent_loop_and_case_run_on_the_device(client):
+    """A `while` with a data-dependent trip count and a `case` run as conditional CUDA-graph nodes from their second
+    execution on: the host reads no predicate back (the client's counter of stream synchronisations inside executions
+    stands still), trip counts and branches still follow the data (zero trips, out-of-range index -> last branch)."""
+    b = Builder()
+    x, lim = b.arg((64,), "f32"), b.arg((), "f32")
+    def cond(s, v, l): return s.compare(s.reduce_max(v, (0,)), l, "LT")
+    def body(s, v, l): return [s.add(s.mul(v, s.full((64,), 1.5, "f32")), s.full((64,), 0.25, "f32")), l]
+    text = b.module(b.while_([x, lim], cond, body))
+    exe = client.compile(text)
+    v0 = np.linspace(0.1, 1.0, 64).astype(np.float32)
+    settled = None
+    for limit in [50.0, 400.0, 0.5, 3.0, 1e4]:                      # 0.5: zero trips
+        args = [v0, np.float32(limit)]
+        before = client.host_syncs()
+        got = [o.to_numpy() for o in exe.execute([client.buffer_from_host(a) for a in args])]
+        want = interp.run_text(text, args)
+        np.testing.assert_allclose(got[0], want[0], rtol=1e-5)
+        if settled is not None:
+            assert client.host_syncs() == before, "a recorded loop must not read its predicate back"
+        if limit == 50.0:
+            assert client.host_syncs() > before                     # the first execution goes through the host
+            settled = True
+    b = Builder()
+    i, u = b.arg((), "i32"), b.arg((6, 5), "f32")
+    idx = b.max(i, b.const(-7, "i32"))                              # computed on the device: the index lives in the arena
+    outs = b.case(idx, [lambda s: [s.add(u, u)], lambda s: [s.mul(u, u)], lambda s: [s.tanh(u)]], [((6, 5), "f32")])
+    text = b.module([b.exp(outs[0])])
+    exe = client.compile(text)
+    ub = f32(6, 5)
+    for n, sel in enumerate([1, 0, 2, 9, -3, 1]):
+        before = client.host_syncs()
+        got = exe.execute([client.buffer_from_host(np.int32(sel)), client.buffer_from_host(ub)])[0].to_numpy()
+        want = interp.run_text(text, [np.int32(sel), ub])[0]
+        np.testing.assert_allclose(got, want, rtol=1e-5)
+        if n > 0:
+            assert client.host_syncs() == before, "a recorded case must not read its index back"
+
+
 def test_scan_with_dynamic_slices(client):
     """A scan body: read xs[t] with dynamic_slice, update a carry, write ys[t]
     with dynamic_update_slice (the shape of lax.scan lowerings)."""
