@@ -6,7 +6,7 @@
 //                       operand tiles with TMA tiled copies (cp.async.bulk.tensor, this GPU's memory only, plain
 //                       single-CTA form) into a ring of 128-byte-swizzled shared-memory stages; warp 1 issues
 //                       tcgen05.mma.kind::f16 from shared-memory descriptors into one of two accumulators in tensor
-//                       memory; warps 2-5 read a finished accumulator back (tcgen05.ld), round and store it while
+//                       memory; warps 2-9 read a finished accumulator back (tcgen05.ld), round and store it while
 //                       the next tile's products already run into the other accumulator.
 //   gemv16_nc_kernel /  M <= 8 (a decode step): the weights are read exactly once with 128-bit loads and the rate is
 //   gemv16_kc_kernel    set by HBM, so no tensor cores. nc: n contiguous in B; kc: k contiguous in B.
@@ -49,7 +49,7 @@ cudaError_t launch_k(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, c
 }
 
 
-constexpr int G_BM = 128, G_BK = 64, G_THREADS = 192;
+constexpr int G_BM = 128, G_BK = 64, G_THREADS = 320;   // TMA warp, MMA warp, eight read-back warps
 
 template <int BN>
 struct G16Cfg {
@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm16_tma_kernel(const __grid_c
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&acc_full[b]), 1);
-      mbar_init(smem_u32(&acc_empty[b]), 4);
+      mbar_init(smem_u32(&acc_empty[b]), 8);
     }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -294,8 +294,10 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm16_tma_kernel(const __grid_c
       __syncwarp();
     }
   } else {
-    // ------------------------------ accumulator read-back (warps 2-5: lane quadrant warp % 4) -----------------
-    const int quad = warp & 3;
+    // ------------------------------ accumulator read-back (warps 2-9: lane quadrant warp % 4, two warps per quadrant,
+    // each with one half of the tile's columns: with four warps the read-back of a 128 x 256 tile took longer than the
+    // 12 k-tiles of a K = 768 product and set that product's time) ------------------------------------------------
+    const int quad = warp & 3, half = (warp - 2) >> 2;
     uint32_t tl = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++tl) {
@@ -313,10 +315,10 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm16_tma_kernel(const __grid_c
       const long long row = split ? ((long long)sp * p.G + g) * p.M + m : (long long)g * p.M + m;
       const int kind = split ? 2 : p.c_kind;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
         uint32_t v[32];
         tmem_load32(tmem + ((uint32_t)(32 * quad) << 16) + ab * BN + (uint32_t)c0, v);
-        if (c0 + 32 == BN) {
+        if (c0 + 32 == (half + 1) * (BN / 2)) {
           // the accumulator is in registers: hand it back to the MMA warp before storing
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
