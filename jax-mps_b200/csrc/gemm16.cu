@@ -315,10 +315,19 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm16_tma_kernel(const __grid_c
       const long long row = split ? ((long long)sp * p.G + g) * p.M + m : (long long)g * p.M + m;
       const int kind = split ? 2 : p.c_kind;
 #pragma unroll 1
-      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
+      // rows of C that start off 16-byte lines (N not a multiple of 8) go out in narrow stores: there the second warp
+      // of a quadrant only adds pressure, the first one takes every column
+      const bool shared_cols = split || (p.N & 7) == 0;
+      const int c_begin = shared_cols ? half * (BN / 2) : 0, c_end = shared_cols ? (half + 1) * (BN / 2) : (half == 0 ? BN : 0);
+      if (c_begin >= c_end) {
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&acc_empty[ab]));
+      }
+      for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         uint32_t v[32];
         tmem_load32(tmem + ((uint32_t)(32 * quad) << 16) + ab * BN + (uint32_t)c0, v);
-        if (c0 + 32 == (half + 1) * (BN / 2)) {
+        if (c0 + 32 == c_end) {
           // the accumulator is in registers: hand it back to the MMA warp before storing
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
