@@ -624,6 +624,52 @@ class Builder:
                                 "unique_indices": "false"}, regions=[reg])
         return y
 
+    @staticmethod
+    def _window_props(rank, window, strides, padding, base_dilations=None, window_dilations=None):
+        strides = tuple(strides or (1,) * rank)
+        padding = tuple(tuple(p) for p in (padding or ((0, 0),) * rank))
+        props = {"window_dimensions": "array<i64: " + ", ".join(str(int(v)) for v in window) + ">",
+                 "window_strides": "array<i64: " + ", ".join(str(int(v)) for v in strides) + ">",
+                 "padding": "dense<[" + ", ".join(f"[{int(a)}, {int(b)}]" for a, b in padding) + f"]> : tensor<{rank}x2xi64>"}
+        if base_dilations is not None:
+            props["base_dilations"] = "array<i64: " + ", ".join(str(int(v)) for v in base_dilations) + ">"
+        if window_dilations is not None:
+            props["window_dilations"] = "array<i64: " + ", ".join(str(int(v)) for v in window_dilations) + ">"
+        return props, strides, padding
+
+    def reduce_window(self, x: Val, init, op: str, window, strides=None, padding=None, base_dilations=None,
+                      window_dilations=None) -> Val:
+        """stablehlo.reduce_window with the body `op` (add, maximum, minimum, multiply, and, or): what lax.reduce_window,
+        pooling and cumulative sums lower to. `init` is a scalar Val or a Python number. No gradient."""
+        rank = x.ndim
+        props, strides, padding = self._window_props(rank, window, strides, padding, base_dilations, window_dilations)
+        bd = tuple(base_dilations or (1,) * rank)
+        wd = tuple(window_dilations or (1,) * rank)
+        shape = []
+        for d in range(rank):
+            padded = (x.shape[d] - 1) * bd[d] + 1 + padding[d][0] + padding[d][1] if x.shape[d] else 0
+            win = (window[d] - 1) * wd[d] + 1
+            shape.append(0 if padded < win else (padded - win) // strides[d] + 1)
+        if not isinstance(init, Val):
+            init = self.const(init, x.dtype)
+        reg = self.region([((), x.dtype)] * 2, lambda s, a, b: s._binary(op, a, b))
+        (y,) = self.emit("stablehlo.reduce_window", [x, init], [(tuple(shape), x.dtype)], props=props, regions=[reg])
+        return y
+
+    def select_and_scatter(self, operand: Val, source: Val, init, window, strides=None, padding=None,
+                           select: str = "GE", scatter: str = "add") -> Val:
+        """stablehlo.select_and_scatter (the gradient of max / min pooling): per window the element chosen by
+        compare(a, b, `select`) receives the window's `source` value, combined with `scatter`. No gradient."""
+        rank = operand.ndim
+        props, _, _ = self._window_props(rank, window, strides, padding)
+        if not isinstance(init, Val):
+            init = self.const(init, operand.dtype)
+        sel = self.region([((), operand.dtype)] * 2, lambda s, a, b: s.compare(a, b, select))
+        sc = self.region([((), operand.dtype)] * 2, lambda s, a, b: s._binary(scatter, a, b))
+        (y,) = self.emit("stablehlo.select_and_scatter", [operand, source, init], [(operand.shape, operand.dtype)],
+                         props=props, regions=[sel, sc])
+        return y
+
     def take_along_last(self, x: Val, idx: Val) -> Val:
         """x[i, idx[i]] for 2-D x and 1-D idx (jnp.take_along_axis on the last
         axis, lowered with operand batching dims)."""

@@ -818,7 +818,7 @@ struct SkinnyWeightHoist {
 // ---------------------------------------------------------------------------
 // op classification
 // ---------------------------------------------------------------------------
-enum class Cat { ELEMENTWISE, DUP, INDEXING, REDUCE, DOT, CONV, SCATTER, WHILE, CASE, ALL_REDUCE, ALL_GATHER, RETURN, TOKEN, PARTITION_ID, UNSUPPORTED };
+enum class Cat { ELEMENTWISE, DUP, INDEXING, REDUCE, DOT, CONV, SCATTER, WINDOW, WHILE, CASE, ALL_REDUCE, ALL_GATHER, RETURN, TOKEN, PARTITION_ID, UNSUPPORTED };
 
 Cat categorize(Op* op) {
   const std::string sh = op->short_name();
@@ -834,6 +834,7 @@ Cat categorize(Op* op) {
   if (sh == "dot_general") return Cat::DOT;
   if (sh == "convolution") return Cat::CONV;
   if (sh == "scatter") return Cat::SCATTER;
+  if (sh == "reduce_window" || sh == "select_and_scatter") return Cat::WINDOW;
   if (sh == "while") return Cat::WHILE;
   if (sh == "case") return Cat::CASE;
   if (sh == "all_reduce") return Cat::ALL_REDUCE;
@@ -847,7 +848,7 @@ void collect_unsupported(Block* b, std::set<std::string>& out, bool in_combiner)
   for (auto& op : b->ops) {
     Cat c = categorize(op.get());
     if (c == Cat::UNSUPPORTED) out.insert(op->name);
-    bool comb = c == Cat::REDUCE || c == Cat::SCATTER || c == Cat::ALL_REDUCE || c == Cat::ALL_GATHER;
+    bool comb = c == Cat::REDUCE || c == Cat::SCATTER || c == Cat::WINDOW || c == Cat::ALL_REDUCE || c == Cat::ALL_GATHER;
     for (auto& r : op->regions) collect_unsupported(r.get(), out, comb);
   }
 }
@@ -1325,6 +1326,223 @@ struct Planner {
     L.block[0] = kThreads; L.block[1] = L.block[2] = 1;
     L.outs = outs;
     L.ins = em.inputs;
+    return L;
+  }
+
+  // ---- window operations (src/pjrt_plugin/ops/reduction.cc:165-626 of the reference) ---------------------------------
+  // Geometry of a window operation: per dimension the window size, stride, padding in front, base (input) dilation and
+  // window dilation. `padding` is dense<...> : tensor<R x 2 x i64> (possibly a splat), the rest array<i64: ...>.
+  struct WindowGeom { std::vector<int64_t> win, stride, pad_lo, bdil, wdil; };
+  WindowGeom window_geometry(Op* op, int rank) {
+    WindowGeom g;
+    auto list = [&](const char* name, int64_t dflt) {
+      std::vector<int64_t> v = op->has(name) ? attr_i64s(op->attr(name)) : std::vector<int64_t>();
+      if (v.empty()) v.assign(rank, dflt);
+      if ((int)v.size() != rank) throw CompileError(op->name + ": " + name + " must have one entry per dimension");
+      return v;
+    };
+    g.win = list("window_dimensions", 1);
+    g.stride = list("window_strides", 1);
+    g.bdil = list("base_dilations", 1);
+    g.wdil = list("window_dilations", 1);
+    g.pad_lo.assign(rank, 0);
+    if (op->has("padding")) {
+      DenseValue d = attr_dense(op->attr("padding"));
+      if (d.type.numel() != 2 * rank || dt_size(d.type.dt) != 8) throw CompileError(op->name + ": padding must be a [rank, 2] i64 tensor");
+      for (int k = 0; k < rank; k++) memcpy(&g.pad_lo[k], d.data.data() + 16 * k, 8);
+    }
+    for (int k = 0; k < rank; k++)
+      if (g.win[k] < 1 || g.stride[k] < 1 || g.bdil[k] < 1 || g.wdil[k] < 1) throw CompileError(op->name + ": window sizes, strides and dilations must be positive");
+    return g;
+  }
+
+  // the value of element `at` of input `v` of a hand-assembled kernel (storage type -> compute type)
+  static std::string load_expr(Value* v, const std::string& name, const std::string& at) {
+    std::string e = name + "[" + at + "]";
+    if (v->type.dt == DT::BF16) return "bf16_to_f(" + e + ")";
+    if (v->type.dt == DT::F16) return "f16_to_f(" + e + ")";
+    if (v->type.dt == DT::PRED) return "(" + e + " != 0)";
+    return e;
+  }
+
+  // stablehlo.reduce_window (pooling, cumulative sums): one thread per output element walks its window; positions
+  // in the padding, or between the elements of a dilated input, contribute the init value. The body may be any
+  // reduction computation (it is emitted as it stands), with several inputs reduced together.
+  Launch gen_reduce_window(Op* op, BlockState& st) {
+    const size_t n = op->operands.size() / 2;
+    if (n < 1 || op->operands.size() != 2 * n || op->results.size() != n || op->regions.size() != 1)
+      throw CompileError("stablehlo.reduce_window: malformed operands");
+    const TensorType& it = op->operands[0]->type;
+    const TensorType& ot = op->results[0]->type;
+    const int R = it.rank();
+    if (ot.rank() != R) throw CompileError("stablehlo.reduce_window: result rank differs from the input's");
+    WindowGeom g = window_geometry(op, R);
+    std::vector<Value*> ins;
+    for (size_t k = 0; k < 2 * n; k++) {
+      if (!slot_of.count(op->operands[k])) throw CompileError("internal: operand of reduce_window has no storage");
+      ins.push_back(op->operands[k]);
+    }
+    std::vector<Value*> outs(op->results.begin(), op->results.end());
+    Emitter em;
+    em.is_internal = [](Op*) { return false; };
+    em.idx_t = idx_type_for(ins, ot.numel() + kThreads);
+    em.indent_ = 2;
+    Ctx root;
+    root.shape = ot.dims;
+    root.lin = "lin";
+    em.ensure_idx(root);
+    const std::string I = em.idx_t;
+    std::ostringstream src;
+    src << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(" << signature(outs, ins) << ") {\n";
+    src << "  const " << I << " lin = (" << I << ")blockIdx.x * " << kThreads << " + threadIdx.x;\n";
+    src << "  if (lin >= (" << I << ")" << ot.numel() << "LL) return;\n";
+    src << em.str();
+    for (size_t k = 0; k < n; k++)
+      src << "  const " << c_type(ins[n + k]->type.dt) << " init" << k << " = " << load_expr(ins[n + k], "in" + std::to_string(n + k), "0") << ";\n"
+          << "  " << c_type(outs[k]->type.dt) << " acc" << k << " = init" << k << ";\n";
+    std::vector<int64_t> istr(R, 1);
+    for (int d = R - 2; d >= 0; d--) istr[d] = istr[d + 1] * it.dims[d + 1];
+    for (int d = 0; d < R; d++) {
+      const std::string w = "w" + std::to_string(d);
+      src << "  for (int " << w << " = 0; " << w << " < " << g.win[d] << "; ++" << w << ") {\n";
+      // position in the dilated, padded input, then the input element it falls on (if any)
+      src << "  const long long p" << d << " = (long long)" << (root.idx[d] == "0" ? std::string("0") : root.idx[d]) << " * " << g.stride[d] << " + " << w << " * "
+          << g.wdil[d] << " - " << g.pad_lo[d] << ";\n";
+      src << "  const bool ok" << d << " = " << (d ? "ok" + std::to_string(d - 1) + " && " : "") << "p" << d << " >= 0 && p" << d << " % " << g.bdil[d]
+          << " == 0 && p" << d << " / " << g.bdil[d] << " < " << it.dims[d] << ";\n";
+    }
+    {
+      std::string at;
+      for (int d = 0; d < R; d++) at += (d ? " + " : "") + std::string("(p") + std::to_string(d) + " / " + std::to_string(g.bdil[d]) + ") * " + std::to_string(istr[d]) + "LL";
+      if (R == 0) at = "0";
+      const std::string okl = R ? "ok" + std::to_string(R - 1) : "true";
+      Emitter be;
+      be.idx_t = I;
+      be.name_prefix = "b";
+      be.indent_ = 2;
+      be.round_small_floats = true;
+      std::vector<std::string> args;
+      for (size_t k = 0; k < n; k++) args.push_back("acc" + std::to_string(k));
+      for (size_t k = 0; k < n; k++) {
+        be.line(std::string("const ") + c_type(ins[k]->type.dt) + " val" + std::to_string(k) + " = " + okl + " ? " +
+                load_expr(ins[k], "in" + std::to_string(k), "(" + I + ")(" + okl + " ? " + at + " : 0)") + " : init" + std::to_string(k) + ";");
+        args.push_back("val" + std::to_string(k));
+      }
+      auto res = be.emit_scalar_region(op->regions[0].get(), args);
+      for (size_t k = 0; k < n; k++) be.line("acc" + std::to_string(k) + " = " + res[k] + ";");
+      src << be.str();
+    }
+    for (int d = 0; d < R; d++) src << "  }\n";
+    for (size_t k = 0; k < n; k++) src << "  out" << k << "[lin] = " << store_expr(outs[k]->type.dt, "acc" + std::to_string(k)) << ";\n";
+    src << "}\n";
+    Launch L;
+    L.kernel = add_kernel(src.str(), "window");
+    L.grid[0] = (unsigned)std::max<int64_t>(1, (ot.numel() + kThreads - 1) / kThreads); L.grid[1] = L.grid[2] = 1;
+    L.block[0] = kThreads; L.block[1] = L.block[2] = 1;
+    L.outs = outs;
+    L.ins = ins;
+    return L;
+  }
+
+  // stablehlo.select_and_scatter (the gradient of max / min pooling): in gather form, so that it is deterministic. One
+  // thread per operand element visits the windows that cover it in row-major order of the windows; for each it scans
+  // the window's in-bounds elements in row-major order with the select computation (the current choice stays while
+  // select(current, candidate) holds, so ties go to the first element for GE / LE and to the last for GT / LT; padding is
+  // never selected, as in the reference) and, when the chosen element is its own, folds the window's source value into its
+  // result with the scatter computation, starting from the init value.
+  Launch gen_select_and_scatter(Op* op, BlockState& st) {
+    if (op->operands.size() != 3 || op->results.size() != 1 || op->regions.size() != 2)
+      throw CompileError("stablehlo.select_and_scatter: malformed operands");
+    Value *operand = op->operands[0], *source = op->operands[1], *init = op->operands[2], *out = op->results[0];
+    const TensorType& ot = operand->type;
+    const TensorType& stt = source->type;
+    const int R = ot.rank();
+    if (stt.rank() != R) throw CompileError("stablehlo.select_and_scatter: source rank differs from the operand's");
+    WindowGeom g = window_geometry(op, R);
+    for (int d = 0; d < R; d++)
+      if (g.bdil[d] != 1 || g.wdil[d] != 1) throw CompileError("stablehlo.select_and_scatter has no dilations");
+    for (Value* v : {operand, source, init})
+      if (!slot_of.count(v)) throw CompileError("internal: operand of select_and_scatter has no storage");
+    std::vector<Value*> ins = {operand, source, init}, outs = {out};
+    Emitter em;
+    em.is_internal = [](Op*) { return false; };
+    em.idx_t = idx_type_for(ins, ot.numel() + kThreads);
+    em.indent_ = 2;
+    Ctx root;
+    root.shape = ot.dims;
+    root.lin = "lin";
+    em.ensure_idx(root);
+    const std::string I = em.idx_t;
+    std::vector<int64_t> ostr(R, 1), sstr(R, 1);
+    for (int d = R - 2; d >= 0; d--) { ostr[d] = ostr[d + 1] * ot.dims[d + 1]; sstr[d] = sstr[d + 1] * stt.dims[d + 1]; }
+    const char* ct = c_type(ot.dt);
+    std::ostringstream src;
+    src << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(" << signature(outs, ins) << ") {\n";
+    src << "  const " << I << " lin = (" << I << ")blockIdx.x * " << kThreads << " + threadIdx.x;\n";
+    src << "  if (lin >= (" << I << ")" << ot.numel() << "LL) return;\n";
+    src << em.str();
+    src << "  " << ct << " acc = " << load_expr(init, "in2", "0") << ";\n";
+    // windows that cover this element: s * stride <= i + pad < s * stride + win
+    for (int d = 0; d < R; d++) {
+      const std::string i = root.idx[d] == "0" ? "0" : root.idx[d];
+      src << "  const long long q" << d << " = (long long)" << i << " + " << g.pad_lo[d] << ";\n";
+      src << "  const long long slo" << d << " = q" << d << " - " << (g.win[d] - 1) << " <= 0 ? 0 : (q" << d << " - " << (g.win[d] - 1) << " + " << (g.stride[d] - 1)
+          << ") / " << g.stride[d] << ";\n";
+      src << "  const long long shi" << d << " = q" << d << " < 0 ? -1 : (q" << d << " / " << g.stride[d] << " < " << stt.dims[d] << " ? q" << d << " / " << g.stride[d]
+          << " : " << (stt.dims[d] - 1) << ");\n";
+    }
+    for (int d = 0; d < R; d++) src << "  for (long long s" << d << " = slo" << d << "; s" << d << " <= shi" << d << "; ++s" << d << ") {\n";
+    src << "  bool have = false;\n  " << ct << " cur = acc;\n  long long cur_at = -1;\n";
+    for (int d = 0; d < R; d++) {
+      src << "  for (int w" << d << " = 0; w" << d << " < " << g.win[d] << "; ++w" << d << ") {\n";
+      src << "  const long long p" << d << " = s" << d << " * " << g.stride[d] << " + w" << d << " - " << g.pad_lo[d] << ";\n";
+      src << "  const bool ok" << d << " = " << (d ? "ok" + std::to_string(d - 1) + " && " : "") << "p" << d << " >= 0 && p" << d << " < " << ot.dims[d] << ";\n";
+    }
+    {
+      std::string at;
+      for (int d = 0; d < R; d++) at += (d ? " + " : "") + std::string("p") + std::to_string(d) + " * " + std::to_string(ostr[d]) + "LL";
+      if (R == 0) at = "0";
+      const std::string okl = R ? "ok" + std::to_string(R - 1) : "true";
+      Emitter se;
+      se.idx_t = I;
+      se.name_prefix = "s";
+      se.indent_ = 2;
+      se.line("if (" + okl + ") {");
+      se.line("const long long at = " + at + ";");
+      se.line(std::string("const ") + ct + " cand = " + load_expr(operand, "in0", "at") + ";");
+      se.line("bool keep = false;");
+      se.line("if (have) {");
+      auto res = se.emit_scalar_region(op->regions[0].get(), {"cur", "cand"});
+      se.line("keep = " + res[0] + ";");
+      se.line("}");
+      se.line("if (!keep) { cur = cand; cur_at = at; have = true; }");
+      se.line("}");
+      src << se.str();
+    }
+    for (int d = 0; d < R; d++) src << "  }\n";
+    {
+      std::string sat;
+      for (int d = 0; d < R; d++) sat += (d ? " + " : "") + std::string("s") + std::to_string(d) + " * " + std::to_string(sstr[d]) + "LL";
+      if (R == 0) sat = "0";
+      Emitter ce;
+      ce.idx_t = I;
+      ce.name_prefix = "c";
+      ce.indent_ = 2;
+      ce.line("if (have && cur_at == (long long)lin) {");
+      ce.line(std::string("const ") + c_type(source->type.dt) + " sv = " + load_expr(source, "in1", sat) + ";");
+      auto res = ce.emit_scalar_region(op->regions[1].get(), {"acc", "sv"});
+      ce.line("acc = " + res[0] + ";");
+      ce.line("}");
+      src << ce.str();
+    }
+    for (int d = 0; d < R; d++) src << "  }\n";
+    src << "  out0[lin] = " << store_expr(out->type.dt, "acc") << ";\n}\n";
+    Launch L;
+    L.kernel = add_kernel(src.str(), "window");
+    L.grid[0] = (unsigned)std::max<int64_t>(1, (ot.numel() + kThreads - 1) / kThreads); L.grid[1] = L.grid[2] = 1;
+    L.block[0] = kThreads; L.block[1] = L.block[2] = 1;
+    L.outs = outs;
+    L.ins = ins;
     return L;
   }
 
@@ -3332,6 +3550,11 @@ struct Planner {
         }
         case Cat::SCATTER: {
           plan.steps.push_back(lower_scatter(op, st));
+          break;
+        }
+        case Cat::WINDOW: {
+          Launch L = op->short_name() == "reduce_window" ? gen_reduce_window(op, st) : gen_select_and_scatter(op, st);
+          add_launch(plan, L, op->short_name(), st);
           break;
         }
         case Cat::TOKEN: {

@@ -577,6 +577,90 @@ class Interp:
             full[wd] += oi[offset_dims[k]]
         return [operand[tuple(full)].reshape(t.shape)]
 
+    @staticmethod
+    def _window_geometry(op, rank):
+        def lst(name, dflt):
+            v = attr_i64s(op.attrs[name]) if name in op.attrs else []
+            return list(v) if len(v) else [dflt] * rank
+        win, stride = lst("window_dimensions", 1), lst("window_strides", 1)
+        bdil, wdil = lst("base_dilations", 1), lst("window_dilations", 1)
+        pad = [(0, 0)] * rank
+        if "padding" in op.attrs:
+            dv = mt.dense_array(op.attrs["padding"])
+            pad = [tuple(int(v) for v in row) for row in np.asarray(dv).reshape(rank, 2)]
+        return win, stride, pad, bdil, wdil
+
+    def op_reduce_window(self, op, x, env):
+        """stablehlo.reduce_window: the input is dilated, then padded, both with the init value
+        (src/pjrt_plugin/ops/reduction.cc:165-458 handles the pooling and cumulative forms); every window offset is
+        folded into the accumulator with the body, offsets in row-major order."""
+        n = len(x) // 2
+        ins, inits = x[:n], x[n:]
+        rank = ins[0].ndim
+        win, stride, pad, bdil, wdil = self._window_geometry(op, rank)
+        oshape = op.result_types[0].shape
+        padded = []
+        for a, i in zip(ins, inits):
+            dil = tuple((a.shape[d] - 1) * bdil[d] + 1 if a.shape[d] else 0 for d in range(rank))
+            full = np.full(tuple(max(0, dil[d] + pad[d][0] + pad[d][1]) for d in range(rank)), i, dtype=a.dtype)
+            # negative padding crops: place the dilated input through index arithmetic
+            src = np.full(dil, i, dtype=a.dtype)
+            src[tuple(slice(None, None, bdil[d]) for d in range(rank))] = a
+            sl_dst, sl_src = [], []
+            for d in range(rank):
+                lo = pad[d][0]
+                s0, d0 = max(0, -lo), max(0, lo)
+                ln = min(dil[d] - s0, full.shape[d] - d0)
+                sl_src.append(slice(s0, s0 + max(ln, 0)))
+                sl_dst.append(slice(d0, d0 + max(ln, 0)))
+            full[tuple(sl_dst)] = src[tuple(sl_src)]
+            padded.append(full)
+        acc = [np.broadcast_to(np.asarray(i, dtype=a.dtype), oshape).copy() for a, i in zip(ins, inits)]
+        for off in np.ndindex(*win):
+            sl = tuple(slice(off[d] * wdil[d], off[d] * wdil[d] + (oshape[d] - 1) * stride[d] + 1, stride[d]) if oshape[d] else slice(0, 0)
+                       for d in range(rank))
+            vals = [p[sl] for p in padded]
+            self._vector += 1
+            outs = self.region(op.regions[0], env, acc + vals)
+            self._vector -= 1
+            acc = [self.cast(o, t.dtype) for o, t in zip(outs, op.result_types)]
+        return acc
+
+    def op_select_and_scatter(self, op, x, env):
+        """stablehlo.select_and_scatter: per window the in-bounds element chosen by the select body (scanned in row-major
+        order, the current choice stays while select(current, candidate) holds; padding is never chosen:
+        src/pjrt_plugin/ops/reduction.cc:531-549) receives the window's source value through the scatter body."""
+        operand, source, init = x
+        rank = operand.ndim
+        win, stride, pad, _, _ = self._window_geometry(op, rank)
+        sshape = source.shape
+        have = np.zeros(sshape, dtype=bool)
+        cur = np.zeros(sshape, dtype=operand.dtype)
+        cur_at = np.full(sshape + (rank,), -1, dtype=np.int64)
+        grids = np.meshgrid(*[np.arange(n) for n in sshape], indexing="ij") if rank else []
+        for off in np.ndindex(*win):
+            pos = [grids[d] * stride[d] + off[d] - pad[d][0] for d in range(rank)]
+            ok = np.ones(sshape, dtype=bool)
+            for d in range(rank):
+                ok &= (pos[d] >= 0) & (pos[d] < operand.shape[d])
+            cand = operand[tuple(np.clip(pos[d], 0, max(operand.shape[d] - 1, 0)) for d in range(rank))] if rank else operand
+            self._vector += 1
+            keep = np.asarray(self.region(op.regions[0], env, [cur, cand])[0]).astype(bool)
+            self._vector -= 1
+            take = ok & (~have | ~keep)
+            cur = np.where(take, cand, cur)
+            for d in range(rank):
+                cur_at[..., d] = np.where(take, pos[d], cur_at[..., d])
+            have |= take
+        out = np.broadcast_to(np.asarray(init, dtype=operand.dtype), operand.shape).copy()
+        for sidx in np.ndindex(*sshape):                       # windows in row-major order
+            if not have[sidx]:
+                continue
+            at = tuple(int(v) for v in cur_at[sidx])
+            r = self.region(op.regions[1], env, [out[at], source[sidx]])[0]
+            out[at] = self.cast(np.asarray(r), op.result_types[0].dtype)
+        return [out]
+
     def op_scatter(self, op, x, env):
         """stablehlo.scatter, one operand. Out-of-bounds windows are skipped.
         Body classification as in gather_scatter.cc:13-53."""
