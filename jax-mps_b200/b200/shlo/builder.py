@@ -670,6 +670,22 @@ class Builder:
                          props=props, regions=[sel, sc])
         return y
 
+    def scatter(self, operand: Val, indices: Val, updates: Val, op: str = "add", *, update_window_dims=(),
+                inserted_window_dims=(), scatter_dims_to_operand_dims=(), index_vector_dim=None, input_batching_dims=(),
+                scatter_indices_batching_dims=()) -> Val:
+        """stablehlo.scatter with explicit dimension numbers (`op` in add, multiply, minimum, maximum, or "set"); no gradient."""
+        ivd = indices.ndim if index_vector_dim is None else index_vector_dim
+        sdn = (f"#stablehlo.scatter<update_window_dims = {list(update_window_dims)}, inserted_window_dims = {list(inserted_window_dims)}, "
+               + (f"input_batching_dims = {list(input_batching_dims)}, scatter_indices_batching_dims = {list(scatter_indices_batching_dims)}, "
+                  if input_batching_dims else "")
+               + f"scatter_dims_to_operand_dims = {list(scatter_dims_to_operand_dims)}, index_vector_dim = {ivd}>")
+        body = (lambda s, a, u: u) if op == "set" else (lambda s, a, u: s._binary(op, a, u))
+        reg = self.region([((), operand.dtype)] * 2, body)
+        (y,) = self.emit("stablehlo.scatter", [operand, indices, updates], [(operand.shape, operand.dtype)],
+                         props={"scatter_dimension_numbers": sdn, "indices_are_sorted": "false",
+                                "unique_indices": "false"}, regions=[reg])
+        return y
+
     def take_along_last(self, x: Val, idx: Val) -> Val:
         """x[i, idx[i]] for 2-D x and 1-D idx (jnp.take_along_axis on the last
         axis, lowered with operand batching dims)."""

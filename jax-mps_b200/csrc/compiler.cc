@@ -2337,10 +2337,97 @@ struct Planner {
     return s;
   }
 
+  // stablehlo.scatter in its general form (windows of any shape, point updates, batching dimensions;
+  // src/pjrt_plugin/ops/gather_scatter.cc:296-699). A generated kernel turns every update element into the linear index of
+  // the operand element it lands on (or a sentinel when its window does not fit, which drops the whole window), then
+  // the pairs (destination, update element) are sorted by destination with the stable radix sort and every run is
+  // applied in update order: deterministic like the row form.
+  Step lower_scatter_general(Op* op, int kind, Plan& plan, BlockState& st) {
+    Value *operand = op->operands[0], *indices = op->operands[1], *updates = op->operands[2], *out = op->results[0];
+    auto f = attr_struct(op->attr("scatter_dimension_numbers"));
+    const auto uwd = f["update_window_dims"], iwd = f["inserted_window_dims"], sdo = f["scatter_dims_to_operand_dims"];
+    const auto ibd = f["input_batching_dims"], sbd = f["scatter_indices_batching_dims"];
+    const int IR = indices->type.rank(), R = operand->type.rank(), UR = updates->type.rank();
+    const int ivd = f.count("index_vector_dim") && !f["index_vector_dim"].empty() ? (int)f["index_vector_dim"][0] : IR;
+    const int64_t U = updates->type.numel(), numel = operand->type.numel();
+    if (U >= (1LL << 31) - 1024 || numel >= (1LL << 31) - 1) throw CompileError("stablehlo.scatter: more than 2^31 elements");
+    auto has = [](const std::vector<int64_t>& v, int64_t x) { return std::find(v.begin(), v.end(), x) != v.end(); };
+    std::vector<int> scatter_dims, window_dims, idx_batch_dims;
+    for (int d = 0; d < UR; d++) if (!has(uwd, d)) scatter_dims.push_back(d);
+    for (int d = 0; d < R; d++) if (!has(iwd, d) && !has(ibd, d)) window_dims.push_back(d);
+    for (int d = 0; d < IR; d++) if (d != ivd) idx_batch_dims.push_back(d);
+    if (window_dims.size() != uwd.size() || scatter_dims.size() != idx_batch_dims.size() || ibd.size() != sbd.size())
+      throw CompileError("stablehlo.scatter: inconsistent scatter_dimension_numbers " + op->attr("scatter_dimension_numbers"));
+    const int64_t ncomp = ivd < IR ? indices->type.dims[ivd] : 1;
+    if ((int64_t)sdo.size() != ncomp) throw CompileError("stablehlo.scatter: scatter_dims_to_operand_dims does not match the index vector");
+    TensorType t;
+    t.dt = DT::I32;
+    t.dims = {scatter_elems_scratch_ints(U)};
+    const int scratch = new_slot(Slot::TEMP, t, st.arena);
+    // ---- the key kernel
+    Emitter em;
+    em.is_internal = [](Op*) { return false; };
+    em.idx_t = "int";
+    em.indent_ = 2;
+    Ctx root;
+    root.shape = updates->type.dims;
+    root.lin = "e";
+    em.ensure_idx(root);
+    auto uidx = [&](int d) { return root.idx[d]; };
+    std::vector<int64_t> istr(IR, 1), ostr(R, 1);
+    for (int d = IR - 2; d >= 0; d--) istr[d] = istr[d + 1] * indices->type.dims[d + 1];
+    for (int d = R - 2; d >= 0; d--) ostr[d] = ostr[d + 1] * operand->type.dims[d + 1];
+    std::ostringstream src;
+    src << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(int* __restrict__ keys, const " << s_type(indices->type.dt)
+        << "* __restrict__ idx) {\n";
+    src << "  const int e = (int)blockIdx.x * " << kThreads << " + threadIdx.x;\n  if (e >= " << U << ") return;\n";
+    src << em.str();
+    // position of this update's index vector in the index tensor
+    std::string ibase = "0LL";
+    for (size_t k = 0; k < idx_batch_dims.size(); k++)
+      ibase += " + (long long)" + uidx(scatter_dims[k]) + " * " + std::to_string(istr[idx_batch_dims[k]]) + "LL";
+    src << "  const long long ib = " << ibase << ";\n";
+    for (int d = 0; d < R; d++) src << "  long long f" << d << " = 0;\n";
+    for (size_t k = 0; k < sdo.size(); k++)
+      src << "  f" << sdo[k] << " = (long long)idx[ib + " << (ivd < IR ? (long long)k * istr[ivd] : 0LL) << "LL];\n";
+    for (size_t q = 0; q < ibd.size(); q++) {
+      const int pos = (int)(std::find(idx_batch_dims.begin(), idx_batch_dims.end(), (int)sbd[q]) - idx_batch_dims.begin());
+      if (pos >= (int)scatter_dims.size()) throw CompileError("stablehlo.scatter: scatter_indices_batching_dims names the index vector dimension");
+      src << "  f" << ibd[q] << " = (long long)" << uidx(scatter_dims[pos]) << ";\n";
+    }
+    src << "  bool ok = true;\n";
+    for (int d = 0; d < R; d++) {
+      int64_t wsize = 1;
+      for (size_t k = 0; k < window_dims.size(); k++) if (window_dims[k] == d) wsize = updates->type.dims[uwd[k]];
+      src << "  ok = ok && f" << d << " >= 0 && f" << d << " + " << wsize << " <= " << operand->type.dims[d] << ";\n";
+    }
+    for (size_t k = 0; k < window_dims.size(); k++) src << "  f" << window_dims[k] << " += (long long)" << uidx((int)uwd[k]) << ";\n";
+    std::string dest = "0LL";
+    for (int d = 0; d < R; d++) dest += " + f" + std::to_string(d) + " * " + std::to_string(ostr[d]) + "LL";
+    src << "  keys[e] = ok ? (int)(" << dest << ") : " << numel << ";\n  keys[" << U << " + e] = e;\n}\n";
+    Step ks;
+    ks.kind = Step::KERNEL;
+    ks.kernel = add_kernel(src.str(), "scatter_keys");
+    ks.label = "scatter keys";
+    ks.grid[0] = (unsigned)std::max<int64_t>(1, (U + kThreads - 1) / kThreads); ks.grid[1] = ks.grid[2] = 1;
+    ks.block[0] = kThreads; ks.block[1] = ks.block[2] = 1;
+    ks.args = {scratch, slot_of.at(indices)};
+    ks.n_outs = 1;
+    plan.steps.push_back(std::move(ks));
+    Step s;
+    s.kind = Step::SCATTER;
+    s.label = op->name;
+    s.dtype = operand->type.dt;
+    s.bytes = operand->type.bytes();
+    s.iparams = {numel, 1, U, 0, kind, 1};
+    s.args = {slot_of.at(operand), slot_of.at(indices), slot_of.at(updates), slot_of.at(out), scratch};
+    return s;
+  }
+
   // stablehlo.scatter in its row form (what jnp.take's gradient and x.at[idx].add(rows) lower to): the index
   // vector holds one coordinate along operand dimension 0 and every update is a whole row. Updates are applied
   // in update order per row with an fp32 accumulator, so the result is deterministic (src/pjrt_plugin/ops/gather_scatter.cc:296-699 handles the general form).
-  Step lower_scatter(Op* op, BlockState& st) {
+  Step lower_scatter(Op* op, Plan& plan, BlockState& st) {
     if (op->operands.size() != 3 || op->results.size() != 1)
       throw CompileError("stablehlo.scatter: only one operand / one update tensor is supported");
     Value *operand = op->operands[0], *indices = op->operands[1], *updates = op->operands[2], *out = op->results[0];
@@ -2358,8 +2445,6 @@ struct Planner {
       ok = k < indices->type.rank() - 1 && indices->type.dims[k] == updates->type.dims[k];
       U *= updates->type.dims[k];
     }
-    if (!ok) throw CompileError("stablehlo.scatter: only the row form is supported (one index along dimension 0, "
-                                "whole-row update windows); got " + op->attr("scatter_dimension_numbers"));
     Block* body = op->regions[0].get();
     int kind = -1;                                    // 0 assign, 1 add, 2 multiply, 3 minimum, 4 maximum
     if (body->ops.size() == 1 && body->ops[0]->operands.size() == 1 && body->ops[0]->operands[0] == body->args[1]) kind = 0;
@@ -2375,6 +2460,7 @@ struct Planner {
     ensure_slot(out, st);
     for (auto* o : op->operands)
       if (!slot_of.count(o)) throw CompileError("internal: operand of scatter has no storage");
+    if (!ok) return lower_scatter_general(op, kind, plan, st);
     Step s;
     s.kind = Step::SCATTER;
     s.label = op->name;
@@ -3549,7 +3635,7 @@ struct Planner {
           break;
         }
         case Cat::SCATTER: {
-          plan.steps.push_back(lower_scatter(op, st));
+          plan.steps.push_back(lower_scatter(op, plan, st));
           break;
         }
         case Cat::WINDOW: {
@@ -4027,7 +4113,7 @@ std::unique_ptr<CompiledProgram> compile_module(Module& m, const CompileOptions&
       long long n = 0;
       for (auto& s : p.steps) {
         if (s.kind == Step::KERNEL || s.kind == Step::ALL_REDUCE || s.kind == Step::ALL_GATHER) n += 1;
-        else if (s.kind == Step::SCATTER) n += scatter_rows_launches(s.iparams[0], s.iparams[2]);
+        else if (s.kind == Step::SCATTER) n += (s.iparams.size() > 5 && s.iparams[5] == 1) ? scatter_elems_launches(s.iparams[0]) : scatter_rows_launches(s.iparams[0], s.iparams[2]);
         else if (s.kind == Step::IGEMM) n += s.ig.split_k > 1 ? 2 : 1;
         else if (s.kind == Step::GEMM16) n += (s.g16.path == 0 && s.g16.split_k > 1) ? 2 : 1;
         else if (s.kind == Step::REPACK16) n += (s.iparams[0] + 65534) / 65535;

@@ -1533,6 +1533,31 @@ __global__ void __launch_bounds__(256) scatter_apply_kernel(T* __restrict__ out,
   }
 }
 
+// General scatter: (destination element, update element) pairs sorted by destination, ties in update order; one
+// thread per run of equal destinations folds the run's updates into the element in that order.
+template <typename T, typename A>
+__global__ void __launch_bounds__(256) scatter_apply_elems_kernel(T* __restrict__ out, const T* __restrict__ upd, const int* __restrict__ key,
+                                                                const int* __restrict__ order, int U, long long numel, int kind) {
+  const int p = blockIdx.x * 256 + threadIdx.x;
+  if (p >= U) return;
+  const int dest = key[p];
+  if (dest >= numel || (p > 0 && key[p - 1] == dest)) return;
+  A acc = scatter_load(out + dest);
+  for (int q = p; q < U && key[q] == dest; ++q) {
+    const A v = scatter_load(upd + order[q]);
+    A r;
+    switch (kind) {
+      case 0: r = v; break;
+      case 1: r = acc + v; break;
+      case 2: r = acc * v; break;
+      case 3: r = (v < acc || v != v) ? v : acc; break;
+      default: r = (v > acc || v != v) ? v : acc; break;
+    }
+    acc = r;
+  }
+  scatter_store(out + dest, acc);
+}
+
 }  // namespace
 
 cudaError_t launch_igemm_f32(const IGemmLaunch& p, const void* A, const void* B, void* C, const void* const* tables,
@@ -1979,6 +2004,41 @@ cudaError_t launch_scatter_rows(int elem_kind, int index_bytes, int kind, long l
   *launches += 1;
   return cudaGetLastError();
 }
+
+cudaError_t launch_scatter_elems(int elem_kind, int kind, long long numel, int updates, void* out, const void* upd, int* scratch,
+                                 cudaStream_t stream, int* launches) {
+  if (updates <= 0 || numel <= 0) return cudaSuccess;
+  int *key = scratch, *order = scratch + updates;
+  int *key_b = scratch + 2 * (long long)updates, *order_b = scratch + 3 * (long long)updates, *hist = scratch + 4 * (long long)updates;
+  const int nblocks = (updates + 1023) / 1024;
+  const int passes = scatter_radix_passes(numel);
+  for (int pass = 0; pass < passes; ++pass) {
+    radix_hist_kernel<<<nblocks, 1024, 0, stream>>>(key, updates, 8 * pass, hist, nblocks);
+    radix_scan_kernel<<<1, 1024, 0, stream>>>(hist, 256 * nblocks);
+    radix_scatter_kernel<<<nblocks, 1024, 0, stream>>>(key, order, key_b, order_b, updates, 8 * pass, hist, nblocks);
+    std::swap(key, key_b);
+    std::swap(order, order_b);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const unsigned grid = (unsigned)((updates + 255) / 256);
+  if (elem_kind == 0)
+    scatter_apply_elems_kernel<float, float><<<grid, 256, 0, stream>>>((float*)out, (const float*)upd, key, order, updates, numel, kind);
+  else if (elem_kind == 1)
+    scatter_apply_elems_kernel<unsigned short, float><<<grid, 256, 0, stream>>>((unsigned short*)out, (const unsigned short*)upd, key, order,
+                                                                                updates, numel, kind);
+  else
+    scatter_apply_elems_kernel<int, int><<<grid, 256, 0, stream>>>((int*)out, (const int*)upd, key, order, updates, numel, kind);
+  *launches += 3 * passes + 1;
+  return cudaGetLastError();
+}
+
+long long scatter_elems_scratch_ints(long long updates) {
+  updates = std::max<long long>(updates, 1);
+  return 4 * updates + 256 * ((updates + 1023) / 1024);
+}
+
+int scatter_elems_launches(long long numel) { return 3 * scatter_radix_passes(numel) + 1; }
 
 static int scatter_radix_passes(long long rows) {
   int bits = 1;

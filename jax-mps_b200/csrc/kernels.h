@@ -45,6 +45,12 @@ cudaError_t launch_scatter_rows(int elem_kind, int index_bytes, int kind, long l
                                 void* out, const void* indices, const void* upd, int* scratch, cudaStream_t stream,
                                 int* launches);
 
+// General scatter, second half: `scratch` holds, written by the program's own key kernel, updates destination element
+// indices (>= numel: dropped) followed by updates update element indices; they are sorted by destination (stable radix
+// sort) and applied run by run in update order. `scratch` has scatter_elems_scratch_ints(updates) ints.
+cudaError_t launch_scatter_elems(int elem_kind, int kind, long long numel, int updates, void* out, const void* upd, int* scratch,
+                                 cudaStream_t stream, int* launches);
+
 // Split-K fp32 product C[M,N] = A[M,K] * B[K,N] (dense row-major device pointers) whose partial sums go to a
 // file-scope device array instead of allocated memory. `*why` explains a refusal. The first call on a device
 // resolves the array's device address (cudaGetSymbolAddress); make it before any stream capture.

@@ -59,6 +59,8 @@ struct Plan;
 // Row scatter (kernels.cu): ints of scratch and kernel launches for `updates` updates into `rows` rows.
 long long scatter_rows_scratch_ints(long long rows, long long updates);
 int scatter_rows_launches(long long rows, long long updates);
+long long scatter_elems_scratch_ints(long long updates);
+int scatter_elems_launches(long long numel);
 
 struct Step {
   enum Kind { KERNEL, IGEMM, MEMCPY, MEMSET, WHILE, CASE, ALL_REDUCE, SCATTER, JOIN, GEMM16, REPACK16, TRANSPOSE, ALL_GATHER } kind = KERNEL;

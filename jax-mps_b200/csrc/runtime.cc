@@ -947,6 +947,13 @@ b200_error* run_step(ExecCtx& x, const Step& s) {
       void *operand = x.ptrs[s.args[0]], *out = x.ptrs[s.args[3]];
       if (operand != out && s.bytes) CUDA_TRY(cudaMemcpyAsync(out, operand, s.bytes, cudaMemcpyDeviceToDevice, st));
       const int ek = s.dtype == DT::F32 ? 0 : s.dtype == DT::BF16 ? 1 : 2;
+      if (s.iparams.size() > 5 && s.iparams[5] == 1) {
+        // general form: the key kernel in front of this step has filled the scratch with (destination, update) pairs
+        cudaError_t e = launch_scatter_elems(ek, (int)s.iparams[4], s.iparams[0], (int)s.iparams[2], out, x.ptrs[s.args[2]],
+                                             (int*)x.ptrs[s.args[4]], st, &x.launches);
+        if (e != cudaSuccess) return make_error(B200_INTERNAL, "launch of " + s.label + " failed: " + cudaGetErrorString(e));
+        return nullptr;
+      }
       cudaError_t e = launch_scatter_rows(ek, (int)s.iparams[3], (int)s.iparams[4], s.iparams[0], s.iparams[1], (int)s.iparams[2], out,
                                           x.ptrs[s.args[1]], x.ptrs[s.args[2]], (int*)x.ptrs[s.args[4]], st, &x.launches);
       if (e != cudaSuccess) return make_error(B200_INTERNAL, "launch of " + s.label + " failed: " + cudaGetErrorString(e));
