@@ -155,6 +155,7 @@ NvrtcApi& nvrtc() {
 struct NcclApi {
   ncclResult_t (*GetUniqueId)(ncclUniqueId*);
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+  ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;   // optional
   ncclResult_t (*CommInitAll)(ncclComm_t*, int, const int*);
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
   ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
@@ -191,6 +192,7 @@ NcclApi& nccl() {
     };
     get("ncclGetUniqueId", (void**)&api.GetUniqueId);
     get("ncclCommInitRank", (void**)&api.CommInitRank);
+    *(void**)&api.CommInitRankConfig = dlsym(h, "ncclCommInitRankConfig");      // optional (NCCL 2.17 and later)
     get("ncclCommInitAll", (void**)&api.CommInitAll);
     get("ncclAllReduce", (void**)&api.AllReduce);
     get("ncclAllGather", (void**)&api.AllGather);
@@ -1291,7 +1293,18 @@ b200_error* create_client(const b200_client_options* o, ncclComm_t given_comm, b
       if (!o->nccl_unique_id) return make_error(B200_INVALID_ARGUMENT, "num_processes > 1 needs nccl_unique_id");
       ncclUniqueId id;
       memcpy(&id, o->nccl_unique_id, sizeof id);
-      ncclResult_t r = n.CommInitRank(&c->comm, c->nprocs, id, c->rank);
+      // A small CTA budget for the communicator leaves the SMs to the backward pass while a gradient bucket is in
+      // flight (the all-reduce then takes longer but hides under compute); B200_NCCL_MAX_CTAS sets it.
+      const char* max_ctas = getenv("B200_NCCL_MAX_CTAS");
+      ncclResult_t r;
+      if (max_ctas && n.CommInitRankConfig && atoi(max_ctas) > 0) {
+        ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+        cfg.maxCTAs = atoi(max_ctas);
+        cfg.minCTAs = 1;
+        r = n.CommInitRankConfig(&c->comm, c->nprocs, id, c->rank, &cfg);
+      } else {
+        r = n.CommInitRank(&c->comm, c->nprocs, id, c->rank);
+      }
       if (r != ncclSuccess) return make_error(B200_INTERNAL, std::string("ncclCommInitRank: ") + n.GetErrorString(r));
     }
     // collectives that overlap with compute run on a stream of their own, at the highest priority so that their
