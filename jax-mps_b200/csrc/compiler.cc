@@ -240,6 +240,20 @@ struct Inliner {
         return;
       }
     }
+    // the same round trip through a reshape: convert(reshape(convert(x))) back to x's type is reshape(x), a view
+    if (sh == "convert" && op->operands.size() == 1 && op->operands[0]->def && op->operands[0]->def->short_name() == "reshape" &&
+        op->operands[0]->def->operands[0]->def && op->operands[0]->def->operands[0]->def->short_name() == "convert") {
+      Op* inner_cv = op->operands[0]->def->operands[0]->def;
+      Value* inner = inner_cv->operands[0];
+      const DT a = inner->type.dt, mid = inner_cv->results[0]->type.dt;
+      const bool widens = (a == DT::BF16 || a == DT::F16) && (mid == DT::F32 || mid == DT::F64);
+      if (widens && op->results[0]->type.dt == a && inner->type.numel() == op->results[0]->type.numel()) {
+        op->name = "stablehlo.reshape";
+        op->attrs.clear();
+        op->operands = {res(inner)};
+        sh = "reshape";
+      }
+    }
     // x + broadcast(0), x * broadcast(1), x - broadcast(0), x / broadcast(1) -> x
     // (src/pjrt_plugin/passes/canonicalize_broadcast_identity.cc)
     if ((sh == "add" || sh == "multiply" || sh == "subtract" || sh == "divide") && op->operands.size() == 2 &&
