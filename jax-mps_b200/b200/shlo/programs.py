@@ -740,3 +740,52 @@ def distilbert_inputs(prog: Program, seed: int = 0, weight_std: float = 0.02, ma
         else:
             out.append((rng.standard_normal(s) * weight_std).astype(np.float32))
     return out
+
+
+# ---------------------------------------------------------------------------
+# Threefry-2x32 as elementwise integer operations (what jax.random lowers to where no fused kernel exists; the
+# reference pins its fused Metal kernel bit for bit against the CPU backend: tests/configs/random.py:54-74)
+# ---------------------------------------------------------------------------
+def _threefry2x32(b: Builder, k0: Val, k1: Val, x0: Val, x1: Val):
+    """Twenty rounds of Threefry-2x32 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3") on ui32 tensors of one
+    shape; k0 and k1 are already broadcast to it."""
+    shape = x0.shape
+    u = lambda v: b.full(shape, int(v), "ui32")
+    rotl = lambda v, r: b.or_(b.shl(v, u(r)), b.shr_logical(v, u(32 - r)))
+    ks = [k0, k1, b.xor(b.xor(k0, k1), u(0x1BD11BDA))]
+    rot = [(13, 15, 26, 6), (17, 29, 16, 24)]
+    x0, x1 = b.add(x0, ks[0]), b.add(x1, ks[1])
+    for i in range(5):
+        for r in rot[i % 2]:
+            x0 = b.add(x0, x1)
+            x1 = b.xor(rotl(x1, r), x0)
+        x0 = b.add(x0, ks[(i + 1) % 3])
+        x1 = b.add(b.add(x1, ks[(i + 2) % 3]), u(i + 1))
+    return x0, x1
+
+
+def threefry_block(n: int) -> Program:
+    """key ui32[2], x0 ui32[n], x1 ui32[n] -> the two output words per lane."""
+    b = Builder()
+    key, x0, x1 = b.arg((2,), "ui32"), b.arg((n,), "ui32"), b.arg((n,), "ui32")
+    k0 = b.broadcast_in_dim(b.reshape(b.slice(key, (0,), (1,)), ()), (n,), ())
+    k1 = b.broadcast_in_dim(b.reshape(b.slice(key, (1,), (2,)), ()), (n,), ())
+    y0, y1 = _threefry2x32(b, k0, k1, x0, x1)
+    return Program("threefry_block", b.module([y0, y1], name="jit_threefry"),
+                   [("key", (2,), "ui32"), ("x0", (n,), "ui32"), ("x1", (n,), "ui32")],
+                   [("y0", (n,), "ui32"), ("y1", (n,), "ui32")], 1, {"n": n})
+
+
+def threefry_bits(n: int) -> Program:
+    """key ui32[2] -> n random ui32 words the way jax.random.bits lays them out: the counters 0 .. n-1 (n even) split into
+    a lower and an upper half, one Threefry block per pair, the two output halves concatenated."""
+    assert n % 2 == 0
+    b = Builder()
+    key = b.arg((2,), "ui32")
+    h = n // 2
+    counts = b.iota((n,), "ui32", 0)
+    k0 = b.broadcast_in_dim(b.reshape(b.slice(key, (0,), (1,)), ()), (h,), ())
+    k1 = b.broadcast_in_dim(b.reshape(b.slice(key, (1,), (2,)), ()), (h,), ())
+    y0, y1 = _threefry2x32(b, k0, k1, b.slice(counts, (0,), (h,)), b.slice(counts, (h,), (n,)))
+    return Program("threefry_bits", b.module([b.concatenate([y0, y1], 0)], name="jit_random_bits"), [("key", (2,), "ui32")],
+                   [("bits", (n,), "ui32")], 1, {"n": n})
