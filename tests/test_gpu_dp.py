@@ -18,8 +18,8 @@ pytestmark = pytest.mark.gpu
 def _rank_main(rank, world, id_pipe, q, overlap):
     sys.path.insert(0, str(ROOT / "jax-mps_b200"))
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    if overlap:
-        os.environ["B200_ALL_REDUCE_OVERLAP"] = "1"     # buckets of the all-reduce issued inside the backward pass
+    if not overlap:
+        os.environ["B200_NO_ALL_REDUCE_OVERLAP"] = "1"  # one all-reduce after the last gradient instead of buckets inside the backward pass
     try:
         import b200
         from b200.shlo import programs

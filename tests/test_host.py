@@ -89,15 +89,15 @@ def test_resnet_plan_shape():
     assert plan.count("igemm ") == 20 + 19 + 20 + 3        # 20 convs fwd, 19 input grads, 20 kernel grads, dense fwd + 2 grads
     assert "all_reduce" not in plan
     dp = programs.resnet18_train_step(batch=4, image=8, width=8, n_partitions=2)
-    plan2, _ = b200.compile_to_plan(dp.text, num_processes=2, process_index=1)
+    os.environ["B200_NO_ALL_REDUCE_OVERLAP"] = "1"
+    try:
+        plan2, _ = b200.compile_to_plan(dp.text, num_processes=2, process_index=1)
+    finally:
+        del os.environ["B200_NO_ALL_REDUCE_OVERLAP"]
     assert plan2.count("all_reduce") == 63                  # 62 gradient leaves + the loss
     assert "join" not in plan2 and "overlapped" not in plan2
     check_runs(plan2, overlapped=False)
-    os.environ["B200_ALL_REDUCE_OVERLAP"] = "1"
-    try:
-        plan3, _ = b200.compile_to_plan(dp.text, num_processes=2, process_index=1)
-    finally:
-        del os.environ["B200_ALL_REDUCE_OVERLAP"]
+    plan3, _ = b200.compile_to_plan(dp.text, num_processes=2, process_index=1)       # the default: buckets inside the backward pass
     assert plan3.count("all_reduce") == 63
     check_runs(plan3, overlapped=True)
 
