@@ -983,26 +983,30 @@ bool gemm16_plan(Gemm16Launch& g, bool aligned) {
   const long long mt = (g.M + 127) / 128;
   const int ktiles = (g.K + 63) / 64;
   auto tiles_for = [&](int bn) { return mt * ((g.N + bn - 1) / bn) * g.G; };
-  // Tile width by a small cost model: cycles per 64-deep k-tile of a 128 x bn tile (a 256-wide tile is bound by the
-  // tensor pipe, narrower ones by the shared-memory reads of the MMA unit), a fixed cost per tile, and whole waves
-  // of tiles over the SMs. Ties go to the wider tile.
+  // Tile width and K split by a small cost model: cycles per 64-deep k-tile of a 128 x bn tile (a 256-wide tile is
+  // bound by the tensor pipe, narrower ones by the shared-memory reads of the MMA unit), a fixed cost per tile, whole
+  // waves of CTAs over the SMs, and for a split the pass that adds the partial sums (a launch plus its traffic). A split
+  // is considered only while it fits one wave and leaves each CTA four k-tiles. Ties go to the wider tile, then to the
+  // smaller split.
   {
     double best = 1e30;
+    int best_split = 1;
     for (int bn : {256, 128, 64}) {
       if (bn > 64 && g.N <= bn / 2) continue;
       const double per_kt = bn == 256 ? 512.0 : (bn == 128 ? 256.0 : 192.0);
-      const long long waves = (tiles_for(bn) + SMS - 1) / SMS;
-      const double cost = (double)waves * (ktiles * per_kt + 400.0);
-      if (cost < best * 0.999) { best = cost; g.bn = bn; }
+      const long long t = tiles_for(bn);
+      for (int split = 1; split <= 16; ++split) {
+        if (split > 1 && (t * split > SMS || ktiles / split < 4)) break;
+        const int kps = (ktiles + split - 1) / split;
+        const long long waves = (t * split + SMS - 1) / SMS;
+        double cost = (double)waves * (kps * per_kt + 400.0);
+        if (split > 1) cost += 2500.0 + (double)g.G * g.M * g.N * 4.0 * (split + 1) / 3000.0;     // second pass: launch + bytes at ~3 KB per cycle
+        if (cost < best * 0.999) { best = cost; g.bn = bn; best_split = split; }
+      }
     }
-  }
-  const long long tiles = tiles_for(g.bn);
-  g.kt_per_split = ktiles;
-  if (tiles * 2 <= SMS && ktiles >= 8) {
-    // too few tiles for the GPU: split K so that about one wave of CTAs runs, each with at least four k-tiles
-    int split = (int)std::min<long long>(SMS / tiles, ktiles / 4);
-    if (split > 1) {
-      g.kt_per_split = (ktiles + split - 1) / split;
+    g.kt_per_split = ktiles;
+    if (best_split > 1) {
+      g.kt_per_split = (ktiles + best_split - 1) / best_split;
       g.split_k = (ktiles + g.kt_per_split - 1) / g.kt_per_split;
       if (g.split_k > 1) g.scratch_floats = (long long)g.split_k * g.G * g.M * g.N;
       else g.kt_per_split = ktiles;
