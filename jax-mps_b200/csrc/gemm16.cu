@@ -999,7 +999,8 @@ bool gemm16_plan(Gemm16Launch& g, bool aligned) {
         if (split > 1 && (t * split > SMS || ktiles / split < 4)) break;
         const int kps = (ktiles + split - 1) / split;
         const long long waves = (t * split + SMS - 1) / SMS;
-        double cost = (double)waves * (kps * per_kt + 400.0);
+        const double fill_kt = (128.0 + bn) * 64.0 * 2.0 / 90.0;            // one SM takes its tiles in at about 90 bytes per cycle
+        double cost = (double)waves * (kps * std::max(per_kt, fill_kt) + 400.0);
         if (split > 1) cost += 2500.0 + (double)g.G * g.M * g.N * 4.0 * (split + 1) / 3000.0;     // second pass: launch + bytes at ~3 KB per cycle
         if (cost < best * 0.999) { best = cost; g.bn = bn; best_split = split; }
       }
