@@ -670,6 +670,43 @@ class Builder:
                          props=props, regions=[sel, sc])
         return y
 
+    def sort(self, xs: Sequence[Val], dim: int = -1, comparator: Callable | None = None, *, descending: bool = False,
+             num_keys: int = 1, stable: bool = True) -> list[Val]:
+        """stablehlo.sort of several operands of one shape along `dim`. `comparator(sub, a0, b0, a1, b1, ...)` returns
+        the i1 "a goes before b"; by default what jnp.sort / lax.sort_key_val emit: the first `num_keys` operands
+        compared lexicographically, floats in their total order (-NaN < -inf < ... < -0 < +0 < ... < inf < NaN).
+        No gradient."""
+        xs = list(xs)
+        dim = dim % xs[0].ndim
+        assert all(x.shape == xs[0].shape for x in xs)
+
+        def default(sub, *ab):
+            direction = "GT" if descending else "LT"
+            out = None
+            for k in reversed(range(num_keys)):
+                a, b = ab[2 * k], ab[2 * k + 1]
+                ctype = "TOTALORDER" if a.dtype in FLOATS else None
+                first = sub.compare(a, b, direction, ctype)
+                if out is None:
+                    out = first
+                else:
+                    out = sub.or_(first, sub.and_(sub.compare(a, b, "EQ", ctype), out))
+            return out
+
+        targs = []
+        for x in xs:
+            targs += [((), x.dtype)] * 2
+        reg = self.region(targs, comparator or default)
+        return list(self.emit("stablehlo.sort", xs, [(x.shape, x.dtype) for x in xs],
+                              props={"dimension": f"{dim} : i64", "is_stable": "true" if stable else "false"}, regions=[reg]))
+
+    def top_k(self, x: Val, k: int) -> list[Val]:
+        """chlo.top_k: the k largest values along the last dimension in descending order and their positions (i32);
+        equal values keep the order of their positions. No gradient."""
+        assert 0 <= k <= x.shape[-1]
+        shape = x.shape[:-1] + (k,)
+        return list(self.emit("chlo.top_k", [x], [(shape, x.dtype), (shape, "i32")], props={"k": f"{k} : i64"}))
+
     def scatter(self, operand: Val, indices: Val, updates: Val, op: str = "add", *, update_window_dims=(),
                 inserted_window_dims=(), scatter_dims_to_operand_dims=(), index_vector_dim=None, input_batching_dims=(),
                 scatter_indices_batching_dims=()) -> Val:

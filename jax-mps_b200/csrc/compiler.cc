@@ -417,6 +417,73 @@ struct Inliner {
     // is written as what it means, result[b, i, j] = sum over k of lhs[b, i, k] * rhs[b, k, j]: both operands broadcast
     // to [batch, lhs free, rhs free, contracted], multiplied and reduced over the trailing dimensions. The broadcasts
     // and the multiply are evaluated inside the reduction kernel; nothing of the large shape is stored.
+    // chlo.top_k (src/pjrt_plugin/ops/sort_fft_complex.cc:41-88): a stable descending sort of the values together with
+    // their positions along the last dimension, of which the first k are kept. NaN goes after every number.
+    if (op->name == "chlo.top_k" && op->operands.size() == 1 && op->results.size() == 2) {
+      Value* x = op->operands[0];
+      const TensorType xt = x->type;
+      const int R = xt.rank();
+      if (R < 1) throw CompileError("chlo.top_k of a scalar");
+      const int64_t kk = op->results[0]->type.dims.empty() ? 0 : op->results[0]->type.dims.back();
+      auto make = [&](const std::string& name, std::vector<Value*> ins, std::vector<Value*> outs, std::map<std::string, std::string> attrs) {
+        auto o = std::make_unique<Op>();
+        o->name = name;
+        o->operands = std::move(ins);
+        o->attrs = std::move(attrs);
+        for (size_t q = 0; q < outs.size(); q++) { outs[q]->def = o.get(); outs[q]->def_index = (int)q; o->results.push_back(outs[q]); }
+        return o;
+      };
+      TensorType it = xt;
+      it.dt = DT::I32;
+      Value* pos = m.new_value(it, "");
+      process(make("stablehlo.iota", {}, {pos}, {{"iota_dimension", std::to_string(R - 1) + " : i64"}}), b);
+      Value* sv = m.new_value(xt, "");
+      Value* sp = m.new_value(it, "");
+      auto sort = make("stablehlo.sort", {x, res(pos)}, {sv, sp}, {{"dimension", std::to_string(R - 1) + " : i64"}, {"is_stable", "true"}});
+      auto body = std::make_unique<Block>();
+      body->parent_op = sort.get();
+      TensorType st, bt, pt;
+      st.dt = xt.dt;
+      bt.dt = DT::PRED;
+      pt.dt = DT::I32;
+      Value* args[4] = {m.new_value(st, "%a"), m.new_value(st, "%b"), m.new_value(pt, "%pa"), m.new_value(pt, "%pb")};
+      for (Value* v : args) { v->owner = body.get(); v->arg_index = (int)body->args.size(); body->args.push_back(v); }
+      auto inner = [&](const std::string& name, std::vector<Value*> ins, std::map<std::string, std::string> attrs) {
+        Value* r = m.new_value(bt, "");
+        auto o = make(name, std::move(ins), {r}, std::move(attrs));
+        o->parent = body.get();
+        body->ops.push_back(std::move(o));
+        return r;
+      };
+      auto cmp = [&](Value* l, Value* r, const char* dir) {
+        const char* ct = dt_is_float(xt.dt) ? "FLOAT" : (dt_is_unsigned(xt.dt) || xt.dt == DT::PRED ? "UNSIGNED" : "SIGNED");
+        return inner("stablehlo.compare", {l, r}, {{"comparison_direction", std::string("#stablehlo<comparison_direction ") + dir + ">"},
+                                                    {"compare_type", std::string("#stablehlo<comparison_type ") + ct + ">"}});
+      };
+      Value* first = cmp(args[0], args[1], "GT");
+      if (dt_is_float(xt.dt)) {
+        Value* b_nan = cmp(args[1], args[1], "NE");
+        Value* a_num = cmp(args[0], args[0], "EQ");
+        first = inner("stablehlo.or", {first, inner("stablehlo.and", {b_nan, a_num}, {})}, {});
+      }
+      auto ret = std::make_unique<Op>();
+      ret->name = "stablehlo.return";
+      ret->operands = {first};
+      ret->parent = body.get();
+      body->ops.push_back(std::move(ret));
+      sort->regions.push_back(std::move(body));
+      process(std::move(sort), b);
+      std::string zeros = "array<i64", lim = "array<i64", ones = "array<i64";
+      for (int d = 0; d < R; d++) {
+        zeros += (d ? ", 0" : ": 0");
+        ones += (d ? ", 1" : ": 1");
+        lim += (d ? ", " : ": ") + std::to_string(d == R - 1 ? kk : xt.dims[d]);
+      }
+      zeros += ">"; ones += ">"; lim += ">";
+      for (int q = 0; q < 2; q++)
+        process(make("stablehlo.slice", {res(q == 0 ? sv : sp)}, {op->results[q]}, {{"start_indices", zeros}, {"limit_indices", lim}, {"strides", ones}}), b);
+      return;
+    }
     if (sh == "dot_general" && op->operands.size() == 2 && op->results.size() == 1 && op->has("dot_dimension_numbers")) {
       auto integral = [](DT d) { return d == DT::PRED || dt_is_signed(d) || dt_is_unsigned(d); };
       const TensorType rt = op->results[0]->type;
@@ -832,7 +899,7 @@ struct SkinnyWeightHoist {
 // ---------------------------------------------------------------------------
 // op classification
 // ---------------------------------------------------------------------------
-enum class Cat { ELEMENTWISE, DUP, INDEXING, REDUCE, DOT, CONV, SCATTER, WINDOW, WHILE, CASE, ALL_REDUCE, ALL_GATHER, RETURN, TOKEN, PARTITION_ID, UNSUPPORTED };
+enum class Cat { ELEMENTWISE, DUP, INDEXING, REDUCE, DOT, CONV, SCATTER, WINDOW, SORT, WHILE, CASE, ALL_REDUCE, ALL_GATHER, RETURN, TOKEN, PARTITION_ID, UNSUPPORTED };
 
 Cat categorize(Op* op) {
   const std::string sh = op->short_name();
@@ -849,6 +916,7 @@ Cat categorize(Op* op) {
   if (sh == "convolution") return Cat::CONV;
   if (sh == "scatter") return Cat::SCATTER;
   if (sh == "reduce_window" || sh == "select_and_scatter") return Cat::WINDOW;
+  if (sh == "sort") return Cat::SORT;
   if (sh == "while") return Cat::WHILE;
   if (sh == "case") return Cat::CASE;
   if (sh == "all_reduce") return Cat::ALL_REDUCE;
@@ -862,7 +930,7 @@ void collect_unsupported(Block* b, std::set<std::string>& out, bool in_combiner)
   for (auto& op : b->ops) {
     Cat c = categorize(op.get());
     if (c == Cat::UNSUPPORTED) out.insert(op->name);
-    bool comb = c == Cat::REDUCE || c == Cat::SCATTER || c == Cat::WINDOW || c == Cat::ALL_REDUCE || c == Cat::ALL_GATHER;
+    bool comb = c == Cat::REDUCE || c == Cat::SCATTER || c == Cat::WINDOW || c == Cat::SORT || c == Cat::ALL_REDUCE || c == Cat::ALL_GATHER;
     for (auto& r : op->regions) collect_unsupported(r.get(), out, comb);
   }
 }
@@ -1558,6 +1626,203 @@ struct Planner {
     L.outs = outs;
     L.ins = ins;
     return L;
+  }
+
+  // stablehlo.sort (src/pjrt_plugin/ops/sort_fft_complex.cc:135-250 of the reference, which recognises ascending and
+  // descending comparators; here the comparator region is compiled as it stands). A stable merge sort over a
+  // permutation: a block sorts a tile of up to kSortTile elements of one row in shared memory, starting from runs of
+  // one element and doubling; every element finds its place in the merged run by a binary search of the sibling run
+  // (elements of the left run go before equal elements of the right run, which is what makes the sort stable for any
+  // strict weak order). Rows longer than a tile continue with one launch per doubling over a permutation in global
+  // memory; the last pass of either kind writes the sorted operands. All operands move together.
+  static constexpr int kSortTile = 1024;
+  void lower_sort(Op* op, Plan& plan, BlockState& st) {
+    const size_t k = op->operands.size();
+    if (k < 1 || op->results.size() != k || op->regions.size() != 1 || op->regions[0]->args.size() != 2 * k)
+      throw CompileError("stablehlo.sort: malformed operands or comparator");
+    const TensorType& t0 = op->operands[0]->type;
+    const int R = t0.rank();
+    int64_t dim = op->has("dimension") ? attr_int(op->attr("dimension")) : R - 1;
+    if (dim < 0) dim += R;
+    if (R == 0 || dim < 0 || dim >= R) throw CompileError("stablehlo.sort: dimension out of range");
+    int64_t smem = 0;
+    for (size_t q = 0; q < k; q++) {
+      if (op->operands[q]->type.dims != t0.dims || !(op->results[q]->type == op->operands[q]->type))
+        throw CompileError("stablehlo.sort: operands and results must share one shape");
+      if (!slot_of.count(op->operands[q])) throw CompileError("internal: operand of sort has no storage");
+      smem += dt_size(op->operands[q]->type.dt);
+    }
+    std::vector<Value*> ins(op->operands.begin(), op->operands.end()), outs(op->results.begin(), op->results.end());
+    for (auto* o : outs) ensure_slot(o, st);
+    const int64_t N = t0.dims[dim], numel = t0.numel();
+    if (numel == 0) return;
+    int64_t inner = 1;
+    for (int d = (int)dim + 1; d < R; d++) inner *= t0.dims[d];
+    const int64_t rows = numel / N;
+    if (N >= (1LL << 30)) throw CompileError("stablehlo.sort: more than 2^30 elements along the sorted dimension");
+    if (smem * kSortTile > 36 * 1024) throw CompileError("stablehlo.sort: operands of more than 36 bytes per element together are not supported");
+    const int64_t tiles = (N + kSortTile - 1) / kSortTile;
+    if (rows * tiles >= (1LL << 31)) throw CompileError("stablehlo.sort: too many rows");
+    const bool one_tile = tiles == 1;
+
+    // shared pieces of source text
+    auto comparator = [&](Emitter& e) {
+      // bool before(a0, b0, a1, b1, ...): the comparator region on compute types
+      std::string sig;
+      std::vector<std::string> args;
+      for (size_t q = 0; q < k; q++) {
+        const std::string ct = c_type(ins[q]->type.dt);
+        sig += (q ? ", " : "") + ct + " a" + std::to_string(q) + ", " + ct + " b" + std::to_string(q);
+        args.push_back("a" + std::to_string(q));
+        args.push_back("b" + std::to_string(q));
+      }
+      e.line("auto before = [&](" + sig + ") -> bool {");
+      auto res = e.emit_scalar_region(op->regions[0].get(), args);
+      if (res.size() != 1) throw CompileError("stablehlo.sort: the comparator must return one value");
+      e.line("return " + res[0] + ";");
+      e.line("};");
+    };
+    auto row_base = [&](std::ostringstream& src) {
+      src << "  const long long base = (row / " << inner << "LL) * " << (N * inner) << "LL + row % " << inner << "LL;\n";
+    };
+    auto call_before = [&](const std::string& x, const std::string& y) {
+      std::string c = "before(";
+      for (size_t q = 0; q < k; q++) c += (q ? ", " : "") + x + std::to_string(q) + ", " + y + std::to_string(q);
+      return c + ")";
+    };
+
+    int perm[2] = {-1, -1};
+    if (!one_tile) {
+      TensorType pt;
+      pt.dt = DT::I32;
+      pt.dims = {numel};
+      perm[0] = new_slot(Slot::TEMP, pt, st.arena);
+      perm[1] = new_slot(Slot::TEMP, pt, st.arena);
+    }
+    // ---- tile kernel
+    {
+      std::ostringstream src;
+      src << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(";
+      if (one_tile) src << signature(outs, ins);
+      else src << "int* __restrict__ perm_out, " << signature({}, ins);
+      src << ") {\n";
+      src << "  __shared__ int sp[2][" << kSortTile << "];\n";
+      for (size_t q = 0; q < k; q++) src << "  __shared__ " << s_type(ins[q]->type.dt) << " sv" << q << "[" << kSortTile << "];\n";
+      src << "  const long long row = (long long)blockIdx.x / " << tiles << ";\n";
+      src << "  const int t0 = (int)((long long)blockIdx.x % " << tiles << ") * " << kSortTile << ";\n";
+      src << "  const int cnt = " << N << " - t0 < " << kSortTile << " ? " << N << " - t0 : " << kSortTile << ";\n";
+      row_base(src);
+      src << "  for (int i = threadIdx.x; i < cnt; i += " << kThreads << ") {\n    sp[0][i] = i;\n";
+      for (size_t q = 0; q < k; q++) src << "    sv" << q << "[i] = in" << q << "[base + (long long)(t0 + i) * " << inner << "LL];\n";
+      src << "  }\n  __syncthreads();\n";
+      Emitter ce;
+      ce.idx_t = "int";
+      ce.name_prefix = "c";
+      ce.indent_ = 2;
+      comparator(ce);
+      src << ce.str();
+      src << "  int cur = 0;\n";
+      src << "  for (int w = 1; w < cnt; w <<= 1) {\n";
+      src << "    for (int i = threadIdx.x; i < cnt; i += " << kThreads << ") {\n";
+      src << "      const int run = i / (2 * w) * (2 * w);\n";
+      src << "      const bool right = i - run >= w;\n";
+      src << "      const int me = sp[cur][i];\n";
+      for (size_t q = 0; q < k; q++) src << "      const " << c_type(ins[q]->type.dt) << " a" << q << " = " << load_expr(ins[q], "sv" + std::to_string(q), "me") << ";\n";
+      src << "      int lo = right ? run : run + w;\n";
+      src << "      int hi = right ? run + w : run + 2 * w;\n";
+      src << "      if (hi > cnt) hi = cnt;\n      if (lo > hi) lo = hi;\n";
+      src << "      int l = lo, h = hi;\n";
+      src << "      while (l < h) {\n        const int mid = (l + h) >> 1;\n        const int other = sp[cur][mid];\n";
+      for (size_t q = 0; q < k; q++) src << "        const " << c_type(ins[q]->type.dt) << " b" << q << " = " << load_expr(ins[q], "sv" + std::to_string(q), "other") << ";\n";
+      src << "        const bool goes_first = right ? !" << call_before("a", "b") << " : " << call_before("b", "a") << ";\n";
+      src << "        if (goes_first) l = mid + 1; else h = mid;\n      }\n";
+      src << "      sp[cur ^ 1][run + (right ? i - run - w : i - run) + (l - lo)] = me;\n";
+      src << "    }\n    __syncthreads();\n    cur ^= 1;\n  }\n";
+      src << "  for (int i = threadIdx.x; i < cnt; i += " << kThreads << ") {\n";
+      if (one_tile) {
+        for (size_t q = 0; q < k; q++) src << "    out" << q << "[base + (long long)(t0 + i) * " << inner << "LL] = sv" << q << "[sp[cur][i]];\n";
+      } else {
+        src << "    perm_out[row * " << N << "LL + t0 + i] = t0 + sp[cur][i];\n";
+      }
+      src << "  }\n}\n";
+      Step s;
+      s.kind = Step::KERNEL;
+      s.kernel = add_kernel(src.str(), "sort_tile");
+      s.label = "sort (tiles)";
+      s.grid[0] = (unsigned)(rows * tiles); s.grid[1] = s.grid[2] = 1;
+      s.block[0] = kThreads; s.block[1] = s.block[2] = 1;
+      if (one_tile) { for (auto* o : outs) s.args.push_back(slot_of.at(o)); s.n_outs = (int)k; }
+      else { s.args.push_back(perm[0]); s.n_outs = 1; }
+      for (auto* i : ins) s.args.push_back(slot_of.at(i));
+      plan.steps.push_back(std::move(s));
+    }
+    if (one_tile) return;
+    // ---- merge passes: the width of the sorted runs comes from a constant, so that all passes but the last share a kernel
+    int merge_kernel[2] = {-1, -1};          // [writes the operands]
+    auto merge_source = [&](bool final_pass) {
+      std::ostringstream src;
+      src << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(";
+      if (final_pass) src << signature(outs, ins);
+      else src << "int* __restrict__ perm_out, " << signature({}, ins);
+      src << ", const int* __restrict__ perm_in, const int* __restrict__ width) {\n";
+      src << "  const long long lin = (long long)blockIdx.x * " << kThreads << " + threadIdx.x;\n";
+      src << "  if (lin >= " << numel << "LL) return;\n";
+      src << "  const long long row = lin / " << N << "LL;\n  const long long i = lin % " << N << "LL;\n";
+      row_base(src);
+      src << "  const int* __restrict__ P = perm_in + row * " << N << "LL;\n";
+      src << "  const long long w = width[0];\n";
+      Emitter ce;
+      ce.idx_t = "int";
+      ce.name_prefix = "c";
+      ce.indent_ = 2;
+      comparator(ce);
+      src << ce.str();
+      src << "  const long long run = i / (2 * w) * (2 * w);\n";
+      src << "  const bool right = i - run >= w;\n";
+      src << "  const int me = P[i];\n";
+      for (size_t q = 0; q < k; q++) src << "  const " << c_type(ins[q]->type.dt) << " a" << q << " = " << load_expr(ins[q], "in" + std::to_string(q), "base + (long long)me * " + std::to_string(inner) + "LL") << ";\n";
+      src << "  long long lo = right ? run : run + w;\n";
+      src << "  long long hi = right ? run + w : run + 2 * w;\n";
+      src << "  if (hi > " << N << "LL) hi = " << N << "LL;\n  if (lo > hi) lo = hi;\n";
+      src << "  long long l = lo, h = hi;\n";
+      src << "  while (l < h) {\n    const long long mid = (l + h) >> 1;\n    const int other = P[mid];\n";
+      for (size_t q = 0; q < k; q++) src << "    const " << c_type(ins[q]->type.dt) << " b" << q << " = " << load_expr(ins[q], "in" + std::to_string(q), "base + (long long)other * " + std::to_string(inner) + "LL") << ";\n";
+      src << "    const bool goes_first = right ? !" << call_before("a", "b") << " : " << call_before("b", "a") << ";\n";
+      src << "    if (goes_first) l = mid + 1; else h = mid;\n  }\n";
+      src << "  const long long dest = run + (right ? i - run - w : i - run) + (l - lo);\n";
+      if (final_pass) {
+        for (size_t q = 0; q < k; q++) src << "  out" << q << "[base + dest * " << inner << "LL] = in" << q << "[base + (long long)me * " << inner << "LL];\n";
+      } else {
+        src << "  perm_out[row * " << N << "LL + dest] = me;\n";
+      }
+      src << "}\n";
+      return src.str();
+    };
+    int from = 0;
+    for (int64_t w = kSortTile; w < N; w <<= 1) {
+      const bool final_pass = 2 * w >= N;
+      int& kern = merge_kernel[final_pass ? 1 : 0];
+      if (kern < 0) kern = add_kernel(merge_source(final_pass), final_pass ? "sort_merge_out" : "sort_merge");
+      TensorType wt;
+      wt.dt = DT::I32;
+      std::vector<uint8_t> wb(4);
+      const int32_t w32 = (int32_t)w;
+      memcpy(wb.data(), &w32, 4);
+      const int wslot = const_slot(wt, wb);
+      Step s;
+      s.kind = Step::KERNEL;
+      s.kernel = kern;
+      s.label = "sort (merge runs of " + std::to_string(w) + ")";
+      s.grid[0] = (unsigned)((numel + kThreads - 1) / kThreads); s.grid[1] = s.grid[2] = 1;
+      s.block[0] = kThreads; s.block[1] = s.block[2] = 1;
+      if (final_pass) { for (auto* o : outs) s.args.push_back(slot_of.at(o)); s.n_outs = (int)k; }
+      else { s.args.push_back(perm[from ^ 1]); s.n_outs = 1; }
+      for (auto* i : ins) s.args.push_back(slot_of.at(i));
+      s.args.push_back(perm[from]);
+      s.args.push_back(wslot);
+      plan.steps.push_back(std::move(s));
+      from ^= 1;
+    }
   }
 
   // dynamic_update_slice of a loop-carried tensor written back to the same position of the loop state: the result
@@ -3655,6 +3920,10 @@ struct Planner {
         case Cat::WINDOW: {
           Launch L = op->short_name() == "reduce_window" ? gen_reduce_window(op, st) : gen_select_and_scatter(op, st);
           add_launch(plan, L, op->short_name(), st);
+          break;
+        }
+        case Cat::SORT: {
+          lower_sort(op, plan, st);
           break;
         }
         case Cat::TOKEN: {

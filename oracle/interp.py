@@ -730,6 +730,107 @@ class Interp:
                 raise RuntimeError("oracle while: iteration limit")
         return cur
 
+    # ---- sorting ---------------------------------------------------------------------------------------
+    SORT_RANK_MAX = 2048                    # rows up to this length are sorted by the all-pairs definition
+
+    def _sort_before(self, blk, env, lhs, rhs):
+        """The comparator region on arrays: lhs[k] goes before rhs[k] (elementwise over broadcast shapes)."""
+        args = []
+        for a, b in zip(lhs, rhs):
+            shape = np.broadcast_shapes(a.shape, b.shape)
+            args += [np.broadcast_to(a, shape), np.broadcast_to(b, shape)]
+        self._vector += 1
+        (r,) = self.region(blk, env, args)
+        self._vector -= 1
+        return np.asarray(r).astype(bool)
+
+    def _sort_positions_by_rank(self, blk, env, rows):
+        """Position of every element in the stable order, from the definition: the elements that go before it plus the
+        equivalent elements (neither before the other) in front of it. rows: one [R, n] array per operand."""
+        R, n = rows[0].shape
+        pos = np.empty((R, n), np.int64)
+        chunk = max(1, (1 << 22) // max(1, n * n))
+        earlier = np.tril(np.ones((n, n), bool), -1)           # [i, j]: j < i
+        for r0 in range(0, R, chunk):
+            sl = slice(r0, min(R, r0 + chunk))
+            xi = [v[sl, :, None] for v in rows]
+            xj = [v[sl, None, :] for v in rows]
+            j_before_i = self._sort_before(blk, env, xj, xi)    # [c, i, j]
+            i_before_j = self._sort_before(blk, env, xi, xj)
+            tie = ~j_before_i & ~i_before_j & earlier[None]
+            pos[sl] = j_before_i.sum(-1) + tie.sum(-1)
+        return pos
+
+    def _sort_positions_by_merging(self, blk, env, rows):
+        """The same order for long rows: runs of one element are merged pairwise, every element finding its place in
+        the sibling run by bisection with the comparator (left-run elements go in front of equivalent right-run ones)."""
+        R, n = rows[0].shape
+        perm = np.broadcast_to(np.arange(n), (R, n)).copy()
+        ar = np.arange(n)
+        rr = np.arange(R)[:, None]
+        w = 1
+        while w < n:
+            run = ar // (2 * w) * (2 * w)
+            right = (ar - run) >= w
+            lo = np.where(right, run, np.minimum(run + w, n))
+            hi = np.minimum(np.where(right, run + w, run + 2 * w), n)
+            lo = np.minimum(lo, hi)
+            me = [np.take_along_axis(v, perm, 1) for v in rows]
+            l = np.broadcast_to(lo, (R, n)).copy()
+            h = np.broadcast_to(hi, (R, n)).copy()
+            while True:
+                open_ = l < h
+                if not open_.any():
+                    break
+                mid = np.where(open_, (l + h) // 2, 0)
+                other = [v[rr, perm[rr, mid]] for v in rows]
+                first = np.where(right[None], ~self._sort_before(blk, env, me, other), self._sort_before(blk, env, other, me))
+                l = np.where(open_ & first, mid + 1, l)
+                h = np.where(open_ & ~first, mid, h)
+            dest = run[None] + np.where(right, ar - run - w, ar - run)[None] + (l - lo[None])
+            nxt = np.empty_like(perm)
+            nxt[rr, dest] = perm
+            perm = nxt
+            w *= 2
+        pos = np.empty_like(perm)
+        pos[rr, perm] = ar[None]
+        return pos
+
+    def op_sort(self, op, x, env):
+        """stablehlo.sort along `dimension` with the comparator region; always stable, which is_stable = false permits
+        (src/pjrt_plugin/ops/sort_fft_complex.cc:135-250 sorts by the direction it reads out of the comparator)."""
+        rank = x[0].ndim
+        dim = attr_int(op.attrs["dimension"]) if "dimension" in op.attrs else rank - 1
+        dim %= rank
+        n = x[0].shape[dim]
+        if x[0].size == 0:
+            return [np.array(v) for v in x]
+        moved = [np.moveaxis(np.asarray(v), dim, -1) for v in x]
+        lead = moved[0].shape[:-1]
+        rows = [np.ascontiguousarray(m).reshape(-1, n) for m in moved]
+        blk = op.regions[0]
+        pos = (self._sort_positions_by_rank if n <= self.SORT_RANK_MAX else self._sort_positions_by_merging)(blk, env, rows)
+        outs = []
+        rr = np.arange(rows[0].shape[0])[:, None]
+        for v in rows:
+            o = np.empty_like(v)
+            o[rr, pos] = v
+            outs.append(np.moveaxis(o.reshape(lead + (n,)), -1, dim))
+        return outs
+
+    def op_top_k(self, op, x, env):
+        """chlo.top_k: the k largest along the last dimension, descending, equal values by ascending position, NaN
+        after every number (src/pjrt_plugin/ops/sort_fft_complex.cc:41-88 sorts the negated values stably)."""
+        a = np.asarray(x[0])
+        k = op.result_types[0].shape[-1]
+        if a.dtype.kind == "f":
+            nan = np.isnan(a)
+            order = np.lexsort((np.where(nan, 0.0, -a.astype(np.float64)), nan), axis=-1)      # stable; NaN last
+        else:
+            order = np.argsort(~a, axis=-1, kind="stable")          # bitwise not reverses integer order without overflow
+        order = order[..., :k]
+        return [np.take_along_axis(a, order, -1), order.astype(np.int32)]
+
     def op_case(self, op, x, env):
         i = int(x[0])
         n = len(op.regions)
