@@ -275,6 +275,13 @@ class Builder:
     def cbrt(self, x): return self._unary("cbrt", x)
     def tan(self, x): return self._unary("tan", x)
 
+    def chlo_unary(self, name: str, x: Val, form: str = "op") -> Val:
+        """One of the chlo unary functions (sinh, cosh, asin, acos, atan, asinh, acosh, atanh, erf, erf_inv, tan) in the
+        form jax emits it: the chlo operation itself ("op") or a custom call to @mhlo.<name> ("custom_call"). No gradient."""
+        if form == "custom_call":
+            return self.custom_call(f"mhlo.{name}", [x], [(x.shape, x.dtype)])[0]
+        return self.emit(f"chlo.{name}", [x], [(x.shape, x.dtype)])[0]
+
     def square(self, x): return self.mul(x, x)
 
     def compare(self, a: Val, b: Val, direction: str, ctype: str | None = None) -> Val:
@@ -699,6 +706,24 @@ class Builder:
         reg = self.region(targs, comparator or default)
         return list(self.emit("stablehlo.sort", xs, [(x.shape, x.dtype) for x in xs],
                               props={"dimension": f"{dim} : i64", "is_stable": "true" if stable else "false"}, regions=[reg]))
+
+    def rng_bit_generator(self, state: Val, shape, dtype: str = "ui32", algorithm: str = "DEFAULT") -> list[Val]:
+        """stablehlo.rng_bit_generator: (new state, random bits of `shape` and integer `dtype`) from a state of two
+        (or three) 64-bit words or as many 32-bit ones, what lax.rng_bit_generator emits."""
+        return list(self.emit("stablehlo.rng_bit_generator", [state], [(state.shape, state.dtype), (tuple(shape), dtype)],
+                              props={"rng_algorithm": f"#stablehlo<rng_algorithm {algorithm}>"}))
+
+    def cholesky(self, a: Val, lower: bool = True) -> Val:
+        """stablehlo.cholesky of a batch of symmetric positive definite matrices. No gradient."""
+        return self.emit("stablehlo.cholesky", [a], [(a.shape, a.dtype)], props={"lower": "true" if lower else "false"})[0]
+
+    def triangular_solve(self, a: Val, b: Val, *, left_side: bool = True, lower: bool = True, unit_diagonal: bool = False,
+                         transpose_a: str = "NO_TRANSPOSE") -> Val:
+        """stablehlo.triangular_solve: op(a) x = b (left_side) or x op(a) = b. No gradient."""
+        tf = lambda v: "true" if v else "false"
+        return self.emit("stablehlo.triangular_solve", [a, b], [(b.shape, b.dtype)],
+                         props={"left_side": tf(left_side), "lower": tf(lower), "unit_diagonal": tf(unit_diagonal),
+                                "transpose_a": f"#stablehlo<transpose {transpose_a}>"})[0]
 
     def top_k(self, x: Val, k: int) -> list[Val]:
         """chlo.top_k: the k largest values along the last dimension in descending order and their positions (i32);

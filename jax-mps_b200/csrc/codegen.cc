@@ -88,7 +88,9 @@ static const std::map<std::string, const char*>& unary_fn() {
       {"logistic", "op_logistic"}, {"sign", "op_sign"}, {"log_plus_one", "op_log1p"},
       {"exponential_minus_one", "op_expm1"}, {"cbrt", "op_cbrt"}, {"not", "op_not"}, {"popcnt", "op_popcnt"},
       {"count_leading_zeros", "op_clz"}, {"round_nearest_even", "op_rne"}, {"round_nearest_afz", "op_rafz"},
-      {"is_finite", "op_isfinite"}, {"erf", "op_erf"}};
+      {"is_finite", "op_isfinite"}, {"erf", "op_erf"}, {"sinh", "op_sinh"}, {"cosh", "op_cosh"}, {"asin", "op_asin"},
+      {"acos", "op_acos"}, {"atan", "op_atan"}, {"asinh", "op_asinh"}, {"acosh", "op_acosh"}, {"atanh", "op_atanh"},
+      {"erf_inv", "op_erfinv"}};
   return m;
 }
 

@@ -182,6 +182,24 @@ struct Inliner {
   void process(std::unique_ptr<Op> op, Block* b) {
     for (auto& o : op->operands) o = res(o);
     std::string sh = op->short_name();
+    // A composite that names a chlo operation this compiler has itself (unary mathematics, atan2, top_k) is that
+    // operation; any other composite is its decomposition (src/pjrt_plugin/ops/control_flow.cc:2206-2250).
+    if (sh == "composite" && op->has("name")) {
+      const std::string cname = attr_str(op->attr("name"));
+      if (cname.rfind("chlo.", 0) == 0) {
+        const std::string fn = cname.substr(5);
+        const bool same = !op->results.empty() && !op->operands.empty() && op->operands[0]->type == op->results[0]->type;
+        const bool unary = op->operands.size() == 1 && op->results.size() == 1 && same && is_elementwise_op(fn) && dt_is_float(op->results[0]->type.dt);
+        const bool atan2 = fn == "atan2" && op->operands.size() == 2 && op->results.size() == 1 && same && op->operands[1]->type == op->results[0]->type;
+        const bool topk = fn == "top_k" && op->operands.size() == 1 && op->results.size() == 2;
+        if (unary || atan2 || topk) {
+          op->name = atan2 ? "stablehlo.atan2" : cname;
+          op->attrs.clear();
+          process(std::move(op), b);
+          return;
+        }
+      }
+    }
     if (op->name == "func.call" || sh == "composite") {
       std::string callee = attr_str(op->attr(sh == "composite" ? "decomposition" : "callee"));
       if (!callee.empty() && callee[0] == '@') callee = callee.substr(1);
@@ -221,6 +239,23 @@ struct Inliner {
         }
         throw CompileError("custom_call @" + tgt + " that changes the shape needs an SPMD partitioner; "
                            "compile the per-shard (manual) program instead");
+      }
+      // Unary mathematics and top-k that jax emits as custom calls (src/pjrt_plugin/ops/control_flow.cc:1440-1477): the
+      // same operations as their chlo forms.
+      if (tgt.rfind("mhlo.", 0) == 0 && op->operands.size() == 1) {
+        const std::string fn = tgt.substr(5);
+        if (op->results.size() == 1 && is_elementwise_op(fn) && op->operands[0]->type == op->results[0]->type) {
+          op->name = "chlo." + fn;
+          op->attrs.clear();
+          process(std::move(op), b);
+          return;
+        }
+        if (fn == "topk" && op->results.size() == 2) {
+          op->name = "chlo.top_k";
+          op->attrs.clear();
+          process(std::move(op), b);
+          return;
+        }
       }
     }
     // convert(convert(x, wider type), type of x) -> x when the first conversion is exact (bf16 -> f32 -> bf16 between two
@@ -899,7 +934,7 @@ struct SkinnyWeightHoist {
 // ---------------------------------------------------------------------------
 // op classification
 // ---------------------------------------------------------------------------
-enum class Cat { ELEMENTWISE, DUP, INDEXING, REDUCE, DOT, CONV, SCATTER, WINDOW, SORT, WHILE, CASE, ALL_REDUCE, ALL_GATHER, RETURN, TOKEN, PARTITION_ID, UNSUPPORTED };
+enum class Cat { ELEMENTWISE, DUP, INDEXING, REDUCE, DOT, CONV, SCATTER, WINDOW, SORT, RNG, LINALG, WHILE, CASE, ALL_REDUCE, ALL_GATHER, RETURN, TOKEN, PARTITION_ID, UNSUPPORTED };
 
 Cat categorize(Op* op) {
   const std::string sh = op->short_name();
@@ -917,6 +952,8 @@ Cat categorize(Op* op) {
   if (sh == "scatter") return Cat::SCATTER;
   if (sh == "reduce_window" || sh == "select_and_scatter") return Cat::WINDOW;
   if (sh == "sort") return Cat::SORT;
+  if (sh == "rng_bit_generator") return Cat::RNG;
+  if (sh == "cholesky" || sh == "triangular_solve") return Cat::LINALG;
   if (sh == "while") return Cat::WHILE;
   if (sh == "case") return Cat::CASE;
   if (sh == "all_reduce") return Cat::ALL_REDUCE;
@@ -1823,6 +1860,154 @@ struct Planner {
       plan.steps.push_back(std::move(s));
       from ^= 1;
     }
+  }
+
+  // stablehlo.rng_bit_generator (src/pjrt_plugin/ops/control_flow.cc:2301-2362 of the reference: bits from the
+  // library's generator keyed by the first two state words, the counter in the state advanced by one per 16 bytes of
+  // output; which algorithm the attribute names is not distinguished there, nor here). The state is 16 bytes (a 64-bit
+  // key, then a 64-bit counter) or 24 bytes (the counter 128 bits wide). The output, read as bytes, is the start of the
+  // Philox-4x32-10 stream of that key from that counter on: 16 bytes per counter value, words in little-endian order,
+  // so that consecutive calls with the returned state continue the stream without overlap. One thread per counter value.
+  void lower_rng_bit_generator(Op* op, Plan& plan, BlockState& st) {
+    if (op->operands.size() != 1 || op->results.size() != 2) throw CompileError("stablehlo.rng_bit_generator: malformed operands");
+    Value *state = op->operands[0], *out_state = op->results[0], *out = op->results[1];
+    const size_t sbytes = state->type.bytes();
+    if (!(sbytes == 16 || sbytes == 24) || !(state->type == out_state->type) || !(dt_is_unsigned(state->type.dt) || dt_is_signed(state->type.dt)))
+      throw CompileError("stablehlo.rng_bit_generator: the state must be 16 or 24 bytes of integers, got " + state->type.str());
+    if (!(dt_is_unsigned(out->type.dt) || dt_is_signed(out->type.dt)))
+      throw CompileError("stablehlo.rng_bit_generator: the output must be of an integer type, got " + out->type.str());
+    if (!slot_of.count(state)) throw CompileError("internal: state of rng_bit_generator has no storage");
+    ensure_slot(out_state, st);
+    ensure_slot(out, st);
+    const long long bytes = (long long)out->type.numel() * dt_size(out->type.dt);
+    const long long blocks = (bytes + 15) / 16;
+    std::ostringstream src;
+    src << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(" << s_type(state->type.dt) << "* __restrict__ out_state, "
+        << s_type(out->type.dt) << "* __restrict__ out, const " << s_type(state->type.dt) << "* __restrict__ state) {\n";
+    src << "  const u32* sw = (const u32*)state;\n";
+    src << "  const u32 k0 = sw[0], k1 = sw[1];\n";
+    src << "  const u64 lo64 = (u64)sw[2] | ((u64)sw[3] << 32);\n";
+    src << "  const u64 hi64 = " << (sbytes == 24 ? "(u64)sw[4] | ((u64)sw[5] << 32)" : "0") << ";\n";
+    src << "  const long long j = (long long)blockIdx.x * " << kThreads << " + threadIdx.x;\n";
+    src << "  if (j == 0) {\n    u32* ow = (u32*)out_state;\n    const u64 lo = lo64 + " << blocks << "ULL;\n";
+    src << "    ow[0] = k0; ow[1] = k1; ow[2] = (u32)lo; ow[3] = (u32)(lo >> 32);\n";
+    if (sbytes == 24) src << "    const u64 hi = hi64 + (lo < lo64 ? 1ULL : 0ULL);\n    ow[4] = (u32)hi; ow[5] = (u32)(hi >> 32);\n";
+    src << "  }\n";
+    src << "  if (j >= " << blocks << "LL) return;\n";
+    src << "  const u64 lo = lo64 + (u64)j;\n  const u64 hi = hi64 + (lo < lo64 ? 1ULL : 0ULL);\n";
+    src << "  u32 r[4];\n  philox4x32_10((u32)lo, (u32)(lo >> 32), (u32)hi, (u32)(hi >> 32), k0, k1, r);\n";
+    src << "  if ((j + 1) * 16 <= " << bytes << "LL) {\n    ((uint4*)out)[j] = make_uint4(r[0], r[1], r[2], r[3]);\n  } else {\n";
+    src << "    for (int q = 0; q < (int)(" << bytes << "LL - j * 16); ++q) ((u8*)out)[j * 16 + q] = (u8)(r[q >> 2] >> (8 * (q & 3)));\n  }\n}\n";
+    Step s;
+    s.kind = Step::KERNEL;
+    s.kernel = add_kernel(src.str(), "rng_bits");
+    s.label = op->name;
+    s.grid[0] = (unsigned)std::max<long long>(1, (blocks + kThreads - 1) / kThreads); s.grid[1] = s.grid[2] = 1;
+    s.block[0] = kThreads; s.block[1] = s.block[2] = 1;
+    s.args = {slot_of.at(out_state), slot_of.at(out), slot_of.at(state)};
+    s.n_outs = 2;
+    plan.steps.push_back(std::move(s));
+  }
+
+  // stablehlo.cholesky (src/pjrt_plugin/ops/linalg.cc:553-570 of the reference hands it to LAPACK on the host). One
+  // block per matrix factors it in place in the result, column by column: the square root of the pivot, the column
+  // scaled by it, then the trailing triangle updated with the column's outer product; every element is written by one
+  // thread per step, so the result does not depend on scheduling. Only the named triangle of the input is read; the
+  // other triangle of the result is zero. A matrix that is not positive definite gives NaN from its first bad pivot on.
+  void lower_cholesky(Op* op, Plan& plan, BlockState& st) {
+    if (op->operands.size() != 1 || op->results.size() != 1) throw CompileError("stablehlo.cholesky: malformed operands");
+    Value *a = op->operands[0], *out = op->results[0];
+    const int R = a->type.rank();
+    if (R < 2 || a->type.dims[R - 1] != a->type.dims[R - 2] || !(a->type == out->type))
+      throw CompileError("stablehlo.cholesky: the operand must be a batch of square matrices, got " + a->type.str());
+    if (!(a->type.dt == DT::F32 || a->type.dt == DT::F64)) throw CompileError("stablehlo.cholesky: element type " + a->type.str() + " is not supported (f32, f64)");
+    if (!slot_of.count(a)) throw CompileError("internal: operand of cholesky has no storage");
+    ensure_slot(out, st);
+    const int64_t n = a->type.dims[R - 1], batch = n ? a->type.numel() / (n * n) : 0;
+    if (batch == 0 || n == 0) return;
+    if (n > 46340 || batch >= (1LL << 31)) throw CompileError("stablehlo.cholesky: matrix or batch too large");
+    const bool lower = !op->has("lower") || attr_bool(op->attr("lower"));
+    const std::string T = c_type(a->type.dt);
+    const std::string at = lower ? "(i) * N + (j)" : "(j) * N + (i)";        // element (i, j) of the lower factor
+    std::ostringstream src;
+    src << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(" << signature({out}, {a}) << ") {\n";
+    src << "#define AT(i, j) (" << at << ")\n";
+    src << "  const int N = " << n << ";\n";
+    src << "  " << T << "* o = out0 + (long long)blockIdx.x * N * N;\n  const " << T << "* a = in0 + (long long)blockIdx.x * N * N;\n";
+    src << "  for (int e = threadIdx.x; e < N * N; e += " << kThreads << ") { const int i = e / N, j = e % N; o[AT(i, j)] = i >= j ? a[AT(i, j)] : (" << T << ")0; }\n";
+    src << "  __syncthreads();\n";
+    src << "  for (int j = 0; j < N; ++j) {\n";
+    src << "    if (threadIdx.x == 0) o[AT(j, j)] = op_sqrt(o[AT(j, j)]);\n    __syncthreads();\n";
+    src << "    const " << T << " d = o[AT(j, j)];\n";
+    src << "    for (int i = j + 1 + threadIdx.x; i < N; i += " << kThreads << ") o[AT(i, j)] = o[AT(i, j)] / d;\n    __syncthreads();\n";
+    src << "    const int m = N - j - 1;\n";
+    src << "    for (int e = threadIdx.x; e < m * m; e += " << kThreads << ") {\n      const int i = j + 1 + e / m, k = j + 1 + e % m;\n";
+    src << "      if (k <= i) o[AT(i, k)] = o[AT(i, k)] - o[AT(i, j)] * o[AT(k, j)];\n    }\n    __syncthreads();\n  }\n";
+    src << "#undef AT\n}\n";
+    Step s;
+    s.kind = Step::KERNEL;
+    s.kernel = add_kernel(src.str(), "cholesky");
+    s.label = op->name;
+    s.grid[0] = (unsigned)batch; s.grid[1] = s.grid[2] = 1;
+    s.block[0] = kThreads; s.block[1] = s.block[2] = 1;
+    s.args = {slot_of.at(out), slot_of.at(a)};
+    s.n_outs = 1;
+    plan.steps.push_back(std::move(s));
+  }
+
+  // stablehlo.triangular_solve (src/pjrt_plugin/ops/linalg.cc:573-660 of the reference): op(A) X = B or X op(A) = B for a
+  // batch of triangular A. One thread per right-hand-side vector (a column of B on the left side, a row on the right)
+  // substitutes forwards or backwards through its matrix, reading its earlier unknowns back from the result. As in the
+  // reference, a matrix with a zero on a diagonal that counts gives NaN for its whole solution.
+  void lower_triangular_solve(Op* op, Plan& plan, BlockState& st) {
+    if (op->operands.size() != 2 || op->results.size() != 1) throw CompileError("stablehlo.triangular_solve: malformed operands");
+    Value *a = op->operands[0], *bv = op->operands[1], *out = op->results[0];
+    const int R = a->type.rank();
+    if (R < 2 || bv->type.rank() != R || a->type.dims[R - 1] != a->type.dims[R - 2] || !(bv->type == out->type) || a->type.dt != bv->type.dt)
+      throw CompileError("stablehlo.triangular_solve: malformed operand types " + a->type.str() + ", " + bv->type.str());
+    if (!(a->type.dt == DT::F32 || a->type.dt == DT::F64)) throw CompileError("stablehlo.triangular_solve: element type " + a->type.str() + " is not supported (f32, f64)");
+    for (int d = 0; d < R - 2; d++) if (a->type.dims[d] != bv->type.dims[d]) throw CompileError("stablehlo.triangular_solve: batch dimensions differ");
+    if (!slot_of.count(a) || !slot_of.count(bv)) throw CompileError("internal: operand of triangular_solve has no storage");
+    ensure_slot(out, st);
+    const bool left = !op->has("left_side") || attr_bool(op->attr("left_side"));
+    const bool lower = !op->has("lower") || attr_bool(op->attr("lower"));
+    const bool unit = op->has("unit_diagonal") && attr_bool(op->attr("unit_diagonal"));
+    const std::string tr = op->has("transpose_a") ? attr_enum(op->attr("transpose_a")) : "NO_TRANSPOSE";
+    const bool transposed = tr == "TRANSPOSE" || tr == "ADJOINT";
+    const int64_t n = a->type.dims[R - 1], rows = bv->type.dims[R - 2], cols = bv->type.dims[R - 1];
+    if ((left ? rows : cols) != n) throw CompileError("stablehlo.triangular_solve: B does not match A");
+    const int64_t total = bv->type.numel();
+    if (total == 0) return;
+    const int64_t vecs_per = left ? cols : rows, batch = total / (rows * cols);
+    const bool flip = transposed != !left;                 // the matrix the substitution walks is A transposed
+    const bool fwd = lower != flip;                        // ... and it is lower triangular: substitute forwards
+    const std::string T = c_type(a->type.dt);
+    std::ostringstream src;
+    src << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(" << signature({out}, {a, bv}) << ") {\n";
+    src << "  const long long t = (long long)blockIdx.x * " << kThreads << " + threadIdx.x;\n";
+    src << "  if (t >= " << batch * vecs_per << "LL) return;\n";
+    src << "  const int N = " << n << ";\n";
+    src << "  const long long g = t / " << vecs_per << "LL, v = t % " << vecs_per << "LL;\n";
+    src << "  const " << T << "* A = in0 + g * N * N;\n";
+    src << "#define M(i, j) A[" << (flip ? "(long long)(j) * N + (i)" : "(long long)(i) * N + (j)") << "]\n";
+    src << "#define X(i) (g * " << rows * cols << "LL + " << (left ? "(long long)(i) * " + std::to_string(cols) + " + v" : "v * " + std::to_string(cols) + " + (i)") << ")\n";
+    src << "  bool singular = false;\n";
+    if (!unit) src << "  for (int i = 0; i < N; ++i) singular = singular || A[(long long)i * N + i] == (" << T << ")0;\n";
+    src << "  for (int q = 0; q < N; ++q) {\n    const int i = " << (fwd ? "q" : "N - 1 - q") << ";\n";
+    src << "    " << T << " acc = in1[X(i)];\n";
+    src << "    for (int j = " << (fwd ? "0; j < i" : "i + 1; j < N") << "; ++j) acc = acc - M(i, j) * out0[X(j)];\n";
+    src << "    out0[X(i)] = " << (unit ? "acc" : "acc / M(i, i)") << ";\n  }\n";
+    src << "  if (singular) for (int i = 0; i < N; ++i) out0[X(i)] = (" << T << ")__uint_as_float(0x7FC00000u);\n";
+    src << "#undef M\n#undef X\n}\n";
+    Step s;
+    s.kind = Step::KERNEL;
+    s.kernel = add_kernel(src.str(), "triangular_solve");
+    s.label = op->name;
+    s.grid[0] = (unsigned)((batch * vecs_per + kThreads - 1) / kThreads); s.grid[1] = s.grid[2] = 1;
+    s.block[0] = kThreads; s.block[1] = s.block[2] = 1;
+    s.args = {slot_of.at(out), slot_of.at(a), slot_of.at(bv)};
+    s.n_outs = 1;
+    plan.steps.push_back(std::move(s));
   }
 
   // dynamic_update_slice of a loop-carried tensor written back to the same position of the loop state: the result
@@ -3924,6 +4109,15 @@ struct Planner {
         }
         case Cat::SORT: {
           lower_sort(op, plan, st);
+          break;
+        }
+        case Cat::RNG: {
+          lower_rng_bit_generator(op, plan, st);
+          break;
+        }
+        case Cat::LINALG: {
+          if (op->short_name() == "cholesky") lower_cholesky(op, plan, st);
+          else lower_triangular_solve(op, plan, st);
           break;
         }
         case Cat::TOKEN: {

@@ -153,6 +153,8 @@ _UNARY = {
     "log_plus_one": np.log1p, "exponential_minus_one": np.expm1, "cbrt": np.cbrt,
     "round_nearest_even": np.rint, "round_nearest_afz": _round_afz, "popcnt": _popcnt,
     "count_leading_zeros": _clz,
+    "sinh": np.sinh, "cosh": np.cosh, "asin": np.arcsin, "acos": np.arccos, "atan": np.arctan, "asinh": np.arcsinh,
+    "acosh": np.arccosh, "atanh": np.arctanh,
 }
 _BINARY_F = {
     "add": np.add, "subtract": np.subtract, "multiply": np.multiply, "divide": np.divide,
@@ -319,6 +321,10 @@ class Interp:
         if eb == 5 and mb == 10:
             return [a.astype(np.float16).astype(np.float32)]
         raise NotImplementedError("reduce_precision format")
+
+    def op_erf_inv(self, op, x, env):
+        from scipy.special import erfinv
+        return [erfinv(x[0].astype(np.float64))]
 
     def op_erf(self, op, x, env):
         from scipy.special import erf
@@ -730,6 +736,93 @@ class Interp:
                 raise RuntimeError("oracle while: iteration limit")
         return cur
 
+    # ---- dense linear algebra --------------------------------------------------------------------------
+    def op_cholesky(self, op, x, env):
+        """stablehlo.cholesky through LAPACK in float64, as the reference runs it on the host
+        (src/pjrt_plugin/ops/linalg.cc:553-570); only the named triangle is read, the other triangle of the result is
+        zero, a matrix that is not positive definite gives NaN."""
+        a = np.asarray(x[0], np.float64)
+        lower = mt.attr_bool(op.attrs["lower"]) if "lower" in op.attrs else True
+        n = a.shape[-1]
+        flat = a.reshape(-1, n, n)
+        out = np.empty_like(flat)
+        for g, m in enumerate(flat):
+            tri = np.tril(m) if lower else np.triu(m).T
+            sym = tri + np.tril(tri, -1).T
+            try:
+                l = np.linalg.cholesky(sym)
+            except np.linalg.LinAlgError:
+                l = np.full((n, n), np.nan)
+            out[g] = l if lower else l.T
+        return [out.reshape(a.shape)]
+
+    def op_triangular_solve(self, op, x, env):
+        """stablehlo.triangular_solve by substitution in float64 (scipy.linalg.solve_triangular); a matrix with a zero on
+        a diagonal that counts gives NaN for its whole solution (src/pjrt_plugin/ops/linalg.cc:596-628)."""
+        from scipy.linalg import solve_triangular
+        a, b = np.asarray(x[0], np.float64), np.asarray(x[1], np.float64)
+        flag = lambda k, d: mt.attr_bool(op.attrs[k]) if k in op.attrs else d
+        left, lower, unit = flag("left_side", True), flag("lower", True), flag("unit_diagonal", False)
+        trans = enum_word(op.attrs["transpose_a"]) in ("TRANSPOSE", "ADJOINT") if "transpose_a" in op.attrs else False
+        n = a.shape[-1]
+        fa, fb = a.reshape(-1, n, n), b.reshape((-1,) + b.shape[-2:])
+        out = np.empty_like(fb)
+        for g in range(fa.shape[0]):
+            m = np.tril(fa[g]) if lower else np.triu(fa[g])
+            if not unit and np.any(np.diagonal(m) == 0):
+                out[g] = np.nan
+                continue
+            with np.errstate(all="ignore"):
+                if left:
+                    out[g] = solve_triangular(m, fb[g], lower=lower, trans=1 if trans else 0, unit_diagonal=unit, check_finite=False)
+                else:       # X op(A) = B  <=>  op(A)^T X^T = B^T
+                    out[g] = solve_triangular(m, fb[g].T, lower=lower, trans=0 if trans else 1, unit_diagonal=unit, check_finite=False).T
+        return [out.reshape(b.shape)]
+
+    # ---- random bits -----------------------------------------------------------------------------------
+    @staticmethod
+    def philox4x32_10(ctr, key):
+        """Philox-4x32 with ten rounds (Salmon, Moraes, Dror, Shaw, SC 2011) on arrays of 32-bit words held in uint64:
+        ctr = four arrays, key = two scalars; returns the four output words."""
+        mask = np.uint64(0xFFFFFFFF)
+        c = [np.asarray(v, np.uint64) for v in ctr]
+        k = [np.uint64(key[0]), np.uint64(key[1])]
+        for _ in range(10):
+            p0 = np.uint64(0xD2511F53) * c[0]
+            p1 = np.uint64(0xCD9E8D57) * c[2]
+            c = [(p1 >> np.uint64(32)) ^ c[1] ^ k[0], p1 & mask, (p0 >> np.uint64(32)) ^ c[3] ^ k[1], p0 & mask]
+            k = [(k[0] + np.uint64(0x9E3779B9)) & mask, (k[1] + np.uint64(0xBB67AE85)) & mask]
+        return c
+
+    def op_rng_bit_generator(self, op, x, env):
+        """stablehlo.rng_bit_generator: the state is a 64-bit key and a 64- or 128-bit counter; the output bytes are the
+        Philox-4x32-10 stream of the key from the counter on, 16 bytes per counter value, and the returned counter has
+        advanced by one per 16 bytes (src/pjrt_plugin/ops/control_flow.cc:2346-2356 advances it the same way; the bits
+        themselves differ between backends there too)."""
+        state = np.ascontiguousarray(x[0])
+        words = state.view(np.uint32).reshape(-1).astype(np.uint64)
+        if words.size not in (4, 6):
+            raise ValueError("rng_bit_generator: the state must be 16 or 24 bytes")
+        ot = op.result_types[1]
+        dt = np.dtype(mt.np_dtype(ot.dtype))
+        nbytes = int(np.prod(ot.shape, dtype=np.int64)) * dt.itemsize
+        blocks = (nbytes + 15) // 16
+        lo64 = int(words[2]) | int(words[3]) << 32
+        hi64 = (int(words[4]) | int(words[5]) << 32) if words.size == 6 else 0
+        j = np.arange(blocks, dtype=np.uint64)
+        with np.errstate(over="ignore"):
+            lo = np.uint64(lo64) + j
+        hi = (np.uint64(hi64) + (lo < np.uint64(lo64)).astype(np.uint64)) if blocks else np.zeros(0, np.uint64)
+        mask = np.uint64(0xFFFFFFFF)
+        r = self.philox4x32_10([lo & mask, lo >> np.uint64(32), hi & mask, hi >> np.uint64(32)], (words[0], words[1]))
+        stream = np.stack([v.astype(np.uint32) for v in r], axis=-1).reshape(-1)
+        out = stream.view(np.uint8)[:nbytes].copy().view(dt).reshape(ot.shape)
+        nlo = (lo64 + blocks) & ((1 << 64) - 1)
+        nhi = (hi64 + (1 if nlo < lo64 else 0)) & ((1 << 64) - 1)
+        nw = [int(words[0]), int(words[1]), nlo & 0xFFFFFFFF, nlo >> 32] + ([nhi & 0xFFFFFFFF, nhi >> 32] if words.size == 6 else [])
+        new_state = np.array(nw, np.uint32).view(state.dtype).reshape(state.shape)
+        return [new_state, out]
+
     # ---- sorting ---------------------------------------------------------------------------------------
     SORT_RANK_MAX = 2048                    # rows up to this length are sorted by the all-pairs definition
 
@@ -859,6 +952,15 @@ class Interp:
         tgt = mt.attr_str(op.attrs["call_target_name"])
         if tgt in ("Sharding", "SPMDFullToShardShape", "SPMDShardToFullShape"):
             return [x[0].reshape(op.result_types[0].shape)]         # control_flow.cc:1426-1438
+        if tgt.startswith("mhlo.") and len(x) == 1:             # control_flow.cc:1440-1477: the chlo operation of that name
+            fn = tgt[5:]
+            if fn == "topk":
+                return self.op_top_k(op, x, env)
+            if fn in _UNARY:
+                with np.errstate(all="ignore"):
+                    return [_UNARY[fn](x[0].astype(np.float64))]
+            if hasattr(self, "op_" + fn):
+                return getattr(self, "op_" + fn)(op, x, env)
         raise NotImplementedError(f"oracle: custom_call {tgt}")
 
     # ---- collectives ---------------------------------------------------------------------------------

@@ -41,6 +41,41 @@ def test_unary_float(client, name):
     check(client, b.module([y]), [a], rtol=2e-5, atol=1e-5)
 
 
+CHLO_UNARY = {"sinh": (-4, 4), "cosh": (-4, 4), "asin": (-1, 1), "acos": (-1, 1), "atan": (-8, 8), "asinh": (-8, 8), "acosh": (1, 8),
+              "atanh": (-0.99, 0.99), "erf": (-3, 3), "erf_inv": (-0.999, 0.999), "tan": (-1.4, 1.4)}
+
+
+@pytest.mark.parametrize("form", ["op", "custom_call"])
+@pytest.mark.parametrize("name", sorted(CHLO_UNARY))
+def test_chlo_unary(client, name, form):
+    """The functions jax emits as chlo operations, as custom calls to @mhlo.<name> or as composites
+    (src/pjrt_plugin/ops/control_flow.cc:53-66 of the reference lists them)."""
+    lo, hi = CHLO_UNARY[name]
+    b = Builder()
+    x = b.arg((17, 33), "f32")
+    check(client, b.module([b.chlo_unary(name, x, form)]), [f32(17, 33, lo=lo, hi=hi)], rtol=3e-5, atol=1e-5)
+
+
+def test_chlo_composite_runs_as_the_named_operation(client):
+    """A composite named after a chlo function is that function, whatever its decomposition says (here: a wrong one),
+    as in the reference (src/pjrt_plugin/ops/control_flow.cc:2206-2222)."""
+    text = """
+module @test {
+  func.func private @chlo.asin.impl(%arg0: tensor<4xf32>) -> tensor<4xf32> {
+    %0 = stablehlo.negate %arg0 : tensor<4xf32>
+    return %0 : tensor<4xf32>
+  }
+  func.func @main(%arg0: tensor<4xf32>) -> tensor<4xf32> {
+    %0 = stablehlo.composite "chlo.asin" %arg0 {decomposition = @chlo.asin.impl} : (tensor<4xf32>) -> tensor<4xf32>
+    return %0 : tensor<4xf32>
+  }
+}
+"""
+    x = np.array([0.0, 0.5, -0.5, 0.9], np.float32)
+    got, _ = run_gpu(client, text, [x])
+    np.testing.assert_allclose(got[0], np.arcsin(x), rtol=1e-5, atol=1e-5)
+
+
 @pytest.mark.parametrize("name", ["add", "sub", "mul", "div", "max", "min", "pow", "rem", "atan2"])
 def test_binary_float(client, name):
     b = Builder()
