@@ -932,13 +932,237 @@ struct SkinnyWeightHoist {
 };
 
 // ---------------------------------------------------------------------------
+// Attention over a cache for a handful of queries (a decode step): dot_general(Q, K) -> pointwise (scale, mask) ->
+// softmax over the positions -> dot_general(P, V) becomes one operation, `b200.decode_attention`, that keeps the
+// pointwise part as a region and is lowered to one kernel (Planner::lower_decode_attention). The reference matches the
+// same chain into its fused attention call (src/pjrt_plugin/ops/control_flow.cc:1484-1533 runs it; the matcher is on
+// the Python side). Left as it is: anything with more than eight query rows per key / value group, other layouts than
+// row-major [groups,] rows x features operands, or intermediate values that something else reads.
+// ---------------------------------------------------------------------------
+struct DecodeAttentionFusion {
+  Module& m;
+  explicit DecodeAttentionFusion(Module& mod) : m(mod) {}
+  std::map<Value*, int> uses;
+
+  void count(Block* b) {
+    for (auto& op : b->ops) {
+      for (Value* o : op->operands) uses[o]++;
+      for (auto& r : op->regions) count(r.get());
+    }
+  }
+  void run(Block* b) {
+    if (getenv("B200_NO_ATTENTION_FUSION")) return;
+    uses.clear();
+    count(b);
+    fuse_in(b);
+  }
+  void fuse_in(Block* b) {
+    for (auto& op : b->ops)
+      for (auto& r : op->regions) fuse_in(r.get());
+    for (size_t i = 0; i < b->ops.size(); i++)
+      if (b->ops[i]->short_name() == "dot_general" && try_fuse(b, b->ops[i].get())) i = (size_t)-1;     // positions changed: start over
+  }
+
+  static Op* def_in(Value* v, Block* b, const char* short_name) {
+    return v->def && v->def->parent == b && v->def->short_name() == short_name ? v->def : nullptr;
+  }
+  static bool splat_is(Value* v, double want) {
+    Op* d = v->def;
+    if (!d || d->short_name() != "constant") return false;
+    DenseValue dv = attr_dense(d->attr("value"));
+    if (!dv.splat && dv.type.numel() != 1) return false;
+    if (dv.type.dt != DT::F32) return false;
+    float f;
+    memcpy(&f, dv.data.data(), 4);
+    return (double)f == want;
+  }
+  // reduce over the last dimension with a one-operation body
+  static bool last_dim_reduce(Op* r, const char* body_op) {
+    if (!r || r->operands.size() != 2 || r->results.size() != 1 || r->regions.size() != 1) return false;
+    const int rank = r->operands[0]->type.rank();
+    auto dims = attr_i64s(r->attr("dimensions"));
+    if (dims.size() != 1 || dims[0] != rank - 1) return false;
+    Block* body = r->regions[0].get();
+    if (body->ops.size() != 2 || body->args.size() != 2 || body->ops[0]->short_name() != body_op) return false;
+    Op* c = body->ops[0].get();
+    const bool uses_args = (c->operands[0] == body->args[0] && c->operands[1] == body->args[1]) ||
+                           (c->operands[0] == body->args[1] && c->operands[1] == body->args[0]);
+    return uses_args && body->ops[1]->operands.size() == 1 && body->ops[1]->operands[0] == c->results[0];
+  }
+  static bool leading_broadcast(Op* bc, int rank) {
+    if (!bc || bc->operands[0]->type.rank() != rank - 1 || bc->results[0]->type.rank() != rank) return false;
+    auto dims = attr_i64s(bc->attr("broadcast_dimensions"));
+    if ((int)dims.size() != rank - 1) return false;
+    for (int k = 0; k < rank - 1; k++) if (dims[k] != k) return false;
+    return true;
+  }
+  // [G,] rows x cols operands contracted as dims say: batch = leading dimension (or none), contraction lc / rc
+  static bool dot_form(Op* d, int lc, int rc) {
+    if (d->operands.size() != 2 || d->results.size() != 1 || !d->has("dot_dimension_numbers")) return false;
+    const int rank = d->operands[0]->type.rank();
+    if (!(rank == 2 || rank == 3) || d->operands[1]->type.rank() != rank || d->results[0]->type.rank() != rank) return false;
+    auto f = attr_struct(d->attr("dot_dimension_numbers"));
+    const auto lb = f["lhs_batching_dimensions"], rb = f["rhs_batching_dimensions"];
+    const auto lcd = f["lhs_contracting_dimensions"], rcd = f["rhs_contracting_dimensions"];
+    if (rank == 2 ? !(lb.empty() && rb.empty()) : !(lb == std::vector<int64_t>{0} && rb == std::vector<int64_t>{0})) return false;
+    return lcd == std::vector<int64_t>{(int64_t)(rank - 2 + lc)} && rcd == std::vector<int64_t>{(int64_t)(rank - 2 + rc)};
+  }
+
+  bool try_fuse(Block* b, Op* pv) {
+    // ---- from the second product backwards through the softmax
+    if (!dot_form(pv, 1, 0)) return false;
+    Value* pin = pv->operands[0];
+    Value* V = pv->operands[1];
+    const int rank = pin->type.rank();
+    Op* cvt = def_in(pin, b, "convert");
+    Value* P = cvt ? cvt->operands[0] : pin;
+    if (cvt && uses[pin] != 1) return false;
+    Op* div = def_in(P, b, "divide");
+    if (!div || uses[P] != 1 || P->type.dt != DT::F32) return false;
+    Value* e = div->operands[0];
+    Op* bs = def_in(div->operands[1], b, "broadcast_in_dim");
+    if (!bs || uses[bs->results[0]] != 1 || !leading_broadcast(bs, rank)) return false;
+    Op* sum = def_in(bs->operands[0], b, "reduce");
+    if (!sum || uses[sum->results[0]] != 1 || !last_dim_reduce(sum, "add") || sum->operands[0] != e || !splat_is(sum->operands[1], 0.0)) return false;
+    Op* ex = def_in(e, b, "exponential");
+    if (!ex || uses[e] != 2) return false;
+    Op* sub = def_in(ex->operands[0], b, "subtract");
+    if (!sub || uses[sub->results[0]] != 1) return false;
+    Value* Sp = sub->operands[0];
+    Op* bm = def_in(sub->operands[1], b, "broadcast_in_dim");
+    if (!bm || uses[bm->results[0]] != 1 || !leading_broadcast(bm, rank)) return false;
+    Op* mx = def_in(bm->operands[0], b, "reduce");
+    if (!mx || uses[mx->results[0]] != 1 || !last_dim_reduce(mx, "maximum") || mx->operands[0] != Sp ||
+        !splat_is(mx->operands[1], -std::numeric_limits<double>::infinity()))
+      return false;
+    if (uses[Sp] != 2 || Sp->type.dt != DT::F32 || Sp->type.dims != P->type.dims) return false;
+    // ---- the pointwise part between the first product and the softmax
+    std::set<Op*> seen, dots;
+    std::vector<Op*> stack;
+    if (Sp->def && Sp->def->parent == b) stack.push_back(Sp->def);
+    while (!stack.empty()) {
+      Op* o = stack.back();
+      stack.pop_back();
+      if (!seen.insert(o).second) continue;
+      if (o->short_name() == "dot_general") { dots.insert(o); continue; }
+      if (!is_elementwise_op(o->short_name()) || o->results.size() != 1) continue;
+      for (Value* x : o->operands) if (x->def && x->def->parent == b) stack.push_back(x->def);
+    }
+    if (dots.size() != 1) return false;
+    Op* qk = *dots.begin();
+    if (!dot_form(qk, 1, 1)) return false;
+    Value *Q = qk->operands[0], *K = qk->operands[1], *S = qk->results[0];
+    if (uses[S] != 1 || S->type.dims != Sp->type.dims) return false;
+    const DT dt = Q->type.dt;
+    if (!(dt == DT::BF16 || dt == DT::F16) || K->type.dt != dt || V->type.dt != dt || pin->type.dt != dt) return false;
+    if (!(S->type.dt == dt || S->type.dt == DT::F32)) return false;
+    const DT odt = pv->results[0]->type.dt;
+    if (!(odt == dt || odt == DT::F32)) return false;
+    const int64_t M = Q->type.dims[rank - 2], D = Q->type.dims[rank - 1], T = K->type.dims[rank - 2], N = V->type.dims[rank - 1];
+    const int64_t G = rank == 3 ? Q->type.dims[0] : 1;
+    if (M < 1 || M > 8 || D % 8 || N % 8 || D < 8 || N < 8 || D > 256 || N > 256 || T < 1 || T >= (1 << 24) || G < 1 || G > 65535) return false;
+    if (V->type.dims[rank - 2] != T || K->type.dims[rank - 1] != D) return false;
+    if (rank == 3 && (K->type.dims[0] != G || V->type.dims[0] != G)) return false;
+    // the operations that depend on S, in block order; nothing outside them may read their results
+    std::set<Op*> moved;
+    std::function<bool(Op*)> depends = [&](Op* o) -> bool {
+      if (o == qk) return true;
+      if (!seen.count(o) || o->short_name() == "dot_general" || !is_elementwise_op(o->short_name())) return false;
+      bool any = false;
+      for (Value* x : o->operands) if (x->def && x->def->parent == b && depends(x->def)) any = true;
+      if (any) moved.insert(o);
+      return any;
+    };
+    if (!Sp->def || !depends(Sp->def)) return false;
+    for (Op* o : moved) {
+      if (o->results[0] == Sp) continue;
+      int inside = 0;
+      for (Op* u : moved) for (Value* x : u->operands) if (x == o->results[0]) inside++;
+      if (inside != uses[o->results[0]]) return false;
+    }
+    // operand subtrees of pointwise and duplicable operations that only the moved operations read move along, so
+    // that the mask of a step is computed inside the kernel instead of by a launch of its own
+    bool grew = true;
+    while (grew) {
+      grew = false;
+      for (Op* o : std::vector<Op*>(moved.begin(), moved.end()))
+        for (Value* x : o->operands) {
+          Op* d = x->def;
+          if (!d || d->parent != b || moved.count(d) || d == qk || d->results.size() != 1) continue;
+          const std::string sh = d->short_name();
+          if (!(is_elementwise_op(sh) || sh == "constant" || sh == "iota" || sh == "broadcast_in_dim")) continue;
+          int inside = 0;
+          for (Op* u : moved) for (Value* y : u->operands) if (y == x) inside++;
+          if (inside != uses[x]) continue;
+          moved.insert(d);
+          grew = true;
+        }
+    }
+    // ---- build the fused operation in place of the second product
+    auto fused = std::make_unique<Op>();
+    fused->name = "b200.decode_attention";
+    fused->operands = {Q, K, V};
+    fused->parent = b;
+    fused->attrs["label"] = "\"attention M=" + std::to_string(M) + " T=" + std::to_string(T) + " D=" + std::to_string(D) + " N=" + std::to_string(N) + "\"";
+    Value* out = pv->results[0];
+    out->def = fused.get();
+    out->def_index = 0;
+    fused->results.push_back(out);
+    auto body = std::make_unique<Block>();
+    body->parent_op = fused.get();
+    Value* sarg = m.new_value(S->type, "%scores");
+    sarg->owner = body.get();
+    sarg->arg_index = 0;
+    body->args.push_back(sarg);
+    std::set<Op*> gone = {qk, pv, div, bs, sum, ex, sub, bm, mx};
+    if (cvt) gone.insert(cvt);
+    std::vector<std::unique_ptr<Op>> kept;
+    std::unique_ptr<Op> fused_holder = std::move(fused);
+    for (auto& up : b->ops) {
+      Op* o = up.get();
+      if (o == pv) {
+        Op* f = fused_holder.get();
+        // finish the region before the operation takes the product's place
+        auto ret = std::make_unique<Op>();
+        ret->name = "stablehlo.return";
+        ret->operands = {Sp};
+        ret->parent = body.get();
+        body->ops.push_back(std::move(ret));
+        f->regions.push_back(std::move(body));
+        kept.push_back(std::move(fused_holder));
+        continue;
+      }
+      if (moved.count(o)) {
+        for (auto& x : o->operands) if (x == S) x = sarg;
+        o->parent = body.get();
+        body->ops.push_back(std::move(up));
+        continue;
+      }
+      if (gone.count(o)) {
+        // reduce initial values and the like stay where they are; dead code elimination drops what nothing reads
+        for (Value* r : o->results) if (r->def == o) r->def = nullptr;
+        continue;
+      }
+      kept.push_back(std::move(up));
+    }
+    b->ops = std::move(kept);
+    uses.clear();
+    Block* top = b;
+    while (top->parent_op && top->parent_op->parent) top = top->parent_op->parent;
+    count(top);
+    return true;
+  }
+};
+
+// ---------------------------------------------------------------------------
 // op classification
 // ---------------------------------------------------------------------------
-enum class Cat { ELEMENTWISE, DUP, INDEXING, REDUCE, DOT, CONV, SCATTER, WINDOW, SORT, RNG, LINALG, WHILE, CASE, ALL_REDUCE, ALL_GATHER, RETURN, TOKEN, PARTITION_ID, UNSUPPORTED };
+enum class Cat { ELEMENTWISE, DUP, INDEXING, REDUCE, DOT, CONV, SCATTER, WINDOW, SORT, RNG, LINALG, ATTENTION, WHILE, CASE, ALL_REDUCE, ALL_GATHER, RETURN, TOKEN, PARTITION_ID, UNSUPPORTED };
 
 Cat categorize(Op* op) {
   const std::string sh = op->short_name();
   if (sh == "return") return Cat::RETURN;
+  if (op->name == "b200.decode_attention") return Cat::ATTENTION;
   if (op->name.rfind("stablehlo.", 0) != 0 && op->name.rfind("chlo.", 0) != 0 && op->name.rfind("mhlo.", 0) != 0)
     return Cat::UNSUPPORTED;
   if (is_elementwise_op(sh)) return Cat::ELEMENTWISE;
@@ -1906,6 +2130,141 @@ struct Planner {
     s.block[0] = kThreads; s.block[1] = s.block[2] = 1;
     s.args = {slot_of.at(out_state), slot_of.at(out), slot_of.at(state)};
     s.n_outs = 2;
+    plan.steps.push_back(std::move(s));
+  }
+
+  // b200.decode_attention (DecodeAttentionFusion): attention of M <= 8 query rows per group over T cached positions in
+  // one kernel. A block takes 32 positions of one group: it stages their K and V rows and the queries in shared
+  // memory, its warps form the scores (rounded like the product they replace), the region's pointwise code (scale,
+  // mask) runs on each score, a warp per query row takes the chunk's maximum and exponentials and multiplies them into
+  // its part of the V rows. With more than one chunk, the chunk's unnormalised result, maximum and sum go to scratch,
+  // and the last block of the group to arrive (a counter that it sets back to zero) rescales and adds the chunks in
+  // chunk order and divides by the total. Unlike the chain it replaces, the probabilities are not rounded to 16 bits
+  // on their way into the second product.
+  void lower_decode_attention(Op* op, Plan& plan, BlockState& st) {
+    Value *Q = op->operands[0], *K = op->operands[1], *V = op->operands[2], *out = op->results[0];
+    Block* body = op->regions[0].get();
+    Value* sarg = body->args[0];
+    Value* Sp = body->ops.back()->operands[0];
+    const int rank = Q->type.rank();
+    const long long M = Q->type.dims[rank - 2], D = Q->type.dims[rank - 1], T = K->type.dims[rank - 2], N = V->type.dims[rank - 1];
+    const long long G = rank == 3 ? Q->type.dims[0] : 1;
+    const int TC = 32;
+    const long long CH = (T + TC - 1) / TC, D8 = D / 8, N8 = N / 8, PS = N + 4;
+    for (Value* v : {Q, K, V})
+      if (!slot_of.count(v)) throw CompileError("internal: operand of decode_attention has no storage");
+    ensure_slot(out, st);
+    std::set<Op*> inside;
+    for (auto& o : body->ops) inside.insert(o.get());
+    Emitter em;
+    em.is_internal = [&](Op* o) { return inside.count(o) || (is_dup(o) && !st.dup_materialize.count(o) && !slot_of.count(o->results[0])); };
+    std::vector<Value*> all{Sp};
+    for (auto& o : body->ops) for (Value* x : o->operands) all.push_back(x);
+    em.idx_t = idx_type_for(all, G * M * T + 1024);
+    em.indent_ = 6;
+    em.bound[sarg] = "sval";
+    Ctx root;
+    root.shape = Sp->type.dims;
+    root.lin = "lin";
+    em.ensure_idx(root);
+    const std::string rexpr = em.emit(Sp, root);
+    for (Value* v : em.inputs)
+      if (!slot_of.count(v)) throw CompileError("internal: value read by the attention region has no storage: " + v->name);
+    const bool bf = Q->type.dt == DT::BF16;
+    const std::string H2F = bf ? "bf16_to_f" : "f16_to_f";
+    const std::string round_s = sarg->type.dt == DT::F32 ? "mine" : (bf ? "rbf16(mine)" : "rf16(mine)");
+    const std::string I = em.idx_t;
+    auto unpack = [&](const std::string& vec, const std::string& arr) {
+      std::string o;
+      const char* comp[4] = {"x", "y", "z", "w"};
+      for (int q = 0; q < 4; q++) {
+        o += "        " + arr + "[" + std::to_string(2 * q) + "] = " + H2F + "((u16)(" + vec + "." + comp[q] + " & 0xFFFFu));\n";
+        o += "        " + arr + "[" + std::to_string(2 * q + 1) + "] = " + H2F + "((u16)(" + vec + "." + comp[q] + " >> 16));\n";
+      }
+      return o;
+    };
+    std::ostringstream src;
+    src << "extern \"C\" __global__ void __launch_bounds__(256) @NAME@(" << s_type(out->type.dt) << "* __restrict__ out0, float* __restrict__ part, "
+        << "int* __restrict__ cnt, const u16* __restrict__ qp, const u16* __restrict__ kp, const u16* __restrict__ vp";
+    if (!em.inputs.empty()) src << ", " << signature({}, em.inputs);
+    src << ") {\n";
+    src << "  __shared__ __align__(16) u16 ks[" << TC * D << "];\n  __shared__ __align__(16) u16 vs[" << TC * N << "];\n";
+    src << "  __shared__ __align__(16) float qs[" << M * D << "];\n  __shared__ float sc[" << M * TC << "];\n  __shared__ int last_flag;\n";
+    src << "  const int c = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;\n";
+    src << "  const int t0 = c * " << TC << ";\n  const int nt = " << T << " - t0 < " << TC << " ? " << T << " - t0 : " << TC << ";\n";
+    src << "  const float NEG_INF = __uint_as_float(0xFF800000u);\n";
+    src << "  {\n    const uint4* ksrc = (const uint4*)(kp + ((long long)g * " << T << " + t0) * " << D << ");\n";
+    src << "    for (int i = tid; i < nt * " << D8 << "; i += 256) ((uint4*)ks)[i] = ksrc[i];\n";
+    src << "    const uint4* vsrc = (const uint4*)(vp + ((long long)g * " << T << " + t0) * " << N << ");\n";
+    src << "    for (int i = tid; i < nt * " << N8 << "; i += 256) ((uint4*)vs)[i] = vsrc[i];\n";
+    src << "    for (int i = tid; i < " << M * D << "; i += 256) qs[i] = " << H2F << "(qp[(long long)g * " << M * D << " + i]);\n  }\n";
+    src << "  __syncthreads();\n";
+    // scores
+    src << "  for (int tl = warp; tl < nt; tl += 8) {\n    float acc[" << M << "];\n";
+    src << "#pragma unroll\n    for (int m = 0; m < " << M << "; ++m) acc[m] = 0.f;\n";
+    src << "    for (int p = lane; p < " << D8 << "; p += 32) {\n      const uint4 kk = ((const uint4*)ks)[tl * " << D8 << " + p];\n      float kf[8];\n";
+    src << unpack("kk", "kf");
+    src << "#pragma unroll\n      for (int m = 0; m < " << M << "; ++m) {\n        const float4 qa = *(const float4*)(qs + m * " << D << " + p * 8), qb = *(const float4*)(qs + m * " << D << " + p * 8 + 4);\n";
+    src << "        acc[m] = fmaf(kf[0], qa.x, acc[m]); acc[m] = fmaf(kf[1], qa.y, acc[m]); acc[m] = fmaf(kf[2], qa.z, acc[m]); acc[m] = fmaf(kf[3], qa.w, acc[m]);\n";
+    src << "        acc[m] = fmaf(kf[4], qb.x, acc[m]); acc[m] = fmaf(kf[5], qb.y, acc[m]); acc[m] = fmaf(kf[6], qb.z, acc[m]); acc[m] = fmaf(kf[7], qb.w, acc[m]);\n      }\n    }\n";
+    src << "    float mine = 0.f;\n#pragma unroll\n    for (int m = 0; m < " << M << "; ++m) {\n      float r = acc[m];\n";
+    src << "#pragma unroll\n      for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xFFFFFFFFu, r, o);\n      if (lane == m) mine = r;\n    }\n";
+    src << "    if (lane < " << M << ") {\n      const float sval = " << round_s << ";\n";
+    src << "      const " << I << " lin = ((" << I << ")g * " << M << " + lane) * " << T << " + t0 + tl;\n";
+    src << em.str();
+    src << "      sc[lane * " << TC << " + tl] = " << rexpr << ";\n    }\n  }\n  __syncthreads();\n";
+    // softmax of the chunk and the second product, a warp per query row
+    src << "  if (warp < " << M << ") {\n    const int mrow = warp;\n    float mx = NEG_INF;\n";
+    src << "    for (int tl = lane; tl < nt; tl += 32) mx = fmaxf(mx, sc[mrow * " << TC << " + tl]);\n";
+    src << "#pragma unroll\n    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));\n";
+    src << "    const float mref = mx == NEG_INF ? 0.f : mx;\n    float sum = 0.f;\n";
+    src << "    for (int tl = lane; tl < nt; tl += 32) { const float pz = expf(sc[mrow * " << TC << " + tl] - mref); sc[mrow * " << TC << " + tl] = pz; sum += pz; }\n";
+    src << "#pragma unroll\n    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);\n    __syncwarp();\n";
+    src << "    for (int p = lane; p < " << N8 << "; p += 32) {\n      float o8[8];\n#pragma unroll\n      for (int e = 0; e < 8; ++e) o8[e] = 0.f;\n";
+    src << "      for (int tl = 0; tl < nt; ++tl) {\n        const float pz = sc[mrow * " << TC << " + tl];\n        const uint4 vv = ((const uint4*)vs)[tl * " << N8 << " + p];\n        float vf[8];\n";
+    src << unpack("vv", "vf");
+    src << "#pragma unroll\n        for (int e = 0; e < 8; ++e) o8[e] = fmaf(pz, vf[e], o8[e]);\n      }\n";
+    if (CH == 1) {
+      src << "#pragma unroll\n      for (int e = 0; e < 8; ++e) out0[((long long)g * " << M << " + mrow) * " << N << " + p * 8 + e] = " << store_expr(out->type.dt, "(o8[e] / sum)") << ";\n";
+      src << "    }\n  }\n}\n";
+    } else {
+      src << "      float* dst = part + (((long long)g * " << CH << " + c) * " << M << " + mrow) * " << PS << " + p * 8;\n";
+      src << "      *(float4*)dst = make_float4(o8[0], o8[1], o8[2], o8[3]);\n      *(float4*)(dst + 4) = make_float4(o8[4], o8[5], o8[6], o8[7]);\n    }\n";
+      src << "    if (lane == 0) {\n      float* dst = part + (((long long)g * " << CH << " + c) * " << M << " + mrow) * " << PS << " + " << N << ";\n      dst[0] = mx;\n      dst[1] = sum;\n    }\n  }\n";
+      src << "  __threadfence();\n  __syncthreads();\n";
+      src << "  if (tid == 0) last_flag = atomicAdd(cnt + g, 1) == " << (CH - 1) << ";\n  __syncthreads();\n  if (!last_flag) return;\n  __threadfence();\n";
+      src << "  if (warp < " << M << ") {\n    const int mrow = warp;\n    const float* base = part + ((long long)g * " << CH * M << " + mrow) * " << PS << ";\n";
+      // lanes take the chunks' maxima and sums side by side: the row's maximum, then every chunk's weight and the total
+      src << "    float gm = NEG_INF;\n    for (int cc = lane; cc < " << CH << "; cc += 32) gm = fmaxf(gm, __ldcg(base + (long long)cc * " << M * PS << " + " << N << "));\n";
+      src << "#pragma unroll\n    for (int o = 16; o > 0; o >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xFFFFFFFFu, gm, o));\n";
+      src << "    float den = 0.f, wl = 0.f;\n    for (int cc = lane; cc < " << CH << "; cc += 32) {\n      const float mc = __ldcg(base + (long long)cc * " << M * PS << " + " << N << ");\n";
+      src << "      wl = mc == NEG_INF ? 0.f : expf(mc - gm);\n      den += wl * __ldcg(base + (long long)cc * " << M * PS << " + " << (N + 1) << ");\n    }\n";
+      src << "#pragma unroll\n    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xFFFFFFFFu, den, o);\n";
+      src << "    for (int p = lane; p < " << ((N8 + 31) / 32 * 32) << "; p += 32) {\n      const bool mine = p < " << N8 << ";\n      float o8[8];\n#pragma unroll\n      for (int e = 0; e < 8; ++e) o8[e] = 0.f;\n";
+      src << "#pragma unroll 4\n      for (int cc = 0; cc < " << CH << "; ++cc) {\n        const float* row = base + (long long)cc * " << M * PS << ";\n";
+      if (CH <= 32) src << "        const float w = __shfl_sync(0xFFFFFFFFu, wl, cc);\n";
+      else src << "        const float mc = __ldcg(row + " << N << ");\n        const float w = mc == NEG_INF ? 0.f : expf(mc - gm);\n";
+      src << "        if (!mine) continue;\n";
+      src << "        const float4 a = __ldcg((const float4*)(row + p * 8)), b4 = __ldcg((const float4*)(row + p * 8 + 4));\n";
+      src << "        o8[0] = fmaf(w, a.x, o8[0]); o8[1] = fmaf(w, a.y, o8[1]); o8[2] = fmaf(w, a.z, o8[2]); o8[3] = fmaf(w, a.w, o8[3]);\n";
+      src << "        o8[4] = fmaf(w, b4.x, o8[4]); o8[5] = fmaf(w, b4.y, o8[5]); o8[6] = fmaf(w, b4.z, o8[6]); o8[7] = fmaf(w, b4.w, o8[7]);\n      }\n";
+      src << "      if (!mine) continue;\n";
+      src << "#pragma unroll\n      for (int e = 0; e < 8; ++e) out0[((long long)g * " << M << " + mrow) * " << N << " + p * 8 + e] = " << store_expr(out->type.dt, "(o8[e] / den)") << ";\n";
+      src << "    }\n  }\n  if (tid == 0) cnt[g] = 0;\n}\n";
+    }
+    Step s;
+    s.kind = Step::KERNEL;
+    s.kernel = add_kernel(src.str(), "attention");
+    s.label = op->has("label") ? attr_str(op->attr("label")) : op->name;
+    s.grid[0] = (unsigned)CH; s.grid[1] = (unsigned)G; s.grid[2] = 1;
+    s.block[0] = 256; s.block[1] = s.block[2] = 1;
+    TensorType pt;
+    pt.dt = DT::F32;
+    pt.dims = {std::max<long long>(1, CH > 1 ? G * CH * M * PS : 1)};
+    std::vector<int> zeros((size_t)G, 0);
+    s.args = {slot_of.at(out), new_slot(Slot::TEMP, pt, st.arena), table_slot(zeros.data(), zeros.size() * sizeof(int)), slot_of.at(Q), slot_of.at(K), slot_of.at(V)};
+    for (Value* v : em.inputs) s.args.push_back(slot_of.at(v));
+    s.n_outs = 3;
     plan.steps.push_back(std::move(s));
   }
 
@@ -4115,6 +4474,10 @@ struct Planner {
           lower_rng_bit_generator(op, plan, st);
           break;
         }
+        case Cat::ATTENTION: {
+          lower_decode_attention(op, plan, st);
+          break;
+        }
         case Cat::LINALG: {
           if (op->short_name() == "cholesky") lower_cholesky(op, plan, st);
           else lower_triangular_solve(op, plan, st);
@@ -4532,6 +4895,7 @@ std::unique_ptr<CompiledProgram> compile_module(Module& m, const CompileOptions&
   inl.run(f->body.get());
   fix_region_operands(f->body.get(), inl);
   SkinnyWeightHoist(m).run(f->body.get());
+  DecodeAttentionFusion(m).run(f->body.get());
   // unsupported-op check names every offender at once (src/pjrt_plugin/stablehlo_parser.cc:167-184)
   std::set<std::string> bad;
   collect_unsupported(f->body.get(), bad, false);

@@ -1440,7 +1440,8 @@ b200_error* b200_client_compile(b200_client* c, const char* code, size_t code_si
   {
     static const char* names[] = {"B200_NO_WINDOW_UPDATE", "B200_NO_FLAT_ALL_REDUCE", "B200_NO_GEMM16", "B200_NO_ROW_FUSION",
                                   "B200_NO_WEIGHT_HOIST", "B200_NO_LICM", "B200_NO_CSE", "B200_NO_HOIST", "B200_NO_BUNDLES",
-                                  "B200_NO_TILED_TRANSPOSE", "B200_NO_ALL_REDUCE_OVERLAP", "B200_DEBUG_NO_REUSE", "B200_NO_COL4"};
+                                  "B200_NO_TILED_TRANSPOSE", "B200_NO_ALL_REDUCE_OVERLAP", "B200_DEBUG_NO_REUSE", "B200_NO_COL4",
+                                  "B200_NO_ATTENTION_FUSION", "B200_NO_WIDE_POINTWISE", "B200_NO_WIDE_ROWS"};
     for (size_t k = 0; k < sizeof names / sizeof names[0]; k++)
       if (getenv(names[k])) env_bits |= 1u << k;
   }

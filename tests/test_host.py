@@ -188,13 +188,14 @@ def test_weight_widening_is_hoisted_out_of_the_decode_loop():
 def test_bf16_decode_loop_reads_its_weights_in_place():
     """With the native 16-bit kernels the decode loop multiplies by the bf16 weights as they are: no widened copy in
     front of the loop, every product of the body a skinny 16-bit kernel, the key-value caches updated in their
-    windows, and one copy of the normalised activation for the projections that share it."""
+    windows, one copy of the normalised activation for the projections that share it, and the attention over the
+    cache (two products and a softmax) one kernel per layer."""
     prog = programs.gemma_decode_loop(vocab=64, dim=32, layers=2, heads=2, head_dim=16, hidden=64, start=4, new_tokens=4,
                                       cache_len=8)
     plan = b200.compile_to_plan(prog.text, validate=True)[0]
     before, body = _split_at_while(plan)
     assert not any("fusion{convert}" in l for l in before) and "igemm" not in plan      # no widened copy of a weight
-    assert sum("gemv16" in l for l in body) == 2 * 9 + 1
+    assert sum("gemv16" in l for l in body) == 2 * 7 + 1 and sum("attention_" in l for l in body) == 2
     assert sum(l.count(".window") for l in body) >= 2 * 2
     # q, k and v projections read one converted activation (args[0] of three consecutive products is one slot)
     prods = [l for l in body if "gemv16" in l]
@@ -212,13 +213,13 @@ def test_loop_invariant_weights_of_skinny_products_are_transposed_once_and_merge
     assert sum(l.count("transpose batch=") for l in before) == 2 * 7       # seven weights per layer, tiled kernel
     prods = [l for l in body if "gemv16" in l]
     assert sum("N=1024 K=256" in l and "gemv16_kc" in l for l in prods) == 2 * 2   # q | k | v (512 + 256 + 256) and gate | up
-    assert len(prods) == 2 * 6 + 1
+    assert len(prods) == 2 * 4 + 1 and sum("attention_" in l for l in body) == 2
     os.environ["B200_NO_WEIGHT_HOIST"] = "1"
     try:
         plan0 = b200.compile_to_plan(prog.text)[0]
     finally:
         del os.environ["B200_NO_WEIGHT_HOIST"]
-    assert sum("gemv16" in l for l in plan0.splitlines()) == 2 * 9 + 1
+    assert sum("gemv16" in l for l in plan0.splitlines()) == 2 * 7 + 1
 
 
 def test_common_subexpressions_are_computed_once():
