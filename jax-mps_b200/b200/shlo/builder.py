@@ -624,7 +624,10 @@ class Builder:
         win = list(range(n, n + operand.ndim - 1))
         sdn = (f"#stablehlo.scatter<update_window_dims = {win}, inserted_window_dims = [0], "
                f"scatter_dims_to_operand_dims = [0], index_vector_dim = {n}>")
-        body = (lambda s, a, u: u) if op == "set" else (lambda s, a, u: s._binary(op, a, u))
+        if callable(op):
+            body = op                          # any update computation: body(sub, current element, update element)
+        else:
+            body = (lambda s, a, u: u) if op == "set" else (lambda s, a, u: s._binary(op, a, u))
         reg = self.region([((), operand.dtype)] * 2, body)
         (y,) = self.emit("stablehlo.scatter", [operand, idx2, updates], [(operand.shape, operand.dtype)],
                          props={"scatter_dimension_numbers": sdn, "indices_are_sorted": "false",
@@ -735,13 +738,17 @@ class Builder:
     def scatter(self, operand: Val, indices: Val, updates: Val, op: str = "add", *, update_window_dims=(),
                 inserted_window_dims=(), scatter_dims_to_operand_dims=(), index_vector_dim=None, input_batching_dims=(),
                 scatter_indices_batching_dims=()) -> Val:
-        """stablehlo.scatter with explicit dimension numbers (`op` in add, multiply, minimum, maximum, or "set"); no gradient."""
+        """stablehlo.scatter with explicit dimension numbers (`op` names a binary operation, or "set", or is a function
+        building the update computation); no gradient."""
         ivd = indices.ndim if index_vector_dim is None else index_vector_dim
         sdn = (f"#stablehlo.scatter<update_window_dims = {list(update_window_dims)}, inserted_window_dims = {list(inserted_window_dims)}, "
                + (f"input_batching_dims = {list(input_batching_dims)}, scatter_indices_batching_dims = {list(scatter_indices_batching_dims)}, "
                   if input_batching_dims else "")
                + f"scatter_dims_to_operand_dims = {list(scatter_dims_to_operand_dims)}, index_vector_dim = {ivd}>")
-        body = (lambda s, a, u: u) if op == "set" else (lambda s, a, u: s._binary(op, a, u))
+        if callable(op):
+            body = op                          # any update computation: body(sub, current element, update element)
+        else:
+            body = (lambda s, a, u: u) if op == "set" else (lambda s, a, u: s._binary(op, a, u))
         reg = self.region([((), operand.dtype)] * 2, body)
         (y,) = self.emit("stablehlo.scatter", [operand, indices, updates], [(operand.shape, operand.dtype)],
                          props={"scatter_dimension_numbers": sdn, "indices_are_sorted": "false",

@@ -3244,7 +3244,41 @@ struct Planner {
     s.bytes = operand->type.bytes();
     s.iparams = {numel, 1, U, 0, kind, 1};
     s.args = {slot_of.at(operand), slot_of.at(indices), slot_of.at(updates), slot_of.at(out), scratch};
-    return s;
+    if (kind >= 0) return s;
+    // The update computation as written (src/pjrt_plugin/ops/gather_scatter.cc:79-120 of the reference runs such a body
+    // once over gathered values): the scatter step only sorts the pairs, then one thread per run of equal destinations
+    // folds the run's updates into its element in update order through the compiled region.
+    plan.steps.push_back(std::move(s));
+    const int passes = (scatter_elems_launches(numel) - 1) / 3;
+    const long long koff = (passes % 2) ? 2 * U : 0, ooff = (passes % 2) ? 3 * U : U;
+    const char* ct = c_type(operand->type.dt);
+    std::ostringstream as;
+    as << "extern \"C\" __global__ void __launch_bounds__(" << kThreads << ") @NAME@(" << s_type(operand->type.dt) << "* __restrict__ out0, const "
+       << s_type(updates->type.dt) << "* __restrict__ in0, const int* __restrict__ scratch) {\n";
+    as << "  const int* key = scratch + " << koff << "LL;\n  const int* order = scratch + " << ooff << "LL;\n";
+    as << "  const int p = (int)blockIdx.x * " << kThreads << " + threadIdx.x;\n  if (p >= " << U << ") return;\n";
+    as << "  const int dest = key[p];\n  if (dest >= " << numel << " || (p > 0 && key[p - 1] == dest)) return;\n";
+    as << "  " << ct << " acc = " << load_expr(operand, "out0", "dest") << ";\n";
+    as << "  for (int q = p; q < " << U << " && key[q] == dest; ++q) {\n";
+    as << "    const " << ct << " upd = " << load_expr(updates, "in0", "order[q]") << ";\n";
+    Emitter be;
+    be.idx_t = "int";
+    be.name_prefix = "b";
+    be.indent_ = 4;
+    be.round_small_floats = true;
+    auto res = be.emit_scalar_region(op->regions[0].get(), {"acc", "upd"});
+    if (res.size() != 1) throw CompileError("stablehlo.scatter: the update computation must return one value");
+    as << be.str() << "    acc = " << res[0] << ";\n  }\n";
+    as << "  out0[dest] = " << store_expr(operand->type.dt, "acc") << ";\n}\n";
+    Step a;
+    a.kind = Step::KERNEL;
+    a.kernel = add_kernel(as.str(), "scatter_apply");
+    a.label = "scatter apply";
+    a.grid[0] = (unsigned)std::max<int64_t>(1, (U + kThreads - 1) / kThreads); a.grid[1] = a.grid[2] = 1;
+    a.block[0] = kThreads; a.block[1] = a.block[2] = 1;
+    a.args = {slot_of.at(out), slot_of.at(updates), scratch};
+    a.n_outs = 1;
+    return a;
   }
 
   // stablehlo.scatter in its row form (what jnp.take's gradient and x.at[idx].add(rows) lower to): the index
@@ -3276,9 +3310,9 @@ struct Planner {
       kind = sh == "add" ? 1 : sh == "multiply" ? 2 : sh == "minimum" ? 3 : sh == "maximum" ? 4 : -1;
     }
     DT dt = operand->type.dt;
-    if (kind < 0 || !(dt == DT::F32 || dt == DT::BF16 || dt == DT::I32))
-      throw CompileError("stablehlo.scatter: update computation or element type not supported (add/multiply/minimum/"
-                         "maximum/assign on f32, bf16, i32)");
+    // any other update computation or element type: the general form with the computation compiled as it stands
+    if (kind < 0 || !(dt == DT::F32 || dt == DT::BF16 || dt == DT::I32)) { kind = -1; ok = false; }
+    if (updates->type.dt != dt || body->args.size() != 2) throw CompileError("stablehlo.scatter: malformed update computation");
     if (indices->type.dt != DT::I32 && indices->type.dt != DT::I64) throw CompileError("stablehlo.scatter: indices must be i32 or i64");
     ensure_slot(out, st);
     for (auto* o : op->operands)
@@ -4974,7 +5008,7 @@ std::unique_ptr<CompiledProgram> compile_module(Module& m, const CompileOptions&
       long long n = 0;
       for (auto& s : p.steps) {
         if (s.kind == Step::KERNEL || s.kind == Step::ALL_REDUCE || s.kind == Step::ALL_GATHER) n += 1;
-        else if (s.kind == Step::SCATTER) n += (s.iparams.size() > 5 && s.iparams[5] == 1) ? scatter_elems_launches(s.iparams[0]) : scatter_rows_launches(s.iparams[0], s.iparams[2]);
+        else if (s.kind == Step::SCATTER) n += (s.iparams.size() > 5 && s.iparams[5] == 1) ? scatter_elems_launches(s.iparams[0]) - (s.iparams[4] < 0 ? 1 : 0) : scatter_rows_launches(s.iparams[0], s.iparams[2]);
         else if (s.kind == Step::IGEMM) n += s.ig.split_k > 1 ? 2 : 1;
         else if (s.kind == Step::GEMM16) n += (s.g16.path == 0 && s.g16.split_k > 1) ? 2 : 1;
         else if (s.kind == Step::REPACK16) n += (s.iparams[0] + 65534) / 65535;

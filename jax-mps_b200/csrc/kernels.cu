@@ -2021,6 +2021,10 @@ cudaError_t launch_scatter_elems(int elem_kind, int kind, long long numel, int u
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
+  if (kind < 0) {                        // sort only: a generated kernel applies the update computation
+    *launches += 3 * passes;
+    return cudaSuccess;
+  }
   const unsigned grid = (unsigned)((updates + 255) / 256);
   if (elem_kind == 0)
     scatter_apply_elems_kernel<float, float><<<grid, 256, 0, stream>>>((float*)out, (const float*)upd, key, order, updates, numel, kind);

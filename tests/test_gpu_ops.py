@@ -766,6 +766,46 @@ GENERAL_SCATTERS = [
 ]
 
 
+POINT_1D = dict(update_window_dims=(), inserted_window_dims=(0,), scatter_dims_to_operand_dims=(0,), index_vector_dim=1)
+SCATTER_BODIES = {
+    "apply_sin": (lambda s, a, u: s.sin(a), "f32"),                           # lax.scatter_apply(x, idx, jnp.sin)
+    "apply_mul2": (lambda s, a, u: s.mul(a, s.const(2.0, "f32")), "f32"),
+    "subtract": ("subtract", "f32"),
+    "decay_then_add": (lambda s, a, u: s.add(s.mul(a, s.const(0.5, "f32")), u), "f32"),      # depends on the order of duplicates
+    "add_ui8": ("add", "ui8"),
+    "add_i64": ("add", "i64"),
+    "add_f64": ("add", "f64"),
+    "max_i16": ("maximum", "i16"),
+}
+
+
+@pytest.mark.parametrize("name", sorted(SCATTER_BODIES))
+def test_scatter_with_any_update_computation(client, name):
+    """Update computations and element types beyond the built-in five run through the compiled region
+    (tests/configs/slice.py:500-535 of the reference: lax.scatter_apply with sin and with x * 2;
+    src/pjrt_plugin/ops/gather_scatter.cc:79-120). Duplicate destinations are folded in update order."""
+    from b200.shlo.builder import _NP
+    op, dt = SCATTER_BODIES[name]
+    rng = np.random.default_rng(11)
+    for n, idx in [(6, np.array([[0], [2], [4]], np.int32)), (5, np.array([[1], [3]], np.int32)),
+                   (40, rng.integers(-2, 42, (300, 1)).astype(np.int32))]:
+        if name.startswith("apply") and len(idx) > 3:
+            idx = np.unique(idx, axis=0)                # the reference applies a function once per index
+        b = Builder()
+        t, i, u = b.arg((n,), dt), b.arg(idx.shape, "i32"), b.arg((len(idx),), dt)
+        text = b.module([b.scatter(t, i, u, op, **POINT_1D)])
+        plan, _ = b200.compile_to_plan(text)
+        assert "scatter_apply" in plan, plan
+        if dt in ("f32", "f64"):
+            args = [rng.standard_normal(n).astype(_NP[dt]), idx, rng.standard_normal(len(idx)).astype(_NP[dt])]
+        elif dt == "i64":
+            args = [rng.integers(-2**40, 2**40, n), idx, rng.integers(-2**40, 2**40, len(idx))]
+        else:
+            info = np.iinfo(_NP[dt])
+            args = [rng.integers(info.min, info.max, n).astype(_NP[dt]), idx, rng.integers(info.min, info.max, len(idx)).astype(_NP[dt])]
+        check(client, text, args, rtol=1e-5, atol=1e-5, dtypes=[dt, "i32", dt])
+
+
 @pytest.mark.parametrize("os_,is_,us_,dn", GENERAL_SCATTERS)
 def test_general_scatter(client, os_, is_, us_, dn):
     """stablehlo.scatter beyond the row form (point updates, partial windows, batching dimensions;
