@@ -291,6 +291,19 @@ def simple(client, what, dtype, reps):
         text = b.module([b.take_rows(table, idx)])
         arrays = [f((30522, 768)), rng.integers(0, 30522, (4096,)).astype(np.int32)]
         nbytes = 2 * 4096 * 768 * es
+    elif what == "attention":
+        # the decode step of the Gemma-2B-shaped model: 8 query heads on one key / value head, 640 cached positions
+        from b200.shlo import programs
+        G, M, T, D = None, 8, 640, 256
+        text = programs.decode_attention(G, M, T, D, D, dt="bf16")
+        arrays = [f((M, D)), f((T, D)), f((T, D)), np.array(T - 3, np.int32)]
+        dtype, es = "bf16", 2
+        nbytes = (2 * T * D + 2 * M * D) * es + M * D * 4
+    elif what == "sort":
+        shape = (4096, 1024)
+        x = b.arg(shape, dtype)
+        text, arrays = b.module(b.sort([x], 1)), [f(shape)]
+        nbytes = 2 * int(np.prod(shape)) * es
     else:
         table, idx, upd = b.arg((30522, 768), dtype), b.arg((4096,), "i32"), b.arg((4096, 768), dtype)
         text = b.module([b.scatter_rows(table, idx, upd, "add")])
@@ -298,6 +311,7 @@ def simple(client, what, dtype, reps):
         nbytes = (2 * 30522 * 768 + 2 * 4096 * 768) * es          # operand copied to the result, updates read and added
     exe = client.compile(text)
     dts = [dtype if a.dtype == np.float32 else "i32" for a in arrays]
+    arrays = [np.asarray(a) for a in arrays]
     bufs = [client.buffer_from_host(a, dtype=d) for a, d in zip(arrays, dts)]
     record = _events(client)
     for _ in range(3):
@@ -316,7 +330,7 @@ def simple(client, what, dtype, reps):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["conv", "reduce", "scan", "gemma", "distilbert", "gemm", "gemv", "pointwise", "transpose",
-                                     "softmax", "gather", "scatter"])
+                                     "softmax", "gather", "scatter", "attention", "sort"])
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--layout", default="kc", choices=["kc", "nc"])
     ap.add_argument("--layers", type=int, default=None)
@@ -332,7 +346,7 @@ def main():
     if a.what == "scan":
         scan(client, a.reps)
         return
-    if a.what in ("pointwise", "transpose", "softmax", "gather", "scatter"):
+    if a.what in ("pointwise", "transpose", "softmax", "gather", "scatter", "attention", "sort"):
         simple(client, a.what, a.dtype, a.reps)
         return
     if a.what == "gemma":

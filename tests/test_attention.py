@@ -2,7 +2,6 @@
 recognised and runs as one kernel (the reference has the same chain as its fused attention call,
 src/pjrt_plugin/ops/control_flow.cc:1484-1533). The oracle interprets the unfused operations; the GPU result is held to
 it at the tolerance of the 16-bit element type."""
-import math
 import os
 
 import numpy as np
@@ -10,31 +9,8 @@ import pytest
 
 import b200
 from b200.shlo.builder import Builder
+from b200.shlo.programs import decode_attention as attention_program
 from oracle import interp
-
-
-def attention_program(G, M, T, D, N, dt="bf16", masked=True, out_f32=True, scale=True):
-    """q [G, M, D] (or [M, D] when G is None), k [.., T, D], v [.., T, N], `upto` i32: positions <= upto are visible."""
-    b = Builder()
-    lead = () if G is None else (G,)
-    q, k, v = b.arg(lead + (M, D), dt), b.arg(lead + (T, D), dt), b.arg(lead + (T, N), dt)
-    upto = b.arg((), "i32")
-    r = len(lead)
-    batch = ((0,), (0,)) if lead else ((), ())
-    sc = b.convert(b.dot_general(q, k, ((r + 1,), (r + 1,)), batch), "f32")
-    if scale:
-        sc = b.mul(sc, b.full(sc.shape, 1.0 / math.sqrt(D), "f32"))
-    if masked:
-        pos = b.iota(sc.shape, "i32", r + 1)
-        sc = b.select(b.compare(pos, b.bcast(upto, sc.shape), "LE"), sc, b.full(sc.shape, -1e30, "f32"))
-    kept = tuple(range(r + 1))
-    m = b.reduce_max(sc, (r + 1,))
-    e = b.exp(b.sub(sc, b.bcast(m, sc.shape, kept)))
-    pr = b.div(e, b.bcast(b.reduce_sum(e, (r + 1,)), sc.shape, kept))
-    att = b.dot_general(b.convert(pr, dt), v, ((r + 1,), (r,)), batch)
-    if out_f32:
-        att = b.convert(att, "f32")
-    return b.module([att])
 
 
 def _inputs(G, M, T, D, N, seed=0):
