@@ -2209,10 +2209,13 @@ struct Planner {
     src << "        acc[m] = fmaf(kf[4], qb.x, acc[m]); acc[m] = fmaf(kf[5], qb.y, acc[m]); acc[m] = fmaf(kf[6], qb.z, acc[m]); acc[m] = fmaf(kf[7], qb.w, acc[m]);\n      }\n    }\n";
     src << "    float mine = 0.f;\n#pragma unroll\n    for (int m = 0; m < " << M << "; ++m) {\n      float r = acc[m];\n";
     src << "#pragma unroll\n      for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xFFFFFFFFu, r, o);\n      if (lane == m) mine = r;\n    }\n";
-    src << "    if (lane < " << M << ") {\n      const float sval = " << round_s << ";\n";
-    src << "      const " << I << " lin = ((" << I << ")g * " << M << " + lane) * " << T << " + t0 + tl;\n";
+    src << "    if (lane < " << M << ") sc[lane * " << TC << " + tl] = mine;\n  }\n  __syncthreads();\n";
+    // the pointwise part on every score of the chunk at once (its loads, a mask for instance, go out together)
+    src << "  for (int i = tid; i < " << M * TC << "; i += 256) {\n    const int mrow = i / " << TC << ", tl = i % " << TC << ";\n    if (tl < nt) {\n";
+    src << "      const float mine = sc[i];\n      const float sval = " << round_s << ";\n";
+    src << "      const " << I << " lin = ((" << I << ")g * " << M << " + mrow) * " << T << " + t0 + tl;\n";
     src << em.str();
-    src << "      sc[lane * " << TC << " + tl] = " << rexpr << ";\n    }\n  }\n  __syncthreads();\n";
+    src << "      sc[i] = " << rexpr << ";\n    }\n  }\n  __syncthreads();\n";
     // softmax of the chunk and the second product, a warp per query row
     src << "  if (warp < " << M << ") {\n    const int mrow = warp;\n    float mx = NEG_INF;\n";
     src << "    for (int tl = lane; tl < nt; tl += 32) mx = fmaxf(mx, sc[mrow * " << TC << " + tl]);\n";
@@ -2241,7 +2244,7 @@ struct Planner {
       src << "      wl = mc == NEG_INF ? 0.f : expf(mc - gm);\n      den += wl * __ldcg(base + (long long)cc * " << M * PS << " + " << (N + 1) << ");\n    }\n";
       src << "#pragma unroll\n    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xFFFFFFFFu, den, o);\n";
       src << "    for (int p = lane; p < " << ((N8 + 31) / 32 * 32) << "; p += 32) {\n      const bool mine = p < " << N8 << ";\n      float o8[8];\n#pragma unroll\n      for (int e = 0; e < 8; ++e) o8[e] = 0.f;\n";
-      src << "#pragma unroll 4\n      for (int cc = 0; cc < " << CH << "; ++cc) {\n        const float* row = base + (long long)cc * " << M * PS << ";\n";
+      src << "#pragma unroll " << std::min<long long>(CH, 10) << "\n      for (int cc = 0; cc < " << CH << "; ++cc) {\n        const float* row = base + (long long)cc * " << M * PS << ";\n";
       if (CH <= 32) src << "        const float w = __shfl_sync(0xFFFFFFFFu, wl, cc);\n";
       else src << "        const float mc = __ldcg(row + " << N << ");\n        const float w = mc == NEG_INF ? 0.f : expf(mc - gm);\n";
       src << "        if (!mine) continue;\n";
