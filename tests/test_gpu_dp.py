@@ -15,6 +15,17 @@ CFG = dict(batch=8, image=16, width=8)
 pytestmark = pytest.mark.gpu
 
 
+def _stop(procs):
+    """Ends children that are still running (between steps nothing of theirs is in flight that a peer waits for:
+    the test is over either way), so that a failed or timed-out test cannot keep its process tree alive."""
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            p.join(timeout=20)
+        if p.is_alive():
+            p.kill()
+
+
 def _rank_main(rank, world, id_pipe, q, overlap):
     sys.path.insert(0, str(ROOT / "jax-mps_b200"))
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -53,17 +64,21 @@ def test_two_gpu_step_is_the_mean_of_the_shard_steps(overlap):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     recv, send = ctx.Pipe(duplex=False)
-    procs = [ctx.Process(target=_rank_main, args=(0, world, [send], q, overlap)),
-             ctx.Process(target=_rank_main, args=(1, world, recv, q, overlap))]
+    # daemonic children: a rank that waits for a peer that died goes down with the test instead of outliving it
+    procs = [ctx.Process(target=_rank_main, args=(0, world, [send], q, overlap), daemon=True),
+             ctx.Process(target=_rank_main, args=(1, world, recv, q, overlap), daemon=True)]
     for p in procs:
         p.start()
     got = {}
-    for _ in range(world):
-        r, a, b = q.get(timeout=300)
-        assert not isinstance(a, str), f"rank {r} failed: {a}"
-        got[r] = (a, b)
-    for p in procs:
-        p.join(timeout=60)
+    try:
+        for _ in range(world):
+            r, a, b = q.get(timeout=180)
+            assert not isinstance(a, str), f"rank {r} failed: {a}"
+            got[r] = (a, b)
+        for p in procs:
+            p.join(timeout=60)
+    finally:
+        _stop(procs)
     n_leaves = (len(got[0][0]) - 1) // 2
     np.testing.assert_allclose(got[0][0][0], (got[0][1][0] + got[1][1][0]) / 2, rtol=1e-5)
     for i in range(1, len(got[0][0])):
@@ -113,10 +128,13 @@ def test_one_process_drives_two_devices_through_per_device_argument_lists():
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    p = ctx.Process(target=_group_main, args=(q,))
+    p = ctx.Process(target=_group_main, args=(q,), daemon=True)
     p.start()
-    dp, ones, devs, assign, topo = q.get(timeout=300)
-    p.join(timeout=60)
+    try:
+        dp, ones, devs, assign, topo = q.get(timeout=180)
+        p.join(timeout=60)
+    finally:
+        _stop([p])
     assert not isinstance(dp, str), dp
     assert devs == [True, True] and topo == [0, 1]
     assert assign == (1, 2, [[0], [1]])
@@ -163,10 +181,13 @@ def test_all_gather_over_two_devices():
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    p = ctx.Process(target=_gather_main, args=(q,))
+    p = ctx.Process(target=_gather_main, args=(q,), daemon=True)
     p.start()
-    outs, xs, ys = q.get(timeout=300)
-    p.join(timeout=60)
+    try:
+        outs, xs, ys = q.get(timeout=180)
+        p.join(timeout=60)
+    finally:
+        _stop([p])
     assert not isinstance(outs, str), outs
     for d in range(2):
         np.testing.assert_array_equal(outs[d][0], np.concatenate(xs, 0))
