@@ -635,11 +635,12 @@ def lstm_inputs(prog: Program, seed: int = 0) -> list:
     return out
 
 
-def decode_attention(G, M, T, D, N, dt="bf16", masked=True, out_f32=True, scale=True) -> str:
+def decode_attention(G, M, T, D, N, dt="bf16", masked=True, out_f32=True, scale=True, keepdims=False) -> str:
     """Attention of M query rows per group over T cached positions, the chain a decode step contains
     (examples/gemma/model.py:186-230 of the reference): q [G, M, D] (or [M, D] when G is None), k [.., T, D],
     v [.., T, N] and `upto` i32 (positions <= upto are visible); scores scaled by 1 / sqrt(D), softmax in f32,
-    probabilities rounded to `dt` for the second product. Returns the module text."""
+    probabilities rounded to `dt` for the second product; `keepdims` writes the softmax's row statistics as [..., 1]
+    tensors broadcast over all dimensions. Returns the module text."""
     b = Builder()
     lead = () if G is None else (G,)
     q, k, v = b.arg(lead + (M, D), dt), b.arg(lead + (T, D), dt), b.arg(lead + (T, N), dt)
@@ -653,9 +654,14 @@ def decode_attention(G, M, T, D, N, dt="bf16", masked=True, out_f32=True, scale=
         pos = b.iota(sc.shape, "i32", r + 1)
         sc = b.select(b.compare(pos, b.bcast(upto, sc.shape), "LE"), sc, b.full(sc.shape, -1e30, "f32"))
     kept = tuple(range(r + 1))
+
+    def along_rows(stat):                      # a per-row statistic against the rows; keepdims is how jax.nn.softmax spells it
+        if keepdims:
+            return b.broadcast_in_dim(b.reshape(stat, stat.shape + (1,)), sc.shape, tuple(range(r + 2)))
+        return b.bcast(stat, sc.shape, kept)
     m = b.reduce_max(sc, (r + 1,))
-    e = b.exp(b.sub(sc, b.bcast(m, sc.shape, kept)))
-    pr = b.div(e, b.bcast(b.reduce_sum(e, (r + 1,)), sc.shape, kept))
+    e = b.exp(b.sub(sc, along_rows(m)))
+    pr = b.div(e, along_rows(b.reduce_sum(e, (r + 1,))))
     att = b.dot_general(b.convert(pr, dt), v, ((r + 1,), (r,)), batch)
     if out_f32:
         att = b.convert(att, "f32")

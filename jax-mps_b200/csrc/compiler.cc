@@ -989,13 +989,30 @@ struct DecodeAttentionFusion {
                            (c->operands[0] == body->args[1] && c->operands[1] == body->args[0]);
     return uses_args && body->ops[1]->operands.size() == 1 && body->ops[1]->operands[0] == c->results[0];
   }
-  static bool leading_broadcast(Op* bc, int rank) {
-    if (!bc || bc->operands[0]->type.rank() != rank - 1 || bc->results[0]->type.rank() != rank) return false;
+  // The row statistic `stat` (one value per row) broadcast along the row: broadcast_in_dim over the leading
+  // dimensions, or, as jax spells keepdims, a reshape to [..., 1] broadcast over all dimensions. Returns the
+  // operation that made the statistic, or null.
+  Op* row_broadcast_source(Value* v, Block* b, int rank) {
+    Op* bc = def_in(v, b, "broadcast_in_dim");
+    if (!bc || uses[v] != 1 || bc->results[0]->type.rank() != rank) return nullptr;
     auto dims = attr_i64s(bc->attr("broadcast_dimensions"));
-    if ((int)dims.size() != rank - 1) return false;
-    for (int k = 0; k < rank - 1; k++) if (dims[k] != k) return false;
-    return true;
+    Value* src = bc->operands[0];
+    if (src->type.rank() == rank - 1 && (int)dims.size() == rank - 1) {
+      for (int k = 0; k < rank - 1; k++) if (dims[k] != k) return nullptr;
+      return src->def && src->def->parent == b ? src->def : nullptr;
+    }
+    if (src->type.rank() == rank && (int)dims.size() == rank && src->type.dims[rank - 1] == 1) {
+      for (int k = 0; k < rank; k++) if (dims[k] != k) return nullptr;
+      Op* rs = def_in(src, b, "reshape");
+      if (!rs || uses[src] != 1 || rs->operands[0]->type.rank() != rank - 1) return nullptr;
+      for (int k = 0; k < rank - 1; k++) if (rs->operands[0]->type.dims[k] != src->type.dims[k]) return nullptr;
+      Value* inner = rs->operands[0];
+      drop_too.push_back(rs);
+      return inner->def && inner->def->parent == b ? inner->def : nullptr;
+    }
+    return nullptr;
   }
+  std::vector<Op*> drop_too;               // reshapes between a statistic and its broadcast, dropped with the softmax
   // [G,] rows x cols operands contracted as dims say: batch = leading dimension (or none), contraction lc / rc
   static bool dot_form(Op* d, int lc, int rc) {
     if (d->operands.size() != 2 || d->results.size() != 1 || !d->has("dot_dimension_numbers")) return false;
@@ -1020,19 +1037,18 @@ struct DecodeAttentionFusion {
     Op* div = def_in(P, b, "divide");
     if (!div || uses[P] != 1 || P->type.dt != DT::F32) return false;
     Value* e = div->operands[0];
+    drop_too.clear();
     Op* bs = def_in(div->operands[1], b, "broadcast_in_dim");
-    if (!bs || uses[bs->results[0]] != 1 || !leading_broadcast(bs, rank)) return false;
-    Op* sum = def_in(bs->operands[0], b, "reduce");
-    if (!sum || uses[sum->results[0]] != 1 || !last_dim_reduce(sum, "add") || sum->operands[0] != e || !splat_is(sum->operands[1], 0.0)) return false;
+    Op* sum = row_broadcast_source(div->operands[1], b, rank);
+    if (!bs || !sum || sum->short_name() != "reduce" || uses[sum->results[0]] != 1 || !last_dim_reduce(sum, "add") || sum->operands[0] != e || !splat_is(sum->operands[1], 0.0)) return false;
     Op* ex = def_in(e, b, "exponential");
     if (!ex || uses[e] != 2) return false;
     Op* sub = def_in(ex->operands[0], b, "subtract");
     if (!sub || uses[sub->results[0]] != 1) return false;
     Value* Sp = sub->operands[0];
     Op* bm = def_in(sub->operands[1], b, "broadcast_in_dim");
-    if (!bm || uses[bm->results[0]] != 1 || !leading_broadcast(bm, rank)) return false;
-    Op* mx = def_in(bm->operands[0], b, "reduce");
-    if (!mx || uses[mx->results[0]] != 1 || !last_dim_reduce(mx, "maximum") || mx->operands[0] != Sp ||
+    Op* mx = row_broadcast_source(sub->operands[1], b, rank);
+    if (!bm || !mx || mx->short_name() != "reduce" || uses[mx->results[0]] != 1 || !last_dim_reduce(mx, "maximum") || mx->operands[0] != Sp ||
         !splat_is(mx->operands[1], -std::numeric_limits<double>::infinity()))
       return false;
     if (uses[Sp] != 2 || Sp->type.dt != DT::F32 || Sp->type.dims != P->type.dims) return false;
@@ -1116,6 +1132,7 @@ struct DecodeAttentionFusion {
     body->args.push_back(sarg);
     std::set<Op*> gone = {qk, pv, div, bs, sum, ex, sub, bm, mx};
     if (cvt) gone.insert(cvt);
+    for (Op* o : drop_too) gone.insert(o);
     std::vector<std::unique_ptr<Op>> kept;
     std::unique_ptr<Op> fused_holder = std::move(fused);
     for (auto& up : b->ops) {

@@ -36,6 +36,21 @@ def test_attention_chain_becomes_one_kernel():
     assert plan.count("attention_") == 1 and "grid=1x3" in plan, plan
 
 
+def test_keepdims_spelling_of_the_softmax_is_recognised():
+    """jax.nn.softmax keeps the reduced dimension ([..., 1]) and broadcasts over all dimensions; both spellings give the
+    same fused plan, and the interpreter gives the same numbers for both."""
+    plain = attention_program(2, 4, 70, 64, 32)
+    kd = attention_program(2, 4, 70, 64, 32, keepdims=True)
+    assert "reshape" in kd and kd != plain
+    p0, _ = b200.compile_to_plan(plain, validate=True)
+    p1, _ = b200.compile_to_plan(kd, validate=True)
+    assert p1.count("attention_") == 1 and "row_" not in p1 and "gemv16" not in p1, p1
+    strip = lambda p: [l.split("args=")[0] for l in p.splitlines()[1:]]
+    assert strip(p0) == strip(p1)
+    args = _inputs(2, 4, 70, 64, 32) + [np.array(50, np.int32)]
+    np.testing.assert_array_equal(interp.run_text(plain, args)[0], interp.run_text(kd, args)[0])
+
+
 def test_attention_is_left_alone_where_the_kernel_does_not_apply():
     for args in [dict(G=None, M=16, T=64, D=64, N=64),           # more than eight query rows
                  dict(G=None, M=4, T=64, D=512, N=64),           # features beyond the staged row size
