@@ -304,8 +304,16 @@ struct ModuleParser {
   }
   void define(const std::string& name, Value* v) { scopes.back()[name] = v; }
 
+  // "#loc3 = loc(...)" lines that a module printed with debug information carries in front of or behind it
+  void skip_location_aliases() {
+    while (sc.peek("#loc")) {
+      sc.balanced("\n");
+    }
+  }
+
   void parse() {
     bool wrapped = false;
+    skip_location_aliases();
     if (sc.accept("module")) {
       wrapped = true;
       if (sc.accept("@")) m->name = sc.ident();
@@ -314,6 +322,8 @@ struct ModuleParser {
     }
     while (sc.peek("func.func")) func();
     if (wrapped) sc.expect("}");
+    skip_loc(sc);
+    skip_location_aliases();
     sc.ws();
     if (sc.i != sc.n) sc.fail("unexpected trailing text");
   }
@@ -499,6 +509,12 @@ struct ModuleParser {
     if (same_type_ops().count(sh)) {
       do { op->operands.push_back(lookup(sc.ssa())); } while (sc.accept(","));
       sc.expect(":");
+      if (sc.peek("(")) {          // (operand types) -> result type: clamp with scalar bounds
+        read_type_list(sc);
+        sc.expect("->");
+        finish(op, results, read_type_list(sc));
+        return;
+      }
       TensorType t = read_type(sc);
       if (sc.accept(",")) {        // 'clamp'/'select'-style type lists or (..) -> .. forms
         do { t = read_type(sc); } while (sc.accept(","));
@@ -771,6 +787,161 @@ struct ModuleParser {
       operand_list(op, ")");
       sc.expect(":");
       read_type_list(sc);
+      sc.expect("->");
+      finish(op, results, read_type_list(sc));
+      return;
+    }
+    auto functional_type = [&]() {
+      sc.expect(":");
+      read_type_list(sc);
+      sc.expect("->");
+      finish(op, results, read_type_list(sc));
+    };
+    auto keyword_dims = [&](const char* kw) {      // ", kw = [..]" -> array<i64: ..>
+      sc.expect(",");
+      sc.expect(kw);
+      sc.expect("=");
+      return dims_attr();
+    };
+    if (sh == "pad") {
+      // stablehlo.pad %x, %value, low = [..], high = [..], interior = [..] : (types) -> type
+      op->operands.push_back(lookup(sc.ssa()));
+      sc.expect(",");
+      op->operands.push_back(lookup(sc.ssa()));
+      op->attrs["edge_padding_low"] = keyword_dims("low");
+      op->attrs["edge_padding_high"] = keyword_dims("high");
+      op->attrs["interior_padding"] = keyword_dims("interior");
+      functional_type();
+      return;
+    }
+    if (sh == "reverse") {
+      // stablehlo.reverse %x, dims = [..] : type
+      op->operands.push_back(lookup(sc.ssa()));
+      op->attrs["dimensions"] = keyword_dims("dims");
+      sc.expect(":");
+      finish(op, results, {read_type(sc)});
+      return;
+    }
+    if (sh == "reduce_precision") {
+      // stablehlo.reduce_precision %x, format = e5m10 : type
+      op->operands.push_back(lookup(sc.ssa()));
+      sc.expect(",");
+      sc.expect("format");
+      sc.expect("=");
+      const std::string f = sc.ident();
+      const size_t mpos = f.find('m');
+      if (f.size() < 4 || f[0] != 'e' || mpos == std::string::npos) sc.fail("reduce_precision: expected a format like e5m10");
+      op->attrs["exponent_bits"] = f.substr(1, mpos - 1) + " : i32";
+      op->attrs["mantissa_bits"] = f.substr(mpos + 1) + " : i32";
+      sc.expect(":");
+      finish(op, results, {read_type(sc)});
+      return;
+    }
+    if (sh == "cholesky") {
+      // stablehlo.cholesky %a[, lower = true] : type
+      op->operands.push_back(lookup(sc.ssa()));
+      if (sc.accept(",")) {
+        sc.expect("lower");
+        sc.expect("=");
+        op->attrs["lower"] = sc.ident();
+      }
+      sc.expect(":");
+      finish(op, results, {read_type(sc)});
+      return;
+    }
+    if (sh == "rng_bit_generator") {
+      // stablehlo.rng_bit_generator %state, algorithm = DEFAULT : (type) -> (type, type)
+      op->operands.push_back(lookup(sc.ssa()));
+      sc.expect(",");
+      sc.expect("algorithm");
+      sc.expect("=");
+      op->attrs["rng_algorithm"] = "#stablehlo<rng_algorithm " + sc.ident() + ">";
+      functional_type();
+      return;
+    }
+    if (sh == "custom_call") {
+      // stablehlo.custom_call @target(%a, %b) {attributes} : (types) -> types
+      sc.expect("@");
+      sc.ws();
+      const std::string target = (sc.i < sc.n && sc.s[sc.i] == '"') ? sc.string_lit() : sc.ident();
+      op->attrs["call_target_name"] = "\"" + target + "\"";
+      sc.expect("(");
+      operand_list(op, ")");
+      if (sc.accept("{")) read_attr_dict(sc, "}", op->attrs);
+      functional_type();
+      return;
+    }
+    if (sh == "after_all" || sh == "create_token" || sh == "partition_id" || sh == "replica_id") {
+      // stablehlo.after_all %t0, %t1 : !stablehlo.token;  stablehlo.partition_id : tensor<ui32>
+      while (sc.peek("%")) { op->operands.push_back(lookup(sc.ssa())); sc.accept(","); }
+      sc.expect(":");
+      finish(op, results, {read_type(sc)});
+      return;
+    }
+    if (sh == "convolution") {
+      // stablehlo.convolution(%lhs, %rhs) dim_numbers = [b, 0, 1, f]x[0, 1, i, o]->[b, 0, 1, f],
+      //   window = {stride = [..], pad = [[..], ..], lhs_dilate = [..], rhs_dilate = [..], reverse = [..]} {attributes} : (types) -> type
+      sc.expect("(");
+      operand_list(op, ")");
+      sc.expect("dim_numbers");
+      sc.expect("=");
+      std::string dn;
+      for (int part = 0; part < 3; part++) {
+        sc.expect("[");
+        dn += "[" + sc.balanced("]") + "]";
+        sc.expect("]");
+        if (part == 0) { sc.expect("x"); dn += "x"; }
+        if (part == 1) { sc.expect("->"); dn += "->"; }
+      }
+      op->attrs["dimension_numbers"] = "#stablehlo.conv<" + dn + ">";
+      sc.expect(",");
+      sc.expect("window");
+      sc.expect("=");
+      sc.expect("{");
+      if (!sc.accept("}")) {
+        do {
+          const std::string key = sc.ident();
+          sc.expect("=");
+          sc.expect("[");
+          const std::string body = sc.balanced("]");
+          sc.expect("]");
+          if (key == "stride") op->attrs["window_strides"] = "array<i64: " + body + ">";
+          else if (key == "lhs_dilate") op->attrs["lhs_dilation"] = "array<i64: " + body + ">";
+          else if (key == "rhs_dilate") op->attrs["rhs_dilation"] = "array<i64: " + body + ">";
+          else if (key == "reverse") op->attrs["window_reversal"] = "array<i1: " + body + ">";
+          else if (key == "pad") {
+            size_t pairs = 0;
+            for (char ch : body) pairs += ch == '[';
+            op->attrs["padding"] = "dense<[" + body + "]> : tensor<" + std::to_string(pairs) + "x2xi64>";
+          } else sc.fail("convolution: unknown window entry '" + key + "'");
+        } while (sc.accept(","));
+        sc.expect("}");
+      }
+      if (sc.accept("{")) read_attr_dict(sc, "}", op->attrs);
+      functional_type();
+      return;
+    }
+    if (name == "chlo.top_k") {
+      // chlo.top_k(%x, k = 3) : type -> (type, type)
+      sc.expect("(");
+      op->operands.push_back(lookup(sc.ssa()));
+      sc.expect(",");
+      sc.expect("k");
+      sc.expect("=");
+      op->attrs["k"] = std::to_string(sc.integer()) + " : i64";
+      sc.expect(")");
+      sc.expect(":");
+      read_type(sc);
+      sc.expect("->");
+      finish(op, results, read_type_list(sc));
+      return;
+    }
+    if (name.rfind("chlo.", 0) == 0 && sc.peek("%")) {
+      // chlo.erf %x : type -> type (the unary functions; chlo's broadcasting binary operations are not accepted)
+      op->operands.push_back(lookup(sc.ssa()));
+      if (sc.peek(",")) sc.fail("custom assembly of '" + name + "' with several operands is not supported");
+      sc.expect(":");
+      read_type(sc);
       sc.expect("->");
       finish(op, results, read_type_list(sc));
       return;
