@@ -664,12 +664,18 @@ struct ModuleParser {
       // stablehlo.reduce(%a init: %i) applies stablehlo.add across dimensions = [1] : (..) -> ..
       sc.expect("(");
       std::vector<Value*> ins, inits;
-      do {
+      // several inputs are printed as (%a init: %i), (%b init: %j)
+      while (true) {
         ins.push_back(lookup(sc.ssa()));
         sc.expect("init:");
         inits.push_back(lookup(sc.ssa()));
-      } while (sc.accept(","));
-      sc.expect(")");
+        if (sc.accept(",")) continue;                      // further pairs inside the same parentheses
+        sc.expect(")");
+        size_t save = sc.i;
+        if (sc.accept(",") && sc.accept("(")) continue;    // the next pair in parentheses of its own
+        sc.i = save;
+        break;
+      }
       op->operands = ins;
       op->operands.insert(op->operands.end(), inits.begin(), inits.end());
       if (sc.accept("applies")) {

@@ -120,3 +120,26 @@ def test_unknown_custom_assembly_is_still_an_error():
                    "(%arg0: tensor<4xf32>) -> (tensor<4xf32>)")
     with pytest.raises(b200.B200Error, match="several operands|not supported"):
         b200.compile_to_plan(text)
+
+
+def test_reduce_with_several_inputs_in_its_printed_form():
+    """jnp.argmax as jax prints it: each (input init: value) pair in parentheses of its own and a `reducer` region."""
+    pretty = _module("""    %0 = stablehlo.iota dim = 1 : tensor<4x8xi32>
+    %cst = stablehlo.constant dense<0xFF800000> : tensor<f32>
+    %c = stablehlo.constant dense<0> : tensor<i32>
+    %1:2 = stablehlo.reduce(%arg0 init: %cst), (%0 init: %c) across dimensions = [1] : (tensor<4x8xf32>, tensor<4x8xi32>, tensor<f32>, tensor<i32>) -> (tensor<4xf32>, tensor<4xi32>)
+     reducer(%arg1: tensor<f32>, %arg3: tensor<f32>) (%arg2: tensor<i32>, %arg4: tensor<i32>)  {
+      %2 = stablehlo.compare  GT, %arg1, %arg3,  FLOAT : (tensor<f32>, tensor<f32>) -> tensor<i1>
+      %3 = stablehlo.compare  NE, %arg1, %arg1,  FLOAT : (tensor<f32>, tensor<f32>) -> tensor<i1>
+      %4 = stablehlo.or %2, %3 : tensor<i1>
+      %5 = stablehlo.compare  EQ, %arg1, %arg3,  FLOAT : (tensor<f32>, tensor<f32>) -> tensor<i1>
+      %6 = stablehlo.compare  LT, %arg2, %arg4,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>
+      %7 = stablehlo.and %5, %6 : tensor<i1>
+      %8 = stablehlo.or %4, %7 : tensor<i1>
+      %9 = stablehlo.select %4, %arg1, %arg3 : tensor<i1>, tensor<f32>
+      %10 = stablehlo.select %8, %arg2, %arg4 : tensor<i1>, tensor<i32>
+      stablehlo.return %9, %10 : tensor<f32>, tensor<i32>
+    }
+    return %1#0, %1#1 : tensor<4xf32>, tensor<4xi32>""", "(%arg0: tensor<4x8xf32>) -> (tensor<4xf32>, tensor<4xi32>)")
+    plan, _ = b200.compile_to_plan(pretty, validate=True)
+    assert "reduce" in plan
