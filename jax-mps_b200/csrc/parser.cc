@@ -508,6 +508,7 @@ struct ModuleParser {
     }
     if (same_type_ops().count(sh)) {
       do { op->operands.push_back(lookup(sc.ssa())); } while (sc.accept(","));
+      if (sc.accept("{")) read_attr_dict(sc, "}", op->attrs);
       sc.expect(":");
       if (sc.peek("(")) {          // (operand types) -> result type: clamp with scalar bounds
         read_type_list(sc);
@@ -535,7 +536,16 @@ struct ModuleParser {
     if (sh == "convert" || sh == "reshape" || sh == "bitcast_convert" || sh == "is_finite" ||
         sh == "optimization_barrier") {
       do { op->operands.push_back(lookup(sc.ssa())); } while (sc.accept(","));
+      if (sc.accept("{")) read_attr_dict(sc, "}", op->attrs);
       sc.expect(":");
+      if (!sc.peek("(")) {
+        // results typed like the operands: "convert %a : type" where nothing changes, "optimization_barrier %a, %b : t, t"
+        std::vector<TensorType> ts;
+        do { ts.push_back(read_type(sc)); } while (sc.accept(","));
+        if (sc.accept("->")) ts = read_type_list(sc);
+        finish(op, results, ts);
+        return;
+      }
       read_type_list(sc);
       sc.expect("->");
       finish(op, results, read_type_list(sc));

@@ -143,3 +143,14 @@ def test_reduce_with_several_inputs_in_its_printed_form():
     return %1#0, %1#1 : tensor<4xf32>, tensor<4xi32>""", "(%arg0: tensor<4x8xf32>) -> (tensor<4xf32>, tensor<4xi32>)")
     plan, _ = b200.compile_to_plan(pretty, validate=True)
     assert "reduce" in plan
+
+
+def test_short_type_forms_and_attribute_dictionaries():
+    """`convert` to the same type prints one type, `optimization_barrier` prints its operands' types without an arrow,
+    and an elementwise operation may carry an attribute dictionary in front of its type."""
+    pretty = _module("""    %0 = stablehlo.convert %arg0 : tensor<4xf32>
+    %1:2 = stablehlo.optimization_barrier %0, %arg0 : tensor<4xf32>, tensor<4xf32>
+    %2 = stablehlo.add %1#0, %1#1 {mhlo.frontend_attributes = {origin = "x"}} : tensor<4xf32>
+    return %2 : tensor<4xf32>""", "(%arg0: tensor<4xf32>) -> (tensor<4xf32>)")
+    plan, _ = b200.compile_to_plan(pretty, validate=True)
+    assert plan.count("kernel ") == 1 and "add" in plan
