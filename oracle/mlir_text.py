@@ -198,6 +198,7 @@ class Parser:
     def module(self) -> Module:
         name, attrs = "", {}
         wrapped = False
+        self.skip_location_aliases()
         if self.accept("module"):
             wrapped = True
             if self.peek("@"):
@@ -213,7 +214,19 @@ class Parser:
             funcs[f.name] = f
         if wrapped:
             self.expect("}")
+        self.skip_loc()
+        self.skip_location_aliases()
         return Module(name, attrs, funcs)
+
+    def skip_loc(self):
+        if self.accept("loc("):
+            self.balanced(")"); self.expect(")")
+
+    def skip_location_aliases(self):
+        """'#loc3 = loc(...)' lines of a module printed with debug information."""
+        while self.peek("#loc"):
+            j = self.s.find("\n", self.i)
+            self.i = len(self.s) if j < 0 else j
 
     def func(self) -> Func:
         self.expect("func.func")
@@ -258,6 +271,7 @@ class Parser:
         body = Block(args=list(args))
         self.ops_until(body, "}")
         self.expect("}")
+        self.skip_loc()
         return Func(name, args, arg_attrs, rts, body, private)
 
     def ops_until(self, block: Block, close: str):
@@ -367,13 +381,21 @@ class Parser:
             # 'dense<...> : tensor<..>'
             t = Parser(raw[raw.rindex(": ") + 2:]).type()
             return Op("stablehlo.constant", [], results, [t], {"value": raw}, [])
-        if short in _SAME_TYPE_PRETTY:
+        if short in _SAME_TYPE_PRETTY or (short == "clamp"):
             ops = [self.rx(_SSA)]
             while self.accept(","):
                 ops.append(self.rx(_SSA))
+            attrs = {}
+            if self.accept("{"):
+                attrs = self.attr_dict("}")
             self.expect(":")
+            if self.peek("("):                     # (operand types) -> result type: clamp with scalar bounds
+                self.type_list(); self.expect("->")
+                return Op(name, ops, results, self.type_list(), attrs, [])
             t = self.type()
-            return Op(name, ops, results, [t], {}, [])
+            while self.accept(","):
+                t = self.type()
+            return Op(name, ops, results, [t], attrs, [])
         if short == "composite":
             target = self.string()
             ops = []
@@ -386,9 +408,19 @@ class Parser:
             self.expect(":")
             self.type_list(); self.expect("->")
             return Op("stablehlo.composite", ops, results, self.type_list(), attrs, [])
-        if short in ("convert", "reshape", "bitcast_convert"):
+        if short in ("convert", "reshape", "bitcast_convert", "is_finite", "optimization_barrier"):
             ops = [self.rx(_SSA)]
-            self.expect(":"); self.type_list(); self.expect("->")
+            while self.accept(","):
+                ops.append(self.rx(_SSA))
+            self.expect(":")
+            if not self.peek("("):                 # results typed like the operands
+                ts = [self.type()]
+                while self.accept(","):
+                    ts.append(self.type())
+                if self.accept("->"):
+                    ts = self.type_list()
+                return Op(name, ops, results, ts, {}, [])
+            self.type_list(); self.expect("->")
             return Op(name, ops, results, self.type_list(), {}, [])
         if short == "compare":
             d = self.rx(_ID); self.expect(",")
@@ -420,10 +452,32 @@ class Parser:
             ins, inits = [], []
             while True:
                 ins.append(self.rx(_SSA)); self.expect("init:"); inits.append(self.rx(_SSA))
-                if not self.accept(","):
-                    break
-            self.expect(")")
-            self.expect("applies")
+                if self.accept(","):
+                    continue
+                self.expect(")")
+                save = self.i
+                if self.accept(",") and self.accept("("):      # (%a init: %i), (%b init: %j)
+                    continue
+                self.i = save
+                break
+            if not self.accept("applies"):
+                # across dimensions = [..] : types reducer(%a: t, %b: t) (%c: t, %d: t) { ... }
+                self.expect("across"); self.expect("dimensions"); self.expect("=")
+                self.expect("["); dims = self.balanced("]"); self.expect("]")
+                self.expect(":"); self.type_list(); self.expect("->")
+                rts = self.type_list()
+                self.expect("reducer")
+                firsts, seconds = [], []
+                while self.accept("("):
+                    n1 = self.rx(_SSA); self.expect(":"); t1 = self.type(); self.expect(",")
+                    n2 = self.rx(_SSA); self.expect(":"); t2 = self.type(); self.expect(")")
+                    firsts.append((n1, t1)); seconds.append((n2, t2))
+                blk = Block(args=firsts + seconds)
+                self.expect("{")
+                self.ops_until(blk, "}")
+                self.expect("}")
+                return Op(name, ins + inits, results, rts,
+                          {"dimensions": f"array<i64: {dims}>" if dims else "array<i64>"}, [blk])
             body = self.rx(re.compile(r"[\w.]+"))
             self.expect("across"); self.expect("dimensions"); self.expect("=")
             self.expect("["); dims = self.balanced("]"); self.expect("]")
@@ -442,6 +496,169 @@ class Parser:
             ops = self.operands()
             self.expect(":"); self.type_list(); self.expect("->")
             return Op("func.call", ops, results, self.type_list(), {"callee": "@" + callee}, [])
+        def functional(ops, attrs, regions=()):
+            self.expect(":"); self.type_list(); self.expect("->")
+            return Op(name, ops, results, self.type_list(), attrs, list(regions))
+
+        def bracket() -> str:
+            self.expect("["); d = self.balanced("]"); self.expect("]")
+            return f"array<i64: {d}>" if d else "array<i64>"
+
+        def keyword(kw) -> str:
+            self.expect(","); self.expect(kw); self.expect("=")
+            return bracket()
+        if short == "iota":
+            self.expect("dim"); self.expect("=")
+            d = self.rx(re.compile(r"\d+"))
+            self.expect(":")
+            return Op(name, [], results, [self.type()], {"iota_dimension": f"{d} : i64"}, [])
+        if short == "concatenate":
+            ops = []
+            while self.peek("%"):
+                ops.append(self.rx(_SSA)); self.expect(",")
+            self.expect("dim"); self.expect("=")
+            d = self.rx(re.compile(r"\d+"))
+            return functional(ops, {"dimension": f"{d} : i64"})
+        if short == "slice":
+            a = self.rx(_SSA)
+            self.expect("["); spec = self.balanced("]"); self.expect("]")
+            lo, hi, st = [], [], []
+            for part in [x.strip() for x in spec.split(",")] if spec else []:
+                f = part.split(":")
+                lo.append(f[0]); hi.append(f[1]); st.append(f[2] if len(f) > 2 else "1")
+            arr = lambda v: "array<i64: " + ", ".join(v) + ">" if v else "array<i64>"
+            return functional([a], {"start_indices": arr(lo), "limit_indices": arr(hi), "strides": arr(st)})
+        if short in ("dynamic_slice", "dynamic_update_slice"):
+            ops = [self.rx(_SSA)]
+            attrs = {}
+            while self.accept(","):
+                if self.accept("sizes"):
+                    self.expect("=")
+                    attrs["slice_sizes"] = bracket()
+                    break
+                ops.append(self.rx(_SSA))
+            return functional(ops, attrs)
+        if short == "dot_general":
+            a = self.rx(_SSA); self.expect(","); b = self.rx(_SSA)
+            dims = {"batching_dims": ("[]", "[]"), "contracting_dims": ("[]", "[]")}
+            attrs = {}
+            while self.accept(","):
+                key = self.rx(_ID); self.expect("=")
+                if key in dims:
+                    self.expect("["); l = self.balanced("]"); self.expect("]"); self.expect("x")
+                    self.expect("["); r = self.balanced("]"); self.expect("]")
+                    dims[key] = (f"[{l}]", f"[{r}]")
+                else:
+                    attrs[key] = self.balanced(",:")
+            attrs["dot_dimension_numbers"] = (
+                f"#stablehlo.dot<lhs_batching_dimensions = {dims['batching_dims'][0]}, rhs_batching_dimensions = {dims['batching_dims'][1]}, "
+                f"lhs_contracting_dimensions = {dims['contracting_dims'][0]}, rhs_contracting_dimensions = {dims['contracting_dims'][1]}>")
+            return functional([a, b], attrs)
+        if short == "while":
+            # stablehlo.while(%iterArg = %x, ...) : types [attributes {..}] cond { } do { }
+            self.expect("(")
+            names, ops = [], []
+            if not self.accept(")"):
+                while True:
+                    names.append(self.rx(_SSA)); self.expect("="); ops.append(self.rx(_SSA))
+                    if not self.accept(","):
+                        break
+                self.expect(")")
+            types = []
+            if self.accept(":"):
+                types.append(self.type())
+                while self.accept(","):
+                    types.append(self.type())
+            attrs = {}
+            if self.accept("attributes"):
+                self.expect("{"); attrs = self.attr_dict("}")
+            regions = []
+            for kw in ("cond", "do"):
+                self.expect(kw); self.expect("{")
+                blk = Block(args=list(zip(names, types)))
+                self.ops_until(blk, "}")
+                self.expect("}")
+                regions.append(blk)
+            return Op(name, ops, results, types, attrs, regions)
+        if short == "pad":
+            a = self.rx(_SSA); self.expect(","); v = self.rx(_SSA)
+            attrs = {"edge_padding_low": keyword("low"), "edge_padding_high": keyword("high"), "interior_padding": keyword("interior")}
+            return functional([a, v], attrs)
+        if short == "reverse":
+            a = self.rx(_SSA)
+            attrs = {"dimensions": keyword("dims")}
+            self.expect(":")
+            return Op(name, [a], results, [self.type()], attrs, [])
+        if short == "reduce_precision":
+            a = self.rx(_SSA); self.expect(","); self.expect("format"); self.expect("=")
+            m = re.compile(r"e(\d+)m(\d+)").match(self.rx(_ID))
+            self.expect(":")
+            return Op(name, [a], results, [self.type()], {"exponent_bits": f"{m.group(1)} : i32", "mantissa_bits": f"{m.group(2)} : i32"}, [])
+        if short == "cholesky":
+            a = self.rx(_SSA)
+            attrs = {}
+            if self.accept(","):
+                self.expect("lower"); self.expect("=")
+                attrs["lower"] = self.rx(_ID)
+            self.expect(":")
+            return Op(name, [a], results, [self.type()], attrs, [])
+        if short == "rng_bit_generator":
+            a = self.rx(_SSA); self.expect(","); self.expect("algorithm"); self.expect("=")
+            return functional([a], {"rng_algorithm": f"#stablehlo<rng_algorithm {self.rx(_ID)}>"})
+        if short == "custom_call":
+            self.expect("@")
+            self.ws()
+            target = self.string() if self.s[self.i] == '"' else self.rx(re.compile(r"[\w.$]+"))
+            self.expect("(")
+            ops = self.operands()
+            attrs = {"call_target_name": f'"{target}"'}
+            if self.accept("{"):
+                attrs.update(self.attr_dict("}"))
+            return functional(ops, attrs)
+        if short in ("after_all", "create_token", "partition_id", "replica_id"):
+            ops = []
+            while self.peek("%"):
+                ops.append(self.rx(_SSA)); self.accept(",")
+            self.expect(":")
+            return Op(name, ops, results, [self.type()], {}, [])
+        if short == "convolution":
+            self.expect("(")
+            ops = self.operands()
+            self.expect("dim_numbers"); self.expect("=")
+            dn = ""
+            for part in range(3):
+                self.expect("["); dn += "[" + self.balanced("]") + "]"; self.expect("]")
+                if part == 0:
+                    self.expect("x"); dn += "x"
+                if part == 1:
+                    self.expect("->"); dn += "->"
+            attrs = {"dimension_numbers": f"#stablehlo.conv<{dn}>"}
+            self.expect(","); self.expect("window"); self.expect("="); self.expect("{")
+            if not self.accept("}"):
+                while True:
+                    key = self.rx(_ID); self.expect("=")
+                    self.expect("["); body = self.balanced("]"); self.expect("]")
+                    if key == "pad":
+                        attrs["padding"] = f"dense<[{body}]> : tensor<{body.count('[')}x2xi64>"
+                    elif key == "reverse":
+                        attrs["window_reversal"] = f"array<i1: {body}>"
+                    else:
+                        attrs[{"stride": "window_strides", "lhs_dilate": "lhs_dilation", "rhs_dilate": "rhs_dilation"}[key]] = f"array<i64: {body}>"
+                    if not self.accept(","):
+                        break
+                self.expect("}")
+            if self.accept("{"):
+                attrs.update(self.attr_dict("}"))
+            return functional(ops, attrs)
+        if name == "chlo.top_k":
+            self.expect("("); a = self.rx(_SSA); self.expect(","); self.expect("k"); self.expect("=")
+            k = self.rx(re.compile(r"\d+"))
+            self.expect(")"); self.expect(":"); self.type(); self.expect("->")
+            return Op(name, [a], results, self.type_list(), {"k": f"{k} : i64"}, [])
+        if name.startswith("chlo.") and self.peek("%"):
+            a = self.rx(_SSA)
+            self.expect(":"); self.type(); self.expect("->")
+            return Op(name, [a], results, self.type_list(), {}, [])
         raise SyntaxError(f"custom assembly of {name!r} is not supported; print the module in generic form")
 
 

@@ -16,12 +16,24 @@ def _module(body, sig):
     return "module @jit_f {\n  func.func public @main" + sig + " {\n" + body + "\n  }\n}\n"
 
 
-def _same_plan(pretty, generic):
+def _same_plan(pretty, generic, inputs=None):
+    """Both texts give the plan compiler the same plan and, where inputs are given, the interpreter (which has a reader
+    of its own) the same numbers."""
     p1, _ = b200.compile_to_plan(pretty, validate=True)
     p0, _ = b200.compile_to_plan(generic, validate=True)
     body = lambda p: p.splitlines()[1:]
     assert body(p1) == body(p0), (p1, p0)
+    if inputs is not None:
+        from oracle import interp
+        a, b_ = interp.run_text(pretty, inputs), interp.run_text(generic, inputs)
+        assert len(a) == len(b_)
+        for x, y in zip(a, b_):
+            np.testing.assert_array_equal(np.asarray(x), np.asarray(y))
     return p1
+
+
+def _f32(*shape, seed=0):
+    return np.random.default_rng(seed).standard_normal(shape).astype(np.float32)
 
 
 def test_pad_reverse_and_clamp():
@@ -55,7 +67,7 @@ def test_convolution(window, kw):
     out = "x".join(str(d) for d in y.shape)
     pretty = _module(f"""    %0 = stablehlo.convolution(%arg0, %arg1) dim_numbers = [b, 0, 1, f]x[0, 1, i, o]->[b, 0, 1, f], {window} {{batch_group_count = 1 : i64, feature_group_count = 1 : i64, precision_config = [#stablehlo<precision DEFAULT>, #stablehlo<precision DEFAULT>]}} : (tensor<2x9x8x4xf32>, tensor<3x3x4x8xf32>) -> tensor<{out}xf32>
     return %0 : tensor<{out}xf32>""", f"(%arg0: tensor<2x9x8x4xf32>, %arg1: tensor<3x3x4x8xf32>) -> (tensor<{out}xf32>)")
-    plan = _same_plan(pretty, generic)
+    plan = _same_plan(pretty, generic, [_f32(2, 9, 8, 4), _f32(3, 3, 4, 8, seed=1)])
     assert "igemm" in plan
 
 
@@ -69,12 +81,13 @@ def test_cholesky_rng_top_k_and_chlo_functions():
     %values, %indices = chlo.top_k(%arg0, k = 2) : tensor<3x3xf32> -> (tensor<3x2xf32>, tensor<3x2xi32>)
     return %0, %1, %2, %values, %indices : tensor<3x3xf32>, tensor<3x3xf32>, tensor<3x3xf32>, tensor<3x2xf32>, tensor<3x2xi32>""",
                      "(%arg0: tensor<3x3xf32>) -> (tensor<3x3xf32>, tensor<3x3xf32>, tensor<3x3xf32>, tensor<3x2xf32>, tensor<3x2xi32>)")
-    _same_plan(pretty, generic)
+    m = _f32(3, 3) * 0.3
+    _same_plan(pretty, generic, [(m @ m.T + np.eye(3) * 0.5).astype(np.float32) * 0.5])
     b = Builder()
     generic = b.module(b.rng_bit_generator(b.arg((2,), "ui64"), (5, 3), "ui16", "THREE_FRY"))
     pretty = _module("""    %output_state, %output = stablehlo.rng_bit_generator %arg0, algorithm = THREE_FRY : (tensor<2xui64>) -> (tensor<2xui64>, tensor<5x3xui16>)
     return %output_state, %output : tensor<2xui64>, tensor<5x3xui16>""", "(%arg0: tensor<2xui64>) -> (tensor<2xui64>, tensor<5x3xui16>)")
-    _same_plan(pretty, generic)
+    _same_plan(pretty, generic, [np.array([11, 12], np.uint64)])
 
 
 def test_custom_calls_tokens_partition_id_and_reduce_precision():
@@ -89,14 +102,14 @@ def test_custom_calls_tokens_partition_id_and_reduce_precision():
     %3 = stablehlo.after_all %2 : !stablehlo.token
     %4 = stablehlo.after_all  : !stablehlo.token
     return %1 : tensor<4xf32>""", "(%arg0: tensor<4xf32>) -> (tensor<4xf32>)")
-    _same_plan(pretty, generic)
+    _same_plan(pretty, generic, [_f32(4)])
     pretty = _module("""    %0 = stablehlo.partition_id : tensor<ui32>
     %1 = stablehlo.reduce_precision %arg0, format = e5m10 : tensor<4xf32>
     return %0, %1 : tensor<ui32>, tensor<4xf32>""", "(%arg0: tensor<4xf32>) -> (tensor<ui32>, tensor<4xf32>)")
     generic = _module("""    %0 = "stablehlo.partition_id"() : () -> tensor<ui32>
     %1 = "stablehlo.reduce_precision"(%arg0) <{exponent_bits = 5 : i32, mantissa_bits = 10 : i32}> : (tensor<4xf32>) -> tensor<4xf32>
     return %0, %1 : tensor<ui32>, tensor<4xf32>""", "(%arg0: tensor<4xf32>) -> (tensor<ui32>, tensor<4xf32>)")
-    _same_plan(pretty, generic)
+    _same_plan(pretty, generic, [_f32(4)])
 
 
 def test_module_printed_with_debug_information():
@@ -154,3 +167,55 @@ def test_short_type_forms_and_attribute_dictionaries():
     return %2 : tensor<4xf32>""", "(%arg0: tensor<4xf32>) -> (tensor<4xf32>)")
     plan, _ = b200.compile_to_plan(pretty, validate=True)
     assert plan.count("kernel ") == 1 and "add" in plan
+
+
+def test_interpreter_reads_the_printed_forms_of_a_small_jax_program():
+    """A loop, a batched product, iota, concatenate, strided slice, dynamic_slice and an argmax in the forms jax prints:
+    the interpreter's own reader gives what NumPy gives, and the plan compiler accepts the same text."""
+    from oracle import interp
+    text = """#loc = loc(unknown)
+module @jit_f attributes {mhlo.num_partitions = 1 : i32, mhlo.num_replicas = 1 : i32} {
+  func.func public @main(%arg0: tensor<2x4x8xf32> loc(unknown), %arg1: tensor<2x8x3xf32> loc(unknown)) -> (tensor<2x4x3xf32> {jax.result_info = "[0]"}, tensor<6xi32> {jax.result_info = "[1]"}, tensor<2x4xi32> {jax.result_info = "[2]"}) {
+    %0 = stablehlo.dot_general %arg0, %arg1, batching_dims = [0] x [0], contracting_dims = [2] x [1], precision = [DEFAULT, DEFAULT] : (tensor<2x4x8xf32>, tensor<2x8x3xf32>) -> tensor<2x4x3xf32> loc(#loc)
+    %c = stablehlo.constant dense<0> : tensor<i32> loc(#loc)
+    %1:2 = stablehlo.while(%iterArg = %c, %iterArg_0 = %0) : tensor<i32>, tensor<2x4x3xf32>
+     cond {
+      %c_1 = stablehlo.constant dense<3> : tensor<i32>
+      %9 = stablehlo.compare  LT, %iterArg, %c_1,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>
+      stablehlo.return %9 : tensor<i1>
+    } do {
+      %9 = stablehlo.add %iterArg_0, %iterArg_0 : tensor<2x4x3xf32>
+      %c_1 = stablehlo.constant dense<1> : tensor<i32>
+      %10 = stablehlo.add %iterArg, %c_1 : tensor<i32>
+      stablehlo.return %10, %9 : tensor<i32>, tensor<2x4x3xf32>
+    }
+    %2 = stablehlo.iota dim = 0 : tensor<8xi32>
+    %3 = stablehlo.slice %2 [1:8:3] : (tensor<8xi32>) -> tensor<3xi32>
+    %c_2 = stablehlo.constant dense<5> : tensor<i32>
+    %4 = stablehlo.dynamic_slice %2, %c_2, sizes = [3] : (tensor<8xi32>, tensor<i32>) -> tensor<3xi32>
+    %5 = stablehlo.concatenate %3, %4, dim = 0 : (tensor<3xi32>, tensor<3xi32>) -> tensor<6xi32>
+    %6 = stablehlo.iota dim = 2 : tensor<2x4x8xi32>
+    %cst = stablehlo.constant dense<0xFF800000> : tensor<f32>
+    %7:2 = stablehlo.reduce(%arg0 init: %cst), (%6 init: %c) across dimensions = [2] : (tensor<2x4x8xf32>, tensor<2x4x8xi32>, tensor<f32>, tensor<i32>) -> (tensor<2x4xf32>, tensor<2x4xi32>)
+     reducer(%arg2: tensor<f32>, %arg4: tensor<f32>) (%arg3: tensor<i32>, %arg5: tensor<i32>)  {
+      %9 = stablehlo.compare  GT, %arg2, %arg4,  FLOAT : (tensor<f32>, tensor<f32>) -> tensor<i1>
+      %10 = stablehlo.compare  EQ, %arg2, %arg4,  FLOAT : (tensor<f32>, tensor<f32>) -> tensor<i1>
+      %11 = stablehlo.compare  LT, %arg3, %arg5,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>
+      %12 = stablehlo.and %10, %11 : tensor<i1>
+      %13 = stablehlo.or %9, %12 : tensor<i1>
+      %14 = stablehlo.select %9, %arg2, %arg4 : tensor<i1>, tensor<f32>
+      %15 = stablehlo.select %13, %arg3, %arg5 : tensor<i1>, tensor<i32>
+      stablehlo.return %14, %15 : tensor<f32>, tensor<i32>
+    }
+    return %1#1, %5, %7#1 : tensor<2x4x3xf32>, tensor<6xi32>, tensor<2x4xi32> loc(#loc)
+  } loc(#loc)
+} loc(#loc)
+#loc1 = loc("f.py":3:0)
+"""
+    x, y = _f32(2, 4, 8), _f32(2, 8, 3, seed=1)
+    out = interp.run_text(text, [x, y])
+    np.testing.assert_allclose(out[0], 8 * np.einsum("bik,bkj->bij", x.astype(np.float64), y.astype(np.float64)), rtol=1e-5, atol=1e-5)
+    np.testing.assert_array_equal(out[1], [1, 4, 7, 5, 6, 7])
+    np.testing.assert_array_equal(out[2], np.argmax(x, axis=2))
+    plan, _ = b200.compile_to_plan(text, validate=True)
+    assert "while trip=3" in plan and "igemm" in plan
