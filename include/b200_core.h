@@ -198,8 +198,9 @@ const char* b200_executable_plan_text(const b200_executable* exe);
 
 /* Host-only compilation (no device needed): parses and plans the module and returns the plan text and
  * the generated CUDA source as malloc'd strings the caller releases with b200_string_free. With
- * `validate_kernels` the source is also compiled by NVRTC for sm_100a, so generator mistakes surface as
- * an error here. Stands in for the reference's IR dump (JAX_MPS_DUMP_OPTIMIZED_IR,
+ * `validate_kernels` & 1 the source is also compiled by NVRTC for sm_100a, so generator mistakes surface as
+ * an error here; with `validate_kernels` & 2 the plan text ends with a table of the memory its steps name
+ * (arguments, results, temporaries, constants with their bytes). Stands in for the reference's IR dump (JAX_MPS_DUMP_OPTIMIZED_IR,
  * src/pjrt_plugin/stablehlo_parser.cc:210-232), which its fusion tests read. */
 b200_error* b200_compile_to_plan(const char* code, size_t code_size, const b200_compile_options* options,
                                  int num_processes, int process_index, int validate_kernels, char** plan_text,

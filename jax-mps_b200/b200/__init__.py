@@ -208,14 +208,15 @@ def _check(err):
 
 
 def compile_to_plan(text: str | bytes, num_processes: int = 1, process_index: int = 0, validate: bool = False,
-                    disable_fusion: bool = False):
-    """Host-only compile: returns (plan text, generated CUDA source). Needs no GPU."""
+                    disable_fusion: bool = False, slots: bool = False):
+    """Host-only compile: returns (plan text, generated CUDA source). Needs no GPU. With `slots` the plan text ends
+    with a table of the memory its steps name (arguments, results, temporaries, constants with their bytes)."""
     lib = load_library()
     code = text.encode() if isinstance(text, str) else text
     opts = _CompileOptions(C.sizeof(_CompileOptions), 0, 1 if disable_fusion else 0)
     plan, src = _P(), _P()
-    _check(lib.b200_compile_to_plan(code, len(code), C.byref(opts), num_processes, process_index, 1 if validate else 0,
-                                    C.byref(plan), C.byref(src)))
+    _check(lib.b200_compile_to_plan(code, len(code), C.byref(opts), num_processes, process_index,
+                                    (1 if validate else 0) | (2 if slots else 0), C.byref(plan), C.byref(src)))
     out = (C.string_at(plan.value).decode(), C.string_at(src.value).decode())
     lib.b200_string_free(plan)
     lib.b200_string_free(src)

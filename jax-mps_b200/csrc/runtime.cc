@@ -10,6 +10,7 @@
 // instead of one process-wide mutex around a lazy graph, a stream-ordered
 // memory pool (cudaMallocAsync), pinned staging for pageable host arrays, a
 // static kernel plan instead of trace-and-replay, NCCL for all_reduce.
+#include <sstream>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <dlfcn.h>
@@ -1535,7 +1536,7 @@ b200_error* b200_compile_to_plan(const char* code, size_t code_size, const b200_
   }
   std::string src = codegen_prelude();
   for (auto& k : prog->kernels) src += k.body + "\n";
-  if (validate_kernels && !prog->kernels.empty()) {
+  if ((validate_kernels & 1) && !prog->kernels.empty()) {
     NvrtcApi& rt = nvrtc();
     if (!rt.ok) return make_error(B200_FAILED_PRECONDITION, "NVRTC unavailable: " + rt.error);
     nvrtcProgram np;
@@ -1553,7 +1554,44 @@ b200_error* b200_compile_to_plan(const char* code, size_t code_size, const b200_
     }
     rt.DestroyProgram(&np);
   }
-  if (plan_text) *plan_text = strdup(prog->dump.c_str());
+  std::string text = prog->dump;
+  if (validate_kernels & 2) {
+    // the memory the plan's steps name: arguments, results, constants with their bytes, temporaries
+    static const char* kinds[] = {"arg", "const", "temp", "result"};
+    std::ostringstream os;
+    os << "slots:\n";
+    for (size_t k = 0; k < prog->slots.size(); k++) {
+      const Slot& sl = prog->slots[k];
+      os << "  slot " << k << " " << kinds[(int)sl.kind] << " index=" << sl.index << " arena=" << sl.arena << " offset=" << sl.offset
+         << " bytes=" << sl.bytes << " " << sl.type.str();
+      if (sl.kind == Slot::CONST && sl.index >= 0 && (size_t)sl.index < prog->consts.size()) {
+        const auto& b = prog->consts[sl.index].bytes;
+        os << " hex=";
+        if (b.size() <= (1u << 20)) {
+          static const char* digits = "0123456789abcdef";
+          for (uint8_t c : b) os << digits[c >> 4] << digits[c & 15];
+        } else os << "-";
+      }
+      os << "\n";
+    }
+    for (size_t k = 0; k < prog->results.size(); k++) os << "  result " << k << " slot=" << prog->results[k].slot << "\n";
+    // the top-level steps with every argument (the plan text above abbreviates long argument lists)
+    os << "launches:\n";
+    for (const Step& st : prog->main.steps) {
+      if (st.kind == Step::KERNEL) {
+        os << "  kernel " << prog->kernels[st.kernel].name << " grid=" << st.grid[0] << "x" << st.grid[1] << "x" << st.grid[2] << " block="
+           << st.block[0] << "x" << st.block[1] << "x" << st.block[2] << " args=[";
+        for (size_t k = 0; k < st.args.size(); k++) os << (k ? "," : "") << st.args[k];
+        os << "]\n";
+      } else if (st.kind == Step::MEMCPY) {
+        os << "  memcpy bytes=" << st.bytes << " args=[" << st.args[0] << "," << st.args[1] << "]\n";
+      } else {
+        os << "  other kind=" << (int)st.kind << " " << st.label << "\n";
+      }
+    }
+    text += os.str();
+  }
+  if (plan_text) *plan_text = strdup(text.c_str());
   if (cuda_source) *cuda_source = strdup(src.c_str());
   return nullptr;
 }

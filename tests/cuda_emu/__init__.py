@@ -1,0 +1,153 @@
+"""Runs a compiled plan's generated kernels on the CPU: the CUDA source the plan compiler emits is compiled with g++
+against a small shim of the CUDA execution model (one OS thread per CUDA thread of a block, see shim.h) and the plan's
+kernel steps are executed in order over NumPy buffers. Test infrastructure for the generated code (pointwise, reduction,
+row, window, sort, random-bit, factorization and attention kernels); plans with steps that are hand-written CUDA
+(contractions, the built-in scatter) or control flow are reported as unsupported. Nothing in the product imports this."""
+from __future__ import annotations
+
+import ctypes as C
+import hashlib
+import os
+import re
+import subprocess
+import tempfile
+from pathlib import Path
+
+import numpy as np
+
+import b200
+
+HERE = Path(__file__).resolve().parent
+_NP = {"f32": np.float32, "f64": np.float64, "i8": np.int8, "i16": np.int16, "i32": np.int32, "i64": np.int64,
+       "ui8": np.uint8, "ui16": np.uint16, "ui32": np.uint32, "ui64": np.uint64, "i1": np.bool_, "bf16": np.uint16,
+       "f16": np.float16}
+
+
+class Unsupported(Exception):
+    pass
+
+
+_HOST_CONVERSIONS = '''
+DEV void pdl_prologue() {}
+DEV float bf16_to_f(u16 h) { return __uint_as_float(((u32)h) << 16); }
+DEV u16 f_to_bf16(float f) {
+  u32 u = __float_as_uint(f);
+  if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (u16)0x7FFF;
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return (u16)(u >> 16);
+}
+DEV float f16_to_f(u16 h) { _Float16 v; std::memcpy(&v, &h, 2); return (float)v; }
+DEV u16 f_to_f16(float f) { _Float16 v = (_Float16)f; u16 h; std::memcpy(&h, &v, 2); return h; }
+'''
+
+
+def _host_source(src: str) -> str:
+    """The generated translation unit with its four inline-PTX helpers replaced by C++."""
+    out, skip = [], False
+    for line in src.splitlines():
+        if re.match(r"DEV (void pdl_prologue|float bf16_to_f|u16 f_to_bf16|float f16_to_f|u16 f_to_f16)\(", line):
+            if "{" in line and line.rstrip().endswith("}"):
+                continue                                    # one-line definition
+            skip = True
+            continue
+        if skip:
+            if line.startswith("}"):
+                skip = False
+            continue
+        out.append(line)
+    text = "\n".join(out)
+    at = text.index("#define DEV")
+    at = text.index("\n", at) + 1
+    return '#include "shim.h"\n' + text[:at] + _HOST_CONVERSIONS + text[at:]
+
+
+def _build(src: str) -> C.CDLL:
+    host = _host_source(src)
+    key = hashlib.sha256((host + (HERE / "shim.h").read_text() + (HERE / "runner.cc").read_text()).encode()).hexdigest()[:24]
+    cache = Path(tempfile.gettempdir()) / "b200_cuda_emu"
+    cache.mkdir(exist_ok=True)
+    so = cache / f"k{key}.so"
+    if not so.exists():
+        cu = cache / f"k{key}.cc"
+        cu.write_text(host)
+        cmd = ["g++", "-std=c++20", "-O1", "-g0", "-w", "-fPIC", "-shared", "-pthread", f"-I{HERE}", str(cu), str(HERE / "runner.cc"),
+               "-o", str(so) + ".tmp"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("g++ failed on the generated source:\n" + r.stderr[:6000])
+        os.replace(str(so) + ".tmp", so)
+    return C.CDLL(str(so))
+
+
+def _aligned(nbytes: int) -> np.ndarray:
+    raw = np.zeros(max(nbytes, 1) + 256, np.uint8)
+    off = (-raw.ctypes.data) % 256
+    return raw[off:off + max(nbytes, 1)]
+
+
+def _to_bf16_bits(a: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    nan = (u & 0x7FFFFFFF) > 0x7F800000
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return np.where(nan, np.uint16(0x7FFF), r)
+
+
+def run_plan_on_cpu(text: str, inputs: list) -> list:
+    """Compiles `text`, runs the plan's kernel steps on host threads and returns the results as NumPy arrays (bf16
+    results as float32)."""
+    plan, src = b200.compile_to_plan(text, slots=True)
+    _, table = plan.split("slots:\n")
+    table, launches = table.split("launches:\n")
+    steps = []
+    for line in launches.splitlines():
+        m = re.match(r"^  kernel (\S+) grid=(\d+)x(\d+)x(\d+) block=(\d+)x(\d+)x(\d+) args=\[([\d,]*)\]\s*$", line)
+        if m:
+            steps.append(("kernel", m.group(1), [int(m.group(k)) for k in range(2, 8)], [int(v) for v in m.group(8).split(",") if v]))
+            continue
+        m = re.match(r"^  memcpy bytes=(\d+) args=\[(\d+),(\d+)\]\s*$", line)
+        if m:
+            steps.append(("memcpy", int(m.group(1)), None, [int(m.group(2)), int(m.group(3))]))
+            continue
+        raise Unsupported(line.strip()[:80])
+    slots, results = {}, {}
+    for line in table.splitlines():
+        m = re.match(r"^  slot (\d+) (\w+) index=(-?\d+) arena=\d+ offset=\d+ bytes=(\d+) (\S+)(?: hex=(\S*))?$", line)
+        if m:
+            sid, kind, index, nbytes, ty, hx = int(m.group(1)), m.group(2), int(m.group(3)), int(m.group(4)), m.group(5), m.group(6)
+            buf = _aligned(nbytes)
+            tm = re.match(r"tensor<((?:\d+x)*)(\w+)>", ty)
+            shape = tuple(int(v) for v in tm.group(1).split("x") if v) if tm else ()
+            dt = tm.group(2) if tm else "ui8"
+            if kind == "arg":
+                a = np.asarray(inputs[index])
+                raw = _to_bf16_bits(a) if dt == "bf16" else np.ascontiguousarray(a, _NP[dt])
+                buf[:raw.nbytes] = raw.reshape(-1).view(np.uint8)
+            elif kind == "const":
+                if hx in (None, "-"):
+                    raise Unsupported("constant without data")
+                data = np.frombuffer(bytes.fromhex(hx), np.uint8)
+                buf[:data.size] = data
+            slots[sid] = (buf, shape, dt)
+            continue
+        m = re.match(r"^  result (\d+) slot=(\d+)$", line)
+        if m:
+            results[int(m.group(1))] = int(m.group(2))
+    lib = _build(src)
+    lib.emu_launch.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
+    lib.emu_launch.restype = None
+    for kind, name, dims, args in steps:
+        if kind == "memcpy":
+            slots[args[0]][0][:name] = slots[args[1]][0][:name]
+            continue
+        fn = C.cast(getattr(lib, name), C.c_void_p)
+        ptrs = (C.c_void_p * len(args))(*[slots[a][0].ctypes.data for a in args])
+        lib.emu_launch(fn, len(args), ptrs, *dims)
+    outs = []
+    for k in sorted(results):
+        buf, shape, dt = slots[results[k]]
+        n = int(np.prod(shape, dtype=np.int64)) if shape else 1
+        a = buf[:n * np.dtype(_NP[dt]).itemsize].view(_NP[dt]).reshape(shape).copy()
+        if dt == "bf16":
+            a = (a.astype(np.uint32) << 16).view(np.float32)
+        outs.append(a)
+    return outs

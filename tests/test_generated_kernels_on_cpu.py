@@ -1,0 +1,123 @@
+"""The plan compiler's generated CUDA kernels, executed on the CPU: the emitted source is compiled with g++ against a
+shim of the CUDA execution model (tests/cuda_emu: a host thread per CUDA thread, block and warp barriers, shuffles,
+shared memory) and run step by step over NumPy buffers, then compared with the interpreter under oracle/. This holds
+the generated code itself, not only its plan, to the oracle without a GPU: index arithmetic, wide accesses, warp and
+block reductions, the row chains, window operations, the merge sort, Philox, the factorizations and the split-position
+attention kernel with its last-block combine. Hand-written kernels (contractions, transposes, the built-in scatter)
+are outside its reach and stay with the GPU tests."""
+import numpy as np
+import pytest
+
+from b200.shlo import programs
+from b200.shlo.builder import Builder
+from cuda_emu import Unsupported, run_plan_on_cpu
+from oracle import interp
+
+rng = np.random.default_rng(3)
+
+
+def f32(*shape):
+    return rng.standard_normal(shape).astype(np.float32)
+
+
+def _check(text, inputs, rtol=1e-5, atol=1e-5):
+    got = run_plan_on_cpu(text, inputs)
+    want = interp.run_text(text, inputs)
+    assert len(got) == len(want)
+    for g, w in zip(got, want):
+        w = np.asarray(w)
+        assert g.shape == w.shape
+        if g.dtype.kind in "iub":
+            np.testing.assert_array_equal(g, w.astype(g.dtype))
+        else:
+            np.testing.assert_allclose(g.astype(np.float64), w.astype(np.float64), rtol=rtol, atol=atol, equal_nan=True)
+    return got
+
+
+def test_pointwise_fusions_scalar_and_wide():
+    for shape, dt, tol in [((33, 65), "f32", 1e-5), ((64, 256), "f32", 1e-5), ((64, 256), "bf16", 2e-2)]:
+        b = Builder()
+        x, y, s = b.arg(shape, dt), b.arg(shape, dt), b.arg((shape[1],), dt)
+        z = b.max(b.add(b.mul(x, b.broadcast_in_dim(s, shape, (1,))), b.tanh(y)), b.full(shape, 0.0, dt))
+        _check(b.module([z, b.select(b.compare(x, y, "LT"), x, y)]), [f32(*shape), f32(*shape), f32(shape[1])], rtol=tol, atol=tol)
+
+
+def test_integer_kernels_are_exact():
+    b = Builder()
+    x, y = b.arg((1000,), "i32"), b.arg((1000,), "i32")
+    outs = [b.add(x, y), b.mul(x, y), b.div(x, y), b.rem(x, y), b.shl(x, y), b.shr_arith(x, y), b.popcnt(x), b.clz(x)]
+    a0 = rng.integers(-2**31, 2**31 - 1, 1000).astype(np.int32)
+    a1 = rng.integers(-40, 40, 1000).astype(np.int32)
+    _check(b.module(outs), [a0, a1])
+
+
+def test_reductions_rows_columns_and_argmax():
+    b = Builder()
+    x = b.arg((300, 70), "f32")
+    _check(b.module([b.reduce_sum(x, [1]), b.reduce_max(x, [0]), b.reduce_sum(b.mul(x, x), [0, 1]), b.argmax(x, 1)]), [f32(300, 70)],
+           rtol=1e-5, atol=1e-4)
+    b = Builder()
+    x = b.arg((4096, 128), "f32")                                       # the four-columns-per-thread form with its second pass
+    _check(b.module([b.reduce_sum(x, [0]), b.reduce_sum(b.mul(x, x), [0])]), [f32(4096, 128)], rtol=1e-5, atol=2e-3)
+
+
+@pytest.mark.parametrize("rows,n", [(40, 100), (3, 1500), (70, 32)])
+def test_softmax_row_chain(rows, n):
+    b = Builder()
+    x = b.arg((rows, n), "f32")
+    m = b.reduce_max(x, (1,))
+    e = b.exp(b.sub(x, b.broadcast_in_dim(m, x.shape, (0,))))
+    p = b.div(e, b.broadcast_in_dim(b.reduce_sum(e, (1,)), x.shape, (0,)))
+    _check(b.module([p]), [f32(rows, n)], rtol=1e-5, atol=1e-6)
+
+
+def test_window_operations():
+    b = Builder()
+    x = b.arg((2, 9, 10, 3), "f32")
+    win, st, pad = (1, 3, 3, 1), (1, 2, 2, 1), ((0, 0), (1, 1), (1, 1), (0, 0))
+    fwd = b.reduce_window(x, -np.inf, "maximum", win, st, pad)
+    src = b.arg(fwd.shape, "f32")
+    bwd = b.select_and_scatter(x, src, 0.0, win, st, pad, select="GE")
+    cum = b.reduce_window(b.reshape(x, (18, 30)), 0.0, "add", (1, 30), (1, 1), ((0, 0), (29, 0)))
+    xv = np.round(f32(2, 9, 10, 3) * 2) / 2
+    _check(b.module([fwd, bwd, cum]), [xv, f32(*fwd.shape)], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("shape,dim,desc", [((5, 700), 1, False), ((3, 3000), 1, True), ((1500, 3), 0, False)])
+def test_sort_and_top_k(shape, dim, desc):
+    keys = (np.round(f32(*shape) * 2) / 2 + 0.0).astype(np.float32)
+    tag = np.arange(keys.size, dtype=np.int32).reshape(shape)
+    b = Builder()
+    _check(b.module(b.sort([b.arg(shape, "f32"), b.arg(shape, "i32")], dim, descending=desc)), [keys, tag])
+    if dim == 1:
+        b = Builder()
+        _check(b.module(b.top_k(b.arg(shape, "f32"), 7)), [keys])
+
+
+def test_random_bits_and_factorizations():
+    b = Builder()
+    _check(b.module(b.rng_bit_generator(b.arg((2,), "ui64"), (1000, 3), "ui16")), [np.array([5, (1 << 64) - 2], np.uint64)])
+    m = rng.standard_normal((3, 6, 6))
+    a = (m @ np.swapaxes(m, 1, 2) + 6 * np.eye(6)).astype(np.float32)
+    b = Builder()
+    av = b.arg(a.shape, "f32")
+    l = b.cholesky(av)
+    x = b.triangular_solve(l, b.arg((3, 6, 2), "f32"), transpose_a="TRANSPOSE")
+    y = b.triangular_solve(l, b.arg((3, 4, 6), "f32"), left_side=False)
+    _check(b.module([l, x, y]), [a, f32(3, 6, 2), f32(3, 4, 6)], rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("G,M,T,D,N,upto", [(None, 8, 100, 64, 64, 70), (2, 3, 24, 64, 32, 11), (None, 4, 70, 128, 64, 3)])
+def test_decode_attention_kernel(G, M, T, D, N, upto):
+    """Several chunks with the last block's combine, one chunk, and chunks that the mask empties."""
+    text = programs.decode_attention(G, M, T, D, N)
+    lead = () if G is None else (G,)
+    args = [f32(*lead, M, D), f32(*lead, T, D), f32(*lead, T, N), np.array(upto, np.int32)]
+    _check(text, args, rtol=2e-2, atol=2e-2)
+
+
+def test_plans_with_hand_written_steps_are_reported():
+    b = Builder()
+    x, w = b.arg((64, 64), "f32"), b.arg((64, 64), "f32")
+    with pytest.raises(Unsupported):
+        run_plan_on_cpu(b.module([b.matmul(x, w)]), [f32(64, 64), f32(64, 64)])
