@@ -121,3 +121,28 @@ def test_plans_with_hand_written_steps_are_reported():
     x, w = b.arg((64, 64), "f32"), b.arg((64, 64), "f32")
     with pytest.raises(Unsupported):
         run_plan_on_cpu(b.module([b.matmul(x, w)]), [f32(64, 64), f32(64, 64)])
+
+
+@pytest.mark.parametrize("rows,n,dt,tol", [(48, 96, "f32", 2e-4), (5, 1536, "f32", 2e-4), (64, 256, "bf16", 4e-2)])
+def test_layer_norm_forward_and_backward_row_chains(rows, n, dt, tol):
+    """LayerNorm with its gradient (reductions and pointwise stages that share rows fuse into row kernels: a warp per
+    row for short rows, a block per row for long ones, 16-byte accesses for bf16), next to the column reductions of
+    the scale and shift gradients."""
+    b = Builder()
+    x, gamma, beta, w = b.arg((rows, n), dt), b.arg((n,), dt), b.arg((n,), dt), b.arg((rows, n), dt)
+    xf = b.convert(x, "f32") if dt != "f32" else x
+    mu = b.mean(xf, (1,))
+    xc = b.sub(xf, b.bcast(mu, xf.shape, (0,)))
+    var = b.mean(b.mul(xc, xc), (1,))
+    inv = b.rsqrt(b.add(var, b.full(var.shape, 1e-5, "f32")))
+    y = b.mul(xc, b.bcast(inv, xf.shape, (0,)))
+    gf = b.convert(gamma, "f32") if dt != "f32" else gamma
+    bf = b.convert(beta, "f32") if dt != "f32" else beta
+    y = b.add(b.mul(y, b.bcast(gf, xf.shape, (1,))), b.bcast(bf, xf.shape, (1,)))
+    yo = b.convert(y, dt) if dt != "f32" else y
+    wf = b.convert(w, "f32") if dt != "f32" else w
+    loss = b.reduce_sum(b.mul(b.convert(yo, "f32") if dt != "f32" else yo, wf), (0, 1))
+    grads = b.grad(loss, [x, gamma, beta])
+    import b200
+    assert "row_" in b200.compile_to_plan(b.module([yo, loss] + list(grads)))[0]
+    _check(b.module([yo, loss] + list(grads)), [f32(rows, n), 1 + 0.1 * f32(n), 0.1 * f32(n), f32(rows, n)], rtol=tol, atol=tol * 5)
