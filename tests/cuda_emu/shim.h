@@ -12,6 +12,8 @@
 #include <vector>
 
 using std::isfinite;
+using std::max;
+using std::min;
 using std::isnan;
 using std::isinf;
 using std::signbit;

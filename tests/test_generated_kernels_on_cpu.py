@@ -146,3 +146,45 @@ def test_layer_norm_forward_and_backward_row_chains(rows, n, dt, tol):
     import b200
     assert "row_" in b200.compile_to_plan(b.module([yo, loss] + list(grads)))[0]
     _check(b.module([yo, loss] + list(grads)), [f32(rows, n), 1 + 0.1 * f32(n), 0.1 * f32(n), f32(rows, n)], rtol=tol, atol=tol * 5)
+
+
+def test_indexing_operations_inside_fused_kernels():
+    """transpose, reverse, strided slice, pad with negative-free interior padding, concatenate, broadcast of a reduction,
+    row gather, and dynamic_slice / dynamic_update_slice whose start is clamped into range."""
+    b = Builder()
+    x = b.arg((7, 9, 5), "f32")
+    outs = [b.transpose(x, (2, 0, 1)), b.reverse(x, [1]), b.slice(x, (1, 2, 0), (6, 9, 5), (2, 3, 1)),
+            b.pad(x, b.const(1.5, "f32"), [1, 0, 2], [0, 3, 1], [1, 0, 2]), b.concatenate([x, x], 1),
+            b.bcast(b.reduce_sum(x, (1,)), x.shape, (0, 2))]
+    _check(b.module(outs), [f32(7, 9, 5)])
+    b = Builder()
+    t, i = b.arg((50, 12), "f32"), b.arg((33,), "i32")
+    _check(b.module([b.take_rows(t, i)]), [f32(50, 12), rng.integers(0, 50, 33).astype(np.int32)])
+    b = Builder()
+    x, s = b.arg((5000,), "f32"), b.arg((), "i32")
+    _check(b.module([b.dynamic_slice(x, [s], (100,)), b.dynamic_update_slice(x, b.full((7,), 2.0, "f32"), [s])]),
+           [f32(5000), np.array(4950, np.int32)])
+
+
+@pytest.mark.parametrize("dt", ["i8", "ui8", "i16", "i64", "ui32", "f64"])
+def test_arithmetic_in_every_element_type(dt):
+    from b200.shlo.builder import _NP
+    b = Builder()
+    x, y = b.arg((999,), dt), b.arg((999,), dt)
+    if dt == "f64":
+        a0, a1 = rng.standard_normal(999), rng.standard_normal(999)
+    else:
+        info = np.iinfo(_NP[dt])
+        a0 = rng.integers(info.min, info.max, 999).astype(_NP[dt])
+        a1 = rng.integers(max(info.min, -50), min(info.max, 50), 999).astype(_NP[dt])
+    _check(b.module([b.add(x, y), b.mul(x, y), b.div(x, y), b.max(x, y), b.convert(x, "f32")]), [a0, a1], rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("rows,n", [(1, 1), (3, 31), (65, 33), (3, 129), (1, 1025), (3, 5000)])
+def test_softmax_rows_around_the_warp_and_block_sizes(rows, n):
+    b = Builder()
+    x = b.arg((rows, n), "f32")
+    m = b.reduce_max(x, (1,))
+    e = b.exp(b.sub(x, b.broadcast_in_dim(m, x.shape, (0,))))
+    p = b.div(e, b.broadcast_in_dim(b.reduce_sum(e, (1,)), x.shape, (0,)))
+    _check(b.module([p]), [f32(rows, n)], rtol=1e-5, atol=1e-6)
