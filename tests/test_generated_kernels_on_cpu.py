@@ -188,3 +188,74 @@ def test_softmax_rows_around_the_warp_and_block_sizes(rows, n):
     e = b.exp(b.sub(x, b.broadcast_in_dim(m, x.shape, (0,))))
     p = b.div(e, b.broadcast_in_dim(b.reduce_sum(e, (1,)), x.shape, (0,)))
     _check(b.module([p]), [f32(rows, n)], rtol=1e-5, atol=1e-6)
+
+
+def _random_fusion_graph(seed):
+    """A random graph of pointwise operations, row / column broadcasts and reductions over one [R, C] shape: what the
+    fusion, sibling-reduction and row-chain logic has to cut into kernels."""
+    r = np.random.default_rng(seed)
+    R = int(r.choice([1, 2, 3, 7, 16, 31, 33, 64, 70, 130, 300, 1100]))
+    C = int(r.choice([1, 2, 5, 8, 31, 32, 33, 64, 100, 128, 257, 1030]))
+    if R * C > 40000:
+        C = max(1, 40000 // R)
+    b = Builder()
+    full = [b.arg((R, C), "f32"), b.arg((R, C), "f32")]
+    rows, cols = [b.arg((C,), "f32")], [b.arg((R,), "f32")]
+    inputs = [r.standard_normal((R, C)).astype(np.float32), r.standard_normal((R, C)).astype(np.float32),
+              r.standard_normal((C,)).astype(np.float32), r.standard_normal((R,)).astype(np.float32)]
+    for _ in range(int(r.integers(3, 14))):
+        k = int(r.integers(0, 12))
+        x, y = full[int(r.integers(0, len(full)))], full[int(r.integers(0, len(full)))]
+        if k == 0: full.append(b.tanh(b.add(x, y)))
+        elif k == 1: full.append(b.mul(x, b.tanh(y)))
+        elif k == 2: full.append(b.max(x, b.neg(y)))
+        elif k == 3: full.append(b.add(x, b.bcast(rows[int(r.integers(0, len(rows)))], (R, C), (1,))))
+        elif k == 4: full.append(b.mul(x, b.bcast(cols[int(r.integers(0, len(cols)))], (R, C), (0,))))
+        elif k == 5: rows.append(b.tanh(b.reduce_sum(x, (0,))))
+        elif k == 6: cols.append(b.tanh(b.reduce_sum(x, (1,))))
+        elif k == 7: cols.append(b.reduce_max(x, (1,)))
+        elif k == 8: full.append(b.select(b.compare(x, y, "GT"), x, b.exp(b.neg(b.abs(y)))))
+        elif k == 9: full.append(b.sub(x, b.bcast(b.mean(x, (1,)), (R, C), (0,))))
+        elif k == 10: full.append(b.tanh(b.div(x, b.add(b.abs(y), b.full((R, C), 1.0, "f32")))))
+        else: full.append(b.add(x, b.tanh(b.bcast(b.reduce_sum(b.mul(x, y), (0, 1)), (R, C)))))
+    pool = full[2:] + rows[1:] + cols[1:]
+    outs = [pool[int(i)] for i in r.choice(len(pool), size=min(len(pool), int(r.integers(1, 4))), replace=False)]
+    return b.module(outs), inputs
+
+
+@pytest.mark.parametrize("seed", [0, 3, 17, 41, 77, 102, 150, 211])
+def test_random_fusion_graphs(seed):
+    """Seeds from a sweep of 220 such graphs (all of which agreed with the interpreter)."""
+    text, inputs = _random_fusion_graph(seed)
+    got = run_plan_on_cpu(text, inputs)
+    want = interp.run_text(text, inputs)
+    for g, w in zip(got, want):
+        w = np.asarray(w, np.float64)
+        np.testing.assert_allclose(g.astype(np.float64), w, rtol=2e-4, atol=2e-4 * max(1.0, float(np.max(np.abs(w))) if w.size else 1.0))
+
+
+@pytest.mark.parametrize("seed", [2, 5, 9, 23, 38, 47])
+def test_random_window_geometries(seed):
+    """reduce_window with random windows, strides, paddings (negative too) and both dilations, and select_and_scatter
+    where it applies; seeds from a sweep of 60 geometries."""
+    r = np.random.default_rng(seed)
+    rank = int(r.integers(1, 5))
+    shape = tuple(int(r.integers(1, 9)) for _ in range(rank))
+    win = tuple(int(r.integers(1, min(4, s + 1) + 1)) for s in shape)
+    st = tuple(int(r.integers(1, 4)) for _ in range(rank))
+    pad = tuple((int(r.integers(-1, 3)), int(r.integers(-1, 3))) for _ in range(rank))
+    bd = tuple(int(r.integers(1, 3)) for _ in range(rank))
+    wd = tuple(int(r.integers(1, 3)) for _ in range(rank))
+    op, init = [("add", 0.0), ("maximum", -np.inf), ("minimum", np.inf), ("multiply", 1.0)][int(r.integers(0, 4))]
+    x = (np.round(r.standard_normal(shape) * 4) / 4).astype(np.float32)
+    b = Builder()
+    xv = b.arg(shape, "f32")
+    y = b.reduce_window(xv, init, op, win, st, pad, bd, wd)
+    if any(d <= 0 for d in y.shape):
+        pytest.skip("empty result")
+    outs, inputs = [y], [x]
+    if all(d == 1 for d in bd + wd) and all(p[0] >= 0 and p[1] >= 0 for p in pad):
+        src = b.arg(y.shape, "f32")
+        outs.append(b.select_and_scatter(xv, src, 0.0, win, st, pad, select=["GE", "GT", "LE"][int(r.integers(0, 3))]))
+        inputs.append(r.standard_normal(y.shape).astype(np.float32))
+    _check(b.module(outs), inputs)
