@@ -259,3 +259,13 @@ def test_random_window_geometries(seed):
         outs.append(b.select_and_scatter(xv, src, 0.0, win, st, pad, select=["GE", "GT", "LE"][int(r.integers(0, 3))]))
         inputs.append(r.standard_normal(y.shape).astype(np.float32))
     _check(b.module(outs), inputs)
+
+
+def test_threefry_bits_are_exact():
+    """The 20 rounds of Threefry-2x32 as one generated integer kernel: word for word what the interpreter gives (which
+    tests/test_threefry.py holds to the published known answers)."""
+    p = programs.threefry_bits(4096)
+    args = [np.array([0x13198a2e, 0x03707344], np.uint32)]
+    got, want = run_plan_on_cpu(p.text, args), interp.run_text(p.text, args)
+    assert len(got) == len(want) == 1
+    np.testing.assert_array_equal(got[0], want[0])
