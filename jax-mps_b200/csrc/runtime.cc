@@ -1585,6 +1585,13 @@ b200_error* b200_compile_to_plan(const char* code, size_t code_size, const b200_
         os << "]\n";
       } else if (st.kind == Step::MEMCPY) {
         os << "  memcpy bytes=" << st.bytes << " args=[" << st.args[0] << "," << st.args[1] << "]\n";
+      } else if (st.kind == Step::SCATTER && st.iparams.size() > 5 && st.iparams[5] == 1) {
+        // the general scatter between its generated key kernel and (for update computations of their own) its generated
+        // apply kernel: sorts the (destination, update) pairs in the scratch and, for a built-in computation, applies them
+        os << "  scatter_elems numel=" << st.iparams[0] << " updates=" << st.iparams[2] << " computation=" << st.iparams[4] << " bytes=" << st.bytes
+           << " args=[";
+        for (size_t k = 0; k < st.args.size(); k++) os << (k ? "," : "") << st.args[k];
+        os << "]\n";
       } else {
         os << "  other kind=" << (int)st.kind << " " << st.label << "\n";
       }

@@ -92,6 +92,35 @@ def _to_bf16_bits(a: np.ndarray) -> np.ndarray:
     return np.where(nan, np.uint16(0x7FFF), r)
 
 
+def _scatter_elems(slots, numel, updates, computation, nbytes, args):
+    """The hand-written part of a general scatter, restated: the operand becomes the result, the (destination, update)
+    pairs the generated key kernel left in the scratch are sorted by destination, ties in update order (the device
+    does it by radix passes that end in either half of the scratch: both halves get the sorted pairs here), and a
+    built-in update computation (0 assign, 1 add, 2 multiply, 3 minimum, 4 maximum) is folded into the result in that
+    order; a computation of its own (-1) is left to the generated kernel that follows."""
+    operand, _, upd, out, scratch = (slots[a] for a in args)
+    out[0][:nbytes] = operand[0][:nbytes]
+    sc = scratch[0][:scratch[0].size // 4 * 4].view(np.int32)
+    key, order = sc[:updates].copy(), sc[updates:2 * updates].copy()
+    perm = np.argsort(key, kind="stable")
+    for base in (0, 2 * updates):
+        sc[base:base + updates] = key[perm]
+        sc[base + updates:base + 2 * updates] = order[perm]
+    if computation < 0:
+        return
+    dt = out[2]
+    view = lambda s: s[0][:s[0].size // np.dtype(_NP[s[2]]).itemsize * np.dtype(_NP[s[2]]).itemsize].view(_NP[s[2]])
+    o, u = view(out), view(upd)
+    if dt == "bf16":
+        raise Unsupported("built-in scatter on bf16")
+    fold = {0: lambda a, v: v, 1: lambda a, v: a + v, 2: lambda a, v: a * v,
+            3: lambda a, v: v if (v < a or v != v) else a, 4: lambda a, v: v if (v > a or v != v) else a}[computation]
+    with np.errstate(all="ignore"):
+        for k, q in zip(key[perm], order[perm]):
+            if k < numel:
+                o[k] = fold(o[k], u[q])
+
+
 def run_plan_on_cpu(text: str, inputs: list) -> list:
     """Compiles `text`, runs the plan's kernel steps on host threads and returns the results as NumPy arrays (bf16
     results as float32)."""
@@ -107,6 +136,10 @@ def run_plan_on_cpu(text: str, inputs: list) -> list:
         m = re.match(r"^  memcpy bytes=(\d+) args=\[(\d+),(\d+)\]\s*$", line)
         if m:
             steps.append(("memcpy", int(m.group(1)), None, [int(m.group(2)), int(m.group(3))]))
+            continue
+        m = re.match(r"^  scatter_elems numel=(\d+) updates=(\d+) computation=(-?\d+) bytes=(\d+) args=\[([\d,]*)\]\s*$", line)
+        if m:
+            steps.append(("scatter", [int(m.group(k)) for k in range(1, 5)], None, [int(v) for v in m.group(5).split(",") if v]))
             continue
         raise Unsupported(line.strip()[:80])
     slots, results = {}, {}
@@ -138,6 +171,9 @@ def run_plan_on_cpu(text: str, inputs: list) -> list:
     for kind, name, dims, args in steps:
         if kind == "memcpy":
             slots[args[0]][0][:name] = slots[args[1]][0][:name]
+            continue
+        if kind == "scatter":
+            _scatter_elems(slots, *name, args)
             continue
         fn = C.cast(getattr(lib, name), C.c_void_p)
         ptrs = (C.c_void_p * len(args))(*[slots[a][0].ctypes.data for a in args])

@@ -269,3 +269,38 @@ def test_threefry_bits_are_exact():
     got, want = run_plan_on_cpu(p.text, args), interp.run_text(p.text, args)
     assert len(got) == len(want) == 1
     np.testing.assert_array_equal(got[0], want[0])
+
+
+GENERAL_SCATTERS = [
+    ((9, 7), (20, 2), (20,), dict(update_window_dims=(), inserted_window_dims=(0, 1), scatter_dims_to_operand_dims=(0, 1), index_vector_dim=1)),
+    ((9, 7), (12, 2), (12, 1, 3), dict(update_window_dims=(1, 2), inserted_window_dims=(), scatter_dims_to_operand_dims=(0, 1), index_vector_dim=1)),
+    ((6, 5, 8), (4, 10, 2), (4, 10, 5), dict(update_window_dims=(2,), inserted_window_dims=(0, 2), scatter_dims_to_operand_dims=(0, 2), index_vector_dim=2)),
+    ((4, 6, 5), (4, 7, 1), (4, 7, 5), dict(update_window_dims=(2,), inserted_window_dims=(1,), scatter_dims_to_operand_dims=(1,), index_vector_dim=2,
+                                           input_batching_dims=(0,), scatter_indices_batching_dims=(0,))),
+    ((30,), (1,), (4,), dict(update_window_dims=(0,), inserted_window_dims=(), scatter_dims_to_operand_dims=(0,), index_vector_dim=0)),
+]
+
+
+@pytest.mark.parametrize("os_,is_,us_,dn", GENERAL_SCATTERS)
+def test_general_scatter_key_and_apply_kernels(os_, is_, us_, dn):
+    """The generated halves of a general scatter: the kernel that maps every update element to its destination (point
+    updates, partial windows, batching dimensions, windows that do not fit) and, for update computations of their own,
+    the kernel that folds each run of equal destinations in update order. The radix sort between them is hand-written
+    CUDA and is restated by the harness."""
+    sdo, ivd = dn["scatter_dims_to_operand_dims"], dn["index_vector_dim"]
+    comps = is_[ivd] if ivd < len(is_) else 1
+    idx = np.zeros(is_, np.int32)
+    for k in range(comps):
+        col = rng.integers(-1, os_[sdo[k]] + 1, [n for d, n in enumerate(is_) if d != ivd] if ivd < len(is_) else is_)   # some out of range
+        if ivd < len(is_):
+            np.moveaxis(idx, ivd, -1)[..., k] = col
+        else:
+            idx[...] = col
+    for op, dt in [("add", "i32"), ("maximum", "f32"), (lambda s, a, u: s.add(s.mul(a, s.const(0.5, "f32")), u), "f32"), ("subtract", "i32")]:
+        b = Builder()
+        text = b.module([b.scatter(b.arg(os_, dt), b.arg(is_, "i32"), b.arg(us_, dt), op, **dn)])
+        if dt == "i32":
+            args = [rng.integers(-9, 9, os_).astype(np.int32), idx, rng.integers(-9, 9, us_).astype(np.int32)]
+        else:
+            args = [f32(*os_), idx, f32(*us_)]
+        _check(text, args)
