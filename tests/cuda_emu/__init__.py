@@ -70,7 +70,7 @@ def _build(src: str) -> C.CDLL:
     if not so.exists():
         cu = cache / f"k{key}.cc"
         cu.write_text(host)
-        cmd = ["g++", "-std=c++20", "-O1", "-g0", "-w", "-fPIC", "-shared", "-pthread", f"-I{HERE}", str(cu), str(HERE / "runner.cc"),
+        cmd = ["g++", "-std=c++20", "-O0", "-g0", "-w", "-fPIC", "-shared", "-pthread", f"-I{HERE}", str(cu), str(HERE / "runner.cc"),
                "-o", str(so) + ".tmp"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
