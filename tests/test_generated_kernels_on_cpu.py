@@ -5,8 +5,13 @@ the generated code itself, not only its plan, to the oracle without a GPU: index
 block reductions, the row chains, window operations, the merge sort, Philox, the factorizations and the split-position
 attention kernel with its last-block combine. Hand-written kernels (contractions, transposes, the built-in scatter)
 are outside its reach and stay with the GPU tests."""
+import shutil
+
 import numpy as np
 import pytest
+
+if shutil.which("g++") is None:
+    pytest.skip("needs g++ to build the generated kernels for the host", allow_module_level=True)
 
 from b200.shlo import programs
 from b200.shlo.builder import Builder
