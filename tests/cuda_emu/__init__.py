@@ -61,22 +61,41 @@ def _host_source(src: str) -> str:
     return '#include "shim.h"\n' + text[:at] + _HOST_CONVERSIONS + text[at:]
 
 
-def _build(src: str) -> C.CDLL:
-    host = _host_source(src)
-    key = hashlib.sha256((host + (HERE / "shim.h").read_text() + (HERE / "runner.cc").read_text()).encode()).hexdigest()[:24]
-    cache = Path(tempfile.gettempdir()) / "b200_cuda_emu"
-    cache.mkdir(exist_ok=True)
-    so = cache / f"k{key}.so"
+def _cache_dir() -> Path:
+    d = Path(tempfile.gettempdir()) / "b200_cuda_emu"
+    d.mkdir(exist_ok=True)
+    return d
+
+
+def _compile(cmd, what):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"g++ failed on {what}:\n" + r.stderr[:6000])
+
+
+def _runner() -> Path:
+    """The thread team and its barriers, built once."""
+    key = hashlib.sha256(((HERE / "shim.h").read_text() + (HERE / "runner.cc").read_text()).encode()).hexdigest()[:24]
+    so = _cache_dir() / f"libemu_runner_{key}.so"
     if not so.exists():
-        cu = cache / f"k{key}.cc"
-        cu.write_text(host)
-        cmd = ["g++", "-std=c++20", "-O0", "-g0", "-w", "-fPIC", "-shared", "-pthread", f"-I{HERE}", str(cu), str(HERE / "runner.cc"),
-               "-o", str(so) + ".tmp"]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError("g++ failed on the generated source:\n" + r.stderr[:6000])
+        _compile(["g++", "-std=c++17", "-O1", "-g0", "-w", "-fPIC", "-shared", "-pthread", f"-I{HERE}", str(HERE / "runner.cc"), "-o", str(so) + ".tmp"],
+                 "the runner")
         os.replace(str(so) + ".tmp", so)
-    return C.CDLL(str(so))
+    return so
+
+
+def _build(src: str):
+    runner = _runner()
+    host = _host_source(src)
+    key = hashlib.sha256((host + runner.name).encode()).hexdigest()[:24]
+    so = _cache_dir() / f"k{key}.so"
+    if not so.exists():
+        cu = _cache_dir() / f"k{key}.cc"
+        cu.write_text(host)
+        _compile(["g++", "-std=c++17", "-O0", "-g0", "-w", "-fPIC", "-shared", f"-I{HERE}", str(cu), str(runner), f"-Wl,-rpath,{runner.parent}",
+                  "-o", str(so) + ".tmp"], "the generated source")
+        os.replace(str(so) + ".tmp", so)
+    return C.CDLL(str(runner), mode=C.RTLD_GLOBAL), C.CDLL(str(so))
 
 
 def _aligned(nbytes: int) -> np.ndarray:
@@ -165,9 +184,9 @@ def run_plan_on_cpu(text: str, inputs: list) -> list:
         m = re.match(r"^  result (\d+) slot=(\d+)$", line)
         if m:
             results[int(m.group(1))] = int(m.group(2))
-    lib = _build(src)
-    lib.emu_launch.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
-    lib.emu_launch.restype = None
+    runner, lib = _build(src)
+    runner.emu_launch.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
+    runner.emu_launch.restype = None
     for kind, name, dims, args in steps:
         if kind == "memcpy":
             slots[args[0]][0][:name] = slots[args[1]][0][:name]
@@ -177,7 +196,7 @@ def run_plan_on_cpu(text: str, inputs: list) -> list:
             continue
         fn = C.cast(getattr(lib, name), C.c_void_p)
         ptrs = (C.c_void_p * len(args))(*[slots[a][0].ctypes.data for a in args])
-        lib.emu_launch(fn, len(args), ptrs, *dims)
+        runner.emu_launch(fn, len(args), ptrs, *dims)
     outs = []
     for k in sorted(results):
         buf, shape, dt = slots[results[k]]

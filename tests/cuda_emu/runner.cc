@@ -1,12 +1,64 @@
 // Launches one generated kernel on host threads (see shim.h).
+#include <algorithm>
+#include <condition_variable>
+#include <mutex>
+#include <thread>
+#include <vector>
+
 #include "shim.h"
 
 namespace emu {
-thread_local Dim t_thread, t_block;
+namespace {
+struct Barrier {
+  std::mutex m;
+  std::condition_variable cv;
+  int expected = 0, waiting = 0;
+  unsigned gen = 0;
+  void reset(int n) { expected = n; waiting = 0; }
+  void wait() {
+    std::unique_lock<std::mutex> l(m);
+    const unsigned g = gen;
+    if (++waiting >= expected) { waiting = 0; gen++; cv.notify_all(); }
+    else cv.wait(l, [&] { return gen != g; });
+  }
+  void drop() {                       // a thread that has returned no longer takes part
+    std::unique_lock<std::mutex> l(m);
+    expected--;
+    if (expected > 0 && waiting >= expected) { waiting = 0; gen++; cv.notify_all(); }
+  }
+};
+struct Warp {
+  Barrier bar;
+  unsigned long long buf[32];
+  int lanes = 32;
+};
 thread_local Warp* t_warp = nullptr;
+Barrier g_block_bar;
+}  // namespace
+thread_local Dim t_thread, t_block;
 thread_local int t_lane = 0;
 Dim g_block_dim, g_grid_dim;
-Barrier g_block_bar;
+
+void block_barrier() { g_block_bar.wait(); }
+void warp_barrier() { t_warp->bar.wait(); }
+int warp_lanes() { return t_warp->lanes; }
+unsigned long long warp_exchange(unsigned long long value, int src) {
+  Warp& w = *t_warp;
+  w.buf[t_lane] = value;
+  w.bar.wait();
+  const unsigned long long got = w.buf[(src >= 0 && src < w.lanes) ? src : t_lane];
+  w.bar.wait();
+  return got;
+}
+unsigned warp_ballot(int pred) {
+  Warp& w = *t_warp;
+  w.buf[t_lane] = pred ? 1ull : 0ull;
+  w.bar.wait();
+  unsigned r = 0;
+  for (int l = 0; l < w.lanes; l++) r |= (unsigned)(w.buf[l] & 1ull) << l;
+  w.bar.wait();
+  return r;
+}
 }  // namespace emu
 
 namespace {

@@ -2,18 +2,13 @@
 // thread per CUDA thread of a block, blocks one after the other. Block and warp barriers let a thread that has
 // returned drop out, as exited CUDA threads do. Test infrastructure: nothing in the product includes this file.
 #pragma once
-#include <algorithm>
 #include <cmath>
-#include <condition_variable>
 #include <cstdint>
 #include <cstring>
-#include <mutex>
-#include <thread>
-#include <vector>
 
 using std::isfinite;
-using std::max;
-using std::min;
+template <typename T> static inline T max(T a, T b) { return a < b ? b : a; }
+template <typename T> static inline T min(T a, T b) { return b < a ? b : a; }
 using std::isnan;
 using std::isinf;
 using std::signbit;
@@ -37,34 +32,15 @@ static inline float4 make_float4(float x, float y, float z, float w) { return {x
 
 namespace emu {
 struct Dim { unsigned x = 1, y = 1, z = 1; };
-struct Barrier {
-  std::mutex m;
-  std::condition_variable cv;
-  int expected = 0, waiting = 0;
-  unsigned gen = 0;
-  void reset(int n) { expected = n; waiting = 0; }
-  void wait() {
-    std::unique_lock<std::mutex> l(m);
-    const unsigned g = gen;
-    if (++waiting >= expected) { waiting = 0; gen++; cv.notify_all(); }
-    else cv.wait(l, [&] { return gen != g; });
-  }
-  void drop() {
-    std::unique_lock<std::mutex> l(m);
-    expected--;
-    if (expected > 0 && waiting >= expected) { waiting = 0; gen++; cv.notify_all(); }
-  }
-};
-struct Warp {
-  Barrier bar;
-  unsigned long long buf[32];
-  int lanes = 32;
-};
 extern thread_local Dim t_thread, t_block;
-extern thread_local Warp* t_warp;
 extern thread_local int t_lane;
 extern Dim g_block_dim, g_grid_dim;
-extern Barrier g_block_bar;
+// implemented by the runner (runner.cc), which owns the threads and their barriers
+void block_barrier();
+void warp_barrier();
+unsigned long long warp_exchange(unsigned long long value, int source_lane);     // value of source_lane, own value if out of range
+unsigned warp_ballot(int pred);
+int warp_lanes();
 }  // namespace emu
 
 #define threadIdx emu::t_thread
@@ -72,20 +48,16 @@ extern Barrier g_block_bar;
 #define blockDim emu::g_block_dim
 #define gridDim emu::g_grid_dim
 
-static inline void __syncthreads() { emu::g_block_bar.wait(); }
-static inline void __syncwarp(unsigned = 0xFFFFFFFFu) { emu::t_warp->bar.wait(); }
+static inline void __syncthreads() { emu::block_barrier(); }
+static inline void __syncwarp(unsigned = 0xFFFFFFFFu) { emu::warp_barrier(); }
 static inline void __threadfence() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
 static inline void __threadfence_block() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
 
 template <typename T>
 static inline T emu_exchange(T v, int src) {
-  emu::Warp& w = *emu::t_warp;
   unsigned long long raw = 0;
   std::memcpy(&raw, &v, sizeof(T));
-  w.buf[emu::t_lane] = raw;
-  w.bar.wait();
-  const unsigned long long got = w.buf[(src >= 0 && src < w.lanes) ? src : emu::t_lane];
-  w.bar.wait();
+  const unsigned long long got = emu::warp_exchange(raw, src);
   T r;
   std::memcpy(&r, &got, sizeof(T));
   return r;
@@ -94,16 +66,8 @@ template <typename T> static inline T __shfl_sync(unsigned, T v, int src) { retu
 template <typename T> static inline T __shfl_xor_sync(unsigned, T v, int m) { return emu_exchange(v, emu::t_lane ^ m); }
 template <typename T> static inline T __shfl_down_sync(unsigned, T v, unsigned d) { return emu_exchange(v, emu::t_lane + (int)d < 32 ? emu::t_lane + (int)d : emu::t_lane); }
 template <typename T> static inline T __shfl_up_sync(unsigned, T v, unsigned d) { return emu_exchange(v, emu::t_lane - (int)d >= 0 ? emu::t_lane - (int)d : emu::t_lane); }
-static inline unsigned __ballot_sync(unsigned, int pred) {
-  emu::Warp& w = *emu::t_warp;
-  w.buf[emu::t_lane] = pred ? 1ull : 0ull;
-  w.bar.wait();
-  unsigned r = 0;
-  for (int l = 0; l < w.lanes; l++) r |= (unsigned)(w.buf[l] & 1ull) << l;
-  w.bar.wait();
-  return r;
-}
-static inline int __all_sync(unsigned m, int pred) { return __ballot_sync(m, pred) == (emu::t_warp->lanes == 32 ? 0xFFFFFFFFu : ((1u << emu::t_warp->lanes) - 1u)); }
+static inline unsigned __ballot_sync(unsigned, int pred) { return emu::warp_ballot(pred); }
+static inline int __all_sync(unsigned m, int pred) { return __ballot_sync(m, pred) == (emu::warp_lanes() == 32 ? 0xFFFFFFFFu : ((1u << emu::warp_lanes()) - 1u)); }
 static inline int __any_sync(unsigned m, int pred) { return __ballot_sync(m, pred) != 0; }
 
 static inline float __uint_as_float(unsigned u) { float f; std::memcpy(&f, &u, 4); return f; }
