@@ -1574,7 +1574,7 @@ b200_error* b200_compile_to_plan(const char* code, size_t code_size, const b200_
       }
       os << "\n";
     }
-    for (size_t k = 0; k < prog->results.size(); k++) os << "  result " << k << " slot=" << prog->results[k].slot << "\n";
+    for (size_t k = 0; k < prog->results.size(); k++) os << "  result " << k << " slot=" << prog->results[k].slot << " " << prog->results[k].type.str() << "\n";
     // the top-level steps with every argument (the plan text above abbreviates long argument lists)
     os << "launches:\n";
     for (const Step& st : prog->main.steps) {

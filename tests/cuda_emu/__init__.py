@@ -181,9 +181,9 @@ def run_plan_on_cpu(text: str, inputs: list) -> list:
                 buf[:data.size] = data
             slots[sid] = (buf, shape, dt)
             continue
-        m = re.match(r"^  result (\d+) slot=(\d+)$", line)
-        if m:
-            results[int(m.group(1))] = int(m.group(2))
+        m = re.match(r"^  result (\d+) slot=(\d+) tensor<((?:\d+x)*)(\w+)>$", line)
+        if m:                            # a result may be a reshaped view of a slot: its own type counts
+            results[int(m.group(1))] = (int(m.group(2)), tuple(int(v) for v in m.group(3).split("x") if v), m.group(4))
     runner, lib = _build(src)
     runner.emu_launch.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
     runner.emu_launch.restype = None
@@ -199,7 +199,8 @@ def run_plan_on_cpu(text: str, inputs: list) -> list:
         runner.emu_launch(fn, len(args), ptrs, *dims)
     outs = []
     for k in sorted(results):
-        buf, shape, dt = slots[results[k]]
+        sid, shape, dt = results[k]
+        buf = slots[sid][0]
         n = int(np.prod(shape, dtype=np.int64)) if shape else 1
         a = buf[:n * np.dtype(_NP[dt]).itemsize].view(_NP[dt]).reshape(shape).copy()
         if dt == "bf16":
